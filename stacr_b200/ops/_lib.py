@@ -1,0 +1,110 @@
+"""ctypes binding to the in-tree sm_100a kernel library.
+
+The library exposes a C ABI taking raw device pointers and a stream handle; the wrappers in
+this package pass ``tensor.data_ptr()`` and ``torch.cuda.current_stream().cuda_stream``.
+On a machine with a GPU a missing library is an error (no silent fallback to framework
+ops); on a CPU-only machine the pure-PyTorch oracle paths are used and ``available()`` is
+False.
+"""
+
+from __future__ import annotations
+
+import ctypes
+import threading
+from pathlib import Path
+
+import torch
+
+_HERE = Path(__file__).resolve().parent
+_LIB_PATH = _HERE / "libstacr_b200.so"
+_lock = threading.Lock()
+_lib: ctypes.CDLL | None = None
+_status: dict[int, torch.Tensor] = {}
+_sms: dict[int, int] = {}
+
+STATUS_TEXT = {
+    0: "ok",
+    11: "timeout waiting for a free shared-memory stage (producer)",
+    12: "timeout waiting for a TMA tile to land (MMA issuer)",
+    13: "timeout waiting for the epilogue to drain the accumulator",
+    14: "timeout waiting for the accumulator to be produced (epilogue)",
+    21: "timeout waiting for a peer rank's flag",
+    31: "bad argument detected on the device",
+}
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+def lib_path() -> Path:
+    return _LIB_PATH
+
+
+def load() -> ctypes.CDLL:
+    global _lib
+    if _lib is not None:
+        return _lib
+    with _lock:
+        if _lib is None:
+            if not _LIB_PATH.exists():
+                from .build import ensure_built
+
+                ensure_built()
+            if not _LIB_PATH.exists():
+                raise KernelError(
+                    f"{_LIB_PATH} is missing: run `python -m stacr_b200.ops.build` (needs nvcc)"
+                )
+            _lib = ctypes.CDLL(str(_LIB_PATH))
+    return _lib
+
+
+def available() -> bool:
+    """True when a CUDA device is present (the kernel path is then mandatory)."""
+    return torch.cuda.is_available()
+
+
+def use_kernels(t: torch.Tensor) -> bool:
+    return t.is_cuda
+
+
+def stream_ptr() -> ctypes.c_void_p:
+    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def status_word(device: torch.device | int | None = None) -> torch.Tensor:
+    """Per-device int32 word kernels write a non-zero code to when a bounded wait gives up."""
+    idx = torch.cuda.current_device() if device is None else torch.device(device).index
+    if idx is None:
+        idx = torch.cuda.current_device()
+    word = _status.get(idx)
+    if word is None:
+        word = torch.zeros(1, dtype=torch.int32, device=f"cuda:{idx}")
+        _status[idx] = word
+    return word
+
+
+def check_status(device=None, *, reset: bool = True) -> None:
+    """Synchronising read of the status word; raises KernelError on a recorded failure."""
+    word = status_word(device)
+    code = int(word.item())
+    if code != 0:
+        if reset:
+            word.zero_()
+        raise KernelError(f"kernel status {code}: {STATUS_TEXT.get(code, 'unknown')}")
+
+
+def sm_count(device=None) -> int:
+    idx = torch.cuda.current_device() if device is None else torch.device(device).index
+    if idx not in _sms:
+        _sms[idx] = torch.cuda.get_device_properties(idx).multi_processor_count
+    return _sms[idx]
+
+
+def ptr(t: torch.Tensor | None) -> ctypes.c_void_p:
+    return ctypes.c_void_p(0 if t is None else t.data_ptr())
+
+
+def check_rc(rc: int, what: str) -> None:
+    if rc != 0:
+        raise KernelError(f"{what} failed with code {rc}")

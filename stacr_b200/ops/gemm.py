@@ -1,0 +1,92 @@
+"""bf16 tensor-core GEMM (tcgen05/TMEM/TMA kernel in ``csrc/gemm_tc.cu``)."""
+
+from __future__ import annotations
+
+import ctypes
+
+import torch
+
+from . import _lib
+
+
+def _pick_bn(m: int, n: int, b_mn: bool, sms: int) -> int:
+    if n <= 16 and not b_mn:
+        return 16
+    if n <= 32 and not b_mn:
+        return 32
+    if n <= 64:
+        return 64
+    num_m = (m + 127) // 128
+    best, best_score = 128, -1.0
+    for bn, weight in ((256, 1.0), (128, 0.85)):
+        if bn == 256 and n <= 128:
+            continue
+        tiles = num_m * ((n + bn - 1) // bn)
+        waves = (tiles + sms - 1) // sms
+        score = weight * tiles / (waves * sms) * (n / (((n + bn - 1) // bn) * bn))
+        if score > best_score:
+            best, best_score = bn, score
+    return best
+
+
+def gemm(
+    a: torch.Tensor,
+    b: torch.Tensor,
+    *,
+    a_mn: bool = False,
+    b_mn: bool = False,
+    bias: torch.Tensor | None = None,
+    out: torch.Tensor | None = None,
+    out_dtype: torch.dtype = torch.bfloat16,
+    splits: int = 1,
+    bn: int | None = None,
+    alpha: float = 1.0,
+) -> torch.Tensor:
+    """``out[M,N] = alpha * A @ B^T (+ bias)`` with bf16 operands and fp32 accumulation.
+
+    ``a`` is ``[M,K]`` (``a_mn=False``) or ``[K,M]`` (``a_mn=True``); ``b`` is ``[N,K]``
+    (``b_mn=False``) or ``[K,N]`` (``b_mn=True``).  Rows of both must be contiguous.
+    With ``splits > 1`` (or an explicit fp32 ``out`` passed with ``splits=0`` meaning
+    "accumulate into out") partial tiles are reduced with fp32 atomics into ``out``.
+    """
+    assert a.dtype == torch.bfloat16 and b.dtype == torch.bfloat16, "operands must be bf16"
+    assert a.dim() == 2 and b.dim() == 2 and a.stride(1) == 1 and b.stride(1) == 1
+    if a_mn:
+        k, m = a.shape
+    else:
+        m, k = a.shape
+    if b_mn:
+        kb, n = b.shape
+    else:
+        n, kb = b.shape
+    assert k == kb, f"reduction mismatch {k} vs {kb}"
+    accumulate_into = out is not None and splits == 0
+    if accumulate_into:
+        splits = 1
+    atomic = splits > 1 or accumulate_into
+    if out is None:
+        dtype = torch.float32 if atomic else out_dtype
+        out = (torch.zeros if atomic else torch.empty)((m, n), dtype=dtype, device=a.device)
+    else:
+        assert out.shape == (m, n) and out.stride(1) == 1
+    if atomic:
+        assert out.dtype == torch.float32
+        mode = 2
+    else:
+        mode = {torch.bfloat16: 0, torch.float32: 1}[out.dtype]
+    if bias is not None:
+        assert bias.dtype == torch.float32 and bias.numel() == n and bias.is_contiguous()
+    sms = _lib.sm_count(a.device)
+    if bn is None:
+        bn = _pick_bn(m, n, b_mn, sms)
+    lib = _lib.load()
+    rc = lib.sb_gemm_bf16(
+        _lib.ptr(a), _lib.ptr(b), _lib.ptr(out), _lib.ptr(bias),
+        ctypes.c_int(m), ctypes.c_int(n), ctypes.c_int(k),
+        ctypes.c_int(a.stride(0)), ctypes.c_int(b.stride(0)), ctypes.c_int(out.stride(0)),
+        ctypes.c_int(int(a_mn)), ctypes.c_int(int(b_mn)), ctypes.c_int(mode), ctypes.c_int(max(1, splits)),
+        ctypes.c_int(bn), ctypes.c_float(alpha), ctypes.c_int(sms),
+        _lib.ptr(_lib.status_word(a.device)), _lib.stream_ptr(),
+    )
+    _lib.check_rc(rc, "sb_gemm_bf16")
+    return out

@@ -1,0 +1,74 @@
+"""tcgen05 GEMM kernel against an fp32 PyTorch reference of the same contraction."""
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _ref(a, b, a_mn, b_mn, bias):
+    af = a.float().t() if a_mn else a.float()
+    bf = b.float() if b_mn else b.float().t()
+    out = af @ bf
+    if bias is not None:
+        out = out + bias
+    return out
+
+
+def _check(out, ref, k):
+    err = (out.float() - ref).abs().max().item()
+    scale = ref.abs().max().item() + 1e-6
+    tol = 2e-2 if out.dtype == torch.bfloat16 else 2e-3
+    assert err / scale < tol, f"relative error {err / scale:.3e} (K={k})"
+
+
+@pytest.mark.parametrize(
+    "m,n,k",
+    [(128, 256, 64), (256, 512, 256), (384, 256, 1024), (200, 136, 72), (1024, 1024, 2048), (129, 72, 200)],
+)
+@pytest.mark.parametrize("a_mn,b_mn", [(False, False), (False, True), (True, False), (True, True)])
+def test_gemm_matches_fp32(m, n, k, a_mn, b_mn):
+    from stacr_b200.ops import _lib
+    from stacr_b200.ops.gemm import gemm
+
+    if (a_mn and m % 8) or (b_mn and n % 8) or ((not a_mn or not b_mn) and k % 8):
+        pytest.skip("leading dimension must be a multiple of 8 elements")
+    g = torch.Generator(device="cuda").manual_seed(m * 7 + n * 3 + k)
+    a = torch.randn((k, m) if a_mn else (m, k), device="cuda", generator=g).bfloat16()
+    b = torch.randn((k, n) if b_mn else (n, k), device="cuda", generator=g).bfloat16()
+    bias = torch.randn(n, device="cuda", generator=g)
+    ref = _ref(a, b, a_mn, b_mn, bias)
+    for dtype in (torch.bfloat16, torch.float32):
+        out = gemm(a, b, a_mn=a_mn, b_mn=b_mn, bias=bias, out_dtype=dtype)
+        torch.cuda.synchronize()
+        _lib.check_status()
+        _check(out, ref, k)
+
+
+@pytest.mark.parametrize("bn", [16, 32, 64, 128, 256])
+@pytest.mark.parametrize("a_mn", [False, True])
+def test_gemm_tile_widths_and_split_k(bn, a_mn):
+    from stacr_b200.ops import _lib
+    from stacr_b200.ops.gemm import gemm
+
+    m, n, k = 512, bn, 4096
+    g = torch.Generator(device="cuda").manual_seed(bn)
+    a = torch.randn((k, m) if a_mn else (m, k), device="cuda", generator=g).bfloat16()
+    b = torch.randn(n, k, device="cuda", generator=g).bfloat16()
+    ref = _ref(a, b, a_mn, False, None)
+    out = gemm(a, b, a_mn=a_mn, bn=bn, out_dtype=torch.float32)
+    out_split = gemm(a, b, a_mn=a_mn, bn=bn, splits=8)
+    torch.cuda.synchronize()
+    _lib.check_status()
+    _check(out, ref, k)
+    _check(out_split, ref, k)
+
+
+def test_gemm_repeatable_bits():
+    from stacr_b200.ops.gemm import gemm
+
+    a = torch.randn(1024, 512, device="cuda").bfloat16()
+    b = torch.randn(768, 512, device="cuda").bfloat16()
+    first = gemm(a, b)
+    for _ in range(3):
+        assert torch.equal(first, gemm(a, b))
