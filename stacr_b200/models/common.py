@@ -1,0 +1,84 @@
+"""Shared building blocks of the in-tree model zoo.
+
+The models are defined from a config (random init, no downloads) and name their submodules as
+the Hugging Face implementations do (``transformer.h.N.mlp.c_fc``,
+``gpt_neox.layers.N.mlp.dense_h_to_4h``, ``bert.encoder.layer.N.intermediate.dense``) so that
+surface classification, block discovery and checkpoints line up with what users of the
+reference expect.  Hot element-wise/normalisation ops go through ``stacr_b200.ops.nn_ops``,
+which runs the sm_100a kernels for bf16 CUDA tensors.
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Optional
+
+import torch
+from torch import nn
+from torch.nn import functional as F
+
+from ..ops import nn_ops
+
+
+@dataclass
+class ModelOutput:
+    loss: Optional[torch.Tensor] = None
+    logits: Optional[torch.Tensor] = None
+
+    def __getitem__(self, key):
+        return getattr(self, key)
+
+
+class LayerNorm(nn.LayerNorm):
+    """LayerNorm whose bf16 CUDA path is the fused kernel (fp32 statistics, bf16 in/out)."""
+
+    def forward(self, x):
+        return nn_ops.layer_norm(x, self.weight, self.bias, self.eps)
+
+
+class GELU(nn.Module):
+    def __init__(self, approximate: str = "none"):
+        super().__init__()
+        self.approximate = approximate
+
+    def forward(self, x):
+        return nn_ops.gelu(x, self.approximate)
+
+
+def causal_attention(q, k, v, *, causal: bool, attention_mask=None, dropout_p: float = 0.0, training: bool = False):
+    """Softmax attention on ``[B, H, S, D]`` tensors.
+
+    Uses the fused flash kernel of the framework runtime (no ``S x S`` score tensor).  A padding
+    mask ``[B, S]`` (1 = keep) is turned into an additive bias only when it actually masks something.
+    """
+    bias = None
+    if attention_mask is not None and not bool(attention_mask.all()):
+        keep = attention_mask[:, None, None, :].to(torch.bool)
+        if causal:
+            s = q.shape[-2]
+            keep = keep & torch.ones(s, s, dtype=torch.bool, device=q.device).tril()
+            causal = False
+        bias = keep
+    return F.scaled_dot_product_attention(q, k, v, attn_mask=bias, dropout_p=dropout_p if training else 0.0, is_causal=causal and bias is None)
+
+
+def lm_loss(logits_or_hidden, labels, lm_head: nn.Linear | None = None, chunk: int = 0):
+    """Next-token cross-entropy with the usual shift; ``labels == -100`` are ignored."""
+    if lm_head is not None:
+        hidden = logits_or_hidden[:, :-1].reshape(-1, logits_or_hidden.shape[-1])
+        target = labels[:, 1:].reshape(-1)
+        return nn_ops.linear_cross_entropy(hidden, lm_head.weight, target, chunk=chunk)
+    logits = logits_or_hidden[:, :-1].reshape(-1, logits_or_hidden.shape[-1])
+    return nn_ops.cross_entropy(logits, labels[:, 1:].reshape(-1))
+
+
+def init_weights(module: nn.Module, std: float = 0.02) -> None:
+    if isinstance(module, nn.Linear):
+        nn.init.normal_(module.weight, mean=0.0, std=std)
+        if module.bias is not None:
+            nn.init.zeros_(module.bias)
+    elif isinstance(module, nn.Embedding):
+        nn.init.normal_(module.weight, mean=0.0, std=std)
+    elif isinstance(module, nn.LayerNorm):
+        nn.init.ones_(module.weight)
+        nn.init.zeros_(module.bias)

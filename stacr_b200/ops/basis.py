@@ -1,0 +1,57 @@
+"""Basis initialisation and tracking on the kernel path.
+
+* ``oja_step_kernels``: ``Y = X Q`` (tensor-core projection), ``G = X^T Y`` (skinny MN-major
+  tensor-core product), then the fused Oja + CholeskyQR2 kernel.  Three passes over ``X`` become
+  two, with no fp32 copy of ``X`` (the reference copies ``X`` to fp32 and issues four GEMMs and a
+  QR: stacr/layers.py:350-353 there).
+* ``range_finder_basis``: randomized subspace iteration for the first basis instead of a full
+  SVD of the ``rows x features`` activation (stacr/layers.py:331-335 there), followed by a
+  Rayleigh-Ritz rotation so the columns are ordered by captured energy.
+"""
+
+from __future__ import annotations
+
+import torch
+
+from . import stacr_ops
+
+
+@torch.no_grad()
+def oja_step_kernels(basis: torch.Tensor, x: torch.Tensor, lr: float) -> torch.Tensor:
+    """One Oja update of ``basis`` ``[N, r]`` from bf16 ``x`` ``[rows, N]``; returns the fp32 basis.
+
+    The bf16 views the forward needs are attached to the returned tensor so they are not rebuilt.
+    """
+    rows, _ = x.shape
+    r = basis.shape[1]
+    x = x.contiguous()
+    views = getattr(basis, "_sb_views", None)
+    if views is None:
+        qb = basis.detach().to(torch.bfloat16).contiguous()
+        views = (qb, stacr_ops.pad_basis_transpose(qb))
+    y = stacr_ops.project(x, views[1])  # [rows, rpad] fp32
+    g = stacr_ops.at_b(x, stacr_ops.transpose_pad(y[:, :r]))  # [N, rpad] fp32
+    new_q, qb, qt = stacr_ops.oja_update(basis.detach().float(), g, y, rows, lr)
+    new_q._sb_views = (qb, qt)
+    return new_q
+
+
+@torch.no_grad()
+def range_finder_basis(x: torch.Tensor, rank: int, iters: int = 4, oversample: int = 8) -> torch.Tensor:
+    """Approximate top-``rank`` right singular subspace of bf16 ``x`` by subspace iteration."""
+    rows, n = x.shape
+    x = x.contiguous()
+    width = min(32, rank + oversample, n)
+    gen = torch.Generator(device="cpu").manual_seed(0)
+    q = torch.linalg.qr(torch.randn(n, width, generator=gen).to(x.device)).Q
+    for _ in range(iters):
+        qt = stacr_ops.pad_basis_transpose(q.to(torch.bfloat16).contiguous())
+        y = stacr_ops.project(x, qt)[:, :width]
+        g = stacr_ops.at_b(x, stacr_ops.transpose_pad(y))[:, :width]
+        q = torch.linalg.qr(g).Q
+    qt = stacr_ops.pad_basis_transpose(q.to(torch.bfloat16).contiguous())
+    y = stacr_ops.project(x, qt)[:, :width]
+    evals, evecs = torch.linalg.eigh((y.t() @ y).double())
+    order = torch.argsort(evals, descending=True)[:rank]
+    rotated = q.double() @ evecs[:, order]
+    return torch.linalg.qr(rotated.float()).Q.contiguous()

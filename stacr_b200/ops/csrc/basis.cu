@@ -1,0 +1,168 @@
+// Basis maintenance on the device: the Oja subspace step followed by CholeskyQR2, in one
+// single-CTA kernel (the operands are N x r with r <= 32, a few hundred KB at most).
+//
+//   A = Q + lr * (G / n - Q * (S / n)),   G = X^T Y (from the skinny tensor-core GEMM),
+//                                         S = Y^T Y (reduced here from Y),
+//   Q' = A R^-1 with R^T R = A^T A, applied twice.
+//
+// A is a small perturbation of an orthonormal matrix, so its Gram matrix is close to the
+// identity and CholeskyQR2 reaches fp32 orthogonality; the subspace equals the one a
+// Householder QR returns (column signs may differ, which cancels in C Q^T).
+// Outputs: the fp32 basis, a bf16 copy [N, r] and a zero-padded bf16 transpose [rpad, N]
+// that the projection GEMM reads as its K-major B operand.
+// Replaces four library GEMMs and a cuSOLVER QR per step (stacr/layers.py:350-353 and
+// stacr/oja.py:8-11 of the reference project).
+#include "common.cuh"
+
+namespace sb {
+
+constexpr int RMAX = 32;
+
+// gram[i][j] = sum_rows f(a[row, i]) * f(a[row, j]) over `count` rows of an [count, lda] matrix, where
+// f rounds to bf16 when `round_bf16` is set (so that the same rounded values are used as in the
+// tensor-core product they are compared with).  Row i of the Gram matrix is reduced per pass:
+// per-thread partial sums -> warp shuffles -> one shared-memory partial per warp.
+template <int RP>
+__device__ void block_gram(const float* a, int count, int lda, int r, bool round_bf16, float* gram, float* partial /*[32][RP]*/) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+  for (int i = 0; i < r; ++i) {
+    float acc[RP];
+#pragma unroll
+    for (int j = 0; j < RP; ++j) acc[j] = 0.f;
+    for (int row = threadIdx.x; row < count; row += blockDim.x) {
+      const float* ar = a + static_cast<size_t>(row) * lda;
+      float ai = ar[i];
+      if (round_bf16) ai = __bfloat162float(__float2bfloat16_rn(ai));
+#pragma unroll
+      for (int j = 0; j < RP; ++j) {
+        if (j <= i) {
+          float aj = ar[j];
+          if (round_bf16) aj = __bfloat162float(__float2bfloat16_rn(aj));
+          acc[j] = fmaf(ai, aj, acc[j]);
+        }
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < RP; ++j) {
+      if (j <= i) {
+        float v = acc[j];
+        for (int off = 16; off; off >>= 1) v += __shfl_xor_sync(0xffffffffu, v, off);
+        if (lane == 0) partial[warp * RP + j] = v;
+      }
+    }
+    __syncthreads();
+    if (threadIdx.x <= i) {
+      float total = 0.f;
+      for (int w = 0; w < nwarps; ++w) total += partial[w * RP + threadIdx.x];
+      gram[i * RMAX + threadIdx.x] = total;
+      gram[threadIdx.x * RMAX + i] = total;
+    }
+    __syncthreads();
+  }
+}
+
+// In-place upper Cholesky factor R (R^T R = G) and its inverse, by thread 0.  Returns false in
+// shared flag when a pivot is not positive.
+__device__ void chol_and_invert(float* g, float* rinv, int r, int* ok) {
+  if (threadIdx.x == 0) {
+    *ok = 1;
+    // g <- R (upper), row by row
+    for (int i = 0; i < r; ++i) {
+      float d = g[i * RMAX + i];
+      for (int k = 0; k < i; ++k) d -= g[k * RMAX + i] * g[k * RMAX + i];
+      if (!(d > 1e-20f)) {
+        *ok = 0;
+        d = 1.f;
+      }
+      const float rii = sqrtf(d);
+      g[i * RMAX + i] = rii;
+      for (int j = i + 1; j < r; ++j) {
+        float v = g[i * RMAX + j];
+        for (int k = 0; k < i; ++k) v -= g[k * RMAX + i] * g[k * RMAX + j];
+        g[i * RMAX + j] = v / rii;
+      }
+      for (int j = 0; j < i; ++j) g[i * RMAX + j] = 0.f;
+    }
+    // rinv <- R^-1 (upper) by back substitution
+    for (int j = 0; j < r; ++j) {
+      for (int i = 0; i < r; ++i) rinv[i * RMAX + j] = 0.f;
+      rinv[j * RMAX + j] = 1.f / g[j * RMAX + j];
+      for (int i = j - 1; i >= 0; --i) {
+        float v = 0.f;
+        for (int k = i + 1; k <= j; ++k) v += g[i * RMAX + k] * rinv[k * RMAX + j];
+        rinv[i * RMAX + j] = -v / g[i * RMAX + i];
+      }
+    }
+  }
+  __syncthreads();
+}
+
+template <int RP>
+__global__ void __launch_bounds__(1024) oja_update_kernel(const float* q_in, const float* g, int ldg, const float* y, int ldy,
+                                                          int rows, int n, int r, float lr, float* q_out,
+                                                          __nv_bfloat16* q_bf16, __nv_bfloat16* qt_bf16, int rpad, int* status) {
+  __shared__ float s_mat[RMAX * RMAX];
+  __shared__ float s_inv[RMAX * RMAX];
+  __shared__ float scratch[32 * RP];
+  __shared__ int s_ok;
+  const float inv_n = 1.f / fmaxf(1.f, static_cast<float>(rows));
+  if (lr != 0.f && g != nullptr) {
+    block_gram<RP>(y, rows, ldy, r, true, s_mat, scratch);  // S = Y^T Y
+    for (int row = threadIdx.x; row < n; row += blockDim.x) {
+      float qrow[RP];
+      for (int j = 0; j < r; ++j) qrow[j] = q_in[static_cast<size_t>(row) * r + j];
+      for (int j = 0; j < r; ++j) {
+        float qs = 0.f;
+        for (int k = 0; k < r; ++k) qs = fmaf(qrow[k], s_mat[k * RMAX + j], qs);
+        q_out[static_cast<size_t>(row) * r + j] = qrow[j] + lr * inv_n * (g[static_cast<size_t>(row) * ldg + j] - qs);
+      }
+    }
+  } else {
+    for (int i = threadIdx.x; i < n * r; i += blockDim.x) q_out[i] = q_in[i];
+  }
+  __syncthreads();
+  for (int pass = 0; pass < 2; ++pass) {
+    block_gram<RP>(q_out, n, r, r, false, s_mat, scratch);
+    chol_and_invert(s_mat, s_inv, r, &s_ok);
+    if (!s_ok) {
+      if (threadIdx.x == 0 && status) atomicCAS(status, 0, ST_BAD_ARGUMENT);
+      break;
+    }
+    for (int row = threadIdx.x; row < n; row += blockDim.x) {
+      float a[RP];
+      for (int j = 0; j < r; ++j) a[j] = q_out[static_cast<size_t>(row) * r + j];
+      for (int j = 0; j < r; ++j) {
+        float v = 0.f;
+        for (int k = 0; k <= j; ++k) v = fmaf(a[k], s_inv[k * RMAX + j], v);
+        q_out[static_cast<size_t>(row) * r + j] = v;
+      }
+    }
+    __syncthreads();
+  }
+  for (int i = threadIdx.x; i < n * r; i += blockDim.x) {
+    const float v = q_out[i];
+    if (q_bf16) q_bf16[i] = __float2bfloat16_rn(v);
+  }
+  if (qt_bf16) {
+    for (int i = threadIdx.x; i < n * rpad; i += blockDim.x) {
+      const int j = i / n, row = i - j * n;
+      qt_bf16[i] = (j < r) ? __float2bfloat16_rn(q_out[static_cast<size_t>(row) * r + j]) : __float2bfloat16_rn(0.f);
+    }
+  }
+}
+
+}  // namespace sb
+
+// Q' = orth(Q + lr (G/rows - Q (Y^T Y)/rows)).  g: [n, ldg] fp32; y: [rows, ldy] fp32 (both may be NULL
+// with lr == 0 to only re-orthonormalise and refresh the bf16 copies).  q_out must not alias q_in.
+extern "C" int sb_oja_update(const float* q_in, const float* g, int ldg, const float* y, int ldy, int rows, int n, int r,
+                             float lr, float* q_out, void* q_bf16, void* qt_bf16, int rpad, int* status, void* stream) {
+  if (r < 1 || r > sb::RMAX) return -2;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  __nv_bfloat16* qb = static_cast<__nv_bfloat16*>(q_bf16);
+  __nv_bfloat16* qt = static_cast<__nv_bfloat16*>(qt_bf16);
+  if (r <= 8) sb::oja_update_kernel<8><<<1, 1024, 0, st>>>(q_in, g, ldg, y, ldy, rows, n, r, lr, q_out, qb, qt, rpad, status);
+  else if (r <= 16) sb::oja_update_kernel<16><<<1, 1024, 0, st>>>(q_in, g, ldg, y, ldy, rows, n, r, lr, q_out, qb, qt, rpad, status);
+  else sb::oja_update_kernel<32><<<1, 1024, 0, st>>>(q_in, g, ldg, y, ldy, rows, n, r, lr, q_out, qb, qt, rpad, status);
+  return static_cast<int>(cudaGetLastError());
+}

@@ -1,0 +1,482 @@
+// Residual selection for the compressed linear layer.
+//
+// The residual E = X - C Q^T is never stored: every pass recomputes it from the bf16 input
+// tile, the rank-r coefficients and the basis (r FMAs per element), which is cheaper than a
+// round trip through HBM.  Exact top-k by magnitude is done as a radix select on the 15-bit
+// bf16 magnitude of E:
+//   pass 1  histogram of magnitudes (32768 bins, privatised in shared memory, one global
+//           histogram per row chunk);
+//   scan    per chunk, walk the histogram from the top to find the threshold bin and how many
+//           entries of that bin are still needed (ties inside a bin are equal bf16 values, so
+//           any subset is an exact top-k);
+//   pass 2  recompute E, keep entries above the threshold (plus the needed ties), quantise
+//           with the per-tensor scale amax/qmax known from the histogram, and append
+//           (flat index, value) through a shared-memory staging buffer so that global
+//           appends are one atomic per flush, not one per element.
+// Replaces the chunked subtract + abs + torch.topk + cat + topk pipeline of the reference
+// (stacr/layers.py:16-102 there) and its separate quantisation pass (stacr/quant.py:49-65).
+#include "common.cuh"
+
+namespace sb {
+
+constexpr int NBINS = 32768;
+constexpr int ROWS_UNROLL = 4;  // rows in flight per thread (memory-level parallelism)
+
+struct SelectParams {
+  const __nv_bfloat16* x;   // [rows, n], leading dimension ldx
+  const __nv_bfloat16* c;   // [rows, r] contiguous
+  const __nv_bfloat16* q;   // [n, r] contiguous
+  int rows, n, r, ldx;
+  int chunk_rows;           // rows per selection chunk (== rows for a single global selection)
+  int parts;                // CTAs per chunk
+  unsigned int* hist;       // [nchunks, NBINS]
+  // scan outputs / compaction inputs, one per chunk
+  int* thr_bin;             // threshold bin
+  int* thr_need;            // entries of the threshold bin still needed
+  int* max_bin;             // largest non-empty bin
+  int* tie_count;           // running count of accepted ties
+  int* out_count;           // running count of appended entries
+  const int* out_offset;    // first output slot of each chunk
+  const int* quota;         // entries wanted per chunk
+  int nchunks;
+  int bits;                 // 0: bf16 values, 8: int8 values (int4 is packed from int8 afterwards)
+  long long* out_idx64;     // flat indices (one of the two is used)
+  int* out_idx32;
+  void* out_val;            // bf16 or int8
+  float* out_scale;         // scalar, written by the scan kernel
+  int* status;
+};
+
+__device__ __forceinline__ float bf16_bits_to_float(unsigned short b) {
+  return __uint_as_float(static_cast<uint32_t>(b) << 16);
+}
+
+// Raw bf16 loads of CPT consecutive columns (vectorised when the whole group is in range;
+// the launcher guarantees 16-byte aligned rows) and of one coefficient row.
+template <int CPT>
+struct XVec { unsigned short v[CPT]; };
+
+template <int CPT>
+__device__ __forceinline__ XVec<CPT> load_x(const __nv_bfloat16* xrow, int col, int n) {
+  XVec<CPT> out;
+  if (col + CPT <= n) {
+    if constexpr (CPT == 8) {
+      *reinterpret_cast<uint4*>(out.v) = __ldg(reinterpret_cast<const uint4*>(xrow + col));
+    } else if constexpr (CPT == 4) {
+      *reinterpret_cast<uint2*>(out.v) = __ldg(reinterpret_cast<const uint2*>(xrow + col));
+    } else {
+      *reinterpret_cast<uint32_t*>(out.v) = __ldg(reinterpret_cast<const uint32_t*>(xrow + col));
+    }
+  } else {
+#pragma unroll
+    for (int i = 0; i < CPT; ++i) out.v[i] = (col + i < n) ? __bfloat16_as_ushort(xrow[col + i]) : 0;
+  }
+  return out;
+}
+
+template <int RP>
+struct CVec { unsigned short v[RP]; };
+
+template <int RP>
+__device__ __forceinline__ CVec<RP> load_c(const __nv_bfloat16* crow, int r) {
+  CVec<RP> out;
+  if (r == RP) {  // rows are RP*2 bytes: 16-byte aligned for RP >= 8
+#pragma unroll
+    for (int j = 0; j < RP / 8; ++j)
+      reinterpret_cast<uint4*>(out.v)[j] = __ldg(reinterpret_cast<const uint4*>(crow) + j);
+  } else {
+#pragma unroll
+    for (int j = 0; j < RP; ++j) out.v[j] = (j < r) ? __bfloat16_as_ushort(crow[j]) : 0;
+  }
+  return out;
+}
+
+// Residual of CPT consecutive columns of one row, using register-resident basis rows.
+template <int RP, int CPT>
+__device__ __forceinline__ void residual_row(const XVec<CPT>& xv, const CVec<RP>& cv,
+                                             const float (&qreg)[CPT][RP], float (&e)[CPT]) {
+  float cf[RP];
+#pragma unroll
+  for (int j = 0; j < RP; ++j) cf[j] = bf16_bits_to_float(cv.v[j]);
+#pragma unroll
+  for (int i = 0; i < CPT; ++i) {
+    float acc = 0.f;
+#pragma unroll
+    for (int j = 0; j < RP; ++j) acc = fmaf(cf[j], qreg[i][j], acc);
+    e[i] = bf16_bits_to_float(xv.v[i]) - acc;
+  }
+}
+
+template <int RP, int CPT>
+__device__ __forceinline__ void load_q(const __nv_bfloat16* q, int r, int col, int n, float (&qreg)[CPT][RP]) {
+#pragma unroll
+  for (int i = 0; i < CPT; ++i)
+#pragma unroll
+    for (int j = 0; j < RP; ++j)
+      qreg[i][j] = (col + i < n && j < r) ? __bfloat162float(q[static_cast<size_t>(col + i) * r + j]) : 0.f;
+}
+
+// Work split shared by both passes: blockIdx.x = chunk * parts + part; a CTA walks its row
+// slab with `rl` row lanes and `ctn` column threads (ctn * CPT covers a column block).
+struct Slab {
+  int chunk, row0, row1;
+};
+__device__ __forceinline__ Slab slab_of(const SelectParams& p) {
+  Slab s;
+  s.chunk = blockIdx.x / p.parts;
+  const int part = blockIdx.x - s.chunk * p.parts;
+  const int c0 = s.chunk * p.chunk_rows;
+  const int c1 = min(p.rows, c0 + p.chunk_rows);
+  const int len = c1 - c0;
+  s.row0 = c0 + static_cast<int>((static_cast<long long>(len) * part) / p.parts);
+  s.row1 = c0 + static_cast<int>((static_cast<long long>(len) * (part + 1)) / p.parts);
+  return s;
+}
+
+template <int RP>
+__global__ void __launch_bounds__(512, 1) residual_hist_kernel(const SelectParams p, int ctn, int rl) {
+  constexpr int CPT = 64 / RP;
+  extern __shared__ unsigned int sh_hist[];
+  for (int b = threadIdx.x; b < NBINS; b += blockDim.x) sh_hist[b] = 0;
+  __syncthreads();
+  const Slab s = slab_of(p);
+  const int ct = threadIdx.x % ctn, lane_row = threadIdx.x / ctn;
+  for (int cb = 0; cb < p.n; cb += ctn * CPT) {
+    const int col = cb + ct * CPT;
+    if (col >= p.n || lane_row >= rl) continue;
+    float qreg[CPT][RP];
+    load_q<RP, CPT>(p.q, p.r, col, p.n, qreg);
+    for (int row = s.row0 + lane_row; row < s.row1; row += rl * ROWS_UNROLL) {
+      XVec<CPT> xv[ROWS_UNROLL];
+      CVec<RP> cv[ROWS_UNROLL];
+#pragma unroll
+      for (int u = 0; u < ROWS_UNROLL; ++u) {  // issue every load of the group before any use
+        const int rr = row + u * rl;
+        if (rr < s.row1) {
+          xv[u] = load_x<CPT>(p.x + static_cast<size_t>(rr) * p.ldx, col, p.n);
+          cv[u] = load_c<RP>(p.c + static_cast<size_t>(rr) * p.r, p.r);
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < ROWS_UNROLL; ++u) {
+        if (row + u * rl >= s.row1) continue;
+        float e[CPT];
+        residual_row<RP, CPT>(xv[u], cv[u], qreg, e);
+#pragma unroll
+        for (int i = 0; i < CPT; ++i) {
+          if (col + i < p.n) {
+            unsigned short key = __bfloat16_as_ushort(__float2bfloat16_rn(e[i])) & 0x7FFF;
+            atomicAdd(&sh_hist[key], 1u);
+          }
+        }
+      }
+    }
+  }
+  __syncthreads();
+  unsigned int* gh = p.hist + static_cast<size_t>(s.chunk) * NBINS;
+  for (int b = threadIdx.x; b < NBINS; b += blockDim.x) {
+    unsigned int v = sh_hist[b];
+    if (v) atomicAdd(&gh[b], v);
+  }
+}
+
+// One CTA per chunk: suffix scan over the histogram.
+__global__ void __launch_bounds__(1024) residual_scan_kernel(const SelectParams p) {
+  __shared__ unsigned int part[1024];
+  __shared__ int s_maxbin;
+  const int chunk = blockIdx.x;
+  const unsigned int* gh = p.hist + static_cast<size_t>(chunk) * NBINS;
+  const int t = threadIdx.x;
+  constexpr int PER = NBINS / 1024;  // 32 bins per thread; thread t owns bins [t*PER, (t+1)*PER)
+  unsigned int local[PER];
+  unsigned int sum = 0;
+  int my_max = -1;
+#pragma unroll
+  for (int i = 0; i < PER; ++i) {
+    local[i] = gh[t * PER + i];
+    sum += local[i];
+    if (local[i]) my_max = t * PER + i;
+  }
+  part[t] = sum;
+  if (t == 0) s_maxbin = 0;
+  __syncthreads();
+  if (my_max >= 0) atomicMax(&s_maxbin, my_max);
+  // suffix sums over threads (inclusive): suf[t] = sum_{u >= t} part[u]
+  for (int off = 1; off < 1024; off <<= 1) {
+    unsigned int add = (t + off < 1024) ? part[t + off] : 0u;
+    __syncthreads();
+    part[t] += add;
+    __syncthreads();
+  }
+  const unsigned int k = static_cast<unsigned int>(p.quota[chunk]);
+  const unsigned int above = (t + 1 < 1024) ? part[t + 1] : 0u;  // entries in bins owned by higher threads
+  const unsigned int incl = part[t];
+  if (k > 0 && above < k && incl >= k) {
+    // the threshold bin is among this thread's bins; walk from its top bin down
+    unsigned int run = above;
+    for (int i = PER - 1; i >= 0; --i) {
+      if (run + local[i] >= k) {
+        p.thr_bin[chunk] = t * PER + i;
+        p.thr_need[chunk] = static_cast<int>(k - run);
+        break;
+      }
+      run += local[i];
+    }
+  }
+  if (t == 0) {
+    if (k == 0 || part[0] < k) {  // nothing wanted, or fewer entries than wanted: take everything
+      p.thr_bin[chunk] = (k == 0) ? NBINS : -1;
+      p.thr_need[chunk] = 0;
+    }
+    p.tie_count[chunk] = 0;
+    p.out_count[chunk] = 0;
+  }
+  __syncthreads();
+  if (t == 0) p.max_bin[chunk] = s_maxbin;
+}
+
+// Per-tensor scale from the largest magnitude over all chunks (runs after the scan).
+__global__ void residual_scale_kernel(const SelectParams p) {
+  if (threadIdx.x == 0 && blockIdx.x == 0) {
+    int mb = 0;
+    for (int c = 0; c < p.nchunks; ++c) mb = max(mb, p.max_bin[c]);
+    const float amax = bf16_bits_to_float(static_cast<unsigned short>(mb));
+    const float qmax = (p.bits == 4) ? 7.f : 127.f;
+    *p.out_scale = (p.bits == 0) ? 1.f : fmaxf(amax / qmax, 1.17549435e-38f);
+  }
+}
+
+constexpr int STAGE_CAP = 12288;  // staged (index, value) pairs per CTA between flushes
+
+__device__ __forceinline__ void emit_entry(const SelectParams& p, int o, long long flat, unsigned short bits16,
+                                           float inv_scale) {
+  if (p.out_idx32) p.out_idx32[o] = static_cast<int>(flat);
+  else p.out_idx64[o] = flat;
+  if (p.bits == 0) {
+    reinterpret_cast<unsigned short*>(p.out_val)[o] = bits16;
+  } else {
+    const float lo = (p.bits == 4) ? -8.f : -128.f, hi = (p.bits == 4) ? 7.f : 127.f;
+    float qv = fminf(fmaxf(rintf(bf16_bits_to_float(bits16) * inv_scale), lo), hi);
+    reinterpret_cast<signed char*>(p.out_val)[o] = static_cast<signed char>(qv);
+  }
+}
+
+template <int RP>
+__global__ void __launch_bounds__(512, 1) residual_compact_kernel(const SelectParams p, int ctn, int rl) {
+  constexpr int CPT = 64 / RP;
+  extern __shared__ unsigned char sh_raw[];
+  long long* st_idx = reinterpret_cast<long long*>(sh_raw);
+  unsigned short* st_val = reinterpret_cast<unsigned short*>(st_idx + STAGE_CAP);
+  __shared__ int st_count, st_base;
+  const Slab s = slab_of(p);
+  const int thr = p.thr_bin[s.chunk];
+  const int need = p.thr_need[s.chunk];
+  const int quota = p.quota[s.chunk];
+  const int obase = p.out_offset[s.chunk];
+  const float inv_scale = 1.f / *p.out_scale;
+  if (threadIdx.x == 0) st_count = 0;
+  __syncthreads();
+  const int ct = threadIdx.x % ctn, lane_row = threadIdx.x / ctn;
+
+  // Copy the staged entries out with one global atomic for the whole batch.  Called by every
+  // thread of the CTA (the decision is taken on a count read between two barriers).
+  auto flush = [&](int cnt) {
+    if (cnt > STAGE_CAP) cnt = STAGE_CAP;  // entries past the capacity were appended directly
+    if (threadIdx.x == 0) st_base = atomicAdd(&p.out_count[s.chunk], cnt);
+    __syncthreads();
+    const int base = st_base;
+    for (int i = threadIdx.x; i < cnt; i += blockDim.x)
+      if (base + i < quota) emit_entry(p, obase + base + i, st_idx[i], st_val[i], inv_scale);
+    __syncthreads();
+    if (threadIdx.x == 0) st_count = 0;
+    __syncthreads();
+  };
+
+  for (int cb = 0; cb < p.n; cb += ctn * CPT) {
+    const int col = cb + ct * CPT;
+    const bool active = (col < p.n) && (lane_row < rl);
+    float qreg[CPT][RP];
+    if (active) load_q<RP, CPT>(p.q, p.r, col, p.n, qreg);
+    const int step = rl * ROWS_UNROLL;
+    const int iters = (s.row1 - s.row0 + step - 1) / step;  // uniform across the CTA
+    for (int it = 0; it < iters; ++it) {
+      __syncthreads();
+      const int staged = st_count;
+      __syncthreads();
+      if (staged > STAGE_CAP / 2) flush(staged);
+      const int row = s.row0 + it * step + lane_row;
+      if (active) {
+        XVec<CPT> xv[ROWS_UNROLL];
+        CVec<RP> cv[ROWS_UNROLL];
+#pragma unroll
+        for (int u = 0; u < ROWS_UNROLL; ++u) {
+          const int rr = row + u * rl;
+          if (rr < s.row1) {
+            xv[u] = load_x<CPT>(p.x + static_cast<size_t>(rr) * p.ldx, col, p.n);
+            cv[u] = load_c<RP>(p.c + static_cast<size_t>(rr) * p.r, p.r);
+          }
+        }
+#pragma unroll
+        for (int u = 0; u < ROWS_UNROLL; ++u) {
+          const int rr = row + u * rl;
+          if (rr >= s.row1) continue;
+          float e[CPT];
+          residual_row<RP, CPT>(xv[u], cv[u], qreg, e);
+#pragma unroll
+          for (int i = 0; i < CPT; ++i) {
+            if (col + i >= p.n) continue;
+            const unsigned short bits16 = __bfloat16_as_ushort(__float2bfloat16_rn(e[i]));
+            const int key = bits16 & 0x7FFF;
+            bool take = key > thr;
+            if (!take && key == thr && need > 0) take = atomicAdd(&p.tie_count[s.chunk], 1) < need;
+            if (take) {
+              const long long flat = static_cast<long long>(rr) * p.n + (col + i);
+              const int slot = atomicAdd(&st_count, 1);
+              if (slot < STAGE_CAP) {
+                st_idx[slot] = flat;
+                st_val[slot] = bits16;
+              } else {  // staging buffer full (very dense selection): append directly
+                const int o = atomicAdd(&p.out_count[s.chunk], 1);
+                if (o < quota) emit_entry(p, obase + o, flat, bits16, inv_scale);
+              }
+            }
+          }
+        }
+      }
+    }
+  }
+  __syncthreads();
+  const int staged = st_count;
+  __syncthreads();
+  if (staged > 0) flush(staged);
+}
+
+// e[i] = X[idx] - C[row] . Q[col] for an explicit index list (uniform / block-sparse selectors).
+__global__ void residual_gather_kernel(const __nv_bfloat16* x, const __nv_bfloat16* c, const __nv_bfloat16* q,
+                                       int n, int r, int ldx, const long long* idx64, const int* idx32, long long count,
+                                       __nv_bfloat16* out) {
+  long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x;
+  if (i >= count) return;
+  const long long flat = idx64 ? idx64[i] : static_cast<long long>(idx32[i]);
+  const long long row = flat / n;
+  const int col = static_cast<int>(flat - row * n);
+  float acc = 0.f;
+  for (int j = 0; j < r; ++j)
+    acc = fmaf(__bfloat162float(c[row * r + j]), __bfloat162float(q[static_cast<size_t>(col) * r + j]), acc);
+  out[i] = __float2bfloat16_rn(__bfloat162float(x[row * ldx + col]) - acc);
+}
+
+// energy[row, b] = sum of squared (bf16-rounded) residuals over `bs` consecutive columns;
+// bs is a power of two in [8, 256] dividing n.  One thread per 8 columns, shuffle-reduced.
+__global__ void __launch_bounds__(256) residual_block_energy_kernel(const __nv_bfloat16* x, const __nv_bfloat16* c,
+                                                                    const __nv_bfloat16* q, int rows, int n, int r, int ldx,
+                                                                    int bs, float* energy) {
+  const int row = blockIdx.y;
+  const int tpb = bs / 8;
+  const int col = (blockIdx.x * blockDim.x + threadIdx.x) * 8;
+  float sum = 0.f;
+  if (col < n) {
+    for (int i = 0; i < 8 && col + i < n; ++i) {
+      float acc = 0.f;
+      for (int j = 0; j < r; ++j)
+        acc = fmaf(__bfloat162float(c[static_cast<size_t>(row) * r + j]), __bfloat162float(q[static_cast<size_t>(col + i) * r + j]), acc);
+      const float e = __bfloat162float(__float2bfloat16_rn(__bfloat162float(x[static_cast<size_t>(row) * ldx + col + i]) - acc));
+      sum = fmaf(e, e, sum);
+    }
+  }
+  for (int off = 1; off < tpb; off <<= 1) sum += __shfl_xor_sync(0xffffffffu, sum, off);
+  if (col < n && (threadIdx.x % tpb) == 0) energy[static_cast<size_t>(row) * (n / bs) + col / bs] = sum;
+}
+
+template <int RP>
+static int launch_select(const SelectParams& p, int phase, cudaStream_t st) {
+  constexpr int CPT = 64 / RP;
+  int ctn = (p.n + CPT - 1) / CPT;
+  if (ctn > 512) ctn = 512;
+  int rl = 512 / ctn;
+  if (rl < 1) rl = 1;
+  const int threads = ((ctn * rl + 31) / 32) * 32;
+  const int grid = p.nchunks * p.parts;
+  if (phase == 0) {
+    static bool cfg = false;
+    if (!cfg) {
+      cudaError_t e = cudaFuncSetAttribute(residual_hist_kernel<RP>, cudaFuncAttributeMaxDynamicSharedMemorySize, NBINS * 4);
+      if (e != cudaSuccess) return static_cast<int>(e);
+      cfg = true;
+    }
+    residual_hist_kernel<RP><<<grid, threads, NBINS * 4, st>>>(p, ctn, rl);
+  } else {
+    const int smem = STAGE_CAP * (8 + 2);
+    static bool cfg = false;
+    if (!cfg) {
+      cudaError_t e = cudaFuncSetAttribute(residual_compact_kernel<RP>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+      if (e != cudaSuccess) return static_cast<int>(e);
+      cfg = true;
+    }
+    residual_compact_kernel<RP><<<grid, threads, smem, st>>>(p, ctn, rl);
+  }
+  return static_cast<int>(cudaGetLastError());
+}
+
+}  // namespace sb
+
+// Exact top-k selection of the residual by magnitude, per row chunk.
+//   work: int32 scratch of 6 * nchunks entries (thr_bin, thr_need, max_bin, tie_count, out_count);
+//   hist: uint32 [nchunks, 32768], zeroed by the caller;
+//   quota / out_offset: int32 [nchunks] on the device;
+//   idx32 or idx64 (one non-null) and val (bf16 when bits == 0, int8 when bits == 8) have
+//   sum(quota) entries; scale is one fp32.
+extern "C" int sb_residual_topk(const void* x, const void* c, const void* q, int rows, int n, int r, int ldx,
+                                int chunk_rows, int nchunks, int parts, void* hist, int* work, const int* quota,
+                                const int* out_offset, int bits, int* idx32, long long* idx64, void* val,
+                                float* scale, int* status, void* stream) {
+  using namespace sb;
+  if (rows <= 0 || n <= 0 || nchunks <= 0) return 0;
+  if (r < 1 || r > 32) return -2;
+  if ((ldx & 7) || (reinterpret_cast<uintptr_t>(x) & 15) || (reinterpret_cast<uintptr_t>(c) & 15)) return -3;
+  SelectParams p;
+  p.x = static_cast<const __nv_bfloat16*>(x);
+  p.c = static_cast<const __nv_bfloat16*>(c);
+  p.q = static_cast<const __nv_bfloat16*>(q);
+  p.rows = rows; p.n = n; p.r = r; p.ldx = ldx;
+  p.chunk_rows = chunk_rows; p.parts = parts; p.nchunks = nchunks;
+  p.hist = static_cast<unsigned int*>(hist);
+  p.thr_bin = work; p.thr_need = work + nchunks; p.max_bin = work + 2 * nchunks;
+  p.tie_count = work + 3 * nchunks; p.out_count = work + 4 * nchunks;
+  p.quota = quota; p.out_offset = out_offset;
+  p.bits = bits; p.out_idx32 = idx32; p.out_idx64 = idx64; p.out_val = val; p.out_scale = scale;
+  p.status = status;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  int rc;
+  const int rp = r <= 8 ? 8 : (r <= 16 ? 16 : 32);
+  rc = rp == 8 ? launch_select<8>(p, 0, st) : rp == 16 ? launch_select<16>(p, 0, st) : launch_select<32>(p, 0, st);
+  if (rc) return rc;
+  residual_scan_kernel<<<nchunks, 1024, 0, st>>>(p);
+  residual_scale_kernel<<<1, 32, 0, st>>>(p);
+  rc = static_cast<int>(cudaGetLastError());
+  if (rc) return rc;
+  rc = rp == 8 ? launch_select<8>(p, 1, st) : rp == 16 ? launch_select<16>(p, 1, st) : launch_select<32>(p, 1, st);
+  return rc;
+}
+
+extern "C" int sb_residual_gather(const void* x, const void* c, const void* q, int n, int r, int ldx,
+                                  const long long* idx64, const int* idx32, long long count, void* out, void* stream) {
+  if (count <= 0) return 0;
+  const int threads = 256;
+  const long long blocks = (count + threads - 1) / threads;
+  sb::residual_gather_kernel<<<static_cast<unsigned>(blocks), threads, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(c), static_cast<const __nv_bfloat16*>(q), n, r,
+      ldx, idx64, idx32, count, static_cast<__nv_bfloat16*>(out));
+  return static_cast<int>(cudaGetLastError());
+}
+
+extern "C" int sb_residual_block_energy(const void* x, const void* c, const void* q, int rows, int n, int r, int ldx,
+                                        int bs, float* energy, void* stream) {
+  if (rows <= 0) return 0;
+  if (bs % 8 || bs > 256 || (bs & (bs - 1)) || n % bs) return -2;
+  dim3 grid((n / 8 + 255) / 256, rows);
+  sb::residual_block_energy_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(c), static_cast<const __nv_bfloat16*>(q), rows, n,
+      r, ldx, bs, energy);
+  return static_cast<int>(cudaGetLastError());
+}

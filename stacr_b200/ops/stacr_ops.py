@@ -1,0 +1,194 @@
+"""Python entry points for the compressed-linear kernels (projection, selection, basis, dW)."""
+
+from __future__ import annotations
+
+import ctypes
+import math
+
+import torch
+
+from . import _lib
+from .gemm import gemm
+
+c_int = ctypes.c_int
+c_ll = ctypes.c_longlong
+c_float = ctypes.c_float
+
+
+def rank_pad(rank: int) -> int:
+    """Width of the padded rank panel the tensor-core kernels use (UMMA N is a multiple of 16)."""
+    return 16 if rank <= 16 else 32
+
+
+def pad_basis_transpose(basis_bf16: torch.Tensor) -> torch.Tensor:
+    """``[N, r]`` bf16 basis -> zero-padded ``[rpad, N]`` K-major panel."""
+    n, r = basis_bf16.shape
+    out = torch.zeros(rank_pad(r), n, dtype=torch.bfloat16, device=basis_bf16.device)
+    out[:r] = basis_bf16.t()
+    return out
+
+
+def _splits_for(m_rows: int, k: int, device) -> int:
+    tiles = (m_rows + 127) // 128
+    kb = (k + 63) // 64
+    return max(1, min(kb, _lib.sm_count(device) // max(1, tiles)))
+
+
+def project(x: torch.Tensor, qt_pad: torch.Tensor) -> torch.Tensor:
+    """``X[rows, N] @ Q`` with the padded transposed basis ``[rpad, N]``; fp32 ``[rows, rpad]``."""
+    rows, n = x.shape
+    return gemm(x, qt_pad, splits=max(2, _splits_for(rows, n, x.device)), bn=qt_pad.shape[0])
+
+
+def at_b(a: torch.Tensor, bt_pad: torch.Tensor) -> torch.Tensor:
+    """``A[rows, M]^T @ B`` where ``bt_pad`` is the padded transpose ``[rpad, rows]``; fp32 ``[M, rpad]``."""
+    rows, m = a.shape
+    return gemm(a, bt_pad, a_mn=True, splits=max(2, _splits_for(m, rows, a.device)), bn=bt_pad.shape[0])
+
+
+def transpose_pad(c: torch.Tensor) -> torch.Tensor:
+    """``[rows, r]`` (bf16 or fp32) -> zero-padded bf16 ``[rpad, rows]``."""
+    rows, r = c.shape
+    out = torch.zeros(rank_pad(r), rows, dtype=torch.bfloat16, device=c.device)
+    out[:r] = c.t()
+    return out
+
+
+def residual_topk(
+    x: torch.Tensor,
+    coeff: torch.Tensor,
+    basis_bf16: torch.Tensor,
+    quotas: list[int],
+    chunk_rows: int,
+    bits: int,
+    index_dtype: torch.dtype,
+):
+    """Exact per-chunk top-k of ``|X - C Q^T|``; returns ``(idx, values, scale)``.
+
+    ``values`` are bf16 (``bits == 0``) or int8 holding the 8- or 4-bit codes; ``scale`` is an
+    fp32 scalar tensor.  Entry order is unspecified.
+    """
+    rows, n = x.shape
+    r = coeff.shape[1]
+    nchunks = len(quotas)
+    dev = x.device
+    total = sum(quotas)
+    sms = _lib.sm_count(dev)
+    parts = max(1, sms // nchunks)
+    hist = torch.zeros(nchunks * 32768, dtype=torch.int32, device=dev)
+    work = torch.zeros(6 * nchunks, dtype=torch.int32, device=dev)
+    offsets = [0]
+    for k in quotas[:-1]:
+        offsets.append(offsets[-1] + k)
+    meta = torch.tensor([quotas, offsets], dtype=torch.int32).to(dev, non_blocking=True)
+    idx = torch.empty(total, dtype=index_dtype, device=dev)
+    val = torch.empty(total, dtype=torch.bfloat16 if bits == 0 else torch.int8, device=dev)
+    scale = torch.empty((), dtype=torch.float32, device=dev)
+    is32 = index_dtype == torch.int32
+    lib = _lib.load()
+    rc = lib.sb_residual_topk(
+        _lib.ptr(x), _lib.ptr(coeff), _lib.ptr(basis_bf16), c_int(rows), c_int(n), c_int(r), c_int(x.stride(0)),
+        c_int(chunk_rows), c_int(nchunks), c_int(parts), _lib.ptr(hist), _lib.ptr(work), _lib.ptr(meta[0]), _lib.ptr(meta[1]),
+        c_int(bits), _lib.ptr(idx if is32 else None), _lib.ptr(None if is32 else idx), _lib.ptr(val), _lib.ptr(scale),
+        _lib.ptr(_lib.status_word(dev)), _lib.stream_ptr(),
+    )
+    _lib.check_rc(rc, "sb_residual_topk")
+    return idx, val, scale
+
+
+def residual_gather(x, coeff, basis_bf16, idx: torch.Tensor) -> torch.Tensor:
+    """bf16 residual values at explicit flat indices."""
+    n, r = basis_bf16.shape
+    out = torch.empty(idx.numel(), dtype=torch.bfloat16, device=x.device)
+    is32 = idx.dtype == torch.int32
+    rc = _lib.load().sb_residual_gather(
+        _lib.ptr(x), _lib.ptr(coeff), _lib.ptr(basis_bf16), c_int(n), c_int(r), c_int(x.stride(0)),
+        _lib.ptr(None if is32 else idx), _lib.ptr(idx if is32 else None), c_ll(idx.numel()), _lib.ptr(out), _lib.stream_ptr(),
+    )
+    _lib.check_rc(rc, "sb_residual_gather")
+    return out
+
+
+def residual_block_energy(x, coeff, basis_bf16, block: int) -> torch.Tensor:
+    rows, n = x.shape
+    out = torch.empty(rows, n // block, dtype=torch.float32, device=x.device)
+    rc = _lib.load().sb_residual_block_energy(
+        _lib.ptr(x), _lib.ptr(coeff), _lib.ptr(basis_bf16), c_int(rows), c_int(n), c_int(coeff.shape[1]), c_int(x.stride(0)),
+        c_int(block), _lib.ptr(out), _lib.stream_ptr(),
+    )
+    _lib.check_rc(rc, "sb_residual_block_energy")
+    return out
+
+
+def oja_update(basis_fp32, g, y, rows: int, lr: float):
+    """One fused Oja + CholeskyQR2 step; returns ``(basis_fp32, basis_bf16, basis_t_pad_bf16)``.
+
+    ``g`` is ``X^T Y`` ``[N, >=r]`` fp32 and ``y`` is ``[rows, >=r]`` fp32; pass ``None`` for both
+    (and ``lr=0``) to only re-orthonormalise.
+    """
+    n, r = basis_fp32.shape
+    dev = basis_fp32.device
+    q_in = basis_fp32.contiguous()
+    q_out = torch.empty_like(q_in)
+    qb = torch.empty(n, r, dtype=torch.bfloat16, device=dev)
+    rp = rank_pad(r)
+    qt = torch.empty(rp, n, dtype=torch.bfloat16, device=dev)
+    rc = _lib.load().sb_oja_update(
+        _lib.ptr(q_in), _lib.ptr(g), c_int(0 if g is None else g.stride(0)), _lib.ptr(y), c_int(0 if y is None else y.stride(0)),
+        c_int(rows), c_int(n), c_int(r), c_float(lr if g is not None else 0.0), _lib.ptr(q_out), _lib.ptr(qb), _lib.ptr(qt),
+        c_int(rp), _lib.ptr(_lib.status_word(dev)), _lib.stream_ptr(),
+    )
+    _lib.check_rc(rc, "sb_oja_update")
+    return q_out, qb, qt
+
+
+def weight_grad(
+    dy: torch.Tensor,
+    coeff: torch.Tensor,
+    basis_fp32: torch.Tensor,
+    residual,
+    out_features: int,
+    in_features: int,
+    transposed: bool,
+    out_dtype: torch.dtype,
+) -> torch.Tensor:
+    """``dW = (dY^T C) Q^T + dY^T S`` without rebuilding the dense input.
+
+    ``residual`` is ``None`` or ``(idx, values, scale, bits, length)``.
+    """
+    dev = dy.device
+    rows = dy.shape[0]
+    r = coeff.shape[1]
+    t = at_b(dy, transpose_pad(coeff))  # [O, rpad] fp32
+    colptr = rows_s = vals_s = None
+    if residual is not None and residual[4] > 0:
+        idx, values, scale, bits, length = residual
+        counts = torch.zeros(in_features, dtype=torch.int32, device=dev)
+        cursor = torch.empty(in_features, dtype=torch.int32, device=dev)
+        colptr = torch.empty(in_features + 1, dtype=torch.int32, device=dev)
+        rows_s = torch.empty(length, dtype=torch.int32, device=dev)
+        vals_s = torch.empty(length, dtype=torch.float32, device=dev)
+        is32 = idx.dtype == torch.int32
+        rc = _lib.load().sb_residual_bucket(
+            _lib.ptr(idx if is32 else None), _lib.ptr(None if is32 else idx), c_ll(length), c_int(in_features), _lib.ptr(values),
+            c_int(bits), _lib.ptr(scale), _lib.ptr(counts), _lib.ptr(cursor), _lib.ptr(colptr), _lib.ptr(rows_s), _lib.ptr(vals_s),
+            _lib.stream_ptr(),
+        )
+        _lib.check_rc(rc, "sb_residual_bucket")
+    shape = (in_features, out_features) if transposed else (out_features, in_features)
+    out = torch.empty(shape, dtype=out_dtype, device=dev)
+    rc = _lib.load().sb_dw_fused(
+        _lib.ptr(t), c_int(t.stride(0)), _lib.ptr(basis_fp32), c_int(r), _lib.ptr(dy), c_int(dy.stride(0)), _lib.ptr(colptr),
+        _lib.ptr(rows_s), _lib.ptr(vals_s), c_int(out_features), c_int(in_features), c_int(int(transposed)),
+        c_int(int(out_dtype == torch.bfloat16)), _lib.ptr(out), _lib.stream_ptr(),
+    )
+    _lib.check_rc(rc, "sb_dw_fused")
+    return out
+
+
+def colsum(dy: torch.Tensor) -> torch.Tensor:
+    rows, o = dy.shape
+    out = torch.zeros(o, dtype=torch.float32, device=dy.device)
+    rc = _lib.load().sb_colsum_bf16(_lib.ptr(dy), c_int(rows), c_int(o), c_int(dy.stride(0)), _lib.ptr(out), _lib.stream_ptr())
+    _lib.check_rc(rc, "sb_colsum_bf16")
+    return out

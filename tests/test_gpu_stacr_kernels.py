@@ -1,0 +1,136 @@
+"""Compressed-linear kernels (selection, basis update, weight gradient, full layer) against fp32 PyTorch references."""
+
+import copy
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _setup(rows, n, r, seed=0):
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    base = torch.randn(rows, r, device="cuda", generator=g) @ torch.randn(r, n, device="cuda", generator=g)
+    x = (base + 0.3 * torch.randn(rows, n, device="cuda", generator=g)).bfloat16()
+    q = torch.linalg.qr(torch.randn(n, r, device="cuda", generator=g)).Q.contiguous()
+    qb = q.bfloat16().contiguous()
+    c = (x.float() @ qb.float()).bfloat16().contiguous()
+    e = (x.float() - c.float() @ qb.float().t()).bfloat16()
+    return x, q, qb, c, e
+
+
+@pytest.mark.parametrize("rows,n,r", [(256, 512, 8), (1000, 2048, 8), (512, 768, 16), (300, 1280, 32), (2048, 8192, 8)])
+@pytest.mark.parametrize("bits", [0, 8, 4])
+def test_global_topk_matches_reference_value_set(rows, n, r, bits):
+    from stacr_b200.ops import _lib, stacr_ops
+
+    x, q, qb, c, e = _setup(rows, n, r)
+    k = int(round(0.01 * rows * n))
+    idx, val, scale = stacr_ops.residual_topk(x, c, qb, [k], rows, bits, torch.int32)
+    torch.cuda.synchronize()
+    _lib.check_status()
+    assert idx.numel() == k and idx.unique().numel() == k
+    ref_top = e.reshape(-1).float().abs().topk(k).values.sort().values
+    got_e = e.reshape(-1)[idx.long()].float()
+    # the kernel recomputes the residual with its own fp32 summation order: allow one bf16 ulp
+    torch.testing.assert_close(got_e.abs().sort().values, ref_top, rtol=2e-2, atol=1e-3)
+    if bits == 0:
+        torch.testing.assert_close(val.float(), got_e, rtol=2e-2, atol=1e-3)
+    else:
+        qmax = 127.0 if bits == 8 else 7.0
+        assert abs(float(scale) - float(ref_top[-1]) / qmax) <= 2e-2 * float(scale)
+        deq = val.float() * scale
+        assert (deq - got_e).abs().max() <= 0.51 * float(scale) + 2e-2 * float(got_e.abs().max())
+
+
+def test_chunk_quota_selection_counts_and_values():
+    from stacr_b200.ops import _lib, stacr_ops
+
+    rows, n, r, chunk = 1536, 1024, 8, 512
+    x, q, qb, c, e = _setup(rows, n, r, seed=3)
+    quotas = [int(round(0.005 * chunk * n))] * 3
+    idx, val, _ = stacr_ops.residual_topk(x, c, qb, quotas, chunk, 0, torch.int32)
+    torch.cuda.synchronize()
+    _lib.check_status()
+    rows_of = idx.long() // n
+    for ci, k in enumerate(quotas):
+        mine = idx[(rows_of >= ci * chunk) & (rows_of < (ci + 1) * chunk)]
+        assert mine.numel() == k
+        ref = e[ci * chunk:(ci + 1) * chunk].reshape(-1).float().abs().topk(k).values.sort().values
+        got = e.reshape(-1)[mine.long()].float().abs().sort().values
+        torch.testing.assert_close(got, ref, rtol=2e-2, atol=1e-3)
+
+
+def test_oja_update_matches_framework_step():
+    from stacr_b200.oja import oja_step
+    from stacr_b200.ops import _lib
+    from stacr_b200.ops.basis import oja_step_kernels
+
+    rows, n, r = 2048, 1024, 8
+    x, q, qb, c, e = _setup(rows, n, r, seed=5)
+    new = oja_step_kernels(q, x, 0.05)
+    torch.cuda.synchronize()
+    _lib.check_status()
+    ref = oja_step(q, x, 0.05)
+    gram = new.t() @ new
+    torch.testing.assert_close(gram, torch.eye(r, device="cuda"), atol=1e-4, rtol=0)
+    # same subspace: projector difference small
+    diff = (new @ new.t() - ref @ ref.t()).norm() / (ref @ ref.t()).norm()
+    assert diff < 2e-2, float(diff)
+
+
+@pytest.mark.parametrize("transposed", [False, True])
+@pytest.mark.parametrize("bits", [0, 8, 4])
+def test_weight_grad_matches_fp32_formula(transposed, bits):
+    from stacr_b200.ops import _lib, stacr_ops
+    from stacr_b200.quant import quantize_values
+
+    rows, n, o, r = 1024, 512, 768, 8
+    x, q, qb, c, e = _setup(rows, n, r, seed=7)
+    dy = torch.randn(rows, o, device="cuda").bfloat16()
+    k = 4000
+    idx = torch.randperm(rows * n, device="cuda")[:k].to(torch.int32)
+    vals = e.reshape(-1)[idx.long()]
+    packed = quantize_values(vals, bits)
+    out = stacr_ops.weight_grad(dy, c, qb.float(), (idx, packed.data, packed.scale, packed.bits, packed.length), o, n, transposed, torch.float32)
+    torch.cuda.synchronize()
+    _lib.check_status()
+    s = torch.zeros(rows * n, device="cuda")
+    s[idx.long()] = packed.dequantize(torch.float32)
+    ref = (dy.float().t() @ c.float()) @ qb.float().t() + dy.float().t() @ s.reshape(rows, n)
+    if transposed:
+        ref = ref.t()
+    err = (out - ref).abs().max() / ref.abs().max()
+    assert err < 1e-2, float(err)
+
+
+@pytest.mark.parametrize("mode", ["chunk_topk", "global_topk", "block_sparse", "uniform", "none"])
+def test_layer_forward_backward_on_kernel_path(mode):
+    import stacr_b200 as S
+    from stacr_b200.ops import _lib
+
+    torch.manual_seed(11)
+    lin = torch.nn.Linear(1024, 512, device="cuda")
+    ref = copy.deepcopy(lin)
+    layer = S.STACRLinear.from_linear(lin, rank=8, residual_budget=0.01, residual_mode=mode)
+    base = torch.randn(2048, 8, device="cuda") @ torch.randn(8, 1024, device="cuda")
+    x = (base + 0.2 * torch.randn(2048, 1024, device="cuda")).requires_grad_(True)
+    xr = x.detach().clone().requires_grad_(True)
+    with torch.autocast("cuda", dtype=torch.bfloat16):
+        y = layer(x)
+        yr = ref(xr)
+    assert y.dtype == torch.bfloat16
+    torch.testing.assert_close(y.float(), yr.float(), rtol=3e-2, atol=3e-2)
+    # nothing as large as the input is saved
+    saved = [t for t in y.grad_fn.saved_tensors if t is not lin.weight]
+    assert all(t.numel() < x.numel() // 4 for t in saved)
+    assert len(saved) == (2 if mode == "none" else 5)
+    g = torch.randn_like(y)
+    y.backward(g)
+    yr.backward(g)
+    torch.cuda.synchronize()
+    _lib.check_status()
+    torch.testing.assert_close(x.grad, xr.grad, rtol=3e-2, atol=3e-2)
+    cos = float(S.cosine_similarity(ref.weight.grad, lin.weight.grad))
+    assert cos > 0.9, cos
+    torch.testing.assert_close(lin.bias.grad, ref.bias.grad, rtol=2e-2, atol=2e-1)
