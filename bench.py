@@ -1,0 +1,312 @@
+"""Headline benchmark: full STAC-R training step of a Pythia-1.4B-shaped decoder, tokens/s over N GPUs.
+
+    python bench.py --gpus N --steps K --warmup W            # this framework
+    python bench.py --impl reference --gpus N --steps K ...   # the unmodified reference package
+
+Config (both arms): 24 layers, d_model 2048, 16 heads, MLP 8192, rotary on 25 % of head dims,
+parallel attention+MLP residual, vocab 50304, seq 2048, batch 4 per GPU, bf16 compute, random
+init, uniform-random tokens; STAC-R on the MLP surface with rank 8, residual budget 0.005,
+residual_mode=global_topk, no turbo; AdamW with 8-bit block-wise moments (this framework) --
+the reference arm uses torch AdamW because the external 8-bit optimizer it relies on is not
+installed; data-parallel over N ranks (weak scaling).
+
+Two timed regions of K optimizer steps each, both bracketed by barrier + synchronize and timed
+with CUDA events, max over ranks: (1) device-resident inputs, no host read-back -> ``value``;
+(2) end to end through the public API, with the step's token batch copied from pinned host
+memory and the loss read back every step -> ``e2e``.  One JSON line is printed by rank 0.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+REPO = os.path.dirname(os.path.abspath(__file__))
+
+MODEL = dict(vocab_size=50304, hidden_size=2048, num_hidden_layers=24, num_attention_heads=16, intermediate_size=8192,
+             rotary_pct=0.25, max_position_embeddings=2048, use_parallel_residual=True)
+SEQ, BATCH = 2048, 4
+STACR = dict(rank=8, residual_budget=0.005, residual_mode="global_topk", turbo_after_step=None, surface="mlp", min_features=256)
+SMALL = dict(vocab_size=8192, hidden_size=512, num_hidden_layers=4, num_attention_heads=8, intermediate_size=2048,
+             rotary_pct=0.25, max_position_embeddings=512, use_parallel_residual=True)
+
+
+# ----------------------------------------------------------------------------------- harness
+class ClockSampler:
+    """Samples SM clock, power and throttle reasons with nvidia-smi while a timed region runs."""
+
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+             "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu = gpu_index
+        self.rows: list[list[str]] = []
+        self._stop = threading.Event()
+        self._thread = None
+
+    def _run(self):
+        while not self._stop.is_set():
+            try:
+                out = subprocess.run(["nvidia-smi", f"--id={self.gpu}", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits"],
+                                     capture_output=True, text=True, timeout=5).stdout.strip()
+                if out:
+                    self.rows.append([c.strip() for c in out.splitlines()[0].split(",")])
+            except Exception:
+                pass
+            self._stop.wait(0.2)
+
+    def __enter__(self):
+        self._thread = threading.Thread(target=self._run, daemon=True)
+        self._thread.start()
+        return self
+
+    def __exit__(self, *exc):
+        self._stop.set()
+        self._thread.join(timeout=6)
+
+    def summary(self) -> dict:
+        sm = [float(r[1]) for r in self.rows if len(r) > 8 and r[1].replace(".", "").isdigit()]
+        mx = [float(r[2]) for r in self.rows if len(r) > 8 and r[2].replace(".", "").isdigit()]
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = sorted({n for r in self.rows if len(r) > 8 for n, v in zip(names, r[5:9]) if v.lower().startswith("active")})
+        power = [float(r[3]) for r in self.rows if len(r) > 8 and r[3].replace(".", "").isdigit()]
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None, "reasons": reasons,
+                "power_w_max": max(power) if power else None, "samples": len(self.rows)}
+
+
+def timed_region(torch, dist, steps, step_fn, world):
+    """Barrier + sync, K steps between CUDA events, sync + barrier; returns max-over-ranks seconds."""
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(steps):
+        step_fn(i)
+    e1.record()
+    torch.cuda.synchronize()
+    secs = torch.tensor([e0.elapsed_time(e1) / 1e3], device="cuda")
+    if world > 1:
+        dist.all_reduce(secs, op=dist.ReduceOp.MAX)
+        dist.barrier()
+    return float(secs)
+
+
+def make_tokens(torch, vocab, batch, seq, count, seed):
+    gen = torch.Generator().manual_seed(seed)
+    return [torch.randint(0, vocab, (batch, seq), generator=gen) for _ in range(count)]
+
+
+def emit(payload):
+    print(json.dumps(payload), flush=True)
+
+
+# ----------------------------------------------------------------------------------- this framework
+def run_ours(args):
+    sys.path.insert(0, REPO)
+    import torch
+    import torch.distributed as dist
+
+    import stacr_b200 as S
+    from stacr_b200.models import GPTNeoXForCausalLM, NeoXConfig
+    from stacr_b200.ops import _lib
+    from stacr_b200.optim import AdamW8bit
+    from stacr_b200.parallel import GradSync, broadcast_parameters, init_distributed
+
+    rank, world, local = init_distributed()
+    if world != args.gpus:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}; launch with torchrun --nproc-per-node {args.gpus}")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    torch.manual_seed(1234)
+    shape = SMALL if args.small else MODEL
+    seq, batch = (512, 4) if args.small else (SEQ, BATCH)
+    model = GPTNeoXForCausalLM(NeoXConfig(**shape)).to(dev).train()
+    broadcast_parameters(model)
+    layers = S.apply_stacr(model, **STACR)
+    opt = AdamW8bit(model.parameters(), lr=2e-5, weight_decay=0.0)
+    sync = GradSync(model.parameters(), backend=args.comm) if world > 1 else None
+    host_batches = [t.pin_memory() for t in make_tokens(torch, shape["vocab_size"], batch, seq, 8, 100 + rank)]
+    dev_batches = [t.to(dev) for t in host_batches]
+    counter = {"step": 0}
+
+    def train_step(ids):
+        S.set_step(layers, counter["step"])
+        counter["step"] += 1
+        if sync is not None:
+            sync.zero_grad()
+        else:
+            opt.zero_grad(set_to_none=True)
+        with torch.autocast("cuda", dtype=torch.bfloat16):
+            loss = model(input_ids=ids, labels=ids).loss
+        loss.backward()
+        if sync is not None:
+            sync.finish()
+        opt.step()
+        return loss
+
+    def step_device(i):
+        train_step(dev_batches[i % len(dev_batches)])
+
+    last = {}
+
+    def step_e2e(i):
+        ids = host_batches[i % len(host_batches)].to(dev, non_blocking=True)  # pinned host -> device
+        last["loss"] = float(train_step(ids).detach().float().cpu())            # device -> host read-back
+
+    warm = max(3, args.warmup)
+    for i in range(warm):
+        step_e2e(i)
+    torch.cuda.synchronize()
+    _lib.check_status(dev)
+    torch.cuda.reset_peak_memory_stats(dev)
+    launches0 = _lib.launch_count() + opt.kernel_launches
+    with ClockSampler(local) as clocks:
+        secs = timed_region(torch, dist, args.steps, step_device, world)
+    launches = _lib.launch_count() + opt.kernel_launches - launches0
+    with ClockSampler(local) as clocks_e2e:
+        secs_e2e = timed_region(torch, dist, args.steps, step_e2e, world)
+    _lib.check_status(dev)
+    peak = torch.cuda.max_memory_allocated(dev)
+    rows = batch * seq
+    factor_bytes = sum(layer.stored_bytes(rows, 2)["total"] for layer in layers)
+    dense_bytes = sum(rows * layer.in_features * 2 for layer in layers)
+    tokens = world * batch * seq * args.steps
+    if rank == 0:
+        emit({
+            "metric": "tokens_per_second", "value": tokens / secs, "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
+            "warmup": warm, "ms_per_step": 1e3 * secs / args.steps, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "bf16", "data": "synthetic uniform-random tokens, random-init weights", "impl": "stacr_b200",
+            "config": {
+                "model": "pythia-1.4b-shaped (24L d2048 h16 mlp8192 rotary25% parallel-residual vocab50304)" if not args.small else "small",
+                "global_batch": world * batch, "seq_len": seq, "parallelism": f"dp{world}",
+                "stacr": STACR, "optimizer": "AdamW 8-bit block-wise (in-tree)", "comm": sync.backend if sync else "none",
+                "l2": "inputs larger than L2: every step streams 2.8 GB of bf16 weights and > 10 GB of activations through a 126 MB L2",
+            },
+            "clocks": clocks.summary(),
+            "e2e": {"value": tokens / secs_e2e, "unit": "tokens/s", "h2d_bytes_per_step": batch * seq * 8, "d2h_bytes_per_step": 4,
+                    "ms_per_step": 1e3 * secs_e2e / args.steps, "last_loss": last.get("loss"), "clocks": clocks_e2e.summary()},
+            "gpu_launches": launches,
+            "memory": {"peak_allocated_gb": peak / 1e9, "saved_activation_gb_wrapped_layers": factor_bytes / 1e9,
+                       "dense_saved_gb_same_layers": dense_bytes / 1e9},
+        })
+    if world > 1:
+        dist.destroy_process_group()
+
+
+# ----------------------------------------------------------------------------------- reference
+def run_reference(args):
+    ref_root = os.path.join(REPO, "baseline", "_ref")
+    if not os.path.isdir(os.path.join(ref_root, "stacr")):
+        emit({"impl": "reference", "unavailable": "baseline/_ref is missing (offline pip install of the reference not present)"})
+        return
+    # The reference package is also called `stacr`: keep this repository off the import path.
+    sys.path[:] = [p for p in sys.path if os.path.abspath(p or ".") != REPO]
+    sys.path.insert(0, ref_root)
+    try:
+        import torch
+        import torch.distributed as dist
+        import stacr as ref
+        from torch.nn.parallel import DistributedDataParallel as DDP
+        from transformers import GPTNeoXConfig, GPTNeoXForCausalLM
+    except Exception as exc:  # noqa: BLE001
+        emit({"impl": "reference", "unavailable": f"import failed: {type(exc).__name__}: {exc}"[:300]})
+        return
+    assert os.path.abspath(ref.__file__).startswith(ref_root), ref.__file__
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", str(rank)))
+    if world != args.gpus:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=dev)
+    torch.manual_seed(1234)
+    shape = SMALL if args.small else MODEL
+    seq, batch = (512, 4) if args.small else (SEQ, BATCH)
+    model = GPTNeoXForCausalLM(GPTNeoXConfig(**shape, hidden_dropout=0.0, attention_dropout=0.0)).to(dev).train()
+    layers = ref.apply_stacr(model, **STACR)
+    net = DDP(model, device_ids=[local], static_graph=True, broadcast_buffers=False) if world > 1 else model
+    opt = torch.optim.AdamW(model.parameters(), lr=2e-5, weight_decay=0.0)
+    host_batches = [t.pin_memory() for t in make_tokens(torch, shape["vocab_size"], batch, seq, 8, 100 + rank)]
+    dev_batches = [t.to(dev) for t in host_batches]
+    counter = {"step": 0}
+
+    def train_step(ids):
+        ref.set_step(layers, counter["step"])
+        counter["step"] += 1
+        opt.zero_grad(set_to_none=True)
+        with torch.autocast("cuda", dtype=torch.bfloat16):
+            loss = net(input_ids=ids, labels=ids).loss
+        loss.backward()
+        opt.step()
+        return loss
+
+    last = {}
+
+    def step_device(i):
+        train_step(dev_batches[i % len(dev_batches)])
+
+    def step_e2e(i):
+        ids = host_batches[i % len(host_batches)].to(dev, non_blocking=True)
+        last["loss"] = float(train_step(ids).detach().float().cpu())
+
+    warm = max(3, args.warmup)
+    for i in range(warm):
+        step_e2e(i)
+    torch.cuda.synchronize()
+    torch.cuda.reset_peak_memory_stats(dev)
+    with ClockSampler(local) as clocks:
+        secs = timed_region(torch, dist, args.steps, step_device, world)
+    with ClockSampler(local) as clocks_e2e:
+        secs_e2e = timed_region(torch, dist, args.steps, step_e2e, world)
+    peak = torch.cuda.max_memory_allocated(dev)
+    rows = batch * seq
+    factor_bytes = sum(layer.stored_bytes(rows, 2)["total"] for layer in layers)
+    tokens = world * batch * seq * args.steps
+    if rank == 0:
+        emit({
+            "impl": "reference", "metric": "tokens_per_second", "value": tokens / secs, "unit": "tokens/s", "n_gpus": world,
+            "steps": args.steps, "warmup": warm, "ms_per_step": 1e3 * secs / args.steps, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "bf16", "data": "synthetic uniform-random tokens, random-init weights",
+            "config": {
+                "model": "pythia-1.4b-shaped (HF GPTNeoXForCausalLM from config)" if not args.small else "small",
+                "global_batch": world * batch, "seq_len": seq, "parallelism": f"dp{world}", "stacr": STACR,
+                "optimizer": "torch.optim.AdamW (the reference's 8-bit optimizer needs bitsandbytes, not installed)",
+                "ddp": "torch DistributedDataParallel(static_graph=True, broadcast_buffers=False)",
+                "l2": "inputs larger than L2",
+            },
+            "clocks": clocks.summary(),
+            "e2e": {"value": tokens / secs_e2e, "unit": "tokens/s", "h2d_bytes_per_step": batch * seq * 8, "d2h_bytes_per_step": 4,
+                    "ms_per_step": 1e3 * secs_e2e / args.steps, "last_loss": last.get("loss"), "clocks": clocks_e2e.summary()},
+            "gpu_launches": None,
+            "memory": {"peak_allocated_gb": peak / 1e9, "saved_activation_gb_wrapped_layers": factor_bytes / 1e9},
+        })
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=8)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
+    ap.add_argument("--comm", default="auto", choices=["auto", "symm", "nccl"], help="gradient all-reduce path (this framework)")
+    ap.add_argument("--small", action="store_true", help="tiny shape for smoke runs (not a benchmark number)")
+    args = ap.parse_args()
+    if args.gpus > 1 and "RANK" not in os.environ:
+        raise SystemExit("for --gpus > 1 launch with: python -m torch.distributed.run --nproc-per-node N bench.py --gpus N ...")
+    (run_reference if args.impl == "reference" else run_ours)(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -21,6 +21,7 @@ _lock = threading.Lock()
 _lib: ctypes.CDLL | None = None
 _status: dict[int, torch.Tensor] = {}
 _sms: dict[int, int] = {}
+_launches = 0
 
 STATUS_TEXT = {
     0: "ok",
@@ -108,3 +109,13 @@ def ptr(t: torch.Tensor | None) -> ctypes.c_void_p:
 def check_rc(rc: int, what: str) -> None:
     if rc != 0:
         raise KernelError(f"{what} failed with code {rc}")
+
+
+def count(n: int = 1) -> None:
+    """Record ``n`` launches of this library's kernels (read back with :func:`launch_count`)."""
+    global _launches
+    _launches += n
+
+
+def launch_count() -> int:
+    return _launches

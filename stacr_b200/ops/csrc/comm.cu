@@ -1,0 +1,154 @@
+// All-reduce over NVLink peer memory, written for gradient buffers that live in symmetric memory
+// (every rank can address every rank's copy; optionally one NVSwitch multicast address maps all
+// copies).  One kernel does start barrier -> reduce -> broadcast -> end barrier:
+//
+//   two-shot, peer loads/stores: rank r owns slice r of [lo, hi); for each 16-byte element of
+//     its slice it loads the W copies (one local, W-1 over NVLink), adds, scales and stores the
+//     result into all W copies.  Per rank (W-1)/W of the bytes cross NVLink in each direction.
+//   multimem: the same slice ownership, but the W-way add is one `multimem.ld_reduce` executed
+//     in the switch and the broadcast is one `multimem.st`.
+//
+// Barriers are epoch-tagged flag words in a second symmetric buffer: CTA b of rank A publishes
+// flags[phase][b][A] = epoch into every peer with a system-scope release store, and waits with
+// acquire loads until its own flags[phase][b][*] reach the epoch.  Every wait is bounded; on
+// timeout the kernel records a status code and returns, and the host raises.
+// The grid is at most one CTA per SM so all CTAs of all ranks are co-resident.
+// Replaces the NCCL all-reduce that DistributedDataParallel issues for the reference
+// (experiments/benchmarks/distributed_data.py:87-97 there).
+#include "common.cuh"
+
+namespace sb {
+
+constexpr int MAX_RANKS = 16;
+constexpr int MAX_CTAS = 160;
+
+struct CommArgs {
+  const unsigned long long* peer_ptrs;   // [world] base address of every rank's buffer (as mapped here)
+  const unsigned long long* flag_ptrs;   // [world] base address of every rank's flag buffer
+  unsigned long long mc_ptr;             // multicast address of the buffer (0 = none)
+  int rank, world;
+  long long lo, hi;                      // element range (fp32), 4-element aligned
+  float scale;
+  int epoch;
+  int* status;
+};
+
+__device__ __forceinline__ void st_release_sys(int* p, int v) {
+  asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ int ld_acquire_sys(const int* p) {
+  int v;
+  asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+
+// All threads of the CTA call this.  Returns false when a peer did not arrive in time.
+__device__ bool rank_barrier(const CommArgs& a, int phase, int* s_fail) {
+  __syncthreads();
+  if (threadIdx.x < a.world) {
+    const int peer = threadIdx.x;
+    __threadfence_system();
+    int* remote = reinterpret_cast<int*>(a.flag_ptrs[peer]) + (phase * MAX_CTAS + blockIdx.x) * MAX_RANKS + a.rank;
+    st_release_sys(remote, a.epoch);
+    const int* local = reinterpret_cast<const int*>(a.flag_ptrs[a.rank]) + (phase * MAX_CTAS + blockIdx.x) * MAX_RANKS + peer;
+    const uint64_t t0 = globaltimer_ns();
+    uint32_t polls = 0;
+    while (ld_acquire_sys(local) < a.epoch) {
+      if ((++polls & 255u) == 0u && globaltimer_ns() - t0 > SB_WAIT_LIMIT_NS) {
+        *s_fail = 1;
+        if (a.status) atomicCAS(a.status, 0, ST_TIMEOUT_PEER_FLAG);
+        break;
+      }
+    }
+  }
+  __syncthreads();
+  return *s_fail == 0;
+}
+
+__device__ __forceinline__ void slice_of(const CommArgs& a, long long& begin, long long& end) {
+  const long long vecs = (a.hi - a.lo) / 4;
+  const long long per = (vecs + a.world - 1) / a.world;
+  begin = min(vecs, per * a.rank);
+  end = min(vecs, begin + per);
+}
+
+__global__ void __launch_bounds__(512) allreduce_two_shot_kernel(const CommArgs a) {
+  __shared__ int s_fail;
+  __shared__ unsigned long long s_peers[MAX_RANKS];
+  if (threadIdx.x == 0) s_fail = 0;
+  if (threadIdx.x < a.world) s_peers[threadIdx.x] = a.peer_ptrs[threadIdx.x];
+  __syncthreads();
+  if (!rank_barrier(a, 0, &s_fail)) return;
+  long long begin, end;
+  slice_of(a, begin, end);
+  const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+  for (long long i = begin + blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < end; i += stride) {
+    const long long off = a.lo / 4 + i;
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int p = 0; p < a.world; ++p) {
+      const int src = (a.rank + p) % a.world;  // start at the local copy, spread peer traffic
+      const float4 v = reinterpret_cast<const float4*>(s_peers[src])[off];
+      acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+    }
+    acc.x *= a.scale; acc.y *= a.scale; acc.z *= a.scale; acc.w *= a.scale;
+    for (int p = 0; p < a.world; ++p) {
+      const int dst = (a.rank + p) % a.world;
+      reinterpret_cast<float4*>(s_peers[dst])[off] = acc;
+    }
+  }
+  rank_barrier(a, 1, &s_fail);
+}
+
+__global__ void __launch_bounds__(512) allreduce_multimem_kernel(const CommArgs a) {
+  __shared__ int s_fail;
+  if (threadIdx.x == 0) s_fail = 0;
+  __syncthreads();
+  if (!rank_barrier(a, 0, &s_fail)) return;
+  long long begin, end;
+  slice_of(a, begin, end);
+  const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+  for (long long i = begin + blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < end; i += stride) {
+    float* addr = reinterpret_cast<float*>(a.mc_ptr) + a.lo + i * 4;
+    float x, y, z, w;
+    asm volatile("multimem.ld_reduce.relaxed.sys.global.add.v4.f32 {%0, %1, %2, %3}, [%4];"
+                 : "=f"(x), "=f"(y), "=f"(z), "=f"(w)
+                 : "l"(addr)
+                 : "memory");
+    x *= a.scale; y *= a.scale; z *= a.scale; w *= a.scale;
+    asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(x), "f"(y), "f"(z), "f"(w)
+                 : "memory");
+  }
+  rank_barrier(a, 1, &s_fail);
+}
+
+static int launch_allreduce(bool multimem, const CommArgs& a, int sms, cudaStream_t st) {
+  if (a.world < 1 || a.world > MAX_RANKS) return -2;
+  if ((a.lo & 3) || (a.hi & 3) || a.hi < a.lo) return -3;
+  const long long vecs = (a.hi - a.lo) / 4 / (a.world > 0 ? a.world : 1);
+  int grid = static_cast<int>((vecs + 511) / 512);
+  const int cap = sms < MAX_CTAS ? sms : MAX_CTAS;
+  if (grid > cap / 2) grid = cap / 2;  // leave SMs to the compute kernels this overlaps with
+  if (grid < 1) grid = 1;
+  if (multimem) allreduce_multimem_kernel<<<grid, 512, 0, st>>>(a);
+  else allreduce_two_shot_kernel<<<grid, 512, 0, st>>>(a);
+  return static_cast<int>(cudaGetLastError());
+}
+
+}  // namespace sb
+
+extern "C" int sb_comm_flag_ints() { return 2 * sb::MAX_CTAS * sb::MAX_RANKS; }
+
+extern "C" int sb_allreduce_two_shot(const void* peer_ptrs, const void* flag_ptrs, unsigned long long mc_ptr, int rank, int world,
+                                     long long lo, long long hi, float scale, int epoch, int sms, int* status, void* stream) {
+  sb::CommArgs a{static_cast<const unsigned long long*>(peer_ptrs), static_cast<const unsigned long long*>(flag_ptrs), mc_ptr, rank,
+                 world, lo, hi, scale, epoch, status};
+  return sb::launch_allreduce(false, a, sms, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int sb_allreduce_multimem(const void* peer_ptrs, const void* flag_ptrs, unsigned long long mc_ptr, int rank, int world,
+                                     long long lo, long long hi, float scale, int epoch, int sms, int* status, void* stream) {
+  if (mc_ptr == 0) return -4;
+  sb::CommArgs a{static_cast<const unsigned long long*>(peer_ptrs), static_cast<const unsigned long long*>(flag_ptrs), mc_ptr, rank,
+                 world, lo, hi, scale, epoch, status};
+  return sb::launch_allreduce(true, a, sms, static_cast<cudaStream_t>(stream));
+}

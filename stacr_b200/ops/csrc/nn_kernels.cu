@@ -1,0 +1,409 @@
+// Bandwidth-bound model ops for bf16 training on sm_100a: LayerNorm forward/backward (fp32
+// statistics kept per row), GELU forward/backward (erf and tanh forms), and a fused softmax
+// cross-entropy whose forward pass also writes the logit gradient, so the logits are read
+// twice and written once in total.  All loads and stores are 16-byte vectors.
+// These replace the ATen LayerNorm / GELU / log-softmax + NLL kernels the reference reaches
+// through the Hugging Face model code it trains.
+#include "common.cuh"
+
+namespace sb {
+
+__device__ __forceinline__ void unpack8(const uint4& raw, float (&f)[8]) {
+  const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    f[2 * i] = __low2float(p[i]);
+    f[2 * i + 1] = __high2float(p[i]);
+  }
+}
+__device__ __forceinline__ uint4 pack8(const float (&f)[8]) {
+  return make_uint4(pack_bf16x2(f[0], f[1]), pack_bf16x2(f[2], f[3]), pack_bf16x2(f[4], f[5]), pack_bf16x2(f[6], f[7]));
+}
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int off = 16; off; off >>= 1) v += __shfl_xor_sync(0xffffffffu, v, off);
+  return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int off = 16; off; off >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, off));
+  return v;
+}
+
+// ---------------------------------------------------------------------------- LayerNorm
+// One warp per row; the row (n <= 16384, n % 8 == 0) lives in registers: MAXV vectors of 8 per lane.
+template <int MAXV>
+__global__ void __launch_bounds__(256) layernorm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict__ gamma,
+                                                            const float* __restrict__ beta, int rows, int n, float eps,
+                                                            __nv_bfloat16* __restrict__ y, float* __restrict__ mean_out,
+                                                            float* __restrict__ rstd_out) {
+  const int lane = threadIdx.x & 31;
+  const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (row >= rows) return;
+  const int nvec = n >> 3;
+  const uint4* xr = reinterpret_cast<const uint4*>(x + static_cast<size_t>(row) * n);
+  float v[MAXV][8];
+  float sum = 0.f;
+#pragma unroll
+  for (int i = 0; i < MAXV; ++i) {
+    const int vi = lane + i * 32;
+    if (vi < nvec) {
+      unpack8(__ldg(xr + vi), v[i]);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) sum += v[i][j];
+    }
+  }
+  const float mean = warp_sum(sum) / n;
+  float sq = 0.f;
+#pragma unroll
+  for (int i = 0; i < MAXV; ++i) {
+    if (lane + i * 32 < nvec) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const float d = v[i][j] - mean;
+        sq = fmaf(d, d, sq);
+      }
+    }
+  }
+  const float rstd = rsqrtf(warp_sum(sq) / n + eps);
+  if (lane == 0) {
+    mean_out[row] = mean;
+    rstd_out[row] = rstd;
+  }
+  uint4* yr = reinterpret_cast<uint4*>(y + static_cast<size_t>(row) * n);
+#pragma unroll
+  for (int i = 0; i < MAXV; ++i) {
+    const int vi = lane + i * 32;
+    if (vi < nvec) {
+      float o[8];
+      const float4 g0 = __ldg(reinterpret_cast<const float4*>(gamma) + vi * 2), g1 = __ldg(reinterpret_cast<const float4*>(gamma) + vi * 2 + 1);
+      const float g[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w};
+      float b[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+      if (beta) {
+        const float4 b0 = __ldg(reinterpret_cast<const float4*>(beta) + vi * 2), b1 = __ldg(reinterpret_cast<const float4*>(beta) + vi * 2 + 1);
+        b[0] = b0.x; b[1] = b0.y; b[2] = b0.z; b[3] = b0.w; b[4] = b1.x; b[5] = b1.y; b[6] = b1.z; b[7] = b1.w;
+      }
+#pragma unroll
+      for (int j = 0; j < 8; ++j) o[j] = (v[i][j] - mean) * rstd * g[j] + b[j];
+      yr[vi] = pack8(o);
+    }
+  }
+}
+
+// dx per row (one warp per row, row kept packed in registers and unpacked twice).
+template <int MAXV>
+__global__ void __launch_bounds__(256) layernorm_bwd_dx_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x,
+                                                               const float* __restrict__ gamma, const float* __restrict__ mean,
+                                                               const float* __restrict__ rstd, int rows, int n,
+                                                               __nv_bfloat16* __restrict__ dx) {
+  const int lane = threadIdx.x & 31;
+  const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (row >= rows) return;
+  const int nvec = n >> 3;
+  const uint4* xr = reinterpret_cast<const uint4*>(x + static_cast<size_t>(row) * n);
+  const uint4* dr = reinterpret_cast<const uint4*>(dy + static_cast<size_t>(row) * n);
+  const float mu = mean[row], rs = rstd[row];
+  uint4 xraw[MAXV], draw[MAXV];
+  float s1 = 0.f, s2 = 0.f;
+#pragma unroll
+  for (int i = 0; i < MAXV; ++i) {
+    const int vi = lane + i * 32;
+    if (vi < nvec) {
+      xraw[i] = __ldg(xr + vi);
+      draw[i] = __ldg(dr + vi);
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < MAXV; ++i) {
+    const int vi = lane + i * 32;
+    if (vi < nvec) {
+      float xv[8], dv[8];
+      unpack8(xraw[i], xv);
+      unpack8(draw[i], dv);
+      const float4 g0 = __ldg(reinterpret_cast<const float4*>(gamma) + vi * 2), g1 = __ldg(reinterpret_cast<const float4*>(gamma) + vi * 2 + 1);
+      const float g[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w};
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const float dg = dv[j] * g[j];
+        s1 += dg;
+        s2 = fmaf(dg, (xv[j] - mu) * rs, s2);
+      }
+    }
+  }
+  s1 = warp_sum(s1) / n;
+  s2 = warp_sum(s2) / n;
+  uint4* dxr = reinterpret_cast<uint4*>(dx + static_cast<size_t>(row) * n);
+#pragma unroll
+  for (int i = 0; i < MAXV; ++i) {
+    const int vi = lane + i * 32;
+    if (vi < nvec) {
+      float xv[8], dv[8], o[8];
+      unpack8(xraw[i], xv);
+      unpack8(draw[i], dv);
+      const float4 g0 = __ldg(reinterpret_cast<const float4*>(gamma) + vi * 2), g1 = __ldg(reinterpret_cast<const float4*>(gamma) + vi * 2 + 1);
+      const float g[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w};
+#pragma unroll
+      for (int j = 0; j < 8; ++j) o[j] = rs * (dv[j] * g[j] - s1 - (xv[j] - mu) * rs * s2);
+      dxr[vi] = pack8(o);
+    }
+  }
+}
+
+// dgamma[c] = sum_rows dy * xhat, dbeta[c] = sum_rows dy.  CTA = 64 columns x a slab of rows; 8 column
+// threads x 32 row lanes; lanes reduce through shared memory, one atomic per column per CTA.
+__global__ void __launch_bounds__(256) layernorm_bwd_params_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x,
+                                                                   const float* __restrict__ mean, const float* __restrict__ rstd,
+                                                                   int rows, int n, int slab, float* __restrict__ dgamma,
+                                                                   float* __restrict__ dbeta) {
+  __shared__ float s_g[32][65], s_b[32][65];
+  const int tx = threadIdx.x & 7, ty = threadIdx.x >> 3;
+  const int col = blockIdx.x * 64 + tx * 8;
+  const int r0 = blockIdx.y * slab, r1 = min(rows, r0 + slab);
+  float ag[8] = {0, 0, 0, 0, 0, 0, 0, 0}, ab[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+  if (col < n) {
+    for (int row = r0 + ty; row < r1; row += 32) {
+      float xv[8], dv[8];
+      unpack8(__ldg(reinterpret_cast<const uint4*>(x + static_cast<size_t>(row) * n + col)), xv);
+      unpack8(__ldg(reinterpret_cast<const uint4*>(dy + static_cast<size_t>(row) * n + col)), dv);
+      const float mu = mean[row], rs = rstd[row];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        ag[j] = fmaf(dv[j], (xv[j] - mu) * rs, ag[j]);
+        ab[j] += dv[j];
+      }
+    }
+  }
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    s_g[ty][tx * 8 + j] = ag[j];
+    s_b[ty][tx * 8 + j] = ab[j];
+  }
+  __syncthreads();
+  if (threadIdx.x < 64 && blockIdx.x * 64 + threadIdx.x < n) {
+    float g = 0.f, b = 0.f;
+#pragma unroll
+    for (int r = 0; r < 32; ++r) {
+      g += s_g[r][threadIdx.x];
+      b += s_b[r][threadIdx.x];
+    }
+    atomicAdd(dgamma + blockIdx.x * 64 + threadIdx.x, g);
+    atomicAdd(dbeta + blockIdx.x * 64 + threadIdx.x, b);
+  }
+}
+
+// ---------------------------------------------------------------------------- GELU
+__device__ __forceinline__ float gelu_f(float x, bool tanh_form) {
+  if (tanh_form) {
+    const float u = 0.7978845608028654f * (x + 0.044715f * x * x * x);
+    return 0.5f * x * (1.f + tanhf(u));
+  }
+  return 0.5f * x * (1.f + erff(x * 0.7071067811865476f));
+}
+__device__ __forceinline__ float gelu_grad_f(float x, bool tanh_form) {
+  if (tanh_form) {
+    const float u = 0.7978845608028654f * (x + 0.044715f * x * x * x);
+    const float t = tanhf(u);
+    const float du = 0.7978845608028654f * (1.f + 3.f * 0.044715f * x * x);
+    return 0.5f * (1.f + t) + 0.5f * x * (1.f - t * t) * du;
+  }
+  const float cdf = 0.5f * (1.f + erff(x * 0.7071067811865476f));
+  const float pdf = 0.3989422804014327f * __expf(-0.5f * x * x);
+  return cdf + x * pdf;
+}
+
+__global__ void __launch_bounds__(256) gelu_fwd_kernel(const uint4* __restrict__ x, uint4* __restrict__ y, size_t nvec, int tanh_form) {
+  for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < nvec; i += static_cast<size_t>(gridDim.x) * blockDim.x) {
+    float v[8];
+    unpack8(__ldg(x + i), v);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) v[j] = gelu_f(v[j], tanh_form);
+    y[i] = pack8(v);
+  }
+}
+__global__ void __launch_bounds__(256) gelu_bwd_kernel(const uint4* __restrict__ dy, const uint4* __restrict__ x, uint4* __restrict__ dx,
+                                                       size_t nvec, int tanh_form) {
+  for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < nvec; i += static_cast<size_t>(gridDim.x) * blockDim.x) {
+    float v[8], d[8];
+    unpack8(__ldg(x + i), v);
+    unpack8(__ldg(dy + i), d);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) v[j] = d[j] * gelu_grad_f(v[j], tanh_form);
+    dx[i] = pack8(v);
+  }
+}
+
+// ---------------------------------------------------------------------------- cross-entropy
+// One CTA per row.  Pass 1: running max and sum of exponentials (online softmax); pass 2 writes
+// dlogits = (softmax - onehot) * inv_valid and the row loss.  Rows with target == -100 get zeros.
+__global__ void __launch_bounds__(512) cross_entropy_kernel(const __nv_bfloat16* __restrict__ logits, const long long* __restrict__ target,
+                                                            int v, const float* __restrict__ inv_valid, __nv_bfloat16* __restrict__ dlogits,
+                                                            float* __restrict__ row_loss) {
+  __shared__ float s_m[16], s_s[16];
+  __shared__ float s_max, s_lse;
+  const int row = blockIdx.x;
+  const long long tgt = target[row];
+  const int nvec = v >> 3;
+  const uint4* lr = reinterpret_cast<const uint4*>(logits + static_cast<size_t>(row) * v);
+  uint4* dr = reinterpret_cast<uint4*>(dlogits + static_cast<size_t>(row) * v);
+  if (tgt < 0) {  // ignored row
+    for (int i = threadIdx.x; i < nvec; i += blockDim.x) dr[i] = make_uint4(0, 0, 0, 0);
+    if (threadIdx.x == 0) row_loss[row] = 0.f;
+    return;
+  }
+  float m = -INFINITY, s = 0.f;
+  for (int i = threadIdx.x; i < nvec; i += blockDim.x) {
+    float f[8];
+    unpack8(__ldg(lr + i), f);
+    float lm = f[0];
+#pragma unroll
+    for (int j = 1; j < 8; ++j) lm = fmaxf(lm, f[j]);
+    const float nm = fmaxf(m, lm);
+    float add = 0.f;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) add += __expf(f[j] - nm);
+    s = s * __expf(m - nm) + add;
+    m = nm;
+  }
+  const float wm = warp_max(m);
+  s = warp_sum(s * __expf(m - wm));
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  if (lane == 0) {
+    s_m[warp] = wm;
+    s_s[warp] = s;
+  }
+  __syncthreads();
+  if (warp == 0) {
+    const int nw = blockDim.x >> 5;
+    float mm = lane < nw ? s_m[lane] : -INFINITY;
+    float ss = lane < nw ? s_s[lane] : 0.f;
+    const float gm = warp_max(mm);
+    ss = warp_sum(ss * __expf(mm - gm));
+    if (lane == 0) {
+      s_max = gm;
+      s_lse = gm + __logf(ss);
+    }
+  }
+  __syncthreads();
+  const float lse = s_lse;
+  const float scale = *inv_valid;
+  for (int i = threadIdx.x; i < nvec; i += blockDim.x) {
+    float f[8];
+    unpack8(__ldg(lr + i), f);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      float p = __expf(f[j] - lse);
+      if (i * 8 + j == tgt) {
+        row_loss[row] = lse - f[j];
+        p -= 1.f;
+      }
+      f[j] = p * scale;
+    }
+    dr[i] = pack8(f);
+  }
+}
+
+// ---------------------------------------------------------------------------- cast
+__global__ void __launch_bounds__(256) cast_f32_bf16_kernel(const float4* __restrict__ src, uint2* __restrict__ dst, size_t nvec4) {
+  for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < nvec4; i += static_cast<size_t>(gridDim.x) * blockDim.x) {
+    const float4 v = __ldg(src + i);
+    dst[i] = make_uint2(pack_bf16x2(v.x, v.y), pack_bf16x2(v.z, v.w));
+  }
+}
+
+template <int MAXV>
+static int ln_fwd_launch(const void* x, const float* g, const float* b, int rows, int n, float eps, void* y, float* mean, float* rstd,
+                         cudaStream_t st) {
+  const int wpb = 8;
+  layernorm_fwd_kernel<MAXV><<<(rows + wpb - 1) / wpb, wpb * 32, 0, st>>>(static_cast<const __nv_bfloat16*>(x), g, b, rows, n, eps,
+                                                                          static_cast<__nv_bfloat16*>(y), mean, rstd);
+  return static_cast<int>(cudaGetLastError());
+}
+template <int MAXV>
+static int ln_bwd_launch(const void* dy, const void* x, const float* g, const float* mean, const float* rstd, int rows, int n, void* dx,
+                         float* dg, float* db, int sms, cudaStream_t st) {
+  const int wpb = 8;
+  layernorm_bwd_dx_kernel<MAXV><<<(rows + wpb - 1) / wpb, wpb * 32, 0, st>>>(
+      static_cast<const __nv_bfloat16*>(dy), static_cast<const __nv_bfloat16*>(x), g, mean, rstd, rows, n, static_cast<__nv_bfloat16*>(dx));
+  const int colblocks = (n + 63) / 64;
+  int slabs = (sms * 4 + colblocks - 1) / colblocks;
+  if (slabs < 1) slabs = 1;
+  int slab = (rows + slabs - 1) / slabs;
+  if (slab < 32) slab = 32;
+  dim3 grid(colblocks, (rows + slab - 1) / slab);
+  layernorm_bwd_params_kernel<<<grid, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(dy), static_cast<const __nv_bfloat16*>(x), mean, rstd,
+                                                    rows, n, slab, dg, db);
+  return static_cast<int>(cudaGetLastError());
+}
+
+}  // namespace sb
+
+// y = LayerNorm(x) * gamma + beta for bf16 x [rows, n] (n % 8 == 0, n <= 4096); gamma/beta fp32.
+extern "C" int sb_layernorm_fwd(const void* x, const float* gamma, const float* beta, int rows, int n, float eps, void* y,
+                                float* mean, float* rstd, void* stream) {
+  using namespace sb;
+  if (rows <= 0) return 0;
+  if (n % 8 || n > 4096) return -2;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int nv = (n / 8 + 31) / 32;
+  if (nv <= 4) return ln_fwd_launch<4>(x, gamma, beta, rows, n, eps, y, mean, rstd, st);
+  if (nv <= 8) return ln_fwd_launch<8>(x, gamma, beta, rows, n, eps, y, mean, rstd, st);
+  if (nv <= 16) return ln_fwd_launch<16>(x, gamma, beta, rows, n, eps, y, mean, rstd, st);
+  return -3;
+}
+
+// dx bf16; dgamma/dbeta fp32 [n], zeroed by the caller.
+extern "C" int sb_layernorm_bwd(const void* dy, const void* x, const float* gamma, const float* mean, const float* rstd, int rows,
+                                int n, void* dx, float* dgamma, float* dbeta, int sms, void* stream) {
+  using namespace sb;
+  if (rows <= 0) return 0;
+  if (n % 8 || n > 4096) return -2;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int nv = (n / 8 + 31) / 32;
+  if (nv <= 4) return ln_bwd_launch<4>(dy, x, gamma, mean, rstd, rows, n, dx, dgamma, dbeta, sms, st);
+  if (nv <= 8) return ln_bwd_launch<8>(dy, x, gamma, mean, rstd, rows, n, dx, dgamma, dbeta, sms, st);
+  if (nv <= 16) return ln_bwd_launch<16>(dy, x, gamma, mean, rstd, rows, n, dx, dgamma, dbeta, sms, st);
+  return -3;
+}
+
+extern "C" int sb_gelu_fwd(const void* x, void* y, long long numel, int tanh_form, int sms, void* stream) {
+  if (numel <= 0) return 0;
+  if (numel % 8) return -2;
+  const size_t nvec = static_cast<size_t>(numel / 8);
+  size_t blocks = (nvec + 255) / 256;
+  if (blocks > static_cast<size_t>(sms) * 16) blocks = static_cast<size_t>(sms) * 16;
+  sb::gelu_fwd_kernel<<<static_cast<unsigned>(blocks), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const uint4*>(x), static_cast<uint4*>(y), nvec, tanh_form);
+  return static_cast<int>(cudaGetLastError());
+}
+
+extern "C" int sb_gelu_bwd(const void* dy, const void* x, void* dx, long long numel, int tanh_form, int sms, void* stream) {
+  if (numel <= 0) return 0;
+  if (numel % 8) return -2;
+  const size_t nvec = static_cast<size_t>(numel / 8);
+  size_t blocks = (nvec + 255) / 256;
+  if (blocks > static_cast<size_t>(sms) * 16) blocks = static_cast<size_t>(sms) * 16;
+  sb::gelu_bwd_kernel<<<static_cast<unsigned>(blocks), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const uint4*>(dy), static_cast<const uint4*>(x), static_cast<uint4*>(dx), nvec, tanh_form);
+  return static_cast<int>(cudaGetLastError());
+}
+
+// Row losses and dlogits for bf16 logits [rows, v] (v % 8 == 0); inv_valid = 1 / (#targets != -100) on the device.
+extern "C" int sb_cross_entropy(const void* logits, const long long* target, int rows, int v, const float* inv_valid, void* dlogits,
+                                float* row_loss, void* stream) {
+  if (rows <= 0) return 0;
+  if (v % 8) return -2;
+  sb::cross_entropy_kernel<<<rows, 512, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(logits), target, v, inv_valid, static_cast<__nv_bfloat16*>(dlogits), row_loss);
+  return static_cast<int>(cudaGetLastError());
+}
+
+extern "C" int sb_cast_f32_bf16(const float* src, void* dst, long long numel, int sms, void* stream) {
+  if (numel <= 0) return 0;
+  if (numel % 4) return -2;
+  const size_t nvec = static_cast<size_t>(numel / 4);
+  size_t blocks = (nvec + 255) / 256;
+  if (blocks > static_cast<size_t>(sms) * 16) blocks = static_cast<size_t>(sms) * 16;
+  sb::cast_f32_bf16_kernel<<<static_cast<unsigned>(blocks), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      reinterpret_cast<const float4*>(src), static_cast<uint2*>(dst), nvec);
+  return static_cast<int>(cudaGetLastError());
+}

@@ -89,4 +89,5 @@ def gemm(
         _lib.ptr(_lib.status_word(a.device)), _lib.stream_ptr(),
     )
     _lib.check_rc(rc, "sb_gemm_bf16")
+    _lib.count(1)
     return out

@@ -1,0 +1,80 @@
+"""ctypes entry points for ``csrc/nn_kernels.cu`` (LayerNorm, GELU, cross-entropy, casts)."""
+
+from __future__ import annotations
+
+import ctypes
+
+import torch
+
+from . import _lib
+
+c_int, c_ll, c_float = ctypes.c_int, ctypes.c_longlong, ctypes.c_float
+
+
+def _f32(t):
+    return None if t is None else t.detach().float().contiguous()
+
+
+def layernorm_fwd(x2d: torch.Tensor, weight, bias, eps: float):
+    rows, n = x2d.shape
+    y = torch.empty_like(x2d)
+    mean = torch.empty(rows, dtype=torch.float32, device=x2d.device)
+    rstd = torch.empty(rows, dtype=torch.float32, device=x2d.device)
+    rc = _lib.load().sb_layernorm_fwd(_lib.ptr(x2d), _lib.ptr(_f32(weight)), _lib.ptr(_f32(bias)), c_int(rows), c_int(n), c_float(eps),
+                                      _lib.ptr(y), _lib.ptr(mean), _lib.ptr(rstd), _lib.stream_ptr())
+    _lib.check_rc(rc, "sb_layernorm_fwd")
+    _lib.count(1)
+    return y, mean, rstd
+
+
+def layernorm_bwd(dy2d, x2d, weight, mean, rstd):
+    rows, n = x2d.shape
+    dx = torch.empty_like(x2d)
+    dwb = torch.zeros(2, n, dtype=torch.float32, device=x2d.device)
+    rc = _lib.load().sb_layernorm_bwd(_lib.ptr(dy2d), _lib.ptr(x2d), _lib.ptr(_f32(weight)), _lib.ptr(mean), _lib.ptr(rstd), c_int(rows),
+                                      c_int(n), _lib.ptr(dx), _lib.ptr(dwb[0]), _lib.ptr(dwb[1]), c_int(_lib.sm_count(x2d.device)),
+                                      _lib.stream_ptr())
+    _lib.check_rc(rc, "sb_layernorm_bwd")
+    _lib.count(2)
+    return dx, dwb[0], dwb[1]
+
+
+def gelu_fwd(x: torch.Tensor, tanh_form: bool) -> torch.Tensor:
+    y = torch.empty_like(x)
+    rc = _lib.load().sb_gelu_fwd(_lib.ptr(x), _lib.ptr(y), c_ll(x.numel()), c_int(int(tanh_form)), c_int(_lib.sm_count(x.device)),
+                                 _lib.stream_ptr())
+    _lib.check_rc(rc, "sb_gelu_fwd")
+    _lib.count(1)
+    return y
+
+
+def gelu_bwd(dy: torch.Tensor, x: torch.Tensor, tanh_form: bool) -> torch.Tensor:
+    dx = torch.empty_like(x)
+    rc = _lib.load().sb_gelu_bwd(_lib.ptr(dy), _lib.ptr(x), _lib.ptr(dx), c_ll(x.numel()), c_int(int(tanh_form)),
+                                 c_int(_lib.sm_count(x.device)), _lib.stream_ptr())
+    _lib.check_rc(rc, "sb_gelu_bwd")
+    _lib.count(1)
+    return dx
+
+
+def cross_entropy_fwd(logits: torch.Tensor, target: torch.Tensor):
+    """Mean loss over valid rows and ``d loss / d logits`` (already divided by the valid count)."""
+    rows, v = logits.shape
+    target = target.to(torch.int64)
+    inv_valid = 1.0 / (target != -100).sum().clamp_min(1).float()
+    dlogits = torch.empty_like(logits)
+    row_loss = torch.empty(rows, dtype=torch.float32, device=logits.device)
+    rc = _lib.load().sb_cross_entropy(_lib.ptr(logits), _lib.ptr(target), c_int(rows), c_int(v), _lib.ptr(inv_valid), _lib.ptr(dlogits),
+                                      _lib.ptr(row_loss), _lib.stream_ptr())
+    _lib.check_rc(rc, "sb_cross_entropy")
+    _lib.count(1)
+    return row_loss.sum() * inv_valid, dlogits
+
+
+def cast_bf16(src: torch.Tensor) -> torch.Tensor:
+    """fp32 -> bf16 copy (``numel % 4 == 0``)."""
+    dst = torch.empty(src.shape, dtype=torch.bfloat16, device=src.device)
+    rc = _lib.load().sb_cast_f32_bf16(_lib.ptr(src), _lib.ptr(dst), c_ll(src.numel()), c_int(_lib.sm_count(src.device)), _lib.stream_ptr())
+    _lib.check_rc(rc, "sb_cast_f32_bf16")
+    _lib.count(1)
+    return dst

@@ -1,0 +1,109 @@
+"""Normalisation, activation and loss ops of the model zoo.
+
+For bf16 CUDA tensors these dispatch to the sm_100a kernels in ``csrc/nn_kernels.cu`` (fused
+LayerNorm forward/backward with fp32 statistics, GELU forward/backward, fused softmax
+cross-entropy that writes the logit gradient in place of a second pass).  Everything else uses
+the framework ops, which are also the oracles of the kernel tests.
+"""
+
+from __future__ import annotations
+
+import torch
+from torch.nn import functional as F
+
+from . import _lib
+
+
+def _kernel_tensor(x: torch.Tensor) -> bool:
+    return x.is_cuda and x.dtype == torch.bfloat16
+
+
+# ------------------------------------------------------------------------------ LayerNorm
+class _LayerNormFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, weight, bias, eps):
+        from . import nn_kernels
+
+        x2d = x.reshape(-1, x.shape[-1]).contiguous()
+        y, mean, rstd = nn_kernels.layernorm_fwd(x2d, weight, bias, eps)
+        ctx.save_for_backward(x2d, weight, mean, rstd)
+        ctx.has_bias = bias is not None
+        return y.reshape(x.shape)
+
+    @staticmethod
+    def backward(ctx, dy):
+        from . import nn_kernels
+
+        x2d, weight, mean, rstd = ctx.saved_tensors
+        dy2d = dy.reshape(-1, dy.shape[-1]).contiguous()
+        dx, dw, db = nn_kernels.layernorm_bwd(dy2d, x2d, weight, mean, rstd)
+        return dx.reshape(dy.shape), dw.to(weight.dtype), (db.to(weight.dtype) if ctx.has_bias else None), None
+
+
+def layer_norm(x, weight, bias, eps: float = 1e-5):
+    if _kernel_tensor(x) and x.shape[-1] % 8 == 0 and x.shape[-1] <= 16384:
+        return _LayerNormFn.apply(x, weight, bias, eps)
+    return F.layer_norm(x, (x.shape[-1],), weight, bias, eps)
+
+
+# ------------------------------------------------------------------------------ GELU
+class _GeluFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, tanh_form: bool):
+        from . import nn_kernels
+
+        xc = x.contiguous()
+        ctx.save_for_backward(xc)
+        ctx.tanh_form = tanh_form
+        return nn_kernels.gelu_fwd(xc, tanh_form)
+
+    @staticmethod
+    def backward(ctx, dy):
+        from . import nn_kernels
+
+        (x,) = ctx.saved_tensors
+        return nn_kernels.gelu_bwd(dy.contiguous(), x, ctx.tanh_form), None
+
+
+def gelu(x, approximate: str = "none"):
+    if _kernel_tensor(x) and x.numel() % 8 == 0:
+        return _GeluFn.apply(x, approximate == "tanh")
+    return F.gelu(x, approximate=approximate)
+
+
+# ------------------------------------------------------------------------------ cross-entropy
+class _CrossEntropyFn(torch.autograd.Function):
+    """Mean cross-entropy over rows with ``target != -100``; the forward also produces d(logits)."""
+
+    @staticmethod
+    def forward(ctx, logits, target):
+        from . import nn_kernels
+
+        loss, dlogits = nn_kernels.cross_entropy_fwd(logits.contiguous(), target.contiguous())
+        ctx.save_for_backward(dlogits)
+        return loss
+
+    @staticmethod
+    def backward(ctx, dloss):
+        (dlogits,) = ctx.saved_tensors
+        # dlogits already holds (softmax - onehot) / n_valid; scale by the upstream scalar gradient
+        return dlogits * dloss.to(dlogits.dtype), None
+
+
+def cross_entropy(logits, target):
+    if _kernel_tensor(logits) and logits.shape[-1] % 8 == 0:
+        return _CrossEntropyFn.apply(logits, target)
+    return F.cross_entropy(logits.float(), target, ignore_index=-100)
+
+
+def linear_cross_entropy(hidden, weight, target, chunk: int = 0):
+    """``cross_entropy(hidden @ weight^T, target)`` evaluated in row chunks to bound the logits workspace."""
+    if not chunk or hidden.shape[0] <= chunk:
+        return cross_entropy(F.linear(hidden, weight), target)
+    valid = (target != -100).sum().clamp_min(1)
+    total = hidden.new_zeros((), dtype=torch.float32)
+    for lo in range(0, hidden.shape[0], chunk):
+        t = target[lo:lo + chunk]
+        n = (t != -100).sum()
+        total = total + cross_entropy(F.linear(hidden[lo:lo + chunk], weight), t).float() * n
+    return total / valid

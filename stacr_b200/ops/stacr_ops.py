@@ -93,6 +93,7 @@ def residual_topk(
         _lib.ptr(_lib.status_word(dev)), _lib.stream_ptr(),
     )
     _lib.check_rc(rc, "sb_residual_topk")
+    _lib.count(4)
     return idx, val, scale
 
 
@@ -106,6 +107,7 @@ def residual_gather(x, coeff, basis_bf16, idx: torch.Tensor) -> torch.Tensor:
         _lib.ptr(None if is32 else idx), _lib.ptr(idx if is32 else None), c_ll(idx.numel()), _lib.ptr(out), _lib.stream_ptr(),
     )
     _lib.check_rc(rc, "sb_residual_gather")
+    _lib.count(1)
     return out
 
 
@@ -117,6 +119,7 @@ def residual_block_energy(x, coeff, basis_bf16, block: int) -> torch.Tensor:
         c_int(block), _lib.ptr(out), _lib.stream_ptr(),
     )
     _lib.check_rc(rc, "sb_residual_block_energy")
+    _lib.count(1)
     return out
 
 
@@ -139,6 +142,7 @@ def oja_update(basis_fp32, g, y, rows: int, lr: float):
         c_int(rp), _lib.ptr(_lib.status_word(dev)), _lib.stream_ptr(),
     )
     _lib.check_rc(rc, "sb_oja_update")
+    _lib.count(1)
     return q_out, qb, qt
 
 
@@ -175,6 +179,7 @@ def weight_grad(
             _lib.stream_ptr(),
         )
         _lib.check_rc(rc, "sb_residual_bucket")
+        _lib.count(3)
     shape = (in_features, out_features) if transposed else (out_features, in_features)
     out = torch.empty(shape, dtype=out_dtype, device=dev)
     rc = _lib.load().sb_dw_fused(
@@ -183,6 +188,7 @@ def weight_grad(
         c_int(int(out_dtype == torch.bfloat16)), _lib.ptr(out), _lib.stream_ptr(),
     )
     _lib.check_rc(rc, "sb_dw_fused")
+    _lib.count(1)
     return out
 
 
@@ -191,4 +197,5 @@ def colsum(dy: torch.Tensor) -> torch.Tensor:
     out = torch.zeros(o, dtype=torch.float32, device=dy.device)
     rc = _lib.load().sb_colsum_bf16(_lib.ptr(dy), c_int(rows), c_int(o), c_int(dy.stride(0)), _lib.ptr(out), _lib.stream_ptr())
     _lib.check_rc(rc, "sb_colsum_bf16")
+    _lib.count(1)
     return out

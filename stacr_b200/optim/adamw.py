@@ -1,0 +1,215 @@
+"""AdamW with fp32 or 8-bit block-wise moments, stepped by one multi-tensor kernel launch per group.
+
+On CUDA the update runs in ``csrc/optim.cu``; on CPU the same arithmetic is done with framework
+ops (the 8-bit code path included, so the codec is testable without a GPU).  ``AdamW8bit``
+replaces the external 8-bit optimizer the reference builds through
+stacr/protocols/baselines/bnb_optimizer.py:61-176 (tensors below ``min_8bit_size`` elements keep
+fp32 moments, block size 256).
+"""
+
+from __future__ import annotations
+
+import ctypes
+import math
+
+import numpy as np
+import torch
+
+BLOCK = 256
+
+
+# ----------------------------------------------------------------------------- 8-bit codec (framework ops)
+def encode_first_moment(m: torch.Tensor):
+    """Signed square-root companding, per 256-element block.  Returns ``(uint8 codes, fp32 absmax)``."""
+    flat = m.reshape(-1).float()
+    pad = (-flat.numel()) % BLOCK
+    blocks = torch.nn.functional.pad(flat, (0, pad)).view(-1, BLOCK)
+    amax = blocks.abs().amax(1)
+    safe = amax.clamp_min(1e-38)[:, None]
+    s = torch.sqrt((blocks.abs() / safe).clamp_max(1.0)) * torch.sign(blocks)
+    codes = (128 + torch.round(s * 127)).to(torch.uint8)
+    codes = torch.where(amax[:, None] > 0, codes, torch.full_like(codes, 128))
+    return codes.view(-1)[: flat.numel()], amax
+
+
+def decode_first_moment(codes: torch.Tensor, amax: torch.Tensor) -> torch.Tensor:
+    n = codes.numel()
+    pad = (-n) % BLOCK
+    c = torch.nn.functional.pad(codes.float(), (0, pad), value=128.0).view(-1, BLOCK)
+    s = (c - 128.0) / 127.0
+    return (torch.sign(s) * s * s * amax[:, None]).view(-1)[:n]
+
+
+def encode_second_moment(v: torch.Tensor):
+    """Unsigned fourth-root companding, per 256-element block."""
+    flat = v.reshape(-1).float()
+    pad = (-flat.numel()) % BLOCK
+    blocks = torch.nn.functional.pad(flat, (0, pad)).view(-1, BLOCK)
+    amax = blocks.amax(1)
+    safe = amax.clamp_min(1e-38)[:, None]
+    codes = torch.round((blocks / safe).clamp(0, 1).pow(0.25) * 255).to(torch.uint8)
+    codes = torch.where(amax[:, None] > 0, codes, torch.zeros_like(codes))
+    return codes.view(-1)[: flat.numel()], amax
+
+
+def decode_second_moment(codes: torch.Tensor, amax: torch.Tensor) -> torch.Tensor:
+    n = codes.numel()
+    pad = (-n) % BLOCK
+    c = torch.nn.functional.pad(codes.float(), (0, pad)).view(-1, BLOCK) / 255.0
+    return (c.pow(4) * amax[:, None]).view(-1)[:n]
+
+
+_DESC = np.dtype(
+    [("param", "<u8"), ("grad", "<u8"), ("m", "<u8"), ("v", "<u8"), ("shadow", "<u8"), ("m8", "<u8"), ("v8", "<u8"),
+     ("m_absmax", "<u8"), ("v_absmax", "<u8"), ("numel", "<i8")]
+)
+_CHUNK = np.dtype([("tensor", "<i4"), ("pad", "<i4"), ("offset", "<i8")])
+
+
+class AdamW(torch.optim.Optimizer):
+    """Decoupled-weight-decay Adam.  ``eight_bit=True`` keeps both moments as block-wise 8-bit codes.
+
+    ``bf16_shadow=True`` additionally maintains ``param._bf16_shadow``, a bf16 copy refreshed inside
+    the update kernel so that bf16 forwards need no per-step cast of the master weights.
+    """
+
+    def __init__(self, params, lr=1e-3, betas=(0.9, 0.999), eps=1e-8, weight_decay=0.01, *, eight_bit=False,
+                 min_8bit_size=4096, bf16_shadow=False):
+        if lr < 0 or eps < 0 or not 0 <= betas[0] < 1 or not 0 <= betas[1] < 1 or weight_decay < 0:
+            raise ValueError("invalid AdamW hyper-parameters")
+        super().__init__(params, dict(lr=lr, betas=betas, eps=eps, weight_decay=weight_decay))
+        self.eight_bit, self.min_8bit_size, self.bf16_shadow = bool(eight_bit), int(min_8bit_size), bool(bf16_shadow)
+        self._tables: dict[int, dict] = {}
+        self.kernel_launches = 0
+
+    # ------------------------------------------------------------------ state
+    def _init_state(self, p: torch.Tensor) -> dict:
+        st = self.state[p]
+        if st:
+            return st
+        st["step"] = 0
+        use8 = self.eight_bit and p.numel() >= self.min_8bit_size
+        st["eight_bit"] = use8
+        if use8:
+            nblk = (p.numel() + BLOCK - 1) // BLOCK
+            st["m8"] = torch.full((p.numel(),), 128, dtype=torch.uint8, device=p.device)
+            st["v8"] = torch.zeros(p.numel(), dtype=torch.uint8, device=p.device)
+            st["m_absmax"] = torch.zeros(nblk, dtype=torch.float32, device=p.device)
+            st["v_absmax"] = torch.zeros(nblk, dtype=torch.float32, device=p.device)
+        else:
+            st["exp_avg"] = torch.zeros_like(p, dtype=torch.float32, memory_format=torch.contiguous_format)
+            st["exp_avg_sq"] = torch.zeros_like(p, dtype=torch.float32, memory_format=torch.contiguous_format)
+        if self.bf16_shadow and p.is_cuda:
+            p._bf16_shadow = p.detach().to(torch.bfloat16)
+        return st
+
+    def state_bytes(self) -> int:
+        total = 0
+        for st in self.state.values():
+            total += sum(t.numel() * t.element_size() for t in st.values() if torch.is_tensor(t))
+        return total
+
+    # ------------------------------------------------------------------ CPU / reference arithmetic
+    @staticmethod
+    def _reference_update(p, g, st, lr, b1, b2, eps, wd, bias1, bias2):
+        if st["eight_bit"]:
+            m = decode_first_moment(st["m8"], st["m_absmax"]).view_as(p)
+            v = decode_second_moment(st["v8"], st["v_absmax"]).view_as(p)
+        else:
+            m, v = st["exp_avg"], st["exp_avg_sq"]
+        m = b1 * m + (1 - b1) * g
+        v = b2 * v + (1 - b2) * g * g
+        p.mul_(1 - lr * wd)
+        p.addcdiv_(m / bias1, (v / bias2).sqrt() + eps, value=-lr)
+        if st["eight_bit"]:
+            st["m8"], st["m_absmax"] = encode_first_moment(m)
+            st["v8"], st["v_absmax"] = encode_second_moment(v)
+        else:
+            st["exp_avg"], st["exp_avg_sq"] = m, v
+
+    # ------------------------------------------------------------------ kernel tables
+    def _launch_group(self, gi: int, group: dict, plist: list, grad_scale: float) -> None:
+        from ..ops import _lib
+
+        lib = _lib.load()
+        dev = plist[0].device
+        cache = self._tables.get(gi)
+        sig = tuple((p.data_ptr(), p.numel()) for p in plist)
+        if cache is None or cache["sig"] != sig:
+            chunk = lib.sb_optim_chunk()
+            rows = []
+            for ti, p in enumerate(plist):
+                rows += [(ti, 0, off) for off in range(0, p.numel(), chunk)]
+            chunks = np.array(rows, dtype=_CHUNK)
+            cache = {
+                "sig": sig,
+                "n_chunks": len(rows),
+                "chunks": torch.from_numpy(chunks.view(np.uint8).copy()).to(dev),
+                "host": torch.empty(len(plist) * _DESC.itemsize, dtype=torch.uint8, pin_memory=True),
+                "dev": torch.empty(len(plist) * _DESC.itemsize, dtype=torch.uint8, device=dev),
+            }
+            assert lib.sb_tensor_desc_size() == _DESC.itemsize and lib.sb_chunk_desc_size() == _CHUNK.itemsize
+            self._tables[gi] = cache
+        table = cache["host"].numpy().view(_DESC)
+        for ti, p in enumerate(plist):
+            st = self.state[p]
+            ptr = lambda t: 0 if t is None else t.data_ptr()
+            table[ti] = (
+                p.data_ptr(), p.grad.data_ptr(), ptr(st.get("exp_avg")), ptr(st.get("exp_avg_sq")),
+                ptr(getattr(p, "_bf16_shadow", None)), ptr(st.get("m8")), ptr(st.get("v8")), ptr(st.get("m_absmax")),
+                ptr(st.get("v_absmax")), p.numel(),
+            )
+        cache["dev"].copy_(cache["host"], non_blocking=True)
+        step = self.state[plist[0]]["step"]
+        b1, b2 = group["betas"]
+        rc = lib.sb_adamw_step(
+            _lib.ptr(cache["dev"]), _lib.ptr(cache["chunks"]), ctypes.c_int(cache["n_chunks"]), ctypes.c_int(int(self.eight_bit)),
+            ctypes.c_float(group["lr"]), ctypes.c_float(b1), ctypes.c_float(b2), ctypes.c_float(group["eps"]),
+            ctypes.c_float(group["weight_decay"]), ctypes.c_float(1 - b1 ** step), ctypes.c_float(1 - b2 ** step),
+            ctypes.c_float(grad_scale), _lib.stream_ptr(),
+        )
+        _lib.check_rc(rc, "sb_adamw_step")
+        self.kernel_launches += 1
+
+    @torch.no_grad()
+    def step(self, closure=None, grad_scale: float = 1.0):
+        loss = None
+        if closure is not None:
+            with torch.enable_grad():
+                loss = closure()
+        for gi, group in enumerate(self.param_groups):
+            fast, slow = [], []
+            for p in group["params"]:
+                if p.grad is None:
+                    continue
+                if p.grad.is_sparse:
+                    raise RuntimeError("AdamW does not support sparse gradients")
+                st = self._init_state(p)
+                st["step"] += 1
+                ok = p.is_cuda and p.dtype == torch.float32 and p.grad.dtype == torch.float32 and p.is_contiguous() and p.grad.is_contiguous()
+                (fast if ok else slow).append(p)
+            if fast:
+                steps = {self.state[p]["step"] for p in fast}
+                if len(steps) == 1:
+                    self._launch_group(gi, group, fast, grad_scale)
+                else:
+                    slow += fast
+            b1, b2 = group["betas"]
+            for p in slow:
+                st = self.state[p]
+                g = p.grad.float() * grad_scale
+                work = p.data.float() if p.dtype != torch.float32 else p.data
+                self._reference_update(work, g, st, group["lr"], b1, b2, group["eps"], group["weight_decay"],
+                                       1 - b1 ** st["step"], 1 - b2 ** st["step"])
+                if work is not p.data:
+                    p.data.copy_(work)
+                if hasattr(p, "_bf16_shadow"):
+                    p._bf16_shadow.copy_(p.data)
+        return loss
+
+
+class AdamW8bit(AdamW):
+    """AdamW with 8-bit block-wise moments (256-element blocks, fp32 absmax per block)."""
+
+    def __init__(self, params, lr=1e-3, betas=(0.9, 0.999), eps=1e-8, weight_decay=0.01, min_8bit_size=4096, **kw):
+        super().__init__(params, lr, betas, eps, weight_decay, eight_bit=True, min_8bit_size=min_8bit_size, **kw)

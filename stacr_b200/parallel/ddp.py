@@ -1,0 +1,186 @@
+"""Data-parallel gradient synchronisation with rank-local compression state.
+
+``GradSync`` owns one flat fp32 gradient buffer; every ``param.grad`` is a view into it, so
+gradients are produced in place, reduced in place and consumed in place by the fused optimizer.
+Parameters are grouped into buckets in reverse registration order (the order backward produces
+them).  A post-accumulate hook marks a parameter ready; when a bucket is complete its slice is
+averaged across ranks on a communication stream while backward keeps running.  The reduction
+itself is pluggable:
+
+* ``"symm"``: the in-tree all-reduce kernels over NVLink peer memory / NVSwitch multimem
+  (``stacr_b200.parallel.symm``), used on CUDA when symmetric memory is available;
+* ``"nccl"`` / ``"gloo"``: ``torch.distributed.all_reduce`` (the portable path; also what the
+  CPU tests run with two gloo ranks).
+
+Bases, step counters and residual state of the compressed layers are *not* synchronised: each
+rank tracks the subspace of its own data shard, as the reference prescribes for DDP
+(``broadcast_buffers=False``; experiments/protocols/training.py:507-509 there).
+"""
+
+from __future__ import annotations
+
+import os
+from typing import Iterable
+
+import torch
+import torch.distributed as dist
+from torch import nn
+
+
+def init_distributed(backend: str | None = None) -> tuple[int, int, int]:
+    """Initialise the default process group from torchrun's environment; returns (rank, world, local_rank)."""
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", str(rank)))
+    if world > 1 and not dist.is_initialized():
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        os.environ.setdefault("MASTER_PORT", "29500")
+        if backend is None:
+            backend = "nccl" if torch.cuda.is_available() else "gloo"
+        if backend == "nccl":
+            torch.cuda.set_device(local)
+            dist.init_process_group(backend, device_id=torch.device("cuda", local))
+        else:
+            dist.init_process_group(backend)
+    return rank, world, local
+
+
+def broadcast_parameters(model: nn.Module, src: int = 0) -> None:
+    """Make every rank start from rank ``src``'s parameters (buffers stay rank-local)."""
+    if not (dist.is_initialized() and dist.get_world_size() > 1):
+        return
+    for p in model.parameters():
+        dist.broadcast(p.data, src)
+
+
+class GradSync:
+    """Flat-buffer, bucketed, overlapped gradient averaging for one model replica."""
+
+    def __init__(self, params: Iterable[nn.Parameter], *, bucket_mb: float = 256.0, backend: str = "auto",
+                 group=None, average: bool = True):
+        self.params = [p for p in params if p.requires_grad]
+        if not self.params:
+            raise ValueError("GradSync needs at least one trainable parameter")
+        self.group = group
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.average = average
+        dev = self.params[0].device
+        self.device = dev
+        total = sum(p.numel() for p in self.params)
+        # pad each parameter's slot to 16 bytes so every view is vector-aligned
+        offsets, cursor = [], 0
+        for p in self.params:
+            offsets.append(cursor)
+            cursor += (p.numel() + 3) // 4 * 4
+        self.numel = cursor
+        self.backend = self._pick_backend(backend, dev)
+        self.flat = self._allocate(cursor, dev)
+        self.flat.zero_()
+        for p, off in zip(self.params, offsets):
+            p.grad = self.flat[off:off + p.numel()].view_as(p)
+        # buckets over the reversed parameter list (backward order)
+        limit = int(bucket_mb * 1024 * 1024 / 4)
+        self.buckets: list[tuple[int, int]] = []
+        self._bucket_of: dict[int, int] = {}
+        self._pending: list[int] = []
+        hi = cursor
+        lo = hi
+        members: list[int] = []
+        for idx in range(len(self.params) - 1, -1, -1):
+            lo = offsets[idx]
+            members.append(idx)
+            if hi - lo >= limit or idx == 0:
+                b = len(self.buckets)
+                self.buckets.append((lo, hi))
+                for m in members:
+                    self._bucket_of[m] = b
+                self._pending.append(len(members))
+                members, hi = [], lo
+        self._size = list(self._pending)
+        self._stream = torch.cuda.Stream(device=dev) if dev.type == "cuda" else None
+        self._launched = 0
+        self.reductions = 0
+        self._hooks = [p.register_post_accumulate_grad_hook(self._make_hook(i)) for i, p in enumerate(self.params)]
+        self._total = total
+
+    # ------------------------------------------------------------------ backend plumbing
+    def _pick_backend(self, backend: str, dev: torch.device) -> str:
+        if self.world == 1:
+            return "none"
+        if backend != "auto":
+            return backend
+        if dev.type == "cuda":
+            from . import symm
+
+            return "symm" if symm.available() else "nccl"
+        return "gloo"
+
+    def _allocate(self, numel: int, dev: torch.device) -> torch.Tensor:
+        if self.backend == "symm":
+            from . import symm
+
+            self._symm = symm.SymmetricBuffer(numel, torch.float32, dev, self.group)
+            return self._symm.tensor
+        return torch.empty(numel, dtype=torch.float32, device=dev)
+
+    def _reduce(self, lo: int, hi: int) -> None:
+        if self.backend == "none" or hi <= lo:
+            return
+        self.reductions += 1
+        if self.backend == "symm":
+            self._symm.all_reduce_(lo, hi, average=self.average)
+            return
+        chunk = self.flat[lo:hi]
+        dist.all_reduce(chunk, op=dist.ReduceOp.SUM, group=self.group)
+        if self.average:
+            chunk.div_(self.world)
+
+    # ------------------------------------------------------------------ hooks
+    def _make_hook(self, index: int):
+        def hook(param):
+            b = self._bucket_of[index]
+            self._pending[b] -= 1
+            if self._pending[b] == 0:
+                self._launch(b)
+        return hook
+
+    def _launch(self, b: int) -> None:
+        lo, hi = self.buckets[b]
+        self._launched += 1
+        if self._stream is None:
+            self._reduce(lo, hi)
+            return
+        self._stream.wait_stream(torch.cuda.current_stream(self.device))
+        with torch.cuda.stream(self._stream):
+            self._reduce(lo, hi)
+
+    # ------------------------------------------------------------------ step protocol
+    def zero_grad(self) -> None:
+        """Clear the flat buffer (one memset) and re-arm the buckets.  Call instead of ``optimizer.zero_grad``."""
+        self.flat.zero_()
+        self._pending = list(self._size)
+        self._launched = 0
+        for p in self.params:
+            if p.grad is None or p.grad.data_ptr() < self.flat.data_ptr():
+                raise RuntimeError("a gradient view was replaced; keep set_to_none=False semantics with GradSync")
+
+    def finish(self) -> None:
+        """Reduce buckets whose hooks did not all fire (unused parameters) and join the communication stream."""
+        for b, left in enumerate(self._pending):
+            if left > 0:
+                self._pending[b] = 0
+                self._launch(b)
+        if self._stream is not None:
+            torch.cuda.current_stream(self.device).wait_stream(self._stream)
+
+    def close(self) -> None:
+        for h in self._hooks:
+            h.remove()
+        self._hooks = []
+
+
+def all_reduce_mean_(tensor: torch.Tensor, group=None) -> torch.Tensor:
+    if dist.is_initialized() and dist.get_world_size(group) > 1:
+        dist.all_reduce(tensor, group=group)
+        tensor.div_(dist.get_world_size(group))
+    return tensor

@@ -1,0 +1,78 @@
+"""Symmetric peer memory and the in-tree all-reduce kernels over NVLink / NVSwitch.
+
+Allocation and the peer-pointer exchange go through ``torch.distributed._symmetric_memory`` (CUDA
+VMM allocations mapped into every rank of the node, plus an NVSwitch multicast address when the
+fabric offers one).  The reductions are this framework's own kernels (``csrc/comm.cu``):
+
+* two-shot all-reduce with plain peer loads/stores: each rank reduces its 1/W slice reading every
+  peer's buffer, writes the result back to every peer; barriers are flag words in the symmetric
+  signal pad with bounded waits;
+* one-shot ``multimem.ld_reduce`` / ``multimem.st`` through the NVSwitch multicast address.
+
+``available()`` is False when the build of PyTorch lacks symmetric memory or the process group is
+not NCCL on CUDA; ``GradSync`` then uses the NCCL path.
+"""
+
+from __future__ import annotations
+
+import ctypes
+import os
+
+import torch
+import torch.distributed as dist
+
+from ..ops import _lib
+
+
+def available() -> bool:
+    if os.environ.get("STACR_DISABLE_SYMM", "0") == "1":
+        return False
+    if not (torch.cuda.is_available() and dist.is_initialized() and dist.get_backend() == "nccl"):
+        return False
+    try:
+        import torch.distributed._symmetric_memory  # noqa: F401
+    except Exception:
+        return False
+    return hasattr(_lib.load(), "sb_allreduce_two_shot")
+
+
+class SymmetricBuffer:
+    """A tensor that every rank of the group can address, with in-place all-reduce over its slices."""
+
+    def __init__(self, numel: int, dtype: torch.dtype, device: torch.device, group=None):
+        import torch.distributed._symmetric_memory as symm_mem
+
+        self.group = group if group is not None else dist.group.WORLD
+        self.world = dist.get_world_size(self.group)
+        self.rank = dist.get_rank(self.group)
+        self.tensor = symm_mem.empty(numel, dtype=dtype, device=device)
+        self.handle = symm_mem.rendezvous(self.tensor, self.group)
+        # epoch-tagged barrier flags live in their own symmetric buffer
+        self.flags = symm_mem.empty(_lib.load().sb_comm_flag_ints(), dtype=torch.int32, device=device)
+        self.flags.zero_()
+        self._flag_handle = symm_mem.rendezvous(self.flags, self.group)
+        torch.cuda.synchronize(device)
+        dist.barrier(self.group)  # nobody may publish a flag before every rank has zeroed its own
+        ptrs = [int(p) for p in self.handle.buffer_ptrs]
+        pads = [int(p) for p in self._flag_handle.buffer_ptrs]
+        self._peer_ptrs = torch.tensor(ptrs, dtype=torch.int64, device=device)
+        self._pad_ptrs = torch.tensor(pads, dtype=torch.int64, device=device)
+        self.multicast_ptr = int(getattr(self.handle, "multicast_ptr", 0) or 0)
+        self.use_multimem = self.multicast_ptr != 0 and os.environ.get("STACR_SYMM_MULTIMEM", "1") == "1"
+        self._epoch = 0
+        self.numel = numel
+
+    def all_reduce_(self, lo: int, hi: int, average: bool = True) -> None:
+        """In-place sum (or mean) of ``tensor[lo:hi]`` across ranks, on the current stream."""
+        self._epoch += 1
+        lib = _lib.load()
+        scale = 1.0 / self.world if average else 1.0
+        fn = lib.sb_allreduce_multimem if self.use_multimem else lib.sb_allreduce_two_shot
+        rc = fn(
+            _lib.ptr(self._peer_ptrs), _lib.ptr(self._pad_ptrs), ctypes.c_ulonglong(self.multicast_ptr), ctypes.c_int(self.rank),
+            ctypes.c_int(self.world), ctypes.c_longlong(lo), ctypes.c_longlong(hi), ctypes.c_float(scale),
+            ctypes.c_int(self._epoch), ctypes.c_int(_lib.sm_count(self.tensor.device)), _lib.ptr(_lib.status_word(self.tensor.device)),
+            _lib.stream_ptr(),
+        )
+        _lib.check_rc(rc, "sb_allreduce")
+        _lib.count(1)

@@ -1,0 +1,93 @@
+"""LayerNorm / GELU / cross-entropy / optimizer kernels against fp32 PyTorch references."""
+
+import pytest
+import torch
+from torch.nn import functional as F
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.mark.parametrize("rows,n", [(64, 256), (1000, 768), (4096, 2048), (300, 4096), (77, 1280)])
+def test_layernorm_forward_backward(rows, n):
+    from stacr_b200.ops import nn_ops
+
+    torch.manual_seed(rows + n)
+    x = torch.randn(rows, n, device="cuda").bfloat16().requires_grad_(True)
+    w = torch.randn(n, device="cuda").requires_grad_(True)
+    b = torch.randn(n, device="cuda").requires_grad_(True)
+    y = nn_ops.layer_norm(x, w, b, 1e-5)
+    xr = x.detach().float().requires_grad_(True)
+    wr, br = w.detach().clone().requires_grad_(True), b.detach().clone().requires_grad_(True)
+    yr = F.layer_norm(xr, (n,), wr, br, 1e-5)
+    torch.testing.assert_close(y.float(), yr, rtol=2e-2, atol=2e-2)
+    g = torch.randn_like(yr)
+    y.backward(g.bfloat16())
+    yr.backward(g.bfloat16().float())
+    torch.testing.assert_close(x.grad.float(), xr.grad, rtol=3e-2, atol=3e-2)
+    torch.testing.assert_close(w.grad, wr.grad, rtol=2e-2, atol=rows ** 0.5 * 2e-2)
+    torch.testing.assert_close(b.grad, br.grad, rtol=2e-2, atol=rows ** 0.5 * 2e-2)
+
+
+@pytest.mark.parametrize("form", ["none", "tanh"])
+def test_gelu_forward_backward(form):
+    from stacr_b200.ops import nn_ops
+
+    x = (3 * torch.randn(513, 1024, device="cuda")).bfloat16().requires_grad_(True)
+    y = nn_ops.gelu(x, form)
+    xr = x.detach().float().requires_grad_(True)
+    yr = F.gelu(xr, approximate=form)
+    torch.testing.assert_close(y.float(), yr, rtol=1e-2, atol=1e-2)
+    g = torch.randn_like(yr).bfloat16()
+    y.backward(g)
+    yr.backward(g.float())
+    torch.testing.assert_close(x.grad.float(), xr.grad, rtol=2e-2, atol=2e-2)
+
+
+def test_cross_entropy_loss_and_gradient():
+    from stacr_b200.ops import nn_ops
+
+    rows, v = 515, 50304
+    logits = (2 * torch.randn(rows, v, device="cuda")).bfloat16().requires_grad_(True)
+    target = torch.randint(0, v, (rows,), device="cuda")
+    target[::7] = -100
+    loss = nn_ops.cross_entropy(logits, target)
+    lr = logits.detach().float().requires_grad_(True)
+    ref = F.cross_entropy(lr, target, ignore_index=-100)
+    torch.testing.assert_close(loss, ref, rtol=1e-3, atol=1e-3)
+    (loss * 3.0).backward()
+    (ref * 3.0).backward()
+    err = (logits.grad.float() - lr.grad).abs().max() / lr.grad.abs().max()
+    assert err < 2e-2, float(err)
+    assert logits.grad[0::7].abs().max() == 0
+
+
+@pytest.mark.parametrize("eight_bit", [False, True])
+def test_adamw_kernel_tracks_torch(eight_bit):
+    from stacr_b200.optim import AdamW
+
+    torch.manual_seed(3)
+    shapes = [(1024, 512), (300,), (4097,), (64, 64)]
+    mine = [torch.nn.Parameter(torch.randn(s, device="cuda")) for s in shapes]
+    ref = [torch.nn.Parameter(p.detach().clone()) for p in mine]
+    o1 = AdamW(mine, lr=1e-2, weight_decay=0.1, eight_bit=eight_bit)
+    o2 = torch.optim.AdamW(ref, lr=1e-2, weight_decay=0.1)
+    for _ in range(10):
+        for a, b in zip(mine, ref):
+            g = torch.randn_like(a)
+            a.grad, b.grad = g.clone(), g.clone()
+        o1.step()
+        o2.step()
+    tol = 5e-3 if eight_bit else 1e-5
+    for a, b in zip(mine, ref):
+        assert (a - b).abs().max() < tol * max(1.0, float(b.abs().max()))
+    assert o1.kernel_launches == 10
+    if eight_bit:
+        big = o1.state[mine[0]]
+        assert big["eight_bit"] and big["m8"].dtype == torch.uint8
+        assert not o1.state[mine[1]]["eight_bit"]
+
+
+def test_smoke_entry_point():
+    import __graft_entry__ as entry
+
+    entry.smoke()
