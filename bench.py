@@ -130,7 +130,7 @@ def run_ours(args):
     model = GPTNeoXForCausalLM(NeoXConfig(**shape)).to(dev).train()
     broadcast_parameters(model)
     layers = S.apply_stacr(model, **STACR)
-    opt = AdamW8bit(model.parameters(), lr=2e-5, weight_decay=0.0)
+    opt = AdamW8bit(model.parameters(), lr=2e-5, weight_decay=0.0, bf16_shadow=True)
     sync = GradSync(model.parameters(), backend=args.comm) if world > 1 else None
     host_batches = [t.pin_memory() for t in make_tokens(torch, shape["vocab_size"], batch, seq, 8, 100 + rank)]
     dev_batches = [t.to(dev) for t in host_batches]

@@ -148,6 +148,14 @@ def _compute_dtype(x: torch.Tensor, weight: torch.Tensor) -> torch.dtype:
     return torch.promote_types(x.dtype, weight.dtype) if x.dtype != weight.dtype else x.dtype
 
 
+def _bf16_weight(weight: torch.Tensor) -> torch.Tensor:
+    """bf16 copy of a master weight: the shadow the fused optimizer keeps current, else a cast."""
+    shadow = getattr(weight, "_bf16_shadow", None)
+    if shadow is not None and shadow.shape == weight.shape:
+        return shadow
+    return weight.detach().to(torch.bfloat16)
+
+
 def _basis_views(basis: torch.Tensor):
     """bf16 ``[N, r]`` copy and padded transpose of one basis *version*, cached on the tensor object.
 
@@ -248,7 +256,7 @@ class STACRFunction(torch.autograd.Function):
             from .ops.gemm import gemm
 
             xa = x2d.to(torch.bfloat16).contiguous()
-            wb = weight.detach().to(torch.bfloat16)
+            wb = _bf16_weight(weight)
             bf = None if bias is None else bias.detach().float()
             # Conv1D keeps W as [in, out]: that is the MN-major B operand of the same kernel
             out2d = gemm(xa, wb, b_mn=bool(transposed), bias=bf)
@@ -298,7 +306,7 @@ class STACRFunction(torch.autograd.Function):
 
             ga = g2d.to(torch.bfloat16).contiguous()
             if ctx.needs_input_grad[0]:
-                wb = weight.detach().to(torch.bfloat16)
+                wb = _bf16_weight(weight)
                 # dX = dY W: W[out, in] is MN-major for this product; Conv1D's [in, out] is K-major
                 gx = gemm(ga, wb, b_mn=not ctx.transposed)
                 gx = gx.reshape(*ctx.leading, ctx.in_features).to(ctx.input_dtype)

@@ -7,6 +7,7 @@ from dataclasses import dataclass
 import torch
 from torch import nn
 
+from ..ops import nn_ops
 from .common import GELU, LayerNorm, ModelOutput, causal_attention, init_weights, lm_loss
 
 
@@ -64,6 +65,7 @@ class NeoXAttention(nn.Module):
         self.dense = nn.Linear(cfg.hidden_size, cfg.hidden_size)
         self.attention_dropout = cfg.attention_dropout
         self._tables = None
+        self._half = None
 
     def _rotary(self, seq, device, dtype):
         key = (seq, device, dtype)
@@ -71,13 +73,26 @@ class NeoXAttention(nn.Module):
             self._tables = (key, rotary_tables(seq, self.rot, self.base, device, dtype))
         return self._tables[1]
 
+    def _half_tables(self, seq, device):
+        key = ("half", seq, device)
+        if self._half is None or self._half[0] != key:
+            inv = 1.0 / (self.base ** (torch.arange(0, self.rot, 2, device=device, dtype=torch.float32) / self.rot))
+            ang = torch.outer(torch.arange(seq, device=device, dtype=torch.float32), inv)
+            self._half = (key, ang.cos().contiguous(), ang.sin().contiguous())
+        return self._half[1], self._half[2]
+
     def forward(self, x, attention_mask=None):
         b, s, d = x.shape
-        # NeoX interleaves per head: [H, 3 * head_dim]
-        qkv = self.query_key_value(x).view(b, s, self.n_head, 3 * self.head_dim)
-        q, k, v = (t.transpose(1, 2) for t in qkv.split(self.head_dim, dim=-1))
-        cos, sin = self._rotary(s, x.device, q.dtype)
-        q, k = apply_rotary(q, cos, sin, self.rot), apply_rotary(k, cos, sin, self.rot)
+        qkv = self.query_key_value(x)
+        if nn_ops.rotary_qk_supported(qkv, self.head_dim, self.rot):
+            cos, sin = self._half_tables(s, x.device)
+            qkv = nn_ops.rotary_qk(qkv, cos, sin, s, self.n_head, self.head_dim, self.rot)  # fused, in place
+            q, k, v = (t.transpose(1, 2) for t in qkv.view(b, s, self.n_head, 3 * self.head_dim).split(self.head_dim, dim=-1))
+        else:
+            # NeoX interleaves per head: [H, 3 * head_dim]
+            q, k, v = (t.transpose(1, 2) for t in qkv.view(b, s, self.n_head, 3 * self.head_dim).split(self.head_dim, dim=-1))
+            cos, sin = self._rotary(s, x.device, q.dtype)
+            q, k = apply_rotary(q, cos, sin, self.rot), apply_rotary(k, cos, sin, self.rot)
         ctx = causal_attention(q, k, v, causal=True, attention_mask=attention_mask, dropout_p=self.attention_dropout, training=self.training)
         return self.dense(ctx.transpose(1, 2).reshape(b, s, d))
 

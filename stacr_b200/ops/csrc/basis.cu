@@ -61,6 +61,51 @@ __device__ void block_gram(const float* a, int count, int lda, int r, bool round
   }
 }
 
+// Rank <= 8 fast path: all 36 entries of the upper triangle in one pass over the rows.
+__device__ void block_gram8(const float* a, int count, int lda, int r, bool round_bf16, float* gram, float* partial /*[32][36]*/) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+  float acc[36];
+#pragma unroll
+  for (int k = 0; k < 36; ++k) acc[k] = 0.f;
+  for (int row = threadIdx.x; row < count; row += blockDim.x) {
+    const float* ar = a + static_cast<size_t>(row) * lda;
+    float v[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      v[j] = (j < r) ? ar[j] : 0.f;
+      if (round_bf16) v[j] = __bfloat162float(__float2bfloat16_rn(v[j]));
+    }
+    int k = 0;
+#pragma unroll
+    for (int i = 0; i < 8; ++i)
+#pragma unroll
+      for (int j = 0; j <= i; ++j) {
+        acc[k] = fmaf(v[i], v[j], acc[k]);
+        ++k;
+      }
+  }
+#pragma unroll
+  for (int k = 0; k < 36; ++k) {
+    float v = acc[k];
+    for (int off = 16; off; off >>= 1) v += __shfl_xor_sync(0xffffffffu, v, off);
+    if (lane == 0) partial[warp * 36 + k] = v;
+  }
+  __syncthreads();
+  if (threadIdx.x < 36) {
+    float total = 0.f;
+    for (int w = 0; w < nwarps; ++w) total += partial[w * 36 + threadIdx.x];
+    int i = 0, base = 0;
+    while (base + i + 1 <= static_cast<int>(threadIdx.x)) {
+      base += i + 1;
+      ++i;
+    }
+    const int j = threadIdx.x - base;
+    gram[i * RMAX + j] = total;
+    gram[j * RMAX + i] = total;
+  }
+  __syncthreads();
+}
+
 // In-place upper Cholesky factor R (R^T R = G) and its inverse, by thread 0.  Returns false in
 // shared flag when a pivot is not positive.
 __device__ void chol_and_invert(float* g, float* rinv, int r, int* ok) {
@@ -103,11 +148,12 @@ __global__ void __launch_bounds__(1024) oja_update_kernel(const float* q_in, con
                                                           __nv_bfloat16* q_bf16, __nv_bfloat16* qt_bf16, int rpad, int* status) {
   __shared__ float s_mat[RMAX * RMAX];
   __shared__ float s_inv[RMAX * RMAX];
-  __shared__ float scratch[32 * RP];
+  __shared__ float scratch[32 * (RP > 36 ? RP : 36)];
   __shared__ int s_ok;
   const float inv_n = 1.f / fmaxf(1.f, static_cast<float>(rows));
   if (lr != 0.f && g != nullptr) {
-    block_gram<RP>(y, rows, ldy, r, true, s_mat, scratch);  // S = Y^T Y
+    if (RP == 8) block_gram8(y, rows, ldy, r, true, s_mat, scratch);  // S = Y^T Y
+    else block_gram<RP>(y, rows, ldy, r, true, s_mat, scratch);
     for (int row = threadIdx.x; row < n; row += blockDim.x) {
       float qrow[RP];
       for (int j = 0; j < r; ++j) qrow[j] = q_in[static_cast<size_t>(row) * r + j];
@@ -122,7 +168,8 @@ __global__ void __launch_bounds__(1024) oja_update_kernel(const float* q_in, con
   }
   __syncthreads();
   for (int pass = 0; pass < 2; ++pass) {
-    block_gram<RP>(q_out, n, r, r, false, s_mat, scratch);
+    if (RP == 8) block_gram8(q_out, n, r, r, false, s_mat, scratch);
+    else block_gram<RP>(q_out, n, r, r, false, s_mat, scratch);
     chol_and_invert(s_mat, s_inv, r, &s_ok);
     if (!s_ok) {
       if (threadIdx.x == 0 && status) atomicCAS(status, 0, ST_BAD_ARGUMENT);

@@ -302,6 +302,43 @@ __global__ void __launch_bounds__(512) cross_entropy_kernel(const __nv_bfloat16*
   }
 }
 
+// ---------------------------------------------------------------------------- rotary embedding
+// In-place NeoX-style rotation of the first `rot` dims of the q and k parts of a fused qkv tensor
+// [tokens, heads, 3 * head_dim] (token t is at position t % seq).  out1 = x1 cos - s x2 sin,
+// out2 = x2 cos + s x1 sin with s = +1 (forward) or -1 (backward: the transpose of a rotation).
+// One thread rotates 8 pairs (two 16-byte vectors).
+__global__ void __launch_bounds__(256) rotary_qk_kernel(__nv_bfloat16* __restrict__ qkv, const float* __restrict__ cos_t,
+                                                        const float* __restrict__ sin_t, long long tokens, int seq, int heads,
+                                                        int head_dim, int rot, float sign) {
+  const int half = rot >> 1;
+  const int groups = half >> 3;  // 8-pair groups per (token, head, q|k)
+  const long long total = tokens * heads * 2 * groups;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total; i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const int g = static_cast<int>(i % groups);
+    long long rest = i / groups;
+    const int which = static_cast<int>(rest % 2);
+    rest /= 2;
+    const int head = static_cast<int>(rest % heads);
+    const long long tok = rest / heads;
+    const int pos = static_cast<int>(tok % seq);
+    __nv_bfloat16* base = qkv + (tok * heads + head) * 3 * static_cast<long long>(head_dim) + which * head_dim + g * 8;
+    float a[8], b[8];
+    unpack8(*reinterpret_cast<const uint4*>(base), a);
+    unpack8(*reinterpret_cast<const uint4*>(base + half), b);
+    const float* cr = cos_t + static_cast<size_t>(pos) * half + g * 8;
+    const float* sr = sin_t + static_cast<size_t>(pos) * half + g * 8;
+    float o1[8], o2[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const float c = __ldg(cr + j), sn = sign * __ldg(sr + j);
+      o1[j] = a[j] * c - b[j] * sn;
+      o2[j] = b[j] * c + a[j] * sn;
+    }
+    *reinterpret_cast<uint4*>(base) = pack8(o1);
+    *reinterpret_cast<uint4*>(base + half) = pack8(o2);
+  }
+}
+
 // ---------------------------------------------------------------------------- cast
 __global__ void __launch_bounds__(256) cast_f32_bf16_kernel(const float4* __restrict__ src, uint2* __restrict__ dst, size_t nvec4) {
   for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < nvec4; i += static_cast<size_t>(gridDim.x) * blockDim.x) {
@@ -405,5 +442,18 @@ extern "C" int sb_cast_f32_bf16(const float* src, void* dst, long long numel, in
   if (blocks > static_cast<size_t>(sms) * 16) blocks = static_cast<size_t>(sms) * 16;
   sb::cast_f32_bf16_kernel<<<static_cast<unsigned>(blocks), 256, 0, static_cast<cudaStream_t>(stream)>>>(
       reinterpret_cast<const float4*>(src), static_cast<uint2*>(dst), nvec);
+  return static_cast<int>(cudaGetLastError());
+}
+
+// In-place rotary embedding on the q and k parts of qkv [tokens, heads, 3*head_dim] bf16; rot % 16 == 0, head_dim % 8 == 0.
+extern "C" int sb_rotary_qk(void* qkv, const float* cos_t, const float* sin_t, long long tokens, int seq, int heads, int head_dim,
+                            int rot, float sign, int sms, void* stream) {
+  if (tokens <= 0) return 0;
+  if (rot % 16 || head_dim % 8 || rot > head_dim) return -2;
+  const long long total = tokens * heads * 2 * (rot / 16);
+  long long blocks = (total + 255) / 256;
+  if (blocks > static_cast<long long>(sms) * 16) blocks = static_cast<long long>(sms) * 16;
+  sb::rotary_qk_kernel<<<static_cast<unsigned>(blocks), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<__nv_bfloat16*>(qkv), cos_t, sin_t, tokens, seq, heads, head_dim, rot, sign);
   return static_cast<int>(cudaGetLastError());
 }

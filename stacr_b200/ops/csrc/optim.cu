@@ -77,66 +77,115 @@ __device__ __forceinline__ unsigned char encode_v(float v, float amax) {
   return static_cast<unsigned char>(rintf(sqrtf(sqrtf(fminf(v / amax, 1.f))) * 255.f));
 }
 
-// One CTA (256 threads) = one 256-element quantisation block; CHUNK/256 blocks per chunk.
+// One warp = one 256-element quantisation block (8 consecutive elements per lane, 16-byte
+// loads/stores, absmax by warp shuffles only); one CTA of 8 warps = one 2048-element chunk.
 __global__ void __launch_bounds__(256) adamw_8bit_kernel(const TensorDesc* __restrict__ tensors, const ChunkDesc* __restrict__ chunks,
                                                          AdamArgs a) {
-  __shared__ float red_m[8], red_v[8];
-  const ChunkDesc c = chunks[blockIdx.x / (CHUNK / 256)];
+  const ChunkDesc c = chunks[blockIdx.x];
   const TensorDesc t = tensors[c.tensor];
-  const long long base = c.offset + static_cast<long long>(blockIdx.x % (CHUNK / 256)) * 256;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const long long base = c.offset + static_cast<long long>(warp) * 256;
   if (base >= t.numel) return;
-  const long long i = base + threadIdx.x;
-  const bool ok = i < t.numel;
+  const long long i0 = base + lane * 8;
   const long long qb = base / 256;
-  float m = 0.f, v = 0.f, p = 0.f;
-  if (ok) {
-    const float g = t.grad[i] * a.grad_scale;
-    p = t.param[i];
-    if (t.m8) {
-      m = decode_m(t.m8[i], t.m_absmax[qb]);
-      v = decode_v(t.v8[i], t.v_absmax[qb]);
+  const bool vec = (i0 + 8 <= t.numel) && ((reinterpret_cast<uintptr_t>(t.param + i0) & 15) == 0) &&
+                   ((reinterpret_cast<uintptr_t>(t.grad + i0) & 15) == 0);
+  float p[8], g[8], m[8], v[8];
+  unsigned char cm[8], cv[8];
+  const bool q8 = t.m8 != nullptr;
+  if (vec) {
+    *reinterpret_cast<float4*>(p) = *reinterpret_cast<const float4*>(t.param + i0);
+    *reinterpret_cast<float4*>(p + 4) = *reinterpret_cast<const float4*>(t.param + i0 + 4);
+    *reinterpret_cast<float4*>(g) = __ldg(reinterpret_cast<const float4*>(t.grad + i0));
+    *reinterpret_cast<float4*>(g + 4) = __ldg(reinterpret_cast<const float4*>(t.grad + i0 + 4));
+    if (q8) {
+      *reinterpret_cast<uint2*>(cm) = *reinterpret_cast<const uint2*>(t.m8 + i0);
+      *reinterpret_cast<uint2*>(cv) = *reinterpret_cast<const uint2*>(t.v8 + i0);
     } else {
-      m = t.m[i];
-      v = t.v[i];
+      *reinterpret_cast<float4*>(m) = *reinterpret_cast<const float4*>(t.m + i0);
+      *reinterpret_cast<float4*>(m + 4) = *reinterpret_cast<const float4*>(t.m + i0 + 4);
+      *reinterpret_cast<float4*>(v) = *reinterpret_cast<const float4*>(t.v + i0);
+      *reinterpret_cast<float4*>(v + 4) = *reinterpret_cast<const float4*>(t.v + i0 + 4);
     }
-    m = a.beta1 * m + (1.f - a.beta1) * g;
-    v = a.beta2 * v + (1.f - a.beta2) * g * g;
-    p -= a.lr * a.weight_decay * p;
-    p -= a.lr * (m / a.bias1) / (sqrtf(v / a.bias2) + a.eps);
-    t.param[i] = p;
-    if (t.shadow) t.shadow[i] = __float2bfloat16_rn(p);
-  }
-  if (!t.m8) {
-    if (ok) {
-      t.m[i] = m;
-      t.v[i] = v;
-    }
-    return;
-  }
-  float am = fabsf(m), av = v;
-  for (int off = 16; off; off >>= 1) {
-    am = fmaxf(am, __shfl_xor_sync(0xffffffffu, am, off));
-    av = fmaxf(av, __shfl_xor_sync(0xffffffffu, av, off));
-  }
-  if ((threadIdx.x & 31) == 0) {
-    red_m[threadIdx.x >> 5] = am;
-    red_v[threadIdx.x >> 5] = av;
-  }
-  __syncthreads();
-  am = red_m[0];
-  av = red_v[0];
+  } else {
 #pragma unroll
-  for (int w = 1; w < 8; ++w) {
-    am = fmaxf(am, red_m[w]);
-    av = fmaxf(av, red_v[w]);
+    for (int j = 0; j < 8; ++j) {
+      const bool ok = i0 + j < t.numel;
+      p[j] = ok ? t.param[i0 + j] : 0.f;
+      g[j] = ok ? t.grad[i0 + j] : 0.f;
+      if (q8) {
+        cm[j] = ok ? t.m8[i0 + j] : 128;
+        cv[j] = ok ? t.v8[i0 + j] : 0;
+      } else {
+        m[j] = ok ? t.m[i0 + j] : 0.f;
+        v[j] = ok ? t.v[i0 + j] : 0.f;
+      }
+    }
   }
-  if (ok) {
-    t.m8[i] = encode_m(m, am);
-    t.v8[i] = encode_v(v, av);
+  if (q8) {
+    const float am_old = t.m_absmax[qb], av_old = t.v_absmax[qb];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      m[j] = decode_m(cm[j], am_old);
+      v[j] = decode_v(cv[j], av_old);
+    }
   }
-  if (threadIdx.x == 0) {
-    t.m_absmax[qb] = am;
-    t.v_absmax[qb] = av;
+  float am = 0.f, av = 0.f;
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    const float gj = g[j] * a.grad_scale;
+    m[j] = a.beta1 * m[j] + (1.f - a.beta1) * gj;
+    v[j] = a.beta2 * v[j] + (1.f - a.beta2) * gj * gj;
+    p[j] -= a.lr * a.weight_decay * p[j];
+    p[j] -= a.lr * (m[j] / a.bias1) / (sqrtf(v[j] / a.bias2) + a.eps);
+    if (i0 + j < t.numel) {
+      am = fmaxf(am, fabsf(m[j]));
+      av = fmaxf(av, v[j]);
+    }
+  }
+  if (q8) {
+#pragma unroll
+    for (int off = 16; off; off >>= 1) {
+      am = fmaxf(am, __shfl_xor_sync(0xffffffffu, am, off));
+      av = fmaxf(av, __shfl_xor_sync(0xffffffffu, av, off));
+    }
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      cm[j] = encode_m(m[j], am);
+      cv[j] = encode_v(v[j], av);
+    }
+    if (lane == 0) {
+      t.m_absmax[qb] = am;
+      t.v_absmax[qb] = av;
+    }
+  }
+  if (vec) {
+    *reinterpret_cast<float4*>(t.param + i0) = *reinterpret_cast<const float4*>(p);
+    *reinterpret_cast<float4*>(t.param + i0 + 4) = *reinterpret_cast<const float4*>(p + 4);
+    if (t.shadow) *reinterpret_cast<uint4*>(t.shadow + i0) = make_uint4(pack_bf16x2(p[0], p[1]), pack_bf16x2(p[2], p[3]), pack_bf16x2(p[4], p[5]), pack_bf16x2(p[6], p[7]));
+    if (q8) {
+      *reinterpret_cast<uint2*>(t.m8 + i0) = *reinterpret_cast<const uint2*>(cm);
+      *reinterpret_cast<uint2*>(t.v8 + i0) = *reinterpret_cast<const uint2*>(cv);
+    } else {
+      *reinterpret_cast<float4*>(t.m + i0) = *reinterpret_cast<const float4*>(m);
+      *reinterpret_cast<float4*>(t.m + i0 + 4) = *reinterpret_cast<const float4*>(m + 4);
+      *reinterpret_cast<float4*>(t.v + i0) = *reinterpret_cast<const float4*>(v);
+      *reinterpret_cast<float4*>(t.v + i0 + 4) = *reinterpret_cast<const float4*>(v + 4);
+    }
+  } else {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      if (i0 + j >= t.numel) continue;
+      t.param[i0 + j] = p[j];
+      if (t.shadow) t.shadow[i0 + j] = __float2bfloat16_rn(p[j]);
+      if (q8) {
+        t.m8[i0 + j] = cm[j];
+        t.v8[i0 + j] = cv[j];
+      } else {
+        t.m[i0 + j] = m[j];
+        t.v[i0 + j] = v[j];
+      }
+    }
   }
 }
 
@@ -175,7 +224,7 @@ extern "C" int sb_adamw_step(const void* tensors, const void* chunks, int n_chun
   AdamArgs a{lr, beta1, beta2, eps, weight_decay, bias1, bias2, grad_scale};
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (eight_bit)
-    adamw_8bit_kernel<<<n_chunks * (CHUNK / 256), 256, 0, st>>>(static_cast<const TensorDesc*>(tensors), static_cast<const ChunkDesc*>(chunks), a);
+    adamw_8bit_kernel<<<n_chunks, 256, 0, st>>>(static_cast<const TensorDesc*>(tensors), static_cast<const ChunkDesc*>(chunks), a);
   else
     adamw_fp32_kernel<<<n_chunks, 256, 0, st>>>(static_cast<const TensorDesc*>(tensors), static_cast<const ChunkDesc*>(chunks), a);
   return static_cast<int>(cudaGetLastError());

@@ -111,16 +111,31 @@ __global__ void __launch_bounds__(256) dw_fused_kernel(const float* __restrict__
     for (int c = 0; c < 8; ++c) {
       if (n0 + c >= n_total) continue;
       const int beg = colptr[n0 + c], end = colptr[n0 + c + 1];
-      for (int e = beg; e < end; ++e) {
-        const int row = rows_sorted[e];
-        const float v = vals_sorted[e];
-        const uint2 raw = __ldg(reinterpret_cast<const uint2*>(dy + static_cast<size_t>(row) * ldy + o0));
-        const __nv_bfloat162 p0 = *reinterpret_cast<const __nv_bfloat162*>(&raw.x);
-        const __nv_bfloat162 p1 = *reinterpret_cast<const __nv_bfloat162*>(&raw.y);
-        acc[c][0] = fmaf(v, __low2float(p0), acc[c][0]);
-        acc[c][1] = fmaf(v, __high2float(p0), acc[c][1]);
-        acc[c][2] = fmaf(v, __low2float(p1), acc[c][2]);
-        acc[c][3] = fmaf(v, __high2float(p1), acc[c][3]);
+      // The dY row of an entry is only known after its row index is loaded; keep GATHER entries in
+      // flight per thread so the kernel is bound by bandwidth rather than by one load latency.
+      constexpr int GATHER = 8;
+      for (int e = beg; e < end; e += GATHER) {
+        int rr[GATHER];
+        float vv[GATHER];
+        uint2 raw[GATHER];
+#pragma unroll
+        for (int u = 0; u < GATHER; ++u) {
+          const bool ok = e + u < end;
+          rr[u] = ok ? __ldg(rows_sorted + e + u) : 0;
+          vv[u] = ok ? __ldg(vals_sorted + e + u) : 0.f;
+        }
+#pragma unroll
+        for (int u = 0; u < GATHER; ++u)
+          raw[u] = __ldg(reinterpret_cast<const uint2*>(dy + static_cast<size_t>(rr[u]) * ldy + o0));
+#pragma unroll
+        for (int u = 0; u < GATHER; ++u) {
+          const __nv_bfloat162 p0 = *reinterpret_cast<const __nv_bfloat162*>(&raw[u].x);
+          const __nv_bfloat162 p1 = *reinterpret_cast<const __nv_bfloat162*>(&raw[u].y);
+          acc[c][0] = fmaf(vv[u], __low2float(p0), acc[c][0]);
+          acc[c][1] = fmaf(vv[u], __high2float(p0), acc[c][1]);
+          acc[c][2] = fmaf(vv[u], __low2float(p1), acc[c][2]);
+          acc[c][3] = fmaf(vv[u], __high2float(p1), acc[c][3]);
+        }
       }
     }
   }

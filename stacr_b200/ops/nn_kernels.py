@@ -78,3 +78,12 @@ def cast_bf16(src: torch.Tensor) -> torch.Tensor:
     _lib.check_rc(rc, "sb_cast_f32_bf16")
     _lib.count(1)
     return dst
+
+
+def rotary_qk_(qkv: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, seq: int, heads: int, head_dim: int, rot: int, sign: float) -> None:
+    """In-place rotary embedding of the q and k parts of contiguous bf16 ``qkv`` ``[tokens, heads, 3*head_dim]``."""
+    tokens = qkv.numel() // (heads * 3 * head_dim)
+    rc = _lib.load().sb_rotary_qk(_lib.ptr(qkv), _lib.ptr(cos), _lib.ptr(sin), c_ll(tokens), c_int(seq), c_int(heads), c_int(head_dim),
+                                  c_int(rot), c_float(sign), c_int(_lib.sm_count(qkv.device)), _lib.stream_ptr())
+    _lib.check_rc(rc, "sb_rotary_qk")
+    _lib.count(1)

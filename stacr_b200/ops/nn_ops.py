@@ -107,3 +107,38 @@ def linear_cross_entropy(hidden, weight, target, chunk: int = 0):
         n = (t != -100).sum()
         total = total + cross_entropy(F.linear(hidden[lo:lo + chunk], weight), t).float() * n
     return total / valid
+
+
+# ------------------------------------------------------------------------------ rotary embedding
+class _RotaryQKFn(torch.autograd.Function):
+    """Rotate q and k inside a fused qkv projection output, in place (the projection does not need its output for backward)."""
+
+    @staticmethod
+    def forward(ctx, qkv, cos, sin, seq, heads, head_dim, rot):
+        from . import nn_kernels
+
+        nn_kernels.rotary_qk_(qkv, cos, sin, seq, heads, head_dim, rot, 1.0)
+        ctx.mark_dirty(qkv)
+        ctx.save_for_backward(cos, sin)
+        ctx.dims = (seq, heads, head_dim, rot)
+        return qkv
+
+    @staticmethod
+    def backward(ctx, grad):
+        from . import nn_kernels
+
+        cos, sin = ctx.saved_tensors
+        g = grad.contiguous()
+        if g.data_ptr() == grad.data_ptr():
+            g = grad.clone()
+        nn_kernels.rotary_qk_(g, cos, sin, *ctx.dims, -1.0)
+        return g, None, None, None, None, None, None
+
+
+def rotary_qk_supported(qkv: torch.Tensor, head_dim: int, rot: int) -> bool:
+    return _kernel_tensor(qkv) and qkv.is_contiguous() and rot % 16 == 0 and head_dim % 8 == 0 and rot > 0
+
+
+def rotary_qk(qkv, cos_half, sin_half, seq: int, heads: int, head_dim: int, rot: int):
+    """``qkv``: ``[B, S, heads * 3 * head_dim]`` bf16 (per-head interleaved q|k|v); tables ``[S, rot/2]`` fp32."""
+    return _RotaryQKFn.apply(qkv, cos_half, sin_half, seq, heads, head_dim, rot)

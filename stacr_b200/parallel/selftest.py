@@ -1,0 +1,91 @@
+"""Multi-GPU self-test of the symmetric-memory all-reduce kernels.
+
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 -m stacr_b200.parallel.selftest
+
+Each rank fills a symmetric buffer with rank-dependent values, reduces slices of it with the
+two-shot peer kernel and (when the fabric exposes a multicast address) the multimem kernel, and
+compares with ``torch.distributed.all_reduce`` on a copy.  Also times both against NCCL with CUDA
+events (max over ranks).  Prints one JSON line from rank 0 and exits non-zero on a mismatch.
+"""
+
+from __future__ import annotations
+
+import json
+import sys
+
+import torch
+import torch.distributed as dist
+
+from ..ops import _lib
+from . import symm
+from .ddp import init_distributed
+
+
+def _time(fn, iters=10):
+    for _ in range(3):
+        fn()
+    dist.barrier()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(iters):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    t = torch.tensor([e0.elapsed_time(e1) / iters], device="cuda")
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t)
+
+
+def main() -> int:
+    rank, world, local = init_distributed("nccl")
+    dev = torch.device("cuda", local)
+    report = {"world": world, "available": symm.available()}
+    if world < 2 or not symm.available():
+        if rank == 0:
+            print(json.dumps(report))
+        return 0
+    n = 64 * 1024 * 1024  # 256 MB of fp32
+    buf = symm.SymmetricBuffer(n, torch.float32, dev)
+    report["multicast"] = buf.multicast_ptr != 0
+    ok = True
+    modes = [("two_shot", False)] + ([("multimem", True)] if buf.multicast_ptr else [])
+    for name, mm in modes:
+        buf.use_multimem = mm
+        for lo, hi in ((0, 4096), (1024, 1024 + 1000 * 4), (0, n), (n // 2 + 8, n - 4)):
+            gen = torch.Generator(device=dev).manual_seed(17 * rank + lo)
+            buf.tensor.copy_(torch.randn(n, device=dev, generator=gen))
+            expect = buf.tensor[lo:hi].clone()
+            torch.cuda.synchronize()
+            dist.barrier()
+            dist.all_reduce(expect)
+            expect /= world
+            untouched = buf.tensor[:lo].clone(), buf.tensor[hi:].clone()
+            buf.all_reduce_(lo, hi, average=True)
+            torch.cuda.synchronize()
+            _lib.check_status(dev)
+            err = float((buf.tensor[lo:hi] - expect).abs().max())
+            same = torch.equal(buf.tensor[:lo], untouched[0]) and torch.equal(buf.tensor[hi:], untouched[1])
+            good = err < 1e-5 and same
+            ok &= good
+            if rank == 0 and not good:
+                report.setdefault("failures", []).append({"mode": name, "lo": lo, "hi": hi, "err": err, "outside_untouched": same})
+            dist.barrier()
+        ms = _time(lambda: buf.all_reduce_(0, n, average=False))
+        report[f"{name}_ms_256MB"] = ms
+        report[f"{name}_busbw_GBs"] = 2 * (world - 1) / world * n * 4 / ms / 1e6
+    plain = torch.randn(n, device=dev)
+    ms = _time(lambda: dist.all_reduce(plain))
+    report["nccl_ms_256MB"] = ms
+    report["nccl_busbw_GBs"] = 2 * (world - 1) / world * n * 4 / ms / 1e6
+    flag = torch.tensor([int(ok)], device=dev)
+    dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+    report["ok"] = bool(flag.item())
+    if rank == 0:
+        print(json.dumps(report), flush=True)
+    dist.destroy_process_group()
+    return 0 if report["ok"] else 1
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -91,3 +91,26 @@ def test_smoke_entry_point():
     import __graft_entry__ as entry
 
     entry.smoke()
+
+
+def test_fused_rotary_matches_framework_ops():
+    from stacr_b200.models.neox import apply_rotary, rotary_tables
+    from stacr_b200.ops import nn_ops
+
+    torch.manual_seed(5)
+    b, s, h, hd, rot = 2, 96, 4, 64, 16
+    qkv = torch.randn(b, s, h * 3 * hd, device="cuda").bfloat16()
+    ref_in = qkv.detach().clone().float().requires_grad_(True)
+    q, k, v = (t.transpose(1, 2) for t in ref_in.view(b, s, h, 3 * hd).split(hd, dim=-1))
+    cos, sin = rotary_tables(s, rot, 10000.0, "cuda")
+    ref = torch.cat([apply_rotary(q, cos, sin, rot).transpose(1, 2), apply_rotary(k, cos, sin, rot).transpose(1, 2), v.transpose(1, 2)], dim=-1)
+    inv = 1.0 / (10000.0 ** (torch.arange(0, rot, 2, device="cuda", dtype=torch.float32) / rot))
+    ang = torch.outer(torch.arange(s, device="cuda", dtype=torch.float32), inv)
+    x = (qkv.clone() * 1.0).requires_grad_(True)
+    y = x * 1.0  # non-leaf, so the in-place op is legal
+    out = nn_ops.rotary_qk(y, ang.cos().contiguous(), ang.sin().contiguous(), s, h, hd, rot)
+    torch.testing.assert_close(out.float().view(b, s, h, 3 * hd), ref, rtol=2e-2, atol=2e-2)
+    g = torch.randn_like(ref)
+    ref.backward(g)
+    out.view(b, s, h, 3 * hd).backward(g.bfloat16())
+    torch.testing.assert_close(x.grad.float().view(b, s, h, 3 * hd), ref_in.grad.view(b, s, h, 3 * hd), rtol=3e-2, atol=3e-2)
