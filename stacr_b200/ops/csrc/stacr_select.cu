@@ -480,3 +480,116 @@ extern "C" int sb_residual_block_energy(const void* x, const void* c, const void
       r, ldx, bs, energy);
   return static_cast<int>(cudaGetLastError());
 }
+
+// ------------------------------------------------------------------------------------------------
+// Allocation-free variant (declared in stacr_noalloc.h).  Scratch lives in a file-scope device
+// array; device code names it directly, host code must use the address obtained once per device
+// from cudaGetSymbolAddress (the host-side name of a __device__ variable is not a device address).
+// ------------------------------------------------------------------------------------------------
+#include "stacr_noalloc.h"
+
+namespace sb {
+
+constexpr int NOALLOC_INTS_PER_CHUNK = 8;  // thr_bin, thr_need, max_bin, tie_count, out_count, quota, out_offset, pad
+constexpr size_t NOALLOC_HIST_BYTES = static_cast<size_t>(SB_NOALLOC_MAX_CHUNKS) * NBINS * sizeof(unsigned int);
+constexpr size_t NOALLOC_BYTES = NOALLOC_HIST_BYTES + SB_NOALLOC_MAX_CHUNKS * NOALLOC_INTS_PER_CHUNK * sizeof(int);
+
+static __device__ __align__(256) unsigned char g_noalloc_scratch[NOALLOC_BYTES];
+
+__host__ __device__ inline int noalloc_chunk_quota(int rows, int chunk_rows, int quota_per_chunk, int chunk) {
+  const int begin = chunk * chunk_rows;
+  const int len = (rows - begin) < chunk_rows ? (rows - begin) : chunk_rows;
+  if (len == chunk_rows) return quota_per_chunk;
+  long long q = (static_cast<long long>(quota_per_chunk) * len + chunk_rows / 2) / chunk_rows;
+  return q < 1 ? 1 : static_cast<int>(q);
+}
+
+// Clears the histogram bins and counters of the chunks in use and fills quota / out_offset.
+__global__ void noalloc_prepare_kernel(int rows, int chunk_rows, int quota_per_chunk, int nchunks) {
+  unsigned int* hist = reinterpret_cast<unsigned int*>(g_noalloc_scratch);
+  int* ints = reinterpret_cast<int*>(g_noalloc_scratch + NOALLOC_HIST_BYTES);
+  const size_t bins = static_cast<size_t>(nchunks) * NBINS;
+  for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < bins; i += static_cast<size_t>(gridDim.x) * blockDim.x)
+    hist[i] = 0u;
+  if (blockIdx.x == 0 && threadIdx.x == 0) {
+    int running = 0;
+    for (int c = 0; c < nchunks; ++c) {
+      const int quota = noalloc_chunk_quota(rows, chunk_rows, quota_per_chunk, c);
+      for (int f = 0; f < 5; ++f) ints[f * SB_NOALLOC_MAX_CHUNKS + c] = 0;
+      ints[5 * SB_NOALLOC_MAX_CHUNKS + c] = quota;
+      ints[6 * SB_NOALLOC_MAX_CHUNKS + c] = running;
+      running += quota;
+    }
+  }
+}
+
+// Device address of the scratch array for the current device, looked up on first use.
+static int noalloc_scratch_for_current_device(unsigned char** out) {
+  constexpr int MAX_DEVICES = 64;
+  static unsigned char* cached[MAX_DEVICES] = {nullptr};
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return static_cast<int>(e);
+  if (dev < 0 || dev >= MAX_DEVICES) return -8;
+  if (cached[dev] == nullptr) {
+    void* ptr = nullptr;
+    e = cudaGetSymbolAddress(&ptr, g_noalloc_scratch);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    cached[dev] = static_cast<unsigned char*>(ptr);
+  }
+  *out = cached[dev];
+  return 0;
+}
+
+}  // namespace sb
+
+extern "C" long long sb_residual_topk_noalloc_count(int rows, int chunk_rows, int quota_per_chunk) {
+  if (rows <= 0 || chunk_rows <= 0 || quota_per_chunk < 0) return -1;
+  const int nchunks = (rows + chunk_rows - 1) / chunk_rows;
+  long long total = 0;
+  for (int c = 0; c < nchunks; ++c) total += sb::noalloc_chunk_quota(rows, chunk_rows, quota_per_chunk, c);
+  return total;
+}
+
+extern "C" int sb_residual_topk_noalloc(const void* x, const void* c, const void* q, int rows, int n, int r, int ldx,
+                                        int chunk_rows, int quota_per_chunk, int bits, int* idx32, long long* idx64, void* val,
+                                        float* scale, int* status, void* stream) {
+  using namespace sb;
+  if (rows <= 0 || n <= 0 || chunk_rows <= 0 || quota_per_chunk < 0) return -2;
+  if (r < 1 || r > 32) return -2;
+  if ((idx32 == nullptr) == (idx64 == nullptr)) return -2;
+  if ((ldx & 7) || (reinterpret_cast<uintptr_t>(x) & 15) || (reinterpret_cast<uintptr_t>(c) & 15)) return -3;
+  const int nchunks = (rows + chunk_rows - 1) / chunk_rows;
+  if (nchunks > SB_NOALLOC_MAX_CHUNKS) return -7;  // larger than the built-in scratch: rejected, nothing launched
+  unsigned char* scratch = nullptr;
+  int rc = noalloc_scratch_for_current_device(&scratch);
+  if (rc) return rc;
+  int sms = 0, dev = 0;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  int* ints = reinterpret_cast<int*>(scratch + NOALLOC_HIST_BYTES);
+  SelectParams p;
+  p.x = static_cast<const __nv_bfloat16*>(x);
+  p.c = static_cast<const __nv_bfloat16*>(c);
+  p.q = static_cast<const __nv_bfloat16*>(q);
+  p.rows = rows; p.n = n; p.r = r; p.ldx = ldx;
+  p.chunk_rows = chunk_rows; p.nchunks = nchunks;
+  p.parts = sms / nchunks > 0 ? sms / nchunks : 1;
+  p.hist = reinterpret_cast<unsigned int*>(scratch);
+  p.thr_bin = ints; p.thr_need = ints + SB_NOALLOC_MAX_CHUNKS; p.max_bin = ints + 2 * SB_NOALLOC_MAX_CHUNKS;
+  p.tie_count = ints + 3 * SB_NOALLOC_MAX_CHUNKS; p.out_count = ints + 4 * SB_NOALLOC_MAX_CHUNKS;
+  p.quota = ints + 5 * SB_NOALLOC_MAX_CHUNKS; p.out_offset = ints + 6 * SB_NOALLOC_MAX_CHUNKS;
+  p.bits = bits; p.out_idx32 = idx32; p.out_idx64 = idx64; p.out_val = val; p.out_scale = scale; p.status = status;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  noalloc_prepare_kernel<<<64, 256, 0, st>>>(rows, chunk_rows, quota_per_chunk, nchunks);
+  rc = static_cast<int>(cudaGetLastError());
+  if (rc) return rc;
+  const int rp = r <= 8 ? 8 : (r <= 16 ? 16 : 32);
+  rc = rp == 8 ? launch_select<8>(p, 0, st) : rp == 16 ? launch_select<16>(p, 0, st) : launch_select<32>(p, 0, st);
+  if (rc) return rc;
+  residual_scan_kernel<<<nchunks, 1024, 0, st>>>(p);
+  residual_scale_kernel<<<1, 32, 0, st>>>(p);
+  rc = static_cast<int>(cudaGetLastError());
+  if (rc) return rc;
+  return rp == 8 ? launch_select<8>(p, 1, st) : rp == 16 ? launch_select<16>(p, 1, st) : launch_select<32>(p, 1, st);
+}
