@@ -53,11 +53,15 @@ class SymmetricBuffer:
         self._flag_handle = symm_mem.rendezvous(self.flags, self.group)
         torch.cuda.synchronize(device)
         dist.barrier(self.group)  # nobody may publish a flag before every rank has zeroed its own
-        ptrs = [int(p) for p in self.handle.buffer_ptrs]
-        pads = [int(p) for p in self._flag_handle.buffer_ptrs]
+        off = int(getattr(self.handle, "offset", 0) or 0)  # byte offset of the tensor inside its allocation
+        foff = int(getattr(self._flag_handle, "offset", 0) or 0)
+        ptrs = [int(p) + off for p in self.handle.buffer_ptrs]
+        pads = [int(p) + foff for p in self._flag_handle.buffer_ptrs]
         self._peer_ptrs = torch.tensor(ptrs, dtype=torch.int64, device=device)
         self._pad_ptrs = torch.tensor(pads, dtype=torch.int64, device=device)
         self.multicast_ptr = int(getattr(self.handle, "multicast_ptr", 0) or 0)
+        if self.multicast_ptr:
+            self.multicast_ptr += off
         self.use_multimem = self.multicast_ptr != 0 and os.environ.get("STACR_SYMM_MULTIMEM", "1") == "1"
         self._epoch = 0
         self.numel = numel
