@@ -28,6 +28,9 @@ import threading
 import time
 
 REPO = os.path.dirname(os.path.abspath(__file__))
+# keep stdout to the one JSON line: NCCL prints its version banner to stdout at the VERSION/INFO levels
+if os.environ.get("NCCL_DEBUG", "").upper() in ("", "VERSION"):
+    os.environ["NCCL_DEBUG"] = "WARN"
 
 MODEL = dict(vocab_size=50304, hidden_size=2048, num_hidden_layers=24, num_attention_heads=16, intermediate_size=8192,
              rotary_pct=0.25, max_position_embeddings=2048, use_parallel_residual=True)

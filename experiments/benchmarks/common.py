@@ -1,0 +1,292 @@
+"""Shared machinery of the measurement grids: one matched training cell, paired gradient fidelity, SSP ledger, JSONL output.
+
+``run_config`` runs one cell: build the model (in-tree random init when weights are not available offline), apply
+selective checkpointing / CPU offload / freezing / STAC-R on chosen blocks, pre-stage all batches on the device,
+train with the device-timed loop, and return peak memory, tokens/s, losses and validation perplexity.
+Parity: experiments/benchmarks/common.py:22-686 of the reference project.  Timing uses CUDA events instead of a
+host clock.
+"""
+
+from __future__ import annotations
+
+import gc
+import json
+import math
+import os
+import time
+import uuid
+from contextlib import nullcontext
+from pathlib import Path
+from typing import Any, Callable, Dict, Iterable, Optional
+
+import torch
+
+import stacr_b200 as S
+from stacr_b200.composition import block_target_names, checkpoint_blocks, offload_blocks, transformer_blocks
+from stacr_b200.models import build_model, load_model_and_tokenizer
+from stacr_b200.utils import set_seed  # noqa: F401  (re-exported for the grids)
+
+RESULTS = Path(os.environ.get("STACR_RESULTS", "results"))
+RUN_ID = os.environ.get("STACR_RUN_ID") or uuid.uuid4().hex[:12]
+QUIET = os.environ.get("STACR_QUIET", "0") == "1"
+PARAMETERS: Dict[str, Any] = {}
+_RECORDER: Optional[Callable[..., dict]] = None  # set by the dry-run planner: cells are recorded, not run
+
+
+def configure(**overrides) -> None:
+    """Install CLI overrides (steps, model_id, bs, seq, ...) that ``resolve_parameters`` merges into grid defaults."""
+    PARAMETERS.clear()
+    PARAMETERS.update({k: v for k, v in overrides.items() if v is not None})
+    if "STACR_STEPS" in os.environ and "steps" not in PARAMETERS:
+        PARAMETERS["steps"] = int(os.environ["STACR_STEPS"])
+
+
+def resolve_parameters(**defaults) -> Dict[str, Any]:
+    return {**defaults, **{k: v for k, v in PARAMETERS.items() if k in defaults or k in ("device", "optimizer", "dataset", "attn_impl")}}
+
+
+def set_recorder(fn: Optional[Callable[..., dict]]) -> None:
+    global _RECORDER
+    _RECORDER = fn
+
+
+def sync() -> None:
+    if torch.cuda.is_available():
+        torch.cuda.synchronize()
+
+
+def free_all() -> None:
+    gc.collect()
+    if torch.cuda.is_available():
+        torch.cuda.empty_cache()
+        torch.cuda.reset_peak_memory_stats()
+
+
+def gib(n: float) -> float:
+    return n / 1024**3
+
+
+def amp_ctx(enabled: bool = True, dtype=torch.bfloat16):
+    if not enabled:
+        return nullcontext()
+    return torch.autocast("cuda" if torch.cuda.is_available() else "cpu", dtype=dtype)
+
+
+def load_model(model_id: str, device: str = "cuda", dtype=torch.float32, attn_impl: Optional[str] = None, **overrides):
+    """In-tree architecture by preset name when known (random init), else Hugging Face weights from the local cache."""
+    try:
+        model = build_model(model_id, **overrides)
+    except KeyError:
+        model, _ = load_model_and_tokenizer(model_id, dtype=dtype, attn_implementation=attn_impl, local_files_only=True)
+    return model.to(device=device, dtype=dtype).train()
+
+
+def get_batches(model_id: str, split: str, bs: int, seq: int, count: int, dataset: str = "synthetic", device: str = "cuda", vocab: Optional[int] = None, seed: int = 0):
+    """``count`` language-model batches resident on ``device`` (uniform-random tokens offline)."""
+    gen = torch.Generator().manual_seed(seed + (1 if split != "train" else 0))
+    vocab = vocab or 50257
+    out = []
+    for _ in range(count):
+        ids = torch.randint(0, vocab, (bs, seq), generator=gen).to(device)
+        out.append({"input_ids": ids, "attention_mask": torch.ones_like(ids), "labels": ids.clone()})
+    return out
+
+
+def build_optimizer(model, lr: float = 5e-5, eight_bit: bool = True, weight_decay: float = 0.0):
+    from stacr_b200.optim import AdamW, AdamW8bit
+
+    params = [p for p in model.parameters() if p.requires_grad]
+    name = PARAMETERS.get("optimizer", "adamw8bit" if eight_bit else "adamw")
+    if name == "adamw8bit" and params and params[0].is_cuda:
+        return AdamW8bit(params, lr=lr, weight_decay=weight_decay)
+    if params and params[0].is_cuda:
+        return AdamW(params, lr=lr, weight_decay=weight_decay)
+    return torch.optim.AdamW(params, lr=lr, weight_decay=weight_decay)
+
+
+def apply_selective_checkpointing(model, every: int, offset: int = 0) -> int:
+    if not every:
+        return 0
+    blocks = transformer_blocks(model)
+    return len(checkpoint_blocks(blocks, [i for i in range(len(blocks)) if i % every == offset]))
+
+
+def apply_selective_offload(model, every: int, offset: int = 0) -> int:
+    if not every:
+        return 0
+    blocks = transformer_blocks(model)
+    return len(offload_blocks(blocks, [i for i in range(len(blocks)) if i % every == offset]))
+
+
+def stacr_on_blocks(model, cfg: dict, block_pred: Optional[Callable[[int], bool]] = None):
+    """Apply STAC-R, optionally only to projections inside blocks selected by ``block_pred(index)``."""
+    cfg = dict(cfg)
+    cfg.setdefault("turbo_after_step", None)
+    if block_pred is None:
+        return S.apply_stacr(model, **cfg)
+    blocks = transformer_blocks(model)
+    sel = {k: cfg.pop(k) for k in list(cfg) if k in ("surface", "min_features", "extra_names", "exclude_names", "trainable_only")}
+    names = block_target_names(model, blocks, block_pred, **sel)
+    return S.apply_stacr(model, surface="none", target_names=names, allow_empty=True, **cfg)
+
+
+class SSPLedger:
+    """Saved-surface predictor inputs: bytes autograd would save densely for the wrapped layers vs factor bytes."""
+
+    def __init__(self, layers, value_bytes: int = 2):
+        self.layers, self.value_bytes = list(layers), value_bytes
+        self.wrapped_bytes = self.payload_bytes = self.basis_bytes = 0
+        self.probed = False
+
+    def probe(self, rows: int) -> None:
+        if self.probed:
+            return
+        for layer in self.layers:
+            rep = layer.stored_bytes(rows, self.value_bytes)
+            self.wrapped_bytes += rows * layer.in_features * self.value_bytes
+            self.payload_bytes += rep["coeff"] + rep["residual"] + rep["saved_basis_cast"]
+            self.basis_bytes += rep["persistent_basis"]
+        self.probed = True
+
+    def report(self, baseline_peak_bytes: Optional[int]) -> dict:
+        from stacr_b200.analysis import surface_ledger
+
+        if not self.probed or not baseline_peak_bytes:
+            return {}
+        return surface_ledger(self.wrapped_bytes, self.payload_bytes, baseline_peak_bytes, basis_bytes=self.basis_bytes)
+
+
+def run_config(method: str, seed: int = 42, *, model_id: str = "gpt2-medium", bs: int = 8, seq: int = 1024, steps: int = 60,
+               measure_from: int = 20, stacr_cfg: Optional[dict] = None, stacr_block_pred=None, ckpt_every: int = 0, ckpt_offset: int = 0,
+               offload_every: int = 0, freeze_mlp: bool = False, eight_bit: bool = True, lr: float = 5e-5, amp: bool = True,
+               model_dtype=torch.float32, device: Optional[str] = None, eval_batches: int = 4, dataset: str = "synthetic",
+               attn_impl: Optional[str] = None, baseline_peak_bytes: Optional[int] = None, model_overrides: Optional[dict] = None, **extra) -> dict:
+    """One measurement cell.  Under the dry-run planner the arguments are recorded and a placeholder row returned."""
+    args = dict(method=method, seed=seed, model_id=model_id, bs=bs, seq=seq, steps=steps, measure_from=measure_from, stacr_cfg=stacr_cfg,
+                ckpt_every=ckpt_every, offload_every=offload_every, freeze_mlp=freeze_mlp, eight_bit=eight_bit, dataset=dataset, **extra)
+    if _RECORDER is not None:
+        return _RECORDER(**args)
+    device = device or PARAMETERS.get("device") or ("cuda" if torch.cuda.is_available() else "cpu")
+    cuda = device == "cuda"
+    free_all()
+    set_seed(seed)
+    model = load_model(model_id, device, dtype=model_dtype, attn_impl=attn_impl, **(model_overrides or {}))
+    n_ckpt = apply_selective_checkpointing(model, ckpt_every, ckpt_offset)
+    n_off = apply_selective_offload(model, offload_every, 1 if offload_every > 1 else 0)
+    if freeze_mlp:
+        for name in S.select_target_names(model, surface="mlp"):
+            model.get_submodule(name).requires_grad_(False)
+    if stacr_cfg and extra.get("basis_comparator"):
+        from stacr_b200.comparators.activation import apply_comparator
+
+        layers = apply_comparator(model, extra["basis_comparator"], dict(stacr_cfg))
+    else:
+        layers = stacr_on_blocks(model, stacr_cfg, stacr_block_pred) if stacr_cfg else []
+    opt = build_optimizer(model, lr, eight_bit and cuda)
+    vocab = getattr(getattr(model, "config", None), "vocab_size", None)
+    train = get_batches(model_id, "train", bs, seq, steps, dataset, device, vocab, seed)
+    ledger = SSPLedger(layers)
+    losses = []
+    ev0 = ev1 = None
+    t0 = None
+    for i, batch in enumerate(train):
+        S.set_step(layers, i)
+        if i == measure_from:
+            sync()
+            if cuda:
+                torch.cuda.reset_peak_memory_stats()
+                ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                ev0.record()
+            t0 = time.perf_counter()
+        opt.zero_grad(set_to_none=True)
+        with amp_ctx(amp and cuda):
+            loss = model(**batch).loss
+        value = float(loss)
+        if not math.isfinite(value):
+            raise FloatingPointError(f"Nonfinite loss at step {i}")
+        loss.backward()
+        opt.step()
+        losses.append(value)
+        ledger.probe(bs * seq)
+    if cuda and ev0 is not None:
+        ev1.record()
+        sync()
+        elapsed = ev0.elapsed_time(ev1) / 1e3
+    else:
+        elapsed = time.perf_counter() - (t0 or time.perf_counter())
+    peak = torch.cuda.max_memory_allocated() if cuda else 0
+    measured = max(0, steps - measure_from)
+    val_ppl = None
+    if eval_batches:
+        model.eval()
+        with torch.no_grad(), amp_ctx(amp and cuda):
+            nll = [float(model(**b).loss) for b in get_batches(model_id, "validation", bs, seq, eval_batches, dataset, device, vocab, seed)]
+        val_ppl = math.exp(min(700.0, sum(nll) / len(nll)))
+    row = {
+        "method": method, "seed": seed, "model": model_id, "bs": bs, "seq": seq, "steps": steps, "steps_measured": measured,
+        "n_checkpointed_blocks": n_ckpt, "n_offloaded_blocks": n_off, "n_wrapped_layers": len(layers), "time_s": elapsed,
+        "peak_bytes": peak, "peak_GiB": gib(peak), "tokens_per_s": bs * seq * measured / elapsed if elapsed > 0 and measured else None,
+        "final_train_loss": losses[-1] if losses else None, "validation_ppl": val_ppl, "data": dataset, "status": "ok",
+        "ssp": ledger.report(baseline_peak_bytes), **{k: v for k, v in extra.items() if isinstance(v, (int, float, str, bool, type(None)))},
+    }
+    del model, opt, train, layers
+    free_all()
+    return row
+
+
+def emit(record: dict, path: str | Path) -> None:
+    """Append one enriched JSON line (run id, library versions, CLI overrides)."""
+    path = Path(path)
+    path.parent.mkdir(parents=True, exist_ok=True)
+    enriched = {"run_id": RUN_ID, "torch": torch.__version__, "stacr_b200": S.__version__, "overrides": dict(PARAMETERS),
+                "hwtag": os.environ.get("STACR_HWTAG"), **record}
+    with path.open("a", encoding="utf-8") as fh:
+        fh.write(json.dumps(enriched, default=str) + "\n")
+    if not QUIET:
+        keys = ("method", "model", "peak_GiB", "tokens_per_s", "validation_ppl", "status")
+        print("  " + "  ".join(f"{k}={record[k]:.4g}" if isinstance(record.get(k), float) else f"{k}={record.get(k)}" for k in keys if k in record), flush=True)
+
+
+def gradient_fidelity(model_id: str, stacr_cfg: dict, *, bs: int = 2, seq: int = 256, steps: int = 6, seed: int = 42, device: Optional[str] = None,
+                      model_overrides: Optional[dict] = None) -> dict:
+    """Two-model paired protocol: same weights and batch, exact vs compressed gradients, cosine per step."""
+    import copy
+
+    from stacr_b200.diagnostics import compression_diagnostics
+
+    if _RECORDER is not None:
+        return _RECORDER(method="fidelity", model_id=model_id, stacr_cfg=stacr_cfg, bs=bs, seq=seq, steps=steps, seed=seed)
+    device = device or ("cuda" if torch.cuda.is_available() else "cpu")
+    set_seed(seed)
+    ref = load_model(model_id, device, **(model_overrides or {}))
+    test = copy.deepcopy(ref)
+    paired = dict(test.named_parameters())
+    layers = stacr_on_blocks(test, stacr_cfg)
+    wrapped = {l.source_name + ".weight" for l in layers}
+    vocab = getattr(getattr(ref, "config", None), "vocab_size", None)
+    batches = get_batches(model_id, "train", bs, seq, steps, "synthetic", device, vocab, seed)
+    whole, local = [], []
+    for step, batch in enumerate(batches):
+        S.set_step(layers, step)
+        with torch.no_grad():
+            pass
+        test.train()
+        with amp_ctx(device == "cuda"):
+            test(**batch)  # fits / refreshes the bases
+        for m in (ref, test):
+            m.zero_grad(set_to_none=True)
+            with compression_diagnostics(m), amp_ctx(device == "cuda"):
+                m(**batch).loss.backward()
+        dot = na = nb = 0.0
+        for name, p in ref.named_parameters():
+            if p.grad is None or paired[name].grad is None:
+                continue
+            a, b = p.grad.double(), paired[name].grad.double()
+            d, x, y = float((a * b).sum()), float(a.square().sum()), float(b.square().sum())
+            dot, na, nb = dot + d, na + x, nb + y
+            if name in wrapped and x * y > 0:
+                local.append(d / math.sqrt(x * y))
+        whole.append(dot / math.sqrt(na * nb) if na * nb > 0 else 1.0)
+    return {"model": model_id, "steps": steps, "mean_cosine": sum(whole) / len(whole), "worst_cosine": min(whole),
+            "local_mean_cosine": sum(local) / len(local) if local else None, "local_worst_cosine": min(local) if local else None,
+            "wrapped_layers": len(layers)}

@@ -1,0 +1,538 @@
+"""Protocol runner: one named training run with a method, a set of memory baselines and (optionally) DDP or TP.
+
+``ConvergenceConfig`` mirrors the field names of the reference's runner configuration (the subset that selects
+behaviour; unknown fields are rejected), ``run_convergence_experiment(cfg, logger)`` executes the run and writes
+``config.json`` / ``metrics.jsonl`` / ``profile.jsonl`` / ``final.json`` through the logger.
+Parity: experiments/protocols/training.py:146-5017 of the reference project (DDP helpers :442-528, target selection
+:796-847, replacement :885-1471, baselines :2047-2144, validation :2560-2607, gradient cosine :2610-2742, per-layer
+fidelity :3040-3215, spectrum telemetry :3314-3481, epoch loop :3484-4029, run :4032-5017).
+"""
+
+from __future__ import annotations
+
+import copy
+import math
+import os
+import time
+from dataclasses import asdict, dataclass, field, fields
+from typing import Any, Dict, List, Optional
+
+import torch
+import torch.distributed as dist
+from torch import nn
+
+import stacr_b200 as S
+from stacr_b200.adaptive import STACRConfig as AdaptiveConfig, STACRLinear as AdaptiveLinear, get_basis_pool, set_stacr_runtime_state
+from stacr_b200.models import build_model
+from stacr_b200.parallel import GradSync, broadcast_parameters
+from stacr_b200.protocols.baselines.amp import AMPManager
+from stacr_b200.protocols.baselines.checkpointing import apply_checkpointing
+from stacr_b200.protocols.baselines.offload import OffloadManager
+from stacr_b200.protocols.config.training import BaselineConfig
+from stacr_b200.protocols.layers import CompressedLinear
+from stacr_b200.protocols.planner import plan_stacr_layers, summarize_layer_decisions
+from stacr_b200.protocols.prac import PRACConfig, replace_linear_with_prac, set_prac_global_step
+from stacr_b200.protocols.profiling import PhaseProfiler
+from stacr_b200.protocols.tensor_parallel import sync_replicated_grads
+from stacr_b200.protocols.tp_gpt2 import TPActivationProfiler, apply_tensor_parallel_gpt2, disable_tp_dropout, get_tp_stacr_targets
+from stacr_b200.protocols.utils import set_all_seeds
+
+METHODS = ("baseline", "stacr", "stac", "svd", "tt", "tucker", "prac")
+
+
+@dataclass
+class ConvergenceConfig:
+    experiment: str = "convergence_training"
+    task: str = "synthetic_lm"           # synthetic_lm | wikitext103 | openwebtext | sst2
+    model: str = "gpt2-medium"
+    method: str = "baseline"
+    method_label: Optional[str] = None
+    run_tag: str = "run"
+    rank: int = 8
+    reshape_shape: Optional[List[int]] = None
+    factor_quantization_bits: Optional[int] = None
+    factor_native_backward: bool = True
+    use_lowrank_svd: bool = False
+    baseline: Optional[str] = None
+    baseline_cfg: Any = None
+    epochs: int = 1
+    batch_size: int = 8
+    lr: float = 5e-5
+    weight_decay: float = 0.0005
+    max_length: int = 1024
+    seed: int = 42
+    deterministic: bool = True
+    measure_memory: bool = True
+    monitor_grad_fidelity: bool = False
+    grad_fidelity_interval: int = 100
+    monitor_per_layer_grad_fidelity: bool = False
+    per_layer_grad_fidelity_interval: int = 120
+    monitor_activation_spectrum: bool = False
+    activation_spectrum_interval: int = 120
+    activation_spectrum_rank: int = 8
+    device: str = "auto"
+    use_data_parallel: bool = False
+    use_ddp: bool = False
+    use_tensor_parallel: bool = False
+    use_8bit_optimizer: bool = False
+    tp_scope: str = "mlp_only"
+    tp_stacr_scope: str = "row_only"
+    tp_profile_activations: bool = False
+    max_steps: int = 100
+    train_examples: int = 512
+    eval_examples: int = 32
+    grad_clip: float = 0.0
+    warmup_ratio: float = 0.1
+    save_final_model: bool = False
+    save_every_n_steps: Optional[int] = None
+    phase_profile_full_run: bool = False
+    quiet: bool = True
+    model_overrides: Dict[str, Any] = field(default_factory=dict)
+    # compression (adaptive engine) options, prefixed as in the reference runner
+    stacr_engine: str = "adaptive"
+    stacr_surface: str = "mlp"
+    stacr_min_features: int = 256
+    stacr_residual_mode: str = "block_sparse"
+    stacr_residual_budget: float = 0.005
+    stacr_update_trigger: str = "hybrid"
+    stacr_update_interval: int = 100
+    stacr_energy_threshold: float = 0.05
+    stacr_oja_learning_rate: float = 0.01
+    stacr_warmup_steps: int = 0
+    stacr_freeze_basis_after_warmup: bool = True
+    stacr_quantize_coefficients: bool = True
+    stacr_quantize_residuals: bool = True
+    stacr_residual_quantize_bits: int = 4
+    stacr_basis_dtype: str = "auto"
+    stacr_use_fused_kernel: bool = False
+    stacr_rank_mode: str = "fixed"
+    stacr_rank_min: int = 4
+    stacr_rank_max: int = 64
+    stacr_refresh_trigger: str = "off"
+    stacr_post_warmup_residual_mode: str = "full"
+    stacr_residual_warmup_steps: int = 0
+    stacr_index_compression: str = "none"
+    stacr_cpu_offload: bool = False
+    stacr_planner: str = "none"          # none | bytes: keep a layer only when saved - stored > 0
+    stacr_force_compress_layers: Optional[str] = None
+    prac_update_proj_gap: int = 50
+
+    def __post_init__(self):
+        if self.method not in METHODS:
+            raise ValueError(f"Unknown method {self.method!r}; choose from {METHODS}")
+        if self.use_ddp and self.use_tensor_parallel:
+            raise ValueError("Select DDP or tensor parallelism")
+        if isinstance(self.baseline_cfg, dict):
+            known = {f.name for f in fields(BaselineConfig)}
+            legacy = {"saved_tensors_offload": "offload", "saved_tensors_offload_min_bytes": "offload_min_bytes"}
+            mapped = {legacy.get(k, k): v for k, v in self.baseline_cfg.items()}
+            self.baseline_cfg = BaselineConfig(**{k: v for k, v in mapped.items() if k in known})
+        elif self.baseline_cfg is None:
+            self.baseline_cfg = BaselineConfig.from_legacy(self.baseline) if self.baseline else BaselineConfig()
+        if self.use_8bit_optimizer:
+            self.baseline_cfg.optimizer_8bit = True
+
+    @classmethod
+    def from_raw(cls, raw: Dict[str, Any]) -> "ConvergenceConfig":
+        known = {f.name for f in fields(cls)}
+        stray = sorted(set(raw) - known)
+        if stray:
+            raise ValueError(f"Unknown protocol fields: {stray}")
+        return cls(**raw)
+
+    def to_dict(self) -> Dict[str, Any]:
+        return asdict(self)
+
+
+# ------------------------------------------------------------------------------ distributed helpers
+def init_ddp() -> tuple[int, int, int]:
+    from stacr_b200.parallel import init_distributed
+
+    return init_distributed()
+
+
+def make_distributed_loader(batches: List[dict], rank: int, world: int) -> List[dict]:
+    """Strided split: rank r takes batches r, r+world, ..."""
+    return batches[rank::world] if world > 1 else batches
+
+
+def _ddp_reduce_train_metrics(loss_sum: float, tokens: int, steps: int, peak: float, device) -> dict:
+    if not (dist.is_initialized() and dist.get_world_size() > 1):
+        return {"loss_sum": loss_sum, "tokens": tokens, "steps": steps, "peak_bytes": peak}
+    sums = torch.tensor([loss_sum, tokens, steps], dtype=torch.float64, device=device)
+    dist.all_reduce(sums)
+    mx = torch.tensor([peak], dtype=torch.float32, device=device)
+    dist.all_reduce(mx, op=dist.ReduceOp.MAX)
+    return {"loss_sum": float(sums[0]), "tokens": int(sums[1]), "steps": int(sums[2]), "peak_bytes": float(mx)}
+
+
+# ------------------------------------------------------------------------------ data
+def build_batches(cfg: ConvergenceConfig, vocab: int, count: int, seed: int, device) -> List[dict]:
+    gen = torch.Generator().manual_seed(seed)
+    out = []
+    for _ in range(count):
+        ids = torch.randint(0, vocab, (cfg.batch_size, cfg.max_length), generator=gen)
+        batch = {"input_ids": ids, "attention_mask": torch.ones_like(ids)}
+        if cfg.task == "sst2":
+            batch["labels"] = torch.bernoulli(torch.full((cfg.batch_size,), 0.5), generator=gen).long()
+        else:
+            batch["labels"] = ids.clone()
+        out.append({k: v.to(device) for k, v in batch.items()})
+    return out
+
+
+# ------------------------------------------------------------------------------ targets and replacement
+def select_targets(model: nn.Module, cfg: ConvergenceConfig) -> List[str]:
+    if cfg.use_tensor_parallel:
+        return get_tp_stacr_targets(model, cfg.tp_stacr_scope)
+    return S.select_target_names(model, surface=cfg.stacr_surface, min_features=cfg.stacr_min_features)
+
+
+def _adaptive_config(cfg: ConvergenceConfig) -> AdaptiveConfig:
+    return AdaptiveConfig(
+        rank=cfg.rank, residual_mode="none" if cfg.method == "stac" else cfg.stacr_residual_mode, residual_budget=cfg.stacr_residual_budget,
+        update_trigger=cfg.stacr_update_trigger, update_interval=cfg.stacr_update_interval, energy_threshold=cfg.stacr_energy_threshold,
+        oja_learning_rate=cfg.stacr_oja_learning_rate, warmup_steps=cfg.stacr_warmup_steps, freeze_basis_after_warmup=cfg.stacr_freeze_basis_after_warmup,
+        quantize_coefficients=cfg.stacr_quantize_coefficients, quantize_residuals=cfg.stacr_quantize_residuals,
+        residual_quantize_bits=cfg.stacr_residual_quantize_bits, basis_dtype=cfg.stacr_basis_dtype, use_fused_kernel=cfg.stacr_use_fused_kernel,
+        rank_mode=cfg.stacr_rank_mode, rank_min=cfg.stacr_rank_min, rank_max=max(cfg.stacr_rank_max, cfg.stacr_rank_min),
+        refresh_trigger=cfg.stacr_refresh_trigger, post_warmup_residual_mode=cfg.stacr_post_warmup_residual_mode,
+        residual_warmup_steps=cfg.stacr_residual_warmup_steps, index_compression=cfg.stacr_index_compression, cpu_offload=cfg.stacr_cpu_offload,
+    )
+
+
+def replace_linear_with_stacr(model: nn.Module, names: List[str], cfg: ConvergenceConfig) -> List[nn.Module]:
+    """Wrap the named projections with the configured engine (adaptive by default, as the protocols do)."""
+    if cfg.stacr_engine == "projection":
+        return S.apply_stacr(model, surface="none", target_names=names, rank=cfg.rank, residual_budget=cfg.stacr_residual_budget,
+                             turbo_after_step=None, allow_empty=True)
+    base = _adaptive_config(cfg)
+    layers = []
+    for i, name in enumerate(names):
+        parent_name, _, leaf = name.rpartition(".")
+        parent = model.get_submodule(parent_name) if parent_name else model
+        layer = AdaptiveLinear.from_linear(getattr(parent, leaf), copy.deepcopy(base), layer_index=i, num_layers=len(names))
+        layer.source_name = name
+        setattr(parent, leaf, layer)
+        layers.append(layer)
+    return layers
+
+
+def replace_linear_with_compressed(model: nn.Module, names: List[str], cfg: ConvergenceConfig) -> List[nn.Module]:
+    """SVD / TT / Tucker comparators on the same targets."""
+    out = []
+    for name in names:
+        parent_name, _, leaf = name.rpartition(".")
+        parent = model.get_submodule(parent_name) if parent_name else model
+        lin = getattr(parent, leaf)
+        if not isinstance(lin, nn.Linear):
+            continue
+        rows = cfg.batch_size * cfg.max_length
+        conf: Dict[str, Any] = {"method": cfg.method, "rank": cfg.rank, "quantize_bits": cfg.factor_quantization_bits, "use_lowrank": cfg.use_lowrank_svd}
+        if cfg.method in ("tt", "tucker"):
+            shape = cfg.reshape_shape or _default_tensor_shape(rows, lin.in_features)
+            conf["reshape_shape"] = tuple(shape)
+            conf["ranks"] = [min(cfg.rank, d) for d in shape]
+        wrapped = CompressedLinear.from_linear(lin, conf)
+        setattr(parent, leaf, wrapped)
+        out.append(wrapped)
+    return out
+
+
+def _default_tensor_shape(rows: int, feats: int):
+    def two(n):
+        a = int(math.isqrt(n))
+        while a > 1 and n % a:
+            a -= 1
+        return [a, n // a]
+    return two(rows) + two(feats)
+
+
+# ------------------------------------------------------------------------------ baselines
+def apply_baseline(model: nn.Module, cfg: ConvergenceConfig, device) -> Dict[str, Any]:
+    b = cfg.baseline_cfg
+    state: Dict[str, Any] = {"amp": AMPManager(b.amp, str(device)), "offload": None, "checkpointed": 0}
+    if b.checkpointing != "none":
+        state["checkpointed"] = apply_checkpointing(model, b.checkpointing)
+    if b.offload != "none":
+        state["offload"] = OffloadManager(b.offload, b.offload_min_bytes)
+    if b.c1_checkpoint_compression:
+        from stacr_b200.protocols.checkpointing import STACRCheckpointConfig, enable_c1_checkpointing_for_model
+
+        state["c1"] = enable_c1_checkpointing_for_model(model, STACRCheckpointConfig(enabled=True, warmup_steps=0, min_numel=0), amp_mode=b.amp)
+    return state
+
+
+def build_optimizer(model: nn.Module, cfg: ConvergenceConfig):
+    params = [p for p in model.parameters() if p.requires_grad]
+    if cfg.baseline_cfg.optimizer_8bit:
+        from stacr_b200.optim import AdamW8bit
+
+        return AdamW8bit(params, lr=cfg.lr, weight_decay=cfg.weight_decay), "AdamW8bit(in-tree)"
+    if params[0].is_cuda:
+        from stacr_b200.optim import AdamW
+
+        return AdamW(params, lr=cfg.lr, weight_decay=cfg.weight_decay), "AdamW(in-tree)"
+    return torch.optim.AdamW(params, lr=cfg.lr, weight_decay=cfg.weight_decay), "AdamW"
+
+
+# ------------------------------------------------------------------------------ telemetry
+@torch.no_grad()
+def validate(model, batches, amp: AMPManager, task: str) -> Dict[str, float]:
+    was = model.training
+    model.eval()
+    nll = n = correct = seen = 0
+    for batch in batches:
+        with amp.autocast():
+            out = model(**batch)
+        if task == "sst2":
+            correct += int((out.logits.argmax(-1) == batch["labels"]).sum())
+            seen += batch["labels"].numel()
+        else:
+            nll += float(out.loss)
+            n += 1
+    model.train(was)
+    if task == "sst2":
+        return {"val_accuracy": 100.0 * correct / max(1, seen)}
+    mean = nll / max(1, n)
+    return {"val_loss": mean, "val_ppl": math.exp(min(700.0, mean))}
+
+
+def compute_grad_cosine(model, batch, amp: AMPManager) -> Optional[float]:
+    """Cosine between the gradient through the actual (compressed) backward and the exact gradient on one batch."""
+    from stacr_b200.diagnostics import compression_diagnostics
+
+    params = [p for p in model.parameters() if p.requires_grad]
+    stash = [None if p.grad is None else p.grad.clone() for p in params]
+
+    def grads(compress: bool):
+        model.zero_grad(set_to_none=True)
+        flags = {m: m.training for m in model.modules()}
+        try:
+            if compress:
+                with compression_diagnostics(model), amp.autocast():
+                    model(**batch).loss.backward()
+            else:
+                model.eval()  # compressed layers take their exact path in eval mode
+                with amp.autocast():
+                    model(**batch).loss.backward()
+        finally:
+            for m, f in flags.items():
+                m.training = f
+        return torch.cat([(p.grad if p.grad is not None else torch.zeros_like(p)).reshape(-1).double() for p in params])
+
+    try:
+        exact, approx = grads(False), grads(True)
+        value = float(S.cosine_similarity(exact, approx))
+    except ValueError:
+        value = None
+    for p, g in zip(params, stash):
+        p.grad = g
+    return value
+
+
+def compute_per_layer_grad_fidelity(model, batch, amp: AMPManager, layers) -> Dict[str, float]:
+    """Per wrapped layer: cosine between exact and compressed weight gradients on one batch."""
+    from stacr_b200.diagnostics import compression_diagnostics
+
+    def weight_of(layer):
+        if isinstance(layer, AdaptiveLinear):
+            lin = layer.linear
+            return getattr(lin, "source_weight", None) if hasattr(lin, "source_weight") else lin.weight
+        return layer.weight
+
+    weights = {getattr(l, "source_name", str(i)): weight_of(l) for i, l in enumerate(layers)}
+    stash = {k: (None if w.grad is None else w.grad.clone()) for k, w in weights.items()}
+    out: Dict[str, float] = {}
+    flags = {m: m.training for m in model.modules()}
+    try:
+        model.zero_grad(set_to_none=True)
+        model.eval()
+        with amp.autocast():
+            model(**batch).loss.backward()
+        exact = {k: w.grad.detach().clone() for k, w in weights.items() if w.grad is not None}
+        for m, f in flags.items():
+            m.training = f
+        model.zero_grad(set_to_none=True)
+        with compression_diagnostics(model), amp.autocast():
+            model(**batch).loss.backward()
+        for k, w in weights.items():
+            if k in exact and w.grad is not None:
+                out[k] = float(S.cosine_similarity(exact[k], w.grad))
+    finally:
+        for m, f in flags.items():
+            m.training = f
+        for k, w in weights.items():
+            w.grad = stash[k]
+    return out
+
+
+def compute_activation_spectrum_telemetry(model, batch, amp: AMPManager, layers, rank: int = 8) -> Dict[str, dict]:
+    """Energy captured by the top-``rank`` singular directions of each wrapped layer's input on one batch."""
+    captured: Dict[str, torch.Tensor] = {}
+    hooks = []
+    for i, layer in enumerate(layers):
+        name = getattr(layer, "source_name", str(i))
+        hooks.append(layer.register_forward_pre_hook(lambda m, inp, _n=name: captured.__setitem__(_n, inp[0].detach())))
+    was = model.training
+    model.eval()
+    with torch.no_grad(), amp.autocast():
+        model(**batch)
+    model.train(was)
+    for h in hooks:
+        h.remove()
+    out = {}
+    for name, x in captured.items():
+        s = torch.linalg.svdvals(x.reshape(-1, x.shape[-1]).float()[:4096])
+        e = s.square()
+        out[name] = {"top_rank_energy": float(e[:rank].sum() / e.sum().clamp_min(1e-30)), "stable_rank": float(e.sum() / e[0].clamp_min(1e-30))}
+    return out
+
+
+# ------------------------------------------------------------------------------ the run
+def run_convergence_experiment(cfg: ConvergenceConfig, logger) -> Dict[str, Any]:
+    get_basis_pool().clear()
+    set_all_seeds(cfg.seed, strict=False)
+    rank = dist.get_rank() if dist.is_initialized() else 0
+    world = dist.get_world_size() if dist.is_initialized() else 1
+    cuda = torch.cuda.is_available() and cfg.device in ("auto", "cuda")
+    device = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0"))) if cuda else torch.device("cpu")
+    logger.write_config(cfg.to_dict())
+    model = build_model(cfg.model, **cfg.model_overrides).to(device).train()
+    vocab = model.config.vocab_size
+    tp_profiler = None
+    if cfg.use_tensor_parallel:
+        if world < 2 and not cfg.quiet:
+            print("[TP] single rank: sharding degenerates to the unsharded model")
+        apply_tensor_parallel_gpt2(model, rank, world, None, scope=cfg.tp_scope)
+        disable_tp_dropout(model)
+        if cfg.tp_profile_activations:
+            tp_profiler = TPActivationProfiler(model)
+    elif cfg.use_ddp:
+        broadcast_parameters(model)
+    layers: List[nn.Module] = []
+    plan_summary = None
+    if cfg.method in ("stacr", "stac"):
+        names = select_targets(model, cfg)
+        if cfg.stacr_planner == "bytes":
+            decisions = plan_stacr_layers(model, cfg, names)
+            plan_summary = summarize_layer_decisions(decisions)
+            names = [d.name for d in decisions if d.keep]
+        layers = replace_linear_with_stacr(model, names, cfg)
+    elif cfg.method in ("svd", "tt", "tucker"):
+        layers = replace_linear_with_compressed(model, select_targets(model, cfg), cfg)
+    elif cfg.method == "prac":
+        layers = replace_linear_with_prac(model, select_targets(model, cfg), PRACConfig(rank=cfg.rank, update_proj_gap=cfg.prac_update_proj_gap, quiet=True))
+    state = apply_baseline(model, cfg, device)
+    amp: AMPManager = state["amp"]
+    optimizer, optimizer_name = build_optimizer(model, cfg)
+    sync = GradSync(model.parameters()) if (cfg.use_ddp and world > 1) else None
+    profiler = PhaseProfiler(out_path=logger.profile_path, enabled=cfg.phase_profile_full_run and logger.profile_path is not None)
+    for layer in layers:
+        if isinstance(layer, AdaptiveLinear):
+            layer.phase_profiler = profiler
+    data_world = world if cfg.use_ddp else 1
+    train = make_distributed_loader(build_batches(cfg, vocab, max(1, cfg.train_examples // cfg.batch_size), cfg.seed, device), rank if cfg.use_ddp else 0, data_world)
+    val = build_batches(cfg, vocab, max(1, cfg.eval_examples // cfg.batch_size), cfg.seed + 1, device)
+    total_steps = min(cfg.max_steps, cfg.epochs * len(train))
+    warm = int(cfg.warmup_ratio * total_steps)
+    if cuda:
+        torch.cuda.reset_peak_memory_stats(device)
+    step = 0
+    loss_sum, tokens = 0.0, 0
+    history: List[float] = []
+    t0 = time.perf_counter()
+    ev = (torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) if cuda else None
+    if ev:
+        ev[0].record()
+    status = "ok"
+    try:
+        while step < total_steps:
+            batch = train[step % len(train)]
+            lr_scale = min(1.0, (step + 1) / max(1, warm)) if step < warm else max(0.0, (total_steps - step) / max(1, total_steps - warm))
+            for g in optimizer.param_groups:
+                g["lr"] = cfg.lr * lr_scale
+            set_stacr_runtime_state(model, step, 0, 1, total_steps)
+            S.set_step([l for l in layers if isinstance(l, S.STACRLinear)], step)
+            if cfg.method == "prac":
+                set_prac_global_step(model, step)
+            with profiler.step(step):
+                sync.zero_grad() if sync else optimizer.zero_grad(set_to_none=True)
+                ctx = state["offload"].training_step() if state["offload"] else _null()
+                with ctx:
+                    with profiler.phase("forward"), amp.autocast():
+                        loss = model(**batch).loss
+                    value = float(loss.detach())
+                    if not math.isfinite(value):
+                        raise FloatingPointError(f"Nonfinite loss at step {step}")
+                    with profiler.phase("backward"):
+                        amp.backward(loss)
+                with profiler.phase("optimizer"):
+                    if sync:
+                        sync.finish()
+                    if cfg.use_tensor_parallel and world > 1:
+                        sync_replicated_grads(model, None)
+                    if cfg.grad_clip > 0:
+                        amp.unscale_(optimizer)
+                        torch.nn.utils.clip_grad_norm_(model.parameters(), cfg.grad_clip)
+                    amp.step(optimizer)
+            loss_sum += value
+            tokens += int(batch["attention_mask"].sum())
+            history.append(value)
+            record = {"step": step, "train_loss": value, "lr": cfg.lr * lr_scale}
+            if cfg.monitor_grad_fidelity and layers and step % cfg.grad_fidelity_interval == 0:
+                record["grad_cosine"] = compute_grad_cosine(model, batch, amp)
+            if cfg.monitor_per_layer_grad_fidelity and layers and step % cfg.per_layer_grad_fidelity_interval == 0:
+                record["per_layer_grad_cosine"] = compute_per_layer_grad_fidelity(model, batch, amp, layers)
+            if cfg.monitor_activation_spectrum and layers and step % cfg.activation_spectrum_interval == 0:
+                record["activation_spectrum"] = compute_activation_spectrum_telemetry(model, batch, amp, layers, cfg.activation_spectrum_rank)
+            logger.log(record)
+            step += 1
+            if cfg.save_every_n_steps and step % cfg.save_every_n_steps == 0 and int(os.environ.get("LOCAL_RANK", "0")) == 0 and getattr(logger, "dir", None):
+                target = logger.dir / f"checkpoint_step_{step}"
+                target.mkdir(parents=True, exist_ok=True)
+                torch.save(model.state_dict(), target / "model.pt")
+    except FloatingPointError as exc:
+        status = f"error: {exc}"
+    if ev:
+        ev[1].record()
+        torch.cuda.synchronize(device)
+        elapsed = ev[0].elapsed_time(ev[1]) / 1e3
+    else:
+        elapsed = time.perf_counter() - t0
+    peak = float(torch.cuda.max_memory_allocated(device)) if cuda else 0.0
+    reduced = _ddp_reduce_train_metrics(loss_sum, tokens, step, peak, device)
+    quality = validate(model, val, amp, cfg.task) if (rank == 0 or cfg.use_tensor_parallel) else {}
+    flags: Dict[str, Any] = {}
+    adaptive = [l for l in layers if isinstance(l, AdaptiveLinear)]
+    if adaptive:
+        flags = {
+            "basis_updates": sum(l.layer_state["basis_updates"] for l in adaptive),
+            "refresh_count_total": sum(l.layer_state["refresh_count_total"] for l in adaptive),
+            "mean_residual_energy": sum(float(l.layer_state["last_residual_energy"]) for l in adaptive) / len(adaptive),
+            "active_ranks": [int(l.layer_state["active_rank"]) for l in adaptive],
+            "low_rank_only_steps": sum(l.layer_state["b1_route_step_count"] for l in adaptive),
+        }
+    final = {
+        "status": status, "run_tag": cfg.run_tag, "method": cfg.method, "model": cfg.model, "world_size": world, "steps": step,
+        "optimizer": optimizer_name, "train_loss_mean": reduced["loss_sum"] / max(1, reduced["steps"]), "train_loss_last": history[-1] if history else None,
+        "train_loss_first": history[0] if history else None, "seconds": elapsed, "tokens_per_second": reduced["tokens"] / elapsed if elapsed > 0 else None,
+        "peak_allocated_bytes": reduced["peak_bytes"], "n_wrapped_layers": len(layers), "baseline": cfg.baseline_cfg.get_description(),
+        "stacr_flags": flags, "planner": plan_summary, "tp_activation_profile": tp_profiler.summary() if tp_profiler else None,
+        "offload": state["offload"].get_stats() if state["offload"] else None, **quality,
+    }
+    if cfg.save_final_model and int(os.environ.get("LOCAL_RANK", "0")) == 0 and getattr(logger, "dir", None):
+        (logger.dir / "checkpoint").mkdir(parents=True, exist_ok=True)
+        torch.save(model.state_dict(), logger.dir / "checkpoint" / "model.pt")
+    logger.write_final(final)
+    if sync:
+        sync.close()
+    return final
+
+
+class _null:
+    def __enter__(self):
+        return None
+
+    def __exit__(self, *exc):
+        return False

@@ -9,15 +9,16 @@ from __future__ import annotations
 
 import torch
 
-from . import bert, gpt2, neox
+from . import bert, gpt2, llama, neox
 from .bert import BertConfig, BertForSequenceClassification
 from .common import ModelOutput
 from .gpt2 import GPT2Config, GPT2LMHeadModel
+from .llama import LlamaConfig, LlamaForCausalLM
 from .neox import GPTNeoXForCausalLM, NeoXConfig
 
 __all__ = [
     "BertConfig", "BertForSequenceClassification", "GPT2Config", "GPT2LMHeadModel", "GPTNeoXForCausalLM", "NeoXConfig",
-    "ModelOutput", "build_model", "load_model_and_tokenizer",
+    "LlamaConfig", "LlamaForCausalLM", "ModelOutput", "build_model", "load_model_and_tokenizer",
 ]
 
 
@@ -32,6 +33,8 @@ def build_model(name: str, task: str = "language_modeling", **overrides):
         return GPT2LMHeadModel(GPT2Config(**{**gpt2.PRESETS[key], **overrides}))
     if key in neox.PRESETS:
         return GPTNeoXForCausalLM(NeoXConfig(**{**neox.PRESETS[key], **overrides}))
+    if key in llama.PRESETS:
+        return LlamaForCausalLM(LlamaConfig(**{**llama.PRESETS[key], **overrides}))
     if key in bert.PRESETS:
         return BertForSequenceClassification(BertConfig(**{**bert.PRESETS[key], **overrides}))
     raise KeyError(f"No in-tree architecture for {name!r}")

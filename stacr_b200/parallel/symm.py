@@ -30,7 +30,9 @@ def available() -> bool:
     if not (torch.cuda.is_available() and dist.is_initialized() and dist.get_backend() == "nccl"):
         return False
     try:
-        import torch.distributed._symmetric_memory  # noqa: F401
+        import importlib
+
+        importlib.import_module("torch.distributed._symmetric_memory")
     except Exception:
         return False
     return hasattr(_lib.load(), "sb_allreduce_two_shot")
