@@ -106,6 +106,16 @@ def main(argv=None) -> int:
     code = 0
     for seed in seeds:
         cfg = make_config(prof, seed, overrides)
+        if cfg.task == "ogbn-arxiv":
+            # node classification runs in the graph protocol (full-batch GCN; synthetic graph when the dataset is absent)
+            from .graph import run as run_graph
+
+            epochs = cfg.epochs if cfg.max_steps >= (1 << 62) else min(cfg.epochs, cfg.max_steps)
+            final = run_graph(method="stacr" if cfg.method == "stacr" else "baseline", epochs=epochs, seed=seed, rank=cfg.rank, budget=cfg.stacr_residual_budget)
+            if rank == 0:
+                RunLogger(args.output / args.profile / f"seed{seed}").write_final(final)
+                print(json.dumps({"run_tag": cfg.run_tag, **{k: final[k] for k in list(final)[:6]}}, default=str))
+            continue
         logger = RunLogger(args.output / args.profile / f"seed{seed}") if rank == 0 else NullLogger()
         try:
             final = run_convergence_experiment(cfg, logger)

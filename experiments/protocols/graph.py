@@ -65,7 +65,7 @@ def run(method="stacr", epochs=30, hidden=256, seed=42, rank=8, budget=0.005) ->
     model.eval()
     with torch.no_grad():
         acc = float((model(x, adj)[~train].argmax(-1) == y[~train]).float().mean())
-    return {"method": method, "test_accuracy": acc, "final_loss": float(loss), "wrapped": len(layers)}
+    return {"method": method, "test_accuracy": acc, "final_loss": float(loss.detach()), "wrapped": len(layers)}
 
 
 def main(argv=None) -> int:

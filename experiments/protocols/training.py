@@ -42,95 +42,241 @@ METHODS = ("baseline", "stacr", "stac", "svd", "tt", "tucker", "prac")
 
 @dataclass
 class ConvergenceConfig:
+    """Every switch of a protocol run.  Field names follow the reference runner one for one so that published
+    profile files load unchanged; ``train_examples``, ``eval_examples``, ``warmup_ratio``, ``model_overrides``,
+    ``stacr_engine`` and ``stacr_surface`` exist only here."""
+
     experiment: str = "convergence_training"
-    task: str = "synthetic_lm"           # synthetic_lm | wikitext103 | openwebtext | sst2
-    model: str = "gpt2-medium"
+    task: str = "synthetic_lm"           # synthetic_lm | wikitext103 | openwebtext | sst2 | ogbn-arxiv
+    model: Optional[str] = "gpt2-medium"
     method: str = "baseline"
     method_label: Optional[str] = None
-    run_tag: str = "run"
+    run_tag: Optional[str] = "run"
     rank: int = 8
     reshape_shape: Optional[List[int]] = None
     factor_quantization_bits: Optional[int] = None
     factor_native_backward: bool = True
     use_lowrank_svd: bool = False
+    tact_v3_config_path: Optional[str] = None
+    tact_v3_target_ratio: int = 30
     baseline: Optional[str] = None
     baseline_cfg: Any = None
     epochs: int = 1
     batch_size: int = 8
     lr: float = 5e-5
     weight_decay: float = 0.0005
+    momentum: float = 0.9
     max_length: int = 1024
+    padding_mode: str = "dynamic"
     seed: int = 42
     deterministic: bool = True
     measure_memory: bool = True
+    log_memory_both: bool = True
     monitor_grad_fidelity: bool = False
     grad_fidelity_interval: int = 100
     monitor_per_layer_grad_fidelity: bool = False
     per_layer_grad_fidelity_interval: int = 120
+    monitor_svd_per_layer_grad_fidelity: bool = False
+    svd_per_layer_grad_fidelity_interval: int = 240
+    svd_per_layer_rank: Optional[int] = None
+    svd_per_layer_oversampling: int = 16
+    svd_per_layer_niter: int = 2
     monitor_activation_spectrum: bool = False
     activation_spectrum_interval: int = 120
     activation_spectrum_rank: int = 8
+    activation_spectrum_oversampling: int = 16
+    activation_spectrum_niter: int = 2
     device: str = "auto"
+    num_workers: int = 4
     use_data_parallel: bool = False
     use_ddp: bool = False
     use_tensor_parallel: bool = False
     use_8bit_optimizer: bool = False
-    tp_scope: str = "mlp_only"
+    tp_scope: str = "full"
     tp_stacr_scope: str = "row_only"
     tp_profile_activations: bool = False
-    max_steps: int = 100
+    max_steps: Optional[int] = 100
     train_examples: int = 512
     eval_examples: int = 32
     grad_clip: float = 0.0
     warmup_ratio: float = 0.1
     save_final_model: bool = False
     save_every_n_steps: Optional[int] = None
+    debug_step_metrics_every: int = 0
     phase_profile_full_run: bool = False
+    saved_tensors_compress_min_bytes: int = 100000
+    saved_tensors_compress_dims: int = 4
     quiet: bool = True
+    is_canonical_run: bool = False
     model_overrides: Dict[str, Any] = field(default_factory=dict)
-    # compression (adaptive engine) options, prefixed as in the reference runner
+    # ---- compression (adaptive engine); ``stacr_<x>`` feeds the engine option ``<x>`` unless _ENGINE_ALIASES renames it
     stacr_engine: str = "adaptive"
     stacr_surface: str = "mlp"
-    stacr_min_features: int = 256
     stacr_residual_mode: str = "block_sparse"
     stacr_residual_budget: float = 0.005
+    stacr_residual_threshold: float = 0.1
     stacr_update_trigger: str = "hybrid"
     stacr_update_interval: int = 100
     stacr_energy_threshold: float = 0.05
+    stacr_streaming_algorithm: str = "oja"
     stacr_oja_learning_rate: float = 0.01
     stacr_warmup_steps: int = 0
     stacr_freeze_basis_after_warmup: bool = True
     stacr_quantize_coefficients: bool = True
+    stacr_quantize_bits: int = 8
     stacr_quantize_residuals: bool = True
     stacr_residual_quantize_bits: int = 4
+    stacr_randomized_svd_threshold: int = 1024
+    stacr_randomized_svd_oversampling: int = 4
+    stacr_randomized_svd_niter: int = 2
+    stacr_adaptive_oja_lr: bool = False
+    stacr_adaptive_oja_scale: float = 5.0
+    stacr_adaptive_oja_max_lr: float = 0.1
     stacr_basis_dtype: str = "auto"
+    stacr_backward_mode: str = "sparse"
+    stacr_residual_block_size: int = 16
+    stacr_cpu_offload: bool = False
+    stacr_use_mgs: bool = False
+    stacr_lazy_update: bool = True
+    stacr_lazy_update_threshold: float = 0.01
     stacr_use_fused_kernel: bool = False
     stacr_rank_mode: str = "fixed"
+    stacr_rank_variance_threshold: float = 0.95
     stacr_rank_min: int = 4
     stacr_rank_max: int = 64
-    stacr_refresh_trigger: str = "off"
-    stacr_post_warmup_residual_mode: str = "full"
-    stacr_residual_warmup_steps: int = 0
+    stacr_rank_adjust_interval: int = 100
+    stacr_rank_sensitivity_low: float = 0.03
+    stacr_rank_sensitivity_high: float = 0.1
+    stacr_rank_step_fraction: float = 0.125
+    stacr_streaming_topk: bool = False
+    stacr_streaming_topk_sample_ratio: float = 0.1
+    stacr_chunk_size: int = 512
     stacr_index_compression: str = "none"
-    stacr_cpu_offload: bool = False
-    stacr_planner: str = "none"          # none | bytes: keep a layer only when saved - stored > 0
+    stacr_skip_residual: bool = False
+    stacr_skip_residual_threshold: float = 0.05
+    stacr_buffer_reuse: bool = False
+    stacr_min_features: int = 256
+    stacr_small_layer_rank_scale: float = 1.0
+    stacr_small_layer_residual_scale: float = 1.0
+    stacr_decoder_target_mode: str = "all"     # all | mlp_only | attention_only
+    stacr_use_planner: bool = False
+    stacr_planner_enforce: bool = False
+    stacr_planner: str = "none"                # none | bytes (same as stacr_use_planner + stacr_planner_enforce)
     stacr_force_compress_layers: Optional[str] = None
+    stacr_adaptive_layer_rank: str = "none"
+    stacr_per_layer_rank_schedule: Optional[str] = None   # "c_fc=4,c_proj=12": rank by leaf-name substring
+    stacr_residual_schedule: str = "none"
+    stacr_residual_start: float = 0.05
+    stacr_residual_end: float = 0.001
+    stacr_post_warmup_mode: str = "full"
+    stacr_post_warmup_residual_mode: Optional[str] = None  # alias of stacr_post_warmup_mode; wins when set
+    stacr_residual_warmup_steps: int = 0
+    stacr_post_warmup_threshold: float = 0.1
+    stacr_refresh_trigger: str = "off"
+    stacr_refresh_period: int = 1000
+    stacr_refresh_energy_threshold: float = 0.1
+    stacr_cache_basis_per_optimizer_step: bool = False
+    stacr_oja_update_per_optimizer_step: bool = False
+    stacr_enable_low_rank_only_fast_path: bool = True
+    stacr_use_random_qr_init: bool = False
+    stacr_min_adaptation_steps: int = 50
+    stacr_allow_unadapted_random_qr: bool = False
+    # ---- attention surface
+    stacr_attention: bool = False
+    stacr_attention_rank: Optional[int] = None
+    stacr_attention_residual_mode: Optional[str] = None
+    stacr_basis_sharing: str = "none"
+    stacr_joint_qk: bool = False
+    stacr_gpt2_split_c_attn: bool = False
+    # ---- checkpoint-boundary compression
+    stacr_compress_checkpoint: bool = False
+    stacr_ckpt_target: str = "decoder_block_input"
+    stacr_ckpt_rank: Optional[int] = None
+    stacr_ckpt_warmup_steps: int = 500
+    stacr_ckpt_residual_mode: str = "none"
+    stacr_ckpt_residual_budget: float = 0.005
+    stacr_ckpt_refresh_trigger: str = "residual_energy"
+    stacr_ckpt_refresh_period: int = 200
+    stacr_ckpt_refresh_energy_threshold_mode: str = "auto"
+    stacr_ckpt_refresh_energy_threshold: float = 0.15
+    stacr_ckpt_min_numel: int = 1 << 20
+    stacr_ckpt_basis_dtype: str = "auto"
+    stacr_ckpt_quantize_coefficients: bool = False
+    stacr_ckpt_quantize_bits: int = 8
+    stacr_ckpt_quantize_residuals: bool = True
+    stacr_ckpt_residual_quantize_bits: int = 4
+    stacr_ckpt_allow_inner_stacr: bool = False
+    stacr_ckpt_planner: str = "heuristic"
+    # ---- PRAC comparator
     prac_update_proj_gap: int = 50
+    prac_seed_base: int = 42
+    prac_proj_dtype: str = "auto"
+    # ---- graph protocol (task ogbn-arxiv; read by experiments.protocols.graph)
+    use_neighbor_sampling: bool = False
+    num_neighbors: str = "30,30"
+    use_random_node_loader: bool = False
+    num_parts: int = 40
+    use_stacr_graph: bool = False
+    stacr_graph_tt_rank: int = 8
+    stacr_graph_max_rank: int = 16
+    stacr_graph_sparse_residual: bool = False
+    stacr_graph_residual_budget: float = 0.1
+    stacr_graph_residual_per_node: bool = False
+    stacr_graph_chunk_size: int = 64
+    stacr_graph_edge_eval_chunk_size: int = 100000
+    stacr_graph_use_phantom: bool = False
+    stacr_graph_phantom_samples: int = 5000
+    stacr_graph_phantom_budget_frac: float = 0.2
+    stacr_graph_phantom_seed: Optional[int] = None
+    stacr_graph_use_hybrid: bool = False
+    stacr_graph_hybrid_global_frac: float = 0.8
+    stacr_graph_share_tt: bool = True
+    stacr_graph_random_residual: bool = False
+    stacr_graph_random_seed: int = 42
+    stacr_graph_node_reorder: str = "none"
+    # ---- convolutional comparators: accepted so that old profile files load; no convolutional model ships, so any
+    # value other than the default is refused in __post_init__
+    conv_compression_mode: str = "none"
+    conv_compression_layers: str = "all"
+    conv_skip_3x3: bool = True
+    conv_min_channels: int = 64
+    tucker_ranks: Optional[List[int]] = None
+    conv_v2: bool = False
+    conv_checkpoint: bool = False
+    conv_block_checkpoint: bool = False
+    conv_stage_checkpoint: bool = False
+    conv_saved_hooks: bool = False
+    conv_hooks_mode: str = "channel"
 
     def __post_init__(self):
+        if os.environ.get("STACR_QUIET") == "1":
+            self.quiet = True
+        if self.method_label is None:
+            self.method_label = self.method
         if self.method not in METHODS:
             raise ValueError(f"Unknown method {self.method!r}; choose from {METHODS}")
         if self.use_ddp and self.use_tensor_parallel:
             raise ValueError("Select DDP or tensor parallelism")
+        if self.padding_mode not in ("dynamic", "max_length"):
+            raise ValueError(f"padding_mode must be 'dynamic' or 'max_length', got {self.padding_mode}")
+        if self.stacr_decoder_target_mode not in ("all", "mlp_only", "attention_only"):
+            raise ValueError(f"Unknown stacr_decoder_target_mode {self.stacr_decoder_target_mode!r}")
+        if self.conv_compression_mode != "none" or any((self.conv_v2, self.conv_checkpoint, self.conv_block_checkpoint, self.conv_stage_checkpoint, self.conv_saved_hooks)):
+            raise ValueError("convolutional compression options need a convolutional model; none is available here")
         if isinstance(self.baseline_cfg, dict):
-            known = {f.name for f in fields(BaselineConfig)}
-            legacy = {"saved_tensors_offload": "offload", "saved_tensors_offload_min_bytes": "offload_min_bytes"}
-            mapped = {legacy.get(k, k): v for k, v in self.baseline_cfg.items()}
-            self.baseline_cfg = BaselineConfig(**{k: v for k, v in mapped.items() if k in known})
+            self.baseline_cfg = BaselineConfig.from_mapping(self.baseline_cfg)
         elif self.baseline_cfg is None:
-            self.baseline_cfg = BaselineConfig.from_legacy(self.baseline) if self.baseline else BaselineConfig()
+            self.baseline_cfg = BaselineConfig.from_legacy(self.baseline) if self.baseline not in (None, "none", "baseline") else BaselineConfig()
         if self.use_8bit_optimizer:
             self.baseline_cfg.optimizer_8bit = True
+        if self.stacr_post_warmup_residual_mode is None:
+            self.stacr_post_warmup_residual_mode = self.stacr_post_warmup_mode
+        else:
+            self.stacr_post_warmup_mode = self.stacr_post_warmup_residual_mode
+        if self.stacr_use_planner and self.stacr_planner_enforce:
+            self.stacr_planner = "bytes"
+        if self.max_steps is None:
+            self.max_steps = 1 << 62  # bounded by epochs * batches
 
     @classmethod
     def from_raw(cls, raw: Dict[str, Any]) -> "ConvergenceConfig":
@@ -142,6 +288,31 @@ class ConvergenceConfig:
 
     def to_dict(self) -> Dict[str, Any]:
         return asdict(self)
+
+
+# protocol field (without the ``stacr_`` prefix) -> engine option, where the names differ
+_ENGINE_ALIASES = {
+    "lazy_update": "lazy_update_enabled", "skip_residual": "skip_residual_enabled", "skip_residual_threshold": "skip_residual_energy_threshold",
+    "post_warmup_mode": "post_warmup_residual_mode", "post_warmup_threshold": "post_warmup_residual_threshold",
+}
+# ``stacr_*`` fields that steer the runner, not the engine
+_RUNNER_ONLY = {"engine", "surface", "min_features", "small_layer_rank_scale", "small_layer_residual_scale", "decoder_target_mode", "use_planner",
+                "planner_enforce", "planner", "force_compress_layers", "per_layer_rank_schedule", "attention", "attention_rank",
+                "attention_residual_mode", "gpt2_split_c_attn", "compress_checkpoint", "post_warmup_residual_mode"}
+
+
+def parse_rank_schedule(text: Optional[str]) -> Dict[str, int]:
+    """``"c_fc=4,c_proj=12"`` -> ``{"c_fc": 4, "c_proj": 12}``; a layer takes the rank of the first key its name contains."""
+    out: Dict[str, int] = {}
+    for item in (text or "").split(","):
+        item = item.strip()
+        if not item:
+            continue
+        key, sep, value = item.partition("=")
+        if not sep or not key.strip() or int(value) < 1:
+            raise ValueError(f"Bad rank schedule entry {item!r}; expected name=rank")
+        out[key.strip()] = int(value)
+    return out
 
 
 # ------------------------------------------------------------------------------ distributed helpers
@@ -185,20 +356,37 @@ def build_batches(cfg: ConvergenceConfig, vocab: int, count: int, seed: int, dev
 def select_targets(model: nn.Module, cfg: ConvergenceConfig) -> List[str]:
     if cfg.use_tensor_parallel:
         return get_tp_stacr_targets(model, cfg.tp_stacr_scope)
-    return S.select_target_names(model, surface=cfg.stacr_surface, min_features=cfg.stacr_min_features)
+    surface = {"all": cfg.stacr_surface, "mlp_only": "mlp", "attention_only": "attention"}[cfg.stacr_decoder_target_mode]
+    forced = [n.strip() for n in (cfg.stacr_force_compress_layers or "").split(",") if n.strip()]
+    return S.select_target_names(model, surface=surface, min_features=cfg.stacr_min_features, extra_names=forced)
 
 
-def _adaptive_config(cfg: ConvergenceConfig) -> AdaptiveConfig:
-    return AdaptiveConfig(
-        rank=cfg.rank, residual_mode="none" if cfg.method == "stac" else cfg.stacr_residual_mode, residual_budget=cfg.stacr_residual_budget,
-        update_trigger=cfg.stacr_update_trigger, update_interval=cfg.stacr_update_interval, energy_threshold=cfg.stacr_energy_threshold,
-        oja_learning_rate=cfg.stacr_oja_learning_rate, warmup_steps=cfg.stacr_warmup_steps, freeze_basis_after_warmup=cfg.stacr_freeze_basis_after_warmup,
-        quantize_coefficients=cfg.stacr_quantize_coefficients, quantize_residuals=cfg.stacr_quantize_residuals,
-        residual_quantize_bits=cfg.stacr_residual_quantize_bits, basis_dtype=cfg.stacr_basis_dtype, use_fused_kernel=cfg.stacr_use_fused_kernel,
-        rank_mode=cfg.stacr_rank_mode, rank_min=cfg.stacr_rank_min, rank_max=max(cfg.stacr_rank_max, cfg.stacr_rank_min),
-        refresh_trigger=cfg.stacr_refresh_trigger, post_warmup_residual_mode=cfg.stacr_post_warmup_residual_mode,
-        residual_warmup_steps=cfg.stacr_residual_warmup_steps, index_compression=cfg.stacr_index_compression, cpu_offload=cfg.stacr_cpu_offload,
-    )
+def _adaptive_config(cfg: ConvergenceConfig, **override) -> AdaptiveConfig:
+    engine_fields = {f.name for f in fields(AdaptiveConfig)}
+    opts: Dict[str, Any] = {"rank": cfg.rank}
+    for f in fields(cfg):
+        if not f.name.startswith("stacr_") or f.name.startswith(("stacr_ckpt_", "stacr_graph_")):
+            continue
+        short = f.name[len("stacr_"):]
+        if short in _RUNNER_ONLY:
+            continue
+        target = _ENGINE_ALIASES.get(short, short)
+        if target in engine_fields:
+            opts[target] = getattr(cfg, f.name)
+    opts["rank_max"] = max(int(opts.get("rank_max", 64)), int(opts.get("rank_min", 4)))
+    if cfg.method == "stac":
+        opts["residual_mode"] = "none"
+    opts.update(override)
+    return AdaptiveConfig(**opts)
+
+
+def checkpoint_boundary_config(cfg: ConvergenceConfig):
+    """The ``stacr_ckpt_*`` fields as a checkpoint-boundary codec configuration."""
+    from stacr_b200.protocols.checkpointing import STACRCheckpointConfig
+
+    names = {f.name for f in fields(STACRCheckpointConfig)}
+    opts = {k[len("stacr_ckpt_"):]: v for k, v in cfg.to_dict().items() if k.startswith("stacr_ckpt_") and k[len("stacr_ckpt_"):] in names}
+    return STACRCheckpointConfig(enabled=True, **opts)
 
 
 def replace_linear_with_stacr(model: nn.Module, names: List[str], cfg: ConvergenceConfig) -> List[nn.Module]:
@@ -207,15 +395,44 @@ def replace_linear_with_stacr(model: nn.Module, names: List[str], cfg: Convergen
         return S.apply_stacr(model, surface="none", target_names=names, rank=cfg.rank, residual_budget=cfg.stacr_residual_budget,
                              turbo_after_step=None, allow_empty=True)
     base = _adaptive_config(cfg)
+    schedule = parse_rank_schedule(cfg.stacr_per_layer_rank_schedule)
     layers = []
     for i, name in enumerate(names):
         parent_name, _, leaf = name.rpartition(".")
         parent = model.get_submodule(parent_name) if parent_name else model
-        layer = AdaptiveLinear.from_linear(getattr(parent, leaf), copy.deepcopy(base), layer_index=i, num_layers=len(names))
+        source = getattr(parent, leaf)
+        conf = copy.deepcopy(base)
+        feats = int(source.weight.shape[0] if type(source).__name__ == "Conv1D" else source.weight.shape[1])
+        for key, value in schedule.items():
+            if key in name:
+                conf.rank = min(value, feats)
+                break
+        else:
+            if feats < 1024 and cfg.stacr_small_layer_rank_scale != 1.0:
+                conf.rank = max(1, min(feats, int(round(conf.rank * cfg.stacr_small_layer_rank_scale))))
+        if feats < 1024 and cfg.stacr_small_layer_residual_scale != 1.0:
+            conf.residual_budget = min(1.0, conf.residual_budget * cfg.stacr_small_layer_residual_scale)
+        conf.rank_max = max(conf.rank_max, conf.rank)
+        layer = AdaptiveLinear.from_linear(source, conf, layer_index=i, num_layers=len(names))
         layer.source_name = name
         setattr(parent, leaf, layer)
         layers.append(layer)
     return layers
+
+
+def compress_attention_surface(model: nn.Module, cfg: ConvergenceConfig):
+    """``stacr_attention``: wrap the Q/K/V projections too (own rank / residual mode when given)."""
+    from stacr_b200.protocols.attention import apply_stacr_to_attention
+
+    extra = {}
+    if cfg.stacr_attention_rank is not None:
+        extra["rank"] = int(cfg.stacr_attention_rank)
+    if cfg.stacr_attention_residual_mode is not None:
+        extra["residual_mode"] = cfg.stacr_attention_residual_mode
+    conf = _adaptive_config(cfg, **extra)
+    conf.rank_max = max(conf.rank_max, conf.rank)
+    return apply_stacr_to_attention(model, conf, enable_gpt2_c_attn_split=cfg.stacr_gpt2_split_c_attn, mask_aware=cfg.padding_mode == "max_length",
+                                    joint_qk=cfg.stacr_joint_qk)
 
 
 def replace_linear_with_compressed(model: nn.Module, names: List[str], cfg: ConvergenceConfig) -> List[nn.Module]:
@@ -254,17 +471,41 @@ def apply_baseline(model: nn.Module, cfg: ConvergenceConfig, device) -> Dict[str
     state: Dict[str, Any] = {"amp": AMPManager(b.amp, str(device)), "offload": None, "checkpointed": 0}
     if b.checkpointing != "none":
         state["checkpointed"] = apply_checkpointing(model, b.checkpointing)
+    for key, module_name, fn_name in (("actnn", "actnn_adapter", "try_enable_actnn"), ("gact", "gact_adapter", "try_enable_gact")):
+        level = getattr(b, key)
+        if level != "none":
+            import importlib
+
+            adapter = importlib.import_module(f"stacr_b200.protocols.baselines.{module_name}")
+            _, outcome = getattr(adapter, fn_name)(model, level)
+            state[key] = outcome.to_dict() if hasattr(outcome, "to_dict") else str(outcome)
     if b.offload != "none":
         state["offload"] = OffloadManager(b.offload, b.offload_min_bytes)
     if b.c1_checkpoint_compression:
         from stacr_b200.protocols.checkpointing import STACRCheckpointConfig, enable_c1_checkpointing_for_model
 
         state["c1"] = enable_c1_checkpointing_for_model(model, STACRCheckpointConfig(enabled=True, warmup_steps=0, min_numel=0), amp_mode=b.amp)
+    elif cfg.stacr_compress_checkpoint:
+        from stacr_b200.protocols.checkpointing import enable_c1_checkpointing_for_model
+
+        state["c1"] = enable_c1_checkpointing_for_model(model, checkpoint_boundary_config(cfg), amp_mode=b.amp)
     return state
 
 
 def build_optimizer(model: nn.Module, cfg: ConvergenceConfig):
     params = [p for p in model.parameters() if p.requires_grad]
+    galore = cfg.baseline_cfg.galore_options()
+    if galore is not None:
+        from stacr_b200.comparators.galore_adapter import create_galore_optimizer
+
+        return create_galore_optimizer(model, lr=cfg.lr, weight_decay=cfg.weight_decay, **galore), f"GaLoreAdamW({cfg.baseline_cfg.galore})"
+    if cfg.baseline_cfg.torchao not in ("none", "float8"):
+        from stacr_b200.protocols.baselines.torchao_adapter import try_create_torchao_optimizer
+
+        name = "adamw8bit" if cfg.baseline_cfg.torchao == "auto" else cfg.baseline_cfg.torchao
+        made, result = try_create_torchao_optimizer(params, name, lr=cfg.lr, weight_decay=cfg.weight_decay)
+        if made is not None:
+            return made, f"torchao:{name}"
     if cfg.baseline_cfg.optimizer_8bit:
         from stacr_b200.optim import AdamW8bit
 
@@ -339,7 +580,9 @@ def compute_per_layer_grad_fidelity(model, batch, amp: AMPManager, layers) -> Di
         if isinstance(layer, AdaptiveLinear):
             lin = layer.linear
             return getattr(lin, "source_weight", None) if hasattr(lin, "source_weight") else lin.weight
-        return layer.weight
+        if hasattr(layer, "weight"):
+            return layer.weight
+        return layer.linear.weight  # comparator wrappers keep the dense projection as ``linear``
 
     weights = {getattr(l, "source_name", str(i)): weight_of(l) for i, l in enumerate(layers)}
     stash = {k: (None if w.grad is None else w.grad.clone()) for k, w in weights.items()}
@@ -398,7 +641,8 @@ def run_convergence_experiment(cfg: ConvergenceConfig, logger) -> Dict[str, Any]
     cuda = torch.cuda.is_available() and cfg.device in ("auto", "cuda")
     device = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0"))) if cuda else torch.device("cpu")
     logger.write_config(cfg.to_dict())
-    model = build_model(cfg.model, **cfg.model_overrides).to(device).train()
+    model_name = cfg.model or ("bert-base-uncased" if cfg.task == "sst2" else "gpt2-medium")
+    model = build_model(model_name, **cfg.model_overrides).to(device).train()
     vocab = model.config.vocab_size
     tp_profiler = None
     if cfg.use_tensor_parallel:
@@ -412,6 +656,7 @@ def run_convergence_experiment(cfg: ConvergenceConfig, logger) -> Dict[str, Any]
         broadcast_parameters(model)
     layers: List[nn.Module] = []
     plan_summary = None
+    attention_report = None
     if cfg.method in ("stacr", "stac"):
         names = select_targets(model, cfg)
         if cfg.stacr_planner == "bytes":
@@ -419,10 +664,14 @@ def run_convergence_experiment(cfg: ConvergenceConfig, logger) -> Dict[str, Any]
             plan_summary = summarize_layer_decisions(decisions)
             names = [d.name for d in decisions if d.keep]
         layers = replace_linear_with_stacr(model, names, cfg)
+        if cfg.stacr_attention and cfg.stacr_engine == "adaptive":
+            attention_report = compress_attention_surface(model, cfg)
+            layers += [m for m in model.modules() if isinstance(m, AdaptiveLinear) and m not in layers]
     elif cfg.method in ("svd", "tt", "tucker"):
         layers = replace_linear_with_compressed(model, select_targets(model, cfg), cfg)
     elif cfg.method == "prac":
-        layers = replace_linear_with_prac(model, select_targets(model, cfg), PRACConfig(rank=cfg.rank, update_proj_gap=cfg.prac_update_proj_gap, quiet=True))
+        layers = replace_linear_with_prac(model, select_targets(model, cfg), PRACConfig(rank=cfg.rank, update_proj_gap=cfg.prac_update_proj_gap, seed_base=cfg.prac_seed_base,
+                                                                                    proj_dtype=None if cfg.prac_proj_dtype == "auto" else cfg.prac_proj_dtype, quiet=True))
     state = apply_baseline(model, cfg, device)
     amp: AMPManager = state["amp"]
     optimizer, optimizer_name = build_optimizer(model, cfg)
@@ -434,7 +683,8 @@ def run_convergence_experiment(cfg: ConvergenceConfig, logger) -> Dict[str, Any]
     data_world = world if cfg.use_ddp else 1
     train = make_distributed_loader(build_batches(cfg, vocab, max(1, cfg.train_examples // cfg.batch_size), cfg.seed, device), rank if cfg.use_ddp else 0, data_world)
     val = build_batches(cfg, vocab, max(1, cfg.eval_examples // cfg.batch_size), cfg.seed + 1, device)
-    total_steps = min(cfg.max_steps, cfg.epochs * len(train))
+    accum = int(cfg.baseline_cfg.grad_accum_steps)
+    total_steps = min(cfg.max_steps, max(1, cfg.epochs * len(train) // accum))
     warm = int(cfg.warmup_ratio * total_steps)
     if cuda:
         torch.cuda.reset_peak_memory_stats(device)
@@ -452,7 +702,6 @@ def run_convergence_experiment(cfg: ConvergenceConfig, logger) -> Dict[str, Any]
             lr_scale = min(1.0, (step + 1) / max(1, warm)) if step < warm else max(0.0, (total_steps - step) / max(1, total_steps - warm))
             for g in optimizer.param_groups:
                 g["lr"] = cfg.lr * lr_scale
-            set_stacr_runtime_state(model, step, 0, 1, total_steps)
             S.set_step([l for l in layers if isinstance(l, S.STACRLinear)], step)
             if cfg.method == "prac":
                 set_prac_global_step(model, step)
@@ -460,13 +709,17 @@ def run_convergence_experiment(cfg: ConvergenceConfig, logger) -> Dict[str, Any]
                 sync.zero_grad() if sync else optimizer.zero_grad(set_to_none=True)
                 ctx = state["offload"].training_step() if state["offload"] else _null()
                 with ctx:
-                    with profiler.phase("forward"), amp.autocast():
-                        loss = model(**batch).loss
-                    value = float(loss.detach())
-                    if not math.isfinite(value):
-                        raise FloatingPointError(f"Nonfinite loss at step {step}")
-                    with profiler.phase("backward"):
-                        amp.backward(loss)
+                    value = 0.0
+                    for micro in range(accum):
+                        batch = train[(step * accum + micro) % len(train)]
+                        set_stacr_runtime_state(model, step, micro, accum, total_steps)
+                        with profiler.phase("forward"), amp.autocast():
+                            loss = model(**batch).loss / accum
+                        value += float(loss.detach())
+                        if not math.isfinite(value):
+                            raise FloatingPointError(f"Nonfinite loss at step {step}")
+                        with profiler.phase("backward"):
+                            amp.backward(loss)
                 with profiler.phase("optimizer"):
                     if sync:
                         sync.finish()
@@ -518,7 +771,7 @@ def run_convergence_experiment(cfg: ConvergenceConfig, logger) -> Dict[str, Any]
         "optimizer": optimizer_name, "train_loss_mean": reduced["loss_sum"] / max(1, reduced["steps"]), "train_loss_last": history[-1] if history else None,
         "train_loss_first": history[0] if history else None, "seconds": elapsed, "tokens_per_second": reduced["tokens"] / elapsed if elapsed > 0 else None,
         "peak_allocated_bytes": reduced["peak_bytes"], "n_wrapped_layers": len(layers), "baseline": cfg.baseline_cfg.get_description(),
-        "stacr_flags": flags, "planner": plan_summary, "tp_activation_profile": tp_profiler.summary() if tp_profiler else None,
+        "stacr_flags": flags, "planner": plan_summary, "attention": attention_report.to_dict() if attention_report else None, "tp_activation_profile": tp_profiler.summary() if tp_profiler else None,
         "offload": state["offload"].get_stats() if state["offload"] else None, **quality,
     }
     if cfg.save_final_model and int(os.environ.get("LOCAL_RANK", "0")) == 0 and getattr(logger, "dir", None):

@@ -60,7 +60,12 @@ class RecomputationGuard:
         source = self._source()
         if source is None:
             return None
-        ident, state = next(source)
+        entry = next(source, None)
+        if entry is None:
+            # nothing was recorded for this layer (the first forward ran without autograd, as a compressed
+            # checkpoint boundary does): the replay is the layer's first training forward of the step
+            return None
+        ident, state = entry
         if ident != id(layer):
             raise RuntimeError("STAC-R layer order changed during checkpoint replay")
         return state

@@ -82,18 +82,37 @@ __global__ void __launch_bounds__(512) allreduce_two_shot_kernel(const CommArgs 
   long long begin, end;
   slice_of(a, begin, end);
   const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
-  for (long long i = begin + blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < end; i += stride) {
-    const long long off = a.lo / 4 + i;
-    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+  constexpr int UNROLL = 4;  // independent 16-byte elements in flight per thread
+  for (long long i0 = begin + blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i0 < end; i0 += stride * UNROLL) {
+    float4 acc[UNROLL];
+#pragma unroll
+    for (int u = 0; u < UNROLL; ++u) acc[u] = make_float4(0.f, 0.f, 0.f, 0.f);
     for (int p = 0; p < a.world; ++p) {
       const int src = (a.rank + p) % a.world;  // start at the local copy, spread peer traffic
-      const float4 v = reinterpret_cast<const float4*>(s_peers[src])[off];
-      acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+      const float4* base = reinterpret_cast<const float4*>(s_peers[src]) + a.lo / 4;
+      float4 v[UNROLL];
+#pragma unroll
+      for (int u = 0; u < UNROLL; ++u) {
+        const long long i = i0 + u * stride;
+        v[u] = i < end ? base[i] : make_float4(0.f, 0.f, 0.f, 0.f);
+      }
+#pragma unroll
+      for (int u = 0; u < UNROLL; ++u) {
+        acc[u].x += v[u].x; acc[u].y += v[u].y; acc[u].z += v[u].z; acc[u].w += v[u].w;
+      }
     }
-    acc.x *= a.scale; acc.y *= a.scale; acc.z *= a.scale; acc.w *= a.scale;
+#pragma unroll
+    for (int u = 0; u < UNROLL; ++u) {
+      acc[u].x *= a.scale; acc[u].y *= a.scale; acc[u].z *= a.scale; acc[u].w *= a.scale;
+    }
     for (int p = 0; p < a.world; ++p) {
       const int dst = (a.rank + p) % a.world;
-      reinterpret_cast<float4*>(s_peers[dst])[off] = acc;
+      float4* base = reinterpret_cast<float4*>(s_peers[dst]) + a.lo / 4;
+#pragma unroll
+      for (int u = 0; u < UNROLL; ++u) {
+        const long long i = i0 + u * stride;
+        if (i < end) base[i] = acc[u];
+      }
     }
   }
   rank_barrier(a, 1, &s_fail);
@@ -107,16 +126,30 @@ __global__ void __launch_bounds__(512) allreduce_multimem_kernel(const CommArgs 
   long long begin, end;
   slice_of(a, begin, end);
   const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
-  for (long long i = begin + blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < end; i += stride) {
-    float* addr = reinterpret_cast<float*>(a.mc_ptr) + a.lo + i * 4;
-    float x, y, z, w;
-    asm volatile("multimem.ld_reduce.relaxed.sys.global.add.v4.f32 {%0, %1, %2, %3}, [%4];"
-                 : "=f"(x), "=f"(y), "=f"(z), "=f"(w)
-                 : "l"(addr)
-                 : "memory");
-    x *= a.scale; y *= a.scale; z *= a.scale; w *= a.scale;
-    asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(x), "f"(y), "f"(z), "f"(w)
-                 : "memory");
+  constexpr int UNROLL = 4;
+  for (long long i0 = begin + blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i0 < end; i0 += stride * UNROLL) {
+    float x[UNROLL], y[UNROLL], z[UNROLL], w[UNROLL];
+#pragma unroll
+    for (int u = 0; u < UNROLL; ++u) {
+      const long long i = i0 + u * stride;
+      if (i < end) {
+        float* addr = reinterpret_cast<float*>(a.mc_ptr) + a.lo + i * 4;
+        asm volatile("multimem.ld_reduce.relaxed.sys.global.add.v4.f32 {%0, %1, %2, %3}, [%4];"
+                     : "=f"(x[u]), "=f"(y[u]), "=f"(z[u]), "=f"(w[u])
+                     : "l"(addr)
+                     : "memory");
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < UNROLL; ++u) {
+      const long long i = i0 + u * stride;
+      if (i < end) {
+        float* addr = reinterpret_cast<float*>(a.mc_ptr) + a.lo + i * 4;
+        asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(x[u] * a.scale),
+                     "f"(y[u] * a.scale), "f"(z[u] * a.scale), "f"(w[u] * a.scale)
+                     : "memory");
+      }
+    }
   }
   rank_barrier(a, 1, &s_fail);
 }

@@ -313,7 +313,9 @@ def train_model(model, train_batches, config: dict, *, validation_batches=None) 
         raise ValueError("lr_schedule must be constant, linear or cosine")
     first_step = 0
     if cfg.get("resume_from"):
-        blob = torch.load(cfg["resume_from"], map_location=device, weights_only=False)
+        from .parallel.health import load_checkpoint
+
+        blob = load_checkpoint(cfg["resume_from"], map_location=device)  # refuses a truncated or altered file
         model.load_state_dict(blob["model"])
         optimizer.load_state_dict(blob["optimizer"])
         scaler.load_state_dict(blob.get("scaler", {}))
@@ -383,7 +385,9 @@ def train_model(model, train_batches, config: dict, *, validation_batches=None) 
     if cfg.get("checkpoint_path"):
         target = Path(cfg["checkpoint_path"])
         target.parent.mkdir(parents=True, exist_ok=True)
-        torch.save(
+        from .parallel.health import write_checkpoint
+
+        write_checkpoint(
             {
                 "model": model.state_dict(), "optimizer": optimizer.state_dict(), "scaler": scaler.state_dict(), "step": steps,
                 "config": cfg, "rng_state": torch.get_rng_state(),
