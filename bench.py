@@ -134,7 +134,8 @@ def run_ours(args):
     broadcast_parameters(model)
     layers = S.apply_stacr(model, **STACR)
     opt = AdamW8bit(model.parameters(), lr=2e-5, weight_decay=0.0, bf16_shadow=True)
-    sync = GradSync(model.parameters(), backend=args.comm) if world > 1 else None
+    fused = [layer.weight for layer in layers] if args.fused_dw == "on" else []
+    sync = GradSync(model.parameters(), backend=args.comm, fused=fused) if world > 1 else None
     host_batches = [t.pin_memory() for t in make_tokens(torch, shape["vocab_size"], batch, seq, 8, 100 + rank)]
     dev_batches = [t.to(dev) for t in host_batches]
     counter = {"step": 0}
@@ -190,6 +191,7 @@ def run_ours(args):
                 "model": "pythia-1.4b-shaped (24L d2048 h16 mlp8192 rotary25% parallel-residual vocab50304)" if not args.small else "small",
                 "global_batch": world * batch, "seq_len": seq, "parallelism": f"dp{world}",
                 "stacr": STACR, "optimizer": "AdamW 8-bit block-wise (in-tree)", "comm": sync.backend if sync else "none",
+                "fused_dw_reduce_scatter": bool(sync and sync.n_fused and sync.backend == "symm"),
                 "l2": "inputs larger than L2: every step streams 2.8 GB of bf16 weights and > 10 GB of activations through a 126 MB L2",
             },
             "clocks": clocks.summary(),
@@ -304,6 +306,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--comm", default="auto", choices=["auto", "symm", "nccl"], help="gradient all-reduce path (this framework)")
+    ap.add_argument("--fused-dw", default="on", choices=["on", "off"],
+                    help="N > 1: compressed layers' weight-gradient kernels reduce-scatter in their epilogue over NVLink peer memory")
     ap.add_argument("--small", action="store_true", help="tiny shape for smoke runs (not a benchmark number)")
     args = ap.parse_args()
     if args.gpus > 1 and "RANK" not in os.environ:

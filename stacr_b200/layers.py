@@ -314,10 +314,16 @@ class STACRFunction(torch.autograd.Function):
                 residual = None
                 if ctx.has_residual and res[0].numel():
                     residual = (res[0], res[1], res[2], ctx.residual_bits, ctx.residual_len)
-                gw = stacr_ops.weight_grad(
-                    ga, coeff, q.float(), residual, ctx.out_features, ctx.in_features, ctx.transposed, weight.dtype
-                    if weight.dtype in (torch.float32, torch.bfloat16) else torch.float32,
-                ).to(weight.dtype)
+                sink = getattr(weight, "_sb_grad_sink", None)
+                if sink is not None and weight.dtype == torch.float32:
+                    # the kernel delivers dW into the flat gradient buffer (and across ranks) itself
+                    stacr_ops.weight_grad(ga, coeff, q.float(), residual, ctx.out_features, ctx.in_features, ctx.transposed, torch.float32, sink=sink)
+                    sink.done()
+                else:
+                    gw = stacr_ops.weight_grad(
+                        ga, coeff, q.float(), residual, ctx.out_features, ctx.in_features, ctx.transposed, weight.dtype
+                        if weight.dtype in (torch.float32, torch.bfloat16) else torch.float32,
+                    ).to(weight.dtype)
             if ctx.needs_input_grad[2]:
                 gb = stacr_ops.colsum(ga).to(ctx.bias_dtype)
             return (gx, gw, gb) + (None,) * (ctx.n_args - 3)

@@ -1,5 +1,7 @@
-// Basis maintenance on the device: the Oja subspace step followed by CholeskyQR2, in one
-// single-CTA kernel (the operands are N x r with r <= 32, a few hundred KB at most).
+// Basis maintenance on the device: the Oja subspace step followed by CholeskyQR2 in one kernel (the
+// operands are N x r with r <= 32, a few hundred KB at most).  Rank <= 8 runs as a thread-block cluster
+// of up to 8 CTAs: every thread keeps its rows of Q in registers from the Oja step to the final store, and
+// the three r x r Gram matrices are reduced through distributed shared memory.  Larger ranks use one CTA.
 //
 //   A = Q + lr * (G / n - Q * (S / n)),   G = X^T Y (from the skinny tensor-core GEMM),
 //                                         S = Y^T Y (reduced here from Y),
@@ -12,7 +14,11 @@
 // that the projection GEMM reads as its K-major B operand.
 // Replaces four library GEMMs and a cuSOLVER QR per step (stacr/layers.py:350-353 and
 // stacr/oja.py:8-11 of the reference project).
+#include <cooperative_groups.h>
+
 #include "common.cuh"
+
+namespace cg = cooperative_groups;
 
 namespace sb {
 
@@ -198,6 +204,148 @@ __global__ void __launch_bounds__(1024) oja_update_kernel(const float* q_in, con
   }
 }
 
+
+// ---------------------------------------------------------------------------------------------------------
+// Cluster version for r <= 8.
+constexpr int OJA_ROWS_PT = 4;  // basis rows per thread: n <= cluster size * 1024 * 4
+
+__device__ __forceinline__ void accumulate_upper8(const float (&v)[8], float (&acc)[36]) {
+  int k = 0;
+#pragma unroll
+  for (int i = 0; i < 8; ++i)
+#pragma unroll
+    for (int j = 0; j <= i; ++j) {
+      acc[k] = fmaf(v[i], v[j], acc[k]);
+      ++k;
+    }
+}
+
+// acc (36 upper-triangle sums of this thread) -> symmetric r x r total over the whole cluster in s_gram.
+// s_part must be zero on entry and is zero again on exit.
+__device__ void cluster_gram8(cg::cluster_group& cluster, const float (&acc)[36], float* s_part, float* s_gram) {
+  const int lane = threadIdx.x & 31;
+#pragma unroll
+  for (int k = 0; k < 36; ++k) {
+    float v = acc[k];
+#pragma unroll
+    for (int off = 16; off; off >>= 1) v += __shfl_xor_sync(0xffffffffu, v, off);
+    if (lane == 0) atomicAdd(&s_part[k], v);
+  }
+  cluster.sync();  // every CTA's partial is complete
+  if (threadIdx.x < 36) {
+    float total = 0.f;
+    const int nb = static_cast<int>(cluster.num_blocks());
+    for (int b = 0; b < nb; ++b) total += cluster.map_shared_rank(s_part, b)[threadIdx.x];
+    int i = 0, base = 0;
+    while (base + i + 1 <= static_cast<int>(threadIdx.x)) {
+      base += i + 1;
+      ++i;
+    }
+    const int j = threadIdx.x - base;
+    s_gram[i * RMAX + j] = total;
+    s_gram[j * RMAX + i] = total;
+  }
+  cluster.sync();  // every CTA has read every partial
+  if (threadIdx.x < 36) s_part[threadIdx.x] = 0.f;
+  __syncthreads();
+}
+
+template <int ROWS_PT>
+__global__ void __launch_bounds__(1024) oja_update_cluster8_kernel(const float* __restrict__ q_in, const float* __restrict__ g, int ldg,
+                                                                   const float* __restrict__ y, int ldy, int rows, int n, int r, float lr,
+                                                                   float* __restrict__ q_out, __nv_bfloat16* __restrict__ q_bf16,
+                                                                   __nv_bfloat16* __restrict__ qt_bf16, int rpad, int* status) {
+  cg::cluster_group cluster = cg::this_cluster();
+  __shared__ float s_part[36];
+  __shared__ float s_mat[RMAX * RMAX];
+  __shared__ float s_inv[RMAX * RMAX];
+  __shared__ int s_ok;
+  if (threadIdx.x < 36) s_part[threadIdx.x] = 0.f;
+  __syncthreads();
+  const int gthreads = static_cast<int>(cluster.num_blocks()) * blockDim.x;
+  const int gtid = static_cast<int>(cluster.block_rank()) * blockDim.x + threadIdx.x;
+  const float inv_n = 1.f / fmaxf(1.f, static_cast<float>(rows));
+  float qrow[ROWS_PT][8];
+#pragma unroll
+  for (int t = 0; t < ROWS_PT; ++t) {
+    const int row = gtid + t * gthreads;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) qrow[t][j] = (row < n && j < r) ? q_in[static_cast<size_t>(row) * r + j] : 0.f;
+  }
+  if (lr != 0.f && g != nullptr) {
+    float acc[36];
+#pragma unroll
+    for (int k = 0; k < 36; ++k) acc[k] = 0.f;
+    for (int row = gtid; row < rows; row += gthreads) {  // S = Y^T Y on the bf16-rounded coefficients
+      const float* yr = y + static_cast<size_t>(row) * ldy;
+      float v[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) v[j] = (j < r) ? __bfloat162float(__float2bfloat16_rn(yr[j])) : 0.f;
+      accumulate_upper8(v, acc);
+    }
+    cluster_gram8(cluster, acc, s_part, s_mat);
+#pragma unroll
+    for (int t = 0; t < ROWS_PT; ++t) {
+      const int row = gtid + t * gthreads;
+      if (row >= n) continue;
+      float next[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        float qs = 0.f;
+#pragma unroll
+        for (int k = 0; k < 8; ++k) qs = fmaf(qrow[t][k], s_mat[k * RMAX + j], qs);
+        next[j] = (j < r) ? qrow[t][j] + lr * inv_n * (g[static_cast<size_t>(row) * ldg + j] - qs) : 0.f;
+      }
+#pragma unroll
+      for (int j = 0; j < 8; ++j) qrow[t][j] = next[j];
+    }
+  }
+  for (int pass = 0; pass < 2; ++pass) {  // CholeskyQR2
+    float acc[36];
+#pragma unroll
+    for (int k = 0; k < 36; ++k) acc[k] = 0.f;
+#pragma unroll
+    for (int t = 0; t < ROWS_PT; ++t) accumulate_upper8(qrow[t], acc);  // rows past n are zero
+    cluster_gram8(cluster, acc, s_part, s_mat);
+    chol_and_invert(s_mat, s_inv, r, &s_ok);  // the same numbers in every CTA: the outcome is uniform over the cluster
+    if (!s_ok) {
+      if (threadIdx.x == 0 && status) atomicCAS(status, 0, ST_BAD_ARGUMENT);
+      break;
+    }
+#pragma unroll
+    for (int t = 0; t < ROWS_PT; ++t) {
+      float next[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        float v = 0.f;
+#pragma unroll
+        for (int k = 0; k < 8; ++k)
+          if (k <= j && j < r) v = fmaf(qrow[t][k], s_inv[k * RMAX + j], v);
+        next[j] = v;
+      }
+#pragma unroll
+      for (int j = 0; j < 8; ++j) qrow[t][j] = next[j];
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int t = 0; t < ROWS_PT; ++t) {
+    const int row = gtid + t * gthreads;
+    if (row >= n) continue;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      if (j < r) {
+        q_out[static_cast<size_t>(row) * r + j] = qrow[t][j];
+        if (q_bf16) q_bf16[static_cast<size_t>(row) * r + j] = __float2bfloat16_rn(qrow[t][j]);
+      }
+    }
+    if (qt_bf16)
+      for (int j = 0; j < rpad; ++j)
+        qt_bf16[static_cast<size_t>(j) * n + row] = (j < 8 && j < r) ? __float2bfloat16_rn(qrow[t][j]) : __float2bfloat16_rn(0.f);
+  }
+  cluster.sync();  // no CTA leaves while a peer may still read its shared memory
+}
+
 }  // namespace sb
 
 // Q' = orth(Q + lr (G/rows - Q (Y^T Y)/rows)).  g: [n, ldg] fp32; y: [rows, ldy] fp32 (both may be NULL
@@ -208,6 +356,27 @@ extern "C" int sb_oja_update(const float* q_in, const float* g, int ldg, const f
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   __nv_bfloat16* qb = static_cast<__nv_bfloat16*>(q_bf16);
   __nv_bfloat16* qt = static_cast<__nv_bfloat16*>(qt_bf16);
+  if (r <= 8 && n <= 8 * 1024 * sb::OJA_ROWS_PT) {
+    const int want = (n > rows ? n : rows);
+    unsigned csize = 1;
+    while (csize < 8 && static_cast<int>(csize) * 1024 < want) csize <<= 1;
+    while (static_cast<long long>(csize) * 1024 * sb::OJA_ROWS_PT < n) csize <<= 1;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(csize, 1, 1);
+    cfg.blockDim = dim3(1024, 1, 1);
+    cfg.dynamicSmemBytes = 0;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = csize;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    if (static_cast<long long>(csize) * 1024 >= n)
+      return static_cast<int>(cudaLaunchKernelEx(&cfg, sb::oja_update_cluster8_kernel<1>, q_in, g, ldg, y, ldy, rows, n, r, lr, q_out, qb, qt, rpad, status));
+    return static_cast<int>(cudaLaunchKernelEx(&cfg, sb::oja_update_cluster8_kernel<sb::OJA_ROWS_PT>, q_in, g, ldg, y, ldy, rows, n, r, lr, q_out, qb, qt, rpad, status));
+  }
   if (r <= 8) sb::oja_update_kernel<8><<<1, 1024, 0, st>>>(q_in, g, ldg, y, ldy, rows, n, r, lr, q_out, qb, qt, rpad, status);
   else if (r <= 16) sb::oja_update_kernel<16><<<1, 1024, 0, st>>>(q_in, g, ldg, y, ldy, rows, n, r, lr, q_out, qb, qt, rpad, status);
   else sb::oja_update_kernel<32><<<1, 1024, 0, st>>>(q_in, g, ldg, y, ldy, rows, n, r, lr, q_out, qb, qt, rpad, status);

@@ -154,6 +154,83 @@ __global__ void __launch_bounds__(512) allreduce_multimem_kernel(const CommArgs 
   rank_barrier(a, 1, &s_fail);
 }
 
+// Every rank broadcasts its own slice of [lo, hi) (scaled) to all ranks: the second half of an all-reduce whose
+// first half (the reduce-scatter) was done by the producing kernels with red.add into the owner's copy.
+__global__ void __launch_bounds__(512) allgather_slices_kernel(const CommArgs a) {
+  __shared__ int s_fail;
+  __shared__ unsigned long long s_peers[MAX_RANKS];
+  if (threadIdx.x == 0) s_fail = 0;
+  if (threadIdx.x < a.world) s_peers[threadIdx.x] = a.peer_ptrs[threadIdx.x];
+  __syncthreads();
+  if (!rank_barrier(a, 0, &s_fail)) return;   // all ranks' producers have finished: the owner copies are complete
+  long long begin, end;
+  slice_of(a, begin, end);
+  const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+  const float4* mine = reinterpret_cast<const float4*>(s_peers[a.rank]) + a.lo / 4;
+  constexpr int UNROLL = 4;
+  for (long long i0 = begin + blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i0 < end; i0 += stride * UNROLL) {
+    float4 v[UNROLL];
+#pragma unroll
+    for (int u = 0; u < UNROLL; ++u) {
+      const long long i = i0 + u * stride;
+      v[u] = i < end ? mine[i] : make_float4(0.f, 0.f, 0.f, 0.f);
+      v[u].x *= a.scale; v[u].y *= a.scale; v[u].z *= a.scale; v[u].w *= a.scale;
+    }
+    if (a.mc_ptr != 0) {
+#pragma unroll
+      for (int u = 0; u < UNROLL; ++u) {
+        const long long i = i0 + u * stride;
+        if (i < end) {
+          float* addr = reinterpret_cast<float*>(a.mc_ptr) + a.lo + i * 4;
+          asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(v[u].x), "f"(v[u].y),
+                       "f"(v[u].z), "f"(v[u].w)
+                       : "memory");
+        }
+      }
+    } else {
+      for (int p = 0; p < a.world; ++p) {
+        const int dst = (a.rank + p) % a.world;
+        float4* base = reinterpret_cast<float4*>(s_peers[dst]) + a.lo / 4;
+#pragma unroll
+        for (int u = 0; u < UNROLL; ++u) {
+          const long long i = i0 + u * stride;
+          if (i < end) base[i] = v[u];
+        }
+      }
+    }
+  }
+  rank_barrier(a, 1, &s_fail);
+}
+
+// A barrier across ranks as a kernel of its own (one CTA), on the third flag plane.
+__global__ void __launch_bounds__(32) rank_barrier_kernel(const CommArgs a) {
+  __shared__ int s_fail;
+  if (threadIdx.x == 0) s_fail = 0;
+  __syncthreads();
+  rank_barrier(a, 2, &s_fail);
+}
+
+// One thread waits until *flag >= expected, for at most limit_ns; on expiry it records ST_TIMEOUT_PEER_FLAG and
+// returns.  `observed` (optional) receives the last value read.
+__global__ void flag_wait_kernel(const int* flag, int expected, unsigned long long limit_ns, int* status, int* observed) {
+  const uint64_t t0 = globaltimer_ns();
+  int v = ld_acquire_sys(flag);
+  uint32_t polls = 0;
+  while (v < expected) {
+    if ((++polls & 63u) == 0u && globaltimer_ns() - t0 > limit_ns) {
+      if (status) atomicCAS(status, 0, ST_TIMEOUT_PEER_FLAG);
+      break;
+    }
+    v = ld_acquire_sys(flag);
+  }
+  if (observed) *observed = v;
+}
+
+__global__ void flag_set_kernel(int* flag, int value) {
+  __threadfence_system();
+  st_release_sys(flag, value);
+}
+
 static int launch_allreduce(bool multimem, const CommArgs& a, int sms, cudaStream_t st) {
   if (a.world < 1 || a.world > MAX_RANKS) return -2;
   if ((a.lo & 3) || (a.hi & 3) || a.hi < a.lo) return -3;
@@ -169,7 +246,7 @@ static int launch_allreduce(bool multimem, const CommArgs& a, int sms, cudaStrea
 
 }  // namespace sb
 
-extern "C" int sb_comm_flag_ints() { return 2 * sb::MAX_CTAS * sb::MAX_RANKS; }
+extern "C" int sb_comm_flag_ints() { return 3 * sb::MAX_CTAS * sb::MAX_RANKS; }
 
 extern "C" int sb_allreduce_two_shot(const void* peer_ptrs, const void* flag_ptrs, unsigned long long mc_ptr, int rank, int world,
                                      long long lo, long long hi, float scale, int epoch, int sms, int* status, void* stream) {
@@ -184,4 +261,43 @@ extern "C" int sb_allreduce_multimem(const void* peer_ptrs, const void* flag_ptr
   sb::CommArgs a{static_cast<const unsigned long long*>(peer_ptrs), static_cast<const unsigned long long*>(flag_ptrs), mc_ptr, rank,
                  world, lo, hi, scale, epoch, status};
   return sb::launch_allreduce(true, a, sms, static_cast<cudaStream_t>(stream));
+}
+
+// Broadcast every rank's slice of [lo, hi) to all ranks (scaled).  mc_ptr != 0 selects the multicast store.
+extern "C" int sb_allgather_slices(const void* peer_ptrs, const void* flag_ptrs, unsigned long long mc_ptr, int rank, int world,
+                                   long long lo, long long hi, float scale, int epoch, int sms, int* status, void* stream) {
+  using namespace sb;
+  if (world < 1 || world > MAX_RANKS) return -2;
+  if ((lo & 3) || (hi & 3) || hi < lo) return -3;
+  CommArgs a{static_cast<const unsigned long long*>(peer_ptrs), static_cast<const unsigned long long*>(flag_ptrs), mc_ptr, rank, world,
+             lo, hi, scale, epoch, status};
+  const long long vecs = (hi - lo) / 4 / world;
+  int grid = static_cast<int>((vecs + 511) / 512);
+  const int cap = sms < MAX_CTAS ? sms : MAX_CTAS;
+  if (grid > cap / 2) grid = cap / 2;
+  if (grid < 1) grid = 1;
+  allgather_slices_kernel<<<grid, 512, 0, static_cast<cudaStream_t>(stream)>>>(a);
+  return static_cast<int>(cudaGetLastError());
+}
+
+extern "C" int sb_rank_barrier(const void* flag_ptrs, int rank, int world, int epoch, int* status, void* stream) {
+  using namespace sb;
+  if (world < 1 || world > MAX_RANKS) return -2;
+  CommArgs a{nullptr, static_cast<const unsigned long long*>(flag_ptrs), 0ull, rank, world, 0, 0, 1.f, epoch, status};
+  rank_barrier_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(a);
+  return static_cast<int>(cudaGetLastError());
+}
+
+// Stream-ordered wait on a flag word with a time limit (nanoseconds, capped at 5 s).
+extern "C" int sb_flag_wait(const int* flag, int expected, unsigned long long limit_ns, int* status, int* observed, void* stream) {
+  if (flag == nullptr) return -2;
+  if (limit_ns > 5000000000ull) limit_ns = 5000000000ull;
+  sb::flag_wait_kernel<<<1, 1, 0, static_cast<cudaStream_t>(stream)>>>(flag, expected, limit_ns, status, observed);
+  return static_cast<int>(cudaGetLastError());
+}
+
+extern "C" int sb_flag_set(int* flag, int value, void* stream) {
+  if (flag == nullptr) return -2;
+  sb::flag_set_kernel<<<1, 1, 0, static_cast<cudaStream_t>(stream)>>>(flag, value);
+  return static_cast<int>(cudaGetLastError());
 }

@@ -265,7 +265,7 @@ __global__ void __launch_bounds__(512) cross_entropy_kernel(const __nv_bfloat16*
     m = nm;
   }
   const float wm = warp_max(m);
-  s = warp_sum(s * __expf(m - wm));
+  s = warp_sum(m == -INFINITY ? 0.f : s * __expf(m - wm));  // a thread that saw no element has m = -inf: exp(-inf + inf) would be NaN
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   if (lane == 0) {
     s_m[warp] = wm;
@@ -277,7 +277,7 @@ __global__ void __launch_bounds__(512) cross_entropy_kernel(const __nv_bfloat16*
     float mm = lane < nw ? s_m[lane] : -INFINITY;
     float ss = lane < nw ? s_s[lane] : 0.f;
     const float gm = warp_max(mm);
-    ss = warp_sum(ss * __expf(mm - gm));
+    ss = warp_sum(mm == -INFINITY ? 0.f : ss * __expf(mm - gm));
     if (lane == 0) {
       s_max = gm;
       s_lse = gm + __logf(ss);

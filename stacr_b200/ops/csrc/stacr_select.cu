@@ -20,7 +20,8 @@
 namespace sb {
 
 constexpr int NBINS = 32768;
-constexpr int ROWS_UNROLL = 4;  // rows in flight per thread (memory-level parallelism)
+constexpr int ROWS_UNROLL = 8;  // rows in flight per thread (memory-level parallelism)
+constexpr int CS_ROWS = 256;    // coefficient rows staged in shared memory at a time
 
 struct SelectParams {
   const __nv_bfloat16* x;   // [rows, n], leading dimension ldx
@@ -110,10 +111,57 @@ __device__ __forceinline__ void residual_row(const XVec<CPT>& xv, const CVec<RP>
 template <int RP, int CPT>
 __device__ __forceinline__ void load_q(const __nv_bfloat16* q, int r, int col, int n, float (&qreg)[CPT][RP]) {
 #pragma unroll
-  for (int i = 0; i < CPT; ++i)
+  for (int i = 0; i < CPT; ++i) {
+    if (r == RP && col + i < n) {  // a basis row is RP * 2 bytes: 16-byte aligned for RP >= 8
+      const uint4* src = reinterpret_cast<const uint4*>(q + static_cast<size_t>(col + i) * RP);
 #pragma unroll
-    for (int j = 0; j < RP; ++j)
-      qreg[i][j] = (col + i < n && j < r) ? __bfloat162float(q[static_cast<size_t>(col + i) * r + j]) : 0.f;
+      for (int v = 0; v < RP / 8; ++v) {
+        const uint4 raw = __ldg(src + v);
+        const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          qreg[i][v * 8 + 2 * k] = __uint_as_float(w[k] << 16);
+          qreg[i][v * 8 + 2 * k + 1] = __uint_as_float(w[k] & 0xFFFF0000u);
+        }
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < RP; ++j)
+        qreg[i][j] = (col + i < n && j < r) ? __bfloat162float(q[static_cast<size_t>(col + i) * r + j]) : 0.f;
+    }
+  }
+}
+
+// Coefficient rows [row0, row1) of the slab as fp32 in shared memory, RP values per row (zero-padded past r).
+// Called by every thread of the CTA; ends with a barrier.
+template <int RP>
+__device__ __forceinline__ void stage_coeff(const __nv_bfloat16* c, int r, int row0, int row1, float* s_c) {
+  __syncthreads();  // the previous sub-slab is no longer being read
+  const int total = (row1 - row0) * RP;
+  for (int i = threadIdx.x; i < total; i += blockDim.x) {
+    const int lr = i / RP, j = i - lr * RP;
+    s_c[i] = (j < r) ? __bfloat162float(c[static_cast<size_t>(row0 + lr) * r + j]) : 0.f;
+  }
+  __syncthreads();
+}
+
+// Residual of CPT consecutive columns of one row; the coefficient row is read from shared memory (the address is
+// the same for every lane that works on this row, so the loads are broadcasts).
+template <int RP, int CPT>
+__device__ __forceinline__ void residual_row_s(const XVec<CPT>& xv, const float* crow, const float (&qreg)[CPT][RP], float (&e)[CPT]) {
+  float cf[RP];
+#pragma unroll
+  for (int v = 0; v < RP / 4; ++v) {
+    const float4 t = reinterpret_cast<const float4*>(crow)[v];
+    cf[4 * v] = t.x; cf[4 * v + 1] = t.y; cf[4 * v + 2] = t.z; cf[4 * v + 3] = t.w;
+  }
+#pragma unroll
+  for (int i = 0; i < CPT; ++i) {
+    float acc = 0.f;
+#pragma unroll
+    for (int j = 0; j < RP; ++j) acc = fmaf(cf[j], qreg[i][j], acc);
+    e[i] = bf16_bits_to_float(xv.v[i]) - acc;
+  }
 }
 
 // Work split shared by both passes: blockIdx.x = chunk * parts + part; a CTA walks its row
@@ -137,36 +185,37 @@ template <int RP>
 __global__ void __launch_bounds__(512, 1) residual_hist_kernel(const SelectParams p, int ctn, int rl) {
   constexpr int CPT = 64 / RP;
   extern __shared__ unsigned int sh_hist[];
+  float* s_c = reinterpret_cast<float*>(sh_hist + NBINS);
   for (int b = threadIdx.x; b < NBINS; b += blockDim.x) sh_hist[b] = 0;
-  __syncthreads();
   const Slab s = slab_of(p);
   const int ct = threadIdx.x % ctn, lane_row = threadIdx.x / ctn;
-  for (int cb = 0; cb < p.n; cb += ctn * CPT) {
-    const int col = cb + ct * CPT;
-    if (col >= p.n || lane_row >= rl) continue;
-    float qreg[CPT][RP];
-    load_q<RP, CPT>(p.q, p.r, col, p.n, qreg);
-    for (int row = s.row0 + lane_row; row < s.row1; row += rl * ROWS_UNROLL) {
-      XVec<CPT> xv[ROWS_UNROLL];
-      CVec<RP> cv[ROWS_UNROLL];
+  for (int sb0 = s.row0; sb0 < s.row1; sb0 += CS_ROWS) {
+    const int sb1 = min(s.row1, sb0 + CS_ROWS);
+    stage_coeff<RP>(p.c, p.r, sb0, sb1, s_c);
+    for (int cb = 0; cb < p.n; cb += ctn * CPT) {
+      const int col = cb + ct * CPT;
+      if (col >= p.n || lane_row >= rl) continue;
+      float qreg[CPT][RP];
+      load_q<RP, CPT>(p.q, p.r, col, p.n, qreg);
+      for (int row = sb0 + lane_row; row < sb1; row += rl * ROWS_UNROLL) {
+        XVec<CPT> xv[ROWS_UNROLL];
 #pragma unroll
-      for (int u = 0; u < ROWS_UNROLL; ++u) {  // issue every load of the group before any use
-        const int rr = row + u * rl;
-        if (rr < s.row1) {
-          xv[u] = load_x<CPT>(p.x + static_cast<size_t>(rr) * p.ldx, col, p.n);
-          cv[u] = load_c<RP>(p.c + static_cast<size_t>(rr) * p.r, p.r);
+        for (int u = 0; u < ROWS_UNROLL; ++u) {  // issue every load of the group before any use
+          const int rr = row + u * rl;
+          if (rr < sb1) xv[u] = load_x<CPT>(p.x + static_cast<size_t>(rr) * p.ldx, col, p.n);
         }
-      }
 #pragma unroll
-      for (int u = 0; u < ROWS_UNROLL; ++u) {
-        if (row + u * rl >= s.row1) continue;
-        float e[CPT];
-        residual_row<RP, CPT>(xv[u], cv[u], qreg, e);
+        for (int u = 0; u < ROWS_UNROLL; ++u) {
+          const int rr = row + u * rl;
+          if (rr >= sb1) continue;
+          float e[CPT];
+          residual_row_s<RP, CPT>(xv[u], s_c + (rr - sb0) * RP, qreg, e);
 #pragma unroll
-        for (int i = 0; i < CPT; ++i) {
-          if (col + i < p.n) {
-            unsigned short key = __bfloat16_as_ushort(__float2bfloat16_rn(e[i])) & 0x7FFF;
-            atomicAdd(&sh_hist[key], 1u);
+          for (int i = 0; i < CPT; ++i) {
+            if (col + i < p.n) {
+              unsigned short key = __bfloat16_as_ushort(__float2bfloat16_rn(e[i])) & 0x7FFF;
+              atomicAdd(&sh_hist[key], 1u);
+            }
           }
         }
       }
@@ -192,8 +241,12 @@ __global__ void __launch_bounds__(1024) residual_scan_kernel(const SelectParams 
   unsigned int sum = 0;
   int my_max = -1;
 #pragma unroll
+  for (int v = 0; v < PER / 4; ++v) {  // 32 bins = eight 16-byte loads, all issued before the first use
+    const uint4 raw = reinterpret_cast<const uint4*>(gh + t * PER)[v];
+    local[4 * v] = raw.x; local[4 * v + 1] = raw.y; local[4 * v + 2] = raw.z; local[4 * v + 3] = raw.w;
+  }
+#pragma unroll
   for (int i = 0; i < PER; ++i) {
-    local[i] = gh[t * PER + i];
     sum += local[i];
     if (local[i]) my_max = t * PER + i;
   }
@@ -246,7 +299,7 @@ __global__ void residual_scale_kernel(const SelectParams p) {
   }
 }
 
-constexpr int STAGE_CAP = 12288;  // staged (index, value) pairs per CTA between flushes
+constexpr int WARP_CAP = 768;  // staged (index, value) pairs per warp between flushes (16 warps: 120 KB)
 
 __device__ __forceinline__ void emit_entry(const SelectParams& p, int o, long long flat, unsigned short bits16,
                                            float inv_scale) {
@@ -261,94 +314,139 @@ __device__ __forceinline__ void emit_entry(const SelectParams& p, int o, long lo
   }
 }
 
+// bf16 bits of one residual entry, with exactly the arithmetic of residual_row_s (same operands, same order).
+template <int RP>
+__device__ __forceinline__ unsigned short residual_bits_at(const SelectParams& p, const float* crow, int rr, int c) {
+  float acc = 0.f;
+  const __nv_bfloat16* qrow = p.q + static_cast<size_t>(c) * p.r;
+#pragma unroll
+  for (int j = 0; j < RP; ++j) {
+    const float qv = (j < p.r) ? __bfloat162float(qrow[j]) : 0.f;
+    acc = fmaf(crow[j], qv, acc);
+  }
+  const float x = __bfloat162float(p.x[static_cast<size_t>(rr) * p.ldx + c]);
+  return __bfloat16_as_ushort(__float2bfloat16_rn(x - acc));
+}
+
+// Pass 2.  The row loop only marks candidates: one compare of |e| against the lower edge of the threshold bin per
+// element, collected in a 64-bit mask per thread.  The few marked entries (about the selection density) are then
+// recomputed one by one to get their exact bf16 value, ties of the threshold bin are arbitrated, and the survivors
+// are staged in the warp's own slice of shared memory (positions from a warp prefix sum, the running count lives
+// in a register that all lanes agree on) and copied out with one global atomic per flush.  Warps never wait for
+// one another inside the loop.
 template <int RP>
 __global__ void __launch_bounds__(512, 1) residual_compact_kernel(const SelectParams p, int ctn, int rl) {
   constexpr int CPT = 64 / RP;
+  constexpr unsigned FULL = 0xffffffffu;
   extern __shared__ unsigned char sh_raw[];
-  long long* st_idx = reinterpret_cast<long long*>(sh_raw);
-  unsigned short* st_val = reinterpret_cast<unsigned short*>(st_idx + STAGE_CAP);
-  __shared__ int st_count, st_base;
+  const int nwarps = blockDim.x >> 5, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  long long* st_idx_all = reinterpret_cast<long long*>(sh_raw);
+  unsigned short* st_val_all = reinterpret_cast<unsigned short*>(st_idx_all + static_cast<size_t>(nwarps) * WARP_CAP);
+  float* s_c = reinterpret_cast<float*>(sh_raw + static_cast<size_t>(16) * WARP_CAP * 10);
+  long long* st_idx = st_idx_all + static_cast<size_t>(warp) * WARP_CAP;
+  unsigned short* st_val = st_val_all + static_cast<size_t>(warp) * WARP_CAP;
   const Slab s = slab_of(p);
   const int thr = p.thr_bin[s.chunk];
   const int need = p.thr_need[s.chunk];
   const int quota = p.quota[s.chunk];
   const int obase = p.out_offset[s.chunk];
   const float inv_scale = 1.f / *p.out_scale;
-  if (threadIdx.x == 0) st_count = 0;
-  __syncthreads();
+  // every value that rounds to a magnitude >= thr is >= the midpoint between thr and the bf16 below it; values at
+  // the midpoint itself may round down and are sorted out when the candidate is recomputed
+  const float cut = thr > 0 ? 0.5f * (bf16_bits_to_float(static_cast<unsigned short>(thr)) + bf16_bits_to_float(static_cast<unsigned short>(thr - 1))) : 0.f;
   const int ct = threadIdx.x % ctn, lane_row = threadIdx.x / ctn;
+  int wcnt = 0;  // entries staged by this warp (same value in every lane)
 
-  // Copy the staged entries out with one global atomic for the whole batch.  Called by every
-  // thread of the CTA (the decision is taken on a count read between two barriers).
-  auto flush = [&](int cnt) {
-    if (cnt > STAGE_CAP) cnt = STAGE_CAP;  // entries past the capacity were appended directly
-    if (threadIdx.x == 0) st_base = atomicAdd(&p.out_count[s.chunk], cnt);
-    __syncthreads();
-    const int base = st_base;
-    for (int i = threadIdx.x; i < cnt; i += blockDim.x)
+  auto flush = [&]() {  // whole warp
+    const int cnt = min(wcnt, WARP_CAP);
+    int base = 0;
+    if (lane == 0 && cnt > 0) base = atomicAdd(&p.out_count[s.chunk], cnt);
+    base = __shfl_sync(FULL, base, 0);
+    __syncwarp();
+    for (int i = lane; i < cnt; i += 32)
       if (base + i < quota) emit_entry(p, obase + base + i, st_idx[i], st_val[i], inv_scale);
-    __syncthreads();
-    if (threadIdx.x == 0) st_count = 0;
-    __syncthreads();
+    __syncwarp();
+    wcnt = 0;
   };
 
-  for (int cb = 0; cb < p.n; cb += ctn * CPT) {
-    const int col = cb + ct * CPT;
-    const bool active = (col < p.n) && (lane_row < rl);
-    float qreg[CPT][RP];
-    if (active) load_q<RP, CPT>(p.q, p.r, col, p.n, qreg);
-    const int step = rl * ROWS_UNROLL;
-    const int iters = (s.row1 - s.row0 + step - 1) / step;  // uniform across the CTA
-    for (int it = 0; it < iters; ++it) {
-      __syncthreads();
-      const int staged = st_count;
-      __syncthreads();
-      if (staged > STAGE_CAP / 2) flush(staged);
-      const int row = s.row0 + it * step + lane_row;
-      if (active) {
+  for (int sb0 = s.row0; sb0 < s.row1; sb0 += CS_ROWS) {
+    const int sb1 = min(s.row1, sb0 + CS_ROWS);
+    stage_coeff<RP>(p.c, p.r, sb0, sb1, s_c);
+    for (int cb = 0; cb < p.n; cb += ctn * CPT) {
+      const int col = cb + ct * CPT;
+      const bool active = (col < p.n) && (lane_row < rl);
+      float qreg[CPT][RP];
+      if (active) load_q<RP, CPT>(p.q, p.r, col, p.n, qreg);
+      const int step = rl * ROWS_UNROLL;
+      const int iters = (sb1 - sb0 + step - 1) / step;  // the same for every thread: the warp votes below stay converged
+      for (int it = 0; it < iters; ++it) {
+        if (wcnt > WARP_CAP / 2) flush();
+        const int row = sb0 + it * step + lane_row;
         XVec<CPT> xv[ROWS_UNROLL];
-        CVec<RP> cv[ROWS_UNROLL];
 #pragma unroll
         for (int u = 0; u < ROWS_UNROLL; ++u) {
           const int rr = row + u * rl;
-          if (rr < s.row1) {
-            xv[u] = load_x<CPT>(p.x + static_cast<size_t>(rr) * p.ldx, col, p.n);
-            cv[u] = load_c<RP>(p.c + static_cast<size_t>(rr) * p.r, p.r);
+          if (active && rr < sb1) xv[u] = load_x<CPT>(p.x + static_cast<size_t>(rr) * p.ldx, col, p.n);
+        }
+        unsigned long long marks = 0;  // bit u * CPT + i: entry (row + u * rl, col + i) may belong to the selection
+#pragma unroll
+        for (int u = 0; u < ROWS_UNROLL; ++u) {
+          const int rr = row + u * rl;
+          if (active && rr < sb1) {
+            float e[CPT];
+            residual_row_s<RP, CPT>(xv[u], s_c + (rr - sb0) * RP, qreg, e);
+#pragma unroll
+            for (int i = 0; i < CPT; ++i)
+              if (col + i < p.n && !(fabsf(e[i]) < cut)) marks |= 1ull << (u * CPT + i);
           }
         }
-#pragma unroll
-        for (int u = 0; u < ROWS_UNROLL; ++u) {
-          const int rr = row + u * rl;
-          if (rr >= s.row1) continue;
-          float e[CPT];
-          residual_row<RP, CPT>(xv[u], cv[u], qreg, e);
-#pragma unroll
-          for (int i = 0; i < CPT; ++i) {
-            if (col + i >= p.n) continue;
-            const unsigned short bits16 = __bfloat16_as_ushort(__float2bfloat16_rn(e[i]));
-            const int key = bits16 & 0x7FFF;
+        if (__any_sync(FULL, marks != 0)) {
+          // exact value of every candidate; entries below the bin and surplus ties are dropped
+          unsigned long long todo = marks;
+          while (todo) {
+            const int b = __ffsll(static_cast<long long>(todo)) - 1;
+            todo &= todo - 1;
+            const int rr = row + (b / CPT) * rl, c = col + (b % CPT);
+            const int key = residual_bits_at<RP>(p, s_c + (rr - sb0) * RP, rr, c) & 0x7FFF;
             bool take = key > thr;
-            if (!take && key == thr && need > 0) take = atomicAdd(&p.tie_count[s.chunk], 1) < need;
-            if (take) {
-              const long long flat = static_cast<long long>(rr) * p.n + (col + i);
-              const int slot = atomicAdd(&st_count, 1);
-              if (slot < STAGE_CAP) {
-                st_idx[slot] = flat;
-                st_val[slot] = bits16;
-              } else {  // staging buffer full (very dense selection): append directly
-                const int o = atomicAdd(&p.out_count[s.chunk], 1);
-                if (o < quota) emit_entry(p, obase + o, flat, bits16, inv_scale);
-              }
+            if (!take && key == thr && need > 0) {
+              // ties are equal values: the first `need` askers win; stop asking once the bin is full
+              if (*reinterpret_cast<volatile int*>(&p.tie_count[s.chunk]) < need) take = atomicAdd(&p.tie_count[s.chunk], 1) < need;
             }
+            if (!take) marks &= ~(1ull << b);
           }
+          const int mine = __popcll(marks);
+          int incl = mine;
+#pragma unroll
+          for (int off = 1; off < 32; off <<= 1) {
+            const int v = __shfl_up_sync(FULL, incl, off);
+            if (lane >= off) incl += v;
+          }
+          const int total = __shfl_sync(FULL, incl, 31);
+          int pos = wcnt + incl - mine;
+          todo = marks;
+          while (todo) {
+            const int b = __ffsll(static_cast<long long>(todo)) - 1;
+            todo &= todo - 1;
+            const int rr = row + (b / CPT) * rl, c = col + (b % CPT);
+            const unsigned short bits16 = residual_bits_at<RP>(p, s_c + (rr - sb0) * RP, rr, c);
+            const long long flat = static_cast<long long>(rr) * p.n + c;
+            if (pos < WARP_CAP) {
+              st_idx[pos] = flat;
+              st_val[pos] = bits16;
+            } else {  // this warp's staging slice is full (very dense selection): append directly
+              const int o = atomicAdd(&p.out_count[s.chunk], 1);
+              if (o < quota) emit_entry(p, obase + o, flat, bits16, inv_scale);
+            }
+            ++pos;
+          }
+          wcnt += total;
+          __syncwarp();
         }
       }
     }
   }
-  __syncthreads();
-  const int staged = st_count;
-  __syncthreads();
-  if (staged > 0) flush(staged);
+  flush();
 }
 
 // e[i] = X[idx] - C[row] . Q[col] for an explicit index list (uniform / block-sparse selectors).
@@ -400,13 +498,13 @@ static int launch_select(const SelectParams& p, int phase, cudaStream_t st) {
   if (phase == 0) {
     static bool cfg = false;
     if (!cfg) {
-      cudaError_t e = cudaFuncSetAttribute(residual_hist_kernel<RP>, cudaFuncAttributeMaxDynamicSharedMemorySize, NBINS * 4);
+      cudaError_t e = cudaFuncSetAttribute(residual_hist_kernel<RP>, cudaFuncAttributeMaxDynamicSharedMemorySize, NBINS * 4 + CS_ROWS * RP * 4);
       if (e != cudaSuccess) return static_cast<int>(e);
       cfg = true;
     }
-    residual_hist_kernel<RP><<<grid, threads, NBINS * 4, st>>>(p, ctn, rl);
+    residual_hist_kernel<RP><<<grid, threads, NBINS * 4 + CS_ROWS * RP * 4, st>>>(p, ctn, rl);
   } else {
-    const int smem = STAGE_CAP * (8 + 2);
+    const int smem = 16 * WARP_CAP * (8 + 2) + CS_ROWS * RP * 4;
     static bool cfg = false;
     if (!cfg) {
       cudaError_t e = cudaFuncSetAttribute(residual_compact_kernel<RP>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);

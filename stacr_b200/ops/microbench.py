@@ -1,0 +1,139 @@
+"""Isolated timings of the sm_100a kernels, with roofline fractions against measured peaks.
+
+    python -m stacr_b200.ops.microbench gemm   [--m 8192 --n 8192 --k 2048 --bn 256 --iters 20]
+    python -m stacr_b200.ops.microbench stacr  [--rows 8192 --features 8192 --out 2048 --rank 8]
+    python -m stacr_b200.ops.microbench optim  [--numel 268435456]
+
+Each case runs warm-up launches, then ``--iters`` timed launches between CUDA events; operands are larger than the
+126 MB L2 at the default sizes (the ``stacr`` and ``optim`` cases stream several hundred MB per launch; the default
+``gemm`` case reads 160 MB).  ``--iters 1 --warmup 1`` makes a run small enough to sit under a profiler.
+Fractions are reported against ``MEASURED_PEAKS.json`` at the repository root when present (fields ``hbm_gbs`` and
+``bf16_tflops``) and against 6650 GB/s / 1590 TFLOP/s otherwise; the line says which.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+from pathlib import Path
+
+import torch
+
+
+def peaks() -> dict:
+    path = Path(__file__).resolve().parents[2] / "MEASURED_PEAKS.json"
+    if path.is_file():
+        raw = json.loads(path.read_text())
+        return {"hbm_gbs": float(raw["hbm_gbs"]), "bf16_tflops": float(raw["bf16_tflops"]), "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
+
+
+def timed(fn, iters: int, warmup: int) -> float:
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for _ in range(iters):
+        fn()
+    b.record()
+    torch.cuda.synchronize()
+    return a.elapsed_time(b) / iters
+
+
+def case_gemm(args, pk) -> list:
+    from .gemm import gemm
+
+    m, n, k = args.m, args.n, args.k
+    a = torch.randn(m, k, device="cuda").bfloat16()
+    b = torch.randn(n, k, device="cuda").bfloat16()
+    out = []
+    flops = 2.0 * m * n * k
+    ms = timed(lambda: gemm(a, b, bn=args.bn), args.iters, args.warmup)
+    out.append({"kernel": "gemm_bf16_kernel", "shape": [m, n, k], "bn": args.bn, "ms": ms, "tflops": flops / ms / 1e9,
+                f"frac_of_{pk['source']}_bf16": flops / ms / 1e9 / pk["bf16_tflops"]})
+    if not args.only_ours:
+        ms = timed(lambda: torch.matmul(a, b.t()), args.iters, args.warmup)
+        out.append({"kernel": "cublas (torch.matmul)", "shape": [m, n, k], "ms": ms, "tflops": flops / ms / 1e9})
+    return out
+
+
+def case_stacr(args, pk) -> list:
+    from . import stacr_ops
+    from .basis import oja_step_kernels
+
+    rows, n, o, r = args.rows, args.features, args.out, args.rank
+    base = torch.randn(rows, r, device="cuda") @ torch.randn(r, n, device="cuda")
+    x = (base + 0.3 * torch.randn(rows, n, device="cuda")).bfloat16()
+    del base
+    q = torch.linalg.qr(torch.randn(n, r, device="cuda")).Q.contiguous()
+    qb = q.bfloat16().contiguous()
+    qt = stacr_ops.pad_basis_transpose(qb)
+    c = stacr_ops.project(x, qt)[:, :r].bfloat16().contiguous()
+    k = int(round(args.budget * rows * n))
+    dy = torch.randn(rows, o, device="cuda").bfloat16()
+    x_bytes, dy_bytes, dw_bytes = rows * n * 2, rows * o * 2, o * n * 4
+    out = []
+
+    def add(name, fn, bytes_moved):
+        ms = timed(fn, args.iters, args.warmup)
+        out.append({"kernel": name, "shape": [rows, n, o], "ms": ms, "algorithmic_GB": bytes_moved / 1e9, "GBs": bytes_moved / ms / 1e6,
+                    f"frac_of_{pk['source']}_hbm": bytes_moved / ms / 1e6 / pk["hbm_gbs"]})
+
+    sel = args.only or ""
+    if sel in ("", "project"):
+        add("project (gemm_bf16_kernel, N=16)", lambda: stacr_ops.project(x, qt), x_bytes)
+    if sel in ("", "topk"):
+        add("residual top-k (hist+scan+scale+compact)", lambda: stacr_ops.residual_topk(x, c, qb, [k], rows, 8, torch.int32), 2 * x_bytes)
+    if sel in ("", "oja"):
+        add("oja_update (+ X^T Y gemm)", lambda: oja_step_kernels(q, x, 0.01), 2 * x_bytes)
+    if sel in ("", "dw"):
+        idx, val, scale = stacr_ops.residual_topk(x, c, qb, [k], rows, 8, torch.int32)
+        add("weight_grad (bucket + dw_fused)", lambda: stacr_ops.weight_grad(dy, c, q, (idx, val, scale, 8, k), o, n, False, torch.float32),
+            dy_bytes + dw_bytes + k * o * 2)
+        add("weight_grad low-rank only", lambda: stacr_ops.weight_grad(dy, c, q, None, o, n, False, torch.float32), dy_bytes + dw_bytes)
+    return out
+
+
+def case_optim(args, pk) -> list:
+    from ..optim import AdamW8bit
+
+    p = torch.nn.Parameter(torch.randn(args.numel, device="cuda"))
+    p.grad = torch.randn_like(p) * 1e-3
+    opt = AdamW8bit([p], lr=1e-4, bf16_shadow=True)
+    ms = timed(opt.step, args.iters, args.warmup)
+    moved = args.numel * (4 + 4 + 4 + 2 + 2 + 2 + 2)  # param r/w, grad r, 8-bit m and v r/w, bf16 shadow w
+    return [{"kernel": "adamw_8bit_kernel", "numel": args.numel, "ms": ms, "algorithmic_GB": moved / 1e9, "GBs": moved / ms / 1e6,
+             f"frac_of_{pk['source']}_hbm": moved / ms / 1e6 / pk["hbm_gbs"]}]
+
+
+def main(argv=None) -> int:
+    parser = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
+    parser.add_argument("case", choices=("gemm", "stacr", "optim"))
+    parser.add_argument("--iters", type=int, default=20)
+    parser.add_argument("--warmup", type=int, default=5)
+    parser.add_argument("--m", type=int, default=8192)
+    parser.add_argument("--n", type=int, default=8192)
+    parser.add_argument("--k", type=int, default=2048)
+    parser.add_argument("--bn", type=int, default=256)
+    parser.add_argument("--only-ours", action="store_true")
+    parser.add_argument("--rows", type=int, default=8192)
+    parser.add_argument("--features", type=int, default=8192)
+    parser.add_argument("--out", type=int, default=2048)
+    parser.add_argument("--rank", type=int, default=8)
+    parser.add_argument("--budget", type=float, default=0.005)
+    parser.add_argument("--only", choices=("project", "topk", "oja", "dw"))
+    parser.add_argument("--numel", type=int, default=1 << 28)
+    args = parser.parse_args(argv)
+    from . import _lib
+
+    pk = peaks()
+    rows = {"gemm": case_gemm, "stacr": case_stacr, "optim": case_optim}[args.case](args, pk)
+    _lib.check_status()
+    for row in rows:
+        print(json.dumps(row))
+    return 0
+
+
+if __name__ == "__main__":
+    raise SystemExit(main())

@@ -146,6 +146,16 @@ def oja_update(basis_fp32, g, y, rows: int, lr: float):
     return q_out, qb, qt
 
 
+_PLAN_TARGET = None
+
+
+def _plan_target() -> int:
+    global _PLAN_TARGET
+    if _PLAN_TARGET is None:
+        _PLAN_TARGET = int(_lib.load().sb_dw_plan_target())
+    return _PLAN_TARGET
+
+
 def weight_grad(
     dy: torch.Tensor,
     coeff: torch.Tensor,
@@ -155,16 +165,21 @@ def weight_grad(
     in_features: int,
     transposed: bool,
     out_dtype: torch.dtype,
-) -> torch.Tensor:
+    sink=None,
+):
     """``dW = (dY^T C) Q^T + dY^T S`` without rebuilding the dense input.
 
-    ``residual`` is ``None`` or ``(idx, values, scale, bits, length)``.
+    ``residual`` is ``None`` or ``(idx, values, scale, bits, length)``.  With ``sink`` (see
+    ``parallel.ddp.GradSink``) the gradient is not returned: the kernel adds it straight into the flat gradient
+    buffer, or, across data-parallel ranks, into the copy of the rank that owns each slice (reduce-scatter in the
+    epilogue over NVLink peer memory); the function then returns ``None``.
     """
     dev = dy.device
     rows = dy.shape[0]
     r = coeff.shape[1]
     t = at_b(dy, transpose_pad(coeff))  # [O, rpad] fp32
-    colptr = rows_s = vals_s = None
+    colptr = rows_s = vals_s = plan = None
+    nnz = 0
     if residual is not None and residual[4] > 0:
         idx, values, scale, bits, length = residual
         counts = torch.zeros(in_features, dtype=torch.int32, device=dev)
@@ -172,23 +187,37 @@ def weight_grad(
         colptr = torch.empty(in_features + 1, dtype=torch.int32, device=dev)
         rows_s = torch.empty(length, dtype=torch.int32, device=dev)
         vals_s = torch.empty(length, dtype=torch.float32, device=dev)
+        groups = (in_features + 7) // 8
+        # work plan of the gradient kernel: pieces per strip of 8 features, item count, (strip, piece) items
+        plan = torch.empty(groups + 2 + 2 * (length // _plan_target()), dtype=torch.int32, device=dev)
+        nnz = length
         is32 = idx.dtype == torch.int32
         rc = _lib.load().sb_residual_bucket(
             _lib.ptr(idx if is32 else None), _lib.ptr(None if is32 else idx), c_ll(length), c_int(in_features), _lib.ptr(values),
             c_int(bits), _lib.ptr(scale), _lib.ptr(counts), _lib.ptr(cursor), _lib.ptr(colptr), _lib.ptr(rows_s), _lib.ptr(vals_s),
-            _lib.stream_ptr(),
+            _lib.ptr(plan), _lib.stream_ptr(),
         )
         _lib.check_rc(rc, "sb_residual_bucket")
         _lib.count(3)
+    if sink is not None:
+        rc = _lib.load().sb_dw_fused_sink(
+            _lib.ptr(t), c_int(t.stride(0)), _lib.ptr(basis_fp32), c_int(r), _lib.ptr(dy), c_int(dy.stride(0)), _lib.ptr(colptr),
+            _lib.ptr(rows_s), _lib.ptr(vals_s), c_int(out_features), c_int(in_features), c_int(int(transposed)), _lib.ptr(sink.flat),
+            c_int(sink.mode), ctypes.c_float(sink.scale), c_ll(sink.param_off), c_ll(sink.region_lo), c_ll(sink.per_vecs), c_int(sink.world),
+            _lib.ptr(sink.peer_ptrs), _lib.ptr(plan), c_ll(nnz), _lib.stream_ptr(),
+        )
+        _lib.check_rc(rc, "sb_dw_fused_sink")
+        _lib.count(2 if nnz >= _plan_target() else 1)
+        return None
     shape = (in_features, out_features) if transposed else (out_features, in_features)
     out = torch.empty(shape, dtype=out_dtype, device=dev)
     rc = _lib.load().sb_dw_fused(
         _lib.ptr(t), c_int(t.stride(0)), _lib.ptr(basis_fp32), c_int(r), _lib.ptr(dy), c_int(dy.stride(0)), _lib.ptr(colptr),
         _lib.ptr(rows_s), _lib.ptr(vals_s), c_int(out_features), c_int(in_features), c_int(int(transposed)),
-        c_int(int(out_dtype == torch.bfloat16)), _lib.ptr(out), _lib.stream_ptr(),
+        c_int(int(out_dtype == torch.bfloat16)), _lib.ptr(out), _lib.ptr(plan), c_ll(nnz), _lib.stream_ptr(),
     )
     _lib.check_rc(rc, "sb_dw_fused")
-    _lib.count(1)
+    _lib.count(2 if (nnz >= _plan_target() and out_dtype != torch.bfloat16) else 1)
     return out
 
 

@@ -19,6 +19,8 @@ rank tracks the subspace of its own data shard, as the reference prescribes for 
 
 from __future__ import annotations
 
+import contextlib
+
 import os
 from typing import Iterable
 
@@ -53,12 +55,48 @@ def broadcast_parameters(model: nn.Module, src: int = 0) -> None:
         dist.broadcast(p.data, src)
 
 
+class GradSink:
+    """Where a compressed layer's weight-gradient kernel delivers its result (see ``ops.stacr_ops.weight_grad``).
+
+    ``mode`` 1 adds into this rank's flat buffer; ``mode`` 2 adds each 16-byte element into the copy of the rank that
+    owns its slice of the parameter's slot (the reduce-scatter half of the all-reduce, done inside the kernel over
+    NVLink peer memory).  ``done()`` tells the synchroniser that the parameter's contribution is enqueued.
+    """
+
+    def __init__(self, sync: "GradSync", index: int, offset: int, numel_padded: int):
+        self.sync, self.index = sync, index
+        self.flat = sync.flat
+        self.param_off = offset
+        self.region_lo = offset
+        self.region_hi = offset + numel_padded
+        self.world = sync.world
+        self.scale = 1.0
+        if sync.backend == "symm":
+            self.mode = 2
+            self.per_vecs = sync._symm.slice_vecs(offset, offset + numel_padded)
+            self.peer_ptrs = sync._symm.peer_ptrs
+        else:
+            self.mode, self.per_vecs, self.peer_ptrs = 1, 1, None
+
+    def done(self) -> None:
+        self.sync._fused_done(self.index)
+
+
 class GradSync:
-    """Flat-buffer, bucketed, overlapped gradient averaging for one model replica."""
+    """Flat-buffer, bucketed, overlapped gradient averaging for one model replica.
+
+    ``fused`` names parameters (the weights of compressed layers) whose gradient kernel writes into the flat buffer
+    itself: they get a :class:`GradSink` as ``param._sb_grad_sink``, are left out of the hook-driven buckets, and are
+    finished by an all-gather of owner slices (symmetric-memory backend) or one all-reduce (other backends).
+    """
 
     def __init__(self, params: Iterable[nn.Parameter], *, bucket_mb: float = 256.0, backend: str = "auto",
-                 group=None, average: bool = True):
-        self.params = [p for p in params if p.requires_grad]
+                 group=None, average: bool = True, fused: Iterable[nn.Parameter] = ()):
+        fused_ids = {id(p) for p in fused if p.requires_grad}
+        ordered = [p for p in params if p.requires_grad]
+        # fused parameters first: their slots form the head of the flat buffer
+        self.params = [p for p in ordered if id(p) in fused_ids] + [p for p in ordered if id(p) not in fused_ids]
+        self.n_fused = sum(1 for p in self.params if id(p) in fused_ids)
         if not self.params:
             raise ValueError("GradSync needs at least one trainable parameter")
         self.group = group
@@ -86,10 +124,10 @@ class GradSync:
         hi = cursor
         lo = hi
         members: list[int] = []
-        for idx in range(len(self.params) - 1, -1, -1):
+        for idx in range(len(self.params) - 1, self.n_fused - 1, -1):
             lo = offsets[idx]
             members.append(idx)
-            if hi - lo >= limit or idx == 0:
+            if hi - lo >= limit or idx == self.n_fused:
                 b = len(self.buckets)
                 self.buckets.append((lo, hi))
                 for m in members:
@@ -102,6 +140,15 @@ class GradSync:
         self.reductions = 0
         self._hooks = [p.register_post_accumulate_grad_hook(self._make_hook(i)) for i, p in enumerate(self.params)]
         self._total = total
+        self._offsets = offsets
+        self._syncing = True
+        self.sinks: list[GradSink] = []
+        self._fused_state = [0] * self.n_fused       # 0 idle, 1 delivered by the kernel, 2 accumulated by autograd
+        for i in range(self.n_fused):
+            p = self.params[i]
+            sink = GradSink(self, i, offsets[i], (p.numel() + 3) // 4 * 4)
+            p._sb_grad_sink = sink
+            self.sinks.append(sink)
 
     # ------------------------------------------------------------------ backend plumbing
     def _pick_backend(self, backend: str, dev: torch.device) -> str:
@@ -137,7 +184,14 @@ class GradSync:
 
     # ------------------------------------------------------------------ hooks
     def _make_hook(self, index: int):
+        if index < self.n_fused:
+            def fused_hook(param):
+                self._fused_state[index] = 2      # autograd accumulated a dense gradient locally (layer ran uncompressed)
+            return fused_hook
+
         def hook(param):
+            if not self._syncing:
+                return
             b = self._bucket_of[index]
             self._pending[b] -= 1
             if self._pending[b] == 0:
@@ -154,10 +208,47 @@ class GradSync:
         with torch.cuda.stream(self._stream):
             self._reduce(lo, hi)
 
+    # ------------------------------------------------------------------ fused parameters
+    def _fused_done(self, index: int) -> None:
+        if self._fused_state[index] == 0:
+            self._fused_state[index] = 1
+        if self._syncing and self.world > 1:
+            self._finish_fused(index)
+
+    def _finish_fused(self, index: int) -> None:
+        state = self._fused_state[index]
+        if state in (0, 3) or self.world == 1:
+            return
+        sink = self.sinks[index]
+        self._fused_state[index] = 3
+        self.reductions += 1
+        cur = torch.cuda.current_stream(self.device) if self._stream is not None else None
+        if cur is not None:
+            self._stream.wait_stream(cur)
+        ctx = torch.cuda.stream(self._stream) if self._stream is not None else contextlib.nullcontext()
+        with ctx:
+            if self.backend == "symm" and state == 1:
+                self._symm.all_gather_slices_(sink.region_lo, sink.region_hi, average=self.average)
+            else:
+                self._reduce(sink.region_lo, sink.region_hi)
+                self.reductions -= 1
+
+    @contextlib.contextmanager
+    def no_sync(self):
+        """Gradient accumulation: backward passes inside do not start reductions; ``finish()`` after the last one does."""
+        self._syncing = False
+        try:
+            yield
+        finally:
+            self._syncing = True
+
     # ------------------------------------------------------------------ step protocol
     def zero_grad(self) -> None:
         """Clear the flat buffer (one memset) and re-arm the buckets.  Call instead of ``optimizer.zero_grad``."""
         self.flat.zero_()
+        if self.n_fused and self.backend == "symm":
+            self._symm.barrier()   # no peer may add into this buffer before it is cleared
+        self._fused_state = [0] * self.n_fused
         self._pending = list(self._size)
         self._launched = 0
         for p in self.params:
@@ -170,6 +261,10 @@ class GradSync:
             if left > 0:
                 self._pending[b] = 0
                 self._launch(b)
+        for i in range(self.n_fused):
+            if self._fused_state[i] == 0 and self.backend == "symm":
+                self._fused_state[i] = 1   # unused this step on this rank: peers may still have added into our slice
+            self._finish_fused(i)
         if self._stream is not None:
             torch.cuda.current_stream(self.device).wait_stream(self._stream)
 
@@ -177,6 +272,9 @@ class GradSync:
         for h in self._hooks:
             h.remove()
         self._hooks = []
+        for p in self.params[:self.n_fused]:
+            if hasattr(p, "_sb_grad_sink"):
+                del p._sb_grad_sink
 
 
 def all_reduce_mean_(tensor: torch.Tensor, group=None) -> torch.Tensor:

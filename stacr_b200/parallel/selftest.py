@@ -37,6 +37,47 @@ def _time(fn, iters=10):
     return float(t)
 
 
+def _fused_dw_check(buf, rank, world, dev, report) -> bool:
+    """Weight-gradient kernel with the reduce-scatter in its epilogue + all-gather of owner slices vs NCCL all-reduce."""
+    from ..ops import stacr_ops
+
+    class Sink:
+        pass
+
+    rows, n_in, n_out, r = 2048, 1024, 1536, 8
+    gen = torch.Generator(device=dev).manual_seed(1000 + rank)
+    x = (torch.randn(rows, r, device=dev, generator=gen) @ torch.randn(r, n_in, device=dev, generator=gen)
+         + 0.3 * torch.randn(rows, n_in, device=dev, generator=gen)).bfloat16()
+    q = torch.linalg.qr(torch.randn(n_in, r, device=dev, generator=gen)).Q.contiguous()
+    qb = q.bfloat16().contiguous()
+    c = stacr_ops.project(x, stacr_ops.pad_basis_transpose(qb))[:, :r].bfloat16().contiguous()
+    k = int(round(0.005 * rows * n_in))
+    res = stacr_ops.residual_topk(x, c, qb, [k], rows, 8, torch.int32) + (8, k)
+    dy = torch.randn(rows, n_out, device=dev, generator=gen).bfloat16()
+    want = stacr_ops.weight_grad(dy, c, q, res, n_out, n_in, False, torch.float32)
+    dist.all_reduce(want)
+    want /= world
+    off, numel = 4096, n_out * n_in
+    good = True
+    for mm in ([False, True] if buf.multicast_ptr else [False]):
+        buf.use_multimem = mm
+        buf.tensor.zero_()
+        buf.barrier()                      # every copy is cleared before any rank adds into it
+        sink = Sink()
+        sink.flat, sink.mode, sink.scale, sink.param_off, sink.region_lo, sink.world = buf.tensor, 2, 1.0, off, off, world
+        sink.per_vecs, sink.peer_ptrs = buf.slice_vecs(off, off + numel), buf.peer_ptrs
+        stacr_ops.weight_grad(dy, c, q, res, n_out, n_in, False, torch.float32, sink=sink)
+        buf.all_gather_slices_(off, off + numel, average=True)
+        torch.cuda.synchronize()
+        _lib.check_status(dev)
+        err = float((buf.tensor[off:off + numel].view_as(want) - want).abs().max())
+        clean = float(buf.tensor[:off].abs().max()) == 0.0 and float(buf.tensor[off + numel:off + numel + 4096].abs().max()) == 0.0
+        report[f"fused_dw_{'multimem' if mm else 'p2p'}_max_err"] = err
+        good &= err < 1e-4 * max(1.0, float(want.abs().max())) and clean
+        dist.barrier()
+    return good
+
+
 def main() -> int:
     rank, world, local = init_distributed("nccl")
     dev = torch.device("cuda", local)
@@ -74,6 +115,7 @@ def main() -> int:
         ms = _time(lambda: buf.all_reduce_(0, n, average=False))
         report[f"{name}_ms_256MB"] = ms
         report[f"{name}_busbw_GBs"] = 2 * (world - 1) / world * n * 4 / ms / 1e6
+    ok &= _fused_dw_check(buf, rank, world, dev, report)
     plain = torch.randn(n, device=dev)
     ms = _time(lambda: dist.all_reduce(plain))
     report["nccl_ms_256MB"] = ms

@@ -82,3 +82,35 @@ class SymmetricBuffer:
         )
         _lib.check_rc(rc, "sb_allreduce")
         _lib.count(1)
+
+    def _call(self, fn, lo: int, hi: int, scale: float, name: str, multicast: bool) -> None:
+        self._epoch += 1
+        rc = fn(
+            _lib.ptr(self._peer_ptrs), _lib.ptr(self._pad_ptrs), ctypes.c_ulonglong(self.multicast_ptr if multicast else 0), ctypes.c_int(self.rank),
+            ctypes.c_int(self.world), ctypes.c_longlong(lo), ctypes.c_longlong(hi), ctypes.c_float(scale), ctypes.c_int(self._epoch),
+            ctypes.c_int(_lib.sm_count(self.tensor.device)), _lib.ptr(_lib.status_word(self.tensor.device)), _lib.stream_ptr(),
+        )
+        _lib.check_rc(rc, name)
+        _lib.count(1)
+
+    def all_gather_slices_(self, lo: int, hi: int, average: bool = True) -> None:
+        """Every rank broadcasts its 1/W slice of ``tensor[lo:hi]`` to all ranks (second half of an all-reduce whose
+        reduce-scatter was done by the producing kernels adding into the owner's copy)."""
+        self._call(_lib.load().sb_allgather_slices, lo, hi, 1.0 / self.world if average else 1.0, "sb_allgather_slices", self.use_multimem)
+
+    def barrier(self) -> None:
+        """Cross-rank barrier as a kernel on the current stream (bounded wait; a late peer sets the status word)."""
+        self._epoch += 1
+        rc = _lib.load().sb_rank_barrier(_lib.ptr(self._pad_ptrs), ctypes.c_int(self.rank), ctypes.c_int(self.world), ctypes.c_int(self._epoch),
+                                         _lib.ptr(_lib.status_word(self.tensor.device)), _lib.stream_ptr())
+        _lib.check_rc(rc, "sb_rank_barrier")
+        _lib.count(1)
+
+    @property
+    def peer_ptrs(self) -> torch.Tensor:
+        return self._peer_ptrs
+
+    def slice_vecs(self, lo: int, hi: int) -> int:
+        """16-byte elements per owner slice of ``[lo, hi)`` (the split the reduction kernels use)."""
+        vecs = (hi - lo) // 4
+        return max(1, (vecs + self.world - 1) // self.world)

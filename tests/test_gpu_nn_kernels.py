@@ -43,10 +43,11 @@ def test_gelu_forward_backward(form):
     torch.testing.assert_close(x.grad.float(), xr.grad, rtol=2e-2, atol=2e-2)
 
 
-def test_cross_entropy_loss_and_gradient():
+@pytest.mark.parametrize("rows,v", [(515, 50304), (252, 1024), (7, 8)])
+def test_cross_entropy_loss_and_gradient(rows, v):
+    """The small vocabularies leave most threads of a row's CTA without an element (their running max stays -inf)."""
     from stacr_b200.ops import nn_ops
 
-    rows, v = 515, 50304
     logits = (2 * torch.randn(rows, v, device="cuda")).bfloat16().requires_grad_(True)
     target = torch.randint(0, v, (rows,), device="cuda")
     target[::7] = -100

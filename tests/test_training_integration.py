@@ -236,3 +236,48 @@ def test_two_rank_gloo_gradient_sync_matches_single_process_mean(tmp_path):
             assert float(S.cosine_similarity(w, piece)) > 0.5, name
         else:
             torch.testing.assert_close(piece, w, rtol=1e-4, atol=1e-6, msg=name)
+
+
+_FUSED_WORKER = r'''
+import os, sys, torch, torch.distributed as dist
+sys.path.insert(0, os.environ["REPO"])
+import stacr_b200 as S
+from stacr_b200.models import build_model
+from stacr_b200.parallel import GradSync, broadcast_parameters, init_distributed
+rank, world, _ = init_distributed("gloo")
+g = torch.Generator().manual_seed(7)
+ids = torch.randint(0, 1024, (4, 32), generator=g)
+mine = ids[rank * 2:(rank + 1) * 2]
+results = []
+for fused in (False, True):
+    torch.manual_seed(5)
+    model = build_model("gpt-tiny", n_layer=1, resid_pdrop=0.0, embd_pdrop=0.0, attn_pdrop=0.0)
+    layers = S.apply_stacr(model, rank=4, residual_budget=0.01, turbo_after_step=None)
+    sync = GradSync(model.parameters(), bucket_mb=0.05, fused=[l.weight for l in layers] if fused else ())
+    assert sync.n_fused == (len(layers) if fused else 0)
+    S.set_step(layers, 0)
+    sync.zero_grad()
+    with sync.no_sync():
+        model(input_ids=mine, labels=mine).loss.backward()      # first micro-batch: nothing is reduced yet
+    assert sync.reductions == 0
+    model(input_ids=mine, labels=mine).loss.backward()
+    sync.finish()
+    results.append({n: p.grad.clone() for n, p in model.named_parameters()})
+    sync.close()
+for name, grad in results[0].items():
+    torch.testing.assert_close(results[1][name], grad, rtol=1e-5, atol=1e-7, msg=name)
+    other = [torch.zeros_like(grad) for _ in range(world)]
+    dist.all_gather(other, results[1][name].contiguous())
+    assert torch.equal(other[0], other[1]), name
+print("FUSED_OK", flush=True)
+dist.destroy_process_group()
+'''
+
+
+def test_two_rank_gloo_fused_parameter_slots_and_accumulation(tmp_path):
+    script = tmp_path / "worker_fused.py"
+    script.write_text(_FUSED_WORKER)
+    env = {**os.environ, "REPO": REPO, "MASTER_ADDR": "127.0.0.1", "MASTER_PORT": "29613"}
+    run = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
+                          "--master-port", "29613", str(script)], capture_output=True, text=True, env=env, timeout=240)
+    assert run.returncode == 0 and run.stdout.count("FUSED_OK") == 2, run.stdout[-2000:] + run.stderr[-2000:]
