@@ -111,6 +111,27 @@ def emit(payload):
 
 
 # ----------------------------------------------------------------------------------- this framework
+def kernel_table(torch, step, path, steps=2):
+    """Device time per kernel name over `steps` steps (torch.profiler / CUPTI), written as text.  Not part of any timed region."""
+    from torch.profiler import ProfilerActivity, profile
+
+    with profile(activities=[ProfilerActivity.CUDA]) as prof:
+        for i in range(steps):
+            step(i)
+        torch.cuda.synchronize()
+    rows = []
+    for e in prof.key_averages():
+        t = getattr(e, "device_time_total", None) or getattr(e, "cuda_time_total", 0)
+        if t:
+            rows.append((t / steps / 1e3, e.count // steps, e.key))
+    rows.sort(reverse=True)
+    total = sum(r[0] for r in rows)
+    with open(path, "w") as fh:
+        fh.write(f"kernel time per step: {total:.2f} ms over {sum(r[1] for r in rows)} launches\n")
+        for ms, n, name in rows[:60]:
+            fh.write(f"{ms:9.3f} ms {100 * ms / total:5.1f}% {n:6d}x  {name[:110]}\n")
+
+
 def run_ours(args):
     sys.path.insert(0, REPO)
     import torch
@@ -178,6 +199,8 @@ def run_ours(args):
         secs_e2e = timed_region(torch, dist, args.steps, step_e2e, world)
     _lib.check_status(dev)
     peak = torch.cuda.max_memory_allocated(dev)
+    if args.kernel_table and rank == 0:
+        kernel_table(torch, step_device, args.kernel_table)
     rows = batch * seq
     factor_bytes = sum(layer.stored_bytes(rows, 2)["total"] for layer in layers)
     dense_bytes = sum(rows * layer.in_features * 2 for layer in layers)
@@ -306,8 +329,9 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--comm", default="auto", choices=["auto", "symm", "nccl"], help="gradient all-reduce path (this framework)")
-    ap.add_argument("--fused-dw", default="on", choices=["on", "off"],
+    ap.add_argument("--fused-dw", default="off", choices=["on", "off"],
                     help="N > 1: compressed layers' weight-gradient kernels reduce-scatter in their epilogue over NVLink peer memory")
+    ap.add_argument("--kernel-table", metavar="FILE", help="after the timed regions, write per-kernel device times of two more steps to FILE")
     ap.add_argument("--small", action="store_true", help="tiny shape for smoke runs (not a benchmark number)")
     args = ap.parse_args()
     if args.gpus > 1 and "RANK" not in os.environ:

@@ -205,6 +205,64 @@ __global__ void __launch_bounds__(1024) oja_update_kernel(const float* q_in, con
 }
 
 
+// Upper Cholesky factor of an 8 x 8 Gram matrix and its inverse, entirely in the registers of one thread (every loop
+// has compile-time bounds, so the arrays never touch memory).  Unused trailing rows/columns (r < 8) are treated as
+// identity.  The result goes to rinv (shared, row stride RMAX).
+__device__ __forceinline__ bool chol_and_invert8_regs(const float* g_sh, float* rinv_sh, int r) {
+  float a[8][8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i)
+#pragma unroll
+    for (int j = 0; j < 8; ++j) a[i][j] = (i < r && j < r) ? g_sh[i * RMAX + j] : (i == j ? 1.f : 0.f);
+  bool ok = true;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    float d = a[i][i];
+#pragma unroll
+    for (int k = 0; k < 8; ++k)
+      if (k < i) d -= a[k][i] * a[k][i];
+    if (!(d > 1e-20f)) {
+      ok = false;
+      d = 1.f;
+    }
+    const float rii = sqrtf(d), inv = 1.f / rii;
+    a[i][i] = rii;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      if (j > i) {
+        float v = a[i][j];
+#pragma unroll
+        for (int k = 0; k < 8; ++k)
+          if (k < i) v -= a[k][i] * a[k][j];
+        a[i][j] = v * inv;
+      }
+    }
+  }
+  float x[8][8];  // R^-1, upper triangular, by back substitution column by column
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+#pragma unroll
+    for (int i = 7; i >= 0; --i) {
+      if (i > j) {
+        x[i][j] = 0.f;
+      } else if (i == j) {
+        x[i][j] = 1.f / a[j][j];
+      } else {
+        float v = 0.f;
+#pragma unroll
+        for (int k = 0; k < 8; ++k)
+          if (k > i && k <= j) v += a[i][k] * x[k][j];
+        x[i][j] = -v / a[i][i];
+      }
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < 8; ++i)
+#pragma unroll
+    for (int j = 0; j < 8; ++j) rinv_sh[i * RMAX + j] = x[i][j];
+  return ok;
+}
+
 // ---------------------------------------------------------------------------------------------------------
 // Cluster version for r <= 8.
 constexpr int OJA_ROWS_PT = 4;  // basis rows per thread: n <= cluster size * 1024 * 4
@@ -269,8 +327,15 @@ __global__ void __launch_bounds__(1024) oja_update_cluster8_kernel(const float* 
 #pragma unroll
   for (int t = 0; t < ROWS_PT; ++t) {
     const int row = gtid + t * gthreads;
+    if (r == 8 && row < n) {  // a row is 32 bytes: two 16-byte loads
+      const float4 lo = reinterpret_cast<const float4*>(q_in + static_cast<size_t>(row) * 8)[0];
+      const float4 hi = reinterpret_cast<const float4*>(q_in + static_cast<size_t>(row) * 8)[1];
+      qrow[t][0] = lo.x; qrow[t][1] = lo.y; qrow[t][2] = lo.z; qrow[t][3] = lo.w;
+      qrow[t][4] = hi.x; qrow[t][5] = hi.y; qrow[t][6] = hi.z; qrow[t][7] = hi.w;
+    } else {
 #pragma unroll
-    for (int j = 0; j < 8; ++j) qrow[t][j] = (row < n && j < r) ? q_in[static_cast<size_t>(row) * r + j] : 0.f;
+      for (int j = 0; j < 8; ++j) qrow[t][j] = (row < n && j < r) ? q_in[static_cast<size_t>(row) * r + j] : 0.f;
+    }
   }
   if (lr != 0.f && g != nullptr) {
     float acc[36];
@@ -279,8 +344,16 @@ __global__ void __launch_bounds__(1024) oja_update_cluster8_kernel(const float* 
     for (int row = gtid; row < rows; row += gthreads) {  // S = Y^T Y on the bf16-rounded coefficients
       const float* yr = y + static_cast<size_t>(row) * ldy;
       float v[8];
+      if ((ldy & 3) == 0) {  // rows are 16-byte aligned: two vector loads, then mask the columns past r
+        const float4 lo = reinterpret_cast<const float4*>(yr)[0];
+        const float4 hi = reinterpret_cast<const float4*>(yr)[1];
+        v[0] = lo.x; v[1] = lo.y; v[2] = lo.z; v[3] = lo.w; v[4] = hi.x; v[5] = hi.y; v[6] = hi.z; v[7] = hi.w;
+      } else {
 #pragma unroll
-      for (int j = 0; j < 8; ++j) v[j] = (j < r) ? __bfloat162float(__float2bfloat16_rn(yr[j])) : 0.f;
+        for (int j = 0; j < 8; ++j) v[j] = (j < r) ? yr[j] : 0.f;
+      }
+#pragma unroll
+      for (int j = 0; j < 8; ++j) v[j] = (j < r) ? __bfloat162float(__float2bfloat16_rn(v[j])) : 0.f;
       accumulate_upper8(v, acc);
     }
     cluster_gram8(cluster, acc, s_part, s_mat);
@@ -307,7 +380,8 @@ __global__ void __launch_bounds__(1024) oja_update_cluster8_kernel(const float* 
 #pragma unroll
     for (int t = 0; t < ROWS_PT; ++t) accumulate_upper8(qrow[t], acc);  // rows past n are zero
     cluster_gram8(cluster, acc, s_part, s_mat);
-    chol_and_invert(s_mat, s_inv, r, &s_ok);  // the same numbers in every CTA: the outcome is uniform over the cluster
+    if (threadIdx.x == 0) s_ok = chol_and_invert8_regs(s_mat, s_inv, r) ? 1 : 0;  // the same numbers in every CTA: uniform outcome
+    __syncthreads();
     if (!s_ok) {
       if (threadIdx.x == 0 && status) atomicCAS(status, 0, ST_BAD_ARGUMENT);
       break;

@@ -82,7 +82,7 @@ __global__ void __launch_bounds__(512) allreduce_two_shot_kernel(const CommArgs 
   long long begin, end;
   slice_of(a, begin, end);
   const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
-  constexpr int UNROLL = 4;  // independent 16-byte elements in flight per thread
+  constexpr int UNROLL = 8;  // independent 16-byte elements in flight per thread
   for (long long i0 = begin + blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i0 < end; i0 += stride * UNROLL) {
     float4 acc[UNROLL];
 #pragma unroll
@@ -126,7 +126,7 @@ __global__ void __launch_bounds__(512) allreduce_multimem_kernel(const CommArgs 
   long long begin, end;
   slice_of(a, begin, end);
   const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
-  constexpr int UNROLL = 4;
+  constexpr int UNROLL = 8;
   for (long long i0 = begin + blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i0 < end; i0 += stride * UNROLL) {
     float x[UNROLL], y[UNROLL], z[UNROLL], w[UNROLL];
 #pragma unroll
@@ -167,7 +167,7 @@ __global__ void __launch_bounds__(512) allgather_slices_kernel(const CommArgs a)
   slice_of(a, begin, end);
   const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
   const float4* mine = reinterpret_cast<const float4*>(s_peers[a.rank]) + a.lo / 4;
-  constexpr int UNROLL = 4;
+  constexpr int UNROLL = 8;
   for (long long i0 = begin + blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i0 < end; i0 += stride * UNROLL) {
     float4 v[UNROLL];
 #pragma unroll
@@ -202,6 +202,35 @@ __global__ void __launch_bounds__(512) allgather_slices_kernel(const CommArgs a)
   rank_barrier(a, 1, &s_fail);
 }
 
+// Second half of a GEMM + all-reduce whose epilogue stored every rank's partial tile into that rank's slot of each
+// rank's staging buffer: wait until all ranks have stored (flag barrier), then sum the `world` local slots in fp32 and
+// write the bf16 result to `dst`.  One pass over local memory; nothing crosses NVLink here.
+__global__ void __launch_bounds__(512) allreduce_finish_kernel(const CommArgs a, const __nv_bfloat16* __restrict__ staging,
+                                                               __nv_bfloat16* __restrict__ dst, long long rows, int n) {
+  __shared__ int s_fail;
+  if (threadIdx.x == 0) s_fail = 0;
+  __syncthreads();
+  if (!rank_barrier(a, 0, &s_fail)) return;
+  const long long total = rows * n / 8;  // 16-byte elements per slot
+  const uint4* src = reinterpret_cast<const uint4*>(staging);
+  uint4* out = reinterpret_cast<uint4*>(dst);
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total; i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    float acc[8];
+#pragma unroll
+    for (int k = 0; k < 8; ++k) acc[k] = 0.f;
+    for (int r = 0; r < a.world; ++r) {
+      const uint4 raw = src[static_cast<long long>(r) * total + i];
+      const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        acc[2 * k] += __uint_as_float(w[k] << 16);
+        acc[2 * k + 1] += __uint_as_float(w[k] & 0xFFFF0000u);
+      }
+    }
+    out[i] = make_uint4(pack_bf16x2(acc[0], acc[1]), pack_bf16x2(acc[2], acc[3]), pack_bf16x2(acc[4], acc[5]), pack_bf16x2(acc[6], acc[7]));
+  }
+}
+
 // A barrier across ranks as a kernel of its own (one CTA), on the third flag plane.
 __global__ void __launch_bounds__(32) rank_barrier_kernel(const CommArgs a) {
   __shared__ int s_fail;
@@ -231,14 +260,20 @@ __global__ void flag_set_kernel(int* flag, int value) {
   st_release_sys(flag, value);
 }
 
+// `sms` caps the grid: the reductions run next to compute kernels, and every CTA here takes an SM away from them, so
+// the caller passes a small number (with 8 x 16 bytes in flight per thread a few dozen CTAs saturate the links).
+static int comm_grid(long long vecs_per_rank, int sms) {
+  int grid = static_cast<int>((vecs_per_rank + 511) / 512);
+  const int cap = sms < MAX_CTAS ? sms : MAX_CTAS;
+  if (grid > cap) grid = cap;
+  return grid < 1 ? 1 : grid;
+}
+
 static int launch_allreduce(bool multimem, const CommArgs& a, int sms, cudaStream_t st) {
   if (a.world < 1 || a.world > MAX_RANKS) return -2;
   if ((a.lo & 3) || (a.hi & 3) || a.hi < a.lo) return -3;
   const long long vecs = (a.hi - a.lo) / 4 / (a.world > 0 ? a.world : 1);
-  int grid = static_cast<int>((vecs + 511) / 512);
-  const int cap = sms < MAX_CTAS ? sms : MAX_CTAS;
-  if (grid > cap / 2) grid = cap / 2;  // leave SMs to the compute kernels this overlaps with
-  if (grid < 1) grid = 1;
+  const int grid = comm_grid(vecs, sms);
   if (multimem) allreduce_multimem_kernel<<<grid, 512, 0, st>>>(a);
   else allreduce_two_shot_kernel<<<grid, 512, 0, st>>>(a);
   return static_cast<int>(cudaGetLastError());
@@ -272,10 +307,7 @@ extern "C" int sb_allgather_slices(const void* peer_ptrs, const void* flag_ptrs,
   CommArgs a{static_cast<const unsigned long long*>(peer_ptrs), static_cast<const unsigned long long*>(flag_ptrs), mc_ptr, rank, world,
              lo, hi, scale, epoch, status};
   const long long vecs = (hi - lo) / 4 / world;
-  int grid = static_cast<int>((vecs + 511) / 512);
-  const int cap = sms < MAX_CTAS ? sms : MAX_CTAS;
-  if (grid > cap / 2) grid = cap / 2;
-  if (grid < 1) grid = 1;
+  const int grid = comm_grid(vecs, sms);
   allgather_slices_kernel<<<grid, 512, 0, static_cast<cudaStream_t>(stream)>>>(a);
   return static_cast<int>(cudaGetLastError());
 }
@@ -299,5 +331,18 @@ extern "C" int sb_flag_wait(const int* flag, int expected, unsigned long long li
 extern "C" int sb_flag_set(int* flag, int value, void* stream) {
   if (flag == nullptr) return -2;
   sb::flag_set_kernel<<<1, 1, 0, static_cast<cudaStream_t>(stream)>>>(flag, value);
+  return static_cast<int>(cudaGetLastError());
+}
+
+// See allreduce_finish_kernel.  rows * n must be a multiple of 8; dst is a contiguous [rows, n] bf16 tensor.
+extern "C" int sb_allreduce_finish(const void* flag_ptrs, int rank, int world, int epoch, const void* staging, void* dst,
+                                   long long rows, int n, int sms, int* status, void* stream) {
+  using namespace sb;
+  if (world < 1 || world > MAX_RANKS) return -2;
+  if ((rows * n) % 8) return -3;
+  CommArgs a{nullptr, static_cast<const unsigned long long*>(flag_ptrs), 0ull, rank, world, 0, 0, 1.f, epoch, status};
+  const int grid = comm_grid(rows * n / 8, sms);
+  allreduce_finish_kernel<<<grid, 512, 0, static_cast<cudaStream_t>(stream)>>>(a, static_cast<const __nv_bfloat16*>(staging),
+                                                                               static_cast<__nv_bfloat16*>(dst), rows, n);
   return static_cast<int>(cudaGetLastError());
 }

@@ -31,12 +31,24 @@ struct GemmParams {
   int splits;      // split-K factor (>=1); every split owns >=1 k-block
   int kb_per;      // k-blocks per split
   int ldo;         // leading dimension of the output (elements)
-  int out_mode;    // 0 = bf16 store, 1 = fp32 store, 2 = fp32 atomic add
+  int out_mode;    // 0 = bf16 store, 1 = fp32 store, 2 = fp32 atomic add, 3 = bf16 store into this rank's slot of every rank's staging buffer
   float alpha;
   void* out;
   const float* bias;  // optional, length N (added by split 0 only)
   int* status;
+  // out_mode 3: the staging buffer is symmetric memory holding `world` slots of M x ldo bf16; this rank's partial tile
+  // is stored into slot `slot_off` (bytes) of all `world` copies, through one multicast address or the peer pointers.
+  int world;
+  unsigned long long slot_off;
+  unsigned long long mc_out;         // multicast address of the buffer, 0 = use peer_out
+  unsigned long long peer_out[8];    // every rank's copy as mapped on this GPU
 };
+
+__device__ __forceinline__ void multimem_st_v4(void* addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+  asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(__uint_as_float(a)), "f"(__uint_as_float(b)),
+               "f"(__uint_as_float(c)), "f"(__uint_as_float(d))
+               : "memory");
+}
 
 template <int BN>
 struct GemmCfg {
@@ -254,11 +266,30 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             for (int i = 0; i < 16; ++i)
               if (col0 + i < p.N) o[i] = f[i];
           }
-        } else {
+        } else if (p.out_mode == 2) {
           float* o = reinterpret_cast<float*>(p.out) + static_cast<size_t>(row) * p.ldo + col0;
 #pragma unroll
           for (int i = 0; i < 16; ++i)
             if (col0 + i < p.N) atomicAdd(o + i, f[i]);
+        } else {
+          // all-reduce fused into the epilogue, first half: this rank's partial tile goes into its own slot of every
+          // rank's staging buffer with plain 16-byte stores (posted writes over NVLink; no atomics).  The sum over the
+          // slots is taken locally by sb_allreduce_finish once every rank has stored.
+          // (the launcher guarantees N % 16 == 0 and 16-byte aligned rows for this mode)
+          const size_t off = p.slot_off + (static_cast<size_t>(row) * p.ldo + col0) * 2;
+          const uint32_t w[8] = {pack_bf16x2(f[0], f[1]), pack_bf16x2(f[2], f[3]), pack_bf16x2(f[4], f[5]), pack_bf16x2(f[6], f[7]),
+                                 pack_bf16x2(f[8], f[9]), pack_bf16x2(f[10], f[11]), pack_bf16x2(f[12], f[13]), pack_bf16x2(f[14], f[15])};
+          if (p.mc_out != 0) {
+            char* dst = reinterpret_cast<char*>(p.mc_out) + off;
+            multimem_st_v4(dst, w[0], w[1], w[2], w[3]);
+            multimem_st_v4(dst + 16, w[4], w[5], w[6], w[7]);
+          } else {
+            for (int r = 0; r < p.world; ++r) {
+              uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<char*>(p.peer_out[r]) + off);
+              dst[0] = make_uint4(w[0], w[1], w[2], w[3]);
+              dst[1] = make_uint4(w[4], w[5], w[6], w[7]);
+            }
+          }
         }
       }
       tc_fence_before();
@@ -342,9 +373,9 @@ static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const GemmP
 //   out_mode 0 bf16 / 1 fp32 / 2 fp32 atomic add (required when splits > 1; caller zeroes out).
 //   bn = tile width: 16, 32, 64, 128 or 256.
 // Alignment: base pointers 16-byte aligned, lda/ldb multiples of 8 elements.
-extern "C" int sb_gemm_bf16(const void* A, const void* B, void* out, const float* bias, int M, int N, int K,
-                            int lda, int ldb, int ldo, int a_mn, int b_mn, int out_mode, int splits,
-                            int bn, float alpha, int sms, int* status, void* stream) {
+static int gemm_entry(const void* A, const void* B, void* out, const float* bias, int M, int N, int K, int lda, int ldb, int ldo,
+                      int a_mn, int b_mn, int out_mode, int splits, int bn, float alpha, int sms, int* status, void* stream,
+                      int world, unsigned long long mc_out, const unsigned long long* peer_out, unsigned long long slot_off) {
   using namespace sb;
   if (M <= 0 || N <= 0 || K <= 0) return 0;
   if ((reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(B) & 15) || (lda & 7) || (ldb & 7))
@@ -366,6 +397,8 @@ extern "C" int sb_gemm_bf16(const void* A, const void* B, void* out, const float
   p.kb_per = (num_kb + splits - 1) / splits;
   p.splits = (num_kb + p.kb_per - 1) / p.kb_per;
   p.ldo = ldo; p.out_mode = out_mode; p.alpha = alpha; p.out = out; p.bias = bias; p.status = status;
+  p.world = world; p.mc_out = mc_out; p.slot_off = slot_off;
+  for (int r = 0; r < 8; ++r) p.peer_out[r] = (peer_out != nullptr && r < world) ? peer_out[r] : 0ull;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
 #define SB_DISPATCH(BN_)                                                              \
   if (bn == BN_) {                                                                     \
@@ -383,4 +416,27 @@ extern "C" int sb_gemm_bf16(const void* A, const void* B, void* out, const float
   if (bn == 32) return a_mn ? launch_gemm<32, true, false>(ta, tb, p, sms, st) : launch_gemm<32, false, false>(ta, tb, p, sms, st);
   if (bn == 16) return a_mn ? launch_gemm<16, true, false>(ta, tb, p, sms, st) : launch_gemm<16, false, false>(ta, tb, p, sms, st);
   return -6;
+}
+
+extern "C" int sb_gemm_bf16(const void* A, const void* B, void* out, const float* bias, int M, int N, int K,
+                            int lda, int ldb, int ldo, int a_mn, int b_mn, int out_mode, int splits,
+                            int bn, float alpha, int sms, int* status, void* stream) {
+  if (out_mode < 0 || out_mode > 2) return -7;
+  return gemm_entry(A, B, out, bias, M, N, K, lda, ldb, ldo, a_mn, b_mn, out_mode, splits, bn, alpha, sms, status, stream, 1, 0ull, nullptr, 0ull);
+}
+
+// First half of a GEMM + all-reduce: every rank calls it with its partial operands and the epilogue stores the bf16
+// tile into slot `rank` of the staging buffer of each of the `world` ranks (one multimem.st through the NVSwitch
+// multicast address mc_out, or one plain store per peer pointer when mc_out == 0).  A staging buffer holds `world`
+// slots of M x N bf16 (slot r at byte offset r * M * N * 2).  sb_allreduce_finish sums the slots once all ranks have
+// stored.  peer_out is a HOST array of `world` (<= 8) staging addresses.  N % 16 == 0.  A bias (fp32, length N) is
+// added to this rank's partial tile, so exactly one rank should pass it.
+extern "C" int sb_gemm_bf16_allreduce(const void* A, const void* B, const float* bias, int M, int N, int K, int lda, int ldb,
+                                      int a_mn, int b_mn, int bn, float alpha, int sms, int rank, int world, unsigned long long mc_out,
+                                      const unsigned long long* peer_out, int* status, void* stream) {
+  if (world < 1 || world > 8 || rank < 0 || rank >= world || (mc_out == 0 && peer_out == nullptr)) return -8;
+  if (N % 16) return -9;
+  const unsigned long long slot = static_cast<unsigned long long>(rank) * M * N * 2ull;
+  void* out = reinterpret_cast<void*>(peer_out ? peer_out[rank] : mc_out);  // only its alignment is looked at
+  return gemm_entry(A, B, out, bias, M, N, K, lda, ldb, N, a_mn, b_mn, 3, 1, bn, alpha, sms, status, stream, world, mc_out, peer_out, slot);
 }

@@ -37,6 +37,26 @@ def _time(fn, iters=10):
     return float(t)
 
 
+def _kernel_times(fn, iters=10) -> dict:
+    """Mean device time per kernel name (microseconds) over `iters` calls, from the profiler's kernel records."""
+    from torch.profiler import ProfilerActivity, profile
+
+    for _ in range(3):
+        fn()
+    torch.cuda.synchronize()
+    dist.barrier()
+    with profile(activities=[ProfilerActivity.CUDA]) as prof:
+        for _ in range(iters):
+            fn()
+        torch.cuda.synchronize()
+    out = {}
+    for e in prof.key_averages():
+        t = getattr(e, "device_time_total", None) or getattr(e, "cuda_time_total", 0)
+        if t:
+            out[e.key[:60]] = round(t / iters, 2)
+    return out
+
+
 def _fused_dw_check(buf, rank, world, dev, report) -> bool:
     """Weight-gradient kernel with the reduce-scatter in its epilogue + all-gather of owner slices vs NCCL all-reduce."""
     from ..ops import stacr_ops
@@ -78,6 +98,47 @@ def _fused_dw_check(buf, rank, world, dev, report) -> bool:
     return good
 
 
+def _tp_gemm_check(rank, world, dev, report) -> bool:
+    """GEMM with the all-reduce in its epilogue vs library GEMM + NCCL all-reduce (shapes of a GPT-2-large block at TP degree `world`)."""
+    from .tp import GemmAllReduce
+
+    m, n, k = 4096, 1280, 5120 // world
+    gen = torch.Generator(device=dev).manual_seed(500 + rank)
+    a = (torch.randn(m, k, device=dev, generator=gen) / 8).bfloat16()
+    w = (torch.randn(n, k, device=dev, generator=gen) / 8).bfloat16()
+    bias = torch.randn(n, device=dev, generator=gen) if rank == 0 else None
+    eng = GemmAllReduce(m * n, dev)
+    good = True
+    for mm in ([False, True] if eng.bufs[0].multicast_ptr else [False]):
+        for b in eng.bufs:
+            b.use_multimem = mm
+        want = a.float() @ w.float().t()
+        if bias is not None:
+            want += bias
+        dist.all_reduce(want)
+        for _ in range(3):                       # three calls: both staging buffers and their clearing are exercised
+            got = eng(a, w, bias=bias)
+        torch.cuda.synchronize()
+        _lib.check_status(dev)
+        err = float((got.float() - want).abs().max() / want.abs().max())
+        name = "multimem" if mm else "p2p"
+        report[f"tp_gemm_allreduce_{name}_rel_err"] = err
+        good &= err < 2e-2                       # bf16 partial sums added in bf16
+        report[f"tp_gemm_allreduce_{name}_ms"] = _time(lambda: eng(a, w, bias=bias), iters=20)
+        report[f"tp_gemm_allreduce_{name}_kernel_us"] = _kernel_times(lambda: eng(a, w, bias=bias))
+
+    def library():
+        y = torch.nn.functional.linear(a, w)
+        dist.all_reduce(y)
+        return y
+
+    report["tp_gemm_then_nccl_ms"] = _time(library, iters=20)
+    report["tp_gemm_then_nccl_kernel_us"] = _kernel_times(library)
+    report["tp_gemm_alone_ms"] = _time(lambda: torch.nn.functional.linear(a, w), iters=20)
+    report["tp_shape"] = [m, n, k]
+    return good
+
+
 def main() -> int:
     rank, world, local = init_distributed("nccl")
     dev = torch.device("cuda", local)
@@ -112,10 +173,14 @@ def main() -> int:
             if rank == 0 and not good:
                 report.setdefault("failures", []).append({"mode": name, "lo": lo, "hi": hi, "err": err, "outside_untouched": same})
             dist.barrier()
-        ms = _time(lambda: buf.all_reduce_(0, n, average=False))
-        report[f"{name}_ms_256MB"] = ms
-        report[f"{name}_busbw_GBs"] = 2 * (world - 1) / world * n * 4 / ms / 1e6
+        for ctas in (16, 32, 64, 128):
+            buf.max_ctas = ctas
+            ms = _time(lambda: buf.all_reduce_(0, n, average=False))
+            report[f"{name}_ms_256MB_{ctas}ctas"] = ms
+            report[f"{name}_busbw_GBs_{ctas}ctas"] = 2 * (world - 1) / world * n * 4 / ms / 1e6
+        buf.max_ctas = 32
     ok &= _fused_dw_check(buf, rank, world, dev, report)
+    ok &= _tp_gemm_check(rank, world, dev, report)
     plain = torch.randn(n, device=dev)
     ms = _time(lambda: dist.all_reduce(plain))
     report["nccl_ms_256MB"] = ms

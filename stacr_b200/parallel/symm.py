@@ -67,6 +67,9 @@ class SymmetricBuffer:
         self.use_multimem = self.multicast_ptr != 0 and os.environ.get("STACR_SYMM_MULTIMEM", "1") == "1"
         self._epoch = 0
         self.numel = numel
+        # CTAs per collective kernel: each one takes an SM away from the compute it overlaps with.  The switch-side
+        # reduction (multimem) reaches its bandwidth with very few CTAs; peer loads/stores need many more in flight.
+        self.max_ctas = int(os.environ.get("STACR_COMM_CTAS", "8" if self.use_multimem else "64"))
 
     def all_reduce_(self, lo: int, hi: int, average: bool = True) -> None:
         """In-place sum (or mean) of ``tensor[lo:hi]`` across ranks, on the current stream."""
@@ -77,7 +80,7 @@ class SymmetricBuffer:
         rc = fn(
             _lib.ptr(self._peer_ptrs), _lib.ptr(self._pad_ptrs), ctypes.c_ulonglong(self.multicast_ptr), ctypes.c_int(self.rank),
             ctypes.c_int(self.world), ctypes.c_longlong(lo), ctypes.c_longlong(hi), ctypes.c_float(scale),
-            ctypes.c_int(self._epoch), ctypes.c_int(_lib.sm_count(self.tensor.device)), _lib.ptr(_lib.status_word(self.tensor.device)),
+            ctypes.c_int(self._epoch), ctypes.c_int(self.max_ctas), _lib.ptr(_lib.status_word(self.tensor.device)),
             _lib.stream_ptr(),
         )
         _lib.check_rc(rc, "sb_allreduce")
@@ -88,7 +91,7 @@ class SymmetricBuffer:
         rc = fn(
             _lib.ptr(self._peer_ptrs), _lib.ptr(self._pad_ptrs), ctypes.c_ulonglong(self.multicast_ptr if multicast else 0), ctypes.c_int(self.rank),
             ctypes.c_int(self.world), ctypes.c_longlong(lo), ctypes.c_longlong(hi), ctypes.c_float(scale), ctypes.c_int(self._epoch),
-            ctypes.c_int(_lib.sm_count(self.tensor.device)), _lib.ptr(_lib.status_word(self.tensor.device)), _lib.stream_ptr(),
+            ctypes.c_int(self.max_ctas), _lib.ptr(_lib.status_word(self.tensor.device)), _lib.stream_ptr(),
         )
         _lib.check_rc(rc, name)
         _lib.count(1)

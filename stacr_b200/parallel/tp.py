@@ -1,0 +1,222 @@
+"""Tensor-parallel linears whose collective is fused into the GEMM.
+
+A Megatron-style block has two all-reduces on its critical path in each direction: the output of the row-parallel
+projection in forward and the input gradient of the column-parallel projection in backward.  Both are "GEMM, then
+sum over ranks".  :class:`GemmAllReduce` runs them as ONE tensor-core kernel per rank: the epilogue of every output
+tile adds the tile, as bf16, straight into the copy of the result that each rank holds in symmetric memory (one
+``multimem.red`` through the NVSwitch multicast address, or one ``red.add`` per peer pointer), so the transfer of
+tile i overlaps the math of tile i+1.  A second small kernel waits until every rank has finished adding (flag
+barrier with a bounded wait), moves the local copy into an ordinary tensor (adding the bias) and clears the staging
+copy.  Two staging buffers alternate, which is what makes the clear race-free without a barrier in front of the GEMM:
+a rank can only start adding into buffer ``k+1`` of a peer after that peer has passed the barrier of call ``k``,
+and the peer cleared buffer ``k+1`` before it arrived there.
+
+Replaces the ``clone() + dist.all_reduce`` after the row-parallel GEMM and the ``all_reduce`` of the input gradient
+of the reference (stacr/protocols/tensor_parallel.py:25-64 there).  Without CUDA, symmetric memory or bf16 operands
+the modules fall back to a library GEMM followed by ``torch.distributed.all_reduce``.
+"""
+
+from __future__ import annotations
+
+import ctypes
+from typing import Optional
+
+import torch
+import torch.distributed as dist
+import torch.nn.functional as F
+from torch import nn
+
+from ..ops import _lib
+
+
+def _world(group) -> int:
+    return dist.get_world_size(group) if dist.is_initialized() else 1
+
+
+class GemmAllReduce:
+    """``sum over ranks of (A_r @ B_r^T)`` with the sum done by the GEMM epilogue over NVLink peer memory."""
+
+    def __init__(self, max_elems: int, device: torch.device, group=None):
+        from . import symm
+
+        self.group = group
+        world = _world(group)
+        self.bufs = [symm.SymmetricBuffer(max_elems * world, torch.bfloat16, device, group) for _ in range(2)]
+        for b in self.bufs:
+            b.tensor.zero_()
+        torch.cuda.synchronize(device)
+        dist.barrier(group)
+        self.world, self.rank = self.bufs[0].world, self.bufs[0].rank
+        self.max_elems, self.device = max_elems, device
+        self._peer_lists = [(ctypes.c_ulonglong * 8)(*([int(p) for p in b.peer_ptrs.tolist()] + [0] * (8 - self.world))) for b in self.bufs]
+        self.calls = 0
+        if self.world > 8:
+            raise ValueError("GemmAllReduce supports up to 8 ranks")
+
+    def __call__(self, a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = False, bias: Optional[torch.Tensor] = None,
+                 alpha: float = 1.0) -> torch.Tensor:
+        from ..ops.gemm import _pick_bn
+
+        assert a.dtype == torch.bfloat16 and b.dtype == torch.bfloat16 and a.stride(1) == 1 and b.stride(1) == 1
+        k, m = a.shape if a_mn else a.shape[::-1]
+        n = b.shape[1] if b_mn else b.shape[0]
+        if n % 16 or m * n > self.max_elems:
+            raise ValueError(f"output {m}x{n} needs N % 16 == 0 and at most {self.max_elems} elements")
+        buf = self.bufs[self.calls & 1]
+        peers = self._peer_lists[self.calls & 1]
+        self.calls += 1
+        sms = _lib.sm_count(a.device)
+        lib = _lib.load()
+        if bias is not None:
+            bias = bias.detach().float().contiguous()
+        rc = lib.sb_gemm_bf16_allreduce(
+            _lib.ptr(a), _lib.ptr(b), _lib.ptr(bias), ctypes.c_int(m), ctypes.c_int(n), ctypes.c_int(k),
+            ctypes.c_int(a.stride(0)), ctypes.c_int(b.stride(0)), ctypes.c_int(int(a_mn)), ctypes.c_int(int(b_mn)),
+            ctypes.c_int(_pick_bn(m, n, b_mn, sms)), ctypes.c_float(alpha), ctypes.c_int(sms), ctypes.c_int(self.rank), ctypes.c_int(self.world),
+            ctypes.c_ulonglong(buf.multicast_ptr if buf.use_multimem else 0), peers, _lib.ptr(_lib.status_word(a.device)), _lib.stream_ptr(),
+        )
+        _lib.check_rc(rc, "sb_gemm_bf16_allreduce")
+        out = torch.empty((m, n), dtype=torch.bfloat16, device=a.device)
+        flags = self.bufs[0]          # one flag plane and one epoch counter serve both staging buffers
+        flags._epoch += 1
+        rc = lib.sb_allreduce_finish(
+            _lib.ptr(flags._pad_ptrs), ctypes.c_int(self.rank), ctypes.c_int(self.world), ctypes.c_int(flags._epoch), _lib.ptr(buf.tensor),
+            _lib.ptr(out), ctypes.c_longlong(m), ctypes.c_int(n), ctypes.c_int(max(flags.max_ctas, 32)),
+            _lib.ptr(_lib.status_word(a.device)), _lib.stream_ptr(),
+        )
+        _lib.check_rc(rc, "sb_allreduce_finish")
+        _lib.count(2)
+        return out
+
+
+_ENGINES: dict = {}
+
+
+def engine_for(device: torch.device, max_elems: int, group=None) -> Optional[GemmAllReduce]:
+    """One shared engine per (device, group), grown on demand; ``None`` when the fused path cannot run here."""
+    from . import symm
+
+    if _world(group) < 2 or device.type != "cuda" or not symm.available():
+        return None
+    key = (device.index, id(group))
+    eng = _ENGINES.get(key)
+    if eng is None or eng.max_elems < max_elems:
+        eng = GemmAllReduce(max(max_elems, 1 << 22), device, group)
+        _ENGINES[key] = eng
+    return eng
+
+
+def _bf16(t: torch.Tensor) -> torch.Tensor:
+    return t if t.dtype == torch.bfloat16 else t.to(torch.bfloat16)
+
+
+class _RowParallelFn(torch.autograd.Function):
+    """``y = all_reduce(x_local @ W_local^T) + bias``; no collective in backward."""
+
+    @staticmethod
+    def forward(ctx, x, weight, bias, group, engine):
+        x2d = x.reshape(-1, x.shape[-1])
+        ctx.save_for_backward(x2d, weight)
+        ctx.has_bias, ctx.shape = bias is not None, x.shape
+        if engine is not None:
+            y = engine(_bf16(x2d).contiguous(), _bf16(weight).contiguous(), bias=bias)
+        else:
+            y = F.linear(x2d, weight.to(x2d.dtype), None if bias is None else bias.to(x2d.dtype))
+            if _world(group) > 1:
+                dist.all_reduce(y, group=group)
+        return y.reshape(*x.shape[:-1], weight.shape[0])
+
+    @staticmethod
+    def backward(ctx, gy):
+        x2d, weight = ctx.saved_tensors
+        g2d = gy.reshape(-1, gy.shape[-1])
+        gx = (g2d.to(weight.dtype) @ weight).to(x2d.dtype).reshape(ctx.shape) if ctx.needs_input_grad[0] else None
+        gw = (g2d.t().to(x2d.dtype) @ x2d).to(weight.dtype) if ctx.needs_input_grad[1] else None
+        gb = g2d.sum(0) if ctx.has_bias and ctx.needs_input_grad[2] else None
+        return gx, gw, gb, None, None
+
+
+class _ColumnParallelFn(torch.autograd.Function):
+    """``y = x @ W_local^T + b_local`` on a replicated input; the input gradient is summed over ranks by the GEMM."""
+
+    @staticmethod
+    def forward(ctx, x, weight, bias, group, engine):
+        x2d = x.reshape(-1, x.shape[-1])
+        ctx.save_for_backward(x2d, weight)
+        ctx.has_bias, ctx.shape, ctx.group, ctx.engine = bias is not None, x.shape, group, engine
+        y = F.linear(x2d, weight.to(x2d.dtype), None if bias is None else bias.to(x2d.dtype))
+        return y.reshape(*x.shape[:-1], weight.shape[0])
+
+    @staticmethod
+    def backward(ctx, gy):
+        x2d, weight = ctx.saved_tensors
+        g2d = gy.reshape(-1, gy.shape[-1])
+        gx = None
+        if ctx.needs_input_grad[0]:
+            if ctx.engine is not None:
+                # dX = dY @ W: W [out_local, in] is the [K, N] operand of this product
+                gx = ctx.engine(_bf16(g2d).contiguous(), _bf16(weight).contiguous(), b_mn=True).to(x2d.dtype)
+            else:
+                gx = (g2d.to(weight.dtype) @ weight).to(x2d.dtype)
+                if _world(ctx.group) > 1:
+                    dist.all_reduce(gx, group=ctx.group)
+            gx = gx.reshape(ctx.shape)
+        gw = (g2d.t().to(x2d.dtype) @ x2d).to(weight.dtype) if ctx.needs_input_grad[1] else None
+        gb = g2d.sum(0) if ctx.has_bias and ctx.needs_input_grad[2] else None
+        return gx, gw, gb, None, None
+
+
+class _FusedBase(nn.Module):
+    def __init__(self, linear: nn.Linear, group=None, fused: bool = True):
+        super().__init__()
+        self.weight, self.bias = linear.weight, linear.bias
+        self.in_features, self.out_features = linear.in_features, linear.out_features
+        self.group, self.fused = group, fused
+
+    def _engine(self, x: torch.Tensor, out_elems: int) -> Optional[GemmAllReduce]:
+        autocast_bf16 = torch.is_autocast_enabled(x.device.type) and torch.get_autocast_dtype(x.device.type) == torch.bfloat16
+        if not self.fused or not (x.is_cuda and (x.dtype == torch.bfloat16 or autocast_bf16)):
+            return None
+        return engine_for(x.device, out_elems, self.group)
+
+    def extra_repr(self) -> str:
+        return f"in_features={self.in_features}, out_features={self.out_features}, bias={self.bias is not None}, fused={self.fused}"
+
+
+class RowParallelLinear(_FusedBase):
+    """Holds the input-column shard of a projection; ``forward`` returns the full (summed) output on every rank."""
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        rows = x.numel() // x.shape[-1]
+        ok = self.out_features % 16 == 0 and self.in_features % 8 == 0
+        return _RowParallelFn.apply(x, self.weight, self.bias, self.group, self._engine(x, rows * self.out_features) if ok else None)
+
+
+class ColumnParallelLinear(_FusedBase):
+    """Holds the output-row shard of a projection; the input is replicated and its gradient is summed over ranks."""
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        rows = x.numel() // x.shape[-1]
+        ok = self.in_features % 16 == 0 and self.out_features % 8 == 0
+        return _ColumnParallelFn.apply(x, self.weight, self.bias, self.group, self._engine(x, rows * self.in_features) if ok else None)
+
+
+def _fused_engine(x: torch.Tensor, out_elems: int, group) -> Optional[GemmAllReduce]:
+    autocast_bf16 = torch.is_autocast_enabled(x.device.type) and torch.get_autocast_dtype(x.device.type) == torch.bfloat16
+    if not (x.is_cuda and (x.dtype == torch.bfloat16 or autocast_bf16)):
+        return None
+    return engine_for(x.device, out_elems, group)
+
+
+def row_parallel_linear(x: torch.Tensor, linear: nn.Linear, group=None, fused: bool = True) -> torch.Tensor:
+    """Functional form of :class:`RowParallelLinear` over an existing ``nn.Linear`` shard."""
+    rows = x.numel() // x.shape[-1]
+    ok = fused and linear.out_features % 16 == 0 and linear.in_features % 8 == 0
+    return _RowParallelFn.apply(x, linear.weight, linear.bias, group, _fused_engine(x, rows * linear.out_features, group) if ok else None)
+
+
+def column_parallel_linear(x: torch.Tensor, linear: nn.Linear, group=None, fused: bool = True) -> torch.Tensor:
+    """Functional form of :class:`ColumnParallelLinear` over an existing ``nn.Linear`` shard."""
+    rows = x.numel() // x.shape[-1]
+    ok = fused and linear.in_features % 16 == 0 and linear.out_features % 8 == 0
+    return _ColumnParallelFn.apply(x, linear.weight, linear.bias, group, _fused_engine(x, rows * linear.in_features, group) if ok else None)

@@ -14,6 +14,7 @@ import torch
 from torch import nn
 from torch.nn import functional as F
 
+from ..parallel.tp import column_parallel_linear, row_parallel_linear
 from .tensor_parallel import (convert_conv1d_to_linear, copy_to_tp_region, reduce_from_tp_region, shard_linear_column,
                               shard_linear_row)
 
@@ -51,11 +52,18 @@ class TPGPT2MLP(nn.Module):
         self.act = original_mlp.act
         self.dropout = _find(original_mlp, "dropout", default=nn.Identity())
         self.tp_group = tp_group
+        self.fused_collectives = True
 
     def forward(self, hidden_states):
-        x = copy_to_tp_region(hidden_states, self.tp_group)
-        x = self.c_proj(self.act(self.c_fc(x)))
-        return self.dropout(reduce_from_tp_region(x, self.tp_group))
+        # a plain shard runs with its collective inside the GEMM; a wrapped (compressed) shard keeps the explicit one
+        if type(self.c_fc) is nn.Linear:
+            x = column_parallel_linear(hidden_states, self.c_fc, self.tp_group, self.fused_collectives)
+        else:
+            x = self.c_fc(copy_to_tp_region(hidden_states, self.tp_group))
+        x = self.act(x)
+        if type(self.c_proj) is nn.Linear:
+            return self.dropout(row_parallel_linear(x, self.c_proj, self.tp_group, self.fused_collectives))
+        return self.dropout(reduce_from_tp_region(self.c_proj(x), self.tp_group))
 
 
 class TPGPT2Attention(nn.Module):
@@ -72,19 +80,27 @@ class TPGPT2Attention(nn.Module):
         self.attn_pdrop = float(_find(original_attn, "attn_pdrop", default=getattr(drop, "p", 0.0)))
         self.resid_dropout = _find(original_attn, "resid_dropout", default=nn.Identity())
         self.tp_group = tp_group
+        self.fused_collectives = True
 
     def forward(self, hidden_states, attention_mask=None, **kwargs):
         b, s, _ = hidden_states.shape
-        x = copy_to_tp_region(hidden_states, self.tp_group)
-        q, k, v = self.c_attn(x).split(self.local_heads * self.head_dim, dim=-1)
+        if type(self.c_attn) is nn.Linear:
+            qkv = column_parallel_linear(hidden_states, self.c_attn, self.tp_group, self.fused_collectives)
+        else:
+            qkv = self.c_attn(copy_to_tp_region(hidden_states, self.tp_group))
+        x = hidden_states
+        q, k, v = qkv.split(self.local_heads * self.head_dim, dim=-1)
         shape = lambda t: t.view(b, s, self.local_heads, self.head_dim).transpose(1, 2)
         mask = None
         if attention_mask is not None and attention_mask.dim() == 2 and not bool(attention_mask.all()):
             mask = attention_mask[:, None, None, :].bool() & torch.ones(s, s, dtype=torch.bool, device=x.device).tril()
         ctx = F.scaled_dot_product_attention(shape(q), shape(k), shape(v), attn_mask=mask, is_causal=mask is None,
                                              dropout_p=self.attn_pdrop if self.training else 0.0)
-        out = self.c_proj(ctx.transpose(1, 2).reshape(b, s, self.local_heads * self.head_dim))
-        out = self.resid_dropout(reduce_from_tp_region(out, self.tp_group))
+        merged = ctx.transpose(1, 2).reshape(b, s, self.local_heads * self.head_dim)
+        if type(self.c_proj) is nn.Linear:
+            out = self.resid_dropout(row_parallel_linear(merged, self.c_proj, self.tp_group, self.fused_collectives))
+        else:
+            out = self.resid_dropout(reduce_from_tp_region(self.c_proj(merged), self.tp_group))
         if kwargs.get("output_attentions") is not None or kwargs.get("use_cache") is not None or "layer_past" in kwargs:
             return out, None  # Hugging Face block expects a tuple
         return out
