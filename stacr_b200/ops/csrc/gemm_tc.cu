@@ -59,7 +59,8 @@ struct GemmCfg {
   static constexpr int STAGES_RAW = MAX_SMEM / STAGE_BYTES;
   static constexpr int STAGES = STAGES_RAW > 8 ? 8 : STAGES_RAW;
   static constexpr int TMEM_COLS = (2 * BN <= 32) ? 32 : (2 * BN <= 64) ? 64 : (2 * BN <= 128) ? 128 : (2 * BN <= 256) ? 256 : 512;
-  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*align slack*/ + 256 /*barriers*/;
+  static constexpr int EPI_BYTES = 4 * 32 * 128;  // per epilogue warp: 32 rows x 64 bf16 columns
+  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + EPI_BYTES + 1024 /*align slack*/ + 256 /*barriers*/;
 };
 
 __device__ __forceinline__ void decode_tile(int tile, int num_m, int num_n, int& m_blk, int& n_blk,
@@ -85,7 +86,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
   constexpr int STAGES = Cfg::STAGES;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * Cfg::STAGE_BYTES);
+  uint8_t* epi_stage = smem + STAGES * Cfg::STAGE_BYTES;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(epi_stage + Cfg::EPI_BYTES);
   uint64_t* full_bar = bars;
   uint64_t* empty_bar = bars + STAGES;
   uint64_t* tmem_full = bars + 2 * STAGES;
@@ -228,18 +230,55 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       const bool row_ok = row < p.M;
       const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + acc * BN;
       const bool add_bias = (p.bias != nullptr) && (sp == 0);
+      // bf16 outputs whose rows are 16-byte aligned go through shared memory: every lane owns one ROW of the
+      // accumulator, so direct stores would be 32-byte pieces 2*ldo bytes apart; staged, a warp writes whole
+      // 128-byte row segments (8 lanes x 16 bytes), which is what peer writes over NVLink need.
+      constexpr int GW = BN < 64 ? BN : 64;          // columns per staged group
+      constexpr int UNITS = GW / 8;                  // 16-byte units per staged row
+      const bool staged = (p.out_mode == 0 || p.out_mode == 3) && (p.ldo % 8 == 0) && (p.N % 8 == 0) &&
+                          ((reinterpret_cast<uintptr_t>(p.out) & 15) == 0);
+      uint4* my_stage = reinterpret_cast<uint4*>(epi_stage) + quad * (32 * 8);
 #pragma unroll 1
       for (int c = 0; c < BN / 16; ++c) {
         uint32_t v[16];
         tmem_ld_x16(t_row + c * 16, v);
         tmem_ld_wait();
         const int col0 = n_blk * BN + c * 16;
-        if (col0 >= p.N) continue;  // warp-uniform
+        if (!staged && col0 >= p.N) continue;  // warp-uniform
         float f[16];
 #pragma unroll
         for (int i = 0; i < 16; ++i) {
           f[i] = __uint_as_float(v[i]) * p.alpha;
           if (add_bias && col0 + i < p.N) f[i] += __ldg(p.bias + col0 + i);
+        }
+        if (staged) {
+          const int cu = (c * 2) % UNITS;  // first 16-byte unit of this chunk inside the staged row
+          my_stage[lane * 8 + ((cu) ^ (lane & 7))] = make_uint4(pack_bf16x2(f[0], f[1]), pack_bf16x2(f[2], f[3]), pack_bf16x2(f[4], f[5]), pack_bf16x2(f[6], f[7]));
+          my_stage[lane * 8 + ((cu + 1) ^ (lane & 7))] = make_uint4(pack_bf16x2(f[8], f[9]), pack_bf16x2(f[10], f[11]), pack_bf16x2(f[12], f[13]), pack_bf16x2(f[14], f[15]));
+          if (((c + 1) * 16) % GW != 0) continue;  // group not complete yet
+          __syncwarp();
+          const int gcol0 = n_blk * BN + (c * 16 + 16 - GW);  // first column of the group
+          const int row_base = m_blk * BM + quad * 32;
+#pragma unroll
+          for (int it = 0; it < (32 * UNITS) / 32; ++it) {
+            const int idx = it * 32 + lane;
+            const int r = idx / UNITS, u = idx % UNITS;
+            const int grow = row_base + r, gcol = gcol0 + u * 8;
+            if (grow < p.M && gcol < p.N) {
+              const uint4 w = my_stage[r * 8 + (u ^ (r & 7))];
+              const size_t eoff = (static_cast<size_t>(grow) * p.ldo + gcol) * 2;
+              if (p.out_mode == 0) {
+                *reinterpret_cast<uint4*>(reinterpret_cast<char*>(p.out) + eoff) = w;
+              } else if (p.mc_out != 0) {
+                multimem_st_v4(reinterpret_cast<char*>(p.mc_out) + p.slot_off + eoff, w.x, w.y, w.z, w.w);
+              } else {
+                for (int pr = 0; pr < p.world; ++pr)
+                  *reinterpret_cast<uint4*>(reinterpret_cast<char*>(p.peer_out[pr]) + p.slot_off + eoff) = w;
+              }
+            }
+          }
+          __syncwarp();
+          continue;
         }
         if (!row_ok) continue;
         const bool full = (col0 + 16 <= p.N);
