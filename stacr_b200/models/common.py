@@ -68,8 +68,10 @@ def lm_loss(logits_or_hidden, labels, lm_head: nn.Linear | None = None, chunk: i
         hidden = logits_or_hidden[:, :-1].reshape(-1, logits_or_hidden.shape[-1])
         target = labels[:, 1:].reshape(-1)
         return nn_ops.linear_cross_entropy(hidden, lm_head.weight, target, chunk=chunk)
-    logits = logits_or_hidden[:, :-1].reshape(-1, logits_or_hidden.shape[-1])
-    return nn_ops.cross_entropy(logits, labels[:, 1:].reshape(-1))
+    # every position is scored against the next token; the last one has none and is masked out, which keeps the
+    # [B, S, V] logits as they are (slicing off the last position would copy the whole tensor, forward and backward)
+    shifted = torch.cat((labels[:, 1:], labels.new_full((labels.shape[0], 1), -100)), dim=1)
+    return nn_ops.cross_entropy(logits_or_hidden.reshape(-1, logits_or_hidden.shape[-1]), shifted.reshape(-1))
 
 
 def init_weights(module: nn.Module, std: float = 0.02) -> None:

@@ -237,7 +237,7 @@ __global__ void __launch_bounds__(256) gelu_bwd_kernel(const uint4* __restrict__
 // dlogits = (softmax - onehot) * inv_valid and the row loss.  Rows with target == -100 get zeros.
 __global__ void __launch_bounds__(512) cross_entropy_kernel(const __nv_bfloat16* __restrict__ logits, const long long* __restrict__ target,
                                                             int v, const float* __restrict__ inv_valid, __nv_bfloat16* __restrict__ dlogits,
-                                                            float* __restrict__ row_loss) {
+                                                            float* __restrict__ row_loss, float* __restrict__ row_lse) {
   __shared__ float s_m[16], s_s[16];
   __shared__ float s_max, s_lse;
   const int row = blockIdx.x;
@@ -246,8 +246,12 @@ __global__ void __launch_bounds__(512) cross_entropy_kernel(const __nv_bfloat16*
   const uint4* lr = reinterpret_cast<const uint4*>(logits + static_cast<size_t>(row) * v);
   uint4* dr = reinterpret_cast<uint4*>(dlogits + static_cast<size_t>(row) * v);
   if (tgt < 0) {  // ignored row
-    for (int i = threadIdx.x; i < nvec; i += blockDim.x) dr[i] = make_uint4(0, 0, 0, 0);
-    if (threadIdx.x == 0) row_loss[row] = 0.f;
+    if (dlogits != nullptr)
+      for (int i = threadIdx.x; i < nvec; i += blockDim.x) dr[i] = make_uint4(0, 0, 0, 0);
+    if (threadIdx.x == 0) {
+      row_loss[row] = 0.f;
+      if (row_lse) row_lse[row] = 0.f;
+    }
     return;
   }
   float m = -INFINITY, s = 0.f;
@@ -285,6 +289,13 @@ __global__ void __launch_bounds__(512) cross_entropy_kernel(const __nv_bfloat16*
   }
   __syncthreads();
   const float lse = s_lse;
+  if (dlogits == nullptr) {  // loss only: the gradient is produced by cross_entropy_bwd_kernel when (and if) it is asked for
+    if (threadIdx.x == 0) {
+      row_loss[row] = lse - __bfloat162float(logits[static_cast<size_t>(row) * v + tgt]);
+      if (row_lse) row_lse[row] = lse;
+    }
+    return;
+  }
   const float scale = *inv_valid;
   for (int i = threadIdx.x; i < nvec; i += blockDim.x) {
     float f[8];
@@ -296,6 +307,35 @@ __global__ void __launch_bounds__(512) cross_entropy_kernel(const __nv_bfloat16*
         row_loss[row] = lse - f[j];
         p -= 1.f;
       }
+      f[j] = p * scale;
+    }
+    dr[i] = pack8(f);
+  }
+}
+
+// dlogits = (softmax(logits) - onehot(target)) * inv_valid * dloss from the saved row log-sum-exp: one read of the logits
+// and one write, with the upstream scalar gradient folded in (no separate scaling pass over a [rows, vocab] tensor).
+__global__ void __launch_bounds__(512) cross_entropy_bwd_kernel(const __nv_bfloat16* __restrict__ logits, const long long* __restrict__ target,
+                                                                int v, const float* __restrict__ row_lse, const float* __restrict__ inv_valid,
+                                                                const float* __restrict__ dloss, __nv_bfloat16* __restrict__ dlogits) {
+  const int row = blockIdx.x;
+  const long long tgt = target[row];
+  const int nvec = v >> 3;
+  const uint4* lr = reinterpret_cast<const uint4*>(logits + static_cast<size_t>(row) * v);
+  uint4* dr = reinterpret_cast<uint4*>(dlogits + static_cast<size_t>(row) * v);
+  if (tgt < 0) {
+    for (int i = threadIdx.x; i < nvec; i += blockDim.x) dr[i] = make_uint4(0, 0, 0, 0);
+    return;
+  }
+  const float lse = row_lse[row];
+  const float scale = *inv_valid * *dloss;
+  for (int i = threadIdx.x; i < nvec; i += blockDim.x) {
+    float f[8];
+    unpack8(__ldg(lr + i), f);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      float p = __expf(f[j] - lse);
+      if (i * 8 + j == tgt) p -= 1.f;
       f[j] = p * scale;
     }
     dr[i] = pack8(f);
@@ -425,12 +465,23 @@ extern "C" int sb_gelu_bwd(const void* dy, const void* x, void* dx, long long nu
 }
 
 // Row losses and dlogits for bf16 logits [rows, v] (v % 8 == 0); inv_valid = 1 / (#targets != -100) on the device.
+// dlogits == NULL: losses (and, when row_lse != NULL, the row log-sum-exp for sb_cross_entropy_bwd) only.
 extern "C" int sb_cross_entropy(const void* logits, const long long* target, int rows, int v, const float* inv_valid, void* dlogits,
-                                float* row_loss, void* stream) {
+                                float* row_loss, float* row_lse, void* stream) {
   if (rows <= 0) return 0;
   if (v % 8) return -2;
   sb::cross_entropy_kernel<<<rows, 512, 0, static_cast<cudaStream_t>(stream)>>>(
-      static_cast<const __nv_bfloat16*>(logits), target, v, inv_valid, static_cast<__nv_bfloat16*>(dlogits), row_loss);
+      static_cast<const __nv_bfloat16*>(logits), target, v, inv_valid, static_cast<__nv_bfloat16*>(dlogits), row_loss, row_lse);
+  return static_cast<int>(cudaGetLastError());
+}
+
+// dlogits (may alias logits) = (softmax - onehot) * inv_valid * dloss; inv_valid and dloss are device scalars.
+extern "C" int sb_cross_entropy_bwd(const void* logits, const long long* target, int rows, int v, const float* row_lse, const float* inv_valid,
+                                    const float* dloss, void* dlogits, void* stream) {
+  if (rows <= 0) return 0;
+  if (v % 8) return -2;
+  sb::cross_entropy_bwd_kernel<<<rows, 512, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(logits), target, v, row_lse, inv_valid, dloss, static_cast<__nv_bfloat16*>(dlogits));
   return static_cast<int>(cudaGetLastError());
 }
 

@@ -58,17 +58,29 @@ def gelu_bwd(dy: torch.Tensor, x: torch.Tensor, tanh_form: bool) -> torch.Tensor
 
 
 def cross_entropy_fwd(logits: torch.Tensor, target: torch.Tensor):
-    """Mean loss over valid rows and ``d loss / d logits`` (already divided by the valid count)."""
+    """Mean loss over valid rows; returns ``(loss, target_int64, row_lse, inv_valid)`` for :func:`cross_entropy_bwd`."""
     rows, v = logits.shape
     target = target.to(torch.int64)
     inv_valid = 1.0 / (target != -100).sum().clamp_min(1).float()
-    dlogits = torch.empty_like(logits)
     row_loss = torch.empty(rows, dtype=torch.float32, device=logits.device)
-    rc = _lib.load().sb_cross_entropy(_lib.ptr(logits), _lib.ptr(target), c_int(rows), c_int(v), _lib.ptr(inv_valid), _lib.ptr(dlogits),
-                                      _lib.ptr(row_loss), _lib.stream_ptr())
+    row_lse = torch.empty(rows, dtype=torch.float32, device=logits.device)
+    rc = _lib.load().sb_cross_entropy(_lib.ptr(logits), _lib.ptr(target), c_int(rows), c_int(v), _lib.ptr(inv_valid), _lib.ptr(None),
+                                      _lib.ptr(row_loss), _lib.ptr(row_lse), _lib.stream_ptr())
     _lib.check_rc(rc, "sb_cross_entropy")
     _lib.count(1)
-    return row_loss.sum() * inv_valid, dlogits
+    return row_loss.sum() * inv_valid, target, row_lse, inv_valid
+
+
+def cross_entropy_bwd(logits: torch.Tensor, target: torch.Tensor, row_lse: torch.Tensor, inv_valid: torch.Tensor, dloss: torch.Tensor) -> torch.Tensor:
+    """``d loss / d logits`` scaled by the upstream scalar ``dloss`` (a device tensor: no host read)."""
+    rows, v = logits.shape
+    dlogits = torch.empty_like(logits)
+    scale = dloss.detach().float().reshape(1)
+    rc = _lib.load().sb_cross_entropy_bwd(_lib.ptr(logits), _lib.ptr(target), c_int(rows), c_int(v), _lib.ptr(row_lse), _lib.ptr(inv_valid),
+                                          _lib.ptr(scale), _lib.ptr(dlogits), _lib.stream_ptr())
+    _lib.check_rc(rc, "sb_cross_entropy_bwd")
+    _lib.count(1)
+    return dlogits
 
 
 def cast_bf16(src: torch.Tensor) -> torch.Tensor:

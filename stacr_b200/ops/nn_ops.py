@@ -73,21 +73,24 @@ def gelu(x, approximate: str = "none"):
 
 # ------------------------------------------------------------------------------ cross-entropy
 class _CrossEntropyFn(torch.autograd.Function):
-    """Mean cross-entropy over rows with ``target != -100``; the forward also produces d(logits)."""
+    """Mean cross-entropy over rows with ``target != -100``.  Forward reads the logits once (loss and row log-sum-exp);
+    backward reads them once more and writes the gradient with the upstream scalar folded in."""
 
     @staticmethod
     def forward(ctx, logits, target):
         from . import nn_kernels
 
-        loss, dlogits = nn_kernels.cross_entropy_fwd(logits.contiguous(), target.contiguous())
-        ctx.save_for_backward(dlogits)
+        logits = logits.contiguous()
+        loss, tgt, lse, inv_valid = nn_kernels.cross_entropy_fwd(logits, target.contiguous())
+        ctx.save_for_backward(logits, tgt, lse, inv_valid)
         return loss
 
     @staticmethod
     def backward(ctx, dloss):
-        (dlogits,) = ctx.saved_tensors
-        # dlogits already holds (softmax - onehot) / n_valid; scale by the upstream scalar gradient
-        return dlogits * dloss.to(dlogits.dtype), None
+        from . import nn_kernels
+
+        logits, tgt, lse, inv_valid = ctx.saved_tensors
+        return nn_kernels.cross_entropy_bwd(logits, tgt, lse, inv_valid, dloss), None
 
 
 def cross_entropy(logits, target):
