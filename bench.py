@@ -199,8 +199,8 @@ def run_ours(args):
         secs_e2e = timed_region(torch, dist, args.steps, step_e2e, world)
     _lib.check_status(dev)
     peak = torch.cuda.max_memory_allocated(dev)
-    if args.kernel_table and rank == 0:
-        kernel_table(torch, step_device, args.kernel_table)
+    if args.kernel_table:  # every rank runs the extra steps (their collectives need all ranks); rank 0 writes the table
+        kernel_table(torch, step_device, args.kernel_table if rank == 0 else os.devnull)
     rows = batch * seq
     factor_bytes = sum(layer.stored_bytes(rows, 2)["total"] for layer in layers)
     dense_bytes = sum(rows * layer.in_features * 2 for layer in layers)

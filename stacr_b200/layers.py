@@ -320,9 +320,16 @@ class STACRFunction(torch.autograd.Function):
                     stacr_ops.weight_grad(ga, coeff, q.float(), residual, ctx.out_features, ctx.in_features, ctx.transposed, torch.float32, sink=sink)
                     sink.done()
                 else:
+                    # a gradient synchroniser may lend the parameter's slot of its flat buffer for the first
+                    # backward pass after zero_grad: the kernel then writes there and nothing is copied or accumulated
+                    slot = getattr(weight, "_sb_grad_out", None) if getattr(weight, "_sb_grad_fresh", False) else None
+                    if slot is not None and slot.dtype == weight.dtype:
+                        weight._sb_grad_fresh = False
+                    else:
+                        slot = None
                     gw = stacr_ops.weight_grad(
                         ga, coeff, q.float(), residual, ctx.out_features, ctx.in_features, ctx.transposed, weight.dtype
-                        if weight.dtype in (torch.float32, torch.bfloat16) else torch.float32,
+                        if weight.dtype in (torch.float32, torch.bfloat16) else torch.float32, out=slot,
                     ).to(weight.dtype)
             if ctx.needs_input_grad[2]:
                 gb = stacr_ops.colsum(ga).to(ctx.bias_dtype)

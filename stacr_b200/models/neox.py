@@ -83,7 +83,9 @@ class NeoXAttention(nn.Module):
 
     def forward(self, x, attention_mask=None):
         b, s, d = x.shape
-        qkv = self.query_key_value(x)
+        # project the flattened tokens: the 2-D result is a tensor of its own, whereas the 3-D form would be a VIEW of it,
+        # and an in-place op on a view makes autograd re-materialise the base (three extra copies of qkv per layer)
+        qkv = self.query_key_value(x.reshape(b * s, d))
         if nn_ops.rotary_qk_supported(qkv, self.head_dim, self.rot):
             cos, sin = self._half_tables(s, x.device)
             qkv = nn_ops.rotary_qk(qkv, cos, sin, s, self.n_head, self.head_dim, self.rot)  # fused, in place

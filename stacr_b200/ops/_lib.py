@@ -95,11 +95,25 @@ def check_status(device=None, *, reset: bool = True) -> None:
         raise KernelError(f"kernel status {code}: {STATUS_TEXT.get(code, 'unknown')}")
 
 
+_reserved_sms = 0
+
+
+def reserve_sms(n: int) -> None:
+    """Leave ``n`` SMs to kernels that run next to the compute stream (collectives overlapped with backward).
+
+    The persistent GEMMs launch one CTA per SM and split their tiles statically among them; a CTA that finds its SM
+    taken starts late and delays the whole kernel, so while a communication kernel is resident the GEMMs are launched
+    with that many CTAs fewer.
+    """
+    global _reserved_sms
+    _reserved_sms = max(0, int(n))
+
+
 def sm_count(device=None) -> int:
     idx = torch.cuda.current_device() if device is None else torch.device(device).index
     if idx not in _sms:
         _sms[idx] = torch.cuda.get_device_properties(idx).multi_processor_count
-    return _sms[idx]
+    return max(1, _sms[idx] - _reserved_sms)
 
 
 def ptr(t: torch.Tensor | None) -> ctypes.c_void_p:

@@ -386,6 +386,11 @@ static int make_map(CUtensorMap* map, const void* ptr, uint64_t inner, uint64_t 
   return r == CUDA_SUCCESS ? 0 : -2;
 }
 
+// The same encoder for the other translation units of the library.
+int make_tensor_map_bf16(CUtensorMap* map, const void* ptr, uint64_t inner, uint64_t outer, uint64_t ld, uint32_t box_outer) {
+  return make_map(map, ptr, inner, outer, ld, box_outer);
+}
+
 template <int BN, bool A_MN, bool B_MN>
 static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, int sms,
                        cudaStream_t stream) {

@@ -9,6 +9,11 @@ import torch
 from . import _lib
 
 
+import os
+
+_TWO_CTA_DEFAULT = os.environ.get("STACR_GEMM_2CTA", "1") == "1"
+
+
 def _pick_bn(m: int, n: int, b_mn: bool, sms: int) -> int:
     if n <= 16 and not b_mn:
         return 16
@@ -41,6 +46,7 @@ def gemm(
     splits: int = 1,
     bn: int | None = None,
     alpha: float = 1.0,
+    two_cta: bool | None = None,
 ) -> torch.Tensor:
     """``out[M,N] = alpha * A @ B^T (+ bias)`` with bf16 operands and fp32 accumulation.
 
@@ -80,6 +86,18 @@ def gemm(
     if bn is None:
         bn = _pick_bn(m, n, b_mn, sms)
     lib = _lib.load()
+    if two_cta is None:
+        two_cta = _TWO_CTA_DEFAULT and bn == 256 and m >= 512 and n >= 512
+    if two_cta and not atomic:
+        # CTA pairs on 256 x 256 tiles (tcgen05.mma.cta_group::2): each CTA stages half of the B tile
+        rc = lib.sb_gemm_bf16_2cta(
+            _lib.ptr(a), _lib.ptr(b), _lib.ptr(out), _lib.ptr(bias), ctypes.c_int(m), ctypes.c_int(n), ctypes.c_int(k),
+            ctypes.c_int(a.stride(0)), ctypes.c_int(b.stride(0)), ctypes.c_int(out.stride(0)), ctypes.c_int(int(a_mn)), ctypes.c_int(int(b_mn)),
+            ctypes.c_int(mode), ctypes.c_float(alpha), ctypes.c_int(sms), _lib.ptr(_lib.status_word(a.device)), _lib.stream_ptr(),
+        )
+        _lib.check_rc(rc, "sb_gemm_bf16_2cta")
+        _lib.count(1)
+        return out
     rc = lib.sb_gemm_bf16(
         _lib.ptr(a), _lib.ptr(b), _lib.ptr(out), _lib.ptr(bias),
         ctypes.c_int(m), ctypes.c_int(n), ctypes.c_int(k),

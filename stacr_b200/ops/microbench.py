@@ -49,7 +49,14 @@ def case_gemm(args, pk) -> list:
     b = torch.randn(n, k, device="cuda").bfloat16()
     out = []
     flops = 2.0 * m * n * k
-    ms = timed(lambda: gemm(a, b, bn=args.bn), args.iters, args.warmup)
+    if args.two_cta:
+        ref = torch.matmul(a, b.t()).float()
+        got = gemm(a, b, two_cta=True).float()
+        err = float((got - ref).abs().max() / ref.abs().max())
+        ms = timed(lambda: gemm(a, b, two_cta=True), args.iters, args.warmup)
+        out.append({"kernel": "gemm2_bf16_kernel (cta_group::2)", "shape": [m, n, k], "ms": ms, "tflops": flops / ms / 1e9, "max_rel_err_vs_cublas": err,
+                    f"frac_of_{pk['source']}_bf16": flops / ms / 1e9 / pk["bf16_tflops"]})
+    ms = timed(lambda: gemm(a, b, bn=args.bn, two_cta=False), args.iters, args.warmup)
     out.append({"kernel": "gemm_bf16_kernel", "shape": [m, n, k], "bn": args.bn, "ms": ms, "tflops": flops / ms / 1e9,
                 f"frac_of_{pk['source']}_bf16": flops / ms / 1e9 / pk["bf16_tflops"]})
     if not args.only_ours:
@@ -117,6 +124,7 @@ def main(argv=None) -> int:
     parser.add_argument("--k", type=int, default=2048)
     parser.add_argument("--bn", type=int, default=256)
     parser.add_argument("--only-ours", action="store_true")
+    parser.add_argument("--two-cta", action="store_true", help="also run the CTA-pair kernel and check it against the library")
     parser.add_argument("--rows", type=int, default=8192)
     parser.add_argument("--features", type=int, default=8192)
     parser.add_argument("--out", type=int, default=2048)

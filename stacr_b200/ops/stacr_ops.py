@@ -166,6 +166,7 @@ def weight_grad(
     transposed: bool,
     out_dtype: torch.dtype,
     sink=None,
+    out: torch.Tensor | None = None,
 ):
     """``dW = (dY^T C) Q^T + dY^T S`` without rebuilding the dense input.
 
@@ -210,7 +211,10 @@ def weight_grad(
         _lib.count(2 if nnz >= _plan_target() else 1)
         return None
     shape = (in_features, out_features) if transposed else (out_features, in_features)
-    out = torch.empty(shape, dtype=out_dtype, device=dev)
+    if out is None:
+        out = torch.empty(shape, dtype=out_dtype, device=dev)
+    else:  # the caller's buffer (for example the parameter's slot of a flat gradient buffer) is written directly
+        assert out.shape == shape and out.dtype == out_dtype and out.is_contiguous()
     rc = _lib.load().sb_dw_fused(
         _lib.ptr(t), c_int(t.stride(0)), _lib.ptr(basis_fp32), c_int(r), _lib.ptr(dy), c_int(dy.stride(0)), _lib.ptr(colptr),
         _lib.ptr(rows_s), _lib.ptr(vals_s), c_int(out_features), c_int(in_features), c_int(int(transposed)),

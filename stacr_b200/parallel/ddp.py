@@ -114,8 +114,12 @@ class GradSync:
         self.backend = self._pick_backend(backend, dev)
         self.flat = self._allocate(cursor, dev)
         self.flat.zero_()
-        for p, off in zip(self.params, offsets):
-            p.grad = self.flat[off:off + p.numel()].view_as(p)
+        self._views = [self.flat[off:off + p.numel()].view_as(p) for p, off in zip(self.params, offsets)]
+        for p, view in zip(self.params, self._views):
+            p.grad = view
+            p._sb_grad_out = view          # compressed layers write their first gradient of a step straight into the slot
+            p._sb_grad_fresh = False
+        self._written = [True] * len(self.params)
         # buckets over the reversed parameter list (backward order)
         limit = int(bucket_mb * 1024 * 1024 / 4)
         self.buckets: list[tuple[int, int]] = []
@@ -186,10 +190,12 @@ class GradSync:
     def _make_hook(self, index: int):
         if index < self.n_fused:
             def fused_hook(param):
+                self._adopt(index, param)
                 self._fused_state[index] = 2      # autograd accumulated a dense gradient locally (layer ran uncompressed)
             return fused_hook
 
         def hook(param):
+            self._adopt(index, param)
             if not self._syncing:
                 return
             b = self._bucket_of[index]
@@ -201,12 +207,25 @@ class GradSync:
     def _launch(self, b: int) -> None:
         lo, hi = self.buckets[b]
         self._launched += 1
+        if self.backend == "symm" and self._stream is not None:
+            from ..ops import _lib
+
+            _lib.reserve_sms(self._symm.max_ctas)   # until finish(): the collectives of this step share the GPU with backward
         if self._stream is None:
             self._reduce(lo, hi)
             return
         self._stream.wait_stream(torch.cuda.current_stream(self.device))
         with torch.cuda.stream(self._stream):
             self._reduce(lo, hi)
+
+    def _adopt(self, index: int, param) -> None:
+        """Make the parameter's gradient live in its slot of the flat buffer (a copy only if autograd produced it elsewhere)."""
+        view = self._views[index]
+        g = param.grad
+        if g is not None and g.data_ptr() != view.data_ptr():
+            view.copy_(g)
+            param.grad = view
+        self._written[index] = True
 
     # ------------------------------------------------------------------ fused parameters
     def _fused_done(self, index: int) -> None:
@@ -244,19 +263,36 @@ class GradSync:
 
     # ------------------------------------------------------------------ step protocol
     def zero_grad(self) -> None:
-        """Clear the flat buffer (one memset) and re-arm the buckets.  Call instead of ``optimizer.zero_grad``."""
-        self.flat.zero_()
-        if self.n_fused and self.backend == "symm":
+        """Forget the gradients and re-arm the buckets.  Call instead of ``optimizer.zero_grad``.
+
+        Nothing is cleared up front: every parameter's gradient is dropped (``grad = None``) so that autograd hands over
+        its first gradient of the step instead of accumulating into zeros, and the hook moves it into the slot (or finds
+        it already there when a compressed layer wrote the slot directly).  Slots that no backward pass touched are
+        cleared in ``finish``.  The fused reduce-scatter path still needs zeros in every copy before any rank adds.
+        """
+        fused_adds = self.n_fused and self.backend == "symm"
+        if fused_adds:
+            self.flat[: self.sinks[-1].region_hi].zero_()
             self._symm.barrier()   # no peer may add into this buffer before it is cleared
+        for i, p in enumerate(self.params):
+            if fused_adds and i < self.n_fused:
+                p.grad = self._views[i]
+                self._written[i] = True
+                continue
+            p.grad = None
+            p._sb_grad_fresh = True
+            self._written[i] = False
         self._fused_state = [0] * self.n_fused
         self._pending = list(self._size)
         self._launched = 0
-        for p in self.params:
-            if p.grad is None or p.grad.data_ptr() < self.flat.data_ptr():
-                raise RuntimeError("a gradient view was replaced; keep set_to_none=False semantics with GradSync")
 
     def finish(self) -> None:
         """Reduce buckets whose hooks did not all fire (unused parameters) and join the communication stream."""
+        for i, done in enumerate(self._written):
+            if not done:                      # no gradient reached this parameter in this step
+                self._views[i].zero_()
+                self.params[i].grad = self._views[i]
+                self._written[i] = True
         for b, left in enumerate(self._pending):
             if left > 0:
                 self._pending[b] = 0
@@ -267,14 +303,19 @@ class GradSync:
             self._finish_fused(i)
         if self._stream is not None:
             torch.cuda.current_stream(self.device).wait_stream(self._stream)
+        if self.backend == "symm":
+            from ..ops import _lib
+
+            _lib.reserve_sms(0)
 
     def close(self) -> None:
         for h in self._hooks:
             h.remove()
         self._hooks = []
-        for p in self.params[:self.n_fused]:
-            if hasattr(p, "_sb_grad_sink"):
-                del p._sb_grad_sink
+        for p in self.params:
+            for attr in ("_sb_grad_sink", "_sb_grad_out", "_sb_grad_fresh"):
+                if hasattr(p, attr):
+                    delattr(p, attr)
 
 
 def all_reduce_mean_(tensor: torch.Tensor, group=None) -> torch.Tensor:

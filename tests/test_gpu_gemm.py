@@ -72,3 +72,23 @@ def test_gemm_repeatable_bits():
     first = gemm(a, b)
     for _ in range(3):
         assert torch.equal(first, gemm(a, b))
+
+
+@pytest.mark.parametrize("a_mn,b_mn", [(False, False), (False, True), (True, False), (True, True)])
+@pytest.mark.parametrize("m,n,k,out_dtype", [(512, 512, 256, torch.bfloat16), (1024, 768, 192, torch.float32), (704, 520, 136, torch.bfloat16)])
+def test_cta_pair_kernel_matches_fp32_reference(a_mn, b_mn, m, n, k, out_dtype):
+    """tcgen05.mma.cta_group::2 on 256 x 256 pair tiles, all operand layouts, ragged edges and a bias."""
+    from stacr_b200.ops import _lib
+    from stacr_b200.ops.gemm import gemm
+
+    torch.manual_seed(m + n + k)
+    a = torch.randn(m, k, device="cuda").bfloat16()
+    b = torch.randn(n, k, device="cuda").bfloat16()
+    bias = torch.randn(n, device="cuda")
+    ref = a.float() @ b.float().t() + bias
+    aa = a.t().contiguous() if a_mn else a
+    bb = b.t().contiguous() if b_mn else b
+    got = gemm(aa, bb, a_mn=a_mn, b_mn=b_mn, bias=bias, out_dtype=out_dtype, two_cta=True)
+    _lib.check_status()
+    tol = 2e-2 if out_dtype == torch.bfloat16 else 2e-3
+    assert float((got.float() - ref).abs().max() / ref.abs().max()) < tol
