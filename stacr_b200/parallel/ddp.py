@@ -123,6 +123,7 @@ class GradSync:
         # buckets over the reversed parameter list (backward order)
         limit = int(bucket_mb * 1024 * 1024 / 4)
         self.buckets: list[tuple[int, int]] = []
+        self._members: list[list[int]] = []
         self._bucket_of: dict[int, int] = {}
         self._pending: list[int] = []
         hi = cursor
@@ -134,6 +135,7 @@ class GradSync:
             if hi - lo >= limit or idx == self.n_fused:
                 b = len(self.buckets)
                 self.buckets.append((lo, hi))
+                self._members.append(list(members))
                 for m in members:
                     self._bucket_of[m] = b
                 self._pending.append(len(members))
@@ -195,7 +197,7 @@ class GradSync:
             return fused_hook
 
         def hook(param):
-            self._adopt(index, param)
+            self._written[index] = True       # moved into its slot together with the rest of its bucket
             if not self._syncing:
                 return
             b = self._bucket_of[index]
@@ -204,9 +206,26 @@ class GradSync:
                 self._launch(b)
         return hook
 
+    def _adopt_bucket(self, b: int) -> None:
+        """Move the gradients of bucket ``b`` that autograd produced elsewhere into their slots with one multi-tensor copy."""
+        src, dst = [], []
+        for i in self._members[b]:
+            p, view = self.params[i], self._views[i]
+            g = p.grad
+            if g is None:
+                view.zero_()
+            elif g.data_ptr() != view.data_ptr():
+                src.append(g)
+                dst.append(view)
+            p.grad = view
+            self._written[i] = True
+        if src:
+            torch._foreach_copy_(dst, src)
+
     def _launch(self, b: int) -> None:
         lo, hi = self.buckets[b]
         self._launched += 1
+        self._adopt_bucket(b)
         if self.backend == "symm" and self._stream is not None:
             from ..ops import _lib
 
@@ -270,13 +289,15 @@ class GradSync:
         it already there when a compressed layer wrote the slot directly).  Slots that no backward pass touched are
         cleared in ``finish``.  The fused reduce-scatter path still needs zeros in every copy before any rank adds.
         """
-        fused_adds = self.n_fused and self.backend == "symm"
-        if fused_adds:
+        if self.n_fused:
+            # slots that the gradient kernels add into (locally or from other ranks) must start from zero
             self.flat[: self.sinks[-1].region_hi].zero_()
-            self._symm.barrier()   # no peer may add into this buffer before it is cleared
+            if self.backend == "symm":
+                self._symm.barrier()   # no peer may add into this buffer before it is cleared
         for i, p in enumerate(self.params):
-            if fused_adds and i < self.n_fused:
+            if i < self.n_fused:
                 p.grad = self._views[i]
+                p._sb_grad_fresh = False
                 self._written[i] = True
                 continue
             p.grad = None
@@ -288,15 +309,10 @@ class GradSync:
 
     def finish(self) -> None:
         """Reduce buckets whose hooks did not all fire (unused parameters) and join the communication stream."""
-        for i, done in enumerate(self._written):
-            if not done:                      # no gradient reached this parameter in this step
-                self._views[i].zero_()
-                self.params[i].grad = self._views[i]
-                self._written[i] = True
         for b, left in enumerate(self._pending):
-            if left > 0:
+            if left > 0 or any(self.params[i].grad is None or self.params[i].grad.data_ptr() != self._views[i].data_ptr() for i in self._members[b]):
                 self._pending[b] = 0
-                self._launch(b)
+                self._launch(b)       # adopts (or clears) every slot of the bucket first
         for i in range(self.n_fused):
             if self._fused_state[i] == 0 and self.backend == "symm":
                 self._fused_state[i] = 1   # unused this step on this rank: peers may still have added into our slice
