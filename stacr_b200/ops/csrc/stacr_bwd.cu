@@ -9,6 +9,8 @@
 // the rank-r expansion is fused into the same pass.  The dense X is never rebuilt.
 // Replaces the COO build + coalesce + cuSPARSE SpMM + two library GEMMs of the reference
 // (stacr/layers.py:173-196 there).
+#include <cstdlib>
+
 #include "common.cuh"
 
 namespace sb {
@@ -396,7 +398,15 @@ static inline bool dw_wide(int o_total, int ldy, const void* dy) {
 }  // namespace sb
 
 // Target number of residual entries one weight-gradient CTA walks (see col_scan_kernel).
-extern "C" int sb_dw_plan_target() { return 384; }
+extern "C" int sb_dw_plan_target() {
+  static int target = 0;
+  if (target == 0) {
+    const char* env = getenv("STACR_DW_TARGET");  // tuning knob; read once
+    const int v = env ? atoi(env) : 0;
+    target = (v >= 64 && v <= 65536) ? v : 384;
+  }
+  return target;
+}
 
 // Bucket the residual entries by input feature.  counts/cursor: int32 [n] scratch (counts zeroed by the
 // caller); colptr: int32 [n+1]; rows_sorted/vals_sorted: [nnz].  plan (optional): int32 scratch of

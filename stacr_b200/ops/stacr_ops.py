@@ -54,6 +54,9 @@ def transpose_pad(c: torch.Tensor) -> torch.Tensor:
     return out
 
 
+_META: dict = {}
+
+
 def residual_topk(
     x: torch.Tensor,
     coeff: torch.Tensor,
@@ -75,12 +78,18 @@ def residual_topk(
     total = sum(quotas)
     sms = _lib.sm_count(dev)
     parts = max(1, sms // nchunks)
-    hist = torch.zeros(nchunks * 32768, dtype=torch.int32, device=dev)
-    work = torch.zeros(6 * nchunks, dtype=torch.int32, device=dev)
-    offsets = [0]
-    for k in quotas[:-1]:
-        offsets.append(offsets[-1] + k)
-    meta = torch.tensor([quotas, offsets], dtype=torch.int32).to(dev, non_blocking=True)
+    scratch = torch.zeros(nchunks * (32768 + 6), dtype=torch.int32, device=dev)   # histogram and counters: one fill
+    hist, work = scratch[: nchunks * 32768], scratch[nchunks * 32768:]
+    key = (dev.index, tuple(quotas))
+    meta = _META.get(key)
+    if meta is None:                      # per-chunk quotas and output offsets, uploaded once per distinct schedule
+        offsets = [0]
+        for k in quotas[:-1]:
+            offsets.append(offsets[-1] + k)
+        meta = torch.tensor([quotas, offsets], dtype=torch.int32).to(dev)
+        if len(_META) > 256:
+            _META.clear()
+        _META[key] = meta
     idx = torch.empty(total, dtype=index_dtype, device=dev)
     val = torch.empty(total, dtype=torch.bfloat16 if bits == 0 else torch.int8, device=dev)
     scale = torch.empty((), dtype=torch.float32, device=dev)
