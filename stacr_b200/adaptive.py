@@ -725,6 +725,29 @@ class STACRLowRankOnlyFunction(torch.autograd.Function):
         return gx, gw, gb, None, None, None
 
 
+def stacr_stored_bytes(batch: int, features: int, rank: int, residual_budget: float = 0.0, dtype: torch.dtype = torch.float32,
+                       coeff_bits: Optional[int] = None, residual_bits: Optional[int] = None, basis_dtype: Optional[torch.dtype] = None) -> dict:
+    """Bytes the adaptive layer keeps for one batch, as a flat dict (the breakdown comes from ``memory_accounting``).
+
+    Parity: stacr/adaptive.py:3749-3789 of the reference project.
+    """
+    from .memory_accounting import stacr_stored_bytes as _breakdown
+
+    b = _breakdown(batch, features, rank, residual_budget, dtype, coeff_bits=coeff_bits, residual_bits=residual_bits, basis_dtype=basis_dtype,
+                   include_meta=False, include_basis=False)
+    total = b.total_bytes
+    dense = batch * features * torch.empty((), dtype=dtype).element_size()
+    return {"total_bytes": total, "basis_bytes": b.details.get("basis_bytes", 0), "coefficients_bytes": b.details.get("coeff_bytes", 0),
+            "residual_bytes": b.details.get("residual_value_bytes", 0) + b.details.get("residual_index_bytes", 0),
+            "compression_ratio": dense / max(total, 1)}
+
+
+def stacr_compression_ratio(batch: int, features: int, rank: int, residual_budget: float = 0.0, coeff_bits: Optional[int] = None,
+                            residual_bits: Optional[int] = None) -> float:
+    """``dense bytes / stored bytes`` for fp32 activations (stacr/adaptive.py:3792-3813 of the reference project)."""
+    return stacr_stored_bytes(batch, features, rank, residual_budget, coeff_bits=coeff_bits, residual_bits=residual_bits)["compression_ratio"]
+
+
 class _TransposedProjection(nn.Module):
     """Linear-like facade over a Conv1D's ``[in, out]`` weight; keeps the original Parameters."""
 

@@ -49,6 +49,14 @@ def synthetic_token_examples(count: int, seq_len: int, vocab_size: int, seed: in
     return out
 
 
+def tokenize_text_dataset(dataset, tokenizer, text_key: str, max_length: int):
+    """Fixed-length tokenisation of a ``datasets`` table (truncate and pad to ``max_length``); the text columns are dropped."""
+    def encode(batch):
+        return tokenizer(batch[text_key], truncation=True, padding="max_length", max_length=max_length)
+
+    return dataset.map(encode, batched=True, remove_columns=dataset.column_names)
+
+
 def packed_text_blocks(texts, tokenizer, seq_len: int, max_examples: int | None = None) -> list[dict]:
     """Concatenate tokenised documents (EOS-separated) and cut fixed ``seq_len`` blocks."""
     eos = tokenizer.eos_token_id

@@ -403,7 +403,7 @@ extern "C" int sb_dw_plan_target() {
   if (target == 0) {
     const char* env = getenv("STACR_DW_TARGET");  // tuning knob; read once
     const int v = env ? atoi(env) : 0;
-    target = (v >= 64 && v <= 65536) ? v : 384;
+    target = (v >= 64 && v <= 65536) ? v : 256;
   }
   return target;
 }
