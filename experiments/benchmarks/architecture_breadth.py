@@ -1,0 +1,29 @@
+"""Nine additional transformer families and checkpoint composition.
+
+Grid ``architecture_breadth`` (deployment; 36 cells).  Parity: experiments/benchmarks/architecture_breadth.py.
+
+    python -m experiments.benchmarks.architecture_breadth --dry-run
+    python -m experiments.benchmarks.architecture_breadth --steps 20 --seeds 42
+"""
+
+from __future__ import annotations
+
+from . import _entry
+
+NAME = "architecture_breadth"
+
+
+def cells():
+    return _entry.cells(NAME)
+
+
+def run(seeds=(42,), output=None):
+    return _entry.run(NAME, seeds, output)
+
+
+def main(argv=None) -> int:
+    return _entry.main(NAME, argv)
+
+
+if __name__ == "__main__":
+    raise SystemExit(main())

@@ -1,0 +1,29 @@
+"""Dropout-pinned gradient fidelity of basis controls.
+
+Grid ``basis_fidelity`` (fidelity; 5 cells).  Parity: experiments/benchmarks/basis_fidelity.py.
+
+    python -m experiments.benchmarks.basis_fidelity --dry-run
+    python -m experiments.benchmarks.basis_fidelity --steps 20 --seeds 42
+"""
+
+from __future__ import annotations
+
+from . import _entry
+
+NAME = "basis_fidelity"
+
+
+def cells():
+    return _entry.cells(NAME)
+
+
+def run(seeds=(42,), output=None):
+    return _entry.run(NAME, seeds, output)
+
+
+def main(argv=None) -> int:
+    return _entry.main(NAME, argv)
+
+
+if __name__ == "__main__":
+    raise SystemExit(main())

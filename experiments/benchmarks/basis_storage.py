@@ -1,0 +1,29 @@
+"""Allocation-only duplicated-basis and residual-storage controls.
+
+Grid ``basis_storage`` (mechanism; 5 cells).  Parity: experiments/benchmarks/basis_storage.py.
+
+    python -m experiments.benchmarks.basis_storage --dry-run
+    python -m experiments.benchmarks.basis_storage --steps 20 --seeds 42
+"""
+
+from __future__ import annotations
+
+from . import _entry
+
+NAME = "basis_storage"
+
+
+def cells():
+    return _entry.cells(NAME)
+
+
+def run(seeds=(42,), output=None):
+    return _entry.run(NAME, seeds, output)
+
+
+def main(argv=None) -> int:
+    return _entry.main(NAME, argv)
+
+
+if __name__ == "__main__":
+    raise SystemExit(main())

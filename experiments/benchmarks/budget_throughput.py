@@ -1,0 +1,29 @@
+"""Batch and sequence throughput under a fixed memory budget.
+
+Grid ``budget_throughput`` (deployment; 12 cells).  Parity: experiments/benchmarks/budget_throughput.py.
+
+    python -m experiments.benchmarks.budget_throughput --dry-run
+    python -m experiments.benchmarks.budget_throughput --steps 20 --seeds 42
+"""
+
+from __future__ import annotations
+
+from . import _entry
+
+NAME = "budget_throughput"
+
+
+def cells():
+    return _entry.cells(NAME)
+
+
+def run(seeds=(42,), output=None):
+    return _entry.run(NAME, seeds, output)
+
+
+def main(argv=None) -> int:
+    return _entry.main(NAME, argv)
+
+
+if __name__ == "__main__":
+    raise SystemExit(main())

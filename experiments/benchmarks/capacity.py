@@ -1,0 +1,29 @@
+"""GPT-2 model and batch feasibility probes.
+
+Grid ``capacity`` (deployment; 18 cells).  Parity: experiments/benchmarks/capacity.py.
+
+    python -m experiments.benchmarks.capacity --dry-run
+    python -m experiments.benchmarks.capacity --steps 20 --seeds 42
+"""
+
+from __future__ import annotations
+
+from . import _entry
+
+NAME = "capacity"
+
+
+def cells():
+    return _entry.cells(NAME)
+
+
+def run(seeds=(42,), output=None):
+    return _entry.run(NAME, seeds, output)
+
+
+def main(argv=None) -> int:
+    return _entry.main(NAME, argv)
+
+
+if __name__ == "__main__":
+    raise SystemExit(main())

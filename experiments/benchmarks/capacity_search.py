@@ -1,0 +1,29 @@
+"""Ascending batch search to the first allocation failure.
+
+Grid ``capacity_search`` (deployment; 16 cells).  Parity: experiments/benchmarks/capacity_search.py.
+
+    python -m experiments.benchmarks.capacity_search --dry-run
+    python -m experiments.benchmarks.capacity_search --steps 20 --seeds 42
+"""
+
+from __future__ import annotations
+
+from . import _entry
+
+NAME = "capacity_search"
+
+
+def cells():
+    return _entry.cells(NAME)
+
+
+def run(seeds=(42,), output=None):
+    return _entry.run(NAME, seeds, output)
+
+
+def main(argv=None) -> int:
+    return _entry.main(NAME, argv)
+
+
+if __name__ == "__main__":
+    raise SystemExit(main())

@@ -1,0 +1,29 @@
+"""Full/selective checkpointing and disjoint/overlapping compression.
+
+Grid ``checkpoint_frontier`` (deployment; 7 cells).  Parity: experiments/benchmarks/checkpoint_frontier.py.
+
+    python -m experiments.benchmarks.checkpoint_frontier --dry-run
+    python -m experiments.benchmarks.checkpoint_frontier --steps 20 --seeds 42
+"""
+
+from __future__ import annotations
+
+from . import _entry
+
+NAME = "checkpoint_frontier"
+
+
+def cells():
+    return _entry.cells(NAME)
+
+
+def run(seeds=(42,), output=None):
+    return _entry.run(NAME, seeds, output)
+
+
+def main(argv=None) -> int:
+    return _entry.main(NAME, argv)
+
+
+if __name__ == "__main__":
+    raise SystemExit(main())

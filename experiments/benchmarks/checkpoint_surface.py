@@ -1,0 +1,29 @@
+"""Saved-surface depletion as checkpoint density increases.
+
+Grid ``checkpoint_surface`` (mechanism; 10 cells).  Parity: experiments/benchmarks/checkpoint_surface.py.
+
+    python -m experiments.benchmarks.checkpoint_surface --dry-run
+    python -m experiments.benchmarks.checkpoint_surface --steps 20 --seeds 42
+"""
+
+from __future__ import annotations
+
+from . import _entry
+
+NAME = "checkpoint_surface"
+
+
+def cells():
+    return _entry.cells(NAME)
+
+
+def run(seeds=(42,), output=None):
+    return _entry.run(NAME, seeds, output)
+
+
+def main(argv=None) -> int:
+    return _entry.main(NAME, argv)
+
+
+if __name__ == "__main__":
+    raise SystemExit(main())

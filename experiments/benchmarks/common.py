@@ -130,6 +130,95 @@ def stacr_on_blocks(model, cfg: dict, block_pred: Optional[Callable[[int], bool]
     return S.apply_stacr(model, surface="none", target_names=names, allow_empty=True, **cfg)
 
 
+def runtime_metadata() -> dict:
+    """Versions of the libraries in use, the CUDA toolkit torch was built for, the device name and whether the
+    in-tree kernel library is loaded.  Environment variables are never recorded."""
+    import importlib.metadata as md
+
+    versions = {}
+    for name in ("torch", "transformers", "datasets", "numpy"):
+        try:
+            versions[name] = md.version(name)
+        except md.PackageNotFoundError:
+            pass
+    from stacr_b200.ops import _lib
+
+    return {"versions": versions, "cuda": torch.version.cuda, "device": torch.cuda.get_device_name() if torch.cuda.is_available() else "cpu",
+            "kernel_library": bool(_lib.available())}
+
+
+def nvml_used(dev: int = 0) -> float:
+    """Device memory in use according to NVML, in GiB (all processes); NaN without NVML.  Read-only query."""
+    try:
+        import pynvml
+
+        pynvml.nvmlInit()
+        return gib(pynvml.nvmlDeviceGetMemoryInfo(pynvml.nvmlDeviceGetHandleByIndex(dev)).used)
+    except Exception:
+        return float("nan")
+
+
+def blocks_of(model) -> list:
+    """The model's transformer blocks (``RuntimeError`` for an unknown layout)."""
+    try:
+        return transformer_blocks(model)
+    except ValueError as exc:
+        raise RuntimeError(f"cannot locate blocks for {type(model).__name__}") from exc
+
+
+def apply_cpu_offload(model, every: int = 1, offset: int = 0) -> int:
+    """Keep the saved tensors of every ``every``-th block in pinned host memory; returns the number of blocks."""
+    return apply_selective_offload(model, every, offset)
+
+
+def freeze_surface_params(model, surface: str = "mlp", min_features: int = 256) -> int:
+    """Turn off gradients of the projections a surface selects (for probes that train everything else); returns the count."""
+    names = set(S.select_target_names(model, surface=surface, min_features=min_features))
+    count = 0
+    for name, module in model.named_modules():
+        if name in names:
+            for p in module.parameters(recurse=False):
+                p.requires_grad_(False)
+                count += 1
+    return count
+
+
+def restrict_cfg_to_blocks(model, cfg: dict, block_pred: Callable[[int], bool]) -> dict:
+    """A copy of ``cfg`` whose selection is the explicit list of surface projections inside the chosen blocks."""
+    names = block_target_names(model, transformer_blocks(model), block_pred, surface=str(cfg.get("surface", "mlp")),
+                               min_features=int(cfg.get("min_features", 256)))
+    out = dict(cfg)
+    out["surface"], out["extra_names"] = "none", names
+    return out
+
+
+def instrument_rows(layers) -> tuple:
+    """Count the rows (tokens) each layer sees: ``(rows_by_module_id, hook_handles)``; remove the handles when done."""
+    rows: Dict[int, int] = {}
+
+    def count(module, inputs):
+        x = inputs[0]
+        rows[id(module)] = rows.get(id(module), 0) + x.numel() // x.shape[-1]
+
+    return rows, [layer.register_forward_pre_hook(count) for layer in layers]
+
+
+@torch.no_grad()
+def validation_ppl(model, batches, amp: bool = True) -> float:
+    """Token-weighted perplexity over ``batches`` (each sequence contributes ``len - 1`` predictions)."""
+    was_training = model.training
+    model.eval()
+    nll, count = 0.0, 0
+    for batch in batches:
+        with amp_ctx(amp and batch["input_ids"].is_cuda):
+            loss = model(**batch).loss
+        n = batch["labels"].numel() - batch["labels"].shape[0]
+        nll += float(loss) * n
+        count += n
+    model.train(was_training)
+    return math.exp(min(nll / max(count, 1), 50.0))
+
+
 class SSPLedger:
     """Saved-surface predictor inputs: bytes autograd would save densely for the wrapped layers vs factor bytes."""
 

@@ -1,0 +1,29 @@
+"""Checkpoint density, Turbo-fast, full residual, and quality frontier.
+
+Grid ``composed_frontier`` (deployment; 9 cells).  Parity: experiments/benchmarks/composed_frontier.py.
+
+    python -m experiments.benchmarks.composed_frontier --dry-run
+    python -m experiments.benchmarks.composed_frontier --steps 20 --seeds 42
+"""
+
+from __future__ import annotations
+
+from . import _entry
+
+NAME = "composed_frontier"
+
+
+def cells():
+    return _entry.cells(NAME)
+
+
+def run(seeds=(42,), output=None):
+    return _entry.run(NAME, seeds, output)
+
+
+def main(argv=None) -> int:
+    return _entry.main(NAME, argv)
+
+
+if __name__ == "__main__":
+    raise SystemExit(main())

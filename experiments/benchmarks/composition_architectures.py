@@ -1,0 +1,29 @@
+"""Composition-law validation on Pythia and Qwen.
+
+Grid ``composition_architectures`` (mechanism; 16 cells).  Parity: experiments/benchmarks/composition_architectures.py.
+
+    python -m experiments.benchmarks.composition_architectures --dry-run
+    python -m experiments.benchmarks.composition_architectures --steps 20 --seeds 42
+"""
+
+from __future__ import annotations
+
+from . import _entry
+
+NAME = "composition_architectures"
+
+
+def cells():
+    return _entry.cells(NAME)
+
+
+def run(seeds=(42,), output=None):
+    return _entry.run(NAME, seeds, output)
+
+
+def main(argv=None) -> int:
+    return _entry.main(NAME, argv)
+
+
+if __name__ == "__main__":
+    raise SystemExit(main())

@@ -1,0 +1,29 @@
+"""Additive memory prediction across six basis/compression choices.
+
+Grid ``composition_law`` (mechanism; 18 cells).  Parity: experiments/benchmarks/composition_law.py.
+
+    python -m experiments.benchmarks.composition_law --dry-run
+    python -m experiments.benchmarks.composition_law --steps 20 --seeds 42
+"""
+
+from __future__ import annotations
+
+from . import _entry
+
+NAME = "composition_law"
+
+
+def cells():
+    return _entry.cells(NAME)
+
+
+def run(seeds=(42,), output=None):
+    return _entry.run(NAME, seeds, output)
+
+
+def main(argv=None) -> int:
+    return _entry.main(NAME, argv)
+
+
+if __name__ == "__main__":
+    raise SystemExit(main())

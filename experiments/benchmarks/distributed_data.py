@@ -27,6 +27,11 @@ from .registry import EXPERIMENTS
 SEEDS = [42, 123, 456]
 
 
+def complement(k: int):
+    """Predicate selecting the blocks a 1-in-``k`` checkpointing plan leaves alone (``index % k != 0``)."""
+    return lambda index, _k=int(k): index % _k != 0
+
+
 def one_run(cell: dict, seed: int, *, device: str, smoke: bool = False) -> dict:
     cell = dict(cell)
     method = cell.pop("method")
@@ -43,7 +48,7 @@ def one_run(cell: dict, seed: int, *, device: str, smoke: bool = False) -> dict:
     if cell.get("stacr_cfg"):
         k = cell.get("complement")
         cfg = dict(cell["stacr_cfg"], min_features=64) if smoke else cell["stacr_cfg"]
-        layers = common.stacr_on_blocks(model, cfg, (lambda i, _k=k: i % _k != 0) if k else None)
+        layers = common.stacr_on_blocks(model, cfg, complement(k) if k else None)
     opt = common.build_optimizer(model, 5e-5, device == "cuda")
     sync = GradSync(model.parameters()) if world > 1 else None
     vocab = model.config.vocab_size

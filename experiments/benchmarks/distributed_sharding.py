@@ -24,9 +24,51 @@ from . import common
 from .registry import EXPERIMENTS
 
 
-def one_run(cell: dict, seed: int, smoke: bool = False) -> dict:
+def complement(k: int):
+    """Predicate selecting the blocks a 1-in-``k`` checkpointing plan leaves alone (``index % k != 0``)."""
+    return lambda index, _k=int(k): index % _k != 0
+
+
+def arm_filter(arms):
+    """Restrict a cohort's arms by environment: ``STACR_ARM`` keeps one method, ``STACR_SKIP_ARMS`` drops a list.
+
+    ``arms`` is a list of cells (mappings with a ``method`` key) or of ``(name, options)`` pairs.
+    """
+    def name_of(arm):
+        return arm["method"] if isinstance(arm, dict) else arm[0]
+
+    only = os.environ.get("STACR_ARM", "").strip()
+    skip = set(os.environ.get("STACR_SKIP_ARMS", "").replace(",", " ").split())
+    kept = [a for a in arms if name_of(a) not in skip]
+    if only:
+        kept = [a for a in kept if name_of(a) == only]
+        if not kept:
+            raise SystemExit(f"STACR_ARM={only!r} matches no arm in this cohort")
+    return kept
+
+
+def build_opt_honest(model, lr: float = 5e-5):
+    """Plain torch AdamW whose moments take the parameters' dtype; returns ``(optimizer, label, state_dtype)``.
+
+    Sharded parameters are DTensors, which the in-tree multi-tensor AdamW does not take, so the sharded cohorts
+    report the optimizer they really ran.
+    """
+    dtype = next(model.parameters()).dtype
+    short = str(dtype).replace("torch.", "")
+    return torch.optim.AdamW(model.parameters(), lr=lr), f"torch_adamw_{short}_states", str(dtype)
+
+
+def shard(model):
+    """FSDP2: shard every transformer block, then the root module."""
     from torch.distributed.fsdp import fully_shard
 
+    for block in transformer_blocks(model):
+        fully_shard(block)
+    fully_shard(model)
+    return model
+
+
+def one_run(cell: dict, seed: int, smoke: bool = False) -> dict:
     cell = dict(cell)
     method = cell.pop("method")
     model_id, bs, seq = ("llama-tiny", 2, 64) if smoke else (cell["model_id"], cell["bs"], cell["seq"])
@@ -36,10 +78,10 @@ def one_run(cell: dict, seed: int, smoke: bool = False) -> dict:
     common.set_seed(seed)
     model = common.load_model(model_id, device, dtype=torch.bfloat16 if device == "cuda" else torch.float32)
     layers = common.stacr_on_blocks(model, dict(cell["stacr_cfg"], min_features=64 if smoke else 256)) if cell.get("stacr_cfg") else []
-    for block in transformer_blocks(model):
-        fully_shard(block)
-    fully_shard(model)
-    opt = torch.optim.AdamW(model.parameters(), lr=5e-5)
+    ckpt_every = int(cell.get("ckpt_every", 0) or 0)
+    n_ckpt = common.apply_selective_checkpointing(model, ckpt_every) if ckpt_every else 0
+    shard(model)
+    opt, opt_label, state_dtype = build_opt_honest(model)
     vocab = model.config.vocab_size
     rank, world = dist.get_rank(), dist.get_world_size()
     batches = common.get_batches(model_id, "train", bs, seq, steps * world, "synthetic", device, vocab, seed)[rank::world][:steps]
@@ -61,8 +103,38 @@ def one_run(cell: dict, seed: int, smoke: bool = False) -> dict:
     dist.all_reduce(peak, op=dist.ReduceOp.MAX)
     measured = max(0, len(batches) - measure_from)
     return {"tag": f"fsdp2_w{world}", "method": method, "seed": seed, "world_size": world, "model": model_id, "bs_per_rank": bs, "seq": seq,
-            "n_wrapped_layers": len(layers), "time_s": dt, "peak_GiB_max_rank": common.gib(float(peak)),
-            "tokens_per_s_per_rank": bs * seq * measured / dt if dt > 0 and measured else None, "final_train_loss": float(loss), "status": "ok"}
+            "n_wrapped_layers": len(layers), "n_checkpointed_blocks": n_ckpt, "optimizer_actual": opt_label, "optimizer_state_dtype": state_dtype, "time_s": dt, "peak_GiB_max_rank": common.gib(float(peak)),
+            "tokens_per_s_per_rank": bs * seq * measured / dt if dt > 0 and measured else None, "final_train_loss": float(loss.detach()), "status": "ok"}
+
+
+def run_cohort(name: str, cells, out, smoke: bool = False, seeds=(42,)) -> list:
+    """Run every arm of one cohort for every seed; rank 0 appends a record per run (``OOM``/``error`` runs included)."""
+    rank, world = dist.get_rank(), dist.get_world_size()
+    records, base = [], None
+    for cell in arm_filter(cells):
+        for seed in seeds:
+            try:
+                rec = one_run(cell, seed, smoke=smoke)
+            except torch.cuda.OutOfMemoryError:
+                rec = {"tag": f"fsdp2_w{world}", "method": cell["method"], "model": cell.get("model_id"), "seed": seed, "status": "OOM"}
+                torch.cuda.empty_cache()
+            except Exception as exc:  # a failed arm must not take the cohort down with it
+                rec = {"tag": f"fsdp2_w{world}", "method": cell["method"], "model": cell.get("model_id"), "seed": seed, "status": "error",
+                       "error": f"{type(exc).__name__}: {str(exc)[:200]}"}
+                if torch.cuda.is_available():
+                    torch.cuda.empty_cache()
+            rec["cohort"] = name
+            if rec.get("status") == "ok" and cell["method"] == "baseline" and base is None:
+                base = rec["peak_GiB_max_rank"]
+            if base and rec.get("status") == "ok":
+                rec["peak_saving_pct_vs_baseline"] = 100.0 * (base - rec["peak_GiB_max_rank"]) / base
+            records.append(rec)
+            if rank == 0:
+                if smoke:
+                    print(f"  smoke {rec['method']:14s} {rec.get('status')} loss={rec.get('final_train_loss')}", flush=True)
+                else:
+                    common.emit(rec, out)
+    return records
 
 
 def main() -> int:
@@ -77,17 +149,11 @@ def main() -> int:
     cells = EXPERIMENTS["distributed_sharding"]["cells"]
     if smoke:
         cells = cells[:2]
+    by_model: dict = {}
     for cell in cells:
-        try:
-            rec = one_run(cell, 42, smoke=smoke)
-        except torch.cuda.OutOfMemoryError:
-            rec = {"method": cell["method"], "model": cell["model_id"], "status": "OOM"}
-            torch.cuda.empty_cache()
-        if dist.get_rank() == 0:
-            if smoke:
-                print(f"  smoke {rec['method']:14s} {rec.get('status')} loss={rec.get('final_train_loss')}", flush=True)
-            else:
-                common.emit(rec, out)
+        by_model.setdefault(cell.get("model_id", "model"), []).append(cell)
+    for model_id, group in by_model.items():
+        run_cohort(model_id, group, out, smoke=smoke)
     dist.destroy_process_group()
     return 0
 

@@ -1,0 +1,29 @@
+"""Sparse checkpoint schedules bracketing equal memory and time.
+
+Grid ``equal_budget_frontier`` (deployment; 8 cells).  Parity: experiments/benchmarks/equal_budget_frontier.py.
+
+    python -m experiments.benchmarks.equal_budget_frontier --dry-run
+    python -m experiments.benchmarks.equal_budget_frontier --steps 20 --seeds 42
+"""
+
+from __future__ import annotations
+
+from . import _entry
+
+NAME = "equal_budget_frontier"
+
+
+def cells():
+    return _entry.cells(NAME)
+
+
+def run(seeds=(42,), output=None):
+    return _entry.run(NAME, seeds, output)
+
+
+def main(argv=None) -> int:
+    return _entry.main(NAME, argv)
+
+
+if __name__ == "__main__":
+    raise SystemExit(main())

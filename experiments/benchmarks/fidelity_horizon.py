@@ -1,0 +1,29 @@
+"""Basis adaptation over 6 to 240 pinned-gradient steps.
+
+Grid ``fidelity_horizon`` (fidelity; 6 cells).  Parity: experiments/benchmarks/fidelity_horizon.py.
+
+    python -m experiments.benchmarks.fidelity_horizon --dry-run
+    python -m experiments.benchmarks.fidelity_horizon --steps 20 --seeds 42
+"""
+
+from __future__ import annotations
+
+from . import _entry
+
+NAME = "fidelity_horizon"
+
+
+def cells():
+    return _entry.cells(NAME)
+
+
+def run(seeds=(42,), output=None):
+    return _entry.run(NAME, seeds, output)
+
+
+def main(argv=None) -> int:
+    return _entry.main(NAME, argv)
+
+
+if __name__ == "__main__":
+    raise SystemExit(main())

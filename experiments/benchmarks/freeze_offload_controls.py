@@ -1,0 +1,29 @@
+"""Frozen MLP and CPU activation offload controls.
+
+Grid ``freeze_offload_controls`` (mechanism; 5 cells).  Parity: experiments/benchmarks/freeze_offload_controls.py.
+
+    python -m experiments.benchmarks.freeze_offload_controls --dry-run
+    python -m experiments.benchmarks.freeze_offload_controls --steps 20 --seeds 42
+"""
+
+from __future__ import annotations
+
+from . import _entry
+
+NAME = "freeze_offload_controls"
+
+
+def cells():
+    return _entry.cells(NAME)
+
+
+def run(seeds=(42,), output=None):
+    return _entry.run(NAME, seeds, output)
+
+
+def main(argv=None) -> int:
+    return _entry.main(NAME, argv)
+
+
+if __name__ == "__main__":
+    raise SystemExit(main())

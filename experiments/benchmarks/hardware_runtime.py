@@ -1,0 +1,29 @@
+"""Runtime and model scale across GPU memory capacities.
+
+Grid ``hardware_runtime`` (systems; 8 cells).  Parity: experiments/benchmarks/hardware_runtime.py.
+
+    python -m experiments.benchmarks.hardware_runtime --dry-run
+    python -m experiments.benchmarks.hardware_runtime --steps 20 --seeds 42
+"""
+
+from __future__ import annotations
+
+from . import _entry
+
+NAME = "hardware_runtime"
+
+
+def cells():
+    return _entry.cells(NAME)
+
+
+def run(seeds=(42,), output=None):
+    return _entry.run(NAME, seeds, output)
+
+
+def main(argv=None) -> int:
+    return _entry.main(NAME, argv)
+
+
+if __name__ == "__main__":
+    raise SystemExit(main())

@@ -1,0 +1,29 @@
+"""INSTANT SST-2, MRPC, and GPT-2 protocols with calibration.
+
+Grid ``instant_comparison`` (comparators; 9 cells).  Parity: experiments/benchmarks/instant_comparison.py.
+
+    python -m experiments.benchmarks.instant_comparison --dry-run
+    python -m experiments.benchmarks.instant_comparison --steps 20 --seeds 42
+"""
+
+from __future__ import annotations
+
+from . import _entry
+
+NAME = "instant_comparison"
+
+
+def cells():
+    return _entry.cells(NAME)
+
+
+def run(seeds=(42,), output=None):
+    return _entry.run(NAME, seeds, output)
+
+
+def main(argv=None) -> int:
+    return _entry.main(NAME, argv)
+
+
+if __name__ == "__main__":
+    raise SystemExit(main())

@@ -1,0 +1,29 @@
+"""Single-model gradient probes on 7B/8B and Pythia.
+
+Grid ``large_model_fidelity`` (fidelity; 3 cells).  Parity: experiments/benchmarks/large_model_fidelity.py.
+
+    python -m experiments.benchmarks.large_model_fidelity --dry-run
+    python -m experiments.benchmarks.large_model_fidelity --steps 20 --seeds 42
+"""
+
+from __future__ import annotations
+
+from . import _entry
+
+NAME = "large_model_fidelity"
+
+
+def cells():
+    return _entry.cells(NAME)
+
+
+def run(seeds=(42,), output=None):
+    return _entry.run(NAME, seeds, output)
+
+
+def main(argv=None) -> int:
+    return _entry.main(NAME, argv)
+
+
+if __name__ == "__main__":
+    raise SystemExit(main())

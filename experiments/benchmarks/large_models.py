@@ -1,0 +1,29 @@
+"""7B/8B context lengths, batches, and composed memory frontier.
+
+Grid ``large_models`` (deployment; 12 cells).  Parity: experiments/benchmarks/large_models.py.
+
+    python -m experiments.benchmarks.large_models --dry-run
+    python -m experiments.benchmarks.large_models --steps 20 --seeds 42
+"""
+
+from __future__ import annotations
+
+from . import _entry
+
+NAME = "large_models"
+
+
+def cells():
+    return _entry.cells(NAME)
+
+
+def run(seeds=(42,), output=None):
+    return _entry.run(NAME, seeds, output)
+
+
+def main(argv=None) -> int:
+    return _entry.main(NAME, argv)
+
+
+if __name__ == "__main__":
+    raise SystemExit(main())

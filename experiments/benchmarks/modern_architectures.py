@@ -1,0 +1,29 @@
+"""Qwen3 and 3B-tier model surfaces and batch sizes.
+
+Grid ``modern_architectures`` (deployment; 12 cells).  Parity: experiments/benchmarks/modern_architectures.py.
+
+    python -m experiments.benchmarks.modern_architectures --dry-run
+    python -m experiments.benchmarks.modern_architectures --steps 20 --seeds 42
+"""
+
+from __future__ import annotations
+
+from . import _entry
+
+NAME = "modern_architectures"
+
+
+def cells():
+    return _entry.cells(NAME)
+
+
+def run(seeds=(42,), output=None):
+    return _entry.run(NAME, seeds, output)
+
+
+def main(argv=None) -> int:
+    return _entry.main(NAME, argv)
+
+
+if __name__ == "__main__":
+    raise SystemExit(main())

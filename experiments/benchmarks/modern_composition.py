@@ -1,0 +1,29 @@
+"""Checkpoint density and Turbo-fast on modern decoder MLPs.
+
+Grid ``modern_composition`` (deployment; 12 cells).  Parity: experiments/benchmarks/modern_composition.py.
+
+    python -m experiments.benchmarks.modern_composition --dry-run
+    python -m experiments.benchmarks.modern_composition --steps 20 --seeds 42
+"""
+
+from __future__ import annotations
+
+from . import _entry
+
+NAME = "modern_composition"
+
+
+def cells():
+    return _entry.cells(NAME)
+
+
+def run(seeds=(42,), output=None):
+    return _entry.run(NAME, seeds, output)
+
+
+def main(argv=None) -> int:
+    return _entry.main(NAME, argv)
+
+
+if __name__ == "__main__":
+    raise SystemExit(main())

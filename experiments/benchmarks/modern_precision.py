@@ -1,0 +1,29 @@
+"""Precision controls and 600-step modern-model quality.
+
+Grid ``modern_precision`` (quality; 12 cells).  Parity: experiments/benchmarks/modern_precision.py.
+
+    python -m experiments.benchmarks.modern_precision --dry-run
+    python -m experiments.benchmarks.modern_precision --steps 20 --seeds 42
+"""
+
+from __future__ import annotations
+
+from . import _entry
+
+NAME = "modern_precision"
+
+
+def cells():
+    return _entry.cells(NAME)
+
+
+def run(seeds=(42,), output=None):
+    return _entry.run(NAME, seeds, output)
+
+
+def main(argv=None) -> int:
+    return _entry.main(NAME, argv)
+
+
+if __name__ == "__main__":
+    raise SystemExit(main())

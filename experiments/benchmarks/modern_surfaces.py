@@ -1,0 +1,29 @@
+"""Modern-model surface expansion and its quality cost.
+
+Grid ``modern_surfaces`` (deployment; 6 cells).  Parity: experiments/benchmarks/modern_surfaces.py.
+
+    python -m experiments.benchmarks.modern_surfaces --dry-run
+    python -m experiments.benchmarks.modern_surfaces --steps 20 --seeds 42
+"""
+
+from __future__ import annotations
+
+from . import _entry
+
+NAME = "modern_surfaces"
+
+
+def cells():
+    return _entry.cells(NAME)
+
+
+def run(seeds=(42,), output=None):
+    return _entry.run(NAME, seeds, output)
+
+
+def main(argv=None) -> int:
+    return _entry.main(NAME, argv)
+
+
+if __name__ == "__main__":
+    raise SystemExit(main())

@@ -1,0 +1,29 @@
+"""Rank, residual budget, and basis-update operating points.
+
+Grid ``parameter_sweep`` (deployment; 32 cells).  Parity: experiments/benchmarks/parameter_sweep.py.
+
+    python -m experiments.benchmarks.parameter_sweep --dry-run
+    python -m experiments.benchmarks.parameter_sweep --steps 20 --seeds 42
+"""
+
+from __future__ import annotations
+
+from . import _entry
+
+NAME = "parameter_sweep"
+
+
+def cells():
+    return _entry.cells(NAME)
+
+
+def run(seeds=(42,), output=None):
+    return _entry.run(NAME, seeds, output)
+
+
+def main(argv=None) -> int:
+    return _entry.main(NAME, argv)
+
+
+if __name__ == "__main__":
+    raise SystemExit(main())

@@ -1,0 +1,29 @@
+"""FP32 model controls and OpenWebText corpus comparison.
+
+Grid ``precision_corpus`` (quality; 12 cells).  Parity: experiments/benchmarks/precision_corpus.py.
+
+    python -m experiments.benchmarks.precision_corpus --dry-run
+    python -m experiments.benchmarks.precision_corpus --steps 20 --seeds 42
+"""
+
+from __future__ import annotations
+
+from . import _entry
+
+NAME = "precision_corpus"
+
+
+def cells():
+    return _entry.cells(NAME)
+
+
+def run(seeds=(42,), output=None):
+    return _entry.run(NAME, seeds, output)
+
+
+def main(argv=None) -> int:
+    return _entry.main(NAME, argv)
+
+
+if __name__ == "__main__":
+    raise SystemExit(main())

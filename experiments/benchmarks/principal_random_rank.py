@@ -1,0 +1,29 @@
+"""PRAC at recommended rank versus STAC-R at matched rank.
+
+Grid ``principal_random_rank`` (fidelity; 4 cells).  Parity: experiments/benchmarks/principal_random_rank.py.
+
+    python -m experiments.benchmarks.principal_random_rank --dry-run
+    python -m experiments.benchmarks.principal_random_rank --steps 20 --seeds 42
+"""
+
+from __future__ import annotations
+
+from . import _entry
+
+NAME = "principal_random_rank"
+
+
+def cells():
+    return _entry.cells(NAME)
+
+
+def run(seeds=(42,), output=None):
+    return _entry.run(NAME, seeds, output)
+
+
+def main(argv=None) -> int:
+    return _entry.main(NAME, argv)
+
+
+if __name__ == "__main__":
+    raise SystemExit(main())

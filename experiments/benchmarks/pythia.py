@@ -1,0 +1,29 @@
+"""Pythia-1.4B baseline, checkpoint, full residual, and Turbo-fast.
+
+Grid ``pythia`` (quality; 4 cells).  Parity: experiments/benchmarks/pythia.py.
+
+    python -m experiments.benchmarks.pythia --dry-run
+    python -m experiments.benchmarks.pythia --steps 20 --seeds 42
+"""
+
+from __future__ import annotations
+
+from . import _entry
+
+NAME = "pythia"
+
+
+def cells():
+    return _entry.cells(NAME)
+
+
+def run(seeds=(42,), output=None):
+    return _entry.run(NAME, seeds, output)
+
+
+def main(argv=None) -> int:
+    return _entry.main(NAME, argv)
+
+
+if __name__ == "__main__":
+    raise SystemExit(main())

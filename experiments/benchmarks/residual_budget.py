@@ -1,0 +1,29 @@
+"""Residual on/off, 0.5%, and 1% quality-memory-time tradeoffs.
+
+Grid ``residual_budget`` (quality; 4 cells).  Parity: experiments/benchmarks/residual_budget.py.
+
+    python -m experiments.benchmarks.residual_budget --dry-run
+    python -m experiments.benchmarks.residual_budget --steps 20 --seeds 42
+"""
+
+from __future__ import annotations
+
+from . import _entry
+
+NAME = "residual_budget"
+
+
+def cells():
+    return _entry.cells(NAME)
+
+
+def run(seeds=(42,), output=None):
+    return _entry.run(NAME, seeds, output)
+
+
+def main(argv=None) -> int:
+    return _entry.main(NAME, argv)
+
+
+if __name__ == "__main__":
+    raise SystemExit(main())

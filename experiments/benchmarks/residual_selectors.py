@@ -1,0 +1,29 @@
+"""Chunked, global, block-sparse, and sampled residual selection.
+
+Grid ``residual_selectors`` (systems; 5 cells).  Parity: experiments/benchmarks/residual_selectors.py.
+
+    python -m experiments.benchmarks.residual_selectors --dry-run
+    python -m experiments.benchmarks.residual_selectors --steps 20 --seeds 42
+"""
+
+from __future__ import annotations
+
+from . import _entry
+
+NAME = "residual_selectors"
+
+
+def cells():
+    return _entry.cells(NAME)
+
+
+def run(seeds=(42,), output=None):
+    return _entry.run(NAME, seeds, output)
+
+
+def main(argv=None) -> int:
+    return _entry.main(NAME, argv)
+
+
+if __name__ == "__main__":
+    raise SystemExit(main())

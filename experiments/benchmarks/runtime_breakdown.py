@@ -1,0 +1,29 @@
+"""Refresh interval, frozen basis, and quantized residual overhead.
+
+Grid ``runtime_breakdown`` (systems; 10 cells).  Parity: experiments/benchmarks/runtime_breakdown.py.
+
+    python -m experiments.benchmarks.runtime_breakdown --dry-run
+    python -m experiments.benchmarks.runtime_breakdown --steps 20 --seeds 42
+"""
+
+from __future__ import annotations
+
+from . import _entry
+
+NAME = "runtime_breakdown"
+
+
+def cells():
+    return _entry.cells(NAME)
+
+
+def run(seeds=(42,), output=None):
+    return _entry.run(NAME, seeds, output)
+
+
+def main(argv=None) -> int:
+    return _entry.main(NAME, argv)
+
+
+if __name__ == "__main__":
+    raise SystemExit(main())

@@ -1,0 +1,29 @@
+"""Context-length and batch capacity on Llama and Qwen.
+
+Grid ``sequence_length`` (deployment; 20 cells).  Parity: experiments/benchmarks/sequence_length.py.
+
+    python -m experiments.benchmarks.sequence_length --dry-run
+    python -m experiments.benchmarks.sequence_length --steps 20 --seeds 42
+"""
+
+from __future__ import annotations
+
+from . import _entry
+
+NAME = "sequence_length"
+
+
+def cells():
+    return _entry.cells(NAME)
+
+
+def run(seeds=(42,), output=None):
+    return _entry.run(NAME, seeds, output)
+
+
+def main(argv=None) -> int:
+    return _entry.main(NAME, argv)
+
+
+if __name__ == "__main__":
+    raise SystemExit(main())

@@ -1,0 +1,29 @@
+"""Exact and compressed gradients using one model in memory.
+
+Grid ``single_model_fidelity`` (fidelity; 2 cells).  Parity: experiments/benchmarks/single_model_fidelity.py.
+
+    python -m experiments.benchmarks.single_model_fidelity --dry-run
+    python -m experiments.benchmarks.single_model_fidelity --steps 20 --seeds 42
+"""
+
+from __future__ import annotations
+
+from . import _entry
+
+NAME = "single_model_fidelity"
+
+
+def cells():
+    return _entry.cells(NAME)
+
+
+def run(seeds=(42,), output=None):
+    return _entry.run(NAME, seeds, output)
+
+
+def main(argv=None) -> int:
+    return _entry.main(NAME, argv)
+
+
+if __name__ == "__main__":
+    raise SystemExit(main())

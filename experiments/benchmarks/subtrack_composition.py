@@ -1,0 +1,29 @@
+"""Upstream SubTrack++ BERT/SST-2 and adaptive STAC-R composition.
+
+Grid ``subtrack_composition`` (comparators; 3 cells).  Parity: experiments/benchmarks/subtrack_composition.py.
+
+    python -m experiments.benchmarks.subtrack_composition --dry-run
+    python -m experiments.benchmarks.subtrack_composition --steps 20 --seeds 42
+"""
+
+from __future__ import annotations
+
+from . import _entry
+
+NAME = "subtrack_composition"
+
+
+def cells():
+    return _entry.cells(NAME)
+
+
+def run(seeds=(42,), output=None):
+    return _entry.run(NAME, seeds, output)
+
+
+def main(argv=None) -> int:
+    return _entry.main(NAME, argv)
+
+
+if __name__ == "__main__":
+    raise SystemExit(main())

@@ -1,0 +1,29 @@
+"""MLP, attention, and all-linear compression on GPT-2.
+
+Grid ``surface_expansion`` (deployment; 5 cells).  Parity: experiments/benchmarks/surface_expansion.py.
+
+    python -m experiments.benchmarks.surface_expansion --dry-run
+    python -m experiments.benchmarks.surface_expansion --steps 20 --seeds 42
+"""
+
+from __future__ import annotations
+
+from . import _entry
+
+NAME = "surface_expansion"
+
+
+def cells():
+    return _entry.cells(NAME)
+
+
+def run(seeds=(42,), output=None):
+    return _entry.run(NAME, seeds, output)
+
+
+def main(argv=None) -> int:
+    return _entry.main(NAME, argv)
+
+
+if __name__ == "__main__":
+    raise SystemExit(main())

@@ -1,0 +1,29 @@
+"""Same-block versus disjoint checkpoint composition on SwiGLU.
+
+Grid ``swiglu_composition`` (deployment; 3 cells).  Parity: experiments/benchmarks/swiglu_composition.py.
+
+    python -m experiments.benchmarks.swiglu_composition --dry-run
+    python -m experiments.benchmarks.swiglu_composition --steps 20 --seeds 42
+"""
+
+from __future__ import annotations
+
+from . import _entry
+
+NAME = "swiglu_composition"
+
+
+def cells():
+    return _entry.cells(NAME)
+
+
+def run(seeds=(42,), output=None):
+    return _entry.run(NAME, seeds, output)
+
+
+def main(argv=None) -> int:
+    return _entry.main(NAME, argv)
+
+
+if __name__ == "__main__":
+    raise SystemExit(main())

@@ -1,0 +1,29 @@
+"""Rank and residual fidelity on three modern decoder families.
+
+Grid ``swiglu_fidelity`` (fidelity; 12 cells).  Parity: experiments/benchmarks/swiglu_fidelity.py.
+
+    python -m experiments.benchmarks.swiglu_fidelity --dry-run
+    python -m experiments.benchmarks.swiglu_fidelity --steps 20 --seeds 42
+"""
+
+from __future__ import annotations
+
+from . import _entry
+
+NAME = "swiglu_fidelity"
+
+
+def cells():
+    return _entry.cells(NAME)
+
+
+def run(seeds=(42,), output=None):
+    return _entry.run(NAME, seeds, output)
+
+
+def main(argv=None) -> int:
+    return _entry.main(NAME, argv)
+
+
+if __name__ == "__main__":
+    raise SystemExit(main())

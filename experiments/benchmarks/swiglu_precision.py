@@ -1,0 +1,29 @@
+"""SwiGLU precision and optimizer allocation controls.
+
+Grid ``swiglu_precision`` (mechanism; 8 cells).  Parity: experiments/benchmarks/swiglu_precision.py.
+
+    python -m experiments.benchmarks.swiglu_precision --dry-run
+    python -m experiments.benchmarks.swiglu_precision --steps 20 --seeds 42
+"""
+
+from __future__ import annotations
+
+from . import _entry
+
+NAME = "swiglu_precision"
+
+
+def cells():
+    return _entry.cells(NAME)
+
+
+def run(seeds=(42,), output=None):
+    return _entry.run(NAME, seeds, output)
+
+
+def main(argv=None) -> int:
+    return _entry.main(NAME, argv)
+
+
+if __name__ == "__main__":
+    raise SystemExit(main())

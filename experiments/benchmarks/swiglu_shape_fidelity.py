@@ -1,0 +1,29 @@
+"""Pinned gradient fidelity at two-example 1024-token shapes.
+
+Grid ``swiglu_shape_fidelity`` (fidelity; 2 cells).  Parity: experiments/benchmarks/swiglu_shape_fidelity.py.
+
+    python -m experiments.benchmarks.swiglu_shape_fidelity --dry-run
+    python -m experiments.benchmarks.swiglu_shape_fidelity --steps 20 --seeds 42
+"""
+
+from __future__ import annotations
+
+from . import _entry
+
+NAME = "swiglu_shape_fidelity"
+
+
+def cells():
+    return _entry.cells(NAME)
+
+
+def run(seeds=(42,), output=None):
+    return _entry.run(NAME, seeds, output)
+
+
+def main(argv=None) -> int:
+    return _entry.main(NAME, argv)
+
+
+if __name__ == "__main__":
+    raise SystemExit(main())

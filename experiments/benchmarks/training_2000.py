@@ -1,0 +1,29 @@
+"""Seven GPT-2 Medium training arms at 2000 steps.
+
+Grid ``training_2000`` (quality; 7 cells).  Parity: experiments/benchmarks/training_2000.py.
+
+    python -m experiments.benchmarks.training_2000 --dry-run
+    python -m experiments.benchmarks.training_2000 --steps 20 --seeds 42
+"""
+
+from __future__ import annotations
+
+from . import _entry
+
+NAME = "training_2000"
+
+
+def cells():
+    return _entry.cells(NAME)
+
+
+def run(seeds=(42,), output=None):
+    return _entry.run(NAME, seeds, output)
+
+
+def main(argv=None) -> int:
+    return _entry.main(NAME, argv)
+
+
+if __name__ == "__main__":
+    raise SystemExit(main())

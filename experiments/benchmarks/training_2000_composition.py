@@ -1,0 +1,29 @@
+"""Disjoint full-residual composition at 2000 steps.
+
+Grid ``training_2000_composition`` (quality; 2 cells).  Parity: experiments/benchmarks/training_2000_composition.py.
+
+    python -m experiments.benchmarks.training_2000_composition --dry-run
+    python -m experiments.benchmarks.training_2000_composition --steps 20 --seeds 42
+"""
+
+from __future__ import annotations
+
+from . import _entry
+
+NAME = "training_2000_composition"
+
+
+def cells():
+    return _entry.cells(NAME)
+
+
+def run(seeds=(42,), output=None):
+    return _entry.run(NAME, seeds, output)
+
+
+def main(argv=None) -> int:
+    return _entry.main(NAME, argv)
+
+
+if __name__ == "__main__":
+    raise SystemExit(main())

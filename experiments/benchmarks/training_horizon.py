@@ -1,0 +1,29 @@
+"""Long-horizon quality on WikiText and OpenWebText.
+
+Grid ``training_horizon`` (quality; 12 cells).  Parity: experiments/benchmarks/training_horizon.py.
+
+    python -m experiments.benchmarks.training_horizon --dry-run
+    python -m experiments.benchmarks.training_horizon --steps 20 --seeds 42
+"""
+
+from __future__ import annotations
+
+from . import _entry
+
+NAME = "training_horizon"
+
+
+def cells():
+    return _entry.cells(NAME)
+
+
+def run(seeds=(42,), output=None):
+    return _entry.run(NAME, seeds, output)
+
+
+def main(argv=None) -> int:
+    return _entry.main(NAME, argv)
+
+
+if __name__ == "__main__":
+    raise SystemExit(main())

@@ -789,3 +789,7 @@ class _null:
 
     def __exit__(self, *exc):
         return False
+
+
+from .training_helpers import *  # noqa: E402,F401,F403  (stand-alone pieces of the protocol, part of this module's API)
+from .training_helpers import __all__ as _HELPER_NAMES  # noqa: E402

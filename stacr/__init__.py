@@ -41,6 +41,8 @@ class _AliasFinder:
             return None
         from importlib.machinery import ModuleSpec
 
+        own = (module.__spec__, getattr(module, "__loader__", None))
+
         class _Loader:
             @staticmethod
             def create_module(spec):
@@ -48,7 +50,7 @@ class _AliasFinder:
 
             @staticmethod
             def exec_module(mod):
-                return None
+                mod.__spec__, mod.__loader__ = own      # the import system stamped the alias spec on it; put the real one back
 
         return ModuleSpec(fullname, _Loader(), is_package=hasattr(module, "__path__"))
 

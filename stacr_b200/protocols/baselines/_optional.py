@@ -27,6 +27,15 @@ class AdapterResult:
     def ok(self) -> bool:
         return self.status is AdapterStatus.OK
 
+    @property
+    def reason(self) -> str:
+        """The message, under the name result records of the optional baselines use."""
+        return self.message
+
+    @property
+    def meta(self) -> Dict[str, Any]:
+        return {"version": self.version, **self.details}
+
     def to_dict(self) -> Dict[str, Any]:
         return {"status": self.status.value, "message": self.message, "version": self.version, "ok": self.ok, **self.details}
 
@@ -38,3 +47,11 @@ def probe(module_name: str) -> Tuple[bool, Optional[str], Any]:
         return True, getattr(mod, "__version__", "unknown"), mod
     except Exception as exc:  # noqa: BLE001
         return False, f"{type(exc).__name__}: {exc}", None
+
+
+def final_json(baseline: str, result: AdapterResult, output_dir: str) -> Dict[str, Any]:
+    """The ``final.json`` body of a run whose optional baseline was enabled, skipped or failed.
+
+    A skipped baseline still gets a well-formed record so that sweeps stay complete and plottable.
+    """
+    return {"baseline": baseline, "status": result.status.value, "reason": result.message, "meta": result.meta, "output_dir": str(output_dir)}

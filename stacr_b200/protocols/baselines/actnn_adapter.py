@@ -11,10 +11,12 @@ from typing import Optional, Tuple
 import torch
 from torch import nn
 
-from ._optional import AdapterResult, AdapterStatus, probe
+from ._optional import AdapterResult, AdapterStatus, final_json, probe
 
 ACTNNStatus = AdapterStatus
 ACTNNResult = AdapterResult
+ActNNStatus = AdapterStatus
+ActNNResult = AdapterResult
 _LEVEL_BITS = {"L0": 32, "L1": 4, "L2": 2, "L3": 2, "L4": 2, "L5": 2}
 
 
@@ -73,3 +75,19 @@ class ACTNNController:
         ctrl = getattr(self.model, "controller", None)
         if self.enabled and ctrl is not None and hasattr(ctrl, "iterate"):
             ctrl.iterate(*args, **kwargs)
+
+    def get_config(self) -> dict:
+        return {"baseline": "actnn", "level": self.level, "enabled": self.enabled, "bits": _get_bits_for_level(self.level), **self.result.to_dict()}
+
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *exc) -> None:
+        return None
+
+
+ActNNController = ACTNNController
+
+
+def create_actnn_final_json(result: AdapterResult, output_dir: str) -> dict:
+    return final_json("actnn", result, output_dir)

@@ -11,7 +11,7 @@ from typing import Optional, Tuple
 import torch
 from torch import nn
 
-from ._optional import AdapterResult, AdapterStatus, probe
+from ._optional import AdapterResult, AdapterStatus, final_json, probe
 
 GACTStatus = AdapterStatus
 GACTResult = AdapterResult
@@ -73,3 +73,60 @@ class GACTController:
         ctrl = getattr(self.model, "controller", None)
         if self.enabled and ctrl is not None and hasattr(ctrl, "iterate"):
             ctrl.iterate(*args, **kwargs)
+
+    def install_hook(self) -> None:
+        ctrl = getattr(self.model, "controller", None)
+        if self.enabled and ctrl is not None and hasattr(ctrl, "install_hook"):
+            ctrl.install_hook()
+
+    def uninstall_hook(self) -> None:
+        ctrl = getattr(self.model, "controller", None)
+        if self.enabled and ctrl is not None and hasattr(ctrl, "uninstall_hook"):
+            ctrl.uninstall_hook()
+
+    def get_config(self) -> dict:
+        return {"baseline": "gact", "level": self.level, "enabled": self.enabled, "bits": _get_bits_for_level(self.level), **self.result.to_dict()}
+
+    def __enter__(self):
+        self.install_hook()
+        return self
+
+    def __exit__(self, *exc) -> None:
+        self.uninstall_hook()
+
+
+class MockGACTController:
+    """Stand-in with the controller's interface that changes nothing, for loops written against the controller."""
+
+    def __init__(self, model: nn.Module, level: str = "L1"):
+        self.model, self.level, self.auto_precision, self._iter = model, level, False, 0
+
+    def install_hook(self) -> None:
+        return None
+
+    def uninstall_hook(self) -> None:
+        return None
+
+    def iterate(self, get_grad_fn=None) -> None:
+        self._iter += 1
+
+    @property
+    def enabled(self) -> bool:
+        return False
+
+    @property
+    def iteration(self) -> int:
+        return self._iter
+
+    def get_config(self) -> dict:
+        return {"baseline": "gact", "level": self.level, "enabled": False, "reason": "mock_controller"}
+
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *exc) -> None:
+        return None
+
+
+def create_gact_final_json(result: AdapterResult, output_dir: str) -> dict:
+    return final_json("gact", result, output_dir)

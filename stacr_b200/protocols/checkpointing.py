@@ -13,6 +13,7 @@ enable function that rejects tensor- and data-parallel wrappers).
 
 from __future__ import annotations
 
+import dataclasses
 from dataclasses import dataclass
 from typing import Any, Dict, Iterable, List, Optional, Tuple
 
@@ -484,4 +485,93 @@ def enable_c1_checkpointing_for_model(model: nn.Module, config: STACRCheckpointC
         site.module._c1_inner_forward = inner
         site.module.forward = forward
     runtime.activate()
+    return runtime
+
+
+# ------------------------------------------------------------------------------ registration from a run configuration
+@dataclass
+class ResolvedCheckpointSite:
+    """A registered site at call time: the block, its spec and codec, and the boundary tensor among the call's arguments."""
+
+    module: nn.Module
+    spec: STACRCheckpointSpec
+    codec: CheckpointBoundaryCodec
+    target_tensor: Optional[torch.Tensor]
+    target_arg_index: int = 0
+
+
+def build_stacr_checkpoint_config(config: Any) -> STACRCheckpointConfig:
+    """Collect a run configuration's ``stacr_ckpt_*`` attributes (and ``stacr_compress_checkpoint``) into a codec configuration.
+
+    Parity: stacr/protocols/checkpointing.py:1186-1210.  Attributes the run configuration lacks keep the defaults.
+    """
+    defaults = STACRCheckpointConfig()
+    picked = {}
+    for f in dataclasses.fields(STACRCheckpointConfig):
+        if f.name == "enabled":
+            picked[f.name] = bool(getattr(config, "stacr_compress_checkpoint", False))
+        else:
+            value = getattr(config, f"stacr_ckpt_{f.name}", getattr(defaults, f.name))
+            kind = type(getattr(defaults, f.name))
+            picked[f.name] = value if value is None or kind is type(None) else kind(value)
+    return STACRCheckpointConfig(**picked)
+
+
+def _spec_for(site: CheckpointSiteCandidate, cfg: STACRCheckpointConfig, amp_mode: str, device: torch.device) -> STACRCheckpointSpec:
+    rank = min(int(cfg.rank or _default_ckpt_rank(site.model_family, site.hidden_size)), site.hidden_size)
+    return STACRCheckpointSpec(
+        site_id=site.name, module_type=type(site.module).__name__, model_family=site.model_family, hidden_size=site.hidden_size, rank=rank,
+        residual_mode=cfg.residual_mode, residual_budget=cfg.residual_budget, basis_dtype=_resolve_ckpt_basis_dtype(cfg.basis_dtype, amp_mode, device),
+        quantize_coefficients=cfg.quantize_coefficients, quantize_bits=cfg.quantize_bits, quantize_residuals=cfg.quantize_residuals,
+        residual_quantize_bits=cfg.residual_quantize_bits, warmup_steps=cfg.warmup_steps, refresh_trigger=cfg.refresh_trigger,
+        refresh_period=cfg.refresh_period,
+        refresh_energy_threshold=_resolve_ckpt_refresh_energy_threshold(cfg.refresh_energy_threshold_mode, cfg.refresh_energy_threshold, rank, site.hidden_size),
+        min_numel=cfg.min_numel)
+
+
+def collect_c1_site_candidates(model: nn.Module, config: Any) -> List[Tuple[CheckpointSiteCandidate, STACRCheckpointSpec]]:
+    """Every transformer block that can carry a boundary codec, paired with the spec the run configuration gives it.
+
+    Parity: stacr/protocols/checkpointing.py:1213-1296.  Raises when the architecture has no recognised block stack.
+    """
+    cfg = build_stacr_checkpoint_config(config)
+    sites = discover_checkpoint_sites(model)
+    if not sites:
+        raise ValueError("checkpoint-boundary compression found no transformer blocks in this model")
+    amp_mode = str(getattr(getattr(config, "baseline_cfg", None), "amp", "none") or "none")
+    device = next(model.parameters()).device
+    return [(site, _spec_for(site, cfg, amp_mode, device)) for site in sites]
+
+
+def register_c1_sites(model: nn.Module, config: Any, *, runtime: Optional[STACRCheckpointRuntime] = None) -> STACRCheckpointRuntime:
+    """Register a codec on each candidate block (after the byte planner's veto when it is set to ``enforce``).
+
+    The blocks' forwards are left alone: a caller that checkpoints ``block.forward`` itself asks
+    ``runtime.resolve_site(function)`` for the codec.  Parity: stacr/protocols/checkpointing.py:1299-1345.
+    """
+    runtime = runtime or STACRCheckpointRuntime()
+    runtime.registry.clear()
+    cfg = build_stacr_checkpoint_config(config)
+    pairs = collect_c1_site_candidates(model, config)
+    runtime.site_count_total = len(pairs)
+    runtime.planner_mode, runtime.planner_summary, runtime.planner_decisions = cfg.planner, None, None
+    keep = {site.name for site, _ in pairs}
+    if cfg.planner != "off":
+        from .planner import plan_stacr_checkpoint_sites, summarize_checkpoint_site_decisions
+
+        decisions = plan_stacr_checkpoint_sites(model, config, [s.name for s, _ in pairs], pairs[0][0].hidden_size)
+        runtime.planner_decisions = [d.to_dict() if hasattr(d, "to_dict") else dataclasses.asdict(d) for d in decisions]
+        runtime.planner_summary = summarize_checkpoint_site_decisions(decisions)
+        if cfg.planner == "enforce":
+            keep = {d.name for d in decisions if d.keep}
+            if not keep:
+                reasons: Dict[str, int] = {}
+                for d in decisions:
+                    reasons[d.reason] = reasons.get(d.reason, 0) + 1
+                raise ValueError("the byte planner rejected every checkpoint site: " + ", ".join(f"{k}={v}" for k, v in sorted(reasons.items())))
+    device = next(model.parameters()).device
+    for site, spec in pairs:
+        if site.name in keep:
+            runtime.registry.register(site.module, spec)
+            runtime.registry.codec_for(spec.site_id).to(device)
     return runtime
