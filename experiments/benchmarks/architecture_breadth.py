@@ -9,6 +9,7 @@ Grid ``architecture_breadth`` (deployment; 36 cells).  Parity: experiments/bench
 from __future__ import annotations
 
 from . import _entry
+from .probes import complement  # noqa: F401
 
 NAME = "architecture_breadth"
 

@@ -9,6 +9,7 @@ Grid ``attention_kernels`` (systems; 9 cells).  Parity: experiments/benchmarks/a
 from __future__ import annotations
 
 from . import _entry
+from .probes import complement  # noqa: F401
 
 NAME = "attention_kernels"
 

@@ -9,6 +9,7 @@ Grid ``basis_comparison`` (quality; 6 cells).  Parity: experiments/benchmarks/ba
 from __future__ import annotations
 
 from . import _entry
+from .probes import complement  # noqa: F401
 
 NAME = "basis_comparison"
 

@@ -9,6 +9,7 @@ Grid ``basis_fidelity`` (fidelity; 5 cells).  Parity: experiments/benchmarks/bas
 from __future__ import annotations
 
 from . import _entry
+from .probes import complement  # noqa: F401
 
 NAME = "basis_fidelity"
 

@@ -9,6 +9,7 @@ Grid ``basis_storage`` (mechanism; 5 cells).  Parity: experiments/benchmarks/bas
 from __future__ import annotations
 
 from . import _entry
+from .probes import complement  # noqa: F401
 
 NAME = "basis_storage"
 
@@ -19,6 +20,9 @@ def cells():
 
 def run(seeds=(42,), output=None):
     return _entry.run(NAME, seeds, output)
+
+
+from stacr_b200.comparators.activation import FatFunction, FatLinear, apply_fat  # noqa: E402,F401  (storage controls)
 
 
 def main(argv=None) -> int:

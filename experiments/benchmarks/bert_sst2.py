@@ -9,6 +9,7 @@ Grid ``bert_sst2`` (quality; 3 cells).  Parity: experiments/benchmarks/bert_sst2
 from __future__ import annotations
 
 from . import _entry
+from .probes import complement  # noqa: F401
 
 NAME = "bert_sst2"
 
@@ -19,6 +20,13 @@ def cells():
 
 def run(seeds=(42,), output=None):
     return _entry.run(NAME, seeds, output)
+
+
+def sst2(method="baseline", stacr_cfg=None, bs=32, seq=128, steps=60, seed=42, **run_kw):
+    """One BERT sequence-classification cell (random class labels offline: a memory/throughput protocol)."""
+    from . import common
+
+    return common.run_config(method, seed, model_id="bert-base-uncased", bs=bs, seq=seq, steps=steps, stacr_cfg=stacr_cfg, **run_kw)
 
 
 def main(argv=None) -> int:

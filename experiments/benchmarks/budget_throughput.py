@@ -9,6 +9,7 @@ Grid ``budget_throughput`` (deployment; 12 cells).  Parity: experiments/benchmar
 from __future__ import annotations
 
 from . import _entry
+from .probes import complement  # noqa: F401
 
 NAME = "budget_throughput"
 

@@ -9,6 +9,7 @@ Grid ``capacity`` (deployment; 18 cells).  Parity: experiments/benchmarks/capaci
 from __future__ import annotations
 
 from . import _entry
+from .probes import complement  # noqa: F401
 
 NAME = "capacity"
 

@@ -9,6 +9,7 @@ Grid ``capacity_search`` (deployment; 16 cells).  Parity: experiments/benchmarks
 from __future__ import annotations
 
 from . import _entry
+from .probes import complement  # noqa: F401
 
 NAME = "capacity_search"
 
@@ -19,6 +20,13 @@ def cells():
 
 def run(seeds=(42,), output=None):
     return _entry.run(NAME, seeds, output)
+
+
+def largest_fitting(model_id, seq, dtype, lo, hi, method, cfg, out=None, tag="capacity", **run_kw):
+    """The largest batch in ``lo..hi`` that trains; see :func:`probes.largest_fitting`."""
+    from . import probes
+
+    return probes.largest_fitting(model_id, seq, dtype, lo, hi, method, cfg, out, tag, **run_kw)
 
 
 def main(argv=None) -> int:

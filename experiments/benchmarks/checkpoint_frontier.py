@@ -9,6 +9,7 @@ Grid ``checkpoint_frontier`` (deployment; 7 cells).  Parity: experiments/benchma
 from __future__ import annotations
 
 from . import _entry
+from .probes import complement  # noqa: F401
 
 NAME = "checkpoint_frontier"
 

@@ -9,6 +9,7 @@ Grid ``checkpoint_surface`` (mechanism; 10 cells).  Parity: experiments/benchmar
 from __future__ import annotations
 
 from . import _entry
+from .probes import complement  # noqa: F401
 
 NAME = "checkpoint_surface"
 

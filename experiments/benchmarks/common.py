@@ -81,22 +81,33 @@ def load_model(model_id: str, device: str = "cuda", dtype=torch.float32, attn_im
     return model.to(device=device, dtype=dtype).train()
 
 
-def get_batches(model_id: str, split: str, bs: int, seq: int, count: int, dataset: str = "synthetic", device: str = "cuda", vocab: Optional[int] = None, seed: int = 0):
-    """``count`` language-model batches resident on ``device`` (uniform-random tokens offline)."""
+def get_batches(model_id: str, split: str, bs: int, seq: int, count: int, dataset: str = "synthetic", device: str = "cuda", vocab: Optional[int] = None, seed: int = 0,
+                num_labels: int = 0):
+    """``count`` batches resident on ``device`` (uniform-random tokens offline): language-model labels, or with ``num_labels``
+    one random class per sequence (a memory/throughput protocol; quality columns of such rows are not meaningful)."""
     gen = torch.Generator().manual_seed(seed + (1 if split != "train" else 0))
     vocab = vocab or 50257
     out = []
     for _ in range(count):
         ids = torch.randint(0, vocab, (bs, seq), generator=gen).to(device)
-        out.append({"input_ids": ids, "attention_mask": torch.ones_like(ids), "labels": ids.clone()})
+        labels = torch.randint(0, num_labels, (bs,), generator=gen).to(device) if num_labels else ids.clone()
+        out.append({"input_ids": ids, "attention_mask": torch.ones_like(ids), "labels": labels})
     return out
 
 
-def build_optimizer(model, lr: float = 5e-5, eight_bit: bool = True, weight_decay: float = 0.0):
+def build_optimizer(model, lr: float = 5e-5, eight_bit: bool = True, weight_decay: float = 0.0, kind: Optional[str] = None):
+    """AdamW (8-bit block-wise by default on CUDA); ``kind`` ``"subtrack"``/``"galore"`` builds the low-rank-state optimizers."""
     from stacr_b200.optim import AdamW, AdamW8bit
 
+    if kind in ("subtrack", "galore"):
+        from stacr_b200.comparators.galore_adapter import create_galore_optimizer
+        from stacr_b200.comparators.subtrack_adapter import create_subtrack_optimizer
+
+        if kind == "subtrack":
+            return create_subtrack_optimizer(model, {"lr": lr, "weight_decay": weight_decay})
+        return create_galore_optimizer(model, lr=lr, rank=8, weight_decay=weight_decay)
     params = [p for p in model.parameters() if p.requires_grad]
-    name = PARAMETERS.get("optimizer", "adamw8bit" if eight_bit else "adamw")
+    name = kind or PARAMETERS.get("optimizer", "adamw8bit" if eight_bit else "adamw")
     if name == "adamw8bit" and params and params[0].is_cuda:
         return AdamW8bit(params, lr=lr, weight_decay=weight_decay)
     if params and params[0].is_cuda:
@@ -260,6 +271,17 @@ def run_config(method: str, seed: int = 42, *, model_id: str = "gpt2-medium", bs
     free_all()
     set_seed(seed)
     model = load_model(model_id, device, dtype=model_dtype, attn_impl=attn_impl, **(model_overrides or {}))
+    num_labels = int(getattr(model.config, "num_labels", 2)) if type(model).__name__.endswith("ForSequenceClassification") else 0
+    adapter_report = None
+    if extra.get("lora") or extra.get("qlora"):
+        from stacr_b200.protocols.lora import apply_lora, trainable_parameter_report
+
+        adapters = apply_lora(model, r=8, alpha=16.0, quantize_base=bool(extra.get("qlora")))
+        adapter_report = {"adapter_rank": 8, "n_adapters": len(adapters), **trainable_parameter_report(model)}
+        if stacr_cfg:                      # only trainable projections save inputs: an adapter-only run has an empty MLP surface
+            stacr_cfg = dict(stacr_cfg, allow_empty=True, trainable_only=True)
+            adapter_report["n_eligible_mlp_layers"] = len(S.select_target_names(model, surface=stacr_cfg.get("surface", "mlp"), min_features=int(stacr_cfg.get("min_features", 256))))
+            adapter_report["empty_compression_control"] = adapter_report["n_eligible_mlp_layers"] == 0
     n_ckpt = apply_selective_checkpointing(model, ckpt_every, ckpt_offset)
     n_off = apply_selective_offload(model, offload_every, 1 if offload_every > 1 else 0)
     if freeze_mlp:
@@ -271,14 +293,20 @@ def run_config(method: str, seed: int = 42, *, model_id: str = "gpt2-medium", bs
         layers = apply_comparator(model, extra["basis_comparator"], dict(stacr_cfg))
     else:
         layers = stacr_on_blocks(model, stacr_cfg, stacr_block_pred) if stacr_cfg else []
-    opt = build_optimizer(model, lr, eight_bit and cuda)
+    opt = build_optimizer(model, lr, eight_bit and cuda, kind=extra.get("optimizer"))
     vocab = getattr(getattr(model, "config", None), "vocab_size", None)
-    train = get_batches(model_id, "train", bs, seq, steps, dataset, device, vocab, seed)
+    train = get_batches(model_id, "train", bs, seq, steps, dataset, device, vocab, seed, num_labels)
     ledger = SSPLedger(layers)
     losses = []
     ev0 = ev1 = None
     t0 = None
+    trace_at = {s_ for s_ in (10, 50, 100, 200, 300, 400, 500, steps - 1) if s_ < steps} if extra.get("trace_memory") else set()
+    marks, phases = [], None
     for i, batch in enumerate(train):
+        if extra.get("phase_profile") and cuda and i == min(measure_from + 1, steps - 1):
+            phases = _phase_peaks(model, opt, batch, amp)
+            losses.append(phases.pop("loss"))
+            continue
         S.set_step(layers, i)
         if i == measure_from:
             sync()
@@ -290,13 +318,18 @@ def run_config(method: str, seed: int = 42, *, model_id: str = "gpt2-medium", bs
         opt.zero_grad(set_to_none=True)
         with amp_ctx(amp and cuda):
             loss = model(**batch).loss
-        value = float(loss)
+        value = float(loss.detach())
         if not math.isfinite(value):
             raise FloatingPointError(f"Nonfinite loss at step {i}")
         loss.backward()
         opt.step()
         losses.append(value)
         ledger.probe(bs * seq)
+        if i in trace_at:
+            sync()
+            marks.append({"step": i, "allocated_GiB": gib(torch.cuda.max_memory_allocated()) if cuda else 0.0,
+                          "reserved_GiB": gib(torch.cuda.max_memory_reserved()) if cuda else 0.0, "nvml_GiB": nvml_used(0) if cuda else float("nan"),
+                          "elapsed_s": time.perf_counter() - (t0 or time.perf_counter())})
     if cuda and ev0 is not None:
         ev1.record()
         sync()
@@ -309,7 +342,7 @@ def run_config(method: str, seed: int = 42, *, model_id: str = "gpt2-medium", bs
     if eval_batches:
         model.eval()
         with torch.no_grad(), amp_ctx(amp and cuda):
-            nll = [float(model(**b).loss) for b in get_batches(model_id, "validation", bs, seq, eval_batches, dataset, device, vocab, seed)]
+            nll = [float(model(**b).loss) for b in get_batches(model_id, "validation", bs, seq, eval_batches, dataset, device, vocab, seed, num_labels)]
         val_ppl = math.exp(min(700.0, sum(nll) / len(nll)))
     row = {
         "method": method, "seed": seed, "model": model_id, "bs": bs, "seq": seq, "steps": steps, "steps_measured": measured,
@@ -318,9 +351,45 @@ def run_config(method: str, seed: int = 42, *, model_id: str = "gpt2-medium", bs
         "final_train_loss": losses[-1] if losses else None, "validation_ppl": val_ppl, "data": dataset, "status": "ok",
         "ssp": ledger.report(baseline_peak_bytes), **{k: v for k, v in extra.items() if isinstance(v, (int, float, str, bool, type(None)))},
     }
+    if num_labels:
+        row.update(label_protocol="random_classes", quality_metric_valid=False)
+    if adapter_report:
+        row.update(adapter_report)
+    if marks:
+        row.update(marks=marks, final_allocated_GiB=marks[-1]["allocated_GiB"], final_reserved_GiB=marks[-1]["reserved_GiB"], final_nvml_GiB=marks[-1]["nvml_GiB"])
+    if phases:
+        row["phase_peaks_GiB"] = phases
     del model, opt, train, layers
     free_all()
     return row
+
+
+def _phase_peaks(model, opt, batch, amp: bool) -> dict:
+    """One training step with the allocator's peak read after each phase: where in the step the memory peak is set.
+
+    Returns GiB figures: resident bytes before the step, the peak reached during forward, backward and the optimizer
+    step, and what is still held when forward ends (the saved activations plus the loss graph).
+    """
+    sync()
+    before = torch.cuda.memory_allocated()
+    out = {"resident_before_step": gib(before)}
+    opt.zero_grad(set_to_none=True)
+    torch.cuda.reset_peak_memory_stats()
+    with amp_ctx(amp):
+        loss = model(**batch).loss
+    sync()
+    out["forward_peak"], out["held_after_forward"] = gib(torch.cuda.max_memory_allocated()), gib(torch.cuda.memory_allocated() - before)
+    torch.cuda.reset_peak_memory_stats()
+    loss.backward()
+    sync()
+    out["backward_peak"] = gib(torch.cuda.max_memory_allocated())
+    torch.cuda.reset_peak_memory_stats()
+    opt.step()
+    sync()
+    out["optimizer_peak"] = gib(torch.cuda.max_memory_allocated())
+    out["peak_phase"] = max(("forward_peak", "backward_peak", "optimizer_peak"), key=lambda k: out[k])
+    out["loss"] = float(loss.detach())
+    return out
 
 
 def emit(record: dict, path: str | Path) -> None:

@@ -9,6 +9,7 @@ Grid ``composed_frontier`` (deployment; 9 cells).  Parity: experiments/benchmark
 from __future__ import annotations
 
 from . import _entry
+from .probes import complement  # noqa: F401
 
 NAME = "composed_frontier"
 

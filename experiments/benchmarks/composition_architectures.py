@@ -9,6 +9,7 @@ Grid ``composition_architectures`` (mechanism; 16 cells).  Parity: experiments/b
 from __future__ import annotations
 
 from . import _entry
+from .probes import complement  # noqa: F401
 
 NAME = "composition_architectures"
 

@@ -9,6 +9,7 @@ Grid ``composition_law`` (mechanism; 18 cells).  Parity: experiments/benchmarks/
 from __future__ import annotations
 
 from . import _entry
+from .probes import complement  # noqa: F401
 
 NAME = "composition_law"
 

@@ -9,6 +9,7 @@ Grid ``equal_budget_frontier`` (deployment; 8 cells).  Parity: experiments/bench
 from __future__ import annotations
 
 from . import _entry
+from .probes import complement  # noqa: F401
 
 NAME = "equal_budget_frontier"
 

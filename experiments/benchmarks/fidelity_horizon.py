@@ -9,6 +9,7 @@ Grid ``fidelity_horizon`` (fidelity; 6 cells).  Parity: experiments/benchmarks/f
 from __future__ import annotations
 
 from . import _entry
+from .probes import complement  # noqa: F401
 
 NAME = "fidelity_horizon"
 

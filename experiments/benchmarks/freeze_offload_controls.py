@@ -9,6 +9,7 @@ Grid ``freeze_offload_controls`` (mechanism; 5 cells).  Parity: experiments/benc
 from __future__ import annotations
 
 from . import _entry
+from .probes import complement  # noqa: F401
 
 NAME = "freeze_offload_controls"
 

@@ -49,8 +49,14 @@ def run_experiment(name: str, seeds: Iterable[int] = (42,), output: str | os.Pat
     meta = EXPERIMENTS[name]
     out = output or (common.RESULTS / f"{name}.jsonl")
     rows = []
+    stopped: set = set()            # (method, model) pairs of an ascending probe that already ran out of memory
     for cell in meta["cells"]:
         for seed in (seeds if meta.get("seeds") else list(seeds)[:1]):
+            probe_key = (cell.get("method"), cell.get("model_id"), seed) if cell.get("probe") == "ascending" else None
+            if probe_key in stopped:
+                rows.append({"method": cell.get("method"), "model": cell.get("model_id"), "bs": cell.get("bs"), "seed": seed, "fits": False,
+                             "status": "skipped_larger_than_first_failure", "experiment": name})
+                continue
             try:
                 row = _run_cell(cell, seed)
             except torch.cuda.OutOfMemoryError:
@@ -59,6 +65,10 @@ def run_experiment(name: str, seeds: Iterable[int] = (42,), output: str | os.Pat
             except FloatingPointError as exc:
                 row = {"method": cell.get("method"), "model": cell.get("model_id"), "seed": seed, "status": "nonfinite", "error": str(exc)}
             row["experiment"] = name
+            if probe_key is not None:
+                row["fits"] = row.get("status") == "ok"
+                if not row["fits"]:
+                    stopped.add(probe_key)
             rows.append(row)
             if common._RECORDER is None:
                 common.emit(row, out)

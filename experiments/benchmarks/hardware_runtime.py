@@ -9,6 +9,7 @@ Grid ``hardware_runtime`` (systems; 8 cells).  Parity: experiments/benchmarks/ha
 from __future__ import annotations
 
 from . import _entry
+from .probes import complement  # noqa: F401
 
 NAME = "hardware_runtime"
 
@@ -19,6 +20,9 @@ def cells():
 
 def run(seeds=(42,), output=None):
     return _entry.run(NAME, seeds, output)
+
+
+from .probes import gpu_gib  # noqa: E402,F401
 
 
 def main(argv=None) -> int:

@@ -9,6 +9,7 @@ Grid ``instant_comparison`` (comparators; 9 cells).  Parity: experiments/benchma
 from __future__ import annotations
 
 from . import _entry
+from .probes import complement  # noqa: F401
 
 NAME = "instant_comparison"
 
@@ -19,6 +20,11 @@ def cells():
 
 def run(seeds=(42,), output=None):
     return _entry.run(NAME, seeds, output)
+
+
+def enumerate_cells():
+    """The grid's cells in run order (same as :func:`cells`)."""
+    return cells()
 
 
 def main(argv=None) -> int:

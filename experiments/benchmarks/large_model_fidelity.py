@@ -9,6 +9,7 @@ Grid ``large_model_fidelity`` (fidelity; 3 cells).  Parity: experiments/benchmar
 from __future__ import annotations
 
 from . import _entry
+from .probes import complement  # noqa: F401
 
 NAME = "large_model_fidelity"
 

@@ -9,6 +9,7 @@ Grid ``large_models`` (deployment; 12 cells).  Parity: experiments/benchmarks/la
 from __future__ import annotations
 
 from . import _entry
+from .probes import complement  # noqa: F401
 
 NAME = "large_models"
 
@@ -19,6 +20,9 @@ def cells():
 
 def run(seeds=(42,), output=None):
     return _entry.run(NAME, seeds, output)
+
+
+from .probes import maxbatch, maxlen, one, sweep  # noqa: E402,F401  (search helpers bound to this grid's arms by the caller)
 
 
 def main(argv=None) -> int:

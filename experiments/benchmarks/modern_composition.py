@@ -9,6 +9,7 @@ Grid ``modern_composition`` (deployment; 12 cells).  Parity: experiments/benchma
 from __future__ import annotations
 
 from . import _entry
+from .probes import complement  # noqa: F401
 
 NAME = "modern_composition"
 

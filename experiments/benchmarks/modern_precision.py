@@ -9,6 +9,7 @@ Grid ``modern_precision`` (quality; 12 cells).  Parity: experiments/benchmarks/m
 from __future__ import annotations
 
 from . import _entry
+from .probes import complement  # noqa: F401
 
 NAME = "modern_precision"
 

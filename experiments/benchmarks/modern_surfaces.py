@@ -9,6 +9,7 @@ Grid ``modern_surfaces`` (deployment; 6 cells).  Parity: experiments/benchmarks/
 from __future__ import annotations
 
 from . import _entry
+from .probes import complement  # noqa: F401
 
 NAME = "modern_surfaces"
 

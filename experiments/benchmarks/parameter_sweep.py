@@ -9,6 +9,7 @@ Grid ``parameter_sweep`` (deployment; 32 cells).  Parity: experiments/benchmarks
 from __future__ import annotations
 
 from . import _entry
+from .probes import complement  # noqa: F401
 
 NAME = "parameter_sweep"
 

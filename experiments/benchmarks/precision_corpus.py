@@ -9,6 +9,7 @@ Grid ``precision_corpus`` (quality; 12 cells).  Parity: experiments/benchmarks/p
 from __future__ import annotations
 
 from . import _entry
+from .probes import complement  # noqa: F401
 
 NAME = "precision_corpus"
 

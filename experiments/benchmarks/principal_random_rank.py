@@ -9,6 +9,7 @@ Grid ``principal_random_rank`` (fidelity; 4 cells).  Parity: experiments/benchma
 from __future__ import annotations
 
 from . import _entry
+from .probes import complement  # noqa: F401
 
 NAME = "principal_random_rank"
 

@@ -9,6 +9,7 @@ Grid ``pythia`` (quality; 4 cells).  Parity: experiments/benchmarks/pythia.py.
 from __future__ import annotations
 
 from . import _entry
+from .probes import complement  # noqa: F401
 
 NAME = "pythia"
 

@@ -133,7 +133,8 @@ EXPERIMENTS = {
     "swiglu_composition": _meta("swiglu_composition", "Same-block versus disjoint checkpoint composition on SwiGLU", "deployment", seeds=False,
                                 cells=[dict(LLAMA1B, method=a, **kw) for a, kw in (("ckpt_k2", dict(ckpt_every=2)), ("ckpt_k2_same_block_turbo", dict(ckpt_every=2, stacr_cfg=dict(SWIGLU, turbo_after_step=2))), ("ckpt_k2_disjoint_turbo", dict(ckpt_every=2, stacr_cfg=dict(SWIGLU, turbo_after_step=2), complement=2)))]),
     "basis_storage": _meta("basis_storage", "Allocation-only duplicated-basis and residual-storage controls", "mechanism", seeds=False,
-                           cells=[dict(GPT2M, method=f"basis_{d}", stacr_cfg=dict(R8, basis_dtype=d)) for d in ("float32", "bfloat16")] + [dict(GPT2M, method=f"residual_bits_{b}", stacr_cfg=dict(R8, residual_bits=b)) for b in (0, 4, 8)]),
+                           cells=[dict(GPT2M, method=f"basis_{d}", stacr_cfg=dict(R8, basis_dtype=d)) for d in ("float32", "bfloat16")] + [dict(GPT2M, method=f"residual_bits_{b}", stacr_cfg=dict(R8, residual_bits=b)) for b in (0, 4, 8)]
+                           + [dict(GPT2M, method=f"fat_{n}", comparator="fat", stacr_cfg=dict(R8, basis_per_call=b, fat_residual=f)) for n, b, f in (("basis_per_call", True, False), ("residual", False, True), ("both", True, True))]),
     "subtrack_composition": _meta("subtrack_composition", "Upstream SubTrack++ BERT/SST-2 and adaptive STAC-R composition", "comparators", standard=False,
                                   cells=[dict(model_id="bert-base-uncased", bs=32, seq=128, task="sequence_classification", method=m, optimizer=o, **kw) for m, o, kw in (("subtrack", "subtrack", {}), ("subtrack_stacr", "subtrack", dict(stacr_cfg=R8, engine="adaptive")), ("adamw", "adamw", {}))]),
     "instant_comparison": _meta("instant_comparison", "INSTANT SST-2, MRPC, and GPT-2 protocols with calibration", "comparators", standard=False,

@@ -9,6 +9,7 @@ Grid ``residual_budget`` (quality; 4 cells).  Parity: experiments/benchmarks/res
 from __future__ import annotations
 
 from . import _entry
+from .probes import complement  # noqa: F401
 
 NAME = "residual_budget"
 

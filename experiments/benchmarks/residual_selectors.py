@@ -9,6 +9,7 @@ Grid ``residual_selectors`` (systems; 5 cells).  Parity: experiments/benchmarks/
 from __future__ import annotations
 
 from . import _entry
+from .probes import complement  # noqa: F401
 
 NAME = "residual_selectors"
 

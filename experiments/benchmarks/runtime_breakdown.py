@@ -9,6 +9,7 @@ Grid ``runtime_breakdown`` (systems; 10 cells).  Parity: experiments/benchmarks/
 from __future__ import annotations
 
 from . import _entry
+from .probes import complement  # noqa: F401
 
 NAME = "runtime_breakdown"
 

@@ -9,6 +9,7 @@ Grid ``single_model_fidelity`` (fidelity; 2 cells).  Parity: experiments/benchma
 from __future__ import annotations
 
 from . import _entry
+from .probes import complement  # noqa: F401
 
 NAME = "single_model_fidelity"
 
@@ -19,6 +20,9 @@ def cells():
 
 def run(seeds=(42,), output=None):
     return _entry.run(NAME, seeds, output)
+
+
+from .probes import grads  # noqa: E402,F401  (paired gradients of one model, RNG seeded per call)
 
 
 def main(argv=None) -> int:

@@ -9,6 +9,7 @@ Grid ``subtrack_composition`` (comparators; 3 cells).  Parity: experiments/bench
 from __future__ import annotations
 
 from . import _entry
+from .probes import complement  # noqa: F401
 
 NAME = "subtrack_composition"
 
@@ -19,6 +20,11 @@ def cells():
 
 def run(seeds=(42,), output=None):
     return _entry.run(NAME, seeds, output)
+
+
+def enumerate_cells():
+    """The grid's cells in run order (same as :func:`cells`)."""
+    return cells()
 
 
 def main(argv=None) -> int:

@@ -9,6 +9,7 @@ Grid ``surface_expansion`` (deployment; 5 cells).  Parity: experiments/benchmark
 from __future__ import annotations
 
 from . import _entry
+from .probes import complement  # noqa: F401
 
 NAME = "surface_expansion"
 

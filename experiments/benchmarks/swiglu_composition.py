@@ -9,6 +9,7 @@ Grid ``swiglu_composition`` (deployment; 3 cells).  Parity: experiments/benchmar
 from __future__ import annotations
 
 from . import _entry
+from .probes import complement  # noqa: F401
 
 NAME = "swiglu_composition"
 

@@ -9,6 +9,7 @@ Grid ``swiglu_fidelity`` (fidelity; 12 cells).  Parity: experiments/benchmarks/s
 from __future__ import annotations
 
 from . import _entry
+from .probes import complement  # noqa: F401
 
 NAME = "swiglu_fidelity"
 

@@ -9,6 +9,7 @@ Grid ``swiglu_precision`` (mechanism; 8 cells).  Parity: experiments/benchmarks/
 from __future__ import annotations
 
 from . import _entry
+from .probes import complement  # noqa: F401
 
 NAME = "swiglu_precision"
 

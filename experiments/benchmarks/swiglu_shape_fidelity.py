@@ -9,6 +9,7 @@ Grid ``swiglu_shape_fidelity`` (fidelity; 2 cells).  Parity: experiments/benchma
 from __future__ import annotations
 
 from . import _entry
+from .probes import complement  # noqa: F401
 
 NAME = "swiglu_shape_fidelity"
 

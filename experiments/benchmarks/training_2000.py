@@ -9,6 +9,7 @@ Grid ``training_2000`` (quality; 7 cells).  Parity: experiments/benchmarks/train
 from __future__ import annotations
 
 from . import _entry
+from .probes import complement  # noqa: F401
 
 NAME = "training_2000"
 

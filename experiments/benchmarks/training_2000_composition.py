@@ -9,6 +9,7 @@ Grid ``training_2000_composition`` (quality; 2 cells).  Parity: experiments/benc
 from __future__ import annotations
 
 from . import _entry
+from .probes import complement  # noqa: F401
 
 NAME = "training_2000_composition"
 

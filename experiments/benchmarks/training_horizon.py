@@ -9,6 +9,7 @@ Grid ``training_horizon`` (quality; 12 cells).  Parity: experiments/benchmarks/t
 from __future__ import annotations
 
 from . import _entry
+from .probes import complement  # noqa: F401
 
 NAME = "training_horizon"
 

@@ -80,7 +80,90 @@ class PracLinear(_ComparatorBase):
         self._install(basis)
 
 
-COMPARATORS = {"stacr": (STACRLinear, 0.005), "lowrank": (STACRLinear, 0.0), "untracked": (UntrackedLinear, 0.0),
+class FatFunction(torch.autograd.Function):
+    """Storage control: the same factors as the compressed layer, saved the wasteful way.
+
+    ``basis_per_call`` saves a private copy of the basis with every call instead of a reference to the layer's one
+    buffer; ``fat_residual`` saves int64 positions and fp32 values instead of narrow indices and quantised values.
+    The arithmetic is the layer's reference arithmetic in PyTorch, so the only thing that moves between this control
+    and the real layer is what autograd holds (parity: experiments/benchmarks/basis_storage.py:20-95).
+    """
+
+    @staticmethod
+    def forward(ctx, x, weight, bias, basis, budget, residual_bits, chunk_rows, transposed, basis_per_call, fat_residual):
+        from ..layers import _select_chunk_topk
+        from ..quant import quantize_values
+
+        feats = basis.shape[0]
+        x2d = x.reshape(-1, feats)
+        w = weight.to(x2d.dtype)
+        out = x2d @ (w if transposed else w.t())
+        if bias is not None:
+            out = out + bias.to(out.dtype)
+        q = basis.to(x2d.dtype)
+        coeff = x2d @ q
+        idx, val = _select_chunk_topk(x2d, coeff, q, float(budget), chunk_rows) if float(budget) > 0 else (None, None)
+        saved = [coeff, weight, q.clone() if basis_per_call else basis]
+        ctx.scale = None
+        if idx is not None:
+            if fat_residual or not residual_bits:
+                saved += [idx.long() if fat_residual else idx, val.float() if fat_residual else val]
+            else:
+                packed = quantize_values(val, int(residual_bits))
+                saved += [idx, packed.data]
+                ctx.scale, ctx.bits, ctx.count = packed.scale, int(residual_bits), val.numel()
+        ctx.save_for_backward(*saved)
+        ctx.meta = (x.shape[:-1], feats, out.shape[1], bool(transposed), bias is not None and bias.requires_grad)
+        return out.reshape(*x.shape[:-1], out.shape[1])
+
+    @staticmethod
+    def backward(ctx, dy):
+        from ..quant import QuantizedValues
+
+        lead, feats, outs, transposed, bias_grad = ctx.meta
+        coeff, weight, q = ctx.saved_tensors[:3]
+        g = dy.reshape(-1, outs)
+        dx = dw = db = None
+        if ctx.needs_input_grad[0]:
+            w = weight.to(g.dtype)
+            dx = (g @ (w.t() if transposed else w)).reshape(*lead, feats)
+        if ctx.needs_input_grad[1]:
+            dw = (g.t() @ coeff.to(g.dtype)) @ q.to(g.dtype).t()
+            if len(ctx.saved_tensors) > 3:
+                idx, val = ctx.saved_tensors[3], ctx.saved_tensors[4]
+                if ctx.scale is not None:
+                    val = QuantizedValues(val, ctx.scale, ctx.bits, ctx.count).dequantize(torch.float32)
+                rows, cols = torch.div(idx.long(), feats, rounding_mode="floor"), idx.long() % feats
+                dw = dw.float().t().index_add(0, cols, g[rows].float() * val.float()[:, None]).t()
+            dw = (dw.t() if transposed else dw).to(weight.dtype)
+        if bias_grad:
+            db = g.sum(0)
+        return dx, dw, db, None, None, None, None, None, None, None
+
+
+class FatLinear(STACRLinear):
+    basis_per_call = True
+    fat_residual = True
+
+    def forward(self, x):
+        if not (self.training and torch.is_grad_enabled() and self.weight.requires_grad) or x.numel() == 0:
+            return self._exact(x)
+        self._sync_host()
+        self._refresh_basis(x.reshape(-1, self.in_features))
+        budget = 0.0 if self._turbo() else self.residual_budget
+        return FatFunction.apply(x, self.weight, self.bias, self.basis, budget, self.residual_bits, self.chunk_rows, self.transposed,
+                                 self.basis_per_call, self.fat_residual)
+
+
+def apply_fat(model, config: dict, basis_per_call: bool = True, fat_residual: bool = True):
+    """Wrap the configured surface with the storage control; the two flags pick which saving is undone."""
+    layers = apply_comparator(model, "fat", config)
+    for layer in layers:
+        layer.basis_per_call, layer.fat_residual = bool(basis_per_call), bool(fat_residual)
+    return layers
+
+
+COMPARATORS = {"fat": (FatLinear, 0.005), "stacr": (STACRLinear, 0.005), "lowrank": (STACRLinear, 0.0), "untracked": (UntrackedLinear, 0.0),
                "oasis": (OasisLinear, 0.0), "prac": (PracLinear, 0.0)}
 
 
@@ -92,7 +175,7 @@ def apply_comparator(model, kind: str, config: dict):
         raise ValueError(f"Unknown basis comparator {kind!r}; choose {sorted(COMPARATORS)}")
     cls, budget = COMPARATORS[kind]
     cfg = dict(config)
-    if kind == "stacr":
+    if kind in ("stacr", "fat"):
         cfg.setdefault("residual_budget", budget)
     else:
         cfg["residual_budget"] = 0.0
@@ -109,6 +192,8 @@ def apply_comparator(model, kind: str, config: dict):
         layer.train(src.training)
         if isinstance(layer, PracLinear):
             layer.refresh_every, layer.principal_frac = int(cfg.get("refresh_every", 500)), float(cfg.get("principal_frac", 0.5))
+        if isinstance(layer, FatLinear):
+            layer.basis_per_call, layer.fat_residual = bool(cfg.get("basis_per_call", True)), bool(cfg.get("fat_residual", True))
         if isinstance(layer, OasisLinear):
             layer.gamma = float(cfg.get("gamma", 1.0))
         setattr(parent, leaf, layer)

@@ -342,3 +342,117 @@ def test_top_level_experiment_scripts_run_by_path(tmp_path):
     row = train.main(["--config", "synthetic_stacr", "--steps", "2", "--device", "cpu", "--output", str(tmp_path / "r.csv")])
     assert row["steps"] == 2 and evaluate.main(["--csv", str(tmp_path / "r.csv"), "--columns", "steps", "train_loss"]) == 0
     assert subprocess.run([sys.executable, "-m", "experiments.benchmarks.residual_budget", "--dry-run"], capture_output=True, cwd=ROOT, timeout=300).returncode == 0
+
+
+def test_nf4_codes_round_trip_and_lora_composition_surface():
+    import stacr_b200 as S
+    from stacr_b200.models import build_model
+    from stacr_b200.protocols.lora import NF4_LEVELS, LoRALinear, NF4Linear, apply_lora, nf4_dequantize, nf4_quantize, trainable_parameter_report
+
+    assert len(NF4_LEVELS) == 16 and NF4_LEVELS[0] == -1.0 and NF4_LEVELS[7] == 0.0 and NF4_LEVELS[-1] == 1.0 and list(NF4_LEVELS) == sorted(NF4_LEVELS)
+    torch.manual_seed(0)
+    w = torch.randn(40, 96) * 0.05
+    back = nf4_dequantize(*nf4_quantize(w), w.shape)
+    assert float((back - w).norm() / w.norm()) < 0.12                                  # 16 levels on Gaussian weights
+    exact = torch.tensor(NF4_LEVELS).repeat(8)[:64].reshape(1, 64) * 0.5                 # values on the grid survive exactly (up to the 8-bit scale)
+    assert torch.allclose(nf4_dequantize(*nf4_quantize(exact), exact.shape), exact, atol=5e-3)
+    lin = nn.Linear(96, 40)
+    q = NF4Linear(lin)
+    assert 4.0 < 8 * q.weight_bytes() / lin.weight.numel() < 4.3 and not any(p.requires_grad for p in q.parameters())
+    x = torch.randn(5, 96, requires_grad=True)
+    q(x).sum().backward()
+    assert torch.allclose(x.grad, q.dequantize().sum(0).expand(5, -1), atol=1e-5)
+    adapter = LoRALinear(nn.Linear(16, 8), r=4, alpha=8)
+    probe = torch.randn(3, 16)
+    assert torch.equal(adapter(probe), adapter.base(probe))                             # B starts at zero: the adapter is a no-op
+    adapter.lora_B.data.normal_()
+    assert torch.allclose(adapter(probe), nn.functional.linear(probe, adapter.merged_weight(), adapter.base.bias), atol=1e-5)
+
+    model = build_model("gpt2", **TINY_GPT)
+    adapters = apply_lora(model)
+    report = trainable_parameter_report(model)
+    assert len(adapters) == 2 and 0 < report["trainable_pct"] < 10 and report["nf4_weight_bytes"] == 0
+    assert all(("lora_" in n) == p.requires_grad for n, p in model.named_parameters())
+    assert S.select_target_names(model, surface="mlp", min_features=32) == []           # frozen MLP: empty compression surface
+    assert len(S.select_target_names(model, surface="mlp", min_features=32, trainable_only=False)) == 4
+    ids = torch.randint(0, 128, (2, 8))
+    model(input_ids=ids, labels=ids).loss.backward()
+    assert adapters[0].lora_B.grad.abs().sum() > 0 and model.transformer.h[0].mlp.c_fc.weight.grad is None
+    bert = build_model("bert-base-uncased", **TINY_BERT)
+    assert len(apply_lora(bert, quantize_base=True)) == 4 and trainable_parameter_report(bert)["nf4_weight_bytes"] > 0
+    assert isinstance(bert.bert.encoder.layer[0].intermediate.dense, NF4Linear)
+    with pytest.raises(ValueError):
+        apply_lora(build_model("gpt2", **TINY_GPT), target_modules=["nope"])
+
+
+def test_fat_storage_control_matches_the_layer_and_saves_more():
+    from stacr_b200.comparators.activation import apply_comparator, apply_fat
+
+    def make():
+        torch.manual_seed(0)
+        return nn.Sequential(nn.Linear(64, 128), nn.GELU(), nn.Linear(128, 64)).train()
+
+    cfg = dict(rank=4, residual_budget=0.05, surface="all", min_features=1, turbo_after_step=None, residual_bits=8)
+    x = torch.randn(3, 16, 64)
+    real, lean, fat = make(), make(), make()
+    apply_comparator(real, "stacr", cfg)
+    apply_fat(lean, cfg, basis_per_call=True, fat_residual=False)
+    apply_fat(fat, cfg, basis_per_call=True, fat_residual=True)
+    grads = []
+    for m in (real, lean, fat):
+        m(x).square().sum().backward()
+        grads.append([p.grad.clone() for p in m.parameters()])
+    for a, b in zip(grads[0], grads[1]):
+        assert torch.allclose(a, b, rtol=1e-4, atol=1e-5)               # same factors, same arithmetic
+    for a, b in zip(grads[0], grads[2]):
+        assert torch.allclose(a, b, rtol=0.05, atol=0.05 * float(a.abs().max()))   # unquantised residual values differ slightly
+
+    def held(model):
+        seen = []
+        with torch.autograd.graph.saved_tensors_hooks(lambda t: seen.append(t) or t, lambda t: t):
+            model[0](x)
+        return seen
+
+    fat_saved, lean_saved = held(fat), held(lean)
+    assert any(t.dtype == torch.int64 for t in fat_saved) and not any(t.dtype == torch.int64 for t in lean_saved)
+    assert all(t.data_ptr() != fat[0].basis.data_ptr() for t in fat_saved)      # a private basis copy per call
+    assert sum(t.numel() * t.element_size() for t in fat_saved) > sum(t.numel() * t.element_size() for t in lean_saved)
+
+
+def test_benchmark_runner_adapter_trace_probe_and_search_helpers():
+    from experiments.benchmarks import allocator_stability, capacity_search, common, lora, probes, qlora, rate_distortion, swiglu_surfaces
+    from stacr_b200.models import build_model
+
+    over = dict(device="cpu", model_overrides=TINY_GPT)
+    old = dict(lora.CFG)
+    lora.CFG["min_features"] = 32
+    try:
+        rows = {(a, s): lora.run_lora("gpt2", 2, 16, 4, 42, a, s, **over) for a in (False, True) for s in (False, True)}
+    finally:
+        lora.CFG.clear()
+        lora.CFG.update(old)
+    assert rows[(False, True)]["n_wrapped_layers"] == 4 and rows[(True, True)]["n_wrapped_layers"] == 0
+    assert rows[(True, True)]["empty_compression_control"] is True and rows[(True, False)]["n_adapters"] == 2
+    with pytest.raises(ValueError):
+        lora.run_lora("gpt2", 2, 16, 4, 42, True, False, qlora=True)
+    row = qlora.run_qlora("qlora", False, 2, 16, 3, 42, device="cpu", model_overrides=TINY_BERT)
+    assert row["quant"] and row["nf4_weight_bytes"] > 0 and row["label_protocol"] == "random_classes" and row["quality_metric_valid"] is False
+    assert type(qlora.build("full", device="cpu", **TINY_BERT)).__name__.endswith("ForSequenceClassification")
+    stored, dense, n = rate_distortion.payload_bytes("stacr", 4, 0.01, "gpt2", 2, 16, min_features=32, **TINY_GPT)
+    assert n == 4 and 0 < stored < dense
+    low, _, _ = rate_distortion.payload_bytes("lowrank", 4, 0.01, "gpt2", 2, 16, min_features=32, **TINY_GPT)
+    assert low < stored
+    best = capacity_search.largest_fitting("gpt2", 16, torch.float32, 1, 3, "baseline", None, steps=2, **over)
+    assert best["bs"] == 3
+    traced = allocator_stability.trace("stacr_r8", dict(rank=4, surface="mlp", min_features=32, residual_budget=0.01), "gpt2", 2, 16, 12, **over)
+    assert [m["step"] for m in traced["marks"]] == [10, 11] and "final_reserved_GiB" in traced
+    assert probes.maxlen("gpt2", "baseline", {}, [8, 16], steps=2, measure_from=0, eval_batches=0, **over)["seq"] == 16
+    assert probes.one("no-such-model", "t", "baseline", {}, 1, 8, device="cpu", steps=1, measure_from=0) is None      # failure is recorded, not raised
+    assert swiglu_surfaces.down_proj_names(build_model("llama-tiny"))[0].endswith("mlp.down_proj")
+    cfg = swiglu_surfaces.cfg_for("llama-tiny", "down", {"_down_only": True, "min_features": 32}, 16)
+    assert cfg["rank"] == 16 and cfg["surface"] == "none" and cfg["extra_names"] and "_down_only" not in cfg
+    sub = common.run_config("sub", model_id="bert-base-uncased", bs=2, seq=8, steps=3, measure_from=0, eval_batches=0, optimizer="subtrack",
+                            device="cpu", model_overrides=TINY_BERT)
+    assert sub["status"] == "ok" and sub["label_protocol"] == "random_classes"
+    g, loss = probes.grads(build_model("gpt2", **TINY_GPT), {"input_ids": torch.randint(0, 128, (1, 8)), "labels": torch.randint(0, 128, (1, 8))}, 7)
+    assert loss > 0 and all(v.dtype == torch.float32 for v in g.values())
