@@ -171,6 +171,21 @@ def _basis_views(basis: torch.Tensor):
     return cached
 
 
+_ZERO_FACTORS: dict = {}
+
+
+def _zero_factors(rows: int, cols: int, device):
+    """Cached all-zero rank-1 coefficient column ``[rows, 1]`` and basis ``[cols, 1]`` (bf16)."""
+    key = (rows, cols, device)
+    hit = _ZERO_FACTORS.get(key)
+    if hit is None:
+        if len(_ZERO_FACTORS) > 64:
+            _ZERO_FACTORS.clear()
+        hit = (torch.zeros(rows, 1, dtype=torch.bfloat16, device=device), torch.zeros(cols, 1, dtype=torch.bfloat16, device=device))
+        _ZERO_FACTORS[key] = hit
+    return hit
+
+
 def _select_residual_kernels(x, coeff, qb, budget, chunk_rows, mode, block_size, sample_ratio, bits):
     """Kernel-path selection.  Returns ``(idx, QuantizedValues)`` or ``(None, None)``."""
     from .ops import stacr_ops
@@ -210,12 +225,16 @@ def _select_residual_kernels(x, coeff, qb, budget, chunk_rows, mode, block_size,
     if mode == "block_sparse" and block_size % 8 == 0 and block_size <= 256 and not (block_size & (block_size - 1)):
         energy = stacr_ops.residual_block_energy(x, coeff, qb, block_size)  # [rows, feats/bs]
         per_row = feats // block_size
-        parts = []
-        for lo, hi in _chunk_bounds(rows, chunk_rows):
-            flat = energy[lo:hi].reshape(-1)
-            count = max(1, int(round(budget * flat.numel())))
-            parts.append(flat.topk(count, sorted=False).indices + lo * per_row)
-        blocks = torch.cat(parts)
+        bounds = list(_chunk_bounds(rows, chunk_rows))
+        counts = [max(1, int(round(budget * (hi - lo) * per_row))) for lo, hi in bounds]
+        if per_row % 8 == 0 and len(bounds) <= 16 and rows * per_row < 2 ** 31:
+            # the radix-select kernel run on the block energies themselves: with a zero rank-1 basis its "residual" is its input,
+            # so one call ranks every chunk's blocks (by bf16-rounded energy, the resolution every selector here uses)
+            zc, zq = _zero_factors(rows, per_row, x.device)
+            blocks, _, _ = stacr_ops.residual_topk(energy.to(torch.bfloat16), zc, zq, counts, max(1, int(chunk_rows)), 0, torch.int32)
+            blocks = blocks.long()
+        else:
+            blocks = torch.cat([energy[lo:hi].reshape(-1).topk(c, sorted=False).indices + lo * per_row for (lo, hi), c in zip(bounds, counts)])
         idx = (blocks[:, None] * block_size + torch.arange(block_size, device=x.device)).reshape(-1).to(idt)
         return idx, quantize_values(stacr_ops.residual_gather(x, coeff, qb, idx), bits)
     # sampled (a control selector whose dense workspace is part of its definition) and odd block sizes

@@ -92,11 +92,23 @@ class GemmAllReduce:
 _ENGINES: dict = {}
 
 
+def _max_fused_world() -> int:
+    """Largest tensor-parallel degree served by the fused kernel (``STACR_TP_FUSED_MAX_WORLD``, default 2).
+
+    Every rank stores its partial tile into a slot on *every* rank, so each GPU receives ``world`` tiles per GEMM where a
+    reduce-scatter + all-gather moves ``2 (world - 1) / world``: the same bytes at degree 2 (where the fused kernel measured
+    faster than a library GEMM followed by NCCL), four times as many at degree 8 (where it measured slower).
+    """
+    import os
+
+    return int(os.environ.get("STACR_TP_FUSED_MAX_WORLD", "2"))
+
+
 def engine_for(device: torch.device, max_elems: int, group=None) -> Optional[GemmAllReduce]:
     """One shared engine per (device, group), grown on demand; ``None`` when the fused path cannot run here."""
     from . import symm
 
-    if _world(group) < 2 or device.type != "cuda" or not symm.available():
+    if _world(group) < 2 or _world(group) > _max_fused_world() or device.type != "cuda" or not symm.available():
         return None
     key = (device.index, id(group))
     eng = _ENGINES.get(key)
