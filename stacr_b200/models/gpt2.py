@@ -116,7 +116,10 @@ class GPT2LMHeadModel(nn.Module):
 
     def forward(self, input_ids, attention_mask=None, labels=None, **_):
         hidden = self.transformer(input_ids, attention_mask)
-        if labels is not None and self.config.loss_chunk:
+        # training on a GPU with the stock 50257-entry vocabulary: the head and the loss run together on a padded logits
+        # buffer (an odd leading dimension would push the library onto unaligned GEMM kernels); no logits are returned
+        fused_head = self.training and hidden.is_cuda and self.config.vocab_size % 8 != 0 and torch.is_autocast_enabled()
+        if labels is not None and (self.config.loss_chunk or fused_head):
             return ModelOutput(loss=lm_loss(hidden, labels, self.lm_head, self.config.loss_chunk))
         logits = self.lm_head(hidden)
         loss = lm_loss(logits, labels) if labels is not None else None

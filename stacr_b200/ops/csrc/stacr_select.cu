@@ -465,25 +465,61 @@ __global__ void residual_gather_kernel(const __nv_bfloat16* x, const __nv_bfloat
 }
 
 // energy[row, b] = sum of squared (bf16-rounded) residuals over `bs` consecutive columns;
-// bs is a power of two in [8, 256] dividing n.  One thread per 8 columns, shuffle-reduced.
-__global__ void __launch_bounds__(256) residual_block_energy_kernel(const __nv_bfloat16* x, const __nv_bfloat16* c,
-                                                                    const __nv_bfloat16* q, int rows, int n, int r, int ldx,
-                                                                    int bs, float* energy) {
-  const int row = blockIdx.y;
+// bs is a power of two in [8, 256] dividing n.  A thread owns 8 consecutive columns for BE_ROWS rows: its 8 basis rows
+// stay in registers, the coefficient rows of the CTA come from shared memory as broadcasts, X is read with one 16-byte
+// load per row, and the bs / 8 lanes of a block are shuffle-reduced.
+constexpr int BE_ROWS = 32;
+
+template <int RP>
+__global__ void __launch_bounds__(256) residual_block_energy_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ c,
+                                                                    const __nv_bfloat16* __restrict__ q, int rows, int n, int r, int ldx,
+                                                                    int bs, float* __restrict__ energy) {
+  __shared__ float s_c[BE_ROWS * RP];
+  const int row0 = blockIdx.y * BE_ROWS;
+  const int nrows = min(BE_ROWS, rows - row0);
+  for (int i = threadIdx.x; i < BE_ROWS * RP; i += blockDim.x) {
+    const int lr = i / RP, j = i - lr * RP;
+    s_c[i] = (lr < nrows && j < r) ? __bfloat162float(c[static_cast<size_t>(row0 + lr) * r + j]) : 0.f;
+  }
+  __syncthreads();
   const int tpb = bs / 8;
   const int col = (blockIdx.x * blockDim.x + threadIdx.x) * 8;
-  float sum = 0.f;
-  if (col < n) {
-    for (int i = 0; i < 8 && col + i < n; ++i) {
-      float acc = 0.f;
-      for (int j = 0; j < r; ++j)
-        acc = fmaf(__bfloat162float(c[static_cast<size_t>(row) * r + j]), __bfloat162float(q[static_cast<size_t>(col + i) * r + j]), acc);
-      const float e = __bfloat162float(__float2bfloat16_rn(__bfloat162float(x[static_cast<size_t>(row) * ldx + col + i]) - acc));
-      sum = fmaf(e, e, sum);
+  const bool live = col < n;  // n is a multiple of bs >= 8, so a live thread owns 8 valid columns
+  float qreg[8][RP];
+#pragma unroll
+  for (int i = 0; i < 8; ++i)
+#pragma unroll
+    for (int j = 0; j < RP; ++j) qreg[i][j] = (live && j < r) ? __bfloat162float(q[static_cast<size_t>(col + i) * r + j]) : 0.f;
+  const bool vec = ((ldx & 7) == 0) && ((reinterpret_cast<uintptr_t>(x) & 15) == 0);
+  for (int lr = 0; lr < nrows; ++lr) {
+    float sum = 0.f;
+    if (live) {
+      const __nv_bfloat16* xr = x + static_cast<size_t>(row0 + lr) * ldx + col;
+      float xv[8];
+      if (vec) {
+        const uint4 raw = *reinterpret_cast<const uint4*>(xr);
+        const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          xv[2 * k] = __uint_as_float(w[k] << 16);
+          xv[2 * k + 1] = __uint_as_float(w[k] & 0xFFFF0000u);
+        }
+      } else {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) xv[i] = __bfloat162float(xr[i]);
+      }
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        float acc = 0.f;
+#pragma unroll
+        for (int j = 0; j < RP; ++j) acc = fmaf(s_c[lr * RP + j], qreg[i][j], acc);
+        const float e = __bfloat162float(__float2bfloat16_rn(xv[i] - acc));
+        sum = fmaf(e, e, sum);
+      }
     }
+    for (int off = 1; off < tpb; off <<= 1) sum += __shfl_xor_sync(0xffffffffu, sum, off);
+    if (live && (threadIdx.x % tpb) == 0) energy[static_cast<size_t>(row0 + lr) * (n / bs) + col / bs] = sum;
   }
-  for (int off = 1; off < tpb; off <<= 1) sum += __shfl_xor_sync(0xffffffffu, sum, off);
-  if (col < n && (threadIdx.x % tpb) == 0) energy[static_cast<size_t>(row) * (n / bs) + col / bs] = sum;
 }
 
 template <int RP>
@@ -572,10 +608,18 @@ extern "C" int sb_residual_block_energy(const void* x, const void* c, const void
                                         int bs, float* energy, void* stream) {
   if (rows <= 0) return 0;
   if (bs % 8 || bs > 256 || (bs & (bs - 1)) || n % bs) return -2;
-  dim3 grid((n / 8 + 255) / 256, rows);
-  sb::residual_block_energy_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
-      static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(c), static_cast<const __nv_bfloat16*>(q), rows, n,
-      r, ldx, bs, energy);
+  if (r < 1 || r > 32) return -2;
+  dim3 grid((n / 8 + 255) / 256, (rows + sb::BE_ROWS - 1) / sb::BE_ROWS);
+  const __nv_bfloat16* xb = static_cast<const __nv_bfloat16*>(x);
+  const __nv_bfloat16* cb = static_cast<const __nv_bfloat16*>(c);
+  const __nv_bfloat16* qb = static_cast<const __nv_bfloat16*>(q);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (r <= 8)
+    sb::residual_block_energy_kernel<8><<<grid, 256, 0, st>>>(xb, cb, qb, rows, n, r, ldx, bs, energy);
+  else if (r <= 16)
+    sb::residual_block_energy_kernel<16><<<grid, 256, 0, st>>>(xb, cb, qb, rows, n, r, ldx, bs, energy);
+  else
+    sb::residual_block_energy_kernel<32><<<grid, 256, 0, st>>>(xb, cb, qb, rows, n, r, ldx, bs, energy);
   return static_cast<int>(cudaGetLastError());
 }
 

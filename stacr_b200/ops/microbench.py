@@ -96,8 +96,12 @@ def case_stacr(args, pk) -> list:
         add("oja_update (+ X^T Y gemm)", lambda: oja_step_kernels(q, x, 0.01), 2 * x_bytes)
     if sel in ("", "dw"):
         idx, val, scale = stacr_ops.residual_topk(x, c, qb, [k], rows, 8, torch.int32)
-        add("weight_grad (bucket + dw_fused)", lambda: stacr_ops.weight_grad(dy, c, q, (idx, val, scale, 8, k), o, n, False, torch.float32),
+        add("weight_grad gather form (bucket + dw_fused)", lambda: stacr_ops.weight_grad(dy, c, q, (idx, val, scale, 8, k), o, n, False, torch.float32, dense=False),
             dy_bytes + dw_bytes + k * o * 2)
+        add("weight_grad dense form (rebuild + CTA-pair GEMM)", lambda: stacr_ops.weight_grad(dy, c, q, (idx, val, scale, 8, k), o, n, False, torch.float32, dense=True),
+            dy_bytes + dw_bytes + 2 * x_bytes)
+        out[-1]["TFLOPs"] = 2.0 * rows * n * o / out[-1]["ms"] / 1e9
+        add("rebuild_input (C Q^T + S in bf16)", lambda: stacr_ops.rebuild_input(c, q, (idx, val, scale, 8, k), rows, n), x_bytes)
         add("weight_grad low-rank only", lambda: stacr_ops.weight_grad(dy, c, q, None, o, n, False, torch.float32), dy_bytes + dw_bytes)
     return out
 

@@ -99,16 +99,65 @@ def cross_entropy(logits, target):
     return F.cross_entropy(logits.float(), target, ignore_index=-100)
 
 
+class _PaddedHeadCEFn(torch.autograd.Function):
+    """``cross_entropy(hidden @ weight^T, target)`` for a vocabulary that is not a multiple of 8 (GPT-2: 50257).
+
+    Library GEMMs fall back to unaligned legacy kernels when the logits' leading dimension is odd, and the loss kernel needs
+    16-byte rows.  Here the logits live in a buffer whose rows are padded to a multiple of 64 columns: the in-tree GEMM writes
+    the first ``V`` columns (its output takes a leading dimension), the padding holds a large negative value so that it gets
+    no probability, and both backward products read the same padded buffer through strided views.
+    """
+
+    @staticmethod
+    def forward(ctx, hidden, weight, target):
+        from . import nn_kernels
+        from .gemm import gemm
+
+        rows, v = hidden.shape[0], weight.shape[0]
+        vp = (v + 63) // 64 * 64
+        h = hidden if hidden.dtype == torch.bfloat16 else hidden.to(torch.bfloat16)
+        h = h.contiguous()
+        w = weight.detach().to(torch.bfloat16).contiguous()
+        logits = torch.empty(rows, vp, dtype=torch.bfloat16, device=hidden.device)
+        logits[:, v:].fill_(-30000.0)
+        gemm(h, w, out=logits[:, :v])
+        loss, tgt, lse, inv_valid = nn_kernels.cross_entropy_fwd(logits, target.contiguous())
+        ctx.save_for_backward(h, w, logits, tgt, lse, inv_valid)
+        ctx.v, ctx.hidden_dtype, ctx.weight_dtype = v, hidden.dtype, weight.dtype
+        return loss
+
+    @staticmethod
+    def backward(ctx, dloss):
+        from . import nn_kernels
+        from .gemm import gemm
+
+        h, w, logits, tgt, lse, inv_valid = ctx.saved_tensors
+        d = nn_kernels.cross_entropy_bwd(logits, tgt, lse, inv_valid, dloss)[:, :ctx.v]      # [rows, V] view, rows padded
+        dh = gemm(d, w, b_mn=True).to(ctx.hidden_dtype) if ctx.needs_input_grad[0] else None
+        dw = gemm(d, h, a_mn=True, b_mn=True, out_dtype=torch.float32).to(ctx.weight_dtype) if ctx.needs_input_grad[1] else None
+        return dh, dw, None
+
+
 def linear_cross_entropy(hidden, weight, target, chunk: int = 0):
     """``cross_entropy(hidden @ weight^T, target)`` evaluated in row chunks to bound the logits workspace."""
+    from . import _lib
+
+    padded = hidden.is_cuda and weight.shape[0] % 8 != 0 and hidden.shape[-1] % 8 == 0 and _lib.available() and \
+        (hidden.dtype == torch.bfloat16 or torch.is_autocast_enabled())
+    if padded:
+        def head(h, t):
+            return _PaddedHeadCEFn.apply(h, weight, t)
+    else:
+        def head(h, t):
+            return cross_entropy(F.linear(h, weight), t)
     if not chunk or hidden.shape[0] <= chunk:
-        return cross_entropy(F.linear(hidden, weight), target)
+        return head(hidden, target)
     valid = (target != -100).sum().clamp_min(1)
     total = hidden.new_zeros((), dtype=torch.float32)
     for lo in range(0, hidden.shape[0], chunk):
         t = target[lo:lo + chunk]
         n = (t != -100).sum()
-        total = total + cross_entropy(F.linear(hidden[lo:lo + chunk], weight), t).float() * n
+        total = total + head(hidden[lo:lo + chunk], t).float() * n
     return total / valid
 
 

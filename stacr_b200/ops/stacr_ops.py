@@ -2,6 +2,8 @@
 
 from __future__ import annotations
 
+import os
+
 import ctypes
 import math
 
@@ -165,6 +167,40 @@ def _plan_target() -> int:
     return _PLAN_TARGET
 
 
+_REBUILD: dict = {}
+
+
+def _dense_threshold() -> int:
+    """Smallest ``rows * in_features * out_features`` for which the weight gradient is formed as a dense tensor-core product
+    of ``dY`` with the transiently rebuilt input (``STACR_DW_DENSE_MIN``, default 2**33; 0 = always, -1 = never)."""
+    return int(os.environ.get("STACR_DW_DENSE_MIN", str(1 << 33)))
+
+
+def rebuild_input(coeff: torch.Tensor, basis_fp32: torch.Tensor, residual, rows: int, in_features: int) -> torch.Tensor:
+    """``bf16(C Q^T + S)`` in a per-shape scratch buffer that later calls overwrite (valid until the next call of this shape)."""
+    dev = coeff.device
+    key = (dev.index, rows, in_features)
+    buf = _REBUILD.get(key)
+    if buf is None:
+        if len(_REBUILD) > 8:
+            _REBUILD.clear()
+        buf = torch.empty(rows, in_features, dtype=torch.bfloat16, device=dev)
+        _REBUILD[key] = buf
+    idx = values = scale = None
+    bits, length = 0, 0
+    if residual is not None and residual[4] > 0:
+        idx, values, scale, bits, length = residual
+    is32 = idx is not None and idx.dtype == torch.int32
+    rc = _lib.load().sb_rebuild_input(
+        _lib.ptr(coeff), _lib.ptr(basis_fp32), c_int(coeff.shape[1]), c_int(rows), c_int(in_features), _lib.ptr(idx if is32 else None),
+        _lib.ptr(None if (is32 or idx is None) else idx), c_ll(length), _lib.ptr(values), c_int(int(bits)), _lib.ptr(scale), _lib.ptr(buf),
+        c_int(in_features), _lib.stream_ptr(),
+    )
+    _lib.check_rc(rc, "sb_rebuild_input")
+    _lib.count(2 if length else 1)
+    return buf
+
+
 def weight_grad(
     dy: torch.Tensor,
     coeff: torch.Tensor,
@@ -176,8 +212,14 @@ def weight_grad(
     out_dtype: torch.dtype,
     sink=None,
     out: torch.Tensor | None = None,
+    dense: bool | None = None,
 ):
-    """``dW = (dY^T C) Q^T + dY^T S`` without rebuilding the dense input.
+    """``dW = (dY^T C) Q^T + dY^T S`` from the saved factors.
+
+    Two forms.  The gather form never rebuilds the input: a skinny GEMM gives ``dY^T C``, the residual is bucketed by feature
+    and one kernel expands the rank-r term and gathers ``dY`` rows.  The dense form (``dense=True``; chosen automatically for
+    large layers that carry a residual, see ``_dense_threshold``) rebuilds ``bf16(C Q^T + S)`` in a scratch buffer for the
+    duration of the call and runs one tensor-core GEMM with ``dY``; what is saved between forward and backward is the same.
 
     ``residual`` is ``None`` or ``(idx, values, scale, bits, length)``.  With ``sink`` (see
     ``parallel.ddp.GradSink``) the gradient is not returned: the kernel adds it straight into the flat gradient
@@ -187,6 +229,22 @@ def weight_grad(
     dev = dy.device
     rows = dy.shape[0]
     r = coeff.shape[1]
+    has_residual = residual is not None and residual[4] > 0
+    if dense is None:
+        floor = _dense_threshold()
+        dense = has_residual and sink is None and floor >= 0 and rows * in_features * out_features >= floor
+    if dense and sink is None and dy.stride(1) == 1 and dy.stride(0) % 8 == 0 and in_features % 8 == 0 and out_features % 8 == 0 \
+            and basis_fp32.dtype == torch.float32 and basis_fp32.is_contiguous() and coeff.is_contiguous():
+        # large layer with a residual: one dense product on the tensor cores with the input rebuilt for this call only
+        xhat = rebuild_input(coeff, basis_fp32, residual, rows, in_features)
+        shape = (in_features, out_features) if transposed else (out_features, in_features)
+        if out is None:
+            out = torch.empty(shape, dtype=out_dtype, device=dev)
+        else:
+            assert out.shape == shape and out.dtype == out_dtype and out.is_contiguous()
+        if transposed:
+            return gemm(xhat, dy, a_mn=True, b_mn=True, out=out, out_dtype=out_dtype)
+        return gemm(dy, xhat, a_mn=True, b_mn=True, out=out, out_dtype=out_dtype)
     t = at_b(dy, transpose_pad(coeff))  # [O, rpad] fp32
     colptr = rows_s = vals_s = plan = None
     nnz = 0

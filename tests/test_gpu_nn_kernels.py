@@ -115,3 +115,30 @@ def test_fused_rotary_matches_framework_ops():
     ref.backward(g)
     out.view(b, s, h, 3 * hd).backward(g.bfloat16())
     torch.testing.assert_close(x.grad.float().view(b, s, h, 3 * hd), ref_in.grad.view(b, s, h, 3 * hd), rtol=3e-2, atol=3e-2)
+
+
+def test_padded_vocabulary_head_matches_fp32_reference():
+    """Head + loss on a logits buffer padded from an odd vocabulary (GPT-2's 50257 in miniature), forward and backward."""
+    from stacr_b200.ops import _lib, nn_ops
+
+    torch.manual_seed(3)
+    rows, d, v = 520, 256, 1003
+    h = (torch.randn(rows, d, device="cuda") * 0.5).requires_grad_(True)
+    w = (torch.randn(v, d, device="cuda") * 0.05).requires_grad_(True)
+    t = torch.randint(0, v, (rows,), device="cuda")
+    t[::7] = -100
+    with torch.autocast("cuda", dtype=torch.bfloat16):
+        loss = nn_ops.linear_cross_entropy(h, w, t)
+    loss.backward()
+    torch.cuda.synchronize()
+    _lib.check_status()
+    hr, wr = h.detach().clone().requires_grad_(True), w.detach().clone().requires_grad_(True)
+    ref = torch.nn.functional.cross_entropy(hr @ wr.t(), t, ignore_index=-100)
+    ref.backward()
+    assert abs(float(loss) - float(ref)) < 2e-2
+    assert float((h.grad - hr.grad).abs().max() / hr.grad.abs().max()) < 3e-2
+    assert float((w.grad - wr.grad).abs().max() / wr.grad.abs().max()) < 3e-2
+    # chunked evaluation gives the same mean
+    with torch.autocast("cuda", dtype=torch.bfloat16):
+        chunked = nn_ops.linear_cross_entropy(h.detach(), w.detach(), t, chunk=128)
+    assert abs(float(chunked) - float(ref)) < 2e-2

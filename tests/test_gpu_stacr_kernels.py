@@ -104,6 +104,41 @@ def test_weight_grad_matches_fp32_formula(transposed, bits):
     assert err < 1e-2, float(err)
 
 
+@pytest.mark.parametrize("transposed", [False, True])
+@pytest.mark.parametrize("bits", [0, 8, 4])
+def test_weight_grad_dense_route_matches_fp32_formula(transposed, bits):
+    """The tensor-core route: the input is rebuilt in bf16 for the call and multiplied with dY by the CTA-pair GEMM."""
+    from stacr_b200.ops import _lib, stacr_ops
+    from stacr_b200.quant import quantize_values
+
+    rows, n, o, r = 1024, 512, 768, 8
+    x, q, qb, c, e = _setup(rows, n, r, seed=9)
+    dy = torch.randn(rows, o, device="cuda").bfloat16()
+    k = 4001                                                  # odd: the last 4-bit code shares its byte with padding
+    idx = torch.randperm(rows * n, device="cuda")[:k].to(torch.int32)
+    packed = quantize_values(e.reshape(-1)[idx.long()], bits)
+    residual = (idx, packed.data, packed.scale, packed.bits, packed.length)
+    s = torch.zeros(rows * n, device="cuda")
+    s[idx.long()] = packed.dequantize(torch.float32)
+    xhat = stacr_ops.rebuild_input(c, qb.float(), residual, rows, n)
+    want_x = c.float() @ qb.float().t() + s.reshape(rows, n)
+    torch.testing.assert_close(xhat.float(), want_x, rtol=1e-2, atol=1e-2)
+    out = stacr_ops.weight_grad(dy, c, qb.float(), residual, o, n, transposed, torch.float32, dense=True)
+    sparse = stacr_ops.weight_grad(dy, c, qb.float(), residual, o, n, transposed, torch.float32, dense=False)
+    torch.cuda.synchronize()
+    _lib.check_status()
+    ref = dy.float().t() @ want_x
+    if transposed:
+        ref = ref.t()
+    assert out.shape == ref.shape
+    assert float((out - ref).abs().max() / ref.abs().max()) < 1e-2
+    assert float((out - sparse).abs().max() / ref.abs().max()) < 1e-2
+    # low-rank only (no residual entries) through the same route
+    lr = stacr_ops.weight_grad(dy, c, qb.float(), None, o, n, transposed, torch.float32, dense=True)
+    ref_lr = (dy.float().t() @ c.float()) @ qb.float().t()
+    assert float((lr - (ref_lr.t() if transposed else ref_lr)).abs().max() / ref_lr.abs().max()) < 1e-2
+
+
 @pytest.mark.parametrize("mode", ["chunk_topk", "global_topk", "block_sparse", "uniform", "none"])
 def test_layer_forward_backward_on_kernel_path(mode):
     import stacr_b200 as S
