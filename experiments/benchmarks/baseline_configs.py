@@ -62,7 +62,7 @@ def run_gpt2m_turbo_dp(args, rank, world, dev):
     model = build_model("gpt2-medium").to(dev).train()
     broadcast_parameters(model)
     layers = S.apply_stacr(model, rank=8, residual_budget=0.005, turbo_after_step=50, surface="mlp")
-    opt = AdamW(model.parameters(), lr=5e-5, weight_decay=0.0)
+    opt = AdamW(model.parameters(), lr=5e-5, weight_decay=0.0, bf16_shadow=True)
     sync = GradSync(model.parameters()) if world > 1 else None
     data = _tokens(model.config.vocab_size, batch, seq, 8, 100 + rank, dev)
     state = {"step": 0}
@@ -105,7 +105,7 @@ def run_gpt2l_tp(args, rank, world, dev):
     names = get_tp_stacr_targets(model, "all_linear")
     layers = S.apply_stacr(model, surface="none", target_names=names, rank=8, residual_budget=0.005, residual_mode="block_sparse",
                            turbo_after_step=None, allow_empty=False)
-    opt = AdamW(model.parameters(), lr=5e-5, weight_decay=0.0)
+    opt = AdamW(model.parameters(), lr=5e-5, weight_decay=0.0, bf16_shadow=True)
     data = _tokens(model.config.vocab_size, batch, seq, 8, 100, dev)   # the same batch on every rank: this is model parallelism
     state = {"step": 0}
 
@@ -144,7 +144,7 @@ def run_bert_adaptive_composed(args, rank, world, dev):
     model = build_model(cfg["model_name"], "sequence_classification").to(dev).train()
     broadcast_parameters(model)
     layers, info = configure_model(model, cfg)
-    opt = AdamW(model.parameters(), lr=float(cfg["lr"]), weight_decay=0.0)
+    opt = AdamW(model.parameters(), lr=float(cfg["lr"]), weight_decay=0.0, bf16_shadow=True)
     sync = GradSync(model.parameters()) if world > 1 else None
     gen = torch.Generator().manual_seed(100 + rank)
     data = [(torch.randint(0, model.config.vocab_size, (batch, seq), generator=gen).to(dev), torch.bernoulli(torch.full((batch,), 0.5), generator=gen).long().to(dev))

@@ -13,14 +13,15 @@
 
 namespace sb {
 
-constexpr int RB_COLS = 8;      // columns per thread: one 16-byte store
-constexpr int RB_ROWS = 32;     // rows per CTA
+constexpr int RB_COLS = 8;       // columns per thread: one 16-byte store
+constexpr int RB_ROWS = 64;      // rows per CTA: the thread's 8 basis rows are loaded once and reused for all of them
+constexpr int RB_THREADS = 128;  // 1024 columns per CTA
 constexpr int RB_RMAX = 32;
 
 template <int RP>
-__global__ void __launch_bounds__(256) rebuild_lowrank_kernel(const __nv_bfloat16* __restrict__ c, const float* __restrict__ q, int r, int rows,
+__global__ void __launch_bounds__(RB_THREADS) rebuild_lowrank_kernel(const __nv_bfloat16* __restrict__ c, const float* __restrict__ q, int r, int rows,
                                                               int n, __nv_bfloat16* __restrict__ out, int ldo) {
-  __shared__ float s_c[RB_ROWS * RP];
+  __shared__ __align__(16) float s_c[RB_ROWS * RP];
   const int row0 = blockIdx.y * RB_ROWS;
   const int nrows = min(RB_ROWS, rows - row0);
   for (int i = threadIdx.x; i < RB_ROWS * RP; i += blockDim.x) {
@@ -31,20 +32,35 @@ __global__ void __launch_bounds__(256) rebuild_lowrank_kernel(const __nv_bfloat1
   const int col0 = (blockIdx.x * blockDim.x + threadIdx.x) * RB_COLS;
   if (col0 >= n) return;
   float qreg[RB_COLS][RP];
+  if (r == RP && col0 + RB_COLS <= n && ((reinterpret_cast<uintptr_t>(q) & 15) == 0)) {
+    // a basis row is RP floats = RP / 4 16-byte vectors; the thread's 8 rows are one contiguous block
+    const float4* src = reinterpret_cast<const float4*>(q + static_cast<size_t>(col0) * RP);
 #pragma unroll
-  for (int i = 0; i < RB_COLS; ++i)
+    for (int i = 0; i < RB_COLS; ++i)
 #pragma unroll
-    for (int j = 0; j < RP; ++j) qreg[i][j] = (col0 + i < n && j < r) ? __ldg(q + static_cast<size_t>(col0 + i) * r + j) : 0.f;
+      for (int v = 0; v < RP / 4; ++v) {
+        const float4 t = __ldg(src + i * (RP / 4) + v);
+        qreg[i][4 * v] = t.x; qreg[i][4 * v + 1] = t.y; qreg[i][4 * v + 2] = t.z; qreg[i][4 * v + 3] = t.w;
+      }
+  } else {
+#pragma unroll
+    for (int i = 0; i < RB_COLS; ++i)
+#pragma unroll
+      for (int j = 0; j < RP; ++j) qreg[i][j] = (col0 + i < n && j < r) ? __ldg(q + static_cast<size_t>(col0 + i) * r + j) : 0.f;
+  }
   const bool vec = (col0 + RB_COLS <= n) && ((ldo & 7) == 0) && ((reinterpret_cast<uintptr_t>(out) & 15) == 0);
   for (int lr = 0; lr < nrows; ++lr) {
     float acc[RB_COLS];
 #pragma unroll
     for (int i = 0; i < RB_COLS; ++i) acc[i] = 0.f;
 #pragma unroll
-    for (int j = 0; j < RP; ++j) {
-      const float cj = s_c[lr * RP + j];  // same address for the whole warp: a broadcast
+    for (int v = 0; v < RP / 4; ++v) {
+      const float4 cv = *reinterpret_cast<const float4*>(s_c + lr * RP + 4 * v);  // same address for the whole warp: a broadcast
+      const float cj[4] = {cv.x, cv.y, cv.z, cv.w};
 #pragma unroll
-      for (int i = 0; i < RB_COLS; ++i) acc[i] = fmaf(cj, qreg[i][j], acc[i]);
+      for (int k = 0; k < 4; ++k)
+#pragma unroll
+        for (int i = 0; i < RB_COLS; ++i) acc[i] = fmaf(cj[k], qreg[i][4 * v + k], acc[i]);
     }
     __nv_bfloat16* o = out + static_cast<size_t>(row0 + lr) * ldo + col0;
     if (vec) {
@@ -93,15 +109,15 @@ extern "C" int sb_rebuild_input(const void* c, const float* q, int r, int rows, 
   if (nnz > 0 && ((idx32 == nullptr) == (idx64 == nullptr))) return -2;
   if (nnz > 0 && bits != 0 && bits != 4 && bits != 8) return -2;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  const dim3 grid((n + 256 * RB_COLS - 1) / (256 * RB_COLS), (rows + RB_ROWS - 1) / RB_ROWS);
+  const dim3 grid((n + RB_THREADS * RB_COLS - 1) / (RB_THREADS * RB_COLS), (rows + RB_ROWS - 1) / RB_ROWS);
   const __nv_bfloat16* cb = static_cast<const __nv_bfloat16*>(c);
   __nv_bfloat16* ob = static_cast<__nv_bfloat16*>(out);
   if (r <= 8)
-    rebuild_lowrank_kernel<8><<<grid, 256, 0, st>>>(cb, q, r, rows, n, ob, ldo);
+    rebuild_lowrank_kernel<8><<<grid, RB_THREADS, 0, st>>>(cb, q, r, rows, n, ob, ldo);
   else if (r <= 16)
-    rebuild_lowrank_kernel<16><<<grid, 256, 0, st>>>(cb, q, r, rows, n, ob, ldo);
+    rebuild_lowrank_kernel<16><<<grid, RB_THREADS, 0, st>>>(cb, q, r, rows, n, ob, ldo);
   else
-    rebuild_lowrank_kernel<32><<<grid, 256, 0, st>>>(cb, q, r, rows, n, ob, ldo);
+    rebuild_lowrank_kernel<32><<<grid, RB_THREADS, 0, st>>>(cb, q, r, rows, n, ob, ldo);
   if (nnz > 0) {
     const int threads = 256;
     const long long blocks = (nnz + threads - 1) / threads;
