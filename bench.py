@@ -163,6 +163,46 @@ def kernel_table(torch, step, path, steps=2):
             fh.write(f"{ms:9.3f} ms {100 * ms / total:5.1f}% {n:6d}x  {name[:110]}\n")
 
 
+def gap_report(torch, step, path, steps=2):
+    """Where the GPU idles inside a step: kernel intervals of `steps` profiled steps are merged and every gap longer than
+    20 us is listed with the host operation that was running when the gap ended.  Written as text; not part of any timed region."""
+    from torch.profiler import ProfilerActivity, profile
+
+    with profile(activities=[ProfilerActivity.CPU, ProfilerActivity.CUDA]) as prof:
+        for i in range(steps):
+            step(i)
+        torch.cuda.synchronize()
+    events = prof.events()
+    kernels = sorted(((e.time_range.start, e.time_range.end, e.name) for e in events if e.device_type == torch.autograd.DeviceType.CUDA),
+                     key=lambda t: t[0])
+    host = sorted(((e.time_range.start, e.time_range.end, e.name) for e in events if e.device_type == torch.autograd.DeviceType.CPU),
+                  key=lambda t: t[0])
+    if not kernels:
+        return
+    gaps, busy_end = [], kernels[0][1]
+    for start, end, name in kernels[1:]:
+        if start - busy_end > 20:
+            running = [h for h in host if h[0] <= start <= h[1]]
+            top = max(running, key=lambda h: h[1] - h[0])[2] if running else "-"
+            leaf = min(running, key=lambda h: h[1] - h[0])[2] if running else "-"
+            gaps.append((start - busy_end, name[:60], top[:50], leaf[:50]))
+        busy_end = max(busy_end, end)
+    span = kernels[-1][1] - kernels[0][0]
+    idle = sum(g[0] for g in gaps)
+    by = {}
+    for g in gaps:
+        key = (g[2], g[3])
+        by[key] = (by.get(key, (0, 0))[0] + g[0], by.get(key, (0, 0))[1] + 1)
+    with open(path, "w") as fh:
+        fh.write(f"span {span / 1e3 / steps:.2f} ms per step, idle in gaps > 20 us: {idle / 1e3 / steps:.2f} ms per step over {len(gaps) // steps} gaps\n")
+        fh.write("idle ms/step  gaps/step  outermost host op  |  innermost host op when the next kernel started\n")
+        for (top, leaf), (us, n) in sorted(by.items(), key=lambda kv: -kv[1][0])[:40]:
+            fh.write(f"{us / 1e3 / steps:10.3f} {n // steps:8d}  {top}  |  {leaf}\n")
+        fh.write("largest single gaps (us, next kernel, host op):\n")
+        for g in sorted(gaps, reverse=True)[:25]:
+            fh.write(f"{g[0]:10.0f}  {g[1]}  |  {g[3]}\n")
+
+
 def run_ours(args):
     sys.path.insert(0, REPO)
     import torch
@@ -235,6 +275,8 @@ def run_ours(args):
     peak = torch.cuda.max_memory_allocated(dev)
     if args.kernel_table:  # every rank runs the extra steps (their collectives need all ranks); rank 0 writes the table
         kernel_table(torch, step_device, args.kernel_table if rank == 0 else os.devnull)
+    if args.gap_report:
+        gap_report(torch, step_device, args.gap_report if rank == 0 else os.devnull)
     rows = batch * seq
     factor_bytes = sum(layer.stored_bytes(rows, 2)["total"] for layer in layers)
     dense_bytes = sum(rows * layer.in_features * 2 for layer in layers)
@@ -371,6 +413,7 @@ def main():
     ap.add_argument("--comm", default="auto", choices=["auto", "symm", "nccl"], help="gradient all-reduce path (this framework)")
     ap.add_argument("--fused-dw", default="off", choices=["on", "off"],
                     help="N > 1: compressed layers' weight-gradient kernels reduce-scatter in their epilogue over NVLink peer memory")
+    ap.add_argument("--gap-report", metavar="FILE", help="after the timed regions, write where the GPU idles inside two more steps to FILE")
     ap.add_argument("--kernel-table", metavar="FILE", help="after the timed regions, write per-kernel device times of two more steps to FILE")
     ap.add_argument("--small", action="store_true", help="tiny shape for smoke runs (not a benchmark number)")
     args = ap.parse_args()

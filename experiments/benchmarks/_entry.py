@@ -31,6 +31,45 @@ def run(name: str, seeds: Iterable[int] = (42,), output=None) -> List[dict]:
     return grids.run_experiment(name, seeds, output)
 
 
+def arms(name: str) -> List[str]:
+    """The distinct method names of the grid, in run order."""
+    seen: List[str] = []
+    for cell in cells(name):
+        m = str(cell.get("method", cell.get("comparator", "")))
+        if m not in seen:
+            seen.append(m)
+    return seen
+
+
+def one(name: str, method: str, seed: int = 42, **overrides) -> dict:
+    """Run the first cell of the grid whose method is ``method`` (keyword overrides replace cell fields) and return its row."""
+    from . import grids
+
+    for cell in cells(name):
+        if str(cell.get("method")) == method:
+            return grids._run_cell({**cell, **overrides}, seed)
+    raise KeyError(f"grid {name!r} has no method {method!r}; choose from {arms(name)}")
+
+
+def run_cohort(name: str, selector: str, seeds: Iterable[int] = (42,), output=None) -> List[dict]:
+    """Run the cells whose method name contains ``selector`` (the ``--cohort`` flag of the command line)."""
+    from . import common, grids
+    from .registry import EXPERIMENTS
+
+    rows = []
+    for cell in EXPERIMENTS[name]["cells"]:
+        if selector in str(cell.get("method", cell.get("comparator", ""))):
+            for seed in seeds:
+                row = grids._run_cell(dict(cell), seed)
+                row["experiment"] = name
+                rows.append(row)
+                if output is not None and common._RECORDER is None:
+                    common.emit(row, output)
+    if not rows:
+        raise KeyError(f"selector {selector!r} matches no cell of {name!r}")
+    return rows
+
+
 def main(name: str, argv: Optional[List[str]] = None) -> int:
     from .__main__ import main as cli
 

@@ -18,8 +18,20 @@ def cells():
     return _entry.cells(NAME)
 
 
+def rows():
+    return _entry.cells(NAME)
+
+
+def arms():
+    return _entry.arms(NAME)
+
+
 def run(seeds=(42,), output=None):
     return _entry.run(NAME, seeds, output)
+
+
+def run_cohort(selector, seeds=(42,), output=None):
+    return _entry.run_cohort(NAME, selector, seeds, output)
 
 
 def trace(method, cfg, model_id="qwen2.5-1.5b", bs=2, seq=1024, steps=600, **run_kw):
@@ -31,6 +43,10 @@ def trace(method, cfg, model_id="qwen2.5-1.5b", bs=2, seq=1024, steps=600, **run
 
     return common.run_config(method, 42, model_id=model_id, bs=bs, seq=seq, steps=steps, measure_from=0, eval_batches=0,
                              stacr_cfg=dict(cfg, turbo_after_step=None) if cfg else None, trace_memory=True, **run_kw)
+
+
+def one(method, seed=42, **overrides):
+    return _entry.one(NAME, method, seed, **overrides)
 
 
 def main(argv=None) -> int:

@@ -18,11 +18,27 @@ def cells():
     return _entry.cells(NAME)
 
 
+def rows():
+    return _entry.cells(NAME)
+
+
+def arms():
+    return _entry.arms(NAME)
+
+
 def run(seeds=(42,), output=None):
     return _entry.run(NAME, seeds, output)
 
 
+def run_cohort(selector, seeds=(42,), output=None):
+    return _entry.run_cohort(NAME, selector, seeds, output)
+
+
 from .probes import gpu_gib  # noqa: E402,F401
+
+
+def one(method, seed=42, **overrides):
+    return _entry.one(NAME, method, seed, **overrides)
 
 
 def main(argv=None) -> int:

@@ -18,13 +18,29 @@ def cells():
     return _entry.cells(NAME)
 
 
+def rows():
+    return _entry.cells(NAME)
+
+
+def arms():
+    return _entry.arms(NAME)
+
+
 def run(seeds=(42,), output=None):
     return _entry.run(NAME, seeds, output)
+
+
+def run_cohort(selector, seeds=(42,), output=None):
+    return _entry.run_cohort(NAME, selector, seeds, output)
 
 
 def enumerate_cells():
     """The grid's cells in run order (same as :func:`cells`)."""
     return cells()
+
+
+def one(method, seed=42, **overrides):
+    return _entry.one(NAME, method, seed, **overrides)
 
 
 def main(argv=None) -> int:

@@ -18,8 +18,20 @@ def cells():
     return _entry.cells(NAME)
 
 
+def rows():
+    return _entry.cells(NAME)
+
+
+def arms():
+    return _entry.arms(NAME)
+
+
 def run(seeds=(42,), output=None):
     return _entry.run(NAME, seeds, output)
+
+
+def run_cohort(selector, seeds=(42,), output=None):
+    return _entry.run_cohort(NAME, selector, seeds, output)
 
 
 from .probes import maxbatch, maxlen, one, sweep  # noqa: E402,F401  (search helpers bound to this grid's arms by the caller)

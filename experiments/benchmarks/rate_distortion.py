@@ -18,8 +18,20 @@ def cells():
     return _entry.cells(NAME)
 
 
+def rows():
+    return _entry.cells(NAME)
+
+
+def arms():
+    return _entry.arms(NAME)
+
+
 def run(seeds=(42,), output=None):
     return _entry.run(NAME, seeds, output)
+
+
+def run_cohort(selector, seeds=(42,), output=None):
+    return _entry.run_cohort(NAME, selector, seeds, output)
 
 
 def payload_bytes(kind, rank, budget, model_id="gpt2-medium", bs=4, seq=512, min_features=256, **overrides):
@@ -37,6 +49,10 @@ def payload_bytes(kind, rank, budget, model_id="gpt2-medium", bs=4, seq=512, min
     stored = sum(sum(v for k, v in layer.stored_bytes(rows, 2).items() if k in ("coeff", "residual", "basis")) for layer in layers)
     dense = sum(rows * layer.in_features * 2 for layer in layers)
     return stored, dense, len(layers)
+
+
+def one(method, seed=42, **overrides):
+    return _entry.one(NAME, method, seed, **overrides)
 
 
 def main(argv=None) -> int:

@@ -18,8 +18,20 @@ def cells():
     return _entry.cells(NAME)
 
 
+def rows():
+    return _entry.cells(NAME)
+
+
+def arms():
+    return _entry.arms(NAME)
+
+
 def run(seeds=(42,), output=None):
     return _entry.run(NAME, seeds, output)
+
+
+def run_cohort(selector, seeds=(42,), output=None):
+    return _entry.run_cohort(NAME, selector, seeds, output)
 
 
 def down_proj_names(model):
@@ -38,6 +50,10 @@ def cfg_for(model_id, surf_name, surf_cfg, rank):
         cfg["surface"], cfg["extra_names"] = "none", down_proj_names(probe)
         del probe
     return cfg
+
+
+def one(method, seed=42, **overrides):
+    return _entry.one(NAME, method, seed, **overrides)
 
 
 def main(argv=None) -> int:

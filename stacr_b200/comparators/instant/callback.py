@@ -78,3 +78,64 @@ class Calibrator:
             self.model.train(was_training)
         update_compression(self.model, self.P, self.Q)
         return {n: (int(self.P[n].shape[1]), int(self.Q[n].shape[1])) for n in self.P}
+
+
+# ------------------------------------------------------------------------------ module-level form
+# Scripts written against the upstream layout register hooks once per calibration window through module functions and
+# read the accumulated Gram matrices from module dictionaries; these wrap one shared Calibrator.
+_ACTIVE: dict = {"calibrator": None}
+layer_inputs: dict = {}
+layer_gradients: dict = {}
+P_dict: dict = {}
+Q_dict: dict = {}
+
+
+def register_hooks(model: nn.Module, model_name=None, var: float = 0.95, over_sampling: int = 7) -> Calibrator:
+    from .model import get_svd_layers
+
+    unregister_hooks()
+    calib = Calibrator(model, get_svd_layers(model, model_name), var=var, over_sampling=over_sampling)
+    calib.gram_x, calib.gram_g, calib.P, calib.Q = layer_inputs, layer_gradients, P_dict, Q_dict
+    calib.register_hooks()
+    _ACTIVE["calibrator"] = calib
+    return calib
+
+
+def unregister_hooks() -> None:
+    calib = _ACTIVE.get("calibrator")
+    if calib is not None:
+        calib.unregister_hooks()
+    _ACTIVE["calibrator"] = None
+    for store in (layer_inputs, layer_gradients, P_dict, Q_dict):
+        store.clear()
+
+
+def save_input_hook(name, module, input, output) -> None:
+    """Accumulate the batch-averaged token Gram matrix of a layer input (the forward-hook body)."""
+    Calibrator._accumulate(_ACTIVE.get("calibrator") or Calibrator(module, []), layer_inputs, name, input[0])
+
+
+def save_grad_hook(name, module, grad_input, grad_output) -> None:
+    """Accumulate the batch-averaged token Gram matrix of a layer's output gradient (the backward-hook body)."""
+    Calibrator._accumulate(_ACTIVE.get("calibrator") or Calibrator(module, []), layer_gradients, name, grad_output[0])
+
+
+class CustomLoggingCallback:
+    """Recalibration on a step schedule for loops that call ``on_step_begin(step, model, batches, loss_of_batch)``.
+
+    The upstream class is a ``transformers.TrainerCallback``; this one has no framework dependency and the in-tree
+    training scripts (``_loop.run``) inline the same schedule.
+    """
+
+    def __init__(self, args):
+        self.args, self.calibrator = args, None
+
+    def on_step_begin(self, step: int, model: nn.Module, batches, loss_of_batch, model_name=None):
+        if not getattr(self.args, "compress", False) or step % max(int(getattr(self.args, "calib_iter", 50)), 1):
+            return None
+        if self.calibrator is None:
+            from .model import get_svd_layers
+
+            self.calibrator = Calibrator(model, get_svd_layers(model, model_name), var=getattr(self.args, "var", 0.95),
+                                         over_sampling=getattr(self.args, "over_sampling", 7))
+        return self.calibrator.run(batches, loss_of_batch)

@@ -108,3 +108,14 @@ def disable_compression(model: nn.Module) -> nn.Module:
 def print_status(model: nn.Module) -> None:
     for name, param in model.named_parameters():
         print(f"{'trainable' if param.requires_grad else 'frozen':9s} {name}")
+
+
+def add_activate_to_module() -> None:
+    """Kept for scripts that call it: the on/off switch is a class attribute of ``InstantLinear`` here, toggled per model by
+    :func:`enable_compression` / :func:`disable_compression`, so ``nn.Module`` is not patched."""
+    return None
+
+
+def add_compression_tensor_to_module() -> None:
+    """Kept for scripts that call it: the two subspaces are attributes of ``InstantLinear``, installed by :func:`update_compression`."""
+    return None

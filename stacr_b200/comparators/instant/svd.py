@@ -28,3 +28,4 @@ def energy_basis(gram: torch.Tensor, var: float = 0.95, oversample: int = 7) -> 
 def SVD_expected_value(input: torch.Tensor, var: float = 0.95, p: int = 7) -> torch.Tensor:
     """Name used by the INSTANT scripts for :func:`energy_basis`."""
     return energy_basis(input, var=var, oversample=p)
+from .utils import log_svd_shapes  # noqa: E402,F401  (also importable from here, as in the upstream layout)

@@ -63,18 +63,19 @@ __device__ __forceinline__ float decode_m(unsigned char c, float amax) {
   const float s = (static_cast<float>(c) - 128.f) * (1.f / 127.f);
   return copysignf(s * s, s) * amax;
 }
-__device__ __forceinline__ unsigned char encode_m(float m, float amax) {
-  if (amax <= 0.f) return 128;
-  const float s = sqrtf(fminf(fabsf(m) / amax, 1.f));
+// The encoders take 1 / absmax (0 when the block is all zero), computed once per quantisation block.
+__device__ __forceinline__ unsigned char encode_m(float m, float inv_amax) {
+  if (inv_amax <= 0.f) return 128;
+  const float s = sqrtf(fminf(fabsf(m) * inv_amax, 1.f));
   return static_cast<unsigned char>(128.f + rintf(copysignf(s, m) * 127.f));
 }
 __device__ __forceinline__ float decode_v(unsigned char c, float amax) {
   const float s = static_cast<float>(c) * (1.f / 255.f);
   return s * s * s * s * amax;
 }
-__device__ __forceinline__ unsigned char encode_v(float v, float amax) {
-  if (amax <= 0.f) return 0;
-  return static_cast<unsigned char>(rintf(sqrtf(sqrtf(fminf(v / amax, 1.f))) * 255.f));
+__device__ __forceinline__ unsigned char encode_v(float v, float inv_amax) {
+  if (inv_amax <= 0.f) return 0;
+  return static_cast<unsigned char>(rintf(sqrtf(sqrtf(fminf(v * inv_amax, 1.f))) * 255.f));
 }
 
 // One warp = one 256-element quantisation block (8 consecutive elements per lane, 16-byte
@@ -131,13 +132,14 @@ __global__ void __launch_bounds__(256) adamw_8bit_kernel(const TensorDesc* __res
     }
   }
   float am = 0.f, av = 0.f;
+  const float inv_b1 = 1.f / a.bias1, inv_b2 = 1.f / a.bias2, decay = 1.f - a.lr * a.weight_decay;
+  const float step1 = a.lr * inv_b1;  // one reciprocal per element instead of three divisions
 #pragma unroll
   for (int j = 0; j < 8; ++j) {
     const float gj = g[j] * a.grad_scale;
     m[j] = a.beta1 * m[j] + (1.f - a.beta1) * gj;
     v[j] = a.beta2 * v[j] + (1.f - a.beta2) * gj * gj;
-    p[j] -= a.lr * a.weight_decay * p[j];
-    p[j] -= a.lr * (m[j] / a.bias1) / (sqrtf(v[j] / a.bias2) + a.eps);
+    p[j] = p[j] * decay - step1 * m[j] * __frcp_rn(sqrtf(v[j] * inv_b2) + a.eps);
     if (i0 + j < t.numel) {
       am = fmaxf(am, fabsf(m[j]));
       av = fmaxf(av, v[j]);
@@ -149,10 +151,11 @@ __global__ void __launch_bounds__(256) adamw_8bit_kernel(const TensorDesc* __res
       am = fmaxf(am, __shfl_xor_sync(0xffffffffu, am, off));
       av = fmaxf(av, __shfl_xor_sync(0xffffffffu, av, off));
     }
+    const float inv_am = am > 0.f ? 1.f / am : 0.f, inv_av = av > 0.f ? 1.f / av : 0.f;
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
-      cm[j] = encode_m(m[j], am);
-      cv[j] = encode_v(v[j], av);
+      cm[j] = encode_m(m[j], inv_am);
+      cv[j] = encode_v(v[j], inv_av);
     }
     if (lane == 0) {
       t.m_absmax[qb] = am;
