@@ -350,6 +350,10 @@ class STACRFunction(torch.autograd.Function):
                         ga, coeff, q.float(), residual, ctx.out_features, ctx.in_features, ctx.transposed, weight.dtype
                         if weight.dtype in (torch.float32, torch.bfloat16) else torch.float32, out=slot,
                     ).to(weight.dtype)
+                    ready = getattr(weight, "_sb_grad_ready", None) if slot is not None else None
+                    if ready is not None and not getattr(weight, "_sb_tied", False):
+                        ready()          # the slot is the gradient: nothing goes back through autograd (it would be cloned)
+                        gw = None
             if ctx.needs_input_grad[2]:
                 gb = stacr_ops.colsum(ga).to(ctx.bias_dtype)
             return (gx, gw, gb) + (None,) * (ctx.n_args - 3)

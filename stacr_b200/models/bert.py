@@ -8,7 +8,7 @@ import torch
 from torch import nn
 from torch.nn import functional as F
 
-from .common import GELU, LayerNorm, ModelOutput, causal_attention, init_weights
+from .common import causal_attention, GELU, init_weights, LayerNorm, Linear, ModelOutput
 
 
 @dataclass
@@ -56,9 +56,9 @@ class BertSelfAttention(nn.Module):
     def __init__(self, cfg):
         super().__init__()
         self.n_head, self.head_dim = cfg.num_attention_heads, cfg.hidden_size // cfg.num_attention_heads
-        self.query = nn.Linear(cfg.hidden_size, cfg.hidden_size)
-        self.key = nn.Linear(cfg.hidden_size, cfg.hidden_size)
-        self.value = nn.Linear(cfg.hidden_size, cfg.hidden_size)
+        self.query = Linear(cfg.hidden_size, cfg.hidden_size)
+        self.key = Linear(cfg.hidden_size, cfg.hidden_size)
+        self.value = Linear(cfg.hidden_size, cfg.hidden_size)
         self.p = cfg.attention_probs_dropout_prob
 
     def forward(self, x, attention_mask=None):
@@ -72,7 +72,7 @@ class BertSelfAttention(nn.Module):
 class BertSelfOutput(nn.Module):
     def __init__(self, cfg):
         super().__init__()
-        self.dense = nn.Linear(cfg.hidden_size, cfg.hidden_size)
+        self.dense = Linear(cfg.hidden_size, cfg.hidden_size)
         self.LayerNorm = LayerNorm(cfg.hidden_size, eps=cfg.layer_norm_eps)
         self.dropout = nn.Dropout(cfg.hidden_dropout_prob)
 
@@ -93,7 +93,7 @@ class BertAttention(nn.Module):
 class BertIntermediate(nn.Module):
     def __init__(self, cfg):
         super().__init__()
-        self.dense = nn.Linear(cfg.hidden_size, cfg.intermediate_size)
+        self.dense = Linear(cfg.hidden_size, cfg.intermediate_size)
         self.intermediate_act_fn = GELU("none")
 
     def forward(self, x):
@@ -103,7 +103,7 @@ class BertIntermediate(nn.Module):
 class BertOutput(nn.Module):
     def __init__(self, cfg):
         super().__init__()
-        self.dense = nn.Linear(cfg.intermediate_size, cfg.hidden_size)
+        self.dense = Linear(cfg.intermediate_size, cfg.hidden_size)
         self.LayerNorm = LayerNorm(cfg.hidden_size, eps=cfg.layer_norm_eps)
         self.dropout = nn.Dropout(cfg.hidden_dropout_prob)
 
@@ -137,7 +137,7 @@ class BertEncoder(nn.Module):
 class BertPooler(nn.Module):
     def __init__(self, cfg):
         super().__init__()
-        self.dense = nn.Linear(cfg.hidden_size, cfg.hidden_size)
+        self.dense = Linear(cfg.hidden_size, cfg.hidden_size)
 
     def forward(self, x):
         return torch.tanh(self.dense(x[:, 0]))
@@ -161,7 +161,7 @@ class BertForSequenceClassification(nn.Module):
         self.config = cfg
         self.bert = BertModel(cfg)
         self.dropout = nn.Dropout(cfg.hidden_dropout_prob)
-        self.classifier = nn.Linear(cfg.hidden_size, cfg.num_labels)
+        self.classifier = Linear(cfg.hidden_size, cfg.num_labels)
         self.apply(init_weights)
 
     def forward(self, input_ids, attention_mask=None, token_type_ids=None, labels=None, **_):

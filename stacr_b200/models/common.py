@@ -36,6 +36,14 @@ class LayerNorm(nn.LayerNorm):
         return nn_ops.layer_norm(x, self.weight, self.bias, self.eps)
 
 
+class Linear(nn.Linear):
+    """``nn.Linear`` (same parameters, same state-dict keys) whose training path on a B200 forms the weight gradient in
+    fp32 directly (see ``ops.nn_ops.linear``); everywhere else it is the stock layer."""
+
+    def forward(self, x):
+        return nn_ops.linear(x, self.weight, self.bias)
+
+
 class GELU(nn.Module):
     def __init__(self, approximate: str = "none"):
         super().__init__()

@@ -7,7 +7,7 @@ from dataclasses import dataclass
 import torch
 from torch import nn
 
-from .common import GELU, LayerNorm, ModelOutput, causal_attention, init_weights, lm_loss
+from .common import causal_attention, GELU, init_weights, LayerNorm, Linear, lm_loss, ModelOutput
 
 
 @dataclass
@@ -44,8 +44,8 @@ class GPT2Attention(nn.Module):
     def __init__(self, cfg: GPT2Config):
         super().__init__()
         self.n_head, self.head_dim = cfg.n_head, cfg.n_embd // cfg.n_head
-        self.c_attn = nn.Linear(cfg.n_embd, 3 * cfg.n_embd)
-        self.c_proj = nn.Linear(cfg.n_embd, cfg.n_embd)
+        self.c_attn = Linear(cfg.n_embd, 3 * cfg.n_embd)
+        self.c_proj = Linear(cfg.n_embd, cfg.n_embd)
         self.attn_pdrop = cfg.attn_pdrop
         self.resid_dropout = nn.Dropout(cfg.resid_pdrop)
 
@@ -60,9 +60,9 @@ class GPT2Attention(nn.Module):
 class GPT2MLP(nn.Module):
     def __init__(self, cfg: GPT2Config):
         super().__init__()
-        self.c_fc = nn.Linear(cfg.n_embd, cfg.inner)
+        self.c_fc = Linear(cfg.n_embd, cfg.inner)
         self.act = GELU("tanh")
-        self.c_proj = nn.Linear(cfg.inner, cfg.n_embd)
+        self.c_proj = Linear(cfg.inner, cfg.n_embd)
         self.dropout = nn.Dropout(cfg.resid_pdrop)
 
     def forward(self, x):
@@ -106,13 +106,14 @@ class GPT2LMHeadModel(nn.Module):
         super().__init__()
         self.config = cfg
         self.transformer = GPT2Model(cfg)
-        self.lm_head = nn.Linear(cfg.n_embd, cfg.vocab_size, bias=False)
+        self.lm_head = Linear(cfg.n_embd, cfg.vocab_size, bias=False)
         self.apply(init_weights)
         for name, p in self.named_parameters():
             if name.endswith("c_proj.weight"):
                 nn.init.normal_(p, mean=0.0, std=0.02 / (2 * cfg.n_layer) ** 0.5)
         if cfg.tie_word_embeddings:
             self.lm_head.weight = self.transformer.wte.weight
+            self.lm_head.weight._sb_tied = True     # two gradients per backward: layers must hand theirs to autograd
 
     def forward(self, input_ids, attention_mask=None, labels=None, **_):
         hidden = self.transformer(input_ids, attention_mask)

@@ -8,7 +8,7 @@ import torch
 from torch import nn
 from torch.nn import functional as F
 
-from .common import ModelOutput, causal_attention, init_weights, lm_loss
+from .common import causal_attention, init_weights, Linear, lm_loss, ModelOutput
 from .neox import apply_rotary, rotary_tables
 
 
@@ -56,10 +56,10 @@ class LlamaAttention(nn.Module):
         self.n_head, self.n_kv = cfg.num_attention_heads, cfg.num_key_value_heads
         self.head_dim = cfg.hidden_size // cfg.num_attention_heads
         self.theta = cfg.rope_theta
-        self.q_proj = nn.Linear(cfg.hidden_size, self.n_head * self.head_dim, bias=cfg.attention_bias)
-        self.k_proj = nn.Linear(cfg.hidden_size, self.n_kv * self.head_dim, bias=cfg.attention_bias)
-        self.v_proj = nn.Linear(cfg.hidden_size, self.n_kv * self.head_dim, bias=cfg.attention_bias)
-        self.o_proj = nn.Linear(self.n_head * self.head_dim, cfg.hidden_size, bias=False)
+        self.q_proj = Linear(cfg.hidden_size, self.n_head * self.head_dim, bias=cfg.attention_bias)
+        self.k_proj = Linear(cfg.hidden_size, self.n_kv * self.head_dim, bias=cfg.attention_bias)
+        self.v_proj = Linear(cfg.hidden_size, self.n_kv * self.head_dim, bias=cfg.attention_bias)
+        self.o_proj = Linear(self.n_head * self.head_dim, cfg.hidden_size, bias=False)
         self._tables = None
 
     def forward(self, x, attention_mask=None):
@@ -82,9 +82,9 @@ class LlamaAttention(nn.Module):
 class LlamaMLP(nn.Module):
     def __init__(self, cfg: LlamaConfig):
         super().__init__()
-        self.gate_proj = nn.Linear(cfg.hidden_size, cfg.intermediate_size, bias=False)
-        self.up_proj = nn.Linear(cfg.hidden_size, cfg.intermediate_size, bias=False)
-        self.down_proj = nn.Linear(cfg.intermediate_size, cfg.hidden_size, bias=False)
+        self.gate_proj = Linear(cfg.hidden_size, cfg.intermediate_size, bias=False)
+        self.up_proj = Linear(cfg.hidden_size, cfg.intermediate_size, bias=False)
+        self.down_proj = Linear(cfg.intermediate_size, cfg.hidden_size, bias=False)
 
     def forward(self, x):
         return self.down_proj(F.silu(self.gate_proj(x)) * self.up_proj(x))
@@ -124,10 +124,11 @@ class LlamaForCausalLM(nn.Module):
         super().__init__()
         self.config = cfg
         self.model = LlamaModel(cfg)
-        self.lm_head = nn.Linear(cfg.hidden_size, cfg.vocab_size, bias=False)
+        self.lm_head = Linear(cfg.hidden_size, cfg.vocab_size, bias=False)
         self.apply(init_weights)
         if cfg.tie_word_embeddings:
             self.lm_head.weight = self.model.embed_tokens.weight
+            self.lm_head.weight._sb_tied = True     # two gradients per backward: layers must hand theirs to autograd
 
     def forward(self, input_ids, attention_mask=None, labels=None, **_):
         hidden = self.model(input_ids, attention_mask)

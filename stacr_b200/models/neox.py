@@ -8,7 +8,7 @@ import torch
 from torch import nn
 
 from ..ops import nn_ops
-from .common import GELU, LayerNorm, ModelOutput, causal_attention, init_weights, lm_loss
+from .common import causal_attention, GELU, init_weights, LayerNorm, Linear, lm_loss, ModelOutput
 
 
 @dataclass
@@ -61,8 +61,8 @@ class NeoXAttention(nn.Module):
         self.head_dim = cfg.hidden_size // cfg.num_attention_heads
         self.rot = int(self.head_dim * cfg.rotary_pct)
         self.base = cfg.rotary_emb_base
-        self.query_key_value = nn.Linear(cfg.hidden_size, 3 * cfg.hidden_size)
-        self.dense = nn.Linear(cfg.hidden_size, cfg.hidden_size)
+        self.query_key_value = Linear(cfg.hidden_size, 3 * cfg.hidden_size)
+        self.dense = Linear(cfg.hidden_size, cfg.hidden_size)
         self.attention_dropout = cfg.attention_dropout
         self._tables = None
         self._half = None
@@ -102,9 +102,9 @@ class NeoXAttention(nn.Module):
 class NeoXMLP(nn.Module):
     def __init__(self, cfg: NeoXConfig):
         super().__init__()
-        self.dense_h_to_4h = nn.Linear(cfg.hidden_size, cfg.intermediate_size)
+        self.dense_h_to_4h = Linear(cfg.hidden_size, cfg.intermediate_size)
         self.act = GELU("none")
-        self.dense_4h_to_h = nn.Linear(cfg.intermediate_size, cfg.hidden_size)
+        self.dense_4h_to_h = Linear(cfg.intermediate_size, cfg.hidden_size)
 
     def forward(self, x):
         return self.dense_4h_to_h(self.act(self.dense_h_to_4h(x)))
@@ -149,7 +149,7 @@ class GPTNeoXForCausalLM(nn.Module):
         super().__init__()
         self.config = cfg
         self.gpt_neox = NeoXModel(cfg)
-        self.embed_out = nn.Linear(cfg.hidden_size, cfg.vocab_size, bias=False)
+        self.embed_out = Linear(cfg.hidden_size, cfg.vocab_size, bias=False)
         self.apply(init_weights)
         if cfg.tie_word_embeddings:
             self.embed_out.weight = self.gpt_neox.embed_in.weight

@@ -69,7 +69,13 @@ def use_kernels(t: torch.Tensor) -> bool:
     return t.is_cuda
 
 
+_raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+
+
 def stream_ptr() -> ctypes.c_void_p:
+    """The current CUDA stream of the current device as a raw handle (called once per kernel launch: kept cheap)."""
+    if _raw_stream is not None:
+        return ctypes.c_void_p(_raw_stream(torch.cuda.current_device()))
     return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
 
 

@@ -14,6 +14,24 @@ import os
 _TWO_CTA_DEFAULT = os.environ.get("STACR_GEMM_2CTA", "1") == "1"
 
 
+_TYPED = None
+
+
+def _typed_lib():
+    """The kernel library with argument types declared for the two GEMM entry points: plain Python ints and floats are
+    converted by ctypes itself, which is several microseconds cheaper per launch than building c_int / c_void_p objects."""
+    global _TYPED
+    if _TYPED is None:
+        lib = _lib.load()
+        vp, ci, cf = ctypes.c_void_p, ctypes.c_int, ctypes.c_float
+        lib.sb_gemm_bf16.argtypes = [vp, vp, vp, vp, ci, ci, ci, ci, ci, ci, ci, ci, ci, ci, ci, cf, ci, vp, vp]
+        lib.sb_gemm_bf16.restype = ci
+        lib.sb_gemm_bf16_2cta.argtypes = [vp, vp, vp, vp, ci, ci, ci, ci, ci, ci, ci, ci, ci, cf, ci, vp, vp]
+        lib.sb_gemm_bf16_2cta.restype = ci
+        _TYPED = lib
+    return _TYPED
+
+
 def _pick_bn(m: int, n: int, b_mn: bool, sms: int) -> int:
     if n <= 16 and not b_mn:
         return 16
@@ -85,27 +103,21 @@ def gemm(
     sms = _lib.sm_count(a.device)
     if bn is None:
         bn = _pick_bn(m, n, b_mn, sms)
-    lib = _lib.load()
+    lib = _typed_lib()
     if two_cta is None:
         two_cta = _TWO_CTA_DEFAULT and bn == 256 and m >= 512 and n >= 512
+    bias_ptr = None if bias is None else bias.data_ptr()
+    status = _lib.status_word(a.device).data_ptr()
+    stream = _lib.stream_ptr()
     if two_cta and not atomic:
         # CTA pairs on 256 x 256 tiles (tcgen05.mma.cta_group::2): each CTA stages half of the B tile
-        rc = lib.sb_gemm_bf16_2cta(
-            _lib.ptr(a), _lib.ptr(b), _lib.ptr(out), _lib.ptr(bias), ctypes.c_int(m), ctypes.c_int(n), ctypes.c_int(k),
-            ctypes.c_int(a.stride(0)), ctypes.c_int(b.stride(0)), ctypes.c_int(out.stride(0)), ctypes.c_int(int(a_mn)), ctypes.c_int(int(b_mn)),
-            ctypes.c_int(mode), ctypes.c_float(alpha), ctypes.c_int(sms), _lib.ptr(_lib.status_word(a.device)), _lib.stream_ptr(),
-        )
+        rc = lib.sb_gemm_bf16_2cta(a.data_ptr(), b.data_ptr(), out.data_ptr(), bias_ptr, m, n, k, a.stride(0), b.stride(0), out.stride(0),
+                                   int(a_mn), int(b_mn), mode, alpha, sms, status, stream)
         _lib.check_rc(rc, "sb_gemm_bf16_2cta")
         _lib.count(1)
         return out
-    rc = lib.sb_gemm_bf16(
-        _lib.ptr(a), _lib.ptr(b), _lib.ptr(out), _lib.ptr(bias),
-        ctypes.c_int(m), ctypes.c_int(n), ctypes.c_int(k),
-        ctypes.c_int(a.stride(0)), ctypes.c_int(b.stride(0)), ctypes.c_int(out.stride(0)),
-        ctypes.c_int(int(a_mn)), ctypes.c_int(int(b_mn)), ctypes.c_int(mode), ctypes.c_int(max(1, splits)),
-        ctypes.c_int(bn), ctypes.c_float(alpha), ctypes.c_int(sms),
-        _lib.ptr(_lib.status_word(a.device)), _lib.stream_ptr(),
-    )
+    rc = lib.sb_gemm_bf16(a.data_ptr(), b.data_ptr(), out.data_ptr(), bias_ptr, m, n, k, a.stride(0), b.stride(0), out.stride(0),
+                          int(a_mn), int(b_mn), mode, max(1, splits), bn, alpha, sms, status, stream)
     _lib.check_rc(rc, "sb_gemm_bf16")
     _lib.count(1)
     return out

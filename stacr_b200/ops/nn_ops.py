@@ -161,6 +161,70 @@ def linear_cross_entropy(hidden, weight, target, chunk: int = 0):
     return total / valid
 
 
+# ------------------------------------------------------------------------------ plain linear layer
+class _LinearFn(torch.autograd.Function):
+    """``y = x W^T + b`` for a projection that is not compressed.
+
+    Forward and the input gradient are plain library GEMMs on bf16 operands (the bf16 copy of the weight is the shadow the
+    fused optimizer keeps current, when there is one).  The weight gradient is one in-tree GEMM ``dY^T X`` with fp32
+    accumulation *and fp32 output*: under autocast the library path produces a bf16 ``dW``, casts it to fp32 and, with a
+    flat gradient buffer, copies it into its slot; here the kernel writes fp32 once, straight into the slot when a gradient
+    synchroniser has lent one (``weight._sb_grad_out``).
+    """
+
+    @staticmethod
+    def forward(ctx, x, weight, bias):
+        from ..layers import _bf16_weight
+
+        x2d = x.reshape(-1, x.shape[-1])
+        xa = (x2d if x2d.dtype == torch.bfloat16 else x2d.to(torch.bfloat16)).contiguous()
+        wb = _bf16_weight(weight)
+        y = F.linear(xa, wb, None if bias is None else bias.detach().to(torch.bfloat16))
+        ctx.save_for_backward(xa, weight)
+        ctx.lead, ctx.in_dtype, ctx.bias_dtype = x.shape[:-1], x.dtype, None if bias is None else bias.dtype
+        return y.reshape(*ctx.lead, weight.shape[0])
+
+    @staticmethod
+    def backward(ctx, dy):
+        from ..layers import _bf16_weight
+        from . import stacr_ops
+        from .gemm import gemm
+
+        xa, weight = ctx.saved_tensors
+        out_features, in_features = weight.shape
+        g = dy.reshape(-1, out_features)
+        g = (g if g.dtype == torch.bfloat16 else g.to(torch.bfloat16)).contiguous()
+        dx = dw = db = None
+        if ctx.needs_input_grad[0]:
+            dx = torch.mm(g, _bf16_weight(weight)).reshape(*ctx.lead, in_features).to(ctx.in_dtype)
+        if ctx.needs_input_grad[1]:
+            slot = getattr(weight, "_sb_grad_out", None) if getattr(weight, "_sb_grad_fresh", False) else None
+            if slot is not None and slot.dtype == torch.float32 and weight.dtype == torch.float32:
+                weight._sb_grad_fresh = False
+            else:
+                slot = None
+            dw = gemm(g, xa, a_mn=True, b_mn=True, out=slot, out_dtype=torch.float32)
+            ready = getattr(weight, "_sb_grad_ready", None) if slot is not None else None
+            if ready is not None and not getattr(weight, "_sb_tied", False):
+                ready()      # the slot is the gradient: nothing goes back through autograd (it would be cloned)
+                dw = None
+            elif dw.dtype != weight.dtype:
+                dw = dw.to(weight.dtype)
+        if ctx.bias_dtype is not None and ctx.needs_input_grad[2]:
+            db = stacr_ops.colsum(g).to(ctx.bias_dtype)
+        return dx, dw, db
+
+
+def linear(x, weight, bias=None):
+    """Linear map with the fp32-direct weight gradient on a B200 when the activations are (or autocast makes them) bf16."""
+    usable = (x.is_cuda and weight.is_cuda and weight.dim() == 2 and x.shape[-1] % 8 == 0 and weight.shape[0] % 8 == 0 and x.numel() > 0
+              and (x.dtype == torch.bfloat16 or (torch.is_autocast_enabled() and torch.get_autocast_dtype("cuda") == torch.bfloat16))
+              and torch.is_grad_enabled() and weight.requires_grad)
+    if usable:
+        return _LinearFn.apply(x, weight, bias)
+    return F.linear(x, weight, bias)
+
+
 # ------------------------------------------------------------------------------ rotary embedding
 class _RotaryQKFn(torch.autograd.Function):
     """Rotate q and k inside a fused qkv projection output, in place (the projection does not need its output for backward)."""

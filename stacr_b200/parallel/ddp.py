@@ -117,9 +117,10 @@ class GradSync:
         self._views = [self.flat[off:off + p.numel()].view_as(p) for p, off in zip(self.params, offsets)]
         for p, view in zip(self.params, self._views):
             p.grad = view
-            p._sb_grad_out = view          # compressed layers write their first gradient of a step straight into the slot
+            p._sb_grad_out = view          # layers write their first gradient of a step straight into the slot ...
             p._sb_grad_fresh = False
         self._written = [True] * len(self.params)
+        self._counted = [False] * len(self.params)
         # buckets over the reversed parameter list (backward order)
         limit = int(bucket_mb * 1024 * 1024 / 4)
         self.buckets: list[tuple[int, int]] = []
@@ -145,6 +146,9 @@ class GradSync:
         self._launched = 0
         self.reductions = 0
         self._hooks = [p.register_post_accumulate_grad_hook(self._make_hook(i)) for i, p in enumerate(self.params)]
+        for i, p in enumerate(self.params):
+            if i >= self.n_fused:
+                p._sb_grad_ready = self._make_ready(i)     # ... and then call this instead of returning the gradient to autograd
         self._total = total
         self._offsets = offsets
         self._syncing = True
@@ -198,13 +202,30 @@ class GradSync:
 
         def hook(param):
             self._written[index] = True       # moved into its slot together with the rest of its bucket
-            if not self._syncing:
-                return
+            if not self._syncing or self._counted[index]:
+                return                        # a layer that handed its slot over directly has already been counted this pass
+            self._counted[index] = True
             b = self._bucket_of[index]
             self._pending[b] -= 1
             if self._pending[b] == 0:
                 self._launch(b)
         return hook
+
+    def _make_ready(self, index: int):
+        """Hand-over used by layers that have written a parameter's gradient into its slot themselves.
+
+        Returning the slot to autograd would not do: the engine clones a gradient that anything else still references
+        (the slot is referenced from here), and the clone would then be copied back.  The layer instead writes the slot,
+        calls this, and returns no gradient for the parameter.  Only valid for a parameter that receives one gradient per
+        backward pass; tied parameters (``param._sb_tied``) keep the ordinary route.
+        """
+        hook = self._make_hook(index)
+
+        def ready():
+            param = self.params[index]
+            param.grad = self._views[index]
+            hook(param)
+        return ready
 
     def _adopt_bucket(self, b: int) -> None:
         """Move the gradients of bucket ``b`` that autograd produced elsewhere into their slots with one multi-tensor copy."""
@@ -305,6 +326,7 @@ class GradSync:
             self._written[i] = False
         self._fused_state = [0] * self.n_fused
         self._pending = list(self._size)
+        self._counted = [False] * len(self.params)
         self._launched = 0
 
     def finish(self) -> None:
@@ -329,7 +351,7 @@ class GradSync:
             h.remove()
         self._hooks = []
         for p in self.params:
-            for attr in ("_sb_grad_sink", "_sb_grad_out", "_sb_grad_fresh"):
+            for attr in ("_sb_grad_sink", "_sb_grad_out", "_sb_grad_fresh", "_sb_grad_ready"):
                 if hasattr(p, attr):
                     delattr(p, attr)
 

@@ -142,3 +142,46 @@ def test_padded_vocabulary_head_matches_fp32_reference():
     with torch.autocast("cuda", dtype=torch.bfloat16):
         chunked = nn_ops.linear_cross_entropy(h.detach(), w.detach(), t, chunk=128)
     assert abs(float(chunked) - float(ref)) < 2e-2
+
+
+def test_plain_linear_writes_fp32_weight_gradient_and_uses_a_lent_slot():
+    from stacr_b200.models.common import Linear
+    from stacr_b200.ops import _lib
+
+    torch.manual_seed(5)
+    lin = Linear(264, 520, device="cuda")
+    ref = torch.nn.Linear(264, 520, device="cuda")
+    ref.load_state_dict(lin.state_dict())
+    x = torch.randn(3, 200, 264, device="cuda", requires_grad=True)
+    xr = x.detach().clone().requires_grad_(True)
+    with torch.autocast("cuda", dtype=torch.bfloat16):
+        y = lin(x)
+        yr = ref(xr)
+    assert y.dtype == torch.bfloat16 and type(y.grad_fn).__name__.startswith("_LinearFn")
+    torch.testing.assert_close(y.float(), yr.float(), rtol=2e-2, atol=2e-2)
+    g = torch.randn_like(y)
+    y.backward(g)
+    yr.backward(g)
+    torch.cuda.synchronize()
+    _lib.check_status()
+    assert lin.weight.grad.dtype == torch.float32
+    exact = g.float().reshape(-1, 520).t() @ x.detach().reshape(-1, 264).bfloat16().float()
+    assert float((lin.weight.grad - exact).abs().max() / exact.abs().max()) < 2e-3          # fp32 accumulation and output
+    torch.testing.assert_close(lin.weight.grad, ref.weight.grad, rtol=3e-2, atol=3e-2 * float(exact.abs().max()))
+    torch.testing.assert_close(lin.bias.grad, ref.bias.grad, rtol=2e-2, atol=0.5)
+    torch.testing.assert_close(x.grad, xr.grad, rtol=3e-2, atol=3e-2)
+    # a lent slot is written in place and becomes the gradient; a second backward accumulates into it
+    lin.zero_grad(set_to_none=True)
+    flat = torch.full((64 + lin.weight.numel() + 64,), -77.0, device="cuda")
+    slot = flat[64:64 + lin.weight.numel()].view_as(lin.weight)
+    lin.weight._sb_grad_out, lin.weight._sb_grad_fresh = slot, True
+    with torch.autocast("cuda", dtype=torch.bfloat16):
+        lin(x.detach()).backward(g)
+    assert lin.weight.grad.data_ptr() == slot.data_ptr() and not lin.weight._sb_grad_fresh
+    torch.testing.assert_close(slot, exact, rtol=2e-3, atol=2e-3 * float(exact.abs().max()))
+    assert bool((flat[:64] == -77.0).all()) and bool((flat[-64:] == -77.0).all())
+    with torch.autocast("cuda", dtype=torch.bfloat16):
+        lin(x.detach()).backward(g)
+    torch.testing.assert_close(lin.weight.grad, 2 * exact, rtol=2e-3, atol=4e-3 * float(exact.abs().max()))
+    # fp32 inputs outside autocast and tiny heads keep the stock path
+    assert not type(lin(x.detach()).grad_fn).__name__.startswith("_LinearFn")

@@ -281,3 +281,48 @@ def test_two_rank_gloo_fused_parameter_slots_and_accumulation(tmp_path):
     run = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
                           "--master-port", "29613", str(script)], capture_output=True, text=True, env=env, timeout=240)
     assert run.returncode == 0 and run.stdout.count("FUSED_OK") == 2, run.stdout[-2000:] + run.stderr[-2000:]
+
+
+def test_gradient_slot_hand_over_counts_each_parameter_once():
+    """A layer that wrote a parameter's gradient into its slot calls ``_sb_grad_ready`` and returns nothing to autograd."""
+    import torch
+    from torch import nn
+
+    from stacr_b200.parallel.ddp import GradSync
+
+    torch.manual_seed(0)
+    model = nn.Sequential(nn.Linear(8, 8), nn.Linear(8, 4))
+    sync = GradSync(model.parameters(), backend="none")
+    w = model[0].weight
+    assert callable(w._sb_grad_ready) and w._sb_grad_out.shape == w.shape
+    sync.zero_grad()
+    assert w.grad is None and w._sb_grad_fresh
+
+    class Direct(torch.autograd.Function):
+        @staticmethod
+        def forward(ctx, x, weight):
+            ctx.save_for_backward(x, weight)
+            return x @ weight.t()
+
+        @staticmethod
+        def backward(ctx, dy):
+            x, weight = ctx.saved_tensors
+            slot = weight._sb_grad_out
+            torch.mm(dy.t(), x, out=slot)
+            weight._sb_grad_fresh = False
+            weight._sb_grad_ready()
+            return dy @ weight, None
+
+    x = torch.randn(5, 8)
+    y = model[1](torch.relu(Direct.apply(x, w) + model[0].bias))
+    y.sum().backward()
+    sync.finish()
+    assert w.grad.data_ptr() == w._sb_grad_out.data_ptr()
+    ref = nn.Sequential(nn.Linear(8, 8), nn.Linear(8, 4))
+    ref.load_state_dict(model.state_dict())
+    ref[1](torch.relu(ref[0](x))).sum().backward()
+    for a, b in zip(model.parameters(), ref.parameters()):
+        assert torch.allclose(a.grad, b.grad, atol=1e-6)
+    assert all(sync._written) and all(n == 0 for n in sync._pending)
+    sync.close()
+    assert not hasattr(w, "_sb_grad_ready")
