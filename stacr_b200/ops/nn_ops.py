@@ -173,16 +173,17 @@ class _LinearFn(torch.autograd.Function):
     """
 
     @staticmethod
-    def forward(ctx, x, weight, bias):
+    def forward(ctx, x2d, weight, bias):
+        # 2-D in, 2-D out: the caller reshapes outside, so that the output is not a view made inside the function
+        # (the fused-QKV rotary embedding modifies it in place)
         from ..layers import _bf16_weight
 
-        x2d = x.reshape(-1, x.shape[-1])
         xa = (x2d if x2d.dtype == torch.bfloat16 else x2d.to(torch.bfloat16)).contiguous()
         wb = _bf16_weight(weight)
         y = F.linear(xa, wb, None if bias is None else bias.detach().to(torch.bfloat16))
         ctx.save_for_backward(xa, weight)
-        ctx.lead, ctx.in_dtype, ctx.bias_dtype = x.shape[:-1], x.dtype, None if bias is None else bias.dtype
-        return y.reshape(*ctx.lead, weight.shape[0])
+        ctx.in_dtype, ctx.bias_dtype = x2d.dtype, None if bias is None else bias.dtype
+        return y
 
     @staticmethod
     def backward(ctx, dy):
@@ -192,11 +193,10 @@ class _LinearFn(torch.autograd.Function):
 
         xa, weight = ctx.saved_tensors
         out_features, in_features = weight.shape
-        g = dy.reshape(-1, out_features)
-        g = (g if g.dtype == torch.bfloat16 else g.to(torch.bfloat16)).contiguous()
+        g = (dy if dy.dtype == torch.bfloat16 else dy.to(torch.bfloat16)).contiguous()
         dx = dw = db = None
         if ctx.needs_input_grad[0]:
-            dx = torch.mm(g, _bf16_weight(weight)).reshape(*ctx.lead, in_features).to(ctx.in_dtype)
+            dx = torch.mm(g, _bf16_weight(weight)).to(ctx.in_dtype)
         if ctx.needs_input_grad[1]:
             slot = getattr(weight, "_sb_grad_out", None) if getattr(weight, "_sb_grad_fresh", False) else None
             if slot is not None and slot.dtype == torch.float32 and weight.dtype == torch.float32:
@@ -221,7 +221,8 @@ def linear(x, weight, bias=None):
               and (x.dtype == torch.bfloat16 or (torch.is_autocast_enabled() and torch.get_autocast_dtype("cuda") == torch.bfloat16))
               and torch.is_grad_enabled() and weight.requires_grad)
     if usable:
-        return _LinearFn.apply(x, weight, bias)
+        y = _LinearFn.apply(x.reshape(-1, x.shape[-1]) if x.dim() != 2 else x, weight, bias)
+        return y if x.dim() == 2 else y.reshape(*x.shape[:-1], weight.shape[0])
     return F.linear(x, weight, bias)
 
 

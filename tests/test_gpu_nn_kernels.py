@@ -175,6 +175,7 @@ def test_plain_linear_writes_fp32_weight_gradient_and_uses_a_lent_slot():
     flat = torch.full((64 + lin.weight.numel() + 64,), -77.0, device="cuda")
     slot = flat[64:64 + lin.weight.numel()].view_as(lin.weight)
     lin.weight._sb_grad_out, lin.weight._sb_grad_fresh = slot, True
+    lin.weight._sb_grad_ready = lambda: setattr(lin.weight, "grad", slot)       # what a gradient synchroniser installs
     with torch.autocast("cuda", dtype=torch.bfloat16):
         lin(x.detach()).backward(g)
     assert lin.weight.grad.data_ptr() == slot.data_ptr() and not lin.weight._sb_grad_fresh
