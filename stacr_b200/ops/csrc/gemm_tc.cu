@@ -238,24 +238,39 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       const bool staged = (p.out_mode == 0 || p.out_mode == 3) && (p.ldo % 8 == 0) && (p.N % 8 == 0) &&
                           ((reinterpret_cast<uintptr_t>(p.out) & 15) == 0);
       uint4* my_stage = reinterpret_cast<uint4*>(epi_stage) + quad * (32 * 8);
-#pragma unroll 1
-      for (int c = 0; c < BN / 16; ++c) {
-        uint32_t v[16];
-        tmem_ld_x16(t_row + c * 16, v);
-        tmem_ld_wait();
+      // Two chunks of 16 accumulator columns are in flight: the TMEM load of chunk c + 1 is issued before chunk c is
+      // processed, and a chunk's 16 bias values are fetched (four 16-byte loads, or guarded scalars at the edge) before
+      // the wait, so that neither latency sits on the critical path of this warp.
+      constexpr int NCH = BN / 16;
+      auto load_bias = [&](int c, float (&bv)[16]) {
         const int col0 = n_blk * BN + c * 16;
-        if (!staged && col0 >= p.N) continue;  // warp-uniform
+        if (!add_bias) {
+#pragma unroll
+          for (int i = 0; i < 16; ++i) bv[i] = 0.f;
+        } else if (col0 + 16 <= p.N && ((reinterpret_cast<uintptr_t>(p.bias) & 15) == 0)) {
+#pragma unroll
+          for (int q4 = 0; q4 < 4; ++q4) {
+            const float4 t = __ldg(reinterpret_cast<const float4*>(p.bias + col0) + q4);
+            bv[4 * q4] = t.x; bv[4 * q4 + 1] = t.y; bv[4 * q4 + 2] = t.z; bv[4 * q4 + 3] = t.w;
+          }
+        } else {
+#pragma unroll
+          for (int i = 0; i < 16; ++i) bv[i] = (col0 + i < p.N) ? __ldg(p.bias + col0 + i) : 0.f;
+        }
+      };
+      auto process = [&](int c, const uint32_t (&v)[16], const float (&bv)[16]) {
+        const int col0 = n_blk * BN + c * 16;
+        if (!staged && col0 >= p.N) return;  // warp-uniform
         float f[16];
 #pragma unroll
         for (int i = 0; i < 16; ++i) {
-          f[i] = __uint_as_float(v[i]) * p.alpha;
-          if (add_bias && col0 + i < p.N) f[i] += __ldg(p.bias + col0 + i);
+          f[i] = fmaf(__uint_as_float(v[i]), p.alpha, bv[i]);
         }
         if (staged) {
           const int cu = (c * 2) % UNITS;  // first 16-byte unit of this chunk inside the staged row
           my_stage[lane * 8 + ((cu) ^ (lane & 7))] = make_uint4(pack_bf16x2(f[0], f[1]), pack_bf16x2(f[2], f[3]), pack_bf16x2(f[4], f[5]), pack_bf16x2(f[6], f[7]));
           my_stage[lane * 8 + ((cu + 1) ^ (lane & 7))] = make_uint4(pack_bf16x2(f[8], f[9]), pack_bf16x2(f[10], f[11]), pack_bf16x2(f[12], f[13]), pack_bf16x2(f[14], f[15]));
-          if (((c + 1) * 16) % GW != 0) continue;  // group not complete yet
+          if (((c + 1) * 16) % GW != 0) return;  // group not complete yet
           __syncwarp();
           const int gcol0 = n_blk * BN + (c * 16 + 16 - GW);  // first column of the group
           const int row_base = m_blk * BM + quad * 32;
@@ -278,9 +293,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             }
           }
           __syncwarp();
-          continue;
+          return;
         }
-        if (!row_ok) continue;
+        if (!row_ok) return;
         const bool full = (col0 + 16 <= p.N);
         if (p.out_mode == 0) {
           __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(p.out) + static_cast<size_t>(row) * p.ldo + col0;
@@ -329,6 +344,27 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
               dst[1] = make_uint4(w[4], w[5], w[6], w[7]);
             }
           }
+        }
+      };
+      uint32_t va[16], vb[16];
+      float ba[16], bb[16];
+      tmem_ld_x16(t_row, va);
+      load_bias(0, ba);
+#pragma unroll 1
+      for (int c = 0; c < NCH; c += 2) {
+        tmem_ld_wait();                                   // chunk c is in va
+        if (c + 1 < NCH) {
+          tmem_ld_x16(t_row + (c + 1) * 16, vb);
+          load_bias(c + 1, bb);
+        }
+        process(c, va, ba);
+        if (c + 1 < NCH) {
+          tmem_ld_wait();                                 // chunk c + 1 is in vb
+          if (c + 2 < NCH) {
+            tmem_ld_x16(t_row + (c + 2) * 16, va);
+            load_bias(c + 2, ba);
+          }
+          process(c + 1, vb, bb);
         }
       }
       tc_fence_before();
