@@ -36,3 +36,12 @@ def test_no_fused_engine_without_peers():
     wrapped = RowParallelLinear(nn.Linear(16, 16), fused=True)
     assert wrapped._engine(torch.randn(2, 16), 32) is None
     assert "fused=True" in wrapped.extra_repr()
+
+
+def test_fused_tensor_parallel_degree_limit_is_configurable(monkeypatch):
+    from stacr_b200.parallel import tp
+
+    monkeypatch.delenv("STACR_TP_FUSED_MAX_WORLD", raising=False)
+    assert tp._max_fused_world() == 2
+    monkeypatch.setenv("STACR_TP_FUSED_MAX_WORLD", "4")
+    assert tp._max_fused_world() == 4
