@@ -741,10 +741,15 @@ def run_convergence_experiment(cfg: ConvergenceConfig, logger) -> Dict[str, Any]
                 record["activation_spectrum"] = compute_activation_spectrum_telemetry(model, batch, amp, layers, cfg.activation_spectrum_rank)
             logger.log(record)
             step += 1
-            if cfg.save_every_n_steps and step % cfg.save_every_n_steps == 0 and int(os.environ.get("LOCAL_RANK", "0")) == 0 and getattr(logger, "dir", None):
-                target = logger.dir / f"checkpoint_step_{step}"
-                target.mkdir(parents=True, exist_ok=True)
-                torch.save(model.state_dict(), target / "model.pt")
+            if cfg.save_every_n_steps and step % cfg.save_every_n_steps == 0:
+                if int(os.environ.get("LOCAL_RANK", "0")) == 0 and getattr(logger, "dir", None):
+                    target = logger.dir / f"checkpoint_step_{step}"
+                    target.mkdir(parents=True, exist_ok=True)
+                    torch.save(model.state_dict(), target / "model.pt")
+                if world > 1 and torch.distributed.is_initialized():
+                    # the other ranks wait on the host while one rank writes: the device-side peer waits of the next
+                    # step's collectives are bounded and must not be spent on a checkpoint
+                    torch.distributed.barrier()
     except FloatingPointError as exc:
         status = f"error: {exc}"
     if ev:

@@ -590,14 +590,19 @@ def _kernel_ok(x2d: torch.Tensor, weight: torch.Tensor) -> bool:
 def _kernel_linear(x2d, weight, bias):
     from .ops.gemm import gemm
 
-    return gemm(x2d.to(torch.bfloat16).contiguous(), weight.detach().to(torch.bfloat16).contiguous(),
+    from .layers import _bf16_weight
+
+    # the optimizer's bf16 shadow of the master weight when there is one (no per-call cast of the whole matrix)
+    return gemm(x2d.to(torch.bfloat16).contiguous(), _bf16_weight(weight).contiguous(),
                 bias=None if bias is None else bias.detach().float())
 
 
 def _kernel_dx(g2d, weight):
     from .ops.gemm import gemm
 
-    return gemm(g2d.to(torch.bfloat16).contiguous(), weight.detach().to(torch.bfloat16).contiguous(), b_mn=True)
+    from .layers import _bf16_weight
+
+    return gemm(g2d.to(torch.bfloat16).contiguous(), _bf16_weight(weight).contiguous(), b_mn=True)
 
 
 def _kernel_project(act, basis):

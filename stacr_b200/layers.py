@@ -149,9 +149,19 @@ def _compute_dtype(x: torch.Tensor, weight: torch.Tensor) -> torch.dtype:
 
 
 def _bf16_weight(weight: torch.Tensor) -> torch.Tensor:
-    """bf16 copy of a master weight: the shadow the fused optimizer keeps current, else a cast."""
+    """bf16 copy of a master weight: the shadow the fused optimizer keeps current, else a cast.
+
+    The shadow is trusted only while the master has not been written by anyone else.  The fused optimizer updates master
+    and shadow through raw pointers (no version bump) and records the master's version counter next to the shadow; any
+    other write (``load_state_dict``, a broadcast, another optimizer, a manual edit) bumps the counter, and the shadow is
+    then refreshed from the master here before it is used.
+    """
     shadow = getattr(weight, "_bf16_shadow", None)
-    if shadow is not None and shadow.shape == weight.shape:
+    if shadow is not None and shadow.shape == weight.shape and shadow.device == weight.device:
+        if getattr(weight, "_bf16_shadow_version", None) != weight._version:
+            with torch.no_grad():
+                shadow.copy_(weight.detach())
+            weight._bf16_shadow_version = weight._version
         return shadow
     return weight.detach().to(torch.bfloat16)
 

@@ -10,6 +10,7 @@ False.
 from __future__ import annotations
 
 import ctypes
+import os
 import threading
 from pathlib import Path
 
@@ -43,15 +44,23 @@ def lib_path() -> Path:
 
 
 def load() -> ctypes.CDLL:
+    """The kernel library, built first when it is missing or older than its sources.
+
+    The build runs under a file lock and the link replaces the library atomically, so ranks started together by a launcher
+    build once and never map a half-written file (see ``build.ensure_built``).
+    """
     global _lib
     if _lib is not None:
         return _lib
     with _lock:
         if _lib is None:
-            if not _LIB_PATH.exists():
-                from .build import ensure_built
+            from .build import ensure_built
 
+            try:
                 ensure_built()
+            except OSError:
+                if not _LIB_PATH.exists():
+                    raise
             if not _LIB_PATH.exists():
                 raise KernelError(
                     f"{_LIB_PATH} is missing: run `python -m stacr_b200.ops.build` (needs nvcc)"
@@ -99,6 +108,63 @@ def check_status(device=None, *, reset: bool = True) -> None:
         if reset:
             word.zero_()
         raise KernelError(f"kernel status {code}: {STATUS_TEXT.get(code, 'unknown')}")
+
+
+class _StatusPoller:
+    """Asynchronous reader of one device's status word.
+
+    ``poll`` queues a 4-byte copy of the word into pinned memory behind everything already on the current stream and
+    inspects the copy queued by the previous call, so a training loop can look at the word every step without making the
+    host wait for the GPU: a timeout recorded in step k raises at the end of step k + 1.
+    """
+
+    def __init__(self, device_index: int):
+        self.index = device_index
+        self.host = torch.zeros(2, dtype=torch.int32).pin_memory()
+        self.events = [torch.cuda.Event(), torch.cuda.Event()]
+        self.count = 0
+
+    def poll(self, *, wait: bool = False) -> None:
+        word = status_word(self.index)
+        slot = self.count & 1
+        prev = slot ^ 1
+        if self.count:
+            if wait:
+                self.events[prev].synchronize()
+            if self.events[prev].query():
+                code = int(self.host[prev])
+                if code != 0:
+                    self.host[prev] = 0
+                    word.zero_()
+                    raise KernelError(f"kernel status {code}: {STATUS_TEXT.get(code, 'unknown')}")
+        self.host[slot:slot + 1].copy_(word, non_blocking=True)
+        self.events[slot].record()
+        self.count += 1
+
+
+_pollers: dict[int, _StatusPoller] = {}
+
+
+def poll_status(device=None, *, strict: bool | None = None) -> None:
+    """Non-blocking status check for training loops: raises ``KernelError`` for a failure recorded up to the previous call.
+
+    With ``strict`` (or ``STACR_STRICT_STATUS=1``) the word is read synchronously instead, which costs a device
+    synchronisation per call but reports a failure before anything consumes the step's results.
+    """
+    if not torch.cuda.is_available():
+        return
+    if strict is None:
+        strict = os.environ.get("STACR_STRICT_STATUS", "0") == "1"
+    if strict:
+        check_status(device)
+        return
+    idx = torch.cuda.current_device() if device is None else torch.device(device).index
+    if idx is None:
+        idx = torch.cuda.current_device()
+    poller = _pollers.get(idx)
+    if poller is None:
+        poller = _pollers[idx] = _StatusPoller(idx)
+    poller.poll()
 
 
 _reserved_sms = 0

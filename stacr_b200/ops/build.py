@@ -33,19 +33,39 @@ def sources() -> list[Path]:
     return sorted(CSRC.glob("*.cu"))
 
 
+STAMP = HERE / "libstacr_b200.so.stamp"
+
+
+def source_digest() -> str:
+    """Hash of every source and header the library is built from (file times do not survive every copy of a tree)."""
+    import hashlib
+
+    h = hashlib.sha256()
+    for p in sorted(list(CSRC.glob("*.cu")) + list(CSRC.glob("*.cuh")) + list(CSRC.glob("*.h"))):
+        h.update(p.name.encode())
+        h.update(p.read_bytes())
+    h.update(" ".join(ARCH_FLAGS + NVCC_FLAGS).encode())
+    return h.hexdigest()
+
+
 def is_stale() -> bool:
-    if not LIB.exists():
+    if not LIB.exists() or not STAMP.exists():
         return True
-    stamp = LIB.stat().st_mtime
-    deps = list(CSRC.glob("*.cu")) + list(CSRC.glob("*.cuh")) + list(CSRC.glob("*.h"))
-    return any(p.stat().st_mtime > stamp for p in deps)
+    return STAMP.read_text().strip() != source_digest()
 
 
 def build(verbose: bool = False) -> Path:
+    """Compile every source and link the library; safe to call from several processes at once.
+
+    Objects go to a directory private to the calling process and the link writes a temporary name that is moved over
+    the library with ``os.replace``, so another process either maps the old complete file or the new complete file.
+    """
     nvcc = nvcc_path()
     if nvcc is None:
         raise RuntimeError("nvcc not found; cannot build the sm_100a kernel library")
-    objdir = HERE / "build"
+    digest = source_digest()
+    (HERE / "build").mkdir(exist_ok=True)
+    objdir = HERE / "build" / f"obj.{os.getpid()}"
     objdir.mkdir(exist_ok=True)
     logs = []
 
@@ -60,11 +80,16 @@ def build(verbose: bool = False) -> Path:
 
     with ThreadPoolExecutor(max_workers=min(8, os.cpu_count() or 1)) as pool:
         objs = list(pool.map(compile_one, sources()))
-    link = [nvcc, *ARCH_FLAGS, "-shared", "-o", str(LIB), *map(str, objs)]
+    staged = LIB.with_name(f".{LIB.name}.{os.getpid()}.tmp")
+    link = [nvcc, *ARCH_FLAGS, "-shared", "-o", str(staged), *map(str, objs)]
     proc = subprocess.run(link, capture_output=True, text=True)
     if proc.returncode != 0:
+        staged.unlink(missing_ok=True)
         raise RuntimeError(f"link failed:\n{proc.stdout}\n{proc.stderr}")
-    (objdir / "ptxas.log").write_text("\n".join(f"== {n}\n{log}" for n, log in logs))
+    os.replace(staged, LIB)
+    STAMP.write_text(digest)
+    (HERE / "build" / "ptxas.log").write_text("\n".join(f"== {n}\n{log}" for n, log in logs))
+    shutil.rmtree(objdir, ignore_errors=True)
     if verbose:
         for name, log in logs:
             print(f"== {name}\n{log}")
@@ -72,9 +97,23 @@ def build(verbose: bool = False) -> Path:
 
 
 def ensure_built() -> Path | None:
-    """Build when stale and a compiler is present; return the library path if it exists."""
-    if is_stale() and nvcc_path() is not None:
-        build()
+    """Build when stale and a compiler is present; return the library path if it exists.
+
+    Processes that arrive together (the ranks of one launcher) serialise on a file lock: the first one builds, the
+    others find a fresh library when they get the lock and return without compiling.
+    """
+    if not is_stale() or nvcc_path() is None:
+        return LIB if LIB.exists() else None
+    import fcntl
+
+    (HERE / "build").mkdir(exist_ok=True)
+    with open(HERE / "build" / ".lock", "w") as lock:
+        fcntl.flock(lock, fcntl.LOCK_EX)
+        try:
+            if is_stale():
+                build()
+        finally:
+            fcntl.flock(lock, fcntl.LOCK_UN)
     return LIB if LIB.exists() else None
 
 

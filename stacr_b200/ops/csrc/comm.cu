@@ -16,6 +16,7 @@
 // Replaces the NCCL all-reduce that DistributedDataParallel issues for the reference
 // (experiments/benchmarks/distributed_data.py:87-97 there).
 #include "common.cuh"
+#include <cstdlib>
 
 namespace sb {
 
@@ -31,7 +32,24 @@ struct CommArgs {
   float scale;
   int epoch;
   int* status;
+  unsigned long long wait_ns;            // how long a flag wait may last before the kernel gives up
 };
+
+// Limit of the peer waits: 2 s unless STACR_WAIT_LIMIT_MS names another value (read once) or sb_comm_set_wait_limit_ns
+// was called.  Jobs whose ranks can legitimately drift further apart (a first-use build, a rank-0-only checkpoint that is
+// not fenced by a host barrier) raise it; tests that let a wait run out lower it.
+static unsigned long long g_comm_wait_ns = 0;
+static unsigned long long comm_wait_ns() {
+  if (g_comm_wait_ns == 0) {
+    unsigned long long ns = SB_WAIT_LIMIT_NS;
+    if (const char* env = getenv("STACR_WAIT_LIMIT_MS")) {
+      const long long ms = atoll(env);
+      if (ms > 0) ns = static_cast<unsigned long long>(ms) * 1000000ull;
+    }
+    g_comm_wait_ns = ns;
+  }
+  return g_comm_wait_ns;
+}
 
 __device__ __forceinline__ void st_release_sys(int* p, int v) {
   asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
@@ -54,7 +72,7 @@ __device__ bool rank_barrier(const CommArgs& a, int phase, int* s_fail) {
     const uint64_t t0 = globaltimer_ns();
     uint32_t polls = 0;
     while (ld_acquire_sys(local) < a.epoch) {
-      if ((++polls & 255u) == 0u && globaltimer_ns() - t0 > SB_WAIT_LIMIT_NS) {
+      if ((++polls & 255u) == 0u && globaltimer_ns() - t0 > a.wait_ns) {
         *s_fail = 1;
         if (a.status) atomicCAS(a.status, 0, ST_TIMEOUT_PEER_FLAG);
         break;
@@ -281,12 +299,15 @@ static int launch_allreduce(bool multimem, const CommArgs& a, int sms, cudaStrea
 
 }  // namespace sb
 
+extern "C" void sb_comm_set_wait_limit_ns(unsigned long long ns) { sb::g_comm_wait_ns = ns ? ns : SB_WAIT_LIMIT_NS; }
+extern "C" unsigned long long sb_comm_wait_limit_ns() { return sb::comm_wait_ns(); }
+
 extern "C" int sb_comm_flag_ints() { return 3 * sb::MAX_CTAS * sb::MAX_RANKS; }
 
 extern "C" int sb_allreduce_two_shot(const void* peer_ptrs, const void* flag_ptrs, unsigned long long mc_ptr, int rank, int world,
                                      long long lo, long long hi, float scale, int epoch, int sms, int* status, void* stream) {
   sb::CommArgs a{static_cast<const unsigned long long*>(peer_ptrs), static_cast<const unsigned long long*>(flag_ptrs), mc_ptr, rank,
-                 world, lo, hi, scale, epoch, status};
+                 world, lo, hi, scale, epoch, status, sb::comm_wait_ns()};
   return sb::launch_allreduce(false, a, sms, static_cast<cudaStream_t>(stream));
 }
 
@@ -294,7 +315,7 @@ extern "C" int sb_allreduce_multimem(const void* peer_ptrs, const void* flag_ptr
                                      long long lo, long long hi, float scale, int epoch, int sms, int* status, void* stream) {
   if (mc_ptr == 0) return -4;
   sb::CommArgs a{static_cast<const unsigned long long*>(peer_ptrs), static_cast<const unsigned long long*>(flag_ptrs), mc_ptr, rank,
-                 world, lo, hi, scale, epoch, status};
+                 world, lo, hi, scale, epoch, status, sb::comm_wait_ns()};
   return sb::launch_allreduce(true, a, sms, static_cast<cudaStream_t>(stream));
 }
 
@@ -305,7 +326,7 @@ extern "C" int sb_allgather_slices(const void* peer_ptrs, const void* flag_ptrs,
   if (world < 1 || world > MAX_RANKS) return -2;
   if ((lo & 3) || (hi & 3) || hi < lo) return -3;
   CommArgs a{static_cast<const unsigned long long*>(peer_ptrs), static_cast<const unsigned long long*>(flag_ptrs), mc_ptr, rank, world,
-             lo, hi, scale, epoch, status};
+             lo, hi, scale, epoch, status, sb::comm_wait_ns()};
   const long long vecs = (hi - lo) / 4 / world;
   const int grid = comm_grid(vecs, sms);
   allgather_slices_kernel<<<grid, 512, 0, static_cast<cudaStream_t>(stream)>>>(a);
@@ -315,7 +336,7 @@ extern "C" int sb_allgather_slices(const void* peer_ptrs, const void* flag_ptrs,
 extern "C" int sb_rank_barrier(const void* flag_ptrs, int rank, int world, int epoch, int* status, void* stream) {
   using namespace sb;
   if (world < 1 || world > MAX_RANKS) return -2;
-  CommArgs a{nullptr, static_cast<const unsigned long long*>(flag_ptrs), 0ull, rank, world, 0, 0, 1.f, epoch, status};
+  CommArgs a{nullptr, static_cast<const unsigned long long*>(flag_ptrs), 0ull, rank, world, 0, 0, 1.f, epoch, status, sb::comm_wait_ns()};
   rank_barrier_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(a);
   return static_cast<int>(cudaGetLastError());
 }
@@ -340,7 +361,7 @@ extern "C" int sb_allreduce_finish(const void* flag_ptrs, int rank, int world, i
   using namespace sb;
   if (world < 1 || world > MAX_RANKS) return -2;
   if ((rows * n) % 8) return -3;
-  CommArgs a{nullptr, static_cast<const unsigned long long*>(flag_ptrs), 0ull, rank, world, 0, 0, 1.f, epoch, status};
+  CommArgs a{nullptr, static_cast<const unsigned long long*>(flag_ptrs), 0ull, rank, world, 0, 0, 1.f, epoch, status, sb::comm_wait_ns()};
   const int grid = comm_grid(rows * n / 8, sms);
   allreduce_finish_kernel<<<grid, 512, 0, static_cast<cudaStream_t>(stream)>>>(a, static_cast<const __nv_bfloat16*>(staging),
                                                                                static_cast<__nv_bfloat16*>(dst), rows, n);

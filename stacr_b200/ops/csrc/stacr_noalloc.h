@@ -29,7 +29,8 @@ long long sb_residual_topk_noalloc_count(int rows, int chunk_rows, int quota_per
 // idx32 or idx64 (exactly one non-NULL) and val sized by sb_residual_topk_noalloc_count; val is
 // bf16 when bits == 0 and int8 codes when bits is 8 or 4; scale is one fp32 on the device).
 //
-// Returns 0 on success.  -7 means the request needs more than SB_NOALLOC_MAX_CHUNKS chunks and
+// Returns 0 on success.  -2 also covers a quota_per_chunk larger than chunk_rows * n (a chunk has
+// no more entries than that; the count function above does not know n and cannot check it).  -7 means the request needs more than SB_NOALLOC_MAX_CHUNKS chunks and
 // was rejected before anything was launched; other negative values are argument errors as in
 // sb_residual_topk; positive values are CUDA error codes.
 //

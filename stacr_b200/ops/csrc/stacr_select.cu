@@ -299,6 +299,7 @@ __global__ void residual_scale_kernel(const SelectParams p) {
   }
 }
 
+constexpr int MAX_DEVICES = 64;  // per-device launch configuration flags are indexed by the CUDA device ordinal
 constexpr int WARP_CAP = 768;  // staged (index, value) pairs per warp between flushes (16 warps: 120 KB)
 
 __device__ __forceinline__ void emit_entry(const SelectParams& p, int o, long long flat, unsigned short bits16,
@@ -531,21 +532,24 @@ static int launch_select(const SelectParams& p, int phase, cudaStream_t st) {
   if (rl < 1) rl = 1;
   const int threads = ((ctn * rl + 31) / 32) * 32;
   const int grid = p.nchunks * p.parts;
+  // the shared-memory opt-in is a per-device function attribute: remember it per device, not per process
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= MAX_DEVICES) return -8;
   if (phase == 0) {
-    static bool cfg = false;
-    if (!cfg) {
+    static bool cfg[MAX_DEVICES] = {false};
+    if (!cfg[dev]) {
       cudaError_t e = cudaFuncSetAttribute(residual_hist_kernel<RP>, cudaFuncAttributeMaxDynamicSharedMemorySize, NBINS * 4 + CS_ROWS * RP * 4);
       if (e != cudaSuccess) return static_cast<int>(e);
-      cfg = true;
+      cfg[dev] = true;
     }
     residual_hist_kernel<RP><<<grid, threads, NBINS * 4 + CS_ROWS * RP * 4, st>>>(p, ctn, rl);
   } else {
     const int smem = 16 * WARP_CAP * (8 + 2) + CS_ROWS * RP * 4;
-    static bool cfg = false;
-    if (!cfg) {
+    static bool cfg[MAX_DEVICES] = {false};
+    if (!cfg[dev]) {
       cudaError_t e = cudaFuncSetAttribute(residual_compact_kernel<RP>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
       if (e != cudaSuccess) return static_cast<int>(e);
-      cfg = true;
+      cfg[dev] = true;
     }
     residual_compact_kernel<RP><<<grid, threads, smem, st>>>(p, ctn, rl);
   }
@@ -667,7 +671,6 @@ __global__ void noalloc_prepare_kernel(int rows, int chunk_rows, int quota_per_c
 
 // Device address of the scratch array for the current device, looked up on first use.
 static int noalloc_scratch_for_current_device(unsigned char** out) {
-  constexpr int MAX_DEVICES = 64;
   static unsigned char* cached[MAX_DEVICES] = {nullptr};
   int dev = 0;
   cudaError_t e = cudaGetDevice(&dev);
@@ -700,6 +703,8 @@ extern "C" int sb_residual_topk_noalloc(const void* x, const void* c, const void
   if (rows <= 0 || n <= 0 || chunk_rows <= 0 || quota_per_chunk < 0) return -2;
   if (r < 1 || r > 32) return -2;
   if ((idx32 == nullptr) == (idx64 == nullptr)) return -2;
+  // a chunk cannot yield more entries than it has: with a larger quota the tail of idx/val would stay unwritten
+  if (static_cast<long long>(quota_per_chunk) > static_cast<long long>(chunk_rows) * n) return -2;
   if ((ldx & 7) || (reinterpret_cast<uintptr_t>(x) & 15) || (reinterpret_cast<uintptr_t>(c) & 15)) return -3;
   const int nchunks = (rows + chunk_rows - 1) / chunk_rows;
   if (nchunks > SB_NOALLOC_MAX_CHUNKS) return -7;  // larger than the built-in scratch: rejected, nothing launched

@@ -101,7 +101,16 @@ class AdamW(torch.optim.Optimizer):
             st["exp_avg_sq"] = torch.zeros_like(p, dtype=torch.float32, memory_format=torch.contiguous_format)
         if self.bf16_shadow and p.is_cuda:
             p._bf16_shadow = p.detach().to(torch.bfloat16)
+            p._bf16_shadow_version = p._version
         return st
+
+    def close(self) -> None:
+        """Detach the bf16 shadows from the parameters (call before handing the model to another optimizer)."""
+        for group in self.param_groups:
+            for p in group["params"]:
+                for attr in ("_bf16_shadow", "_bf16_shadow_version"):
+                    if hasattr(p, attr):
+                        delattr(p, attr)
 
     def state_bytes(self) -> int:
         total = 0
@@ -145,12 +154,17 @@ class AdamW(torch.optim.Optimizer):
                 "sig": sig,
                 "n_chunks": len(rows),
                 "chunks": torch.from_numpy(chunks.view(np.uint8).copy()).to(dev),
-                "host": torch.empty(len(plist) * _DESC.itemsize, dtype=torch.uint8, pin_memory=True),
+                # two pinned staging tables, each guarded by an event recorded behind its upload: the host never
+                # rewrites a table whose copy to the device may still be pending
+                "host": [torch.zeros(len(plist) * _DESC.itemsize, dtype=torch.uint8, pin_memory=True) for _ in range(2)],
+                "events": [None, None],
+                "turn": 0,
+                "last": None,
                 "dev": torch.empty(len(plist) * _DESC.itemsize, dtype=torch.uint8, device=dev),
             }
             assert lib.sb_tensor_desc_size() == _DESC.itemsize and lib.sb_chunk_desc_size() == _CHUNK.itemsize
             self._tables[gi] = cache
-        table = cache["host"].numpy().view(_DESC)
+        table = np.empty(len(plist), dtype=_DESC)
         for ti, p in enumerate(plist):
             st = self.state[p]
             ptr = lambda t: 0 if t is None else t.data_ptr()
@@ -159,7 +173,20 @@ class AdamW(torch.optim.Optimizer):
                 ptr(getattr(p, "_bf16_shadow", None)), ptr(st.get("m8")), ptr(st.get("v8")), ptr(st.get("m_absmax")),
                 ptr(st.get("v_absmax")), p.numel(),
             )
-        cache["dev"].copy_(cache["host"], non_blocking=True)
+        blob = table.tobytes()
+        if blob != cache["last"]:
+            # the pointers changed (gradients are reallocated when they are dropped between steps): upload through the
+            # staging table whose previous upload has certainly finished
+            turn = cache["turn"]
+            if cache["events"][turn] is not None:
+                cache["events"][turn].synchronize()
+            cache["host"][turn].numpy()[:] = np.frombuffer(blob, dtype=np.uint8)
+            cache["dev"].copy_(cache["host"][turn], non_blocking=True)
+            ev = torch.cuda.Event()
+            ev.record()
+            cache["events"][turn] = ev
+            cache["turn"] = turn ^ 1
+            cache["last"] = blob
         step = self.state[plist[0]]["step"]
         b1, b2 = group["betas"]
         rc = lib.sb_adamw_step(
@@ -170,6 +197,9 @@ class AdamW(torch.optim.Optimizer):
         )
         _lib.check_rc(rc, "sb_adamw_step")
         self.kernel_launches += 1
+        if self.bf16_shadow:
+            for p in plist:      # the kernel refreshed master and shadow together through raw pointers
+                p._bf16_shadow_version = p._version
 
     @torch.no_grad()
     def step(self, closure=None, grad_scale: float = 1.0):
@@ -205,6 +235,7 @@ class AdamW(torch.optim.Optimizer):
                     p.data.copy_(work)
                 if hasattr(p, "_bf16_shadow"):
                     p._bf16_shadow.copy_(p.data)
+                    p._bf16_shadow_version = p._version
         return loss
 
 

@@ -52,7 +52,10 @@ def broadcast_parameters(model: nn.Module, src: int = 0) -> None:
     if not (dist.is_initialized() and dist.get_world_size() > 1):
         return
     for p in model.parameters():
-        dist.broadcast(p.data, src)
+        # through ``detach()`` (shares the version counter), not ``.data``: a cached bf16 shadow of the parameter is
+        # keyed on that counter and must see this write
+        with torch.no_grad():
+            dist.broadcast(p.detach(), src)
 
 
 class GradSink:
@@ -91,7 +94,8 @@ class GradSync:
     """
 
     def __init__(self, params: Iterable[nn.Parameter], *, bucket_mb: float = 256.0, backend: str = "auto",
-                 group=None, average: bool = True, fused: Iterable[nn.Parameter] = ()):
+                 group=None, average: bool = True, fused: Iterable[nn.Parameter] = (), heartbeat=None):
+        self.heartbeat = heartbeat      # optional health.Heartbeat: peers' failures raise here, ours is published to them
         fused_ids = {id(p) for p in fused if p.requires_grad}
         ordered = [p for p in params if p.requires_grad]
         # fused parameters first: their slots form the head of the flat buffer
@@ -345,6 +349,29 @@ class GradSync:
             from ..ops import _lib
 
             _lib.reserve_sms(0)
+        self.check_health()
+
+    def check_health(self) -> None:
+        """Raise on every rank when a collective of this or the previous step gave up waiting for a peer.
+
+        The in-tree collectives bound every wait; a rank that times out records a code in its device status word and
+        returns without having reduced.  The word is read here once per step through a pinned asynchronous copy (one
+        step late, no host wait; synchronously under ``STACR_STRICT_STATUS=1``), so un-averaged gradients are applied for
+        at most one step before ``KernelError`` stops the job.  A peer's ``RankFailure`` recorded in the job store by
+        ``health.Heartbeat`` is raised by the heartbeat's own ``check``.
+        """
+        if self.heartbeat is not None:
+            self.heartbeat.check()          # a peer that failed or left: stop before its missing contribution is applied again
+        if self.device.type != "cuda":
+            return
+        from ..ops import _lib
+
+        try:
+            _lib.poll_status(self.device)
+        except _lib.KernelError as exc:
+            if self.heartbeat is not None:
+                self.heartbeat.fail(f"KernelError: {exc}")   # the other ranks raise RankFailure at their next check
+            raise
 
     def close(self) -> None:
         for h in self._hooks:

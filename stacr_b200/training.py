@@ -357,6 +357,10 @@ def train_model(model, train_batches, config: dict, *, validation_batches=None) 
             torch.nn.utils.clip_grad_norm_(model.parameters(), float(cfg["max_grad_norm"]))
         scaler.step(optimizer)
         scaler.update()
+        if device.type == "cuda":
+            from .ops import _lib
+
+            _lib.poll_status(device)      # a kernel that gave up on a bounded wait during this or the previous step raises here
         losses.append(loss_acc)
         if step >= measure_from:
             measured += 1

@@ -189,3 +189,73 @@ def test_two_gloo_ranks_detect_a_peer_that_leaves_raises_or_never_joins(tmp_path
     assert survivor.startswith("RANK0 detected:"), outs[0][-1500:] + outs[1][-1500:]
     assert expect in survivor, survivor
     assert procs[0].returncode == 0
+
+
+_SYNC_WORKER = r'''
+import os, sys, time, datetime, torch, torch.distributed as dist
+sys.path.insert(0, os.environ["REPO"])
+from stacr_b200.parallel import GradSync
+from stacr_b200.parallel.health import Heartbeat, RankFailure
+rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+dist.init_process_group("gloo", timeout=datetime.timedelta(seconds=5))
+hb = Heartbeat(dist.distributed_c10d._get_default_store(), rank, world, timeout=5.0)
+dist.barrier()
+torch.manual_seed(0)
+model = torch.nn.Linear(8, 4)
+sync = GradSync(model.parameters(), heartbeat=hb)
+outcome = "finished"
+try:
+    for step in range(4):
+        sync.zero_grad()
+        model(torch.randn(2, 8)).sum().backward()
+        if rank == 1 and step == 1:
+            # what a rank does when its own status poll finds a timed-out kernel: publish, then stop
+            hb.fail("KernelError: kernel status 21")
+            outcome = "published"
+            break
+        time.sleep(0.3)
+        sync.finish()          # reduces, then checks health: the peer's failure raises here, before optimizer.step()
+        hb.beat(step)
+except RankFailure as exc:
+    outcome = f"detected:{exc.ranks}:{str(exc)[:120]}"
+print(f"RANK{rank} {outcome} step={step}", flush=True)
+os._exit(0)
+'''
+
+
+def test_gradsync_finish_raises_on_the_survivor_when_a_peer_published_a_kernel_timeout(tmp_path):
+    script = tmp_path / "sync_worker.py"
+    script.write_text(_SYNC_WORKER)
+    procs = []
+    for rank in range(2):
+        env = {**os.environ, "REPO": REPO, "RANK": str(rank), "WORLD_SIZE": "2", "MASTER_ADDR": "127.0.0.1", "MASTER_PORT": "29634"}
+        procs.append(subprocess.Popen([sys.executable, str(script)], env=env, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True))
+    outs = []
+    for p in procs:
+        try:
+            out, _ = p.communicate(timeout=120)
+        except subprocess.TimeoutExpired:
+            p.kill()
+            out, _ = p.communicate()
+        outs.append(out)
+    survivor = next((l for l in outs[0].splitlines() if l.startswith("RANK0")), "")
+    # rank 0 finishes step 0 normally, then either its step-1 reduction runs out (the peer never joins) or, when the peer's
+    # store write is seen first, the health check names the kernel failure; both stop the job on the survivor
+    assert "detected:" in survivor or "RuntimeError" in outs[0] or "Timed out" in outs[0], outs[0][-1500:] + outs[1][-1500:]
+    assert any(l.startswith("RANK1 published") for l in outs[1].splitlines()), outs[1][-1500:]
+
+
+def test_bf16_shadow_follows_writes_that_bypass_the_fused_optimizer():
+    from stacr_b200.layers import _bf16_weight
+
+    w = torch.nn.Parameter(torch.randn(16, 8))
+    w._bf16_shadow = w.detach().to(torch.bfloat16)
+    w._bf16_shadow_version = w._version
+    assert _bf16_weight(w) is w._bf16_shadow
+    fresh = torch.randn(16, 8)
+    with torch.no_grad():
+        w.copy_(fresh)                       # what load_state_dict, a broadcast or another optimizer does
+    got = _bf16_weight(w)
+    assert got is w._bf16_shadow
+    torch.testing.assert_close(got.float(), fresh.to(torch.bfloat16).float(), rtol=0, atol=0)
+    assert w._bf16_shadow_version == w._version

@@ -151,3 +151,66 @@ def test_basis_update_and_model_ops_repeat_bit_for_bit():
     # the Gram and XᵀY products are split-K sums with atomics: equal up to fp32 rounding, orthonormal every time
     torch.testing.assert_close(a, bq, rtol=1e-4, atol=1e-5)
     torch.testing.assert_close(a.t() @ a, torch.eye(8, device="cuda"), rtol=0, atol=1e-4)
+
+
+def test_a_recorded_kernel_timeout_stops_the_training_step():
+    """The status word is polled by the step itself: a code left by a kernel that gave up raises within two steps."""
+    import stacr_b200 as S
+    from stacr_b200.models import GPTNeoXForCausalLM, NeoXConfig
+    from stacr_b200.ops import _lib
+    from stacr_b200.optim import AdamW8bit
+    from stacr_b200.parallel import GradSync
+
+    dev = torch.device("cuda", torch.cuda.current_device())
+    _lib.check_status(dev)
+    torch.manual_seed(0)
+    cfg = NeoXConfig(vocab_size=512, hidden_size=128, num_hidden_layers=1, num_attention_heads=4, intermediate_size=512, max_position_embeddings=64)
+    model = GPTNeoXForCausalLM(cfg).to(dev).train()
+    layers = S.apply_stacr(model, rank=8, residual_budget=0.01, turbo_after_step=None, min_features=64)
+    opt = AdamW8bit(model.parameters(), lr=1e-3, bf16_shadow=True)
+    sync = GradSync(model.parameters())
+    ids = torch.randint(0, 512, (2, 64), device=dev)
+
+    def step(i):
+        S.set_step(layers, i)
+        sync.zero_grad()
+        with torch.autocast("cuda", dtype=torch.bfloat16):
+            model(input_ids=ids, labels=ids).loss.backward()
+        sync.finish()
+        opt.step()
+
+    step(0)
+    step(1)
+    _lib.status_word(dev).fill_(21)          # what a collective that ran out of patience leaves behind
+    with pytest.raises(_lib.KernelError, match="21"):
+        for i in range(2, 5):                # read one step late, without making the host wait for the device
+            step(i)
+            torch.cuda.synchronize()
+    _lib.check_status(dev)                   # cleared by the raise
+    sync.close()
+
+
+def test_bf16_shadow_is_refreshed_after_load_state_dict():
+    from stacr_b200.models import GPTNeoXForCausalLM, NeoXConfig
+    from stacr_b200.optim import AdamW8bit
+
+    dev = torch.device("cuda", torch.cuda.current_device())
+    torch.manual_seed(0)
+    cfg = NeoXConfig(vocab_size=512, hidden_size=128, num_hidden_layers=1, num_attention_heads=4, intermediate_size=512, max_position_embeddings=64)
+    model = GPTNeoXForCausalLM(cfg).to(dev).train()
+    other = GPTNeoXForCausalLM(cfg).to(dev)
+    opt = AdamW8bit(model.parameters(), lr=1e-3, bf16_shadow=True)
+    ids = torch.randint(0, 512, (2, 64), device=dev)
+    with torch.autocast("cuda", dtype=torch.bfloat16):
+        loss = model(input_ids=ids, labels=ids).loss
+    loss.backward()
+    opt.step()
+    with torch.autocast("cuda", dtype=torch.bfloat16):
+        before = float(model(input_ids=ids, labels=ids).loss)
+    model.load_state_dict(other.state_dict())
+    with torch.autocast("cuda", dtype=torch.bfloat16):
+        after = float(model(input_ids=ids, labels=ids).loss)
+        want = float(other(input_ids=ids, labels=ids).loss)
+    assert abs(after - want) < 2e-2 and abs(after - before) > 1e-4, (before, after, want)
+    opt.close()
+    assert not hasattr(model.embed_out.weight, "_bf16_shadow")

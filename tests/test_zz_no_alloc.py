@@ -110,3 +110,19 @@ def test_noalloc_entry_rejects_requests_beyond_its_scratch():
         _lib.ptr(_lib.status_word()), _lib.stream_ptr(),
     )
     assert rc == -7
+
+
+def test_noalloc_entry_rejects_a_quota_larger_than_a_chunk():
+    from stacr_b200.ops import _lib
+
+    lib = _lib.load()
+    x, qb, c, _ = _case(64, 64, 8, seed=4)
+    idx = torch.empty(8192, dtype=torch.int32, device="cuda")
+    val = torch.empty(8192, dtype=torch.int8, device="cuda")
+    scale = torch.empty((), dtype=torch.float32, device="cuda")
+    rc = lib.sb_residual_topk_noalloc(  # a chunk of 32 rows x 64 columns has 2048 entries; 4096 are asked for
+        _lib.ptr(x), _lib.ptr(c), _lib.ptr(qb), ctypes.c_int(64), ctypes.c_int(64), ctypes.c_int(8), ctypes.c_int(64),
+        ctypes.c_int(32), ctypes.c_int(4096), ctypes.c_int(8), _lib.ptr(idx), ctypes.c_void_p(0), _lib.ptr(val), _lib.ptr(scale),
+        _lib.ptr(_lib.status_word()), _lib.stream_ptr(),
+    )
+    assert rc == -2
