@@ -365,7 +365,9 @@ class STACRFunction(torch.autograd.Function):
                         ready()          # the slot is the gradient: nothing goes back through autograd (it would be cloned)
                         gw = None
             if ctx.needs_input_grad[2]:
-                gb = stacr_ops.colsum(ga).to(ctx.bias_dtype)
+                from .ops.nn_ops import bias_grad
+
+                gb = bias_grad(ga).to(ctx.bias_dtype)
             return (gx, gw, gb) + (None,) * (ctx.n_args - 3)
         with torch.autocast(device_type=g2d.device.type, enabled=False):
             if ctx.needs_input_grad[0]:

@@ -192,12 +192,28 @@ __global__ void __launch_bounds__(256) layernorm_bwd_params_kernel(const __nv_bf
 }
 
 // ---------------------------------------------------------------------------- GELU
+// The exact (erf) form is evaluated through the normal tail Phi(-|x|) = 0.5 * P(t) * exp(-x^2 / 2), t = 1 / (1 + p |x| / sqrt 2),
+// with the five-term rational fit of Abramowitz & Stegun 7.1.26 (absolute error 1.5e-7, far below bf16 resolution; the
+// tail is formed without cancellation, so large negative inputs keep their relative accuracy).  The exponential is the
+// one the derivative needs for the density, so forward costs one ex2 and one reciprocal and backward no more than that:
+// with the library erff the two kernels were bound by instruction issue, not by memory.
+struct GeluParts { float cdf, e; };
+__device__ __forceinline__ GeluParts gelu_parts(float x) {
+  const float ax = fabsf(x);
+  const float t = __frcp_rn(fmaf(0.3275911f * 0.70710678118654752f, ax, 1.f));
+  const float poly = t * fmaf(t, fmaf(t, fmaf(t, fmaf(t, 1.061405429f, -1.453152027f), 1.421413741f), -0.284496736f), 0.254829592f);
+  GeluParts g;
+  g.e = __expf(-0.5f * x * x);
+  const float tail = 0.5f * poly * g.e;
+  g.cdf = x >= 0.f ? 1.f - tail : tail;
+  return g;
+}
 __device__ __forceinline__ float gelu_f(float x, bool tanh_form) {
   if (tanh_form) {
     const float u = 0.7978845608028654f * (x + 0.044715f * x * x * x);
     return 0.5f * x * (1.f + tanhf(u));
   }
-  return 0.5f * x * (1.f + erff(x * 0.7071067811865476f));
+  return x * gelu_parts(x).cdf;
 }
 __device__ __forceinline__ float gelu_grad_f(float x, bool tanh_form) {
   if (tanh_form) {
@@ -206,30 +222,103 @@ __device__ __forceinline__ float gelu_grad_f(float x, bool tanh_form) {
     const float du = 0.7978845608028654f * (1.f + 3.f * 0.044715f * x * x);
     return 0.5f * (1.f + t) + 0.5f * x * (1.f - t * t) * du;
   }
-  const float cdf = 0.5f * (1.f + erff(x * 0.7071067811865476f));
-  const float pdf = 0.3989422804014327f * __expf(-0.5f * x * x);
-  return cdf + x * pdf;
+  const GeluParts g = gelu_parts(x);
+  return fmaf(x * 0.3989422804014327f, g.e, g.cdf);
 }
 
+constexpr int GELU_UNROLL = 4;  // independent 16-byte loads in flight per thread and operand
+
 __global__ void __launch_bounds__(256) gelu_fwd_kernel(const uint4* __restrict__ x, uint4* __restrict__ y, size_t nvec, int tanh_form) {
-  for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < nvec; i += static_cast<size_t>(gridDim.x) * blockDim.x) {
-    float v[8];
-    unpack8(__ldg(x + i), v);
+  const size_t stride = static_cast<size_t>(gridDim.x) * blockDim.x * GELU_UNROLL;
+  for (size_t i0 = static_cast<size_t>(blockIdx.x) * blockDim.x * GELU_UNROLL + threadIdx.x; i0 < nvec; i0 += stride) {
+    uint4 raw[GELU_UNROLL];
 #pragma unroll
-    for (int j = 0; j < 8; ++j) v[j] = gelu_f(v[j], tanh_form);
-    y[i] = pack8(v);
+    for (int u = 0; u < GELU_UNROLL; ++u) {
+      const size_t i = i0 + static_cast<size_t>(u) * blockDim.x;
+      if (i < nvec) raw[u] = __ldg(x + i);
+    }
+#pragma unroll
+    for (int u = 0; u < GELU_UNROLL; ++u) {
+      const size_t i = i0 + static_cast<size_t>(u) * blockDim.x;
+      if (i < nvec) {
+        float v[8];
+        unpack8(raw[u], v);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) v[j] = gelu_f(v[j], tanh_form);
+        y[i] = pack8(v);
+      }
+    }
   }
 }
 __global__ void __launch_bounds__(256) gelu_bwd_kernel(const uint4* __restrict__ dy, const uint4* __restrict__ x, uint4* __restrict__ dx,
                                                        size_t nvec, int tanh_form) {
-  for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < nvec; i += static_cast<size_t>(gridDim.x) * blockDim.x) {
-    float v[8], d[8];
-    unpack8(__ldg(x + i), v);
-    unpack8(__ldg(dy + i), d);
+  const size_t stride = static_cast<size_t>(gridDim.x) * blockDim.x * GELU_UNROLL;
+  for (size_t i0 = static_cast<size_t>(blockIdx.x) * blockDim.x * GELU_UNROLL + threadIdx.x; i0 < nvec; i0 += stride) {
+    uint4 rx[GELU_UNROLL], rd[GELU_UNROLL];
 #pragma unroll
-    for (int j = 0; j < 8; ++j) v[j] = d[j] * gelu_grad_f(v[j], tanh_form);
-    dx[i] = pack8(v);
+    for (int u = 0; u < GELU_UNROLL; ++u) {
+      const size_t i = i0 + static_cast<size_t>(u) * blockDim.x;
+      if (i < nvec) {
+        rx[u] = __ldg(x + i);
+        rd[u] = __ldg(dy + i);
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < GELU_UNROLL; ++u) {
+      const size_t i = i0 + static_cast<size_t>(u) * blockDim.x;
+      if (i < nvec) {
+        float v[8], d[8];
+        unpack8(rx[u], v);
+        unpack8(rd[u], d);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) v[j] = d[j] * gelu_grad_f(v[j], tanh_form);
+        dx[i] = pack8(v);
+      }
+    }
   }
+}
+
+// The same derivative on a [rows, n] matrix (n % 8 == 0), which also leaves the column sums of the bf16 result in
+// `colsum` (fp32, zeroed by the caller): the gradient of the bias of the linear layer that fed the activation, for which
+// a separate pass over the freshly written matrix would otherwise be made.  A thread owns 8 consecutive columns over a
+// slab of rows; its partial sums stay in registers and leave as 8 atomics per slab.
+__global__ void __launch_bounds__(256) gelu_bwd_colsum_kernel(const uint4* __restrict__ dy, const uint4* __restrict__ x, uint4* __restrict__ dx,
+                                                              int rows, int nvecs, int slab, int tanh_form, float* __restrict__ colsum) {
+  const int cv = blockIdx.x * blockDim.x + threadIdx.x;
+  if (cv >= nvecs) return;
+  const int r0 = blockIdx.y * slab, r1 = min(rows, r0 + slab);
+  float acc[8];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+  for (int row = r0; row < r1; row += GELU_UNROLL) {
+    uint4 rx[GELU_UNROLL], rd[GELU_UNROLL];
+#pragma unroll
+    for (int u = 0; u < GELU_UNROLL; ++u) {
+      if (row + u < r1) {
+        const size_t i = static_cast<size_t>(row + u) * nvecs + cv;
+        rx[u] = __ldg(x + i);
+        rd[u] = __ldg(dy + i);
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < GELU_UNROLL; ++u) {
+      if (row + u < r1) {
+        float v[8], d[8];
+        unpack8(rx[u], v);
+        unpack8(rd[u], d);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) v[j] = d[j] * gelu_grad_f(v[j], tanh_form);
+        const uint4 packed = pack8(v);
+        dx[static_cast<size_t>(row + u) * nvecs + cv] = packed;
+        float o[8];
+        unpack8(packed, o);  // sum what was stored (the rounded values), as a later pass over the stored matrix would
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[j] += o[j];
+      }
+    }
+  }
+#pragma unroll
+  for (int j = 0; j < 8; ++j) atomicAdd(colsum + static_cast<size_t>(cv) * 8 + j, acc[j]);
 }
 
 // ---------------------------------------------------------------------------- cross-entropy
@@ -442,13 +531,17 @@ extern "C" int sb_layernorm_bwd(const void* dy, const void* x, const float* gamm
   return -3;
 }
 
+static inline unsigned gelu_blocks(size_t nvec, int sms) {
+  size_t blocks = (nvec + 256 * sb::GELU_UNROLL - 1) / (256 * sb::GELU_UNROLL);
+  if (blocks > static_cast<size_t>(sms) * 8) blocks = static_cast<size_t>(sms) * 8;
+  return static_cast<unsigned>(blocks < 1 ? 1 : blocks);
+}
+
 extern "C" int sb_gelu_fwd(const void* x, void* y, long long numel, int tanh_form, int sms, void* stream) {
   if (numel <= 0) return 0;
   if (numel % 8) return -2;
   const size_t nvec = static_cast<size_t>(numel / 8);
-  size_t blocks = (nvec + 255) / 256;
-  if (blocks > static_cast<size_t>(sms) * 16) blocks = static_cast<size_t>(sms) * 16;
-  sb::gelu_fwd_kernel<<<static_cast<unsigned>(blocks), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+  sb::gelu_fwd_kernel<<<gelu_blocks(nvec, sms), 256, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const uint4*>(x), static_cast<uint4*>(y), nvec, tanh_form);
   return static_cast<int>(cudaGetLastError());
 }
@@ -457,10 +550,26 @@ extern "C" int sb_gelu_bwd(const void* dy, const void* x, void* dx, long long nu
   if (numel <= 0) return 0;
   if (numel % 8) return -2;
   const size_t nvec = static_cast<size_t>(numel / 8);
-  size_t blocks = (nvec + 255) / 256;
-  if (blocks > static_cast<size_t>(sms) * 16) blocks = static_cast<size_t>(sms) * 16;
-  sb::gelu_bwd_kernel<<<static_cast<unsigned>(blocks), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+  sb::gelu_bwd_kernel<<<gelu_blocks(nvec, sms), 256, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const uint4*>(dy), static_cast<const uint4*>(x), static_cast<uint4*>(dx), nvec, tanh_form);
+  return static_cast<int>(cudaGetLastError());
+}
+
+// dx = dy * gelu'(x) on contiguous bf16 [rows, n] (n % 8 == 0) and colsum[n] += column sums of dx (fp32; the caller zeroes it).
+extern "C" int sb_gelu_bwd_colsum(const void* dy, const void* x, void* dx, int rows, int n, int tanh_form, float* colsum, int sms,
+                                  void* stream) {
+  if (rows <= 0 || n <= 0) return 0;
+  if (n % 8) return -2;
+  const int nvecs = n / 8;
+  const int col_blocks = (nvecs + 255) / 256;
+  int slabs = (sms * 8 + col_blocks - 1) / col_blocks;
+  if (slabs > (rows + 7) / 8) slabs = (rows + 7) / 8;   // at least 8 rows per slab: 8 atomics pay for 64 elements or more
+  if (slabs < 1) slabs = 1;
+  if (slabs > 65535) slabs = 65535;
+  const int slab = (rows + slabs - 1) / slabs;
+  dim3 grid(col_blocks, (rows + slab - 1) / slab);
+  sb::gelu_bwd_colsum_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const uint4*>(dy), static_cast<const uint4*>(x), static_cast<uint4*>(dx), rows, nvecs, slab, tanh_form, colsum);
   return static_cast<int>(cudaGetLastError());
 }
 

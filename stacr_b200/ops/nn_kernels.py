@@ -57,6 +57,19 @@ def gelu_bwd(dy: torch.Tensor, x: torch.Tensor, tanh_form: bool) -> torch.Tensor
     return dx
 
 
+def gelu_bwd_colsum(dy: torch.Tensor, x: torch.Tensor, tanh_form: bool):
+    """``(dx, column sums of dx)`` for contiguous bf16 ``[..., n]`` with ``n % 8 == 0``; the sums are fp32 ``[n]``."""
+    n = x.shape[-1]
+    rows = x.numel() // n
+    dx = torch.empty_like(x)
+    sums = torch.zeros(n, dtype=torch.float32, device=x.device)
+    rc = _lib.load().sb_gelu_bwd_colsum(_lib.ptr(dy), _lib.ptr(x), _lib.ptr(dx), c_int(rows), c_int(n), c_int(int(tanh_form)), _lib.ptr(sums),
+                                        c_int(_lib.sm_count(x.device)), _lib.stream_ptr())
+    _lib.check_rc(rc, "sb_gelu_bwd_colsum")
+    _lib.count(1)
+    return dx, sums
+
+
 def cross_entropy_fwd(logits: torch.Tensor, target: torch.Tensor):
     """Mean loss over valid rows; returns ``(loss, target_int64, row_lse, inv_valid)`` for :func:`cross_entropy_bwd`."""
     rows, v = logits.shape

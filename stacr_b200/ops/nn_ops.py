@@ -46,6 +46,58 @@ def layer_norm(x, weight, bias, eps: float = 1e-5):
     return F.layer_norm(x, (x.shape[-1],), weight, bias, eps)
 
 
+# ------------------------------------------------------------------------------ column sums handed from producer to consumer
+class _ColumnSums:
+    """Column sums of a gradient matrix that some kernel produced as a by-product, offered to whoever needs them next.
+
+    The backward of an activation writes ``dX`` and can sum its columns on the way; the backward of the linear layer that
+    fed the activation runs next and needs exactly those sums for its bias gradient.  The two are separate autograd nodes,
+    so the sums travel through this one-entry mailbox keyed by the matrix's storage address, shape and version.  The
+    mailbox keeps the matrix itself alive while its entry exists, so the address cannot be recycled for another tensor
+    and a match is never a coincidence.  An entry offered by a producer is dropped when it is taken; an entry made by
+    ``bias_grad`` itself stays until the next offer, so that two layers that receive the same gradient tensor (the
+    attention output projection and the MLP output projection of a parallel-residual block) sum it once.  A lookup that
+    does not match leaves the caller to compute the sums.
+    """
+
+    def __init__(self):
+        self.clear()
+
+    @staticmethod
+    def _key(t: torch.Tensor, cols: int):
+        return (t.data_ptr(), t.numel(), cols, t._version, t.device.index)
+
+    def offer(self, matrix: torch.Tensor, sums: torch.Tensor, single_use: bool) -> None:
+        self.key, self.sums, self.matrix, self.single_use = self._key(matrix, sums.numel()), sums, matrix, single_use
+
+    def take(self, matrix: torch.Tensor, cols: int):
+        if self.key is None or self.key != self._key(matrix, cols):
+            return None
+        sums = self.sums
+        if self.single_use:
+            self.clear()
+        return sums
+
+    def clear(self) -> None:
+        self.key = self.sums = self.matrix = None
+        self.single_use = False
+
+
+column_sums = _ColumnSums()
+
+
+def bias_grad(g2d: torch.Tensor) -> torch.Tensor:
+    """fp32 column sums of a bf16 gradient matrix ``[rows, out]``: taken from the mailbox when its producer left them there."""
+    from . import stacr_ops
+
+    hit = column_sums.take(g2d, g2d.shape[1])
+    if hit is not None:
+        return hit
+    sums = stacr_ops.colsum(g2d)
+    column_sums.offer(g2d, sums, single_use=False)
+    return sums
+
+
 # ------------------------------------------------------------------------------ GELU
 class _GeluFn(torch.autograd.Function):
     @staticmethod
@@ -62,6 +114,10 @@ class _GeluFn(torch.autograd.Function):
         from . import nn_kernels
 
         (x,) = ctx.saved_tensors
+        if x.dim() >= 2 and x.shape[-1] % 8 == 0:
+            dx, sums = nn_kernels.gelu_bwd_colsum(dy.contiguous(), x, ctx.tanh_form)
+            column_sums.offer(dx, sums, single_use=True)      # the bias gradient of the projection that produced x
+            return dx, None
         return nn_kernels.gelu_bwd(dy.contiguous(), x, ctx.tanh_form), None
 
 
@@ -149,7 +205,7 @@ def linear_cross_entropy(hidden, weight, target, chunk: int = 0):
             return _PaddedHeadCEFn.apply(h, weight, t)
     else:
         def head(h, t):
-            return cross_entropy(F.linear(h, weight), t)
+            return cross_entropy(linear(h, weight), t)
     if not chunk or hidden.shape[0] <= chunk:
         return head(hidden, target)
     valid = (target != -100).sum().clamp_min(1)
@@ -165,11 +221,12 @@ def linear_cross_entropy(hidden, weight, target, chunk: int = 0):
 class _LinearFn(torch.autograd.Function):
     """``y = x W^T + b`` for a projection that is not compressed.
 
-    Forward and the input gradient are plain library GEMMs on bf16 operands (the bf16 copy of the weight is the shadow the
-    fused optimizer keeps current, when there is one).  The weight gradient is one in-tree GEMM ``dY^T X`` with fp32
-    accumulation *and fp32 output*: under autocast the library path produces a bf16 ``dW``, casts it to fp32 and, with a
-    flat gradient buffer, copies it into its slot; here the kernel writes fp32 once, straight into the slot when a gradient
-    synchroniser has lent one (``weight._sb_grad_out``).
+    All three products run on the in-tree tcgen05 GEMM on bf16 operands (the bf16 copy of the weight is the shadow the
+    fused optimizer keeps current, when there is one): forward ``X W^T + b`` with the bias added in the epilogue, the input
+    gradient ``dY W`` reading ``W[out, in]`` as an MN-major operand (no transpose is materialised), and the weight gradient
+    ``dY^T X`` with fp32 accumulation *and fp32 output*: under autocast a library path produces a bf16 ``dW``, casts it to
+    fp32 and, with a flat gradient buffer, copies it into its slot; here the kernel writes fp32 once, straight into the
+    slot when a gradient synchroniser has lent one (``weight._sb_grad_out``).
     """
 
     @staticmethod
@@ -178,9 +235,11 @@ class _LinearFn(torch.autograd.Function):
         # (the fused-QKV rotary embedding modifies it in place)
         from ..layers import _bf16_weight
 
+        from .gemm import gemm
+
         xa = (x2d if x2d.dtype == torch.bfloat16 else x2d.to(torch.bfloat16)).contiguous()
-        wb = _bf16_weight(weight)
-        y = F.linear(xa, wb, None if bias is None else bias.detach().to(torch.bfloat16))
+        wb = _bf16_weight(weight).contiguous()
+        y = gemm(xa, wb, bias=None if bias is None else bias.detach().float().contiguous())
         ctx.save_for_backward(xa, weight)
         ctx.in_dtype, ctx.bias_dtype = x2d.dtype, None if bias is None else bias.dtype
         return y
@@ -196,7 +255,7 @@ class _LinearFn(torch.autograd.Function):
         g = (dy if dy.dtype == torch.bfloat16 else dy.to(torch.bfloat16)).contiguous()
         dx = dw = db = None
         if ctx.needs_input_grad[0]:
-            dx = torch.mm(g, _bf16_weight(weight)).to(ctx.in_dtype)
+            dx = gemm(g, _bf16_weight(weight).contiguous(), b_mn=True).to(ctx.in_dtype)
         if ctx.needs_input_grad[1]:
             slot = getattr(weight, "_sb_grad_out", None) if getattr(weight, "_sb_grad_fresh", False) else None
             if slot is not None and slot.dtype == torch.float32 and weight.dtype == torch.float32:
@@ -211,13 +270,14 @@ class _LinearFn(torch.autograd.Function):
             elif dw.dtype != weight.dtype:
                 dw = dw.to(weight.dtype)
         if ctx.bias_dtype is not None and ctx.needs_input_grad[2]:
-            db = stacr_ops.colsum(g).to(ctx.bias_dtype)
+            db = bias_grad(g).to(ctx.bias_dtype)
         return dx, dw, db
 
 
 def linear(x, weight, bias=None):
     """Linear map with the fp32-direct weight gradient on a B200 when the activations are (or autocast makes them) bf16."""
     usable = (x.is_cuda and weight.is_cuda and weight.dim() == 2 and x.shape[-1] % 8 == 0 and weight.shape[0] % 8 == 0 and x.numel() > 0
+              and _lib.available()
               and (x.dtype == torch.bfloat16 or (torch.is_autocast_enabled() and torch.get_autocast_dtype("cuda") == torch.bfloat16))
               and torch.is_grad_enabled() and weight.requires_grad)
     if usable:

@@ -43,6 +43,54 @@ def test_gelu_forward_backward(form):
     torch.testing.assert_close(x.grad.float(), xr.grad, rtol=2e-2, atol=2e-2)
 
 
+@pytest.mark.parametrize("rows,n,form", [(513, 1024, "none"), (37, 4104, "tanh"), (3, 8, "none"), (4096, 2048, "none")])
+def test_gelu_backward_leaves_the_column_sums_of_its_result(rows, n, form):
+    """The fused derivative + column-sum kernel against fp32: the sums are those of the stored (bf16) result."""
+    from stacr_b200.ops import nn_kernels
+
+    x = (2 * torch.randn(rows, n, device="cuda")).bfloat16()
+    dy = torch.randn(rows, n, device="cuda").bfloat16()
+    dx, sums = nn_kernels.gelu_bwd_colsum(dy, x, form == "tanh")
+    xr = x.float().requires_grad_(True)
+    F.gelu(xr, approximate=form).backward(dy.float())
+    torch.testing.assert_close(dx.float(), xr.grad, rtol=2e-2, atol=2e-2)
+    torch.testing.assert_close(sums, dx.float().sum(0), rtol=1e-4, atol=1e-3 * max(1.0, rows ** 0.5))
+    plain = nn_kernels.gelu_bwd(dy, x, form == "tanh")
+    assert torch.equal(plain, dx)
+
+
+def test_bias_gradient_of_a_linear_feeding_gelu_comes_from_the_activation_backward():
+    """Linear -> GELU -> Linear: the first layer's bias gradient is the by-product of the activation's backward, and equals autograd's."""
+    from stacr_b200.models.common import GELU, Linear
+    from stacr_b200.ops import nn_ops, stacr_ops
+
+    torch.manual_seed(0)
+    a, act, b = Linear(256, 512).cuda(), GELU("none"), Linear(512, 256).cuda()
+    x = torch.randn(4, 96, 256, device="cuda")
+    calls = {"n": 0}
+    real = stacr_ops.colsum
+
+    def counting(t):
+        calls["n"] += 1
+        return real(t)
+
+    stacr_ops.colsum = counting
+    try:
+        with torch.autocast("cuda", dtype=torch.bfloat16):
+            y = b(act(a(x)))
+        y.float().square().mean().backward()
+    finally:
+        stacr_ops.colsum = real
+    assert calls["n"] == 1                      # only the last layer summed its gradient matrix itself
+    ra, rb = torch.nn.Linear(256, 512).cuda(), torch.nn.Linear(512, 256).cuda()
+    ra.load_state_dict(a.state_dict())
+    rb.load_state_dict(b.state_dict())
+    rb(F.gelu(ra(x))).square().mean().backward()
+    for got, want in ((a.bias.grad, ra.bias.grad), (b.bias.grad, rb.bias.grad), (a.weight.grad, ra.weight.grad)):
+        assert float((got - want).norm() / want.norm()) < 3e-2
+    assert nn_ops.column_sums.single_use is False
+
+
 @pytest.mark.parametrize("rows,v", [(515, 50304), (252, 1024), (7, 8)])
 def test_cross_entropy_loss_and_gradient(rows, v):
     """The small vocabularies leave most threads of a row's CTA without an element (their running max stays -inf)."""
