@@ -46,6 +46,7 @@ struct SelectParams {
   void* out_val;            // bf16 or int8
   float* out_scale;         // scalar, written by the scan kernel
   int* status;
+  const int* gate;          // optional [nchunks]: the exact passes skip chunks whose entry is 0 (NULL = run them all)
 };
 
 __device__ __forceinline__ float bf16_bits_to_float(unsigned short b) {
@@ -186,8 +187,9 @@ __global__ void __launch_bounds__(512, 1) residual_hist_kernel(const SelectParam
   constexpr int CPT = 64 / RP;
   extern __shared__ unsigned int sh_hist[];
   float* s_c = reinterpret_cast<float*>(sh_hist + NBINS);
-  for (int b = threadIdx.x; b < NBINS; b += blockDim.x) sh_hist[b] = 0;
   const Slab s = slab_of(p);
+  if (p.gate && !p.gate[s.chunk]) return;
+  for (int b = threadIdx.x; b < NBINS; b += blockDim.x) sh_hist[b] = 0;
   const int ct = threadIdx.x % ctn, lane_row = threadIdx.x / ctn;
   for (int sb0 = s.row0; sb0 < s.row1; sb0 += CS_ROWS) {
     const int sb1 = min(s.row1, sb0 + CS_ROWS);
@@ -234,6 +236,7 @@ __global__ void __launch_bounds__(1024) residual_scan_kernel(const SelectParams 
   __shared__ unsigned int part[1024];
   __shared__ int s_maxbin;
   const int chunk = blockIdx.x;
+  if (p.gate && !p.gate[chunk]) return;
   const unsigned int* gh = p.hist + static_cast<size_t>(chunk) * NBINS;
   const int t = threadIdx.x;
   constexpr int PER = NBINS / 1024;  // 32 bins per thread; thread t owns bins [t*PER, (t+1)*PER)
@@ -347,6 +350,7 @@ __global__ void __launch_bounds__(512, 1) residual_compact_kernel(const SelectPa
   long long* st_idx = st_idx_all + static_cast<size_t>(warp) * WARP_CAP;
   unsigned short* st_val = st_val_all + static_cast<size_t>(warp) * WARP_CAP;
   const Slab s = slab_of(p);
+  if (p.gate && !p.gate[s.chunk]) return;
   const int thr = p.thr_bin[s.chunk];
   const int need = p.thr_need[s.chunk];
   const int quota = p.quota[s.chunk];
@@ -523,6 +527,349 @@ __global__ void __launch_bounds__(256) residual_block_energy_kernel(const __nv_b
   }
 }
 
+// ------------------------------------------------------------------------------------------------
+// Sampled-threshold selection: the same exact top-k with one full pass over X instead of two.
+//
+//   A  histogram of a stratified 1/16 sample of the residual (of every row, one 64-column line in 16, the
+//      line offset rotating with the row, so that heavy rows and heavy columns are both represented); the
+//      last CTA of a chunk to finish turns it into a *candidate* bin t_lo below which, by the sample's
+//      estimate with a safety margin, none of the chunk's top-k entries lie;
+//   C  the full pass: every entry whose magnitude reaches t_lo is appended (index, bf16 bits) to the
+//      chunk's candidate list through per-warp staging, and counted in a second histogram; the last CTA of
+//      a chunk finds the exact threshold bin and tie count among the candidates and checks that the
+//      candidates really contain the top k (at least k of them at or above t_lo, list not overflowed);
+//   E  compaction of the candidate list (a few hundred thousand entries, not the matrix) with the
+//      quantisation fused, as in the exact compaction pass.
+//
+// A chunk whose check fails (an input the sample misjudged) is flagged, its first histogram is cleared,
+// and the exact two-pass kernels, launched behind E with that flag as their gate, redo that chunk; for
+// every other chunk they return at once.  The selection is therefore exact for every input; only its cost
+// depends on the sample being representative.
+// ------------------------------------------------------------------------------------------------
+constexpr int SAMPLE_STRIDE = 16;
+constexpr int SAMPLE_LINE = 64;
+constexpr int SCAN_T = 256;  // threads that take part in a tail scan (NBINS / SCAN_T bins each)
+
+struct Select2Params {
+  SelectParams base;
+  unsigned int* hist2;        // [nchunks, NBINS] histogram of the candidates, zeroed by the caller
+  int* cand_bin;              // [nchunks] t_lo
+  int* cand_count;            // [nchunks] candidates appended (may exceed the capacity: the excess was dropped)
+  int* fallback;              // [nchunks] 1 = redo this chunk with the exact passes
+  int* done_a;                // [nchunks] CTAs of pass A that have finished
+  int* done_c;                // [nchunks] CTAs of pass C that have finished
+  int* done_all;              // [1] CTAs of pass C that have finished, all chunks
+  int* gmax;                  // [1] largest magnitude key seen
+  const int* cand_off;        // [nchunks] first slot of the chunk's candidate list
+  const int* cand_cap;        // [nchunks] its capacity
+  const float* margin;        // [nchunks] safety factor on the sample's estimate
+  long long* cand_idx;
+  unsigned short* cand_val;
+};
+
+// Whole CTA (blockDim.x >= SCAN_T).  Largest bin b with count(bins >= b) >= k, how many entries of b are
+// needed, the largest non-empty bin and the total count; results in s_out[0..3].  k == 0 or total < k leave
+// s_out[0] = -1.  `gh` may have been written by other CTAs' atomics: read through L2.
+__device__ void hist_select(const unsigned int* gh, unsigned int k, unsigned int* s_part, int* s_out) {
+  constexpr int PER = NBINS / SCAN_T;
+  const int t = threadIdx.x;
+  unsigned int sum = 0;
+  int my_max = -1;
+  if (t < SCAN_T) {
+    const uint4* src = reinterpret_cast<const uint4*>(gh + t * PER);
+    for (int v = 0; v < PER / 4; ++v) {
+      const uint4 raw = __ldcg(src + v);
+      sum += raw.x + raw.y + raw.z + raw.w;
+      if (raw.x) my_max = t * PER + 4 * v;
+      if (raw.y) my_max = t * PER + 4 * v + 1;
+      if (raw.z) my_max = t * PER + 4 * v + 2;
+      if (raw.w) my_max = t * PER + 4 * v + 3;
+    }
+    s_part[t] = sum;
+  }
+  if (t == 0) {
+    s_out[0] = -1;
+    s_out[1] = 0;
+    s_out[2] = -1;
+    s_out[3] = 0;
+  }
+  __syncthreads();
+  if (my_max >= 0) atomicMax(&s_out[2], my_max);
+  for (int off = 1; off < SCAN_T; off <<= 1) {  // inclusive suffix sums over the SCAN_T partial counts
+    unsigned int add = 0;
+    if (t < SCAN_T && t + off < SCAN_T) add = s_part[t + off];
+    __syncthreads();
+    if (t < SCAN_T) s_part[t] += add;
+    __syncthreads();
+  }
+  if (t < SCAN_T) {
+    const unsigned int above = (t + 1 < SCAN_T) ? s_part[t + 1] : 0u;
+    const unsigned int incl = s_part[t];
+    if (t == 0) s_out[3] = static_cast<int>(incl);
+    if (k > 0 && above < k && incl >= k) {
+      unsigned int run = above;
+      for (int i = PER - 1; i >= 0; --i) {
+        const unsigned int cnt = __ldcg(gh + t * PER + i);
+        if (run + cnt >= k) {
+          s_out[0] = t * PER + i;
+          s_out[1] = static_cast<int>(k - run);
+          break;
+        }
+        run += cnt;
+      }
+    }
+  }
+  __syncthreads();
+}
+
+template <int RP>
+__global__ void __launch_bounds__(512, 1) residual_sample_kernel(const Select2Params sp) {
+  constexpr int CPT = 64 / RP;   // columns per thread; RP threads cover one 64-column line
+  const SelectParams& p = sp.base;
+  extern __shared__ unsigned int sh_hist[];
+  __shared__ unsigned int s_part[SCAN_T];
+  __shared__ int s_out[4];
+  __shared__ int s_last;
+  for (int b = threadIdx.x; b < NBINS; b += blockDim.x) sh_hist[b] = 0;
+  const int chunk = blockIdx.x / p.parts, part = blockIdx.x - chunk * p.parts;
+  const int c0 = chunk * p.chunk_rows, c1 = min(p.rows, c0 + p.chunk_rows);
+  const int nlines = (p.n + SAMPLE_LINE - 1) / SAMPLE_LINE;
+  const int per_row = (nlines + SAMPLE_STRIDE - 1) / SAMPLE_STRIDE;
+  const int groups = blockDim.x / RP, gid = threadIdx.x / RP, sub = threadIdx.x - gid * RP;
+  const long long items = static_cast<long long>(c1 - c0) * per_row;
+  __syncthreads();
+  for (long long item = static_cast<long long>(part) * groups + gid; item < items; item += static_cast<long long>(p.parts) * groups) {
+    const int row = c0 + static_cast<int>(item / per_row);
+    const int j = static_cast<int>(item - static_cast<long long>(row - c0) * per_row);
+    const int line = ((SAMPLE_STRIDE - (row % SAMPLE_STRIDE)) % SAMPLE_STRIDE) + j * SAMPLE_STRIDE;
+    const int col = line * SAMPLE_LINE + sub * CPT;
+    if (line >= nlines || col >= p.n) continue;
+    const XVec<CPT> xv = load_x<CPT>(p.x + static_cast<size_t>(row) * p.ldx, col, p.n);
+    const CVec<RP> cv = load_c<RP>(p.c + static_cast<size_t>(row) * p.r, p.r);
+    float qreg[CPT][RP];
+    load_q<RP, CPT>(p.q, p.r, col, p.n, qreg);
+    float e[CPT];
+    residual_row<RP, CPT>(xv, cv, qreg, e);
+#pragma unroll
+    for (int i = 0; i < CPT; ++i) {
+      if (col + i < p.n) {
+        const unsigned short key = __bfloat16_as_ushort(__float2bfloat16_rn(e[i])) & 0x7FFF;
+        atomicAdd(&sh_hist[key], 1u);
+      }
+    }
+  }
+  __syncthreads();
+  unsigned int* gh = p.hist + static_cast<size_t>(chunk) * NBINS;
+  for (int b = threadIdx.x; b < NBINS; b += blockDim.x) {
+    const unsigned int v = sh_hist[b];
+    if (v) atomicAdd(&gh[b], v);
+  }
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) s_last = (atomicAdd(&sp.done_a[chunk], 1) == p.parts - 1);
+  __syncthreads();
+  if (!s_last) return;
+  __threadfence();
+  // the sample is complete: scale the wanted count to the sample, add the margin, find the candidate bin
+  hist_select(gh, 0u, s_part, s_out);  // first call only for the sample size (k = 0 finds no bin)
+  const unsigned int sampled = static_cast<unsigned int>(s_out[3]);
+  const long long elems = static_cast<long long>(c1 - c0) * p.n;
+  const int quota = p.quota[chunk];
+  unsigned int want = 0;
+  if (quota > 0 && elems > 0) {
+    const double est = static_cast<double>(quota) * static_cast<double>(sampled) / static_cast<double>(elems);
+    want = static_cast<unsigned int>(est * sp.margin[chunk]) + 8u;
+  }
+  __syncthreads();
+  hist_select(gh, want, s_part, s_out);
+  if (threadIdx.x == 0) {
+    // fewer sampled entries than wanted: every entry is a candidate (the list will overflow and the chunk falls back)
+    sp.cand_bin[chunk] = quota <= 0 ? NBINS : (s_out[0] < 0 ? 0 : s_out[0]);
+  }
+}
+
+template <int RP>
+__global__ void __launch_bounds__(512, 1) residual_candidates_kernel(const Select2Params sp, int ctn, int rl) {
+  constexpr int CPT = 64 / RP;
+  constexpr unsigned FULL = 0xffffffffu;
+  const SelectParams& p = sp.base;
+  extern __shared__ unsigned char sh_raw[];
+  __shared__ int s_wcnt[16];
+  __shared__ unsigned int s_part[SCAN_T];
+  __shared__ int s_out[4];
+  __shared__ int s_last;
+  const int nwarps = blockDim.x >> 5, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  long long* st_idx_all = reinterpret_cast<long long*>(sh_raw);
+  unsigned short* st_val_all = reinterpret_cast<unsigned short*>(st_idx_all + static_cast<size_t>(nwarps) * WARP_CAP);
+  float* s_c = reinterpret_cast<float*>(sh_raw + static_cast<size_t>(16) * WARP_CAP * 10);
+  long long* st_idx = st_idx_all + static_cast<size_t>(warp) * WARP_CAP;
+  unsigned short* st_val = st_val_all + static_cast<size_t>(warp) * WARP_CAP;
+  const Slab s = slab_of(p);
+  const int t_lo = sp.cand_bin[s.chunk];
+  const int cap = sp.cand_cap[s.chunk];
+  const int cbase = sp.cand_off[s.chunk];
+  unsigned int* h2 = sp.hist2 + static_cast<size_t>(s.chunk) * NBINS;
+  // |e| below this cannot round to a magnitude >= t_lo (values at the midpoint may round down: they enter the list with
+  // a key below t_lo and are never selected, because the final threshold is not allowed below t_lo)
+  float cut;
+  if (t_lo >= NBINS) cut = __int_as_float(0x7f800000);   // nothing is wanted: only NaN passes, harmlessly
+  else if (t_lo > 0) cut = 0.5f * (bf16_bits_to_float(static_cast<unsigned short>(t_lo)) + bf16_bits_to_float(static_cast<unsigned short>(t_lo - 1)));
+  else cut = 0.f;
+  const int ct = threadIdx.x % ctn, lane_row = threadIdx.x / ctn;
+  int lmax = 0;
+  if (lane == 0) s_wcnt[warp] = 0;
+  __syncwarp();
+
+  auto append = [&](long long flat, unsigned short b16) {  // one lane
+    const int key = b16 & 0x7FFF;
+    atomicAdd(&h2[key], 1u);
+    lmax = max(lmax, key);
+    const int o = atomicAdd(&sp.cand_count[s.chunk], 1);
+    if (o < cap) {
+      sp.cand_idx[cbase + o] = flat;
+      sp.cand_val[cbase + o] = b16;
+    }
+  };
+  auto flush = [&]() {  // whole warp, converged
+    __syncwarp();
+    const int cnt = min(s_wcnt[warp], WARP_CAP);
+    if (cnt > 0) {
+      int base = 0;
+      if (lane == 0) base = atomicAdd(&sp.cand_count[s.chunk], cnt);
+      base = __shfl_sync(FULL, base, 0);
+      for (int i = lane; i < cnt; i += 32) {
+        const unsigned short b16 = st_val[i];
+        const int key = b16 & 0x7FFF;
+        atomicAdd(&h2[key], 1u);
+        lmax = max(lmax, key);
+        if (base + i < cap) {
+          sp.cand_idx[cbase + base + i] = st_idx[i];
+          sp.cand_val[cbase + base + i] = b16;
+        }
+      }
+    }
+    __syncwarp();
+    if (lane == 0) s_wcnt[warp] = 0;
+    __syncwarp();
+  };
+
+  for (int sb0 = s.row0; sb0 < s.row1; sb0 += CS_ROWS) {
+    const int sb1 = min(s.row1, sb0 + CS_ROWS);
+    stage_coeff<RP>(p.c, p.r, sb0, sb1, s_c);
+    for (int cb = 0; cb < p.n; cb += ctn * CPT) {
+      const int col = cb + ct * CPT;
+      const bool active = (col < p.n) && (lane_row < rl);
+      float qreg[CPT][RP];
+      if (active) load_q<RP, CPT>(p.q, p.r, col, p.n, qreg);
+      const int step = rl * ROWS_UNROLL;
+      const int iters = (sb1 - sb0 + step - 1) / step;  // the same for every thread of the CTA: warps stay converged at the flush
+      for (int it = 0; it < iters; ++it) {
+        __syncwarp();
+        if (s_wcnt[warp] > WARP_CAP / 2) flush();
+        const int row = sb0 + it * step + lane_row;
+        XVec<CPT> xv[ROWS_UNROLL];
+#pragma unroll
+        for (int u = 0; u < ROWS_UNROLL; ++u) {
+          const int rr = row + u * rl;
+          if (active && rr < sb1) xv[u] = load_x<CPT>(p.x + static_cast<size_t>(rr) * p.ldx, col, p.n);
+        }
+#pragma unroll
+        for (int u = 0; u < ROWS_UNROLL; ++u) {
+          const int rr = row + u * rl;
+          if (active && rr < sb1) {
+            float e[CPT];
+            residual_row_s<RP, CPT>(xv[u], s_c + (rr - sb0) * RP, qreg, e);
+#pragma unroll
+            for (int i = 0; i < CPT; ++i) {
+              if (col + i < p.n && !(fabsf(e[i]) < cut)) {
+                const unsigned short b16 = __bfloat16_as_ushort(__float2bfloat16_rn(e[i]));
+                const long long flat = static_cast<long long>(rr) * p.n + col + i;
+                const int pos = atomicAdd(&s_wcnt[warp], 1);
+                if (pos < WARP_CAP) {
+                  st_idx[pos] = flat;
+                  st_val[pos] = b16;
+                } else {
+                  append(flat, b16);  // staging slice full (a very dense stretch): straight to the list
+                }
+              }
+            }
+          }
+        }
+      }
+    }
+  }
+  flush();
+#pragma unroll
+  for (int off = 16; off; off >>= 1) lmax = max(lmax, __shfl_xor_sync(FULL, lmax, off));
+  if (lane == 0 && lmax > 0) atomicMax(sp.gmax, lmax);
+
+  // ---- tail: the last CTA of the chunk finds the exact threshold among the candidates; the last CTA of all sets the scale
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    s_last = (atomicAdd(&sp.done_c[s.chunk], 1) == p.parts - 1) ? 1 : 0;
+    if (atomicAdd(sp.done_all, 1) == static_cast<int>(gridDim.x) - 1) {
+      __threadfence();
+      const int mb = *reinterpret_cast<volatile int*>(sp.gmax);
+      const float amax = bf16_bits_to_float(static_cast<unsigned short>(mb));
+      const float qmax = (p.bits == 4) ? 7.f : 127.f;
+      *p.out_scale = (p.bits == 0) ? 1.f : fmaxf(amax / qmax, 1.17549435e-38f);
+    }
+  }
+  __syncthreads();
+  if (!s_last) return;
+  __threadfence();
+  const int quota = p.quota[s.chunk];
+  hist_select(h2, quota > 0 ? static_cast<unsigned int>(quota) : 0u, s_part, s_out);
+  const int appended = *reinterpret_cast<volatile int*>(&sp.cand_count[s.chunk]);
+  const bool valid = quota <= 0 || (s_out[0] >= t_lo && s_out[0] >= 0 && appended <= cap);
+  if (threadIdx.x == 0) {
+    p.thr_bin[s.chunk] = quota <= 0 ? NBINS : s_out[0];
+    p.thr_need[s.chunk] = s_out[1];
+    p.max_bin[s.chunk] = s_out[2] < 0 ? 0 : s_out[2];
+    p.tie_count[s.chunk] = 0;
+    p.out_count[s.chunk] = 0;
+    sp.fallback[s.chunk] = valid ? 0 : 1;
+  }
+  if (!valid) {  // the exact passes will histogram this chunk from scratch
+    unsigned int* gh = p.hist + static_cast<size_t>(s.chunk) * NBINS;
+    for (int b = threadIdx.x; b < NBINS; b += blockDim.x) gh[b] = 0u;
+  }
+}
+
+// Pass E: one thread per candidate.
+__global__ void __launch_bounds__(256) candidates_compact_kernel(const Select2Params sp, int parts2) {
+  constexpr unsigned FULL = 0xffffffffu;
+  const SelectParams& p = sp.base;
+  const int chunk = blockIdx.x / parts2, part = blockIdx.x - chunk * parts2;
+  if (sp.fallback[chunk]) return;
+  const int thr = p.thr_bin[chunk], need = p.thr_need[chunk], quota = p.quota[chunk], obase = p.out_offset[chunk];
+  const int count = min(sp.cand_count[chunk], sp.cand_cap[chunk]);
+  const int cbase = sp.cand_off[chunk];
+  const float inv_scale = 1.f / *p.out_scale;
+  const int lane = threadIdx.x & 31;
+  for (int i0 = part * static_cast<int>(blockDim.x); i0 < count; i0 += parts2 * static_cast<int>(blockDim.x)) {
+    const int i = i0 + static_cast<int>(threadIdx.x);
+    bool take = false;
+    unsigned short b16 = 0;
+    if (i < count) {
+      b16 = sp.cand_val[cbase + i];
+      const int key = b16 & 0x7FFF;
+      take = key > thr;
+      if (!take && key == thr && need > 0) take = atomicAdd(&p.tie_count[chunk], 1) < need;
+    }
+    const unsigned mask = __ballot_sync(FULL, take);
+    if (mask == 0u) continue;
+    int base = 0;
+    if (lane == (__ffs(mask) - 1)) base = atomicAdd(&p.out_count[chunk], __popc(mask));
+    base = __shfl_sync(FULL, base, __ffs(mask) - 1);
+    if (take) {
+      const int o = base + __popc(mask & ((1u << lane) - 1u));
+      if (o < quota) emit_entry(p, obase + o, sp.cand_idx[cbase + i], b16, inv_scale);
+    }
+  }
+}
+
 template <int RP>
 static int launch_select(const SelectParams& p, int phase, cudaStream_t st) {
   constexpr int CPT = 64 / RP;
@@ -556,6 +903,36 @@ static int launch_select(const SelectParams& p, int phase, cudaStream_t st) {
   return static_cast<int>(cudaGetLastError());
 }
 
+template <int RP>
+static int launch_sampled(const Select2Params& sp, cudaStream_t st) {
+  constexpr int CPT = 64 / RP;
+  const SelectParams& p = sp.base;
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= MAX_DEVICES) return -8;
+  int ctn = (p.n + CPT - 1) / CPT;
+  if (ctn > 512) ctn = 512;
+  int rl = 512 / ctn;
+  if (rl < 1) rl = 1;
+  const int threads = ((ctn * rl + 31) / 32) * 32;
+  const int grid = p.nchunks * p.parts;
+  const int smem_a = NBINS * 4;
+  const int smem_c = 16 * WARP_CAP * (8 + 2) + CS_ROWS * RP * 4;
+  static bool cfg[MAX_DEVICES] = {false};
+  if (!cfg[dev]) {
+    cudaError_t e = cudaFuncSetAttribute(residual_sample_kernel<RP>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_a);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    e = cudaFuncSetAttribute(residual_candidates_kernel<RP>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_c);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    cfg[dev] = true;
+  }
+  residual_sample_kernel<RP><<<grid, 512, smem_a, st>>>(sp);
+  residual_candidates_kernel<RP><<<grid, threads, smem_c, st>>>(sp, ctn, rl);
+  int parts2 = (2 * p.parts) > 64 ? 64 : 2 * p.parts;
+  if (parts2 < 1) parts2 = 1;
+  candidates_compact_kernel<<<p.nchunks * parts2, 256, 0, st>>>(sp, parts2);
+  return static_cast<int>(cudaGetLastError());
+}
+
 }  // namespace sb
 
 // Exact top-k selection of the residual by magnitude, per row chunk.
@@ -584,6 +961,7 @@ extern "C" int sb_residual_topk(const void* x, const void* c, const void* q, int
   p.quota = quota; p.out_offset = out_offset;
   p.bits = bits; p.out_idx32 = idx32; p.out_idx64 = idx64; p.out_val = val; p.out_scale = scale;
   p.status = status;
+  p.gate = nullptr;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   int rc;
   const int rp = r <= 8 ? 8 : (r <= 16 ? 16 : 32);
@@ -595,6 +973,54 @@ extern "C" int sb_residual_topk(const void* x, const void* c, const void* q, int
   if (rc) return rc;
   rc = rp == 8 ? launch_select<8>(p, 1, st) : rp == 16 ? launch_select<16>(p, 1, st) : launch_select<32>(p, 1, st);
   return rc;
+}
+
+// Sampled-threshold form of sb_residual_topk (see the comment above residual_sample_kernel).  Extra arguments:
+//   hist2     uint32 [nchunks, 32768], zeroed by the caller like hist;
+//   work      int32 [12 * nchunks + 2], zeroed by the caller;
+//   cand_off / cand_cap  int32 [nchunks]: slot range of each chunk's candidate list inside cand_idx / cand_val;
+//   margin    fp32 [nchunks]: safety factor applied to the sample's estimate of the candidate count;
+//   cand_idx  int64 [sum cand_cap], cand_val uint16 [sum cand_cap].
+extern "C" int sb_residual_topk_sampled(const void* x, const void* c, const void* q, int rows, int n, int r, int ldx, int chunk_rows,
+                                        int nchunks, int parts, void* hist, void* hist2, int* work, const int* quota,
+                                        const int* out_offset, const int* cand_off, const int* cand_cap, const float* margin,
+                                        long long* cand_idx, void* cand_val, int bits, int* idx32, long long* idx64, void* val,
+                                        float* scale, int* status, void* stream) {
+  using namespace sb;
+  if (rows <= 0 || n <= 0 || nchunks <= 0) return 0;
+  if (r < 1 || r > 32) return -2;
+  if ((ldx & 7) || (reinterpret_cast<uintptr_t>(x) & 15) || (reinterpret_cast<uintptr_t>(c) & 15)) return -3;
+  Select2Params sp;
+  SelectParams& p = sp.base;
+  p.x = static_cast<const __nv_bfloat16*>(x);
+  p.c = static_cast<const __nv_bfloat16*>(c);
+  p.q = static_cast<const __nv_bfloat16*>(q);
+  p.rows = rows; p.n = n; p.r = r; p.ldx = ldx;
+  p.chunk_rows = chunk_rows; p.parts = parts; p.nchunks = nchunks;
+  p.hist = static_cast<unsigned int*>(hist);
+  p.thr_bin = work; p.thr_need = work + nchunks; p.max_bin = work + 2 * nchunks;
+  p.tie_count = work + 3 * nchunks; p.out_count = work + 4 * nchunks;
+  sp.cand_bin = work + 5 * nchunks; sp.cand_count = work + 6 * nchunks; sp.fallback = work + 7 * nchunks;
+  sp.done_a = work + 8 * nchunks; sp.done_c = work + 9 * nchunks;
+  sp.done_all = work + 12 * nchunks; sp.gmax = work + 12 * nchunks + 1;
+  p.quota = quota; p.out_offset = out_offset;
+  p.bits = bits; p.out_idx32 = idx32; p.out_idx64 = idx64; p.out_val = val; p.out_scale = scale;
+  p.status = status;
+  p.gate = sp.fallback;
+  sp.hist2 = static_cast<unsigned int*>(hist2);
+  sp.cand_off = cand_off; sp.cand_cap = cand_cap; sp.margin = margin;
+  sp.cand_idx = cand_idx; sp.cand_val = static_cast<unsigned short*>(cand_val);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int rp = r <= 8 ? 8 : (r <= 16 ? 16 : 32);
+  int rc = rp == 8 ? launch_sampled<8>(sp, st) : rp == 16 ? launch_sampled<16>(sp, st) : launch_sampled<32>(sp, st);
+  if (rc) return rc;
+  // exact passes, gated per chunk by the fallback flags (they return at once for chunks the sampled passes served)
+  rc = rp == 8 ? launch_select<8>(p, 0, st) : rp == 16 ? launch_select<16>(p, 0, st) : launch_select<32>(p, 0, st);
+  if (rc) return rc;
+  residual_scan_kernel<<<nchunks, 1024, 0, st>>>(p);
+  rc = static_cast<int>(cudaGetLastError());
+  if (rc) return rc;
+  return rp == 8 ? launch_select<8>(p, 1, st) : rp == 16 ? launch_select<16>(p, 1, st) : launch_select<32>(p, 1, st);
 }
 
 extern "C" int sb_residual_gather(const void* x, const void* c, const void* q, int n, int r, int ldx,
@@ -727,6 +1153,7 @@ extern "C" int sb_residual_topk_noalloc(const void* x, const void* c, const void
   p.tie_count = ints + 3 * SB_NOALLOC_MAX_CHUNKS; p.out_count = ints + 4 * SB_NOALLOC_MAX_CHUNKS;
   p.quota = ints + 5 * SB_NOALLOC_MAX_CHUNKS; p.out_offset = ints + 6 * SB_NOALLOC_MAX_CHUNKS;
   p.bits = bits; p.out_idx32 = idx32; p.out_idx64 = idx64; p.out_val = val; p.out_scale = scale; p.status = status;
+  p.gate = nullptr;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   noalloc_prepare_kernel<<<64, 256, 0, st>>>(rows, chunk_rows, quota_per_chunk, nchunks);
   rc = static_cast<int>(cudaGetLastError());

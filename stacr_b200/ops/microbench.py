@@ -91,9 +91,19 @@ def case_stacr(args, pk) -> list:
     if sel in ("", "project"):
         add("project (gemm_bf16_kernel, N=16)", lambda: stacr_ops.project(x, qt), x_bytes)
     if sel in ("", "topk"):
-        add("residual top-k (hist+scan+scale+compact)", lambda: stacr_ops.residual_topk(x, c, qb, [k], rows, 8, torch.int32), 2 * x_bytes)
+        add("residual top-k, two exact passes (hist+scan+scale+compact)", lambda: stacr_ops.residual_topk(x, c, qb, [k], rows, 8, torch.int32, sampled=False), 2 * x_bytes)
+        add("residual top-k, sampled threshold (sample+candidates+compact)", lambda: stacr_ops.residual_topk(x, c, qb, [k], rows, 8, torch.int32, sampled=True), x_bytes + x_bytes // 16)
+        out[-1]["stats"] = stacr_ops.last_sampled_selection_stats()
     if sel in ("", "oja"):
         add("oja_update (+ X^T Y gemm)", lambda: oja_step_kernels(q, x, 0.01), 2 * x_bytes)
+    if sel in ("", "gelu"):
+        from . import nn_kernels
+
+        h = torch.randn(rows, n, device="cuda").bfloat16()
+        g = torch.randn(rows, n, device="cuda").bfloat16()
+        add("gelu_fwd", lambda: nn_kernels.gelu_fwd(h, False), 2 * x_bytes)
+        add("gelu_bwd + column sums", lambda: nn_kernels.gelu_bwd_colsum(g, h, False), 3 * x_bytes)
+        add("colsum (separate pass)", lambda: stacr_ops.colsum(g), x_bytes)
     if sel in ("", "dw"):
         idx, val, scale = stacr_ops.residual_topk(x, c, qb, [k], rows, 8, torch.int32)
         add("weight_grad gather form (bucket + dw_fused)", lambda: stacr_ops.weight_grad(dy, c, q, (idx, val, scale, 8, k), o, n, False, torch.float32, dense=False),
@@ -134,7 +144,7 @@ def main(argv=None) -> int:
     parser.add_argument("--out", type=int, default=2048)
     parser.add_argument("--rank", type=int, default=8)
     parser.add_argument("--budget", type=float, default=0.005)
-    parser.add_argument("--only", choices=("project", "topk", "oja", "dw"))
+    parser.add_argument("--only", choices=("project", "topk", "oja", "dw", "gelu"))
     parser.add_argument("--numel", type=int, default=1 << 28)
     args = parser.parse_args(argv)
     from . import _lib

@@ -57,6 +57,47 @@ def transpose_pad(c: torch.Tensor) -> torch.Tensor:
 
 
 _META: dict = {}
+_NBINS = 32768
+_SAMPLE_STRIDE = 16
+
+
+def _sampled_ok(quotas: list[int], rows: int, n: int, chunk_rows: int) -> bool:
+    """Whether every chunk is large and sparse enough for the sampled-threshold selection to pay off."""
+    if os.environ.get("STACR_SELECT_SAMPLED", "1") != "1" or n < 64:
+        return False
+    for i, k in enumerate(quotas):
+        elems = (min(rows, (i + 1) * chunk_rows) - i * chunk_rows) * n
+        if elems < (1 << 19) or k < 1024 or k * 8 > elems:
+            return False
+    return True
+
+
+def _select_meta(dev, quotas: list[int], sampled: bool):
+    """Per-chunk quotas, output offsets and (sampled form) candidate-list layout, uploaded once per distinct schedule."""
+    key = (dev.index, tuple(quotas), sampled)
+    meta = _META.get(key)
+    if meta is None:
+        offsets = [0]
+        for k in quotas[:-1]:
+            offsets.append(offsets[-1] + k)
+        rows_i = [quotas, offsets]
+        margins, total_cap = [], 0
+        if sampled:
+            caps, coffs = [], []
+            for k in quotas:
+                margin = min(3.0, max(1.25, 1.0 + 8.0 / math.sqrt(max(1.0, k / _SAMPLE_STRIDE))))
+                cap = int(1.5 * margin * k) + 8192
+                margins.append(margin)
+                coffs.append(total_cap)
+                caps.append(cap)
+                total_cap += cap
+            rows_i += [coffs, caps]
+        meta = {"ints": torch.tensor(rows_i, dtype=torch.int32).to(dev), "cap": total_cap,
+                "margin": torch.tensor(margins, dtype=torch.float32).to(dev) if sampled else None}
+        if len(_META) > 256:
+            _META.clear()
+        _META[key] = meta
+    return meta
 
 
 def residual_topk(
@@ -67,11 +108,14 @@ def residual_topk(
     chunk_rows: int,
     bits: int,
     index_dtype: torch.dtype,
+    sampled: bool | None = None,
 ):
     """Exact per-chunk top-k of ``|X - C Q^T|``; returns ``(idx, values, scale)``.
 
     ``values`` are bf16 (``bits == 0``) or int8 holding the 8- or 4-bit codes; ``scale`` is an
-    fp32 scalar tensor.  Entry order is unspecified.
+    fp32 scalar tensor.  Entry order is unspecified.  ``sampled`` picks the one-pass form (threshold
+    estimated from a 1/16 sample, exact selection among the candidates above it, exact two-pass redo of
+    any chunk the sample misjudged); ``None`` uses it when every chunk is large and sparse enough.
     """
     rows, n = x.shape
     r = coeff.shape[1]
@@ -80,32 +124,57 @@ def residual_topk(
     total = sum(quotas)
     sms = _lib.sm_count(dev)
     parts = max(1, sms // nchunks)
-    scratch = torch.zeros(nchunks * (32768 + 6), dtype=torch.int32, device=dev)   # histogram and counters: one fill
-    hist, work = scratch[: nchunks * 32768], scratch[nchunks * 32768:]
-    key = (dev.index, tuple(quotas))
-    meta = _META.get(key)
-    if meta is None:                      # per-chunk quotas and output offsets, uploaded once per distinct schedule
-        offsets = [0]
-        for k in quotas[:-1]:
-            offsets.append(offsets[-1] + k)
-        meta = torch.tensor([quotas, offsets], dtype=torch.int32).to(dev)
-        if len(_META) > 256:
-            _META.clear()
-        _META[key] = meta
+    if sampled is None:
+        sampled = _sampled_ok(quotas, rows, n, chunk_rows)
+    meta = _select_meta(dev, quotas, sampled)
+    ints = meta["ints"]
     idx = torch.empty(total, dtype=index_dtype, device=dev)
     val = torch.empty(total, dtype=torch.bfloat16 if bits == 0 else torch.int8, device=dev)
     scale = torch.empty((), dtype=torch.float32, device=dev)
     is32 = index_dtype == torch.int32
     lib = _lib.load()
+    if sampled:
+        # two histograms, the per-chunk counters and two global words: one fill
+        scratch = torch.zeros(nchunks * (2 * _NBINS + 12) + 2, dtype=torch.int32, device=dev)
+        hist, hist2, work = scratch[: nchunks * _NBINS], scratch[nchunks * _NBINS: 2 * nchunks * _NBINS], scratch[2 * nchunks * _NBINS:]
+        cand_idx = torch.empty(meta["cap"], dtype=torch.int64, device=dev)
+        cand_val = torch.empty(meta["cap"], dtype=torch.int16, device=dev)
+        rc = lib.sb_residual_topk_sampled(
+            _lib.ptr(x), _lib.ptr(coeff), _lib.ptr(basis_bf16), c_int(rows), c_int(n), c_int(r), c_int(x.stride(0)), c_int(chunk_rows),
+            c_int(nchunks), c_int(parts), _lib.ptr(hist), _lib.ptr(hist2), _lib.ptr(work), _lib.ptr(ints[0]), _lib.ptr(ints[1]),
+            _lib.ptr(ints[2]), _lib.ptr(ints[3]), _lib.ptr(meta["margin"]), _lib.ptr(cand_idx), _lib.ptr(cand_val), c_int(bits),
+            _lib.ptr(idx if is32 else None), _lib.ptr(None if is32 else idx), _lib.ptr(val), _lib.ptr(scale),
+            _lib.ptr(_lib.status_word(dev)), _lib.stream_ptr(),
+        )
+        _lib.check_rc(rc, "sb_residual_topk_sampled")
+        _lib.count(6)
+        global _LAST_SAMPLED_WORK
+        _LAST_SAMPLED_WORK = (work, nchunks)
+        return idx, val, scale
+    scratch = torch.zeros(nchunks * (_NBINS + 6), dtype=torch.int32, device=dev)   # histogram and counters: one fill
+    hist, work = scratch[: nchunks * _NBINS], scratch[nchunks * _NBINS:]
     rc = lib.sb_residual_topk(
         _lib.ptr(x), _lib.ptr(coeff), _lib.ptr(basis_bf16), c_int(rows), c_int(n), c_int(r), c_int(x.stride(0)),
-        c_int(chunk_rows), c_int(nchunks), c_int(parts), _lib.ptr(hist), _lib.ptr(work), _lib.ptr(meta[0]), _lib.ptr(meta[1]),
+        c_int(chunk_rows), c_int(nchunks), c_int(parts), _lib.ptr(hist), _lib.ptr(work), _lib.ptr(ints[0]), _lib.ptr(ints[1]),
         c_int(bits), _lib.ptr(idx if is32 else None), _lib.ptr(None if is32 else idx), _lib.ptr(val), _lib.ptr(scale),
         _lib.ptr(_lib.status_word(dev)), _lib.stream_ptr(),
     )
     _lib.check_rc(rc, "sb_residual_topk")
     _lib.count(4)
     return idx, val, scale
+
+
+_LAST_SAMPLED_WORK = None
+
+
+def last_sampled_selection_stats() -> dict | None:
+    """Counters of the most recent sampled selection (a synchronising read, for tests and diagnostics): per chunk the
+    candidate bin, the number of candidates the full pass appended and whether the chunk was redone by the exact passes."""
+    if _LAST_SAMPLED_WORK is None:
+        return None
+    work, n = _LAST_SAMPLED_WORK
+    host = work.cpu()
+    return {"candidate_bin": host[5 * n: 6 * n].tolist(), "candidates": host[6 * n: 7 * n].tolist(), "fell_back": host[7 * n: 8 * n].tolist()}
 
 
 def residual_gather(x, coeff, basis_bf16, idx: torch.Tensor) -> torch.Tensor:

@@ -43,6 +43,103 @@ def test_global_topk_matches_reference_value_set(rows, n, r, bits):
         assert (deq - got_e).abs().max() <= 0.51 * float(scale) + 2e-2 * float(got_e.abs().max())
 
 
+def _kernel_order_residual(x, c, qb):
+    """bf16 residual with the kernel's own arithmetic: a chain of fp32 fused multiply-adds over the rank, then one subtraction.
+
+    Each fused step is emulated in float64 (the product of two bf16 values and its sum with an fp32 accumulator are exact
+    there) and rounded to fp32, so the result is bit-identical to the kernel's except for double-rounding ties.
+    """
+    acc = torch.zeros(x.shape, dtype=torch.float32, device=x.device)
+    for j in range(c.shape[1]):
+        acc = (c[:, j:j + 1].double() * qb[:, j].double()[None, :] + acc.double()).float()
+    return (x.float() - acc).bfloat16()
+
+
+def _assert_exact_topk(e, idx, k):
+    """The selected magnitudes are exactly the k largest magnitudes of ``e`` (as a multiset)."""
+    flat = e.reshape(-1).float().abs()
+    assert idx.numel() == k and idx.unique().numel() == k
+    got = flat[idx.long()].sort().values
+    want = flat.topk(k).values.sort().values
+    mism = int((got != want).sum())
+    assert mism <= max(2, k // 50000), f"{mism} of {k} selected magnitudes differ from the exact top-k"
+
+
+@pytest.mark.parametrize("rows,n,r,bits", [(2048, 8192, 8, 8), (4096, 2048, 8, 0), (1024, 4096, 16, 4), (1100, 1280, 32, 0)])
+def test_sampled_threshold_selection_is_the_exact_topk(rows, n, r, bits):
+    from stacr_b200.ops import _lib, stacr_ops
+
+    x, q, qb, c, _ = _setup(rows, n, r, seed=11)
+    e = _kernel_order_residual(x, c, qb)
+    k = int(round(0.005 * rows * n))
+    idx, val, scale = stacr_ops.residual_topk(x, c, qb, [k], rows, bits, torch.int32, sampled=True)
+    torch.cuda.synchronize()
+    _lib.check_status()
+    stats = stacr_ops.last_sampled_selection_stats()
+    assert stats["fell_back"] == [0], stats
+    assert k <= stats["candidates"][0] <= 3 * k + 8192, stats
+    _assert_exact_topk(e, idx, k)
+    got_e = e.reshape(-1)[idx.long()].float()
+    if bits == 0:
+        assert torch.equal(val.float(), got_e)
+    else:
+        qmax = 127.0 if bits == 8 else 7.0
+        want_scale = float(e.float().abs().max()) / qmax
+        assert abs(float(scale) - want_scale) <= 1e-6 * want_scale
+        assert (val.float() * scale - got_e).abs().max() <= 0.5001 * float(scale)
+    # same selection as the two-pass form
+    idx2, _, scale2 = stacr_ops.residual_topk(x, c, qb, [k], rows, bits, torch.int32, sampled=False)
+    _assert_exact_topk(e, idx2, k)
+    assert float(scale2) == float(scale)
+
+
+def test_sampled_threshold_selection_per_chunk_quotas():
+    from stacr_b200.ops import _lib, stacr_ops
+
+    rows, n, r, chunk = 2560, 2048, 8, 512
+    x, q, qb, c, _ = _setup(rows, n, r, seed=5)
+    x[700:720] *= 6.0                       # a stretch of heavy rows inside one chunk
+    c = (x.float() @ qb.float()).bfloat16().contiguous()
+    e = _kernel_order_residual(x, c, qb)
+    quotas = [int(round(0.005 * chunk * n))] * 5
+    idx, val, _ = stacr_ops.residual_topk(x, c, qb, quotas, chunk, 0, torch.int32, sampled=True)
+    torch.cuda.synchronize()
+    _lib.check_status()
+    rows_of = idx.long() // n
+    for ci, k in enumerate(quotas):
+        mine = idx[(rows_of >= ci * chunk) & (rows_of < (ci + 1) * chunk)]
+        lo = ci * chunk * n
+        _assert_exact_topk(e[ci * chunk:(ci + 1) * chunk], mine - lo, k)
+
+
+@pytest.mark.parametrize("case", ["sample_overestimates", "all_ties"])
+def test_sampled_threshold_selection_redoes_a_misjudged_chunk_exactly(case):
+    """Inputs built to fool the sample: the chunk must be flagged, redone by the exact passes, and still be the exact top-k."""
+    from stacr_b200.ops import _lib, stacr_ops
+
+    rows, n, r = 1024, 2048, 8
+    g = torch.Generator(device="cuda").manual_seed(7)
+    qb = torch.linalg.qr(torch.randn(n, r, device="cuda", generator=g)).Q.bfloat16().contiguous()
+    c = torch.zeros(rows, r, device="cuda", dtype=torch.bfloat16)          # zero coefficients: the residual is the input
+    k = int(round(0.005 * rows * n))
+    if case == "all_ties":
+        x = (torch.randint(0, 2, (rows, n), device="cuda", generator=g).float() * 2 - 1).bfloat16()
+    else:
+        x = (0.01 * torch.randn(rows, n, device="cuda", generator=g)).bfloat16()
+        # large entries only where the sampler looks (line + row divisible by 16): it believes they are 16 times as many
+        rr = torch.arange(rows, device="cuda")[:, None]
+        line = torch.arange(n, device="cuda")[None, :] // 64
+        seen = ((line + rr) % 16 == 0)
+        pick = seen & (torch.rand(rows, n, device="cuda", generator=g) < (k / 6) / seen.sum())
+        x = torch.where(pick, torch.full_like(x, 5.0), x)
+    idx, val, _ = stacr_ops.residual_topk(x, c, qb, [k], rows, 0, torch.int32, sampled=True)
+    torch.cuda.synchronize()
+    _lib.check_status()
+    assert stacr_ops.last_sampled_selection_stats()["fell_back"] == [1]
+    _assert_exact_topk(x, idx, k)
+    assert torch.equal(val.float(), x.reshape(-1)[idx.long()].float())
+
+
 def test_chunk_quota_selection_counts_and_values():
     from stacr_b200.ops import _lib, stacr_ops
 
