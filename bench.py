@@ -10,10 +10,13 @@ residual_mode=global_topk, no turbo; AdamW with 8-bit block-wise moments (this f
 the reference arm uses torch AdamW because the external 8-bit optimizer it relies on is not
 installed; data-parallel over N ranks (weak scaling).
 
-Two timed regions of K optimizer steps each, both bracketed by barrier + synchronize and timed
-with CUDA events, max over ranks: (1) device-resident inputs, no host read-back -> ``value``;
-(2) end to end through the public API, with the step's token batch copied from pinned host
-memory and the loss read back every step -> ``e2e``.  One JSON line is printed by rank 0.
+Two measurements, each the median of ``--repeats`` back-to-back timed regions of K optimizer steps
+(every region bracketed by barrier + synchronize and timed with CUDA events, max over ranks):
+(1) device-resident inputs, no host read-back -> ``value``; (2) end to end through the public API,
+with the step's token batch copied from pinned host memory and the loss read back every step ->
+``e2e``.  After the timed regions one extra step measures, for both arms alike, the cosine of every
+wrapped layer's weight gradient to the dense ``dY^T X`` and the bytes autograd actually saved inside
+the wrapped layers.  One JSON line is printed by rank 0.
 """
 
 from __future__ import annotations
@@ -99,6 +102,90 @@ def timed_region(torch, dist, steps, step_fn, world):
         dist.all_reduce(secs, op=dist.ReduceOp.MAX)
         dist.barrier()
     return float(secs)
+
+
+def fidelity_and_saved_bytes(torch, model, layers, run_forward_backward):
+    """Evidence gathered by one extra step outside every timed region, identically for both arms.
+
+    * Saved bytes, measured: while a wrapped layer's forward runs, every tensor autograd saves that is not a parameter is
+      recorded through ``saved_tensors_hooks`` (distinct storage addresses, so a tensor saved twice counts once); the
+      layer's persistent basis is added when the saved basis copy is a different tensor.
+    * Weight-gradient fidelity: a forward hook keeps each wrapped layer's input, a backward hook multiplies it with the
+      incoming output gradient in fp32 (the dense ``dY^T X`` on the same batch and weights), and after the backward pass
+      the layer's own ``weight.grad`` is compared with it by cosine.
+    Returns ``{"dw_cosine_mean", "dw_cosine_worst", "dw_cosine_layers", "saved_bytes_measured", "dense_bytes"}``.
+    """
+    params = {p.data_ptr() for p in model.parameters()}
+    state = {"inside": None, "seen": set(), "bytes": 0, "dense": 0}
+    inputs, dense_dw = {}, {}
+
+    def pack(t):
+        if state["inside"] is not None and t.data_ptr() not in params and t.data_ptr() not in state["seen"]:
+            state["seen"].add(t.data_ptr())
+            state["bytes"] += t.numel() * t.element_size()
+        return t
+
+    def pre_hook(mod, args):
+        state["inside"] = mod
+
+    def fwd_hook(mod, args, out):
+        state["inside"] = None
+        x = args[0].detach()
+        inputs[mod] = x
+        state["dense"] += x.numel() * 2
+
+    def bwd_hook(mod, grad_in, grad_out):
+        x = inputs.pop(mod)
+        dy = grad_out[0]
+        x2 = x.reshape(-1, x.shape[-1]).float()
+        d2 = dy.reshape(-1, dy.shape[-1]).float()
+        dense_dw[mod] = d2.t() @ x2          # [out, in], fp32 (no TF32)
+
+    handles = []
+    for layer in layers:
+        handles += [layer.register_forward_pre_hook(pre_hook), layer.register_forward_hook(fwd_hook),
+                    layer.register_full_backward_hook(bwd_hook)]
+    try:
+        with torch.autograd.graph.saved_tensors_hooks(pack, lambda t: t):
+            run_forward_backward()
+        torch.cuda.synchronize()
+    finally:
+        for h in handles:
+            h.remove()
+    for layer in layers:                      # persistent bases that the saved tensors did not already cover
+        basis = getattr(layer, "basis", None)
+        if basis is not None and basis.data_ptr() not in state["seen"]:
+            state["bytes"] += basis.numel() * basis.element_size()
+    cosines = []
+    for layer in layers:
+        ref = dense_dw.pop(layer, None)
+        grad = layer.weight.grad
+        if ref is None or grad is None:
+            continue
+        g = grad.detach().float()
+        if g.shape != ref.shape:
+            g = g.t()
+        denom = float(g.norm() * ref.norm())
+        cosines.append(float((g * ref).sum()) / denom if denom > 0 else 1.0)
+        del ref
+    return {"dw_cosine_mean": sum(cosines) / max(1, len(cosines)), "dw_cosine_worst": min(cosines) if cosines else None,
+            "dw_cosine_layers": len(cosines), "saved_bytes_measured": state["bytes"], "dense_bytes": state["dense"]}
+
+
+def guarded_evidence(torch, model, layers, run_forward_backward):
+    """The evidence step must never cost the benchmark its line: a failure is reported on stderr and the fields stay null."""
+    try:
+        return fidelity_and_saved_bytes(torch, model, layers, run_forward_backward)
+    except Exception as exc:  # noqa: BLE001
+        print(f"evidence step failed: {type(exc).__name__}: {exc}", file=sys.stderr, flush=True)
+        return None
+
+
+def timed_regions(torch, dist, steps, step_fn, world, repeats):
+    """``repeats`` back-to-back timed regions of ``steps`` steps; returns (median seconds, all seconds)."""
+    all_secs = [timed_region(torch, dist, steps, step_fn, world) for _ in range(max(1, repeats))]
+    return statistics.median(all_secs), all_secs
+
 
 
 class LossReader:
@@ -267,12 +354,27 @@ def run_ours(args):
     torch.cuda.reset_peak_memory_stats(dev)
     launches0 = _lib.launch_count() + opt.kernel_launches
     with ClockSampler(local) as clocks:
-        secs = timed_region(torch, dist, args.steps, step_device, world)
-    launches = _lib.launch_count() + opt.kernel_launches - launches0
+        secs, secs_all = timed_regions(torch, dist, args.steps, step_device, world, args.repeats)
+    launches = (_lib.launch_count() + opt.kernel_launches - launches0) // max(1, args.repeats)
     with ClockSampler(local) as clocks_e2e:
-        secs_e2e = timed_region(torch, dist, args.steps, step_e2e, world)
+        secs_e2e, secs_e2e_all = timed_regions(torch, dist, args.steps, step_e2e, world, args.repeats)
     _lib.check_status(dev)
     peak = torch.cuda.max_memory_allocated(dev)
+
+    def evidence_step():
+        S.set_step(layers, counter["step"])
+        counter["step"] += 1
+        if sync is not None:
+            sync.zero_grad()
+        else:
+            opt.zero_grad(set_to_none=True)
+        with torch.autocast("cuda", dtype=torch.bfloat16):
+            loss = model(input_ids=dev_batches[0], labels=dev_batches[0]).loss
+        loss.backward()
+        if sync is not None:
+            sync.finish()
+
+    evidence = None if args.no_evidence else guarded_evidence(torch, model, layers, evidence_step)
     if args.kernel_table:  # every rank runs the extra steps (their collectives need all ranks); rank 0 writes the table
         kernel_table(torch, step_device, args.kernel_table if rank == 0 else os.devnull)
     if args.gap_report:
@@ -294,12 +396,20 @@ def run_ours(args):
                 "l2": "inputs larger than L2: every step streams 2.8 GB of bf16 weights and > 10 GB of activations through a 126 MB L2",
             },
             "clocks": clocks.summary(),
+            "timing": {"regions": len(secs_all), "steps_per_region": args.steps, "reported": "median region",
+                       "ms_per_step_regions": [1e3 * t / args.steps for t in secs_all],
+                       "e2e_ms_per_step_regions": [1e3 * t / args.steps for t in secs_e2e_all]},
             "e2e": {"value": tokens / secs_e2e, "unit": "tokens/s", "h2d_bytes_per_step": batch * seq * 8, "d2h_bytes_per_step": 4,
                     "ms_per_step": 1e3 * secs_e2e / args.steps, "last_loss": last.get("loss"), "clocks": clocks_e2e.summary(),
                     "how": "own timed region: per step a pinned-host token batch is copied to the device and the loss is copied back to pinned memory and read by the host one step later (the last one inside the region)"},
             "gpu_launches": launches,
             "memory": {"peak_allocated_gb": peak / 1e9, "saved_activation_gb_wrapped_layers": factor_bytes / 1e9,
-                       "dense_saved_gb_same_layers": dense_bytes / 1e9},
+                       "dense_saved_gb_same_layers": dense_bytes / 1e9,
+                       "saved_activation_gb_wrapped_layers_measured": None if evidence is None else evidence["saved_bytes_measured"] / 1e9,
+                       "how": "measured: bytes of the non-parameter tensors autograd saved inside the wrapped layers' forwards (saved_tensors_hooks) plus their persistent bases; the unsuffixed figure is the layers' stored_bytes() formula"},
+            "fidelity": None if evidence is None else {
+                "dw_cosine_mean": evidence["dw_cosine_mean"], "dw_cosine_worst": evidence["dw_cosine_worst"], "layers": evidence["dw_cosine_layers"],
+                "how": "one extra step after the timed regions: each wrapped layer's weight.grad against fp32 dY^T X formed from the same input and output gradient"},
         })
     if world > 1:
         dist.destroy_process_group()
@@ -374,10 +484,20 @@ def run_reference(args):
     torch.cuda.synchronize()
     torch.cuda.reset_peak_memory_stats(dev)
     with ClockSampler(local) as clocks:
-        secs = timed_region(torch, dist, args.steps, step_device, world)
+        secs, secs_all = timed_regions(torch, dist, args.steps, step_device, world, args.repeats)
     with ClockSampler(local) as clocks_e2e:
-        secs_e2e = timed_region(torch, dist, args.steps, step_e2e, world)
+        secs_e2e, secs_e2e_all = timed_regions(torch, dist, args.steps, step_e2e, world, args.repeats)
     peak = torch.cuda.max_memory_allocated(dev)
+
+    def evidence_step():
+        ref.set_step(layers, counter["step"])
+        counter["step"] += 1
+        opt.zero_grad(set_to_none=True)
+        with torch.autocast("cuda", dtype=torch.bfloat16):
+            loss = net(input_ids=dev_batches[0], labels=dev_batches[0]).loss
+        loss.backward()
+
+    evidence = None if args.no_evidence else guarded_evidence(torch, model, layers, evidence_step)
     rows = batch * seq
     factor_bytes = sum(layer.stored_bytes(rows, 2)["total"] for layer in layers)
     tokens = world * batch * seq * args.steps
@@ -398,7 +518,15 @@ def run_reference(args):
                     "ms_per_step": 1e3 * secs_e2e / args.steps, "last_loss": last.get("loss"), "clocks": clocks_e2e.summary(),
                     "how": "own timed region: per step a pinned-host token batch is copied to the device and the loss is copied back to pinned memory and read by the host one step later (the last one inside the region)"},
             "gpu_launches": None,
-            "memory": {"peak_allocated_gb": peak / 1e9, "saved_activation_gb_wrapped_layers": factor_bytes / 1e9},
+            "timing": {"regions": len(secs_all), "steps_per_region": args.steps, "reported": "median region",
+                       "ms_per_step_regions": [1e3 * t / args.steps for t in secs_all],
+                       "e2e_ms_per_step_regions": [1e3 * t / args.steps for t in secs_e2e_all]},
+            "memory": {"peak_allocated_gb": peak / 1e9, "saved_activation_gb_wrapped_layers": factor_bytes / 1e9,
+                       "saved_activation_gb_wrapped_layers_measured": None if evidence is None else evidence["saved_bytes_measured"] / 1e9,
+                       "dense_saved_gb_same_layers": None if evidence is None else evidence["dense_bytes"] / 1e9},
+            "fidelity": None if evidence is None else {
+                "dw_cosine_mean": evidence["dw_cosine_mean"], "dw_cosine_worst": evidence["dw_cosine_worst"], "layers": evidence["dw_cosine_layers"],
+                "how": "one extra step after the timed regions: each wrapped layer's weight.grad against fp32 dY^T X formed from the same input and output gradient"},
         })
     if world > 1:
         dist.destroy_process_group()
@@ -416,6 +544,8 @@ def main():
     ap.add_argument("--gap-report", metavar="FILE", help="after the timed regions, write where the GPU idles inside two more steps to FILE")
     ap.add_argument("--kernel-table", metavar="FILE", help="after the timed regions, write per-kernel device times of two more steps to FILE")
     ap.add_argument("--small", action="store_true", help="tiny shape for smoke runs (not a benchmark number)")
+    ap.add_argument("--repeats", type=int, default=3, help="timed regions of --steps steps per measurement; the median region is reported")
+    ap.add_argument("--no-evidence", action="store_true", help="skip the extra step that measures dW cosine and saved bytes after the timed regions")
     args = ap.parse_args()
     if args.gpus > 1 and "RANK" not in os.environ:
         raise SystemExit("for --gpus > 1 launch with: python -m torch.distributed.run --nproc-per-node N bench.py --gpus N ...")
