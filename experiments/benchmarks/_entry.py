@@ -74,3 +74,30 @@ def main(name: str, argv: Optional[List[str]] = None) -> int:
     from .__main__ import main as cli
 
     return cli(["run", name, *(argv if argv is not None else __import__("sys").argv[1:])])
+
+
+def bind(namespace: dict, name: str) -> None:
+    """Give a grid module its standard entry points: ``NAME``, ``cells``, ``rows``, ``arms``, ``run``, ``run_cohort``,
+    ``one`` and ``main``, all bound to grid ``name`` (names the module has already defined are left alone)."""
+
+    def _cells():
+        return cells(name)
+
+    def _arms():
+        return arms(name)
+
+    def _run(seeds=(42,), output=None):
+        return run(name, seeds, output)
+
+    def _run_cohort(selector, seeds=(42,), output=None):
+        return run_cohort(name, selector, seeds, output)
+
+    def _one(method, seed=42, **overrides):
+        return one(name, method, seed, **overrides)
+
+    def _main(argv=None) -> int:
+        return main(name, argv)
+
+    bound = {"NAME": name, "cells": _cells, "rows": _cells, "arms": _arms, "run": _run, "run_cohort": _run_cohort, "one": _one, "main": _main}
+    for key, value in bound.items():
+        namespace.setdefault(key, value)

@@ -11,27 +11,7 @@ from __future__ import annotations
 from . import _entry
 from .probes import complement  # noqa: F401
 
-NAME = "allocator_stability"
-
-
-def cells():
-    return _entry.cells(NAME)
-
-
-def rows():
-    return _entry.cells(NAME)
-
-
-def arms():
-    return _entry.arms(NAME)
-
-
-def run(seeds=(42,), output=None):
-    return _entry.run(NAME, seeds, output)
-
-
-def run_cohort(selector, seeds=(42,), output=None):
-    return _entry.run_cohort(NAME, selector, seeds, output)
+_entry.bind(globals(), "allocator_stability")
 
 
 def trace(method, cfg, model_id="qwen2.5-1.5b", bs=2, seq=1024, steps=600, **run_kw):
@@ -43,14 +23,6 @@ def trace(method, cfg, model_id="qwen2.5-1.5b", bs=2, seq=1024, steps=600, **run
 
     return common.run_config(method, 42, model_id=model_id, bs=bs, seq=seq, steps=steps, measure_from=0, eval_batches=0,
                              stacr_cfg=dict(cfg, turbo_after_step=None) if cfg else None, trace_memory=True, **run_kw)
-
-
-def one(method, seed=42, **overrides):
-    return _entry.one(NAME, method, seed, **overrides)
-
-
-def main(argv=None) -> int:
-    return _entry.main(NAME, argv)
 
 
 if __name__ == "__main__":

@@ -11,27 +11,7 @@ from __future__ import annotations
 from . import _entry
 from .probes import complement  # noqa: F401
 
-NAME = "bert_sst2"
-
-
-def cells():
-    return _entry.cells(NAME)
-
-
-def rows():
-    return _entry.cells(NAME)
-
-
-def arms():
-    return _entry.arms(NAME)
-
-
-def run(seeds=(42,), output=None):
-    return _entry.run(NAME, seeds, output)
-
-
-def run_cohort(selector, seeds=(42,), output=None):
-    return _entry.run_cohort(NAME, selector, seeds, output)
+_entry.bind(globals(), "bert_sst2")
 
 
 def sst2(method="baseline", stacr_cfg=None, bs=32, seq=128, steps=60, seed=42, **run_kw):
@@ -39,14 +19,6 @@ def sst2(method="baseline", stacr_cfg=None, bs=32, seq=128, steps=60, seed=42, *
     from . import common
 
     return common.run_config(method, seed, model_id="bert-base-uncased", bs=bs, seq=seq, steps=steps, stacr_cfg=stacr_cfg, **run_kw)
-
-
-def one(method, seed=42, **overrides):
-    return _entry.one(NAME, method, seed, **overrides)
-
-
-def main(argv=None) -> int:
-    return _entry.main(NAME, argv)
 
 
 if __name__ == "__main__":

@@ -11,27 +11,7 @@ from __future__ import annotations
 from . import _entry
 from .probes import complement  # noqa: F401
 
-NAME = "capacity_search"
-
-
-def cells():
-    return _entry.cells(NAME)
-
-
-def rows():
-    return _entry.cells(NAME)
-
-
-def arms():
-    return _entry.arms(NAME)
-
-
-def run(seeds=(42,), output=None):
-    return _entry.run(NAME, seeds, output)
-
-
-def run_cohort(selector, seeds=(42,), output=None):
-    return _entry.run_cohort(NAME, selector, seeds, output)
+_entry.bind(globals(), "capacity_search")
 
 
 def largest_fitting(model_id, seq, dtype, lo, hi, method, cfg, out=None, tag="capacity", **run_kw):
@@ -39,14 +19,6 @@ def largest_fitting(model_id, seq, dtype, lo, hi, method, cfg, out=None, tag="ca
     from . import probes
 
     return probes.largest_fitting(model_id, seq, dtype, lo, hi, method, cfg, out, tag, **run_kw)
-
-
-def one(method, seed=42, **overrides):
-    return _entry.one(NAME, method, seed, **overrides)
-
-
-def main(argv=None) -> int:
-    return _entry.main(NAME, argv)
 
 
 if __name__ == "__main__":

@@ -11,27 +11,7 @@ from __future__ import annotations
 from . import _entry
 from .probes import complement  # noqa: F401
 
-NAME = "lora"
-
-
-def cells():
-    return _entry.cells(NAME)
-
-
-def rows():
-    return _entry.cells(NAME)
-
-
-def arms():
-    return _entry.arms(NAME)
-
-
-def run(seeds=(42,), output=None):
-    return _entry.run(NAME, seeds, output)
-
-
-def run_cohort(selector, seeds=(42,), output=None):
-    return _entry.run_cohort(NAME, selector, seeds, output)
+_entry.bind(globals(), "lora")
 
 
 CFG = {"rank": 8, "residual_budget": 0.005, "residual_bits": 8, "surface": "mlp", "min_features": 256, "chunk_rows": 512}
@@ -52,14 +32,6 @@ def run_lora(model_id, bs, seq, steps, seed, use_lora, use_stacr, qlora=False, t
                             stacr_cfg=dict(CFG, turbo_after_step=None) if use_stacr else None, lora=bool(use_lora), **run_kw)
     rec["tag"] = tag
     return rec
-
-
-def one(method, seed=42, **overrides):
-    return _entry.one(NAME, method, seed, **overrides)
-
-
-def main(argv=None) -> int:
-    return _entry.main(NAME, argv)
 
 
 if __name__ == "__main__":

@@ -11,27 +11,7 @@ from __future__ import annotations
 from . import _entry
 from .probes import complement  # noqa: F401
 
-NAME = "peak_anatomy"
-
-
-def cells():
-    return _entry.cells(NAME)
-
-
-def rows():
-    return _entry.cells(NAME)
-
-
-def arms():
-    return _entry.arms(NAME)
-
-
-def run(seeds=(42,), output=None):
-    return _entry.run(NAME, seeds, output)
-
-
-def run_cohort(selector, seeds=(42,), output=None):
-    return _entry.run_cohort(NAME, selector, seeds, output)
+_entry.bind(globals(), "peak_anatomy")
 
 
 def phase_run(method, cfg, model_id="gpt2-medium", bs=8, seq=1024, **run_kw):
@@ -47,14 +27,6 @@ def ce_run(chunk, model_id="gpt2-medium", bs=8, seq=1024, **run_kw):
 
     return common.run_config(f"chunked_ce_{chunk}", 42, model_id=model_id, bs=bs, seq=seq, phase_profile=True, eval_batches=0,
                              model_overrides={**run_kw.pop("model_overrides", {}), "loss_chunk": int(chunk)}, **run_kw)
-
-
-def one(method, seed=42, **overrides):
-    return _entry.one(NAME, method, seed, **overrides)
-
-
-def main(argv=None) -> int:
-    return _entry.main(NAME, argv)
 
 
 if __name__ == "__main__":

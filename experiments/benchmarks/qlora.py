@@ -11,27 +11,7 @@ from __future__ import annotations
 from . import _entry
 from .probes import complement  # noqa: F401
 
-NAME = "qlora"
-
-
-def cells():
-    return _entry.cells(NAME)
-
-
-def rows():
-    return _entry.cells(NAME)
-
-
-def arms():
-    return _entry.arms(NAME)
-
-
-def run(seeds=(42,), output=None):
-    return _entry.run(NAME, seeds, output)
-
-
-def run_cohort(selector, seeds=(42,), output=None):
-    return _entry.run_cohort(NAME, selector, seeds, output)
+_entry.bind(globals(), "qlora")
 
 
 CFG = {"rank": 8, "residual_budget": 0.005, "residual_bits": 8, "surface": "mlp", "min_features": 256, "chunk_rows": 512}
@@ -60,14 +40,6 @@ def run_qlora(kind, use_stacr, bs, seq, steps, seed, tag="", model_id=MODEL, **r
                             eval_batches=0, stacr_cfg=dict(CFG) if use_stacr else None, lora=kind == "lora", qlora=kind == "qlora", **run_kw)
     rec.update(tag=tag, quant=kind == "qlora")
     return rec
-
-
-def one(method, seed=42, **overrides):
-    return _entry.one(NAME, method, seed, **overrides)
-
-
-def main(argv=None) -> int:
-    return _entry.main(NAME, argv)
 
 
 if __name__ == "__main__":

@@ -11,27 +11,7 @@ from __future__ import annotations
 from . import _entry
 from .probes import complement  # noqa: F401
 
-NAME = "rate_distortion"
-
-
-def cells():
-    return _entry.cells(NAME)
-
-
-def rows():
-    return _entry.cells(NAME)
-
-
-def arms():
-    return _entry.arms(NAME)
-
-
-def run(seeds=(42,), output=None):
-    return _entry.run(NAME, seeds, output)
-
-
-def run_cohort(selector, seeds=(42,), output=None):
-    return _entry.run_cohort(NAME, selector, seeds, output)
+_entry.bind(globals(), "rate_distortion")
 
 
 def payload_bytes(kind, rank, budget, model_id="gpt2-medium", bs=4, seq=512, min_features=256, **overrides):
@@ -49,14 +29,6 @@ def payload_bytes(kind, rank, budget, model_id="gpt2-medium", bs=4, seq=512, min
     stored = sum(sum(v for k, v in layer.stored_bytes(rows, 2).items() if k in ("coeff", "residual", "basis")) for layer in layers)
     dense = sum(rows * layer.in_features * 2 for layer in layers)
     return stored, dense, len(layers)
-
-
-def one(method, seed=42, **overrides):
-    return _entry.one(NAME, method, seed, **overrides)
-
-
-def main(argv=None) -> int:
-    return _entry.main(NAME, argv)
 
 
 if __name__ == "__main__":
