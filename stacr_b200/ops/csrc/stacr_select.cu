@@ -567,49 +567,59 @@ struct Select2Params {
   unsigned short* cand_val;
 };
 
-// Whole CTA (blockDim.x >= SCAN_T).  Largest bin b with count(bins >= b) >= k, how many entries of b are
-// needed, the largest non-empty bin and the total count; results in s_out[0..3].  k == 0 or total < k leave
-// s_out[0] = -1.  `gh` may have been written by other CTAs' atomics: read through L2.
-__device__ void hist_select(const unsigned int* gh, unsigned int k, unsigned int* s_part, int* s_out) {
+// Whole CTA (blockDim.x >= SCAN_T).  Copies a chunk's histogram (written by other CTAs' atomics: read through L2) into
+// shared memory with coalesced 16-byte loads and leaves in s_part[t] the number of entries in bins >= t * PER (inclusive
+// suffix sums over SCAN_T segments of PER bins; s_part[0] is the total) and in s_out[2] the largest non-empty bin.
+// A single thread walking 128 bins in global memory costs 128 dependent L2 round trips; from shared memory it is 2 us.
+__device__ void hist_stage(const unsigned int* gh, unsigned int* sh, unsigned int* s_part, int* s_out) {
   constexpr int PER = NBINS / SCAN_T;
   const int t = threadIdx.x;
-  unsigned int sum = 0;
-  int my_max = -1;
+  const uint4* src = reinterpret_cast<const uint4*>(gh);
+  uint4* dst = reinterpret_cast<uint4*>(sh);
+#pragma unroll 4
+  for (int i = t; i < NBINS / 4; i += blockDim.x) dst[i] = __ldcg(src + i);
+  if (t == 0) s_out[2] = -1;
+  __syncthreads();
   if (t < SCAN_T) {
-    const uint4* src = reinterpret_cast<const uint4*>(gh + t * PER);
-    for (int v = 0; v < PER / 4; ++v) {
-      const uint4 raw = __ldcg(src + v);
-      sum += raw.x + raw.y + raw.z + raw.w;
-      if (raw.x) my_max = t * PER + 4 * v;
-      if (raw.y) my_max = t * PER + 4 * v + 1;
-      if (raw.z) my_max = t * PER + 4 * v + 2;
-      if (raw.w) my_max = t * PER + 4 * v + 3;
+    unsigned int sum = 0;
+    int my_max = -1;
+#pragma unroll 8
+    for (int i = 0; i < PER; ++i) {
+      const int ii = (i + t) & (PER - 1);  // rotate the start so that the lanes of a warp hit different banks
+      const unsigned int v = sh[t * PER + ii];
+      sum += v;
+      if (v) my_max = max(my_max, t * PER + ii);
     }
     s_part[t] = sum;
-  }
-  if (t == 0) {
-    s_out[0] = -1;
-    s_out[1] = 0;
-    s_out[2] = -1;
-    s_out[3] = 0;
+    if (my_max >= 0) atomicMax(&s_out[2], my_max);
   }
   __syncthreads();
-  if (my_max >= 0) atomicMax(&s_out[2], my_max);
-  for (int off = 1; off < SCAN_T; off <<= 1) {  // inclusive suffix sums over the SCAN_T partial counts
+  for (int off = 1; off < SCAN_T; off <<= 1) {
     unsigned int add = 0;
     if (t < SCAN_T && t + off < SCAN_T) add = s_part[t + off];
     __syncthreads();
     if (t < SCAN_T) s_part[t] += add;
     __syncthreads();
   }
+}
+
+// After hist_stage: the largest bin b with count(bins >= b) >= k -> s_out[0], and how many entries of b are needed
+// -> s_out[1].  k == 0 or fewer than k entries in total leave s_out[0] = -1.  Ends with a barrier.
+__device__ void hist_locate(const unsigned int* sh, const unsigned int* s_part, unsigned int k, int* s_out) {
+  constexpr int PER = NBINS / SCAN_T;
+  const int t = threadIdx.x;
+  if (t == 0) {
+    s_out[0] = -1;
+    s_out[1] = 0;
+  }
+  __syncthreads();
   if (t < SCAN_T) {
     const unsigned int above = (t + 1 < SCAN_T) ? s_part[t + 1] : 0u;
     const unsigned int incl = s_part[t];
-    if (t == 0) s_out[3] = static_cast<int>(incl);
     if (k > 0 && above < k && incl >= k) {
       unsigned int run = above;
       for (int i = PER - 1; i >= 0; --i) {
-        const unsigned int cnt = __ldcg(gh + t * PER + i);
+        const unsigned int cnt = sh[t * PER + i];
         if (run + cnt >= k) {
           s_out[0] = t * PER + i;
           s_out[1] = static_cast<int>(k - run);
@@ -671,8 +681,8 @@ __global__ void __launch_bounds__(512, 1) residual_sample_kernel(const Select2Pa
   if (!s_last) return;
   __threadfence();
   // the sample is complete: scale the wanted count to the sample, add the margin, find the candidate bin
-  hist_select(gh, 0u, s_part, s_out);  // first call only for the sample size (k = 0 finds no bin)
-  const unsigned int sampled = static_cast<unsigned int>(s_out[3]);
+  hist_stage(gh, sh_hist, s_part, s_out);
+  const unsigned int sampled = s_part[0];
   const long long elems = static_cast<long long>(c1 - c0) * p.n;
   const int quota = p.quota[chunk];
   unsigned int want = 0;
@@ -680,18 +690,49 @@ __global__ void __launch_bounds__(512, 1) residual_sample_kernel(const Select2Pa
     const double est = static_cast<double>(quota) * static_cast<double>(sampled) / static_cast<double>(elems);
     want = static_cast<unsigned int>(est * sp.margin[chunk]) + 8u;
   }
-  __syncthreads();
-  hist_select(gh, want, s_part, s_out);
+  hist_locate(sh_hist, s_part, want, s_out);
   if (threadIdx.x == 0) {
     // fewer sampled entries than wanted: every entry is a candidate (the list will overflow and the chunk falls back)
     sp.cand_bin[chunk] = quota <= 0 ? NBINS : (s_out[0] < 0 ? 0 : s_out[0]);
   }
 }
 
+// Tensor-core helpers of the full pass.  E = X - C Q^T for a 16-row x 8-column tile is one warp-level MMA with the
+// negated coefficients as A, the basis as B and X itself as the incoming accumulator: rank 8 is exactly the K of
+// m16n8k8, ranks up to 16 and 32 take one and two m16n8k16.  (The fifth-generation tcgen05 path needs K >= 16 operands
+// in shared memory behind descriptors and its accumulator in tensor memory, which cannot be preloaded with X from global
+// memory without a round trip through registers; for a K of 8 to 32 whose only purpose is to take 8 to 32 FMAs per element
+// off the issue slots of a bandwidth-bound pass, the register-operand form is the right tool.)
+__device__ __forceinline__ void mma_k8(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t b0) {
+  asm volatile("mma.sync.aligned.m16n8k8.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5}, {%6}, {%0, %1, %2, %3};"
+               : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+               : "r"(a0), "r"(a1), "r"(b0));
+}
+__device__ __forceinline__ void mma_k16(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+               : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+               : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+// Two consecutive basis coefficients q[col, k], q[col, k + 1] as a bf16x2 word (zero past the rank or the last column).
+__device__ __forceinline__ uint32_t q_pair(const __nv_bfloat16* q, int r, int n, int col, int k, bool vec) {
+  if (col >= n) return 0u;
+  const __nv_bfloat16* row = q + static_cast<size_t>(col) * r;
+  if (vec) return __ldg(reinterpret_cast<const uint32_t*>(row + k));
+  const uint32_t lo = (k < r) ? __bfloat16_as_ushort(row[k]) : 0u;
+  const uint32_t hi = (k + 1 < r) ? __bfloat16_as_ushort(row[k + 1]) : 0u;
+  return lo | (hi << 16);
+}
+__device__ __forceinline__ uint32_t word_of(const uint4& v, int i) { return i == 0 ? v.x : i == 1 ? v.y : i == 2 ? v.z : v.w; }
+
+// Pass C.  A warp owns 64-column blocks; for each it keeps the basis fragments in registers and walks the CTA's rows
+// 32 at a time.  Within a block thread t of a quad owns columns [8t, 8t+8) and [32+8t, 32+8t+8) of each of its rows (two
+// 16-byte loads per row), and the MMA's column index is mapped onto those physical columns, so the loads are full
+// sectors and the accumulator registers already hold the thread's own columns.
 template <int RP>
-__global__ void __launch_bounds__(512, 1) residual_candidates_kernel(const Select2Params sp, int ctn, int rl) {
-  constexpr int CPT = 64 / RP;
+__global__ void __launch_bounds__(512, 1) residual_candidates_kernel(const Select2Params sp) {
   constexpr unsigned FULL = 0xffffffffu;
+  constexpr int HW = RP / 2;     // 32-bit words per staged coefficient row
+  constexpr int KB = RP / 8;     // basis registers per 8-column tile
   const SelectParams& p = sp.base;
   extern __shared__ unsigned char sh_raw[];
   __shared__ int s_wcnt[16];
@@ -699,9 +740,10 @@ __global__ void __launch_bounds__(512, 1) residual_candidates_kernel(const Selec
   __shared__ int s_out[4];
   __shared__ int s_last;
   const int nwarps = blockDim.x >> 5, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int g = lane >> 2, t = lane & 3;
   long long* st_idx_all = reinterpret_cast<long long*>(sh_raw);
-  unsigned short* st_val_all = reinterpret_cast<unsigned short*>(st_idx_all + static_cast<size_t>(nwarps) * WARP_CAP);
-  float* s_c = reinterpret_cast<float*>(sh_raw + static_cast<size_t>(16) * WARP_CAP * 10);
+  unsigned short* st_val_all = reinterpret_cast<unsigned short*>(st_idx_all + static_cast<size_t>(16) * WARP_CAP);
+  uint32_t* s_cb = reinterpret_cast<uint32_t*>(sh_raw + static_cast<size_t>(16) * WARP_CAP * 10);  // [CS_ROWS][HW] negated bf16 pairs
   long long* st_idx = st_idx_all + static_cast<size_t>(warp) * WARP_CAP;
   unsigned short* st_val = st_val_all + static_cast<size_t>(warp) * WARP_CAP;
   const Slab s = slab_of(p);
@@ -712,10 +754,10 @@ __global__ void __launch_bounds__(512, 1) residual_candidates_kernel(const Selec
   // |e| below this cannot round to a magnitude >= t_lo (values at the midpoint may round down: they enter the list with
   // a key below t_lo and are never selected, because the final threshold is not allowed below t_lo)
   float cut;
-  if (t_lo >= NBINS) cut = __int_as_float(0x7f800000);   // nothing is wanted: only NaN passes, harmlessly
+  if (t_lo >= NBINS) cut = __int_as_float(0x7f800000);   // nothing is wanted
   else if (t_lo > 0) cut = 0.5f * (bf16_bits_to_float(static_cast<unsigned short>(t_lo)) + bf16_bits_to_float(static_cast<unsigned short>(t_lo - 1)));
   else cut = 0.f;
-  const int ct = threadIdx.x % ctn, lane_row = threadIdx.x / ctn;
+  const bool qvec = (p.r == RP);   // basis rows are RP * 2 bytes: pairs are 4-byte aligned
   int lmax = 0;
   if (lane == 0) s_wcnt[warp] = 0;
   __syncwarp();
@@ -752,47 +794,96 @@ __global__ void __launch_bounds__(512, 1) residual_candidates_kernel(const Selec
     if (lane == 0) s_wcnt[warp] = 0;
     __syncwarp();
   };
+  auto push = [&](int row, int row_end, int col, float e) {  // diverged lanes
+    if (row < row_end && col < p.n) {
+      const unsigned short b16 = __bfloat16_as_ushort(__float2bfloat16_rn(e));
+      const long long flat = static_cast<long long>(row) * p.n + col;
+      const int pos = atomicAdd(&s_wcnt[warp], 1);
+      if (pos < WARP_CAP) {
+        st_idx[pos] = flat;
+        st_val[pos] = b16;
+      } else {
+        append(flat, b16);  // staging slice full (a very dense stretch): straight to the list
+      }
+    }
+  };
 
+  const int nblocks = (p.n + 63) / 64;
   for (int sb0 = s.row0; sb0 < s.row1; sb0 += CS_ROWS) {
     const int sb1 = min(s.row1, sb0 + CS_ROWS);
-    stage_coeff<RP>(p.c, p.r, sb0, sb1, s_c);
-    for (int cb = 0; cb < p.n; cb += ctn * CPT) {
-      const int col = cb + ct * CPT;
-      const bool active = (col < p.n) && (lane_row < rl);
-      float qreg[CPT][RP];
-      if (active) load_q<RP, CPT>(p.q, p.r, col, p.n, qreg);
-      const int step = rl * ROWS_UNROLL;
-      const int iters = (sb1 - sb0 + step - 1) / step;  // the same for every thread of the CTA: warps stay converged at the flush
-      for (int it = 0; it < iters; ++it) {
+    __syncthreads();  // the previous sub-slab's coefficients are no longer being read
+    for (int i = threadIdx.x; i < CS_ROWS * HW; i += blockDim.x) {
+      const int lr = i / HW, k = 2 * (i - lr * HW);
+      const int row = sb0 + lr;
+      uint32_t lo = 0u, hi = 0u;
+      if (row < sb1) {
+        const __nv_bfloat16* crow = p.c + static_cast<size_t>(row) * p.r;
+        if (k < p.r) lo = __bfloat16_as_ushort(crow[k]);
+        if (k + 1 < p.r) hi = __bfloat16_as_ushort(crow[k + 1]);
+      }
+      s_cb[i] = (lo | (hi << 16)) ^ 0x80008000u;  // A = -C
+    }
+    __syncthreads();
+    const int npairs = (sb1 - sb0 + 31) / 32;
+    for (int cb = warp; cb < nblocks; cb += nwarps) {
+      const int n0 = cb * 64;
+      uint32_t bq[8][KB];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        // the tile's column index g belongs to quad thread g / 2, element g % 2 of its j-th column pair
+        const int pc = n0 + (j < 4 ? 8 * (g >> 1) + 2 * j : 32 + 8 * (g >> 1) + 2 * (j - 4)) + (g & 1);
+#pragma unroll
+        for (int kb = 0; kb < KB; ++kb) bq[j][kb] = q_pair(p.q, p.r, p.n, pc, 2 * t + 8 * kb, qvec);
+      }
+      const bool lo_ok = n0 + 8 * t + 8 <= p.n, hi_ok = n0 + 32 + 8 * t + 8 <= p.n;
+      for (int sp2 = 0; sp2 < npairs; ++sp2) {
         __syncwarp();
         if (s_wcnt[warp] > WARP_CAP / 2) flush();
-        const int row = sb0 + it * step + lane_row;
-        XVec<CPT> xv[ROWS_UNROLL];
+        uint4 raw[2][4];
 #pragma unroll
-        for (int u = 0; u < ROWS_UNROLL; ++u) {
-          const int rr = row + u * rl;
-          if (active && rr < sb1) xv[u] = load_x<CPT>(p.x + static_cast<size_t>(rr) * p.ldx, col, p.n);
+        for (int h = 0; h < 2; ++h) {
+          const int rtop = sb0 + sp2 * 32 + h * 16 + g, rbot = rtop + 8;
+          const __nv_bfloat16* xt = p.x + static_cast<size_t>(rtop) * p.ldx + n0 + 8 * t;
+          const __nv_bfloat16* xb = p.x + static_cast<size_t>(rbot) * p.ldx + n0 + 8 * t;
+          const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
+          raw[h][0] = (rtop < sb1 && lo_ok) ? __ldg(reinterpret_cast<const uint4*>(xt)) : zero;
+          raw[h][1] = (rtop < sb1 && hi_ok) ? __ldg(reinterpret_cast<const uint4*>(xt + 32)) : zero;
+          raw[h][2] = (rbot < sb1 && lo_ok) ? __ldg(reinterpret_cast<const uint4*>(xb)) : zero;
+          raw[h][3] = (rbot < sb1 && hi_ok) ? __ldg(reinterpret_cast<const uint4*>(xb + 32)) : zero;
         }
 #pragma unroll
-        for (int u = 0; u < ROWS_UNROLL; ++u) {
-          const int rr = row + u * rl;
-          if (active && rr < sb1) {
-            float e[CPT];
-            residual_row_s<RP, CPT>(xv[u], s_c + (rr - sb0) * RP, qreg, e);
+        for (int h = 0; h < 2; ++h) {
+          const int lr = sp2 * 32 + h * 16 + g;
+          const int rtop = sb0 + lr;
+          uint32_t a[RP / 4];
+          if constexpr (RP == 8) {
+            a[0] = s_cb[lr * HW + t];
+            a[1] = s_cb[(lr + 8) * HW + t];
+          } else {
 #pragma unroll
-            for (int i = 0; i < CPT; ++i) {
-              if (col + i < p.n && !(fabsf(e[i]) < cut)) {
-                const unsigned short b16 = __bfloat16_as_ushort(__float2bfloat16_rn(e[i]));
-                const long long flat = static_cast<long long>(rr) * p.n + col + i;
-                const int pos = atomicAdd(&s_wcnt[warp], 1);
-                if (pos < WARP_CAP) {
-                  st_idx[pos] = flat;
-                  st_val[pos] = b16;
-                } else {
-                  append(flat, b16);  // staging slice full (a very dense stretch): straight to the list
-                }
-              }
+            for (int ks = 0; ks < RP / 16; ++ks) {
+              a[4 * ks + 0] = s_cb[lr * HW + 8 * ks + t];
+              a[4 * ks + 1] = s_cb[(lr + 8) * HW + 8 * ks + t];
+              a[4 * ks + 2] = s_cb[lr * HW + 8 * ks + t + 4];
+              a[4 * ks + 3] = s_cb[(lr + 8) * HW + 8 * ks + t + 4];
             }
+          }
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            const uint32_t wt = word_of(raw[h][j < 4 ? 0 : 1], j & 3);
+            const uint32_t wb = word_of(raw[h][j < 4 ? 2 : 3], j & 3);
+            float d[4] = {__uint_as_float(wt << 16), __uint_as_float(wt & 0xFFFF0000u), __uint_as_float(wb << 16), __uint_as_float(wb & 0xFFFF0000u)};
+            if constexpr (RP == 8) {
+              mma_k8(d, a[0], a[1], bq[j][0]);
+            } else {
+#pragma unroll
+              for (int ks = 0; ks < RP / 16; ++ks) mma_k16(d, a[4 * ks], a[4 * ks + 1], a[4 * ks + 2], a[4 * ks + 3], bq[j][2 * ks], bq[j][2 * ks + 1]);
+            }
+            const int col = n0 + (j < 4 ? 8 * t + 2 * j : 32 + 8 * t + 2 * (j - 4));
+            if (!(fabsf(d[0]) < cut)) push(rtop, sb1, col, d[0]);
+            if (!(fabsf(d[1]) < cut)) push(rtop, sb1, col + 1, d[1]);
+            if (!(fabsf(d[2]) < cut)) push(rtop + 8, sb1, col, d[2]);
+            if (!(fabsf(d[3]) < cut)) push(rtop + 8, sb1, col + 1, d[3]);
           }
         }
       }
@@ -820,7 +911,9 @@ __global__ void __launch_bounds__(512, 1) residual_candidates_kernel(const Selec
   if (!s_last) return;
   __threadfence();
   const int quota = p.quota[s.chunk];
-  hist_select(h2, quota > 0 ? static_cast<unsigned int>(quota) : 0u, s_part, s_out);
+  unsigned int* sh_hist = reinterpret_cast<unsigned int*>(sh_raw);  // the staging slices are idle now: 128 KB for the histogram
+  hist_stage(h2, sh_hist, s_part, s_out);
+  hist_locate(sh_hist, s_part, quota > 0 ? static_cast<unsigned int>(quota) : 0u, s_out);
   const int appended = *reinterpret_cast<volatile int*>(&sp.cand_count[s.chunk]);
   const bool valid = quota <= 0 || (s_out[0] >= t_lo && s_out[0] >= 0 && appended <= cap);
   if (threadIdx.x == 0) {
@@ -837,36 +930,67 @@ __global__ void __launch_bounds__(512, 1) residual_candidates_kernel(const Selec
   }
 }
 
-// Pass E: one thread per candidate.
-__global__ void __launch_bounds__(256) candidates_compact_kernel(const Select2Params sp, int parts2) {
+// Pass E: compaction of the candidate lists.  A CTA takes 1024 candidates at a time, decides, and reserves its output
+// range with one atomic (the positions inside it come from a CTA-wide prefix sum).
+constexpr int CE_ITEMS = 4;
+__global__ void __launch_bounds__(256) candidates_compact_kernel(const Select2Params sp, int ctas_per_chunk) {
   constexpr unsigned FULL = 0xffffffffu;
   const SelectParams& p = sp.base;
-  const int chunk = blockIdx.x / parts2, part = blockIdx.x - chunk * parts2;
+  __shared__ int s_warp[8];
+  __shared__ int s_base;
+  const int chunk = blockIdx.x / ctas_per_chunk, part = blockIdx.x - chunk * ctas_per_chunk;
   if (sp.fallback[chunk]) return;
   const int thr = p.thr_bin[chunk], need = p.thr_need[chunk], quota = p.quota[chunk], obase = p.out_offset[chunk];
   const int count = min(sp.cand_count[chunk], sp.cand_cap[chunk]);
   const int cbase = sp.cand_off[chunk];
   const float inv_scale = 1.f / *p.out_scale;
-  const int lane = threadIdx.x & 31;
-  for (int i0 = part * static_cast<int>(blockDim.x); i0 < count; i0 += parts2 * static_cast<int>(blockDim.x)) {
-    const int i = i0 + static_cast<int>(threadIdx.x);
-    bool take = false;
-    unsigned short b16 = 0;
-    if (i < count) {
-      b16 = sp.cand_val[cbase + i];
-      const int key = b16 & 0x7FFF;
-      take = key > thr;
-      if (!take && key == thr && need > 0) take = atomicAdd(&p.tie_count[chunk], 1) < need;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  constexpr int SPAN = 256 * CE_ITEMS;
+  for (int base0 = part * SPAN; base0 < count; base0 += ctas_per_chunk * SPAN) {
+    unsigned short b16[CE_ITEMS];
+    bool take[CE_ITEMS];
+    int mine = 0;
+#pragma unroll
+    for (int it = 0; it < CE_ITEMS; ++it) {
+      const int i = base0 + it * 256 + static_cast<int>(threadIdx.x);
+      take[it] = false;
+      b16[it] = 0;
+      if (i < count) {
+        b16[it] = sp.cand_val[cbase + i];
+        const int key = b16[it] & 0x7FFF;
+        take[it] = key > thr;
+        if (!take[it] && key == thr && need > 0) take[it] = atomicAdd(&p.tie_count[chunk], 1) < need;
+      }
+      mine += take[it] ? 1 : 0;
     }
-    const unsigned mask = __ballot_sync(FULL, take);
-    if (mask == 0u) continue;
-    int base = 0;
-    if (lane == (__ffs(mask) - 1)) base = atomicAdd(&p.out_count[chunk], __popc(mask));
-    base = __shfl_sync(FULL, base, __ffs(mask) - 1);
-    if (take) {
-      const int o = base + __popc(mask & ((1u << lane) - 1u));
-      if (o < quota) emit_entry(p, obase + o, sp.cand_idx[cbase + i], b16, inv_scale);
+    int incl = mine;
+#pragma unroll
+    for (int off = 1; off < 32; off <<= 1) {
+      const int v = __shfl_up_sync(FULL, incl, off);
+      if (lane >= off) incl += v;
     }
+    if (lane == 31) s_warp[warp] = incl;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      int total = 0;
+      for (int w = 0; w < 8; ++w) {
+        const int c = s_warp[w];
+        s_warp[w] = total;
+        total += c;
+      }
+      s_base = total > 0 ? atomicAdd(&p.out_count[chunk], total) : 0;
+    }
+    __syncthreads();
+    int o = s_base + s_warp[warp] + incl - mine;
+#pragma unroll
+    for (int it = 0; it < CE_ITEMS; ++it) {
+      if (take[it]) {
+        const int i = base0 + it * 256 + static_cast<int>(threadIdx.x);
+        if (o < quota) emit_entry(p, obase + o, sp.cand_idx[cbase + i], b16[it], inv_scale);
+        ++o;
+      }
+    }
+    __syncthreads();  // s_warp and s_base are rewritten by the next round
   }
 }
 
@@ -904,19 +1028,14 @@ static int launch_select(const SelectParams& p, int phase, cudaStream_t st) {
 }
 
 template <int RP>
-static int launch_sampled(const Select2Params& sp, cudaStream_t st) {
-  constexpr int CPT = 64 / RP;
+static int launch_sampled(const Select2Params& sp, int max_cap, cudaStream_t st) {
   const SelectParams& p = sp.base;
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= MAX_DEVICES) return -8;
-  int ctn = (p.n + CPT - 1) / CPT;
-  if (ctn > 512) ctn = 512;
-  int rl = 512 / ctn;
-  if (rl < 1) rl = 1;
-  const int threads = ((ctn * rl + 31) / 32) * 32;
   const int grid = p.nchunks * p.parts;
   const int smem_a = NBINS * 4;
-  const int smem_c = 16 * WARP_CAP * (8 + 2) + CS_ROWS * RP * 4;
+  int smem_c = 16 * WARP_CAP * (8 + 2) + CS_ROWS * RP * 2;
+  if (smem_c < NBINS * 4) smem_c = NBINS * 4;   // the tail scan stages the candidate histogram where the staging slices were
   static bool cfg[MAX_DEVICES] = {false};
   if (!cfg[dev]) {
     cudaError_t e = cudaFuncSetAttribute(residual_sample_kernel<RP>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_a);
@@ -926,10 +1045,11 @@ static int launch_sampled(const Select2Params& sp, cudaStream_t st) {
     cfg[dev] = true;
   }
   residual_sample_kernel<RP><<<grid, 512, smem_a, st>>>(sp);
-  residual_candidates_kernel<RP><<<grid, threads, smem_c, st>>>(sp, ctn, rl);
-  int parts2 = (2 * p.parts) > 64 ? 64 : 2 * p.parts;
-  if (parts2 < 1) parts2 = 1;
-  candidates_compact_kernel<<<p.nchunks * parts2, 256, 0, st>>>(sp, parts2);
+  residual_candidates_kernel<RP><<<grid, 512, smem_c, st>>>(sp);
+  int per_chunk = (max_cap + 256 * CE_ITEMS - 1) / (256 * CE_ITEMS);
+  if (per_chunk < 1) per_chunk = 1;
+  if (per_chunk > 2048) per_chunk = 2048;
+  candidates_compact_kernel<<<p.nchunks * per_chunk, 256, 0, st>>>(sp, per_chunk);
   return static_cast<int>(cudaGetLastError());
 }
 
@@ -980,16 +1100,17 @@ extern "C" int sb_residual_topk(const void* x, const void* c, const void* q, int
 //   work      int32 [12 * nchunks + 2], zeroed by the caller;
 //   cand_off / cand_cap  int32 [nchunks]: slot range of each chunk's candidate list inside cand_idx / cand_val;
 //   margin    fp32 [nchunks]: safety factor applied to the sample's estimate of the candidate count;
-//   cand_idx  int64 [sum cand_cap], cand_val uint16 [sum cand_cap].
+//   cand_idx  int64 [sum cand_cap], cand_val uint16 [sum cand_cap]; max_cap = the largest cand_cap (sizes pass E's grid).
+// n must be a multiple of 8 (16-byte row segments).
 extern "C" int sb_residual_topk_sampled(const void* x, const void* c, const void* q, int rows, int n, int r, int ldx, int chunk_rows,
                                         int nchunks, int parts, void* hist, void* hist2, int* work, const int* quota,
                                         const int* out_offset, const int* cand_off, const int* cand_cap, const float* margin,
-                                        long long* cand_idx, void* cand_val, int bits, int* idx32, long long* idx64, void* val,
-                                        float* scale, int* status, void* stream) {
+                                        long long* cand_idx, void* cand_val, int max_cap, int bits, int* idx32, long long* idx64,
+                                        void* val, float* scale, int* status, void* stream) {
   using namespace sb;
   if (rows <= 0 || n <= 0 || nchunks <= 0) return 0;
   if (r < 1 || r > 32) return -2;
-  if ((ldx & 7) || (reinterpret_cast<uintptr_t>(x) & 15) || (reinterpret_cast<uintptr_t>(c) & 15)) return -3;
+  if ((ldx & 7) || (n & 7) || (reinterpret_cast<uintptr_t>(x) & 15) || (reinterpret_cast<uintptr_t>(c) & 15)) return -3;
   Select2Params sp;
   SelectParams& p = sp.base;
   p.x = static_cast<const __nv_bfloat16*>(x);
@@ -1012,7 +1133,7 @@ extern "C" int sb_residual_topk_sampled(const void* x, const void* c, const void
   sp.cand_idx = cand_idx; sp.cand_val = static_cast<unsigned short*>(cand_val);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const int rp = r <= 8 ? 8 : (r <= 16 ? 16 : 32);
-  int rc = rp == 8 ? launch_sampled<8>(sp, st) : rp == 16 ? launch_sampled<16>(sp, st) : launch_sampled<32>(sp, st);
+  int rc = rp == 8 ? launch_sampled<8>(sp, max_cap, st) : rp == 16 ? launch_sampled<16>(sp, max_cap, st) : launch_sampled<32>(sp, max_cap, st);
   if (rc) return rc;
   // exact passes, gated per chunk by the fallback flags (they return at once for chunks the sampled passes served)
   rc = rp == 8 ? launch_select<8>(p, 0, st) : rp == 16 ? launch_select<16>(p, 0, st) : launch_select<32>(p, 0, st);

@@ -52,35 +52,41 @@ class _ColumnSums:
 
     The backward of an activation writes ``dX`` and can sum its columns on the way; the backward of the linear layer that
     fed the activation runs next and needs exactly those sums for its bias gradient.  The two are separate autograd nodes,
-    so the sums travel through this one-entry mailbox keyed by the matrix's storage address, shape and version.  The
-    mailbox keeps the matrix itself alive while its entry exists, so the address cannot be recycled for another tensor
-    and a match is never a coincidence.  An entry offered by a producer is dropped when it is taken; an entry made by
-    ``bias_grad`` itself stays until the next offer, so that two layers that receive the same gradient tensor (the
-    attention output projection and the MLP output projection of a parallel-residual block) sum it once.  A lookup that
-    does not match leaves the caller to compute the sums.
+    so the sums travel through this mailbox keyed by the matrix's storage address, shape and version.  The mailbox keeps
+    the matrix itself alive while its entry exists, so the address cannot be recycled for another tensor and a match is
+    never a coincidence.  Two slots: ``offered`` holds a producer's by-product and is emptied when it is taken;
+    ``remembered`` holds sums that ``bias_grad`` computed itself and stays until the next such computation, so that two
+    layers that receive the same gradient tensor (the attention output projection and the MLP output projection of a
+    parallel-residual block, whose backward passes are separated by the whole MLP) sum it once.  A lookup that matches
+    neither slot leaves the caller to compute the sums.
     """
 
     def __init__(self):
-        self.clear()
+        self.offered = None        # (key, sums, matrix)
+        self.remembered = None
 
     @staticmethod
     def _key(t: torch.Tensor, cols: int):
         return (t.data_ptr(), t.numel(), cols, t._version, t.device.index)
 
     def offer(self, matrix: torch.Tensor, sums: torch.Tensor, single_use: bool) -> None:
-        self.key, self.sums, self.matrix, self.single_use = self._key(matrix, sums.numel()), sums, matrix, single_use
+        entry = (self._key(matrix, sums.numel()), sums, matrix)
+        if single_use:
+            self.offered = entry
+        else:
+            self.remembered = entry
 
     def take(self, matrix: torch.Tensor, cols: int):
-        if self.key is None or self.key != self._key(matrix, cols):
-            return None
-        sums = self.sums
-        if self.single_use:
-            self.clear()
-        return sums
+        key = self._key(matrix, cols)
+        if self.offered is not None and self.offered[0] == key:
+            sums, self.offered = self.offered[1], None
+            return sums
+        if self.remembered is not None and self.remembered[0] == key:
+            return self.remembered[1]
+        return None
 
     def clear(self) -> None:
-        self.key = self.sums = self.matrix = None
-        self.single_use = False
+        self.offered = self.remembered = None
 
 
 column_sums = _ColumnSums()

@@ -63,7 +63,7 @@ _SAMPLE_STRIDE = 16
 
 def _sampled_ok(quotas: list[int], rows: int, n: int, chunk_rows: int) -> bool:
     """Whether every chunk is large and sparse enough for the sampled-threshold selection to pay off."""
-    if os.environ.get("STACR_SELECT_SAMPLED", "1") != "1" or n < 64:
+    if os.environ.get("STACR_SELECT_SAMPLED", "1") != "1" or n < 64 or n % 8:
         return False
     for i, k in enumerate(quotas):
         elems = (min(rows, (i + 1) * chunk_rows) - i * chunk_rows) * n
@@ -92,7 +92,7 @@ def _select_meta(dev, quotas: list[int], sampled: bool):
                 caps.append(cap)
                 total_cap += cap
             rows_i += [coffs, caps]
-        meta = {"ints": torch.tensor(rows_i, dtype=torch.int32).to(dev), "cap": total_cap,
+        meta = {"ints": torch.tensor(rows_i, dtype=torch.int32).to(dev), "cap": total_cap, "max_cap": max(caps) if sampled else 0,
                 "margin": torch.tensor(margins, dtype=torch.float32).to(dev) if sampled else None}
         if len(_META) > 256:
             _META.clear()
@@ -142,7 +142,7 @@ def residual_topk(
         rc = lib.sb_residual_topk_sampled(
             _lib.ptr(x), _lib.ptr(coeff), _lib.ptr(basis_bf16), c_int(rows), c_int(n), c_int(r), c_int(x.stride(0)), c_int(chunk_rows),
             c_int(nchunks), c_int(parts), _lib.ptr(hist), _lib.ptr(hist2), _lib.ptr(work), _lib.ptr(ints[0]), _lib.ptr(ints[1]),
-            _lib.ptr(ints[2]), _lib.ptr(ints[3]), _lib.ptr(meta["margin"]), _lib.ptr(cand_idx), _lib.ptr(cand_val), c_int(bits),
+            _lib.ptr(ints[2]), _lib.ptr(ints[3]), _lib.ptr(meta["margin"]), _lib.ptr(cand_idx), _lib.ptr(cand_val), c_int(meta["max_cap"]), c_int(bits),
             _lib.ptr(idx if is32 else None), _lib.ptr(None if is32 else idx), _lib.ptr(val), _lib.ptr(scale),
             _lib.ptr(_lib.status_word(dev)), _lib.stream_ptr(),
         )

@@ -88,7 +88,7 @@ def test_bias_gradient_of_a_linear_feeding_gelu_comes_from_the_activation_backwa
     rb(F.gelu(ra(x))).square().mean().backward()
     for got, want in ((a.bias.grad, ra.bias.grad), (b.bias.grad, rb.bias.grad), (a.weight.grad, ra.weight.grad)):
         assert float((got - want).norm() / want.norm()) < 3e-2
-    assert nn_ops.column_sums.single_use is False
+    assert nn_ops.column_sums.offered is None
 
 
 @pytest.mark.parametrize("rows,v", [(515, 50304), (252, 1024), (7, 8)])
