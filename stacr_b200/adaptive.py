@@ -47,8 +47,20 @@ def _scale_for(t: torch.Tensor, qmax: float):
     return t, (scale if scale != 0 else amax).reshape(1)
 
 
+def _codec_on_device(t: torch.Tensor) -> bool:
+    return t.is_cuda and t.dtype in (torch.bfloat16, torch.float32) and t.numel() > 0
+
+
 def quantize_int8(tensor: torch.Tensor):
-    """Symmetric per-tensor int8 (range +-127).  Returns ``(int8 data, scale[1])``."""
+    """Symmetric per-tensor int8 (range +-127).  Returns ``(int8 data, scale[1])``.
+
+    bf16 / fp32 CUDA tensors are encoded by the kernel codec (one reduction pass for the maximum, one pass for the
+    codes, scale kept in fp32 so that it cannot underflow); everything else uses framework ops."""
+    if _codec_on_device(tensor):
+        from .ops import pack_ops
+
+        codes, scale = pack_ops.quantize_symmetric(tensor, 8)
+        return codes, scale
     if tensor.numel() == 0:
         return tensor.to(torch.int8), torch.ones(1, device=tensor.device, dtype=tensor.dtype)
     wide, scale = _scale_for(tensor, 127.0)
@@ -64,6 +76,11 @@ def dequantize_int8(quantized: torch.Tensor, scale: torch.Tensor) -> torch.Tenso
 def quantize_int4(tensor: torch.Tensor):
     """Symmetric per-tensor int4 (range +-7), stored as ``q + 8`` nibbles, two per byte."""
     n = tensor.numel()
+    if _codec_on_device(tensor):
+        from .ops import pack_ops
+
+        codes, scale = pack_ops.quantize_symmetric(tensor.reshape(-1), 4)
+        return codes, scale, n
     if n == 0:
         return tensor.to(torch.uint8), torch.ones(1, device=tensor.device, dtype=tensor.dtype), 0
     wide, scale = _scale_for(tensor.reshape(-1), 7.0)
@@ -507,7 +524,7 @@ class STACRFunction(torch.autograd.Function):
                 q = basis.to(out2d.dtype)
                 coeff = _kernel_project(act, basis) if _kernel_ok(act, weight) else act @ q
                 # relative residual energy by Pythagoras (Q orthonormal): sqrt(|X|^2 - |C|^2) / |X|
-                xn2, cn2 = act.float().square().sum(), coeff.float().square().sum()
+                xn2, cn2 = _sum_squares(act), _sum_squares(coeff)
                 energy = torch.sqrt((xn2 - cn2).clamp_min(0)) / (torch.sqrt(xn2) + 1e-8)
                 if layer is not None:
                     layer._publish_energy(energy, coeff)
@@ -605,6 +622,15 @@ def _kernel_dx(g2d, weight):
     return gemm(g2d.to(torch.bfloat16).contiguous(), _bf16_weight(weight).contiguous(), b_mn=True)
 
 
+def _sum_squares(t: torch.Tensor) -> torch.Tensor:
+    """fp32 ``sum t^2`` as a device scalar: one reduction kernel for bf16 / fp32 CUDA tensors (no fp32 copy of ``t``)."""
+    if _codec_on_device(t) and t.is_contiguous():
+        from .ops import pack_ops
+
+        return pack_ops.sum_squares(t)
+    return t.float().square().sum()
+
+
 def _kernel_project(act, basis):
     from .layers import _basis_views
     from .ops import stacr_ops
@@ -614,17 +640,53 @@ def _kernel_project(act, basis):
 
 
 def _select_with_kernels(act, coeff, q, runtime: _Runtime, weight):
-    cfg, mode = runtime.cfg, runtime.mode
-    if coeff is not None and _kernel_ok(act, weight) and mode == "topk" and not cfg.streaming_topk:
-        from .layers import _basis_views
-        from .ops import stacr_ops
+    """Residual selection of the adaptive engine on the selection kernels where the mode allows it.
 
-        k = int(act.numel() * runtime.budget)
+    * ``topk`` / ``sparse_only`` / ``adaptive_threshold``: the exact top-``k`` kernel (its sampled-threshold form *is* an
+      adaptive threshold followed by an exact trim; the framework form of ``adaptive_threshold`` keeps at most ``k`` entries
+      above a sampled quantile, of which the exact top-``k`` is the limit);
+    * ``block_sparse``: block energies in one pass over the input, ranked by the same kernel, values gathered;
+    * ``threshold``: everything the candidate pass finds above the fixed threshold.
+    The dense residual is never materialised on these paths.  Anything else (odd block sizes, tiny inputs, CPU) goes
+    through :func:`_select_adaptive`.
+    """
+    cfg, mode = runtime.cfg, runtime.mode
+    rows, n = act.shape
+    total = rows * n
+    if not (_kernel_ok(act, weight) and act.dtype == torch.bfloat16 and total > 0 and mode != "none" and total < 2**31 - 1):
+        return _select_adaptive(act, coeff, q, mode, runtime.budget, cfg, runtime.threshold)
+    from .layers import _basis_views, _zero_factors
+    from .ops import stacr_ops
+
+    x = act.contiguous()
+    if coeff is None:                                   # sparse_only: the "residual" is the input itself
+        cb, qb = _zero_factors(rows, n, x.device)
+    else:
+        cb = coeff.contiguous()
+        qb = _basis_views(runtime.layer._current_basis_for_kernels)[0] if runtime.layer is not None else q.contiguous()
+    k = int(total * runtime.budget)
+    if mode in ("topk", "sparse_only", "adaptive_threshold"):
         if k <= 0:
             return None, None
-        qb, _ = _basis_views(runtime.layer._current_basis_for_kernels) if runtime.layer is not None else (q.contiguous(), None)
-        idt = torch.int32 if act.numel() < 2**31 - 1 else torch.int64
-        idx, val, _ = stacr_ops.residual_topk(act.contiguous(), coeff.contiguous(), qb, [k], act.shape[0], 0, idt)
+        idx, val, _ = stacr_ops.residual_topk(x, cb, qb, [k], rows, 0, torch.int32)
+        return idx.long(), val
+    if mode == "block_sparse":
+        bs = cfg.residual_block_size
+        if k <= 0:
+            return None, None
+        per_row = n // bs if n % bs == 0 else 0
+        if per_row and bs % 8 == 0 and bs <= 256 and not (bs & (bs - 1)) and per_row % 8 == 0 and rows * per_row < 2**31 - 1:
+            energy = stacr_ops.residual_block_energy(x, cb, qb, bs)                      # [rows, n / bs]
+            zc, zq = _zero_factors(rows, per_row, x.device)
+            keep = max(1, k // bs)
+            blocks, _, _ = stacr_ops.residual_topk(energy.to(torch.bfloat16), zc, zq, [keep], rows, 0, torch.int32)
+            idx = (blocks.long()[:, None] * bs + torch.arange(bs, device=x.device)).reshape(-1)
+            return idx, stacr_ops.residual_gather(x, cb, qb, idx)
+        return _select_adaptive(act, coeff, q, mode, runtime.budget, cfg, runtime.threshold)
+    if mode == "threshold":
+        idx, val = stacr_ops.residual_above(x, cb, qb, float(runtime.threshold))
+        if idx.numel() == 0:
+            return None, None
         return idx.long(), val
     return _select_adaptive(act, coeff, q, mode, runtime.budget, cfg, runtime.threshold)
 

@@ -89,6 +89,10 @@ def compress_indices(
         return CompressedIndices(mode, row_ptrs=rp, col_indices=empty, **meta)
     if mode is IndexCompressionMode.NONE:
         return CompressedIndices(mode, col_indices=flat_indices, **meta)
+    if flat_indices.is_cuda and flat_indices.dtype in (torch.int32, torch.int64) and nnz < 2**31 - 1 and B_flat < 2**31 - 1 and N < 2**31 - 1:
+        packed = _compress_on_device(flat_indices, B_flat, N, mode, preserve_order, meta)
+        if packed is not None:
+            return packed
     wide = flat_indices.long()
     if mode is IndexCompressionMode.CSR:
         rows = torch.div(wide, N, rounding_mode="floor")
@@ -110,6 +114,26 @@ def compress_indices(
         inverse = torch.argsort(order) if preserve_order else None
         return CompressedIndices(mode, col_indices=gaps, delta_base=base, sort_indices=inverse, **meta)
     raise ValueError(f"Unknown compression mode: {mode}")
+
+
+def _compress_on_device(flat_indices, B_flat, N, mode, preserve_order, meta):
+    """The same encodings produced by the counting-sort / in-row-sort kernels (``ops/csrc/index_pack.cu``): no library sort,
+    no ``bincount``/``cumsum`` chain.  The order inside a CSR row is the scatter's, not the input's; the inverse permutation
+    that comes with it restores the original order exactly as the framework path's does.  ``None`` = not handled here."""
+    from .ops import pack_ops
+
+    if mode is IndexCompressionMode.CSR:
+        row_ptr, cols, _, inverse = pack_ops.csr_pack(flat_indices, B_flat, N, narrow_cols=N < 32768, want_order=False, want_inverse=preserve_order)
+        return CompressedIndices(mode, row_ptrs=row_ptr, col_indices=cols, sort_indices=None if inverse is None else inverse.long(), **meta)
+    if mode is IndexCompressionMode.DELTA:
+        out = pack_ops.delta_pack(flat_indices, B_flat, N, want_inverse=preserve_order)
+        if out is None:
+            return None
+        base, gaps, inverse, max_gap = out
+        base = base.to(torch.int32 if B_flat * N <= 2**31 else torch.int64)
+        gaps = gaps.to(_narrowest_signed(max_gap)) if gaps.numel() else torch.empty(0, dtype=torch.int16, device=flat_indices.device)
+        return CompressedIndices(mode, col_indices=gaps, delta_base=base, sort_indices=None if inverse is None else inverse.long(), **meta)
+    return None
 
 
 def decompress_indices(compressed: CompressedIndices, restore_order: bool = True) -> torch.Tensor:

@@ -565,6 +565,7 @@ struct Select2Params {
   const float* margin;        // [nchunks] safety factor on the sample's estimate
   long long* cand_idx;
   unsigned short* cand_val;
+  float fixed_cut;            // >= 0: pass C lists every entry with |e| >= fixed_cut instead of using the sampled bin
 };
 
 // Whole CTA (blockDim.x >= SCAN_T).  Copies a chunk's histogram (written by other CTAs' atomics: read through L2) into
@@ -757,6 +758,7 @@ __global__ void __launch_bounds__(512, 1) residual_candidates_kernel(const Selec
   if (t_lo >= NBINS) cut = __int_as_float(0x7f800000);   // nothing is wanted
   else if (t_lo > 0) cut = 0.5f * (bf16_bits_to_float(static_cast<unsigned short>(t_lo)) + bf16_bits_to_float(static_cast<unsigned short>(t_lo - 1)));
   else cut = 0.f;
+  if (sp.fixed_cut >= 0.f) cut = sp.fixed_cut;
   const bool qvec = (p.r == RP);   // basis rows are RP * 2 bytes: pairs are 4-byte aligned
   int lmax = 0;
   if (lane == 0) s_wcnt[warp] = 0;
@@ -1028,6 +1030,23 @@ static int launch_select(const SelectParams& p, int phase, cudaStream_t st) {
 }
 
 template <int RP>
+static int launch_candidates_only(const Select2Params& sp, cudaStream_t st) {
+  const SelectParams& p = sp.base;
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= MAX_DEVICES) return -8;
+  int smem_c = 16 * WARP_CAP * (8 + 2) + CS_ROWS * RP * 2;
+  if (smem_c < NBINS * 4) smem_c = NBINS * 4;
+  static bool cfg[MAX_DEVICES] = {false};
+  if (!cfg[dev]) {
+    cudaError_t e = cudaFuncSetAttribute(residual_candidates_kernel<RP>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_c);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    cfg[dev] = true;
+  }
+  residual_candidates_kernel<RP><<<p.nchunks * p.parts, 512, smem_c, st>>>(sp);
+  return static_cast<int>(cudaGetLastError());
+}
+
+template <int RP>
 static int launch_sampled(const Select2Params& sp, int max_cap, cudaStream_t st) {
   const SelectParams& p = sp.base;
   int dev = 0;
@@ -1131,6 +1150,7 @@ extern "C" int sb_residual_topk_sampled(const void* x, const void* c, const void
   sp.hist2 = static_cast<unsigned int*>(hist2);
   sp.cand_off = cand_off; sp.cand_cap = cand_cap; sp.margin = margin;
   sp.cand_idx = cand_idx; sp.cand_val = static_cast<unsigned short*>(cand_val);
+  sp.fixed_cut = -1.f;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const int rp = r <= 8 ? 8 : (r <= 16 ? 16 : 32);
   int rc = rp == 8 ? launch_sampled<8>(sp, max_cap, st) : rp == 16 ? launch_sampled<16>(sp, max_cap, st) : launch_sampled<32>(sp, max_cap, st);
@@ -1142,6 +1162,40 @@ extern "C" int sb_residual_topk_sampled(const void* x, const void* c, const void
   rc = static_cast<int>(cudaGetLastError());
   if (rc) return rc;
   return rp == 8 ? launch_select<8>(p, 1, st) : rp == 16 ? launch_select<16>(p, 1, st) : launch_select<32>(p, 1, st);
+}
+
+// Every residual entry with |e| >= cut, as (flat index, bf16 bits) pairs in cand_idx / cand_val (capacity cap; entries
+// beyond it are counted but dropped).  work: int32 [14] zeroed by the caller, work[6] returns the number found;
+// hist2: uint32 [32768] zeroed (receives the magnitude histogram of what was found); meta: int32 [4] = {0, 0, 0, cap}.
+// One pass over X on the tensor-core residual kernel of the sampled selection; n % 8 == 0.
+extern "C" int sb_residual_above(const void* x, const void* c, const void* q, int rows, int n, int r, int ldx, float cut, int parts, void* hist,
+                                 void* hist2, int* work, const int* meta, long long* cand_idx, void* cand_val, float* scale, int* status,
+                                 void* stream) {
+  using namespace sb;
+  if (rows <= 0 || n <= 0) return 0;
+  if (r < 1 || r > 32 || cut < 0.f) return -2;
+  if ((ldx & 7) || (n & 7) || (reinterpret_cast<uintptr_t>(x) & 15) || (reinterpret_cast<uintptr_t>(c) & 15)) return -3;
+  Select2Params sp;
+  SelectParams& p = sp.base;
+  p.x = static_cast<const __nv_bfloat16*>(x);
+  p.c = static_cast<const __nv_bfloat16*>(c);
+  p.q = static_cast<const __nv_bfloat16*>(q);
+  p.rows = rows; p.n = n; p.r = r; p.ldx = ldx;
+  p.chunk_rows = rows; p.parts = parts; p.nchunks = 1;
+  p.hist = static_cast<unsigned int*>(hist);
+  p.thr_bin = work; p.thr_need = work + 1; p.max_bin = work + 2; p.tie_count = work + 3; p.out_count = work + 4;
+  sp.cand_bin = work + 5; sp.cand_count = work + 6; sp.fallback = work + 7; sp.done_a = work + 8; sp.done_c = work + 9;
+  sp.done_all = work + 12; sp.gmax = work + 13;
+  p.quota = meta; p.out_offset = meta + 1;          // quota 0: the tail computes no threshold
+  p.bits = 0; p.out_idx32 = nullptr; p.out_idx64 = nullptr; p.out_val = nullptr; p.out_scale = scale;
+  p.status = status; p.gate = nullptr;
+  sp.hist2 = static_cast<unsigned int*>(hist2);
+  sp.cand_off = meta + 2; sp.cand_cap = meta + 3; sp.margin = nullptr;
+  sp.cand_idx = cand_idx; sp.cand_val = static_cast<unsigned short*>(cand_val);
+  sp.fixed_cut = cut;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int rp = r <= 8 ? 8 : (r <= 16 ? 16 : 32);
+  return rp == 8 ? launch_candidates_only<8>(sp, st) : rp == 16 ? launch_candidates_only<16>(sp, st) : launch_candidates_only<32>(sp, st);
 }
 
 extern "C" int sb_residual_gather(const void* x, const void* c, const void* q, int n, int r, int ldx,

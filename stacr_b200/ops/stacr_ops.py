@@ -164,6 +164,50 @@ def residual_topk(
     return idx, val, scale
 
 
+_ABOVE_CAP: dict = {}
+
+
+def residual_above(x: torch.Tensor, coeff: torch.Tensor, basis_bf16: torch.Tensor, threshold: float):
+    """Flat indices (int64) and bf16 values of the residual entries with ``|e| > threshold``: one pass over ``X``.
+
+    The number of hits is data dependent, so the call ends with a host read of one counter (as ``nonzero`` would); the list
+    capacity is remembered per shape from call to call and the pass is repeated once when it proves too small.
+    """
+    rows, n = x.shape
+    dev = x.device
+    if n % 8:
+        e = (x.float() - coeff.float() @ basis_bf16.float().t()).to(torch.bfloat16).reshape(-1)
+        idx = (e.float().abs() > threshold).nonzero(as_tuple=True)[0]
+        return idx, e[idx]
+    key = (dev.index, rows, n)
+    cap = _ABOVE_CAP.get(key, max(4096, rows * n // 64))
+    cut = max(0.0, float(threshold) * (1.0 - 2.0 ** -7))      # every value whose bf16 rounding can exceed the threshold
+    lib = _lib.load()
+    parts = _lib.sm_count(dev)
+    while True:
+        scratch = torch.zeros(2 * _NBINS + 14, dtype=torch.int32, device=dev)
+        hist, hist2, work = scratch[:_NBINS], scratch[_NBINS: 2 * _NBINS], scratch[2 * _NBINS:]
+        meta = torch.tensor([0, 0, 0, cap], dtype=torch.int32).to(dev)
+        cand_idx = torch.empty(cap, dtype=torch.int64, device=dev)
+        cand_val = torch.empty(cap, dtype=torch.bfloat16, device=dev)
+        scale = torch.empty((), dtype=torch.float32, device=dev)
+        rc = lib.sb_residual_above(
+            _lib.ptr(x), _lib.ptr(coeff), _lib.ptr(basis_bf16), c_int(rows), c_int(n), c_int(coeff.shape[1]), c_int(x.stride(0)), c_float(cut),
+            c_int(parts), _lib.ptr(hist), _lib.ptr(hist2), _lib.ptr(work), _lib.ptr(meta), _lib.ptr(cand_idx), _lib.ptr(cand_val), _lib.ptr(scale),
+            _lib.ptr(_lib.status_word(dev)), _lib.stream_ptr(),
+        )
+        _lib.check_rc(rc, "sb_residual_above")
+        _lib.count(1)
+        found = int(work[6].item())
+        if found <= cap:
+            break
+        cap = int(found * 1.25) + 1024
+    _ABOVE_CAP[key] = max(4096, int(found * 1.5))
+    idx, val = cand_idx[:found], cand_val[:found]
+    keep = val.float().abs() > threshold
+    return idx[keep], val[keep]
+
+
 _LAST_SAMPLED_WORK = None
 
 

@@ -266,3 +266,40 @@ def test_layer_forward_backward_on_kernel_path(mode):
     cos = float(S.cosine_similarity(ref.weight.grad, lin.weight.grad))
     assert cos > 0.9, cos
     torch.testing.assert_close(lin.bias.grad, ref.bias.grad, rtol=2e-2, atol=2e-1)
+
+
+@pytest.mark.parametrize("mode", ["topk", "block_sparse", "adaptive_threshold", "threshold", "sparse_only"])
+def test_adaptive_engine_selects_on_kernels_without_a_dense_residual(mode, monkeypatch):
+    """Every residual mode of the adaptive engine on a bf16 CUDA layer runs on the selection kernels (the framework
+    selector is not reached) and still trains: the weight gradient stays close to the dense one."""
+    from stacr_b200 import adaptive
+
+    torch.manual_seed(0)
+    lin = torch.nn.Linear(512, 256).cuda()
+    cfg = adaptive.STACRConfig(rank=8, residual_mode=mode, residual_budget=0.02, residual_threshold=1.5, warmup_steps=0, quantize_coefficients=True,
+                               quantize_residuals=True, residual_quantize_bits=8, update_trigger="fixed", update_interval=1000)
+    layer = adaptive.STACRLinear(512, 256, config=cfg).cuda()
+    layer.linear.load_state_dict(lin.state_dict())
+    calls = {"n": 0}
+    real = adaptive._select_adaptive
+
+    def spy(*a, **k):
+        calls["n"] += 1
+        return real(*a, **k)
+
+    monkeypatch.setattr(adaptive, "_select_adaptive", spy)
+    base = torch.randn(2048, 8, device="cuda") @ torch.randn(8, 512, device="cuda")
+    x = (base + 0.2 * torch.randn(2048, 512, device="cuda")).requires_grad_(True)
+    layer.train()
+    for _ in range(2):                                   # first call initialises the basis
+        layer.zero_grad()
+        with torch.autocast("cuda", dtype=torch.bfloat16):
+            y = layer(x)
+        y.float().square().mean().backward()
+    assert calls["n"] == 0
+    with torch.autocast("cuda", dtype=torch.bfloat16):
+        yr = lin(x)
+    yr.float().square().mean().backward()
+    got, want = layer.linear.weight.grad.float().reshape(-1), lin.weight.grad.float().reshape(-1)
+    cos = float(torch.dot(got, want) / (got.norm() * want.norm()))
+    assert cos > (0.6 if mode == "sparse_only" else 0.9), cos
