@@ -600,7 +600,9 @@ def _to_host(t: torch.Tensor) -> torch.Tensor:
 def _kernel_ok(x2d: torch.Tensor, weight: torch.Tensor) -> bool:
     if not x2d.is_cuda:
         return False
-    dt = torch.get_autocast_dtype("cuda") if torch.is_autocast_enabled("cuda") else torch.promote_types(x2d.dtype, weight.dtype)
+    # the dtype the product is formed in: autocast's when it is on, else the activation's own (inside the engine's
+    # autocast-off regions the operands have already been cast, and the weight is cast to the activation dtype)
+    dt = torch.get_autocast_dtype("cuda") if torch.is_autocast_enabled("cuda") else x2d.dtype
     return dt == torch.bfloat16 and x2d.shape[1] % 8 == 0 and weight.shape[1] % 8 == 0 and weight.shape[0] % 8 == 0
 
 

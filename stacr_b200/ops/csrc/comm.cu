@@ -172,6 +172,60 @@ __global__ void __launch_bounds__(512) allreduce_multimem_kernel(const CommArgs 
   rank_barrier(a, 1, &s_fail);
 }
 
+// Reduce-scatter with caller-chosen ownership: every rank reduces the part [own_lo, own_hi) of [lo, hi) that it owns
+// (summing all ranks' copies, scaled) and stores the result into ITS OWN copy only.  Nothing is broadcast: the consumer
+// of the reduced gradient is the owner's shard of the optimizer.  Half the NVLink traffic of the all-reduce above.
+__global__ void __launch_bounds__(512) reduce_to_owner_kernel(const CommArgs a, long long own_lo, long long own_hi) {
+  __shared__ int s_fail;
+  __shared__ unsigned long long s_peers[MAX_RANKS];
+  if (threadIdx.x == 0) s_fail = 0;
+  if (threadIdx.x < a.world) s_peers[threadIdx.x] = a.peer_ptrs[threadIdx.x];
+  __syncthreads();
+  if (!rank_barrier(a, 0, &s_fail)) return;   // every rank's contribution to [lo, hi) is complete
+  const long long b = (own_lo > a.lo ? own_lo : a.lo) / 4, e = (own_hi < a.hi ? own_hi : a.hi) / 4;   // 16-byte elements
+  const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+  float4* mine = reinterpret_cast<float4*>(s_peers[a.rank]);
+  constexpr int UNROLL = 8;
+  for (long long i0 = b + blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i0 < e; i0 += stride * UNROLL) {
+    float4 acc[UNROLL];
+    if (a.mc_ptr != 0) {
+#pragma unroll
+      for (int u = 0; u < UNROLL; ++u) {
+        const long long i = i0 + u * stride;
+        acc[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (i < e) {
+          const float* addr = reinterpret_cast<const float*>(a.mc_ptr) + i * 4;
+          asm volatile("multimem.ld_reduce.relaxed.sys.global.add.v4.f32 {%0, %1, %2, %3}, [%4];"
+                       : "=f"(acc[u].x), "=f"(acc[u].y), "=f"(acc[u].z), "=f"(acc[u].w)
+                       : "l"(addr)
+                       : "memory");
+        }
+      }
+    } else {
+#pragma unroll
+      for (int u = 0; u < UNROLL; ++u) acc[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+      for (int p = 0; p < a.world; ++p) {
+        const int src = (a.rank + p) % a.world;
+        const float4* base = reinterpret_cast<const float4*>(s_peers[src]);
+#pragma unroll
+        for (int u = 0; u < UNROLL; ++u) {
+          const long long i = i0 + u * stride;
+          if (i < e) {
+            const float4 v = base[i];
+            acc[u].x += v.x; acc[u].y += v.y; acc[u].z += v.z; acc[u].w += v.w;
+          }
+        }
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < UNROLL; ++u) {
+      const long long i = i0 + u * stride;
+      if (i < e) mine[i] = make_float4(acc[u].x * a.scale, acc[u].y * a.scale, acc[u].z * a.scale, acc[u].w * a.scale);
+    }
+  }
+  rank_barrier(a, 1, &s_fail);   // no rank may overwrite its contribution while an owner is still reading it
+}
+
 // Every rank broadcasts its own slice of [lo, hi) (scaled) to all ranks: the second half of an all-reduce whose
 // first half (the reduce-scatter) was done by the producing kernels with red.add into the owner's copy.
 __global__ void __launch_bounds__(512) allgather_slices_kernel(const CommArgs a) {
@@ -330,6 +384,21 @@ extern "C" int sb_allgather_slices(const void* peer_ptrs, const void* flag_ptrs,
   const long long vecs = (hi - lo) / 4 / world;
   const int grid = comm_grid(vecs, sms);
   allgather_slices_kernel<<<grid, 512, 0, static_cast<cudaStream_t>(stream)>>>(a);
+  return static_cast<int>(cudaGetLastError());
+}
+
+// Reduce [lo, hi) across ranks into the owner's copy: this rank reduces [own_lo, own_hi) (clipped to [lo, hi); may be
+// empty) and stores it locally.  mc_ptr != 0 selects the in-switch reduction.  All bounds are multiples of 4 elements.
+extern "C" int sb_reduce_to_owner(const void* peer_ptrs, const void* flag_ptrs, unsigned long long mc_ptr, int rank, int world, long long lo,
+                                  long long hi, long long own_lo, long long own_hi, float scale, int epoch, int sms, int* status, void* stream) {
+  using namespace sb;
+  if (world < 1 || world > MAX_RANKS) return -2;
+  if ((lo & 3) || (hi & 3) || (own_lo & 3) || (own_hi & 3) || hi < lo) return -3;
+  CommArgs a{static_cast<const unsigned long long*>(peer_ptrs), static_cast<const unsigned long long*>(flag_ptrs), mc_ptr, rank, world,
+             lo, hi, scale, epoch, status, sb::comm_wait_ns()};
+  const long long b = own_lo > lo ? own_lo : lo, e = own_hi < hi ? own_hi : hi;
+  const int grid = comm_grid(e > b ? (e - b) / 4 : 0, sms);
+  reduce_to_owner_kernel<<<grid, 512, 0, static_cast<cudaStream_t>(stream)>>>(a, own_lo, own_hi);
   return static_cast<int>(cudaGetLastError());
 }
 

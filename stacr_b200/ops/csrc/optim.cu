@@ -26,7 +26,23 @@ struct TensorDesc {
   float* m_absmax;
   float* v_absmax;
   long long numel;
+  // NVSwitch multicast address of the bf16 copy (0 = none).  When set, the updated weight is stored through it, so the
+  // store itself delivers the value to every rank's copy: a rank that updates only its shard of the parameters leaves
+  // all ranks' bf16 weights current without a separate all-gather.  Requires 16-byte aligned full vectors.
+  unsigned long long shadow_mc;
 };
+
+__device__ __forceinline__ void store_shadow(const TensorDesc& t, long long i0, const float (&p)[8]) {
+  const uint4 w = make_uint4(pack_bf16x2(p[0], p[1]), pack_bf16x2(p[2], p[3]), pack_bf16x2(p[4], p[5]), pack_bf16x2(p[6], p[7]));
+  if (t.shadow_mc) {
+    __nv_bfloat16* addr = reinterpret_cast<__nv_bfloat16*>(t.shadow_mc) + i0;
+    asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(__uint_as_float(w.x)), "f"(__uint_as_float(w.y)),
+                 "f"(__uint_as_float(w.z)), "f"(__uint_as_float(w.w))
+                 : "memory");
+  } else {
+    *reinterpret_cast<uint4*>(t.shadow + i0) = w;
+  }
+}
 
 struct ChunkDesc {
   int tensor;
@@ -165,7 +181,7 @@ __global__ void __launch_bounds__(256) adamw_8bit_kernel(const TensorDesc* __res
   if (vec) {
     *reinterpret_cast<float4*>(t.param + i0) = *reinterpret_cast<const float4*>(p);
     *reinterpret_cast<float4*>(t.param + i0 + 4) = *reinterpret_cast<const float4*>(p + 4);
-    if (t.shadow) *reinterpret_cast<uint4*>(t.shadow + i0) = make_uint4(pack_bf16x2(p[0], p[1]), pack_bf16x2(p[2], p[3]), pack_bf16x2(p[4], p[5]), pack_bf16x2(p[6], p[7]));
+    if (t.shadow) store_shadow(t, i0, p);
     if (q8) {
       *reinterpret_cast<uint2*>(t.m8 + i0) = *reinterpret_cast<const uint2*>(cm);
       *reinterpret_cast<uint2*>(t.v8 + i0) = *reinterpret_cast<const uint2*>(cv);

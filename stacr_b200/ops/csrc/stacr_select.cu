@@ -645,27 +645,46 @@ __global__ void __launch_bounds__(512, 1) residual_sample_kernel(const Select2Pa
   const int chunk = blockIdx.x / p.parts, part = blockIdx.x - chunk * p.parts;
   const int c0 = chunk * p.chunk_rows, c1 = min(p.rows, c0 + p.chunk_rows);
   const int nlines = (p.n + SAMPLE_LINE - 1) / SAMPLE_LINE;
-  const int per_row = (nlines + SAMPLE_STRIDE - 1) / SAMPLE_STRIDE;
+  // A group of RP threads owns one 64-column line position and a subset of the rows sampled there, so the basis rows of
+  // its columns are loaded once and the row loads (4 in flight per thread) are independent of one another.
+  constexpr int SU = 4;
   const int groups = blockDim.x / RP, gid = threadIdx.x / RP, sub = threadIdx.x - gid * RP;
-  const long long items = static_cast<long long>(c1 - c0) * per_row;
+  const int G = p.parts * groups;                       // groups working on this chunk
+  const int nslots = G / nlines > 0 ? G / nlines : 1;   // row subsets per line position
+  const int tasks = nlines * nslots;
   __syncthreads();
-  for (long long item = static_cast<long long>(part) * groups + gid; item < items; item += static_cast<long long>(p.parts) * groups) {
-    const int row = c0 + static_cast<int>(item / per_row);
-    const int j = static_cast<int>(item - static_cast<long long>(row - c0) * per_row);
-    const int line = ((SAMPLE_STRIDE - (row % SAMPLE_STRIDE)) % SAMPLE_STRIDE) + j * SAMPLE_STRIDE;
+  for (int tk = part * groups + gid; tk < tasks; tk += G) {
+    const int line = tk % nlines, slot = tk / nlines;
     const int col = line * SAMPLE_LINE + sub * CPT;
-    if (line >= nlines || col >= p.n) continue;
-    const XVec<CPT> xv = load_x<CPT>(p.x + static_cast<size_t>(row) * p.ldx, col, p.n);
-    const CVec<RP> cv = load_c<RP>(p.c + static_cast<size_t>(row) * p.r, p.r);
+    if (col >= p.n) continue;
     float qreg[CPT][RP];
     load_q<RP, CPT>(p.q, p.r, col, p.n, qreg);
-    float e[CPT];
-    residual_row<RP, CPT>(xv, cv, qreg, e);
+    const int first = c0 + ((SAMPLE_STRIDE - ((line + c0) % SAMPLE_STRIDE)) % SAMPLE_STRIDE) + slot * SAMPLE_STRIDE;
+    const int step = SAMPLE_STRIDE * nslots;
+    for (int row = first; row < c1; row += step * SU) {
+      XVec<CPT> xv[SU];
+      CVec<RP> cv[SU];
 #pragma unroll
-    for (int i = 0; i < CPT; ++i) {
-      if (col + i < p.n) {
-        const unsigned short key = __bfloat16_as_ushort(__float2bfloat16_rn(e[i])) & 0x7FFF;
-        atomicAdd(&sh_hist[key], 1u);
+      for (int u = 0; u < SU; ++u) {
+        const int rr = row + u * step;
+        if (rr < c1) {
+          xv[u] = load_x<CPT>(p.x + static_cast<size_t>(rr) * p.ldx, col, p.n);
+          cv[u] = load_c<RP>(p.c + static_cast<size_t>(rr) * p.r, p.r);
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < SU; ++u) {
+        const int rr = row + u * step;
+        if (rr >= c1) continue;
+        float e[CPT];
+        residual_row<RP, CPT>(xv[u], cv[u], qreg, e);
+#pragma unroll
+        for (int i = 0; i < CPT; ++i) {
+          if (col + i < p.n) {
+            const unsigned short key = __bfloat16_as_ushort(__float2bfloat16_rn(e[i])) & 0x7FFF;
+            atomicAdd(&sh_hist[key], 1u);
+          }
+        }
       }
     }
   }
@@ -729,6 +748,13 @@ __device__ __forceinline__ uint32_t word_of(const uint4& v, int i) { return i ==
 // 32 at a time.  Within a block thread t of a quad owns columns [8t, 8t+8) and [32+8t, 32+8t+8) of each of its rows (two
 // 16-byte loads per row), and the MMA's column index is mapped onto those physical columns, so the loads are full
 // sectors and the accumulator registers already hold the thread's own columns.
+//
+// The tensor-core result only *detects*: a compare per element sets a bit in a per-thread mask (no branch in the tile
+// loop).  After 32 rows the marked positions of the whole warp are enumerated into the warp's staging slice as
+// (row, column) pairs with ballot prefix sums, and the lanes then recompute those few entries, one each, with the chained
+// FMA arithmetic of the exact passes, so the stored values are bit-identical to theirs.  Detection uses a cut a little
+// below the bin edge to absorb the difference between the two summation orders; the final threshold has to lie strictly
+// above the candidate bin for the chunk to count as served, so an entry missed at the very edge can never matter.
 template <int RP>
 __global__ void __launch_bounds__(512, 1) residual_candidates_kernel(const Select2Params sp) {
   constexpr unsigned FULL = 0xffffffffu;
@@ -736,35 +762,34 @@ __global__ void __launch_bounds__(512, 1) residual_candidates_kernel(const Selec
   constexpr int KB = RP / 8;     // basis registers per 8-column tile
   const SelectParams& p = sp.base;
   extern __shared__ unsigned char sh_raw[];
-  __shared__ int s_wcnt[16];
   __shared__ unsigned int s_part[SCAN_T];
   __shared__ int s_out[4];
   __shared__ int s_last;
   const int nwarps = blockDim.x >> 5, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, t = lane & 3;
-  long long* st_idx_all = reinterpret_cast<long long*>(sh_raw);
-  unsigned short* st_val_all = reinterpret_cast<unsigned short*>(st_idx_all + static_cast<size_t>(16) * WARP_CAP);
+  const unsigned lane_lt = (1u << lane) - 1u;
+  unsigned long long* st_rc_all = reinterpret_cast<unsigned long long*>(sh_raw);      // (row << 32) | column
+  unsigned short* st_val_all = reinterpret_cast<unsigned short*>(st_rc_all + static_cast<size_t>(16) * WARP_CAP);
   uint32_t* s_cb = reinterpret_cast<uint32_t*>(sh_raw + static_cast<size_t>(16) * WARP_CAP * 10);  // [CS_ROWS][HW] negated bf16 pairs
-  long long* st_idx = st_idx_all + static_cast<size_t>(warp) * WARP_CAP;
+  unsigned long long* st_rc = st_rc_all + static_cast<size_t>(warp) * WARP_CAP;
   unsigned short* st_val = st_val_all + static_cast<size_t>(warp) * WARP_CAP;
   const Slab s = slab_of(p);
   const int t_lo = sp.cand_bin[s.chunk];
   const int cap = sp.cand_cap[s.chunk];
   const int cbase = sp.cand_off[s.chunk];
   unsigned int* h2 = sp.hist2 + static_cast<size_t>(s.chunk) * NBINS;
-  // |e| below this cannot round to a magnitude >= t_lo (values at the midpoint may round down: they enter the list with
-  // a key below t_lo and are never selected, because the final threshold is not allowed below t_lo)
+  // |e| below `cut` cannot round to a magnitude >= t_lo; detection compares against 0.998 of it
   float cut;
   if (t_lo >= NBINS) cut = __int_as_float(0x7f800000);   // nothing is wanted
   else if (t_lo > 0) cut = 0.5f * (bf16_bits_to_float(static_cast<unsigned short>(t_lo)) + bf16_bits_to_float(static_cast<unsigned short>(t_lo - 1)));
   else cut = 0.f;
   if (sp.fixed_cut >= 0.f) cut = sp.fixed_cut;
+  const float detect = cut * 0.998f;
   const bool qvec = (p.r == RP);   // basis rows are RP * 2 bytes: pairs are 4-byte aligned
   int lmax = 0;
-  if (lane == 0) s_wcnt[warp] = 0;
-  __syncwarp();
+  int wcnt = 0;                    // entries staged by this warp: the same value in every lane
 
-  auto append = [&](long long flat, unsigned short b16) {  // one lane
+  auto append = [&](long long flat, unsigned short b16) {  // one lane, straight to the list
     const int key = b16 & 0x7FFF;
     atomicAdd(&h2[key], 1u);
     lmax = max(lmax, key);
@@ -776,7 +801,7 @@ __global__ void __launch_bounds__(512, 1) residual_candidates_kernel(const Selec
   };
   auto flush = [&]() {  // whole warp, converged
     __syncwarp();
-    const int cnt = min(s_wcnt[warp], WARP_CAP);
+    const int cnt = min(wcnt, WARP_CAP);
     if (cnt > 0) {
       int base = 0;
       if (lane == 0) base = atomicAdd(&sp.cand_count[s.chunk], cnt);
@@ -787,27 +812,28 @@ __global__ void __launch_bounds__(512, 1) residual_candidates_kernel(const Selec
         atomicAdd(&h2[key], 1u);
         lmax = max(lmax, key);
         if (base + i < cap) {
-          sp.cand_idx[cbase + base + i] = st_idx[i];
+          const unsigned long long rc = st_rc[i];
+          sp.cand_idx[cbase + base + i] = static_cast<long long>(rc >> 32) * p.n + static_cast<long long>(rc & 0xffffffffu);
           sp.cand_val[cbase + base + i] = b16;
         }
       }
     }
     __syncwarp();
-    if (lane == 0) s_wcnt[warp] = 0;
-    __syncwarp();
+    wcnt = 0;
   };
-  auto push = [&](int row, int row_end, int col, float e) {  // diverged lanes
-    if (row < row_end && col < p.n) {
-      const unsigned short b16 = __bfloat16_as_ushort(__float2bfloat16_rn(e));
-      const long long flat = static_cast<long long>(row) * p.n + col;
-      const int pos = atomicAdd(&s_wcnt[warp], 1);
-      if (pos < WARP_CAP) {
-        st_idx[pos] = flat;
-        st_val[pos] = b16;
-      } else {
-        append(flat, b16);  // staging slice full (a very dense stretch): straight to the list
-      }
+  // bf16 bits of one residual entry with the arithmetic of the exact passes (coefficients from the staged, negated copy)
+  auto exact_bits = [&](int row, int lr, int col) -> unsigned short {
+    const __nv_bfloat16* qrow = p.q + static_cast<size_t>(col) * p.r;
+    float acc = 0.f;
+#pragma unroll
+    for (int j = 0; j < RP; ++j) {
+      const uint32_t w = s_cb[lr * HW + (j >> 1)] ^ 0x80008000u;
+      const float cf = __uint_as_float((j & 1) ? (w & 0xFFFF0000u) : (w << 16));
+      const float qv = (j < p.r) ? __bfloat162float(qrow[j]) : 0.f;
+      acc = fmaf(cf, qv, acc);
     }
+    const float x = __bfloat162float(p.x[static_cast<size_t>(row) * p.ldx + col]);
+    return __bfloat16_as_ushort(__float2bfloat16_rn(x - acc));
   };
 
   const int nblocks = (p.n + 63) / 64;
@@ -839,8 +865,7 @@ __global__ void __launch_bounds__(512, 1) residual_candidates_kernel(const Selec
       }
       const bool lo_ok = n0 + 8 * t + 8 <= p.n, hi_ok = n0 + 32 + 8 * t + 8 <= p.n;
       for (int sp2 = 0; sp2 < npairs; ++sp2) {
-        __syncwarp();
-        if (s_wcnt[warp] > WARP_CAP / 2) flush();
+        if (wcnt > WARP_CAP / 2) flush();
         uint4 raw[2][4];
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
@@ -853,10 +878,10 @@ __global__ void __launch_bounds__(512, 1) residual_candidates_kernel(const Selec
           raw[h][2] = (rbot < sb1 && lo_ok) ? __ldg(reinterpret_cast<const uint4*>(xb)) : zero;
           raw[h][3] = (rbot < sb1 && hi_ok) ? __ldg(reinterpret_cast<const uint4*>(xb + 32)) : zero;
         }
+        unsigned marks[2] = {0u, 0u};   // bit 4 * j + q of marks[h]: accumulator q of tile j of strip h reaches the cut
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
           const int lr = sp2 * 32 + h * 16 + g;
-          const int rtop = sb0 + lr;
           uint32_t a[RP / 4];
           if constexpr (RP == 8) {
             a[0] = s_cb[lr * HW + t];
@@ -881,13 +906,46 @@ __global__ void __launch_bounds__(512, 1) residual_candidates_kernel(const Selec
 #pragma unroll
               for (int ks = 0; ks < RP / 16; ++ks) mma_k16(d, a[4 * ks], a[4 * ks + 1], a[4 * ks + 2], a[4 * ks + 3], bq[j][2 * ks], bq[j][2 * ks + 1]);
             }
-            const int col = n0 + (j < 4 ? 8 * t + 2 * j : 32 + 8 * t + 2 * (j - 4));
-            if (!(fabsf(d[0]) < cut)) push(rtop, sb1, col, d[0]);
-            if (!(fabsf(d[1]) < cut)) push(rtop, sb1, col + 1, d[1]);
-            if (!(fabsf(d[2]) < cut)) push(rtop + 8, sb1, col, d[2]);
-            if (!(fabsf(d[3]) < cut)) push(rtop + 8, sb1, col + 1, d[3]);
+#pragma unroll
+            for (int q4 = 0; q4 < 4; ++q4)
+              if (!(fabsf(d[q4]) < detect)) marks[h] |= 1u << (4 * j + q4);
           }
         }
+        // enumerate the marked positions of the warp into the staging slice, then recompute them one per lane
+        const int first = wcnt;
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          unsigned m = marks[h];
+          while (__any_sync(FULL, m != 0u)) {
+            bool has = m != 0u;
+            int row = 0, col = 0;
+            if (has) {
+              const int bit = __ffs(m) - 1;
+              m &= m - 1u;
+              const int j = bit >> 2, q4 = bit & 3;
+              row = sb0 + sp2 * 32 + h * 16 + g + ((q4 & 2) ? 8 : 0);
+              col = n0 + (j < 4 ? 8 * t + 2 * j : 32 + 8 * t + 2 * (j - 4)) + (q4 & 1);
+              has = row < sb1 && col < p.n;
+            }
+            const unsigned vm = __ballot_sync(FULL, has);
+            const int pos = wcnt + __popc(vm & lane_lt);
+            if (has) {
+              if (pos < WARP_CAP) {
+                st_rc[pos] = (static_cast<unsigned long long>(static_cast<unsigned>(row)) << 32) | static_cast<unsigned>(col);
+              } else {  // staging slice full (a very dense stretch): this lane finishes its entry on its own
+                append(static_cast<long long>(row) * p.n + col, exact_bits(row, row - sb0, col));
+              }
+            }
+            wcnt = min(WARP_CAP, wcnt + __popc(vm));
+          }
+        }
+        __syncwarp();
+        for (int k = first + lane; k < wcnt; k += 32) {
+          const unsigned long long rc = st_rc[k];
+          const int row = static_cast<int>(rc >> 32), col = static_cast<int>(rc & 0xffffffffu);
+          st_val[k] = exact_bits(row, row - sb0, col);
+        }
+        __syncwarp();
       }
     }
   }
@@ -917,7 +975,8 @@ __global__ void __launch_bounds__(512, 1) residual_candidates_kernel(const Selec
   hist_stage(h2, sh_hist, s_part, s_out);
   hist_locate(sh_hist, s_part, quota > 0 ? static_cast<unsigned int>(quota) : 0u, s_out);
   const int appended = *reinterpret_cast<volatile int*>(&sp.cand_count[s.chunk]);
-  const bool valid = quota <= 0 || (s_out[0] >= t_lo && s_out[0] >= 0 && appended <= cap);
+  // served only when the threshold bin lies strictly above the candidate bin (whose lower part detection may have missed)
+  const bool valid = quota <= 0 || (s_out[0] > t_lo && appended <= cap);
   if (threadIdx.x == 0) {
     p.thr_bin[s.chunk] = quota <= 0 ? NBINS : s_out[0];
     p.thr_need[s.chunk] = s_out[1];
