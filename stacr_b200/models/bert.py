@@ -8,7 +8,7 @@ import torch
 from torch import nn
 from torch.nn import functional as F
 
-from .common import causal_attention, GELU, init_weights, LayerNorm, Linear, ModelOutput
+from .common import causal_attention, Embedding, GELU, init_weights, LayerNorm, Linear, ModelOutput
 
 
 @dataclass
@@ -37,7 +37,7 @@ PRESETS = {
 class BertEmbeddings(nn.Module):
     def __init__(self, cfg):
         super().__init__()
-        self.word_embeddings = nn.Embedding(cfg.vocab_size, cfg.hidden_size)
+        self.word_embeddings = Embedding(cfg.vocab_size, cfg.hidden_size)
         self.position_embeddings = nn.Embedding(cfg.max_position_embeddings, cfg.hidden_size)
         self.token_type_embeddings = nn.Embedding(cfg.type_vocab_size, cfg.hidden_size)
         self.LayerNorm = LayerNorm(cfg.hidden_size, eps=cfg.layer_norm_eps)

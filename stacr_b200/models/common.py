@@ -44,6 +44,16 @@ class Linear(nn.Linear):
         return nn_ops.linear(x, self.weight, self.bias)
 
 
+class Embedding(nn.Embedding):
+    """``nn.Embedding`` (same parameter, same state-dict key) whose bf16-autocast path on a B200 is the in-tree lookup and
+    scatter-add (see ``ops.nn_ops.embedding``); the output is then already in the autocast dtype."""
+
+    def forward(self, ids):
+        if self.max_norm is None and not self.sparse and not self.scale_grad_by_freq:
+            return nn_ops.embedding(ids, self.weight, self.padding_idx)
+        return super().forward(ids)
+
+
 class GELU(nn.Module):
     def __init__(self, approximate: str = "none"):
         super().__init__()

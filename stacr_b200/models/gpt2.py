@@ -7,7 +7,7 @@ from dataclasses import dataclass
 import torch
 from torch import nn
 
-from .common import causal_attention, GELU, init_weights, LayerNorm, Linear, lm_loss, ModelOutput
+from .common import causal_attention, Embedding, GELU, init_weights, LayerNorm, Linear, lm_loss, ModelOutput
 
 
 @dataclass
@@ -85,8 +85,8 @@ class GPT2Block(nn.Module):
 class GPT2Model(nn.Module):
     def __init__(self, cfg: GPT2Config):
         super().__init__()
-        self.wte = nn.Embedding(cfg.vocab_size, cfg.n_embd)
-        self.wpe = nn.Embedding(cfg.n_positions, cfg.n_embd)
+        self.wte = Embedding(cfg.vocab_size, cfg.n_embd)
+        self.wpe = Embedding(cfg.n_positions, cfg.n_embd)
         self.drop = nn.Dropout(cfg.embd_pdrop)
         self.h = nn.ModuleList(GPT2Block(cfg) for _ in range(cfg.n_layer))
         self.ln_f = LayerNorm(cfg.n_embd, eps=cfg.layer_norm_epsilon)

@@ -8,7 +8,7 @@ import torch
 from torch import nn
 from torch.nn import functional as F
 
-from .common import causal_attention, init_weights, Linear, lm_loss, ModelOutput
+from .common import causal_attention, Embedding, init_weights, Linear, lm_loss, ModelOutput
 from .neox import apply_rotary, rotary_tables
 
 
@@ -106,7 +106,7 @@ class LlamaDecoderLayer(nn.Module):
 class LlamaModel(nn.Module):
     def __init__(self, cfg: LlamaConfig):
         super().__init__()
-        self.embed_tokens = nn.Embedding(cfg.vocab_size, cfg.hidden_size)
+        self.embed_tokens = Embedding(cfg.vocab_size, cfg.hidden_size)
         self.layers = nn.ModuleList(LlamaDecoderLayer(cfg) for _ in range(cfg.num_hidden_layers))
         self.norm = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps)
 

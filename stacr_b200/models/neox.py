@@ -8,7 +8,7 @@ import torch
 from torch import nn
 
 from ..ops import nn_ops
-from .common import causal_attention, GELU, init_weights, LayerNorm, Linear, lm_loss, ModelOutput
+from .common import causal_attention, Embedding, GELU, init_weights, LayerNorm, Linear, lm_loss, ModelOutput
 
 
 @dataclass
@@ -131,7 +131,7 @@ class NeoXLayer(nn.Module):
 class NeoXModel(nn.Module):
     def __init__(self, cfg: NeoXConfig):
         super().__init__()
-        self.embed_in = nn.Embedding(cfg.vocab_size, cfg.hidden_size)
+        self.embed_in = Embedding(cfg.vocab_size, cfg.hidden_size)
         self.layers = nn.ModuleList(NeoXLayer(cfg) for _ in range(cfg.num_hidden_layers))
         self.final_layer_norm = LayerNorm(cfg.hidden_size, eps=cfg.layer_norm_eps)
 

@@ -321,6 +321,52 @@ __global__ void __launch_bounds__(256) gelu_bwd_colsum_kernel(const uint4* __res
   for (int j = 0; j < 8; ++j) atomicAdd(colsum + static_cast<size_t>(cv) * 8 + j, acc[j]);
 }
 
+// ---------------------------------------------------------------------------- embedding
+// out[t, :] = table[ids[t], :] as bf16, from a bf16 table (the optimizer's shadow copy) or an fp32 one; width % 8 == 0.
+// Ids outside [0, vocab) produce a zero row and set *bad.
+template <typename T>
+__global__ void __launch_bounds__(256) embedding_fwd_kernel(const T* __restrict__ table, const long long* __restrict__ ids, long long tokens,
+                                                            int width, int vocab, uint4* __restrict__ out, int* bad) {
+  const int vecs = width >> 3;
+  const long long total = tokens * vecs;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total; i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const long long tkn = i / vecs;
+    const int v = static_cast<int>(i - tkn * vecs);
+    const long long id = ids[tkn];
+    if (id < 0 || id >= vocab) {
+      if (v == 0) atomicAdd(bad, 1);
+      out[i] = make_uint4(0u, 0u, 0u, 0u);
+      continue;
+    }
+    if constexpr (sizeof(T) == 2) {
+      out[i] = __ldg(reinterpret_cast<const uint4*>(table + id * width) + v);
+    } else {
+      const float4* src = reinterpret_cast<const float4*>(table + id * width) + 2 * v;
+      const float4 a = __ldg(src), b = __ldg(src + 1);
+      out[i] = make_uint4(pack_bf16x2(a.x, a.y), pack_bf16x2(a.z, a.w), pack_bf16x2(b.x, b.y), pack_bf16x2(b.z, b.w));
+    }
+  }
+}
+
+// grad_table[ids[t], :] += dy[t, :] (fp32 accumulation with atomics; the caller zeroes grad_table).  Rows of padding_idx
+// and out-of-range ids receive nothing.
+__global__ void __launch_bounds__(256) embedding_bwd_kernel(const uint4* __restrict__ dy, const long long* __restrict__ ids, long long tokens,
+                                                            int width, int vocab, long long padding_idx, float* __restrict__ grad_table) {
+  const int vecs = width >> 3;
+  const long long total = tokens * vecs;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total; i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const long long tkn = i / vecs;
+    const int v = static_cast<int>(i - tkn * vecs);
+    const long long id = ids[tkn];
+    if (id < 0 || id >= vocab || id == padding_idx) continue;
+    float f[8];
+    unpack8(__ldg(dy + i), f);
+    float* dst = grad_table + id * width + v * 8;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) atomicAdd(dst + j, f[j]);
+  }
+}
+
 // ---------------------------------------------------------------------------- cross-entropy
 // One CTA per row.  Pass 1: running max and sum of exponentials (online softmax); pass 2 writes
 // dlogits = (softmax - onehot) * inv_valid and the row loss.  Rows with target == -100 get zeros.
@@ -602,6 +648,37 @@ extern "C" int sb_cast_f32_bf16(const float* src, void* dst, long long numel, in
   if (blocks > static_cast<size_t>(sms) * 16) blocks = static_cast<size_t>(sms) * 16;
   sb::cast_f32_bf16_kernel<<<static_cast<unsigned>(blocks), 256, 0, static_cast<cudaStream_t>(stream)>>>(
       reinterpret_cast<const float4*>(src), static_cast<uint2*>(dst), nvec);
+  return static_cast<int>(cudaGetLastError());
+}
+
+// Row lookup into bf16 output; table_is_bf16 selects the table's element type.  width % 8 == 0.
+extern "C" int sb_embedding_fwd(const void* table, int table_is_bf16, const long long* ids, long long tokens, int width, int vocab, void* out,
+                                int* bad, int sms, void* stream) {
+  if (tokens <= 0) return 0;
+  if (width % 8) return -2;
+  const long long total = tokens * (width / 8);
+  long long blocks = (total + 255) / 256;
+  if (blocks > static_cast<long long>(sms) * 16) blocks = static_cast<long long>(sms) * 16;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (table_is_bf16)
+    sb::embedding_fwd_kernel<__nv_bfloat16><<<static_cast<unsigned>(blocks), 256, 0, st>>>(static_cast<const __nv_bfloat16*>(table), ids, tokens, width,
+                                                                                          vocab, static_cast<uint4*>(out), bad);
+  else
+    sb::embedding_fwd_kernel<float><<<static_cast<unsigned>(blocks), 256, 0, st>>>(static_cast<const float*>(table), ids, tokens, width, vocab,
+                                                                                  static_cast<uint4*>(out), bad);
+  return static_cast<int>(cudaGetLastError());
+}
+
+// Scatter-add of bf16 output-gradient rows into an fp32 table gradient (zeroed by the caller).
+extern "C" int sb_embedding_bwd(const void* dy, const long long* ids, long long tokens, int width, int vocab, long long padding_idx,
+                                float* grad_table, int sms, void* stream) {
+  if (tokens <= 0) return 0;
+  if (width % 8) return -2;
+  const long long total = tokens * (width / 8);
+  long long blocks = (total + 255) / 256;
+  if (blocks > static_cast<long long>(sms) * 16) blocks = static_cast<long long>(sms) * 16;
+  sb::embedding_bwd_kernel<<<static_cast<unsigned>(blocks), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const uint4*>(dy), ids, tokens, width, vocab, padding_idx, grad_table);
   return static_cast<int>(cudaGetLastError());
 }
 

@@ -765,14 +765,18 @@ __global__ void __launch_bounds__(512, 1) residual_candidates_kernel(const Selec
   __shared__ unsigned int s_part[SCAN_T];
   __shared__ int s_out[4];
   __shared__ int s_last;
+  // Candidate magnitudes crowd into the few hundred bins just above the cut.  Counting them with global atomics makes
+  // every CTA hammer the same few addresses (the hottest bin alone gets ~10^4 serialised updates); instead each CTA counts
+  // a window of HWIN bins above the candidate bin in shared memory and adds its totals once at the end.
+  constexpr int HWIN = 2048;
+  __shared__ unsigned int s_win[HWIN];
   const int nwarps = blockDim.x >> 5, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, t = lane & 3;
   const unsigned lane_lt = (1u << lane) - 1u;
+  for (int b = threadIdx.x; b < HWIN; b += blockDim.x) s_win[b] = 0u;
   unsigned long long* st_rc_all = reinterpret_cast<unsigned long long*>(sh_raw);      // (row << 32) | column
-  unsigned short* st_val_all = reinterpret_cast<unsigned short*>(st_rc_all + static_cast<size_t>(16) * WARP_CAP);
   uint32_t* s_cb = reinterpret_cast<uint32_t*>(sh_raw + static_cast<size_t>(16) * WARP_CAP * 10);  // [CS_ROWS][HW] negated bf16 pairs
   unsigned long long* st_rc = st_rc_all + static_cast<size_t>(warp) * WARP_CAP;
-  unsigned short* st_val = st_val_all + static_cast<size_t>(warp) * WARP_CAP;
   const Slab s = slab_of(p);
   const int t_lo = sp.cand_bin[s.chunk];
   const int cap = sp.cand_cap[s.chunk];
@@ -786,20 +790,60 @@ __global__ void __launch_bounds__(512, 1) residual_candidates_kernel(const Selec
   if (sp.fixed_cut >= 0.f) cut = sp.fixed_cut;
   const float detect = cut * 0.998f;
   const bool qvec = (p.r == RP);   // basis rows are RP * 2 bytes: pairs are 4-byte aligned
+  int wbase = (t_lo >= NBINS) ? 0 : (t_lo > 0 ? t_lo - 1 : 0);   // first bin of the shared window
+  if (sp.fixed_cut >= 0.f) {
+    const int ck = __bfloat16_as_ushort(__float2bfloat16_rn(detect)) & 0x7FFF;
+    wbase = ck > 0 ? ck - 1 : 0;
+  }
   int lmax = 0;
   int wcnt = 0;                    // entries staged by this warp: the same value in every lane
+  auto count_key = [&](int key) {
+    const int w = key - wbase;
+    if (w >= 0 && w < HWIN) atomicAdd(&s_win[w], 1u);
+    else atomicAdd(&h2[key], 1u);
+    lmax = max(lmax, key);
+  };
 
   auto append = [&](long long flat, unsigned short b16) {  // one lane, straight to the list
-    const int key = b16 & 0x7FFF;
-    atomicAdd(&h2[key], 1u);
-    lmax = max(lmax, key);
+    count_key(b16 & 0x7FFF);
     const int o = atomicAdd(&sp.cand_count[s.chunk], 1);
     if (o < cap) {
       sp.cand_idx[cbase + o] = flat;
       sp.cand_val[cbase + o] = b16;
     }
   };
-  auto flush = [&]() {  // whole warp, converged
+  // bf16 bits of one residual entry with the arithmetic of the exact passes (same operands, same order)
+  auto exact_bits = [&](int row, int col) -> unsigned short {
+    const __nv_bfloat16* qrow = p.q + static_cast<size_t>(col) * p.r;
+    const __nv_bfloat16* crow = p.c + static_cast<size_t>(row) * p.r;
+    float cf[RP], qf[RP];
+    if (qvec) {
+#pragma unroll
+      for (int v = 0; v < RP / 8; ++v) {
+        const uint4 cw = __ldg(reinterpret_cast<const uint4*>(crow) + v), qw = __ldg(reinterpret_cast<const uint4*>(qrow) + v);
+        const uint32_t c4[4] = {cw.x, cw.y, cw.z, cw.w}, q4[4] = {qw.x, qw.y, qw.z, qw.w};
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          cf[8 * v + 2 * k] = __uint_as_float(c4[k] << 16);
+          cf[8 * v + 2 * k + 1] = __uint_as_float(c4[k] & 0xFFFF0000u);
+          qf[8 * v + 2 * k] = __uint_as_float(q4[k] << 16);
+          qf[8 * v + 2 * k + 1] = __uint_as_float(q4[k] & 0xFFFF0000u);
+        }
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < RP; ++j) {
+        cf[j] = (j < p.r) ? __bfloat162float(crow[j]) : 0.f;
+        qf[j] = (j < p.r) ? __bfloat162float(qrow[j]) : 0.f;
+      }
+    }
+    float acc = 0.f;
+#pragma unroll
+    for (int j = 0; j < RP; ++j) acc = fmaf(cf[j], qf[j], acc);
+    const float x = __bfloat162float(p.x[static_cast<size_t>(row) * p.ldx + col]);
+    return __bfloat16_as_ushort(__float2bfloat16_rn(x - acc));
+  };
+  auto flush = [&]() {  // whole warp, converged: recompute the staged positions exactly, count them, append them to the list
     __syncwarp();
     const int cnt = min(wcnt, WARP_CAP);
     if (cnt > 0) {
@@ -807,33 +851,18 @@ __global__ void __launch_bounds__(512, 1) residual_candidates_kernel(const Selec
       if (lane == 0) base = atomicAdd(&sp.cand_count[s.chunk], cnt);
       base = __shfl_sync(FULL, base, 0);
       for (int i = lane; i < cnt; i += 32) {
-        const unsigned short b16 = st_val[i];
-        const int key = b16 & 0x7FFF;
-        atomicAdd(&h2[key], 1u);
-        lmax = max(lmax, key);
+        const unsigned long long rc = st_rc[i];
+        const int row = static_cast<int>(rc >> 32), col = static_cast<int>(rc & 0xffffffffu);
+        const unsigned short b16 = exact_bits(row, col);
+        count_key(b16 & 0x7FFF);
         if (base + i < cap) {
-          const unsigned long long rc = st_rc[i];
-          sp.cand_idx[cbase + base + i] = static_cast<long long>(rc >> 32) * p.n + static_cast<long long>(rc & 0xffffffffu);
+          sp.cand_idx[cbase + base + i] = static_cast<long long>(row) * p.n + col;
           sp.cand_val[cbase + base + i] = b16;
         }
       }
     }
     __syncwarp();
     wcnt = 0;
-  };
-  // bf16 bits of one residual entry with the arithmetic of the exact passes (coefficients from the staged, negated copy)
-  auto exact_bits = [&](int row, int lr, int col) -> unsigned short {
-    const __nv_bfloat16* qrow = p.q + static_cast<size_t>(col) * p.r;
-    float acc = 0.f;
-#pragma unroll
-    for (int j = 0; j < RP; ++j) {
-      const uint32_t w = s_cb[lr * HW + (j >> 1)] ^ 0x80008000u;
-      const float cf = __uint_as_float((j & 1) ? (w & 0xFFFF0000u) : (w << 16));
-      const float qv = (j < p.r) ? __bfloat162float(qrow[j]) : 0.f;
-      acc = fmaf(cf, qv, acc);
-    }
-    const float x = __bfloat162float(p.x[static_cast<size_t>(row) * p.ldx + col]);
-    return __bfloat16_as_ushort(__float2bfloat16_rn(x - acc));
   };
 
   const int nblocks = (p.n + 63) / 64;
@@ -911,41 +940,30 @@ __global__ void __launch_bounds__(512, 1) residual_candidates_kernel(const Selec
               if (!(fabsf(d[q4]) < detect)) marks[h] |= 1u << (4 * j + q4);
           }
         }
-        // enumerate the marked positions of the warp into the staging slice, then recompute them one per lane
-        const int first = wcnt;
-#pragma unroll
-        for (int h = 0; h < 2; ++h) {
-          unsigned m = marks[h];
-          while (__any_sync(FULL, m != 0u)) {
-            bool has = m != 0u;
-            int row = 0, col = 0;
-            if (has) {
-              const int bit = __ffs(m) - 1;
-              m &= m - 1u;
-              const int j = bit >> 2, q4 = bit & 3;
-              row = sb0 + sp2 * 32 + h * 16 + g + ((q4 & 2) ? 8 : 0);
-              col = n0 + (j < 4 ? 8 * t + 2 * j : 32 + 8 * t + 2 * (j - 4)) + (q4 & 1);
-              has = row < sb1 && col < p.n;
-            }
-            const unsigned vm = __ballot_sync(FULL, has);
-            const int pos = wcnt + __popc(vm & lane_lt);
-            if (has) {
-              if (pos < WARP_CAP) {
-                st_rc[pos] = (static_cast<unsigned long long>(static_cast<unsigned>(row)) << 32) | static_cast<unsigned>(col);
-              } else {  // staging slice full (a very dense stretch): this lane finishes its entry on its own
-                append(static_cast<long long>(row) * p.n + col, exact_bits(row, row - sb0, col));
-              }
-            }
-            wcnt = min(WARP_CAP, wcnt + __popc(vm));
+        // enumerate the marked positions of the warp into its staging slice (their values are computed at the flush)
+        unsigned long long m = static_cast<unsigned long long>(marks[0]) | (static_cast<unsigned long long>(marks[1]) << 32);
+        while (__any_sync(FULL, m != 0ull)) {
+          bool has = m != 0ull;
+          int row = 0, col = 0;
+          if (has) {
+            const int bit = __ffsll(static_cast<long long>(m)) - 1;
+            m &= m - 1ull;
+            const int h = bit >> 5, j = (bit >> 2) & 7, q4 = bit & 3;
+            row = sb0 + sp2 * 32 + h * 16 + g + ((q4 & 2) ? 8 : 0);
+            col = n0 + (j < 4 ? 8 * t + 2 * j : 32 + 8 * t + 2 * (j - 4)) + (q4 & 1);
+            has = row < sb1 && col < p.n;
           }
+          const unsigned vm = __ballot_sync(FULL, has);
+          const int pos = wcnt + __popc(vm & lane_lt);
+          if (has) {
+            if (pos < WARP_CAP) {
+              st_rc[pos] = (static_cast<unsigned long long>(static_cast<unsigned>(row)) << 32) | static_cast<unsigned>(col);
+            } else {  // staging slice full (a very dense stretch): this lane finishes its entry on its own
+              append(static_cast<long long>(row) * p.n + col, exact_bits(row, col));
+            }
+          }
+          wcnt = min(WARP_CAP, wcnt + __popc(vm));
         }
-        __syncwarp();
-        for (int k = first + lane; k < wcnt; k += 32) {
-          const unsigned long long rc = st_rc[k];
-          const int row = static_cast<int>(rc >> 32), col = static_cast<int>(rc & 0xffffffffu);
-          st_val[k] = exact_bits(row, row - sb0, col);
-        }
-        __syncwarp();
       }
     }
   }
@@ -953,6 +971,11 @@ __global__ void __launch_bounds__(512, 1) residual_candidates_kernel(const Selec
 #pragma unroll
   for (int off = 16; off; off >>= 1) lmax = max(lmax, __shfl_xor_sync(FULL, lmax, off));
   if (lane == 0 && lmax > 0) atomicMax(sp.gmax, lmax);
+  __syncthreads();
+  for (int b = threadIdx.x; b < HWIN; b += blockDim.x) {
+    const unsigned int v = s_win[b];
+    if (v) atomicAdd(&h2[wbase + b], v);
+  }
 
   // ---- tail: the last CTA of the chunk finds the exact threshold among the candidates; the last CTA of all sets the scale
   __threadfence();

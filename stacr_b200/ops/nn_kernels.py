@@ -112,3 +112,32 @@ def rotary_qk_(qkv: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, seq: int
                                   c_int(rot), c_float(sign), c_int(_lib.sm_count(qkv.device)), _lib.stream_ptr())
     _lib.check_rc(rc, "sb_rotary_qk")
     _lib.count(1)
+
+
+def embedding_fwd(table: torch.Tensor, ids: torch.Tensor) -> torch.Tensor:
+    """bf16 rows ``table[ids]`` from a bf16 or fp32 table ``[vocab, width]`` (``width % 8 == 0``); ids are checked on the device."""
+    vocab, width = table.shape
+    flat = ids.reshape(-1).to(torch.int64).contiguous()
+    out = torch.empty(flat.numel(), width, dtype=torch.bfloat16, device=table.device)
+    bad = torch.zeros(1, dtype=torch.int32, device=table.device)
+    rc = _lib.load().sb_embedding_fwd(_lib.ptr(table), c_int(int(table.dtype == torch.bfloat16)), _lib.ptr(flat), c_ll(flat.numel()), c_int(width),
+                                      c_int(vocab), _lib.ptr(out), _lib.ptr(bad), c_int(_lib.sm_count(table.device)), _lib.stream_ptr())
+    _lib.check_rc(rc, "sb_embedding_fwd")
+    _lib.count(1)
+    return out.reshape(*ids.shape, width)
+
+
+def embedding_bwd(dy: torch.Tensor, ids: torch.Tensor, vocab: int, padding_idx: int | None, out: torch.Tensor | None = None) -> torch.Tensor:
+    """fp32 ``[vocab, width]`` gradient of the table: rows of ``dy`` (bf16) summed by id.  ``out`` (contiguous fp32) is cleared and filled."""
+    width = dy.shape[-1]
+    flat = ids.reshape(-1).to(torch.int64).contiguous()
+    d2 = dy.reshape(-1, width).contiguous()
+    if out is None:
+        out = torch.zeros(vocab, width, dtype=torch.float32, device=dy.device)
+    else:
+        out.zero_()
+    rc = _lib.load().sb_embedding_bwd(_lib.ptr(d2), _lib.ptr(flat), c_ll(flat.numel()), c_int(width), c_int(vocab),
+                                      c_ll(-1 if padding_idx is None else padding_idx), _lib.ptr(out), c_int(_lib.sm_count(dy.device)), _lib.stream_ptr())
+    _lib.check_rc(rc, "sb_embedding_bwd")
+    _lib.count(1)
+    return out

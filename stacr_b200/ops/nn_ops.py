@@ -292,6 +292,57 @@ def linear(x, weight, bias=None):
     return F.linear(x, weight, bias)
 
 
+# ------------------------------------------------------------------------------ token embedding
+class _EmbeddingFn(torch.autograd.Function):
+    """bf16 rows of an embedding table; the table's fp32 gradient is scatter-added by an in-tree kernel, straight into the
+    slot a gradient synchroniser has lent when there is one.  The rows are read from the optimizer's bf16 copy of the table
+    when it exists (what a cast of the fp32 rows would give, without touching the fp32 table)."""
+
+    @staticmethod
+    def forward(ctx, weight, ids, padding_idx):
+        from ..layers import _bf16_weight
+        from . import nn_kernels
+
+        table = _bf16_weight(weight) if getattr(weight, "_bf16_shadow", None) is not None else weight.detach()
+        ctx.save_for_backward(ids)
+        ctx.weight, ctx.padding_idx = weight, padding_idx
+        return nn_kernels.embedding_fwd(table.contiguous(), ids)
+
+    @staticmethod
+    def backward(ctx, dy):
+        from . import nn_kernels
+
+        (ids,) = ctx.saved_tensors
+        weight = ctx.weight
+        slot = getattr(weight, "_sb_grad_out", None) if getattr(weight, "_sb_grad_fresh", False) else None
+        if slot is not None and slot.dtype == torch.float32 and weight.dtype == torch.float32 and not getattr(weight, "_sb_tied", False):
+            weight._sb_grad_fresh = False
+        else:
+            slot = None
+        g = (dy if dy.dtype == torch.bfloat16 else dy.to(torch.bfloat16))
+        dw = nn_kernels.embedding_bwd(g, ids, weight.shape[0], ctx.padding_idx, out=slot)
+        ready = getattr(weight, "_sb_grad_ready", None) if slot is not None else None
+        if ready is not None:
+            ready()
+            return None, None, None
+        return dw.to(weight.dtype), None, None
+
+
+def embedding(ids, weight, padding_idx=None):
+    """Token embedding lookup producing bf16 on a B200 under bf16 autocast (see ``_EmbeddingFn``); the stock op elsewhere."""
+    usable = (weight.is_cuda and ids.is_cuda and weight.dim() == 2 and weight.shape[1] % 8 == 0 and _lib.available() and ids.numel() > 0
+              and weight.dtype in (torch.float32, torch.bfloat16) and torch.is_autocast_enabled() and torch.get_autocast_dtype("cuda") == torch.bfloat16)
+    if usable:
+        if torch.is_grad_enabled() and weight.requires_grad:
+            return _EmbeddingFn.apply(weight, ids, padding_idx)
+        from ..layers import _bf16_weight
+        from . import nn_kernels
+
+        table = _bf16_weight(weight) if getattr(weight, "_bf16_shadow", None) is not None else weight.detach()
+        return nn_kernels.embedding_fwd(table.contiguous(), ids)
+    return F.embedding(ids, weight, padding_idx)
+
+
 # ------------------------------------------------------------------------------ rotary embedding
 class _RotaryQKFn(torch.autograd.Function):
     """Rotate q and k inside a fused qkv projection output, in place (the projection does not need its output for backward)."""

@@ -61,7 +61,7 @@ def decode_second_moment(codes: torch.Tensor, amax: torch.Tensor) -> torch.Tenso
 
 _DESC = np.dtype(
     [("param", "<u8"), ("grad", "<u8"), ("m", "<u8"), ("v", "<u8"), ("shadow", "<u8"), ("m8", "<u8"), ("v8", "<u8"),
-     ("m_absmax", "<u8"), ("v_absmax", "<u8"), ("numel", "<i8")]
+     ("m_absmax", "<u8"), ("v_absmax", "<u8"), ("numel", "<i8"), ("shadow_mc", "<u8")]
 )
 _CHUNK = np.dtype([("tensor", "<i4"), ("pad", "<i4"), ("offset", "<i8")])
 
@@ -171,7 +171,7 @@ class AdamW(torch.optim.Optimizer):
             table[ti] = (
                 p.data_ptr(), p.grad.data_ptr(), ptr(st.get("exp_avg")), ptr(st.get("exp_avg_sq")),
                 ptr(getattr(p, "_bf16_shadow", None)), ptr(st.get("m8")), ptr(st.get("v8")), ptr(st.get("m_absmax")),
-                ptr(st.get("v_absmax")), p.numel(),
+                ptr(st.get("v_absmax")), p.numel(), int(getattr(p, "_bf16_shadow_mc", 0) or 0),
             )
         blob = table.tobytes()
         if blob != cache["last"]:
