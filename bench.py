@@ -299,7 +299,7 @@ def run_ours(args):
     from stacr_b200.models import GPTNeoXForCausalLM, NeoXConfig
     from stacr_b200.ops import _lib
     from stacr_b200.optim import AdamW8bit
-    from stacr_b200.parallel import GradSync, broadcast_parameters, init_distributed
+    from stacr_b200.parallel import GradSync, ShardedGradSync, broadcast_parameters, init_distributed
 
     rank, world, local = init_distributed()
     if world != args.gpus:
@@ -312,9 +312,16 @@ def run_ours(args):
     model = GPTNeoXForCausalLM(NeoXConfig(**shape)).to(dev).train()
     broadcast_parameters(model)
     layers = S.apply_stacr(model, **STACR)
-    opt = AdamW8bit(model.parameters(), lr=2e-5, weight_decay=0.0, bf16_shadow=True)
     fused = [layer.weight for layer in layers] if args.fused_dw == "on" else []
-    sync = GradSync(model.parameters(), backend=args.comm, fused=fused) if world > 1 else None
+    zero = world > 1 and args.zero == "on" and not fused
+    if zero:
+        # optimizer sharded over the ranks: buckets are reduced to their owners only, every rank updates 1/W of the matrices
+        # and its update kernel stores the new bf16 weights through the NVSwitch multicast address (no separate all-gather)
+        sync = ShardedGradSync(model.parameters(), backend=args.comm)
+        opt = AdamW8bit(model.parameters(), lr=2e-5, weight_decay=0.0, bf16_shadow=True, shard=sync)
+    else:
+        sync = GradSync(model.parameters(), backend=args.comm, fused=fused) if world > 1 else None
+        opt = AdamW8bit(model.parameters(), lr=2e-5, weight_decay=0.0, bf16_shadow=True)
     host_batches = [t.pin_memory() for t in make_tokens(torch, shape["vocab_size"], batch, seq, 8, 100 + rank)]
     dev_batches = [t.to(dev) for t in host_batches]
     counter = {"step": 0}
@@ -393,6 +400,7 @@ def run_ours(args):
                 "global_batch": world * batch, "seq_len": seq, "parallelism": f"dp{world}",
                 "stacr": STACR, "optimizer": "AdamW 8-bit block-wise (in-tree)", "comm": sync.backend if sync else "none",
                 "fused_dw_reduce_scatter": bool(sync and sync.n_fused and sync.backend == "symm"),
+                "optimizer_sharding": "ZeRO-1: reduce-to-owner buckets, 1/W optimizer per rank, bf16 weights published by multicast stores of the update kernel" if zero else "replicated",
                 "l2": "inputs larger than L2: every step streams 2.8 GB of bf16 weights and > 10 GB of activations through a 126 MB L2",
             },
             "clocks": clocks.summary(),
@@ -541,6 +549,7 @@ def main():
     ap.add_argument("--comm", default="auto", choices=["auto", "symm", "nccl"], help="gradient all-reduce path (this framework)")
     ap.add_argument("--fused-dw", default="off", choices=["on", "off"],
                     help="N > 1: compressed layers' weight-gradient kernels reduce-scatter in their epilogue over NVLink peer memory")
+    ap.add_argument("--zero", default="on", choices=["on", "off"], help="N > 1: shard the optimizer over the ranks (reduce-to-owner + multicast weight publication)")
     ap.add_argument("--gap-report", metavar="FILE", help="after the timed regions, write where the GPU idles inside two more steps to FILE")
     ap.add_argument("--kernel-table", metavar="FILE", help="after the timed regions, write per-kernel device times of two more steps to FILE")
     ap.add_argument("--small", action="store_true", help="tiny shape for smoke runs (not a benchmark number)")

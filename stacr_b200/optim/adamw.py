@@ -74,11 +74,14 @@ class AdamW(torch.optim.Optimizer):
     """
 
     def __init__(self, params, lr=1e-3, betas=(0.9, 0.999), eps=1e-8, weight_decay=0.01, *, eight_bit=False,
-                 min_8bit_size=4096, bf16_shadow=False):
+                 min_8bit_size=4096, bf16_shadow=False, shard=None):
         if lr < 0 or eps < 0 or not 0 <= betas[0] < 1 or not 0 <= betas[1] < 1 or weight_decay < 0:
             raise ValueError("invalid AdamW hyper-parameters")
         super().__init__(params, dict(lr=lr, betas=betas, eps=eps, weight_decay=weight_decay))
         self.eight_bit, self.min_8bit_size, self.bf16_shadow = bool(eight_bit), int(min_8bit_size), bool(bf16_shadow)
+        # ``shard``: a ``parallel.zero.ShardedGradSync``.  Parameters it shards are updated only over the element ranges this
+        # rank owns; their bf16 copies belong to it (views of one flat buffer) and it publishes the update to the other ranks.
+        self.shard = shard
         self._tables: dict[int, dict] = {}
         self.kernel_launches = 0
 
@@ -99,10 +102,16 @@ class AdamW(torch.optim.Optimizer):
         else:
             st["exp_avg"] = torch.zeros_like(p, dtype=torch.float32, memory_format=torch.contiguous_format)
             st["exp_avg_sq"] = torch.zeros_like(p, dtype=torch.float32, memory_format=torch.contiguous_format)
-        if self.bf16_shadow and p.is_cuda:
+        if self.bf16_shadow and p.is_cuda and getattr(p, "_bf16_shadow", None) is None:
             p._bf16_shadow = p.detach().to(torch.bfloat16)
             p._bf16_shadow_version = p._version
         return st
+
+    def _ranges(self, p: torch.Tensor):
+        """Element ranges of ``p`` this rank updates: everything, unless a sharding synchroniser owns the partition."""
+        if self.shard is not None and self.shard.is_sharded(p):
+            return self.shard.owned_ranges(p)
+        return [(0, p.numel())]
 
     def close(self) -> None:
         """Detach the bf16 shadows from the parameters (call before handing the model to another optimizer)."""
@@ -143,12 +152,18 @@ class AdamW(torch.optim.Optimizer):
         lib = _lib.load()
         dev = plist[0].device
         cache = self._tables.get(gi)
-        sig = tuple((p.data_ptr(), p.numel()) for p in plist)
+        ranges = [self._ranges(p) for p in plist]
+        sig = tuple((p.data_ptr(), p.numel(), tuple(r)) for p, r in zip(plist, ranges))
         if cache is None or cache["sig"] != sig:
             chunk = lib.sb_optim_chunk()
             rows = []
-            for ti, p in enumerate(plist):
-                rows += [(ti, 0, off) for off in range(0, p.numel(), chunk)]
+            for ti, (p, rs) in enumerate(zip(plist, ranges)):
+                for a, b in rs:
+                    assert a % chunk == 0, "an owned range must start on a chunk boundary"
+                    rows += [(ti, 0, off) for off in range(a, b, chunk)]
+            if not rows:
+                self._tables[gi] = {"sig": sig, "n_chunks": 0}
+                return
             chunks = np.array(rows, dtype=_CHUNK)
             cache = {
                 "sig": sig,
@@ -164,6 +179,8 @@ class AdamW(torch.optim.Optimizer):
             }
             assert lib.sb_tensor_desc_size() == _DESC.itemsize and lib.sb_chunk_desc_size() == _CHUNK.itemsize
             self._tables[gi] = cache
+        if cache["n_chunks"] == 0:
+            return
         table = np.empty(len(plist), dtype=_DESC)
         for ti, p in enumerate(plist):
             st = self.state[p]
@@ -227,16 +244,45 @@ class AdamW(torch.optim.Optimizer):
             b1, b2 = group["betas"]
             for p in slow:
                 st = self.state[p]
-                g = p.grad.float() * grad_scale
-                work = p.data.float() if p.dtype != torch.float32 else p.data
-                self._reference_update(work, g, st, group["lr"], b1, b2, group["eps"], group["weight_decay"],
-                                       1 - b1 ** st["step"], 1 - b2 ** st["step"])
-                if work is not p.data:
-                    p.data.copy_(work)
+                full = [(0, p.numel())]
+                ranges = self._ranges(p)
+                if ranges == full:
+                    g = p.grad.float() * grad_scale
+                    work = p.data.float() if p.dtype != torch.float32 else p.data
+                    self._reference_update(work, g, st, group["lr"], b1, b2, group["eps"], group["weight_decay"],
+                                           1 - b1 ** st["step"], 1 - b2 ** st["step"])
+                    if work is not p.data:
+                        p.data.copy_(work)
+                else:
+                    self._reference_update_ranges(p, st, ranges, group, grad_scale)
                 if hasattr(p, "_bf16_shadow"):
                     p._bf16_shadow.copy_(p.data)
                     p._bf16_shadow_version = p._version
+        if self.shard is not None:
+            self.shard.publish_updates()
         return loss
+
+    def _reference_update_ranges(self, p, st, ranges, group, grad_scale) -> None:
+        """The framework-op update restricted to chunk-aligned element ranges of a contiguous parameter (sharded optimizer)."""
+        b1, b2 = group["betas"]
+        flat_p, flat_g = p.data.view(-1), p.grad.reshape(-1)
+        for a, b in ranges:
+            sub = {"eight_bit": st["eight_bit"]}
+            if st["eight_bit"]:
+                qa, qb = a // BLOCK, (b + BLOCK - 1) // BLOCK
+                sub.update(m8=st["m8"][a:b], v8=st["v8"][a:b], m_absmax=st["m_absmax"][qa:qb], v_absmax=st["v_absmax"][qa:qb])
+            else:
+                sub.update(exp_avg=st["exp_avg"].view(-1)[a:b], exp_avg_sq=st["exp_avg_sq"].view(-1)[a:b])
+            work = flat_p[a:b].float() if p.dtype != torch.float32 else flat_p[a:b]
+            self._reference_update(work, flat_g[a:b].float() * grad_scale, sub, group["lr"], b1, b2, group["eps"], group["weight_decay"],
+                                   1 - b1 ** st["step"], 1 - b2 ** st["step"])
+            if work is not flat_p[a:b]:
+                flat_p[a:b].copy_(work)
+            if st["eight_bit"]:
+                st["m8"][a:b], st["v8"][a:b] = sub["m8"], sub["v8"]
+                st["m_absmax"][qa:qb], st["v_absmax"][qa:qb] = sub["m_absmax"], sub["v_absmax"]
+            else:
+                st["exp_avg"].view(-1)[a:b], st["exp_avg_sq"].view(-1)[a:b] = sub["exp_avg"], sub["exp_avg_sq"]
 
 
 class AdamW8bit(AdamW):

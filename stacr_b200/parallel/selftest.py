@@ -139,6 +139,95 @@ def _tp_gemm_check(rank, world, dev, report) -> bool:
     return good
 
 
+def _reduce_to_owner_check(buf, rank, world, dev, report) -> bool:
+    """Reduce-to-owner kernel (peer loads and in-switch reduction) against NCCL all-reduce on the owner's slice; the rest of
+    the range must keep its local values."""
+    good = True
+    n = 1 << 22
+    for name, mm in [("p2p", False)] + ([("multimem", True)] if buf.multicast_ptr else []):
+        buf.use_multimem = mm
+        for lo, hi in ((0, 2048 * world * 4), (4096, 4096 + 2048 * world * 37)):
+            gen = torch.Generator(device=dev).manual_seed(31 * rank + lo)
+            buf.tensor[:n].copy_(torch.randn(n, device=dev, generator=gen))
+            before = buf.tensor[:n].clone()
+            expect = before[lo:hi].clone()
+            torch.cuda.synchronize()
+            dist.barrier()
+            dist.all_reduce(expect)
+            expect /= world
+            per = (hi - lo) // world
+            a, b = lo + rank * per, lo + (rank + 1) * per
+            buf.reduce_to_owner_(lo, hi, a, b, average=True)
+            torch.cuda.synchronize()
+            _lib.check_status(dev)
+            err = float((buf.tensor[a:b] - expect[a - lo:b - lo]).abs().max())
+            same = torch.equal(buf.tensor[:a], before[:a]) and torch.equal(buf.tensor[b:n], before[b:n])
+            report[f"reduce_to_owner_{name}_max_err"] = max(err, report.get(f"reduce_to_owner_{name}_max_err", 0.0))
+            good &= err < 1e-5 and same
+            dist.barrier()
+    return good
+
+
+def _sharded_optimizer_check(rank, world, dev, report) -> bool:
+    """A small decoder trained for a few steps with the replicated and with the sharded optimizer: same losses, same bf16
+    weights on every rank (the sharded path publishes them through the multicast stores of the update kernel)."""
+    import stacr_b200 as S
+    from ..models import GPTNeoXForCausalLM, NeoXConfig
+    from ..optim import AdamW8bit
+    from .ddp import GradSync, broadcast_parameters
+    from .zero import ShardedGradSync
+
+    cfg = NeoXConfig(vocab_size=2048, hidden_size=256, num_hidden_layers=2, num_attention_heads=4, intermediate_size=1024, max_position_embeddings=128)
+
+    def run(sharded: bool):
+        torch.manual_seed(7)
+        model = GPTNeoXForCausalLM(cfg).to(dev).train()
+        broadcast_parameters(model)
+        layers = S.apply_stacr(model, rank=8, residual_budget=0.01, residual_mode="global_topk", turbo_after_step=None, min_features=128)
+        if sharded:
+            sync = ShardedGradSync(model.parameters(), bucket_mb=1.0)
+            opt = AdamW8bit(model.parameters(), lr=1e-3, weight_decay=0.0, bf16_shadow=True, shard=sync)
+        else:
+            sync = GradSync(model.parameters(), bucket_mb=1.0)
+            opt = AdamW8bit(model.parameters(), lr=1e-3, weight_decay=0.0, bf16_shadow=True)
+        gen = torch.Generator(device=dev).manual_seed(50 + rank)
+        losses = []
+        for step in range(5):
+            ids = torch.randint(0, cfg.vocab_size, (4, 128), device=dev, generator=gen)
+            S.set_step(layers, step)
+            sync.zero_grad()
+            with torch.autocast("cuda", dtype=torch.bfloat16):
+                loss = model(input_ids=ids, labels=ids).loss
+            loss.backward()
+            sync.finish()
+            opt.step()
+            losses.append(float(loss))
+        torch.cuda.synchronize()
+        _lib.check_status(dev)
+        if sharded:
+            sync.gather_parameters()
+        weights = {n: p.detach().clone() for n, p in model.named_parameters()}
+        shadows = {n: p._bf16_shadow.detach().clone() for n, p in model.named_parameters() if getattr(p, "_bf16_shadow", None) is not None}
+        sync.close()
+        opt.close()
+        return losses, weights, shadows
+
+    la, wa, sa = run(False)
+    lb, wb, sb = run(True)
+    loss_gap = max(abs(a - b) for a, b in zip(la, lb))
+    # selection ties and atomics make two runs differ in the last bits; the two optimizers must agree to that level
+    w_gap = max(float((wa[n] - wb[n]).abs().max() / (wa[n].abs().max() + 1e-12)) for n in wa)
+    s_gap = max(float((sa[n].float() - sb[n].float()).abs().max() / (sa[n].float().abs().max() + 1e-12)) for n in sb if n in sa)
+    # every rank must hold the same bf16 weights after the sharded run
+    digest = torch.stack([v.float().sum() for v in sb.values()])
+    lo, hi = digest.clone(), digest.clone()
+    dist.all_reduce(lo, op=dist.ReduceOp.MIN)
+    dist.all_reduce(hi, op=dist.ReduceOp.MAX)
+    spread = float((hi - lo).abs().max())
+    report.update(sharded_loss_gap=loss_gap, sharded_weight_gap=w_gap, sharded_bf16_gap=s_gap, sharded_rank_spread=spread, sharded_losses=lb)
+    return loss_gap < 5e-2 and w_gap < 2e-2 and s_gap < 2e-2 and spread == 0.0
+
+
 def main() -> int:
     rank, world, local = init_distributed("nccl")
     dev = torch.device("cuda", local)
@@ -180,7 +269,9 @@ def main() -> int:
             report[f"{name}_busbw_GBs_{ctas}ctas"] = 2 * (world - 1) / world * n * 4 / ms / 1e6
         buf.max_ctas = 32
     ok &= _fused_dw_check(buf, rank, world, dev, report)
+    ok &= _reduce_to_owner_check(buf, rank, world, dev, report)
     ok &= _tp_gemm_check(rank, world, dev, report)
+    ok &= _sharded_optimizer_check(rank, world, dev, report)
     plain = torch.randn(n, device=dev)
     ms = _time(lambda: dist.all_reduce(plain))
     report["nccl_ms_256MB"] = ms

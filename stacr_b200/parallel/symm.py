@@ -96,6 +96,20 @@ class SymmetricBuffer:
         _lib.check_rc(rc, name)
         _lib.count(1)
 
+    def reduce_to_owner_(self, lo: int, hi: int, own_lo: int, own_hi: int, average: bool = True) -> None:
+        """Sum (or mean) of ``tensor[lo:hi]`` across ranks, delivered only to owners: this rank ends up with the reduced
+        ``tensor[own_lo:own_hi]`` in its own copy (the rest of ``[lo, hi)`` keeps its local values).  fp32 buffers only."""
+        assert self.tensor.dtype == torch.float32
+        self._epoch += 1
+        rc = _lib.load().sb_reduce_to_owner(
+            _lib.ptr(self._peer_ptrs), _lib.ptr(self._pad_ptrs), ctypes.c_ulonglong(self.multicast_ptr if self.use_multimem else 0),
+            ctypes.c_int(self.rank), ctypes.c_int(self.world), ctypes.c_longlong(lo), ctypes.c_longlong(hi), ctypes.c_longlong(own_lo),
+            ctypes.c_longlong(own_hi), ctypes.c_float(1.0 / self.world if average else 1.0), ctypes.c_int(self._epoch),
+            ctypes.c_int(self.max_ctas), _lib.ptr(_lib.status_word(self.tensor.device)), _lib.stream_ptr(),
+        )
+        _lib.check_rc(rc, "sb_reduce_to_owner")
+        _lib.count(1)
+
     def all_gather_slices_(self, lo: int, hi: int, average: bool = True) -> None:
         """Every rank broadcasts its 1/W slice of ``tensor[lo:hi]`` to all ranks (second half of an all-reduce whose
         reduce-scatter was done by the producing kernels adding into the owner's copy)."""
