@@ -275,7 +275,10 @@ class STACRFunction(torch.autograd.Function):
         residual_mode="chunk_topk",
         residual_block_size=16,
         residual_sample_ratio=0.1,
+        tp=None,
     ):
+        # ``tp``: a ``parallel.tp.TPContext`` when this layer is a tensor-parallel shard.  A row-parallel shard sums its
+        # output over the ranks inside the forward GEMM; a column-parallel shard sums its input gradient inside the backward GEMM.
         feats = basis.shape[0]
         x2d = x.reshape(-1, feats)
         cdt = _compute_dtype(x, weight)
@@ -288,7 +291,10 @@ class STACRFunction(torch.autograd.Function):
             wb = _bf16_weight(weight)
             bf = None if bias is None else bias.detach().float()
             # Conv1D keeps W as [in, out]: that is the MN-major B operand of the same kernel
-            out2d = gemm(xa, wb, b_mn=bool(transposed), bias=bf)
+            if tp is not None and tp.kind == "row":
+                out2d = tp.gemm_sum(xa, wb.contiguous(), b_mn=bool(transposed), bias=bf)
+            else:
+                out2d = gemm(xa, wb, b_mn=bool(transposed), bias=bf)
             qb, qt = _basis_views(basis)
             coeff = stacr_ops.project(xa, qt)[:, : basis.shape[1]].to(torch.bfloat16)
             idx, packed = _select_residual_kernels(
@@ -301,6 +307,8 @@ class STACRFunction(torch.autograd.Function):
                 out2d = x2d.mm(weight) if bias is None else torch.addmm(bias, x2d, weight)
             else:
                 out2d = F.linear(x2d, weight, bias)
+            if tp is not None and tp.kind == "row":
+                out2d = tp.sum_(out2d)
             # compression arithmetic runs in the linear's output dtype with ambient autocast off
             with torch.autocast(device_type=x.device.type, enabled=False):
                 act, q = x2d.to(out2d.dtype), basis.to(out2d.dtype)
@@ -322,6 +330,7 @@ class STACRFunction(torch.autograd.Function):
         ctx.input_dtype = x.dtype
         ctx.bias_dtype = None if bias is None else bias.dtype
         ctx.n_args = len(ctx.needs_input_grad)
+        ctx.tp = tp
         return out2d.reshape(*ctx.leading, ctx.out_features)
 
     @staticmethod
@@ -337,7 +346,10 @@ class STACRFunction(torch.autograd.Function):
             if ctx.needs_input_grad[0]:
                 wb = _bf16_weight(weight)
                 # dX = dY W: W[out, in] is MN-major for this product; Conv1D's [in, out] is K-major
-                gx = gemm(ga, wb, b_mn=not ctx.transposed)
+                if ctx.tp is not None and ctx.tp.kind == "column":
+                    gx = ctx.tp.gemm_sum(ga, wb.contiguous(), b_mn=not ctx.transposed)
+                else:
+                    gx = gemm(ga, wb, b_mn=not ctx.transposed)
                 gx = gx.reshape(*ctx.leading, ctx.in_features).to(ctx.input_dtype)
             if ctx.needs_input_grad[1]:
                 residual = None
@@ -372,7 +384,10 @@ class STACRFunction(torch.autograd.Function):
         with torch.autocast(device_type=g2d.device.type, enabled=False):
             if ctx.needs_input_grad[0]:
                 w = weight.to(g2d.dtype)
-                gx = g2d.mm(w.t() if ctx.transposed else w).reshape(*ctx.leading, ctx.in_features).to(ctx.input_dtype)
+                gx = g2d.mm(w.t() if ctx.transposed else w)
+                if ctx.tp is not None and ctx.tp.kind == "column":
+                    gx = ctx.tp.sum_(gx)
+                gx = gx.reshape(*ctx.leading, ctx.in_features).to(ctx.input_dtype)
             if ctx.needs_input_grad[1]:
                 gw = (g2d.t() @ coeff.to(g2d.dtype)) @ q.to(g2d.dtype).t()
                 if ctx.has_residual and res[0].numel():
@@ -578,6 +593,9 @@ class STACRLinear(nn.Module):
 
     # ------------------------------------------------------------------ forward
     def _exact(self, x: torch.Tensor) -> torch.Tensor:
+        tp = getattr(self, "tp_context", None)
+        if tp is not None:
+            return tp.exact(x, self)
         if not self.transposed:
             return F.linear(x, self.weight, self.bias)
         flat = x.reshape(-1, self.in_features)
@@ -607,7 +625,7 @@ class STACRLinear(nn.Module):
             guard.record_layer(self, (basis, budget))
         return STACRFunction.apply(
             x, self.weight, self.bias, basis, budget, self.residual_bits, self.chunk_rows, self.transposed,
-            self.residual_mode, self.residual_block_size, self.residual_sample_ratio,
+            self.residual_mode, self.residual_block_size, self.residual_sample_ratio, getattr(self, "tp_context", None),
         )
 
     # ------------------------------------------------------------------ accounting

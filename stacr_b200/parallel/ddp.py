@@ -254,7 +254,8 @@ class GradSync:
         if self.backend == "symm" and self._stream is not None:
             from ..ops import _lib
 
-            _lib.reserve_sms(self._symm.max_ctas)   # until finish(): the collectives of this step share the GPU with backward
+            if os.environ.get("STACR_COMM_RESERVE", "1") == "1":
+                _lib.reserve_sms(self._symm.max_ctas)   # until finish(): the collectives of this step share the GPU with backward
         if self._stream is None:
             self._reduce(lo, hi)
             return

@@ -118,6 +118,83 @@ def engine_for(device: torch.device, max_elems: int, group=None) -> Optional[Gem
     return eng
 
 
+class TPContext:
+    """What a compressed linear layer needs to know to act as a tensor-parallel shard.
+
+    ``kind == "row"``: the layer holds input columns; its forward product is a partial sum that has to be added over the
+    ranks.  ``kind == "column"``: the layer holds output rows of a replicated input; its input gradient is the partial sum.
+    In both cases the compressed layer's own GEMM call is replaced by :meth:`gemm_sum`, which runs the product and the sum
+    as one kernel pair over symmetric memory when it can (bf16 CUDA operands, symmetric memory, a supported degree) and
+    as GEMM + ``all_reduce`` otherwise.  Activation compression itself is untouched: a row-parallel shard tracks a basis of
+    its ``N / tp`` input columns, a column-parallel shard one of the replicated input
+    (stacr/protocols/tp_gpt2.py:350-352 of the reference).
+    """
+
+    def __init__(self, kind: str, group=None, fused: bool = True):
+        if kind not in ("row", "column"):
+            raise ValueError("kind must be 'row' or 'column'")
+        self.kind, self.group, self.fused = kind, group, fused
+
+    def gemm_sum(self, a: torch.Tensor, b: torch.Tensor, *, b_mn: bool, bias: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """``sum over ranks of (a @ b^T [+ bias])`` for bf16 CUDA operands (``b`` is ``[N, K]`` or, with ``b_mn``, ``[K, N]``)."""
+        from ..ops.gemm import gemm
+
+        m = a.shape[0]
+        n = b.shape[1] if b_mn else b.shape[0]
+        eng = None
+        if self.fused and n % 16 == 0 and a.shape[1] % 8 == 0:
+            eng = engine_for(a.device, m * n, self.group)
+        if eng is not None:
+            return eng(a, b, b_mn=b_mn, bias=bias)
+        y = gemm(a, b, b_mn=b_mn, bias=bias)
+        if _world(self.group) > 1:
+            dist.all_reduce(y, group=self.group)
+        return y
+
+    def sum_(self, t: torch.Tensor) -> torch.Tensor:
+        if _world(self.group) > 1:
+            t = t.contiguous()
+            dist.all_reduce(t, group=self.group)
+        return t
+
+    def exact(self, x: torch.Tensor, layer) -> torch.Tensor:
+        """The uncompressed path of a wrapped shard (evaluation, frozen weights): plain product plus this shard's collective."""
+        w = layer.weight.t() if layer.transposed else layer.weight
+        if self.kind == "row":
+            y = F.linear(x, w, layer.bias)
+            return self.sum_(y) if not torch.is_grad_enabled() else _AllReduceFn.apply(y, self.group)
+        if torch.is_grad_enabled() and x.requires_grad:
+            x = _CopyFn.apply(x, self.group)
+        return F.linear(x, w, layer.bias)
+
+
+class _AllReduceFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, t, group):
+        t = t.clone()
+        if _world(group) > 1:
+            dist.all_reduce(t, group=group)
+        return t
+
+    @staticmethod
+    def backward(ctx, g):
+        return g, None
+
+
+class _CopyFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, t, group):
+        ctx.group = group
+        return t.view_as(t)
+
+    @staticmethod
+    def backward(ctx, g):
+        g = g.contiguous()
+        if _world(ctx.group) > 1:
+            dist.all_reduce(g, group=ctx.group)
+        return g, None
+
+
 def _bf16(t: torch.Tensor) -> torch.Tensor:
     return t if t.dtype == torch.bfloat16 else t.to(torch.bfloat16)
 

@@ -14,7 +14,7 @@ import torch
 from torch import nn
 from torch.nn import functional as F
 
-from ..parallel.tp import column_parallel_linear, row_parallel_linear
+from ..parallel.tp import TPContext, column_parallel_linear, row_parallel_linear
 from .tensor_parallel import (convert_conv1d_to_linear, copy_to_tp_region, reduce_from_tp_region, shard_linear_column,
                               shard_linear_row)
 
@@ -33,6 +33,25 @@ def shard_gpt2_qkv_column(linear: nn.Linear, tp_rank: int, tp_world_size: int, n
         if linear.bias is not None:
             out.bias.copy_(linear.bias[rows])
     return out
+
+
+def _shard_call(layer, x, kind: str, group, fused: bool):
+    """Run one tensor-parallel shard.  A plain ``nn.Linear`` goes through the functional fused forms; a compressed shard
+    (the projection engine's ``STACRLinear``) is told its role once and then performs the collective inside its own GEMMs;
+    any other wrapper keeps the explicit collectives around it."""
+    from ..layers import STACRLinear
+
+    if type(layer) is nn.Linear:
+        fn = column_parallel_linear if kind == "column" else row_parallel_linear
+        return fn(x, layer, group, fused)
+    if isinstance(layer, STACRLinear):
+        ctx = getattr(layer, "tp_context", None)
+        if ctx is None or ctx.kind != kind or ctx.group is not group or ctx.fused != fused:
+            layer.tp_context = TPContext(kind, group, fused)
+        return layer(x)
+    if kind == "column":
+        return layer(copy_to_tp_region(x, group))
+    return reduce_from_tp_region(layer(x), group)
 
 
 def _find(module, *names, default=None):
@@ -55,15 +74,9 @@ class TPGPT2MLP(nn.Module):
         self.fused_collectives = True
 
     def forward(self, hidden_states):
-        # a plain shard runs with its collective inside the GEMM; a wrapped (compressed) shard keeps the explicit one
-        if type(self.c_fc) is nn.Linear:
-            x = column_parallel_linear(hidden_states, self.c_fc, self.tp_group, self.fused_collectives)
-        else:
-            x = self.c_fc(copy_to_tp_region(hidden_states, self.tp_group))
+        x = _shard_call(self.c_fc, hidden_states, "column", self.tp_group, self.fused_collectives)
         x = self.act(x)
-        if type(self.c_proj) is nn.Linear:
-            return self.dropout(row_parallel_linear(x, self.c_proj, self.tp_group, self.fused_collectives))
-        return self.dropout(reduce_from_tp_region(self.c_proj(x), self.tp_group))
+        return self.dropout(_shard_call(self.c_proj, x, "row", self.tp_group, self.fused_collectives))
 
 
 class TPGPT2Attention(nn.Module):
@@ -84,10 +97,7 @@ class TPGPT2Attention(nn.Module):
 
     def forward(self, hidden_states, attention_mask=None, **kwargs):
         b, s, _ = hidden_states.shape
-        if type(self.c_attn) is nn.Linear:
-            qkv = column_parallel_linear(hidden_states, self.c_attn, self.tp_group, self.fused_collectives)
-        else:
-            qkv = self.c_attn(copy_to_tp_region(hidden_states, self.tp_group))
+        qkv = _shard_call(self.c_attn, hidden_states, "column", self.tp_group, self.fused_collectives)
         x = hidden_states
         q, k, v = qkv.split(self.local_heads * self.head_dim, dim=-1)
         shape = lambda t: t.view(b, s, self.local_heads, self.head_dim).transpose(1, 2)
@@ -97,10 +107,7 @@ class TPGPT2Attention(nn.Module):
         ctx = F.scaled_dot_product_attention(shape(q), shape(k), shape(v), attn_mask=mask, is_causal=mask is None,
                                              dropout_p=self.attn_pdrop if self.training else 0.0)
         merged = ctx.transpose(1, 2).reshape(b, s, self.local_heads * self.head_dim)
-        if type(self.c_proj) is nn.Linear:
-            out = self.resid_dropout(row_parallel_linear(merged, self.c_proj, self.tp_group, self.fused_collectives))
-        else:
-            out = self.resid_dropout(reduce_from_tp_region(self.c_proj(merged), self.tp_group))
+        out = self.resid_dropout(_shard_call(self.c_proj, merged, "row", self.tp_group, self.fused_collectives))
         if kwargs.get("output_attentions") is not None or kwargs.get("use_cache") is not None or "layer_past" in kwargs:
             return out, None  # Hugging Face block expects a tuple
         return out
