@@ -172,6 +172,81 @@ __global__ void __launch_bounds__(512) allreduce_multimem_kernel(const CommArgs 
   rank_barrier(a, 1, &s_fail);
 }
 
+// bf16 all-reduce in place (sum, fp32 accumulation): [lo, hi) are bf16 element indices, multiples of 8.  Rank r owns the r-th
+// of W equal runs of 16-byte vectors: it reduces them (in the switch through the multicast address, or with peer loads) and
+// stores the result into every rank's copy.  Used for the tensor-parallel activations (sum of partial products).
+__global__ void __launch_bounds__(512) allreduce_bf16_kernel(const CommArgs a) {
+  __shared__ int s_fail;
+  __shared__ unsigned long long s_peers[MAX_RANKS];
+  if (threadIdx.x == 0) s_fail = 0;
+  if (threadIdx.x < a.world) s_peers[threadIdx.x] = a.peer_ptrs[threadIdx.x];
+  __syncthreads();
+  if (!rank_barrier(a, 0, &s_fail)) return;
+  const long long v0 = a.lo / 8, vecs = (a.hi - a.lo) / 8;
+  const long long per = (vecs + a.world - 1) / a.world;
+  const long long begin = v0 + min(vecs, per * a.rank), end = v0 + min(vecs, per * (a.rank + 1));
+  const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+  constexpr int UNROLL = 4;
+  for (long long i0 = begin + blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i0 < end; i0 += stride * UNROLL) {
+    uint4 r[UNROLL];
+    if (a.mc_ptr != 0) {
+#pragma unroll
+      for (int u = 0; u < UNROLL; ++u) {
+        const long long i = i0 + u * stride;
+        if (i < end) {
+          const uint4* addr = reinterpret_cast<const uint4*>(a.mc_ptr) + i;
+          asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0, %1, %2, %3}, [%4];"
+                       : "=r"(r[u].x), "=r"(r[u].y), "=r"(r[u].z), "=r"(r[u].w)
+                       : "l"(addr)
+                       : "memory");
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < UNROLL; ++u) {
+        const long long i = i0 + u * stride;
+        if (i < end) {
+          uint4* addr = reinterpret_cast<uint4*>(a.mc_ptr) + i;
+          asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(__uint_as_float(r[u].x)),
+                       "f"(__uint_as_float(r[u].y)), "f"(__uint_as_float(r[u].z)), "f"(__uint_as_float(r[u].w))
+                       : "memory");
+        }
+      }
+    } else {
+      float acc[UNROLL][8];
+#pragma unroll
+      for (int u = 0; u < UNROLL; ++u)
+#pragma unroll
+        for (int k = 0; k < 8; ++k) acc[u][k] = 0.f;
+      for (int p = 0; p < a.world; ++p) {
+        const uint4* base = reinterpret_cast<const uint4*>(s_peers[(a.rank + p) % a.world]);
+#pragma unroll
+        for (int u = 0; u < UNROLL; ++u) {
+          const long long i = i0 + u * stride;
+          if (i < end) {
+            const uint4 raw = base[i];
+            const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+              acc[u][2 * k] += __uint_as_float(w[k] << 16);
+              acc[u][2 * k + 1] += __uint_as_float(w[k] & 0xFFFF0000u);
+            }
+          }
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < UNROLL; ++u) {
+        const long long i = i0 + u * stride;
+        if (i < end) {
+          const uint4 out = make_uint4(pack_bf16x2(acc[u][0], acc[u][1]), pack_bf16x2(acc[u][2], acc[u][3]), pack_bf16x2(acc[u][4], acc[u][5]),
+                                       pack_bf16x2(acc[u][6], acc[u][7]));
+          for (int p = 0; p < a.world; ++p) reinterpret_cast<uint4*>(s_peers[(a.rank + p) % a.world])[i] = out;
+        }
+      }
+    }
+  }
+  rank_barrier(a, 1, &s_fail);
+}
+
 // Reduce-scatter with caller-chosen ownership: every rank reduces the part [own_lo, own_hi) of [lo, hi) that it owns
 // (summing all ranks' copies, scaled) and stores the result into ITS OWN copy only.  Nothing is broadcast: the consumer
 // of the reduced gradient is the owner's shard of the optimizer.  Half the NVLink traffic of the all-reduce above.
@@ -399,6 +474,19 @@ extern "C" int sb_reduce_to_owner(const void* peer_ptrs, const void* flag_ptrs, 
   const long long b = own_lo > lo ? own_lo : lo, e = own_hi < hi ? own_hi : hi;
   const int grid = comm_grid(e > b ? (e - b) / 4 : 0, sms);
   reduce_to_owner_kernel<<<grid, 512, 0, static_cast<cudaStream_t>(stream)>>>(a, own_lo, own_hi);
+  return static_cast<int>(cudaGetLastError());
+}
+
+// In-place bf16 sum over ranks of elements [lo, hi) (multiples of 8) of a symmetric bf16 buffer; mc_ptr != 0 selects the in-switch form.
+extern "C" int sb_allreduce_bf16(const void* peer_ptrs, const void* flag_ptrs, unsigned long long mc_ptr, int rank, int world, long long lo,
+                                 long long hi, int epoch, int sms, int* status, void* stream) {
+  using namespace sb;
+  if (world < 1 || world > MAX_RANKS) return -2;
+  if ((lo & 7) || (hi & 7) || hi < lo) return -3;
+  CommArgs a{static_cast<const unsigned long long*>(peer_ptrs), static_cast<const unsigned long long*>(flag_ptrs), mc_ptr, rank, world,
+             lo, hi, 1.f, epoch, status, sb::comm_wait_ns()};
+  const int grid = comm_grid((hi - lo) / 8 / world, sms);
+  allreduce_bf16_kernel<<<grid, 512, 0, static_cast<cudaStream_t>(stream)>>>(a);
   return static_cast<int>(cudaGetLastError());
 }
 

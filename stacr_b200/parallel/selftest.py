@@ -99,33 +99,39 @@ def _fused_dw_check(buf, rank, world, dev, report) -> bool:
 
 
 def _tp_gemm_check(rank, world, dev, report) -> bool:
-    """GEMM with the all-reduce in its epilogue vs library GEMM + NCCL all-reduce (shapes of a GPT-2-large block at TP degree `world`)."""
-    from .tp import GemmAllReduce
+    """Both tensor-parallel engines (single kernel with the sum in the epilogue; GEMM kernel + bf16 all-reduce kernel) against
+    a library GEMM + NCCL all-reduce (shapes of a GPT-2-large block at TP degree `world`)."""
+    from .tp import GemmAllReduce, GemmThenAllReduce
 
     m, n, k = 4096, 1280, 5120 // world
     gen = torch.Generator(device=dev).manual_seed(500 + rank)
     a = (torch.randn(m, k, device=dev, generator=gen) / 8).bfloat16()
     w = (torch.randn(n, k, device=dev, generator=gen) / 8).bfloat16()
     bias = torch.randn(n, device=dev, generator=gen) if rank == 0 else None
-    eng = GemmAllReduce(m * n, dev)
+    want = a.float() @ w.float().t()
+    if bias is not None:
+        want += bias
+    dist.all_reduce(want)
     good = True
-    for mm in ([False, True] if eng.bufs[0].multicast_ptr else [False]):
-        for b in eng.bufs:
-            b.use_multimem = mm
-        want = a.float() @ w.float().t()
-        if bias is not None:
-            want += bias
-        dist.all_reduce(want)
-        for _ in range(3):                       # three calls: both staging buffers and their clearing are exercised
-            got = eng(a, w, bias=bias)
-        torch.cuda.synchronize()
-        _lib.check_status(dev)
-        err = float((got.float() - want).abs().max() / want.abs().max())
-        name = "multimem" if mm else "p2p"
-        report[f"tp_gemm_allreduce_{name}_rel_err"] = err
-        good &= err < 2e-2                       # bf16 partial sums added in bf16
-        report[f"tp_gemm_allreduce_{name}_ms"] = _time(lambda: eng(a, w, bias=bias), iters=20)
-        report[f"tp_gemm_allreduce_{name}_kernel_us"] = _kernel_times(lambda: eng(a, w, bias=bias))
+    engines = [("pair", GemmThenAllReduce(m * n, dev))]
+    if world <= 8:
+        engines.append(("fused", GemmAllReduce(m * n, dev)))
+    for label, eng in engines:
+        bufs = eng.bufs if label == "fused" else [eng.buf]
+        for mm in ([False, True] if bufs[0].multicast_ptr else [False]):
+            for b in bufs:
+                b.use_multimem = mm
+            for _ in range(3):                       # three calls: buffer reuse (and, for the fused engine, both staging buffers) is exercised
+                got = eng(a, w, bias=bias)
+            torch.cuda.synchronize()
+            _lib.check_status(dev)
+            err = float((got.float() - want).abs().max() / want.abs().max())
+            name = f"{label}_{'multimem' if mm else 'p2p'}"
+            report[f"tp_gemm_allreduce_{name}_rel_err"] = err
+            good &= err < 2e-2                       # bf16 partial sums
+            report[f"tp_gemm_allreduce_{name}_ms"] = _time(lambda: eng(a, w, bias=bias), iters=20)
+            report[f"tp_gemm_allreduce_{name}_kernel_us"] = _kernel_times(lambda: eng(a, w, bias=bias))
+    report["tp_gemm_allreduce_p2p_rel_err"] = report.get("tp_gemm_allreduce_fused_p2p_rel_err", report["tp_gemm_allreduce_pair_p2p_rel_err"])
 
     def library():
         y = torch.nn.functional.linear(a, w)

@@ -96,6 +96,18 @@ class SymmetricBuffer:
         _lib.check_rc(rc, name)
         _lib.count(1)
 
+    def all_reduce_bf16_(self, lo: int, hi: int) -> None:
+        """In-place sum over ranks of ``tensor[lo:hi]`` of a bf16 buffer (bounds multiples of 8), fp32 accumulation."""
+        assert self.tensor.dtype == torch.bfloat16
+        self._epoch += 1
+        rc = _lib.load().sb_allreduce_bf16(
+            _lib.ptr(self._peer_ptrs), _lib.ptr(self._pad_ptrs), ctypes.c_ulonglong(self.multicast_ptr if self.use_multimem else 0),
+            ctypes.c_int(self.rank), ctypes.c_int(self.world), ctypes.c_longlong(lo), ctypes.c_longlong(hi), ctypes.c_int(self._epoch),
+            ctypes.c_int(self.max_ctas), _lib.ptr(_lib.status_word(self.tensor.device)), _lib.stream_ptr(),
+        )
+        _lib.check_rc(rc, "sb_allreduce_bf16")
+        _lib.count(1)
+
     def reduce_to_owner_(self, lo: int, hi: int, own_lo: int, own_hi: int, average: bool = True) -> None:
         """Sum (or mean) of ``tensor[lo:hi]`` across ranks, delivered only to owners: this rank ends up with the reduced
         ``tensor[own_lo:own_hi]`` in its own copy (the rest of ``[lo, hi)`` keeps its local values).  fp32 buffers only."""

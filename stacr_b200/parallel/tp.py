@@ -1,15 +1,21 @@
-"""Tensor-parallel linears whose collective is fused into the GEMM.
+"""Tensor-parallel linears whose collective runs on this library's kernels over symmetric memory.
 
 A Megatron-style block has two all-reduces on its critical path in each direction: the output of the row-parallel
 projection in forward and the input gradient of the column-parallel projection in backward.  Both are "GEMM, then
-sum over ranks".  :class:`GemmAllReduce` runs them as ONE tensor-core kernel per rank: the epilogue of every output
-tile adds the tile, as bf16, straight into the copy of the result that each rank holds in symmetric memory (one
-``multimem.red`` through the NVSwitch multicast address, or one ``red.add`` per peer pointer), so the transfer of
-tile i overlaps the math of tile i+1.  A second small kernel waits until every rank has finished adding (flag
-barrier with a bounded wait), moves the local copy into an ordinary tensor (adding the bias) and clears the staging
-copy.  Two staging buffers alternate, which is what makes the clear race-free without a barrier in front of the GEMM:
-a rank can only start adding into buffer ``k+1`` of a peer after that peer has passed the barrier of call ``k``,
-and the peer cleared buffer ``k+1`` before it arrived there.
+sum over ranks".  Two engines serve them (``STACR_TP_ENGINE``):
+
+* :class:`GemmThenAllReduce` (default): the CTA-pair tensor-core GEMM writes the partial product into a symmetric bf16
+  buffer and a bf16 all-reduce kernel sums it in place, in the switch (``multimem.ld_reduce`` with fp32 accumulation +
+  ``multimem.st``) or with peer loads and stores.  Any degree up to 16.
+* :class:`GemmAllReduce`: ONE tensor-core kernel per rank whose epilogue stores every partial output tile, as whole
+  128-byte row segments, into this rank's slot of a staging buffer on *every* rank (``multimem.st`` or peer stores), so
+  the transfer of tile i overlaps the math of tile i+1; a second small kernel waits on a flag barrier (bounded) and sums
+  the slots locally.  Two staging buffers alternate, so no barrier precedes the GEMM.  Every rank receives ``world``
+  tiles per product, which limits it to small degrees, and the remote stores lengthen the GEMM itself; it is kept as
+  the measured alternative.
+
+A compressed shard (the projection engine's layer) performs the same collective inside its own forward / input-gradient
+product through :class:`TPContext`.
 
 Replaces the ``clone() + dist.all_reduce`` after the row-parallel GEMM and the ``all_reduce`` of the input gradient
 of the reference (stacr/protocols/tensor_parallel.py:25-64 there).  Without CUDA, symmetric memory or bf16 operands
@@ -89,6 +95,35 @@ class GemmAllReduce:
         return out
 
 
+class GemmThenAllReduce:
+    """``sum over ranks of (A_r @ B_r^T)`` as two in-tree kernels: the CTA-pair tensor-core GEMM writes its bf16 result into
+    a symmetric buffer and the bf16 all-reduce kernel sums it in place over NVLink (in the switch when the fabric has a
+    multicast address), after which the result is copied out.  At the sizes of a tensor-parallel GPT-2 block this is
+    faster than the single kernel whose epilogue stores every partial tile into every rank (the remote stores stretch a
+    24 us GEMM to 53 us at 4096 x 1280 x 2560 on two GPUs), and it works at any degree up to 16."""
+
+    def __init__(self, max_elems: int, device: torch.device, group=None):
+        from . import symm
+
+        self.group = group
+        self.buf = symm.SymmetricBuffer(max_elems, torch.bfloat16, device, group)
+        self.buf.max_ctas = max(self.buf.max_ctas, 16)
+        self.world, self.rank, self.max_elems, self.device = self.buf.world, self.buf.rank, max_elems, device
+
+    def __call__(self, a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = False, bias: Optional[torch.Tensor] = None,
+                 alpha: float = 1.0) -> torch.Tensor:
+        from ..ops.gemm import gemm
+
+        m = a.shape[1] if a_mn else a.shape[0]
+        n = b.shape[1] if b_mn else b.shape[0]
+        if (m * n) % 8 or m * n > self.max_elems:
+            raise ValueError(f"output {m}x{n} needs a multiple of 8 elements and at most {self.max_elems}")
+        out = self.buf.tensor[: m * n].view(m, n)
+        gemm(a, b, a_mn=a_mn, b_mn=b_mn, bias=None if bias is None else bias.detach().float().contiguous(), out=out, alpha=alpha)
+        self.buf.all_reduce_bf16_(0, m * n)
+        return out.clone()
+
+
 _ENGINES: dict = {}
 
 
@@ -104,16 +139,27 @@ def _max_fused_world() -> int:
     return int(os.environ.get("STACR_TP_FUSED_MAX_WORLD", "2"))
 
 
-def engine_for(device: torch.device, max_elems: int, group=None) -> Optional[GemmAllReduce]:
-    """One shared engine per (device, group), grown on demand; ``None`` when the fused path cannot run here."""
+def _engine_kind() -> str:
+    """``STACR_TP_ENGINE``: ``pair`` (default) = GEMM kernel + all-reduce kernel over symmetric memory, ``fused`` = the single
+    GEMM kernel with the sum in its epilogue (degrees up to ``STACR_TP_FUSED_MAX_WORLD``), ``nccl`` = library collectives."""
+    import os
+
+    return os.environ.get("STACR_TP_ENGINE", "pair")
+
+
+def engine_for(device: torch.device, max_elems: int, group=None):
+    """One shared engine per (device, group), grown on demand; ``None`` when the symmetric-memory paths cannot run here."""
     from . import symm
 
-    if _world(group) < 2 or _world(group) > _max_fused_world() or device.type != "cuda" or not symm.available():
+    kind = _engine_kind()
+    if _world(group) < 2 or device.type != "cuda" or kind == "nccl" or not symm.available():
         return None
-    key = (device.index, id(group))
+    if kind == "fused" and _world(group) > _max_fused_world():
+        kind = "pair"
+    key = (device.index, id(group), kind)
     eng = _ENGINES.get(key)
     if eng is None or eng.max_elems < max_elems:
-        eng = GemmAllReduce(max(max_elems, 1 << 22), device, group)
+        eng = (GemmAllReduce if kind == "fused" else GemmThenAllReduce)(max(max_elems, 1 << 22), device, group)
         _ENGINES[key] = eng
     return eng
 
@@ -195,6 +241,28 @@ class _CopyFn(torch.autograd.Function):
         return g, None
 
 
+def _on_kernels(t: torch.Tensor) -> bool:
+    """bf16 CUDA operands (directly or through bf16 autocast): the products of the plain shards run on the in-tree GEMM."""
+    if not (t.is_cuda and _lib.available()):
+        return False
+    return t.dtype == torch.bfloat16 or (torch.is_autocast_enabled("cuda") and torch.get_autocast_dtype("cuda") == torch.bfloat16)
+
+
+def _shard_products(g2d, x2d, weight, need_gx: bool, need_gw: bool, kernels: bool):
+    """``(dY W, dY^T X)`` of one shard: in-tree GEMMs on bf16 operands (fp32 weight gradient), framework products otherwise."""
+    if kernels and g2d.shape[1] % 8 == 0 and x2d.shape[1] % 8 == 0 and g2d.shape[0] % 8 == 0:
+        from ..layers import _bf16_weight
+        from ..ops.gemm import gemm
+
+        g = _bf16(g2d).contiguous()
+        gx = gemm(g, _bf16_weight(weight).contiguous(), b_mn=True).to(x2d.dtype) if need_gx else None
+        gw = gemm(g, _bf16(x2d).contiguous(), a_mn=True, b_mn=True, out_dtype=torch.float32).to(weight.dtype) if need_gw else None
+        return gx, gw
+    gx = (g2d.to(weight.dtype) @ weight).to(x2d.dtype) if need_gx else None
+    gw = (g2d.t().to(x2d.dtype) @ x2d).to(weight.dtype) if need_gw else None
+    return gx, gw
+
+
 def _bf16(t: torch.Tensor) -> torch.Tensor:
     return t if t.dtype == torch.bfloat16 else t.to(torch.bfloat16)
 
@@ -207,8 +275,11 @@ class _RowParallelFn(torch.autograd.Function):
         x2d = x.reshape(-1, x.shape[-1])
         ctx.save_for_backward(x2d, weight)
         ctx.has_bias, ctx.shape = bias is not None, x.shape
+        ctx.kernels = _on_kernels(x2d)
         if engine is not None:
-            y = engine(_bf16(x2d).contiguous(), _bf16(weight).contiguous(), bias=bias)
+            from ..layers import _bf16_weight
+
+            y = engine(_bf16(x2d).contiguous(), _bf16_weight(weight).contiguous(), bias=bias)
         else:
             y = F.linear(x2d, weight.to(x2d.dtype), None if bias is None else bias.to(x2d.dtype))
             if _world(group) > 1:
@@ -219,8 +290,9 @@ class _RowParallelFn(torch.autograd.Function):
     def backward(ctx, gy):
         x2d, weight = ctx.saved_tensors
         g2d = gy.reshape(-1, gy.shape[-1])
-        gx = (g2d.to(weight.dtype) @ weight).to(x2d.dtype).reshape(ctx.shape) if ctx.needs_input_grad[0] else None
-        gw = (g2d.t().to(x2d.dtype) @ x2d).to(weight.dtype) if ctx.needs_input_grad[1] else None
+        gx, gw = _shard_products(g2d, x2d, weight, ctx.needs_input_grad[0], ctx.needs_input_grad[1], ctx.kernels)
+        if gx is not None:
+            gx = gx.reshape(ctx.shape)
         gb = g2d.sum(0) if ctx.has_bias and ctx.needs_input_grad[2] else None
         return gx, gw, gb, None, None
 
@@ -233,7 +305,14 @@ class _ColumnParallelFn(torch.autograd.Function):
         x2d = x.reshape(-1, x.shape[-1])
         ctx.save_for_backward(x2d, weight)
         ctx.has_bias, ctx.shape, ctx.group, ctx.engine = bias is not None, x.shape, group, engine
-        y = F.linear(x2d, weight.to(x2d.dtype), None if bias is None else bias.to(x2d.dtype))
+        ctx.kernels = _on_kernels(x2d)
+        if ctx.kernels and x2d.shape[1] % 8 == 0 and weight.shape[0] % 8 == 0:
+            from ..layers import _bf16_weight
+            from ..ops.gemm import gemm
+
+            y = gemm(_bf16(x2d).contiguous(), _bf16_weight(weight).contiguous(), bias=None if bias is None else bias.detach().float().contiguous())
+        else:
+            y = F.linear(x2d, weight.to(x2d.dtype), None if bias is None else bias.to(x2d.dtype))
         return y.reshape(*x.shape[:-1], weight.shape[0])
 
     @staticmethod
@@ -243,14 +322,16 @@ class _ColumnParallelFn(torch.autograd.Function):
         gx = None
         if ctx.needs_input_grad[0]:
             if ctx.engine is not None:
+                from ..layers import _bf16_weight
+
                 # dX = dY @ W: W [out_local, in] is the [K, N] operand of this product
-                gx = ctx.engine(_bf16(g2d).contiguous(), _bf16(weight).contiguous(), b_mn=True).to(x2d.dtype)
+                gx = ctx.engine(_bf16(g2d).contiguous(), _bf16_weight(weight).contiguous(), b_mn=True).to(x2d.dtype)
             else:
-                gx = (g2d.to(weight.dtype) @ weight).to(x2d.dtype)
+                gx, _ = _shard_products(g2d, x2d, weight, True, False, ctx.kernels)
                 if _world(ctx.group) > 1:
                     dist.all_reduce(gx, group=ctx.group)
             gx = gx.reshape(ctx.shape)
-        gw = (g2d.t().to(x2d.dtype) @ x2d).to(weight.dtype) if ctx.needs_input_grad[1] else None
+        _, gw = _shard_products(g2d, x2d, weight, False, ctx.needs_input_grad[1], ctx.kernels)
         gb = g2d.sum(0) if ctx.has_bias and ctx.needs_input_grad[2] else None
         return gx, gw, gb, None, None
 
