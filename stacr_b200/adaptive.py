@@ -1004,6 +1004,12 @@ class STACRLinear(nn.Module):
                 gen = torch.Generator(device="cpu").manual_seed(0)
                 q = orthonormalize(torch.randn(n, r, generator=gen).to(x.device))
                 spectrum = None
+            elif (n > cfg.randomized_svd_threshold and x2d.is_cuda and x2d.dtype == torch.bfloat16 and r <= 32 and n % 8 == 0
+                  and cfg.rank_mode != "variance"):
+                # in-tree randomized range finder (tensor-core products, Gram-Schmidt and Jacobi kernels; no library solver)
+                from .ops.basis import range_finder_basis
+
+                q, spectrum = range_finder_basis(x2d.detach().contiguous(), r, iters=max(2, int(cfg.randomized_svd_niter) + 2)), None
             elif n > cfg.randomized_svd_threshold:
                 width = min(n, r + cfg.randomized_svd_oversampling)
                 _, s, v = torch.svd_lowrank(x, q=width, niter=cfg.randomized_svd_niter)

@@ -38,20 +38,29 @@ def oja_step_kernels(basis: torch.Tensor, x: torch.Tensor, lr: float) -> torch.T
 
 @torch.no_grad()
 def range_finder_basis(x: torch.Tensor, rank: int, iters: int = 4, oversample: int = 8) -> torch.Tensor:
-    """Approximate top-``rank`` right singular subspace of bf16 ``x`` by subspace iteration."""
+    """Approximate top-``rank`` right singular subspace of bf16 ``x`` by subspace iteration.
+
+    Every step is an in-tree kernel: the two skinny products on the tensor cores, the orthonormalisation of the
+    ``[features, width]`` iterate by Gram-Schmidt with re-orthogonalisation, the ``width x width`` Gram matrix of the projected
+    rows in fp64, and its eigen-decomposition by Jacobi rotations (no library QR or eigensolver is called).
+    """
     rows, n = x.shape
     x = x.contiguous()
     width = min(32, rank + oversample, n)
     gen = torch.Generator(device="cpu").manual_seed(0)
-    q = torch.linalg.qr(torch.randn(n, width, generator=gen).to(x.device)).Q
+    q = stacr_ops.orthonormalize_columns_(torch.randn(n, width, generator=gen).to(x.device).contiguous())
     for _ in range(iters):
         qt = stacr_ops.pad_basis_transpose(q.to(torch.bfloat16).contiguous())
         y = stacr_ops.project(x, qt)[:, :width]
         g = stacr_ops.at_b(x, stacr_ops.transpose_pad(y))[:, :width]
-        q = torch.linalg.qr(g).Q
+        q = stacr_ops.orthonormalize_columns_(g.contiguous())
     qt = stacr_ops.pad_basis_transpose(q.to(torch.bfloat16).contiguous())
-    y = stacr_ops.project(x, qt)[:, :width]
-    evals, evecs = torch.linalg.eigh((y.t() @ y).double())
-    order = torch.argsort(evals, descending=True)[:rank]
-    rotated = q.double() @ evecs[:, order]
-    return torch.linalg.qr(rotated.float()).Q.contiguous()
+    y = stacr_ops.project(x, qt)[:, :width].contiguous()
+    _, evecs = stacr_ops.small_eigh(stacr_ops.small_gram(y))
+    # rotate the iterate so that its columns are ordered by captured energy, keep the leading ones; the product of a matrix with
+    # orthonormal columns and an orthogonal one has orthonormal columns, one Gram-Schmidt pass removes the rounding
+    rotated = torch.zeros(n, rank, dtype=torch.float32, device=x.device)
+    lead = evecs[:, :rank].float()
+    for j in range(width):           # width <= 32 rank-one accumulations of an [n, rank] matrix: element-wise kernels only
+        rotated.addcmul_(q[:, j:j + 1], lead[j:j + 1, :])
+    return stacr_ops.orthonormalize_columns_(rotated.contiguous())

@@ -424,6 +424,198 @@ __global__ void __launch_bounds__(1024) oja_update_cluster8_kernel(const float* 
 
 // Q' = orth(Q + lr (G/rows - Q (Y^T Y)/rows)).  g: [n, ldg] fp32; y: [rows, ldy] fp32 (both may be NULL
 // with lr == 0 to only re-orthonormalise and refresh the bf16 copies).  q_out must not alias q_in.
+namespace sb {
+
+// ------------------------------------------------------------------------------------------------
+// Small dense algebra for the basis initialisation (no library solver): orthonormalisation of a tall thin matrix by
+// modified Gram-Schmidt with re-orthogonalisation, the Gram matrix of a tall thin matrix, and the eigen-decomposition of
+// a symmetric matrix of order <= 32 by cyclic Jacobi rotations.  One-off work per layer; written for robustness (the
+// iterates of a subspace iteration are close to collinear, which breaks Cholesky-based orthonormalisation in fp32).
+// ------------------------------------------------------------------------------------------------
+constexpr int SMALL_W = 32;
+
+// In place: columns of a[n, w] (row-major, leading dimension lda) become orthonormal.  One CTA of 1024 threads.
+// For every column: two rounds of (coefficients against all previous columns in ONE block reduction, subtract), then
+// normalise.  A column that vanishes (rank deficiency) is replaced by a unit vector orthogonalised the same way.
+__global__ void __launch_bounds__(1024) mgs_qr_kernel(float* a, int n, int w, int lda) {
+  __shared__ float s_red[32][SMALL_W + 1];
+  __shared__ float s_coef[SMALL_W + 1];
+  const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
+  for (int j = 0; j < w; ++j) {
+    for (int attempt = 0; attempt < 2; ++attempt) {
+      for (int round = 0; round < 2; ++round) {
+        // coefficients c[i] = <a_i, a_j> for i < j, and the squared norm of a_j in slot j
+        float part[SMALL_W + 1];
+#pragma unroll
+        for (int i = 0; i <= SMALL_W; ++i) part[i] = 0.f;
+        for (int row = t; row < n; row += blockDim.x) {
+          const float v = a[static_cast<size_t>(row) * lda + j];
+#pragma unroll
+          for (int i = 0; i < SMALL_W; ++i)
+            if (i < j) part[i] = fmaf(a[static_cast<size_t>(row) * lda + i], v, part[i]);
+          part[SMALL_W] = fmaf(v, v, part[SMALL_W]);
+        }
+#pragma unroll
+        for (int i = 0; i <= SMALL_W; ++i) {
+          float v = part[i];
+#pragma unroll
+          for (int off = 16; off; off >>= 1) v += __shfl_xor_sync(0xffffffffu, v, off);
+          if (lane == 0) s_red[warp][i] = v;
+        }
+        __syncthreads();
+        if (t <= SMALL_W) {
+          float v = 0.f;
+          for (int k = 0; k < 32; ++k) v += s_red[k][t];
+          s_coef[t] = v;
+        }
+        __syncthreads();
+        for (int row = t; row < n; row += blockDim.x) {
+          float v = a[static_cast<size_t>(row) * lda + j];
+          for (int i = 0; i < j; ++i) v = fmaf(-s_coef[i], a[static_cast<size_t>(row) * lda + i], v);
+          a[static_cast<size_t>(row) * lda + j] = v;
+        }
+        __syncthreads();
+      }
+      // norm after the two rounds
+      float nn = 0.f;
+      for (int row = t; row < n; row += blockDim.x) {
+        const float v = a[static_cast<size_t>(row) * lda + j];
+        nn = fmaf(v, v, nn);
+      }
+#pragma unroll
+      for (int off = 16; off; off >>= 1) nn += __shfl_xor_sync(0xffffffffu, nn, off);
+      if (lane == 0) s_red[warp][0] = nn;
+      __syncthreads();
+      if (t == 0) {
+        float v = 0.f;
+        for (int k = 0; k < 32; ++k) v += s_red[k][0];
+        s_coef[0] = v;
+      }
+      __syncthreads();
+      const float norm2 = s_coef[0];
+      __syncthreads();
+      if (norm2 > 1e-20f) {
+        const float inv = rsqrtf(norm2);
+        for (int row = t; row < n; row += blockDim.x) a[static_cast<size_t>(row) * lda + j] *= inv;
+        __syncthreads();
+        break;
+      }
+      // the column vanished: restart it from the unit vector e_(j mod n) and orthogonalise again
+      for (int row = t; row < n; row += blockDim.x) a[static_cast<size_t>(row) * lda + j] = (row == j % n) ? 1.f : 0.f;
+      __syncthreads();
+    }
+  }
+}
+
+// out[w, w] += a^T a for a[rows, w] (row-major, lda), w <= 32; out zeroed by the caller.  CTA (32 x 32 threads) per row slab.
+__global__ void __launch_bounds__(1024) gram_small_kernel(const float* a, int rows, int w, int lda, int slab, double* out) {
+  const int i = threadIdx.y, j = threadIdx.x;
+  const int r0 = blockIdx.x * slab, r1 = min(rows, r0 + slab);
+  double acc = 0.0;
+  if (i < w && j < w)
+    for (int row = r0; row < r1; ++row) acc += static_cast<double>(a[static_cast<size_t>(row) * lda + i]) * static_cast<double>(a[static_cast<size_t>(row) * lda + j]);
+  if (i < w && j < w) atomicAdd(out + i * w + j, acc);
+}
+
+// Eigen-decomposition of the symmetric matrix m[w, w] (fp64, row-major), w <= 32, by cyclic Jacobi rotations in one warp
+// (lane k owns row k of the working matrix and of the accumulated rotations).  Eigenvalues in descending order in
+// evals[w]; the matching eigenvectors are the COLUMNS of evecs[w, w].
+__global__ void __launch_bounds__(32) jacobi_eig_kernel(const double* m, int w, double* evals, double* evecs) {
+  __shared__ double A[SMALL_W][SMALL_W + 1];
+  __shared__ double V[SMALL_W][SMALL_W + 1];
+  __shared__ int order[SMALL_W];
+  const int k = threadIdx.x;
+  for (int j = 0; j < w; ++j) {
+    if (k < w) {
+      A[k][j] = 0.5 * (m[k * w + j] + m[j * w + k]);
+      V[k][j] = (k == j) ? 1.0 : 0.0;
+    }
+  }
+  __syncwarp();
+  for (int sweep = 0; sweep < 30; ++sweep) {
+    double off = 0.0;
+    if (k < w)
+      for (int j = 0; j < w; ++j)
+        if (j != k) off += A[k][j] * A[k][j];
+#pragma unroll
+    for (int o = 16; o; o >>= 1) off += __shfl_xor_sync(0xffffffffu, off, o);
+    double diag = (k < w) ? fabs(A[k][k]) : 0.0;
+#pragma unroll
+    for (int o = 16; o; o >>= 1) diag = fmax(diag, __shfl_xor_sync(0xffffffffu, diag, o));
+    if (off <= 1e-28 * diag * diag + 1e-300) break;
+    for (int p = 0; p < w - 1; ++p) {
+      for (int q = p + 1; q < w; ++q) {
+        const double apq = A[p][q];
+        double c = 1.0, s = 0.0;
+        if (fabs(apq) > 1e-300) {
+          const double theta = (A[q][q] - A[p][p]) / (2.0 * apq);
+          const double tt = (theta >= 0.0 ? 1.0 : -1.0) / (fabs(theta) + sqrt(theta * theta + 1.0));
+          c = 1.0 / sqrt(tt * tt + 1.0);
+          s = tt * c;
+        }
+        __syncwarp();
+        if (k < w) {  // columns p and q of A and V, row k
+          const double akp = A[k][p], akq = A[k][q];
+          A[k][p] = c * akp - s * akq;
+          A[k][q] = s * akp + c * akq;
+          const double vkp = V[k][p], vkq = V[k][q];
+          V[k][p] = c * vkp - s * vkq;
+          V[k][q] = s * vkp + c * vkq;
+        }
+        __syncwarp();
+        if (k < w) {  // rows p and q of A, column k
+          const double apk = A[p][k], aqk = A[q][k];
+          A[p][k] = c * apk - s * aqk;
+          A[q][k] = s * apk + c * aqk;
+        }
+        __syncwarp();
+      }
+    }
+  }
+  if (k == 0) {  // selection sort of the diagonal, descending
+    for (int i = 0; i < w; ++i) order[i] = i;
+    for (int i = 0; i < w; ++i)
+      for (int j = i + 1; j < w; ++j)
+        if (A[order[j]][order[j]] > A[order[i]][order[i]]) {
+          const int tmp = order[i];
+          order[i] = order[j];
+          order[j] = tmp;
+        }
+  }
+  __syncwarp();
+  if (k < w) {
+    evals[k] = A[order[k]][order[k]];
+    for (int j = 0; j < w; ++j) evecs[k * w + j] = V[k][order[j]];
+  }
+}
+
+}  // namespace sb
+
+// Orthonormalise the columns of fp32 a[n, w] in place (w <= 32).
+extern "C" int sb_mgs_qr(float* a, int n, int w, int lda, void* stream) {
+  if (n <= 0 || w <= 0) return 0;
+  if (w > sb::SMALL_W) return -2;
+  sb::mgs_qr_kernel<<<1, 1024, 0, static_cast<cudaStream_t>(stream)>>>(a, n, w, lda);
+  return static_cast<int>(cudaGetLastError());
+}
+
+// out (fp64 [w, w], zeroed by the caller) += a^T a for fp32 a[rows, w], w <= 32.
+extern "C" int sb_gram_small(const float* a, int rows, int w, int lda, double* out, void* stream) {
+  if (rows <= 0 || w <= 0) return 0;
+  if (w > sb::SMALL_W) return -2;
+  const int slab = 256;
+  sb::gram_small_kernel<<<(rows + slab - 1) / slab, dim3(32, 32), 0, static_cast<cudaStream_t>(stream)>>>(a, rows, w, lda, slab, out);
+  return static_cast<int>(cudaGetLastError());
+}
+
+// Symmetric eigen-decomposition of fp64 m[w, w], w <= 32: evals descending, eigenvectors in the columns of evecs.
+extern "C" int sb_jacobi_eig(const double* m, int w, double* evals, double* evecs, void* stream) {
+  if (w <= 0) return 0;
+  if (w > sb::SMALL_W) return -2;
+  sb::jacobi_eig_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(m, w, evals, evecs);
+  return static_cast<int>(cudaGetLastError());
+}
+
 extern "C" int sb_oja_update(const float* q_in, const float* g, int ldg, const float* y, int ldy, int rows, int n, int r,
                              float lr, float* q_out, void* q_bf16, void* qt_bf16, int rpad, int* status, void* stream) {
   if (r < 1 || r > sb::RMAX) return -2;

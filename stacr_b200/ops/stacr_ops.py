@@ -270,6 +270,40 @@ def oja_update(basis_fp32, g, y, rows: int, lr: float):
     return q_out, qb, qt
 
 
+def orthonormalize_columns_(a: torch.Tensor) -> torch.Tensor:
+    """In-place orthonormalisation of the columns of a contiguous fp32 ``[n, w]`` matrix, ``w <= 32`` (Gram-Schmidt with
+    re-orthogonalisation in one kernel: robust for the nearly collinear iterates of a subspace iteration)."""
+    assert a.dtype == torch.float32 and a.dim() == 2 and a.is_contiguous() and a.shape[1] <= 32
+    rc = _lib.load().sb_mgs_qr(_lib.ptr(a), c_int(a.shape[0]), c_int(a.shape[1]), c_int(a.stride(0)), _lib.stream_ptr())
+    _lib.check_rc(rc, "sb_mgs_qr")
+    _lib.count(1)
+    return a
+
+
+def small_gram(a: torch.Tensor) -> torch.Tensor:
+    """fp64 ``a^T a`` of a contiguous fp32 ``[rows, w]`` matrix, ``w <= 32``."""
+    assert a.dtype == torch.float32 and a.dim() == 2 and a.stride(1) == 1 and a.shape[1] <= 32
+    w = a.shape[1]
+    out = torch.zeros(w, w, dtype=torch.float64, device=a.device)
+    rc = _lib.load().sb_gram_small(_lib.ptr(a), c_int(a.shape[0]), c_int(w), c_int(a.stride(0)), _lib.ptr(out), _lib.stream_ptr())
+    _lib.check_rc(rc, "sb_gram_small")
+    _lib.count(1)
+    return out
+
+
+def small_eigh(m: torch.Tensor):
+    """``(eigenvalues descending, eigenvectors in columns)`` of a symmetric fp64 matrix of order ``<= 32`` (cyclic Jacobi)."""
+    assert m.dtype == torch.float64 and m.dim() == 2 and m.shape[0] == m.shape[1] <= 32
+    m = m.contiguous()
+    w = m.shape[0]
+    evals = torch.empty(w, dtype=torch.float64, device=m.device)
+    evecs = torch.empty(w, w, dtype=torch.float64, device=m.device)
+    rc = _lib.load().sb_jacobi_eig(_lib.ptr(m), c_int(w), _lib.ptr(evals), _lib.ptr(evecs), _lib.stream_ptr())
+    _lib.check_rc(rc, "sb_jacobi_eig")
+    _lib.count(1)
+    return evals, evecs
+
+
 _PLAN_TARGET = None
 
 
