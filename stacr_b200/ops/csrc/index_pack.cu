@@ -237,6 +237,28 @@ __global__ void __launch_bounds__(256) move_rows_kernel(const uint4* src, uint4*
   }
 }
 
+// Per-row symmetric int8 codec of a [rows, r] coefficient matrix (r <= 64): scale[row] = max(|row|) / 127 (at least the
+// smallest normal float), q = clamp(rint(x / scale), -127, 127).  One thread per row.
+template <typename T>
+__global__ void __launch_bounds__(256) quantize_rows_kernel(const T* x, long long rows, int r, int ldx, signed char* q, float* scale) {
+  for (long long row = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; row < rows; row += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const T* xr = x + row * ldx;
+    float amax = 0.f;
+    for (int j = 0; j < r; ++j) amax = fmaxf(amax, fabsf(to_f32<T>(xr[j])));
+    const float sc = fmaxf(amax / 127.f, 1.17549435e-38f);
+    scale[row] = sc;
+    const float inv = 1.f / sc;
+    for (int j = 0; j < r; ++j) q[row * r + j] = static_cast<signed char>(fminf(fmaxf(rintf(to_f32<T>(xr[j]) * inv), -127.f), 127.f));
+  }
+}
+
+// out[row, j] = bf16(q[row, j] * scale[row])
+__global__ void __launch_bounds__(256) dequantize_rows_kernel(const signed char* q, const float* scale, long long rows, int r, __nv_bfloat16* out) {
+  const long long total = rows * r;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total; i += static_cast<long long>(gridDim.x) * blockDim.x)
+    out[i] = __float2bfloat16_rn(static_cast<float>(q[i]) * scale[i / r]);
+}
+
 static inline unsigned grid_for(long long work, int threads, int cap) {
   long long g = (work + threads - 1) / threads;
   if (g > cap) g = cap;
@@ -310,5 +332,25 @@ extern "C" int sb_move_rows(const void* src, void* dst, const long long* index, 
   const int vecs = width / 8;
   move_rows_kernel<<<grid_for(count * vecs, 256, 1184 * 2), 256, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const uint4*>(src), static_cast<uint4*>(dst), index, count, vecs, scatter);
+  return static_cast<int>(cudaGetLastError());
+}
+
+// Per-row int8 quantisation of fp32 or bf16 x[rows, r] (leading dimension ldx): q int8 [rows, r] contiguous, scale fp32 [rows].
+extern "C" int sb_quantize_rows_int8(const void* x, int is_bf16, long long rows, int r, int ldx, void* q, float* scale, void* stream) {
+  using namespace sb;
+  if (rows <= 0 || r <= 0) return 0;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const unsigned grid = grid_for(rows, 256, 1184);
+  if (is_bf16) quantize_rows_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(x), rows, r, ldx, static_cast<signed char*>(q), scale);
+  else quantize_rows_kernel<float><<<grid, 256, 0, st>>>(static_cast<const float*>(x), rows, r, ldx, static_cast<signed char*>(q), scale);
+  return static_cast<int>(cudaGetLastError());
+}
+
+// bf16 out[rows, r] = q * scale[row].
+extern "C" int sb_dequantize_rows_int8(const void* q, const float* scale, long long rows, int r, void* out, void* stream) {
+  using namespace sb;
+  if (rows <= 0 || r <= 0) return 0;
+  dequantize_rows_kernel<<<grid_for(rows * r, 256, 1184), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const signed char*>(q), scale, rows, r, static_cast<__nv_bfloat16*>(out));
   return static_cast<int>(cudaGetLastError());
 }

@@ -110,3 +110,27 @@ def move_rows(src: torch.Tensor, index: torch.Tensor, *, scatter_into: torch.Ten
     _lib.check_rc(rc, "sb_move_rows")
     _lib.count(1)
     return dst
+
+
+def quantize_rows_int8(x: torch.Tensor):
+    """Per-row symmetric int8 codes of a ``[rows, r]`` fp32 / bf16 matrix (rows may be strided): ``(int8 [rows, r], fp32 scale [rows, 1])``."""
+    assert x.dim() == 2 and x.stride(1) == 1 and x.dtype in (torch.float32, torch.bfloat16)
+    rows, r = x.shape
+    q = torch.empty(rows, r, dtype=torch.int8, device=x.device)
+    scale = torch.empty(rows, 1, dtype=torch.float32, device=x.device)
+    rc = _lib.load().sb_quantize_rows_int8(_lib.ptr(x), c_int(int(x.dtype == torch.bfloat16)), c_ll(rows), c_int(r), c_int(x.stride(0)), _lib.ptr(q),
+                                           _lib.ptr(scale), _lib.stream_ptr())
+    _lib.check_rc(rc, "sb_quantize_rows_int8")
+    _lib.count(1)
+    return q, scale
+
+
+def dequantize_rows_int8(q: torch.Tensor, scale: torch.Tensor) -> torch.Tensor:
+    """bf16 ``q * scale[row]`` for contiguous int8 ``[rows, r]`` codes and fp32 per-row scales."""
+    rows, r = q.shape
+    out = torch.empty(rows, r, dtype=torch.bfloat16, device=q.device)
+    rc = _lib.load().sb_dequantize_rows_int8(_lib.ptr(q.contiguous()), _lib.ptr(scale.reshape(-1).contiguous()), c_ll(rows), c_int(r), _lib.ptr(out),
+                                             _lib.stream_ptr())
+    _lib.check_rc(rc, "sb_dequantize_rows_int8")
+    _lib.count(1)
+    return out

@@ -194,7 +194,36 @@ class CheckpointBoundaryCodec(nn.Module):
             return "residual_energy"
         return None
 
+    @staticmethod
+    def _on_kernels(flat: torch.Tensor, rank: int) -> bool:
+        """bf16 CUDA boundary tensors run the codec on the in-tree kernels: tensor-core projection, reduction kernels for the
+        Pythagoras energy, per-row int8 codec, and the low-rank reconstruction kernel on the way back."""
+        from ..ops import _lib
+
+        return flat.is_cuda and flat.dtype == torch.bfloat16 and flat.shape[1] % 8 == 0 and rank <= 32 and _lib.available()
+
+    def _project(self, flat: torch.Tensor) -> torch.Tensor:
+        if self._on_kernels(flat, self.spec.rank):
+            from ..layers import _basis_views
+            from ..ops import stacr_ops
+
+            _, qt = _basis_views(self.basis)
+            return stacr_ops.project(flat.contiguous(), qt)[:, : self.basis.shape[1]]          # fp32 coefficients
+        return flat @ self.basis.to(flat.dtype)
+
+    @staticmethod
+    def _sum_squares(t: torch.Tensor) -> torch.Tensor:
+        if t.is_cuda and t.dtype in (torch.bfloat16, torch.float32) and t.is_contiguous():
+            from ..ops import pack_ops
+
+            return pack_ops.sum_squares(t)
+        return t.float().square().sum()
+
     def _quantize_coefficients(self, coeff: torch.Tensor):
+        if coeff.is_cuda and coeff.dtype in (torch.float32, torch.bfloat16) and coeff.stride(1) == 1:
+            from ..ops import pack_ops
+
+            return pack_ops.quantize_rows_int8(coeff)
         amax = coeff.abs().amax(dim=1, keepdim=True).float()
         scale = (amax / 127.0).clamp_min(torch.finfo(torch.float32).tiny)
         q = torch.round(coeff.float() / scale).clamp_(-127, 127).to(torch.int8)
@@ -222,11 +251,10 @@ class CheckpointBoundaryCodec(nn.Module):
             self._update_basis(flat, reason="init")
         if not torch.isfinite(self.basis).all():
             return self._dense(tensor, "basis_nonfinite")
-        q = self.basis.to(flat.dtype)
-        coeff = flat @ q
+        coeff = self._project(flat)
         if not torch.isfinite(coeff).all():
             return self._dense(tensor, "coeff_nonfinite")
-        x2, c2 = flat.float().square().sum(), coeff.float().square().sum()
+        x2, c2 = self._sum_squares(flat), self._sum_squares(coeff if coeff.is_contiguous() else coeff.contiguous())
         energy = float(torch.sqrt((x2 - c2).clamp_min(0)) / (torch.sqrt(x2) + 1e-8))
         if energy != energy:
             return self._dense(tensor, "energy_nonfinite")
@@ -234,8 +262,7 @@ class CheckpointBoundaryCodec(nn.Module):
         reason = self._should_refresh(energy)
         if reason is not None:
             self._update_basis(flat, reason=reason)
-            q = self.basis.to(flat.dtype)
-            coeff = flat @ q
+            coeff = self._project(flat)
         rec = CompressedBoundaryRecord(s.site_id, tuple(tensor.shape), tensor.dtype, tensor.device, False, basis=self.basis)
         if s.quantize_coefficients:
             cq, scale = self._quantize_coefficients(coeff)
@@ -254,8 +281,17 @@ class CheckpointBoundaryCodec(nn.Module):
         self._unpacks += 1
         if packed.is_dense_fallback:
             return packed.dense_tensor
-        coeff = self._dequantize_coefficients(packed.coeff, packed.coeff_scale, packed.original_dtype) if packed.coeff_quantized else packed.coeff
-        out = (coeff @ packed.basis.to(coeff.dtype).t()).reshape(packed.original_shape).to(packed.original_dtype)
+        hidden = packed.basis.shape[0]
+        if packed.coeff.is_cuda and packed.original_dtype == torch.bfloat16 and hidden % 8 == 0 and packed.basis.shape[1] <= 32:
+            from ..ops import pack_ops, stacr_ops
+
+            # dequantise and rebuild C Q^T with the reconstruction kernel of the compressed layers (bf16 out, basis rows in registers)
+            cb = pack_ops.dequantize_rows_int8(packed.coeff, packed.coeff_scale) if packed.coeff_quantized else packed.coeff.to(torch.bfloat16).contiguous()
+            rows = cb.shape[0]
+            out = stacr_ops.rebuild_input(cb, packed.basis.float().contiguous(), None, rows, hidden).clone().reshape(packed.original_shape)
+        else:
+            coeff = self._dequantize_coefficients(packed.coeff, packed.coeff_scale, packed.original_dtype) if packed.coeff_quantized else packed.coeff
+            out = (coeff @ packed.basis.to(coeff.dtype).t()).reshape(packed.original_shape).to(packed.original_dtype)
         if not torch.isfinite(out).all():
             self.fallbacks["recon_nonfinite"] = self.fallbacks.get("recon_nonfinite", 0) + 1
             out = torch.nan_to_num(out)
