@@ -74,6 +74,61 @@ def _wrap_attention_forward(module: nn.Module) -> None:
     module._stacr_mask_wrapped = True
 
 
+class _GatherRows(torch.autograd.Function):
+    """``flat[rows]`` and its adjoint (scatter into zeros) on the row-move kernel for bf16 CUDA matrices."""
+
+    @staticmethod
+    def forward(ctx, flat, rows):
+        from ..ops import pack_ops
+
+        ctx.save_for_backward(rows)
+        ctx.total = flat.shape[0]
+        return pack_ops.move_rows(flat.contiguous(), rows)
+
+    @staticmethod
+    def backward(ctx, grad):
+        from ..ops import pack_ops
+
+        (rows,) = ctx.saved_tensors
+        full = torch.zeros(ctx.total, grad.shape[1], dtype=grad.dtype, device=grad.device)
+        return pack_ops.move_rows(grad.contiguous(), rows, scatter_into=full), None
+
+
+class _ScatterRows(torch.autograd.Function):
+    """Rows placed into a zero matrix of ``total`` rows, and the adjoint (gather), on the same kernel."""
+
+    @staticmethod
+    def forward(ctx, src, rows, total):
+        from ..ops import pack_ops
+
+        ctx.save_for_backward(rows)
+        full = torch.zeros(total, src.shape[1], dtype=src.dtype, device=src.device)
+        return pack_ops.move_rows(src.contiguous(), rows, scatter_into=full)
+
+    @staticmethod
+    def backward(ctx, grad):
+        from ..ops import pack_ops
+
+        (rows,) = ctx.saved_tensors
+        return pack_ops.move_rows(grad.contiguous(), rows), None, None
+
+
+def _rows_on_kernels(t: torch.Tensor) -> bool:
+    from ..ops import _lib
+
+    return t.is_cuda and t.dtype == torch.bfloat16 and t.dim() == 2 and t.shape[1] % 8 == 0 and _lib.available()
+
+
+def gather_rows(flat: torch.Tensor, rows: torch.Tensor) -> torch.Tensor:
+    return _GatherRows.apply(flat, rows) if _rows_on_kernels(flat) else flat.index_select(0, rows)
+
+
+def scatter_rows(src: torch.Tensor, rows: torch.Tensor, total: int) -> torch.Tensor:
+    if _rows_on_kernels(src):
+        return _ScatterRows.apply(src, rows, total)
+    return torch.zeros(total, src.shape[1], dtype=src.dtype, device=src.device).index_copy(0, rows, src)
+
+
 class _MaskAwareSTACRLinear(nn.Module):
     """Runs the wrapped compressed layer on real tokens only."""
 
@@ -90,9 +145,8 @@ class _MaskAwareSTACRLinear(nn.Module):
         rows = keep.reshape(-1).nonzero(as_tuple=False).reshape(-1)
         if rows.numel() == 0:
             return x.new_zeros(x.shape[0], x.shape[1], self.inner.out_features)
-        out_rows = self.inner(flat.index_select(0, rows))
-        out = torch.zeros(flat.shape[0], out_rows.shape[1], dtype=out_rows.dtype, device=out_rows.device)
-        out = out.index_copy(0, rows, out_rows)
+        out_rows = self.inner(gather_rows(flat, rows))
+        out = scatter_rows(out_rows, rows, flat.shape[0])
         return out.view(x.shape[0], x.shape[1], -1)
 
     def __getattr__(self, name: str):

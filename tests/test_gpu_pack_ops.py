@@ -116,3 +116,47 @@ def test_fixed_threshold_pass_lists_exactly_the_entries_above_the_threshold(rows
         both = len(set(got.tolist()) ^ set(want.tolist()))
         assert both <= 2, (both, got.numel(), want.numel())     # tensor-core vs chained-FMA rounding at the threshold itself
         assert (val.float().abs() > thr).all()
+
+
+def test_mask_aware_row_moves_are_differentiable_and_match_index_ops():
+    from stacr_b200.protocols.attention import gather_rows, scatter_rows
+
+    g = torch.Generator(device="cuda").manual_seed(11)
+    flat = torch.randn(200, 256, device="cuda", generator=g).bfloat16().requires_grad_(True)
+    rows = torch.randperm(200, device="cuda", generator=g)[:77].sort().values
+    picked = gather_rows(flat, rows)
+    out = scatter_rows(picked * 2, rows, 200)
+    ref_in = flat.detach().clone().requires_grad_(True)
+    ref = torch.zeros(200, 256, device="cuda", dtype=torch.bfloat16).index_copy(0, rows, ref_in.index_select(0, rows) * 2)
+    assert torch.equal(out, ref)
+    w = torch.randn(200, 256, device="cuda", generator=g).bfloat16()
+    (out * w).sum().backward()
+    (ref * w).sum().backward()
+    assert torch.equal(flat.grad, ref_in.grad)
+
+
+def test_per_row_int8_codec_and_boundary_codec_on_kernels():
+    from stacr_b200.ops import pack_ops
+    from stacr_b200.protocols.checkpointing import CheckpointBoundaryCodec, STACRCheckpointSpec
+
+    g = torch.Generator(device="cuda").manual_seed(13)
+    coeff = torch.randn(1000, 16, device="cuda", generator=g) * torch.linspace(0.01, 30.0, 1000, device="cuda")[:, None]
+    q, scale = pack_ops.quantize_rows_int8(coeff)
+    want_scale = (coeff.abs().amax(1, keepdim=True) / 127.0).clamp_min(torch.finfo(torch.float32).tiny)
+    torch.testing.assert_close(scale, want_scale, rtol=1e-6, atol=0)
+    assert torch.equal(q, torch.round(coeff / want_scale).clamp_(-127, 127).to(torch.int8))
+    deq = pack_ops.dequantize_rows_int8(q, scale)
+    torch.testing.assert_close(deq.float(), (q.float() * scale).bfloat16().float(), rtol=0, atol=0)
+    # the boundary codec end to end on a bf16 tensor with low-rank structure: small reconstruction error, int8 payload
+    hidden, rank = 512, 16
+    spec = STACRCheckpointSpec(site_id="blk0", module_type="block", model_family="gpt2", hidden_size=hidden, rank=rank, basis_dtype=torch.float32,
+                               min_numel=1, warmup_steps=0, quantize_coefficients=True)
+    codec = CheckpointBoundaryCodec(spec).cuda()
+    base = torch.randn(4 * 128, rank, device="cuda", generator=g) @ torch.randn(rank, hidden, device="cuda", generator=g)
+    x = (base + 0.01 * torch.randn(4 * 128, hidden, device="cuda", generator=g)).bfloat16().reshape(4, 128, hidden)
+    rec = codec.pack_tensor(x, training=True)
+    assert not rec.is_dense_fallback and rec.coeff.dtype == torch.int8
+    back = codec.unpack_record(rec)
+    assert back.shape == x.shape and back.dtype == torch.bfloat16
+    rel = float((back.float() - x.float()).norm() / x.float().norm())
+    assert rel < 0.05, rel
