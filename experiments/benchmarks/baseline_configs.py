@@ -47,6 +47,22 @@ def _tokens(vocab, batch, seq, count, seed, device):
     return [torch.randint(0, vocab, (batch, seq), generator=gen).to(device) for _ in range(count)]
 
 
+def _reports(args, step, rank) -> None:
+    """Optional per-kernel device times and idle-gap report of two more steps (the benchmark's own profiler helpers)."""
+    if not (args.kernel_table or args.gap_report):
+        return
+    import importlib.util
+    import pathlib
+
+    spec = importlib.util.spec_from_file_location("_bench", pathlib.Path(__file__).resolve().parents[2] / "bench.py")
+    bench = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(bench)
+    if args.kernel_table:
+        bench.kernel_table(torch, step, args.kernel_table if rank == 0 else os.devnull)
+    if args.gap_report:
+        bench.gap_report(torch, step, args.gap_report if rank == 0 else os.devnull)
+
+
 def _emit(rank, **row):
     if rank == 0:
         print(json.dumps(row), flush=True)
@@ -124,6 +140,7 @@ def run_gpt2l_tp(args, rank, world, dev):
         step(0)
     torch.cuda.reset_peak_memory_stats(dev)
     secs = _timed(args.steps, step, world)
+    _reports(args, step, rank)
     _emit(rank, config="gpt2l_tp", tp_degree=world, steps=args.steps, tokens_per_second=batch * seq * args.steps / secs, ms_per_step=1e3 * secs / args.steps,
           peak_allocated_gb=torch.cuda.max_memory_allocated(dev) / 1e9, wrapped_layers=len(layers),
           saved_gb_wrapped=sum(l.stored_bytes(batch * seq, 2)["total"] for l in layers) / 1e9,
@@ -180,6 +197,8 @@ def main(argv=None) -> int:
     parser.add_argument("--config", required=True, choices=sorted(RUNNERS))
     parser.add_argument("--steps", type=int, default=10)
     parser.add_argument("--warmup", type=int, default=5)
+    parser.add_argument("--kernel-table", metavar="FILE", help="gpt2l_tp: write per-kernel device times of two more steps to FILE")
+    parser.add_argument("--gap-report", metavar="FILE", help="gpt2l_tp: write where the GPU idles inside two more steps to FILE")
     args = parser.parse_args(argv)
     from stacr_b200.ops import _lib
     from stacr_b200.parallel import init_distributed

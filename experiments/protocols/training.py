@@ -81,6 +81,9 @@ class ConvergenceConfig:
     svd_per_layer_rank: Optional[int] = None
     svd_per_layer_oversampling: int = 16
     svd_per_layer_niter: int = 2
+    monitor_reconstruction: bool = False
+    reconstruction_interval: int = 240
+    monitor_c1_drift: bool = True
     monitor_activation_spectrum: bool = False
     activation_spectrum_interval: int = 120
     activation_spectrum_rank: int = 8
@@ -466,9 +469,44 @@ def _default_tensor_shape(rows: int, feats: int):
 
 
 # ------------------------------------------------------------------------------ baselines
+def data_parallel_blockers(cfg: ConvergenceConfig, device) -> List[str]:
+    """Why the legacy single-process ``nn.DataParallel`` arm cannot run this configuration (empty = it can).
+
+    The arm replicates the module per forward and scatters the batch, so it is limited to plain SST-2 / WikiText runs without
+    anything that keeps per-module state across the replicas (checkpoint wrappers, quantised-activation libraries, saved-tensor
+    offload, boundary compression) and without gradient accumulation (experiments/protocols/training.py:2063-2100 of the reference).
+    """
+    b = cfg.baseline_cfg
+    why = []
+    if torch.device(device).type != "cuda":
+        why.append("non-CUDA device")
+    if (torch.cuda.device_count() if torch.cuda.is_available() else 0) < 2:
+        why.append("fewer than 2 CUDA devices")
+    if cfg.task not in ("sst2", "wikitext103"):
+        why.append(f"task={cfg.task}")
+    if b.checkpointing != "none":
+        why.append("checkpointing")
+    for key in ("actnn", "gact", "torchao"):
+        if getattr(b, key, "none") != "none":
+            why.append(key)
+    if b.offload != "none":
+        why.append("saved_tensors_offload")
+    if cfg.stacr_compress_checkpoint or b.c1_checkpoint_compression:
+        why.append("stacr_compress_checkpoint")
+    if int(b.grad_accum_steps) > 1:
+        why.append("grad_accum_steps > 1")
+    return why
+
+
 def apply_baseline(model: nn.Module, cfg: ConvergenceConfig, device) -> Dict[str, Any]:
     b = cfg.baseline_cfg
     state: Dict[str, Any] = {"amp": AMPManager(b.amp, str(device)), "offload": None, "checkpointed": 0}
+    if cfg.use_data_parallel:
+        blockers = data_parallel_blockers(cfg, device)
+        if blockers:
+            state["status"] = "skipped_incompatible"
+            state["reason"] = "DataParallel is limited to simple SST-2/WikiText runs; incompatible with: " + ", ".join(blockers)
+            return state
     if b.checkpointing != "none":
         state["checkpointed"] = apply_checkpointing(model, b.checkpointing)
     for key, module_name, fn_name in (("actnn", "actnn_adapter", "try_enable_actnn"), ("gact", "gact_adapter", "try_enable_gact")):
@@ -673,8 +711,19 @@ def run_convergence_experiment(cfg: ConvergenceConfig, logger) -> Dict[str, Any]
         layers = replace_linear_with_prac(model, select_targets(model, cfg), PRACConfig(rank=cfg.rank, update_proj_gap=cfg.prac_update_proj_gap, seed_base=cfg.prac_seed_base,
                                                                                     proj_dtype=None if cfg.prac_proj_dtype == "auto" else cfg.prac_proj_dtype, quiet=True))
     state = apply_baseline(model, cfg, device)
+    if state.get("status") == "skipped_incompatible":
+        final = {"status": "skipped_incompatible", "reason": state["reason"], "run_tag": cfg.run_tag, "method": cfg.method, "model": cfg.model, "steps": 0}
+        logger.write_final(final)
+        return final
     amp: AMPManager = state["amp"]
     optimizer, optimizer_name = build_optimizer(model, cfg)
+    train_model_ref = model
+    if cfg.use_data_parallel and cuda and torch.cuda.device_count() > 1:
+        # the legacy single-process arm: replicas per forward, batch scattered over the visible GPUs, gradients summed on device 0
+        train_model_ref = torch.nn.DataParallel(model)
+    from .diagnostics import C1DriftTracker, reconstruction_report
+
+    drift = C1DriftTracker() if (state.get("c1") is not None and cfg.monitor_c1_drift) else None
     sync = GradSync(model.parameters()) if (cfg.use_ddp and world > 1) else None
     profiler = PhaseProfiler(out_path=logger.profile_path, enabled=cfg.phase_profile_full_run and logger.profile_path is not None)
     for layer in layers:
@@ -714,7 +763,8 @@ def run_convergence_experiment(cfg: ConvergenceConfig, logger) -> Dict[str, Any]
                         batch = train[(step * accum + micro) % len(train)]
                         set_stacr_runtime_state(model, step, micro, accum, total_steps)
                         with profiler.phase("forward"), amp.autocast():
-                            loss = model(**batch).loss / accum
+                            loss = train_model_ref(**batch).loss
+                            loss = (loss.mean() if loss.dim() else loss) / accum
                         value += float(loss.detach())
                         if not math.isfinite(value):
                             raise FloatingPointError(f"Nonfinite loss at step {step}")
@@ -739,6 +789,15 @@ def run_convergence_experiment(cfg: ConvergenceConfig, logger) -> Dict[str, Any]
                 record["per_layer_grad_cosine"] = compute_per_layer_grad_fidelity(model, batch, amp, layers)
             if cfg.monitor_activation_spectrum and layers and step % cfg.activation_spectrum_interval == 0:
                 record["activation_spectrum"] = compute_activation_spectrum_telemetry(model, batch, amp, layers, cfg.activation_spectrum_rank)
+            if cfg.monitor_reconstruction and layers and step % cfg.reconstruction_interval == 0:
+                def _fwd(batch=batch):
+                    with torch.no_grad(), amp.autocast():
+                        model(**batch)
+                record["reconstruction"] = reconstruction_report(model, layers, _fwd, cfg.svd_per_layer_rank)["summary"]
+            if drift is not None:
+                record["c1_drift"] = drift.update(state["c1"].stats(), global_step=step, optimizer_step=step, loss_value=value)
+                if cuda:
+                    drift.note_memory("after_step", torch.cuda.memory_allocated(device))
             logger.log(record)
             step += 1
             if cfg.save_every_n_steps and step % cfg.save_every_n_steps == 0:
@@ -778,6 +837,7 @@ def run_convergence_experiment(cfg: ConvergenceConfig, logger) -> Dict[str, Any]
         "peak_allocated_bytes": reduced["peak_bytes"], "n_wrapped_layers": len(layers), "baseline": cfg.baseline_cfg.get_description(),
         "stacr_flags": flags, "planner": plan_summary, "attention": attention_report.to_dict() if attention_report else None, "tp_activation_profile": tp_profiler.summary() if tp_profiler else None,
         "offload": state["offload"].get_stats() if state["offload"] else None, **quality,
+        "c1_drift": drift.summary() if drift is not None else None, "data_parallel": bool(train_model_ref is not model),
     }
     if cfg.save_final_model and int(os.environ.get("LOCAL_RANK", "0")) == 0 and getattr(logger, "dir", None):
         (logger.dir / "checkpoint").mkdir(parents=True, exist_ok=True)

@@ -383,3 +383,50 @@ def test_memory_accounting_closed_forms():
     lowrank = M.stacr_stored_bytes(1024, 512, 8, residual_budget=0.0, dtype=torch.float16, coeff_bits=8)
     assert lowrank.total_bytes < full.total_bytes < M.original_bytes((1024, 512), torch.float16)
     assert M.stacr_rho_max(1024, 512, torch.float16) > 1.0
+
+
+def test_reconstruction_oracles_and_drift_tracker():
+    import torch
+
+    import stacr_b200 as S
+    from experiments.protocols.diagnostics import (C1DriftTracker, reconstruct_stacr_activation, reconstruct_svd_lowrank, reconstruction_metrics,
+                                                   reconstruction_report)
+
+    torch.manual_seed(0)
+    base = torch.randn(256, 4) @ torch.randn(4, 64)
+    x = base + 0.05 * torch.randn(256, 64)
+    lin = torch.nn.Linear(64, 32)
+    layer = S.STACRLinear.from_linear(lin, rank=4, residual_budget=0.02, residual_bits=8)
+    layer.train()
+    same, info = reconstruct_stacr_activation(layer, x)
+    assert info["reconstruction_scope"] == "baseline_or_uninitialized_basis" and same is x
+    layer.set_step(0)
+    layer(x).sum().backward()
+    rec, info = reconstruct_stacr_activation(layer, x)
+    m = reconstruction_metrics(x, rec)
+    assert info["rank"] == 4 and info["residual_entries_kept"] == int(round(0.02 * x.numel())) and info["residuals_quantized"]
+    assert m["relative_error"] < 0.2 and m["cosine"] > 0.98
+    srec, sinfo = reconstruct_svd_lowrank(x, 4)
+    assert sinfo["rank"] == 4 and reconstruction_metrics(x, srec)["relative_error"] < 0.2
+    model = torch.nn.Sequential(layer)
+    report = reconstruction_report(model, [layer], lambda: model(x))
+    assert report["summary"]["count"] == 1 and report["layers"][0]["layer"] == "0"
+    # drift: flat energies and losses, then one site's energy jumps while the loss worsens
+    tracker = C1DriftTracker(window=4)
+    stats = lambda e: {"sites": {"blk0": {"packs": 3, "last_residual_energy": 0.05}, "blk1": {"packs": 3, "last_residual_energy": e}}}
+    for step in range(6):
+        out = tracker.update(stats(0.06), global_step=step, optimizer_step=step, loss_value=2.0)
+        assert out["signal"] is None and out["sites_tracked"] == 2
+    out = tracker.update(stats(0.30), global_step=6, optimizer_step=6, loss_value=2.5)
+    assert out["signal"] == "fast" and out["leading_site"] == "blk1"
+    event = tracker.summary()["first_finite_drift_event"]
+    assert event["site"] == "blk1" and event["global_step"] == 6 and event["energy_ratio"] > 4
+    assert tracker.update(stats(0.30), global_step=7, optimizer_step=7, loss_value=float("nan"))["finite"] is False
+
+
+def test_data_parallel_arm_reports_why_it_cannot_run_on_this_host():
+    from experiments.protocols.training import ConvergenceConfig, data_parallel_blockers
+
+    cfg = ConvergenceConfig(task="sst2", use_data_parallel=True)
+    why = data_parallel_blockers(cfg, "cpu")
+    assert "non-CUDA device" in why and "fewer than 2 CUDA devices" in why
