@@ -326,9 +326,7 @@ def run_ours(args):
     dev_batches = [t.to(dev) for t in host_batches]
     counter = {"step": 0}
 
-    def train_step(ids):
-        S.set_step(layers, counter["step"])
-        counter["step"] += 1
+    def core_step(ids):
         if sync is not None:
             sync.zero_grad()
         else:
@@ -340,6 +338,29 @@ def run_ours(args):
             sync.finish()
         opt.step()
         return loss
+
+    def eager_step(ids):
+        S.set_step(layers, counter["step"])
+        counter["step"] += 1
+        return core_step(ids)
+
+    graphed = None
+    graph_launches = 0
+    if args.graph == "on" and sync is None:
+        # the whole step (forward, backward, optimizer) captured once and replayed: one launch per step instead of ~2000
+        from stacr_b200.graphs import GraphedStep
+
+        for i in range(2):
+            eager_step(dev_batches[i])          # bases initialised, caches filled
+        before = _lib.launch_count() + opt.kernel_launches
+        graphed = GraphedStep(core_step, [dev_batches[0]], optimizer=opt, layers=layers, first_step=counter["step"], warmup=2)
+        graph_launches = (_lib.launch_count() + opt.kernel_launches - before) // 3     # two warm-up runs and the capture
+
+    def train_step(ids):
+        if graphed is not None:
+            counter["step"] += 1
+            return graphed(ids)
+        return eager_step(ids)
 
     def step_device(i):
         train_step(dev_batches[i % len(dev_batches)])
@@ -363,13 +384,15 @@ def run_ours(args):
     with ClockSampler(local) as clocks:
         secs, secs_all = timed_regions(torch, dist, args.steps, step_device, world, args.repeats)
     launches = (_lib.launch_count() + opt.kernel_launches - launches0) // max(1, args.repeats)
+    if graphed is not None:
+        launches = graph_launches * args.steps          # the kernels inside the graph, replayed once per step
     with ClockSampler(local) as clocks_e2e:
         secs_e2e, secs_e2e_all = timed_regions(torch, dist, args.steps, step_e2e, world, args.repeats)
     _lib.check_status(dev)
     peak = torch.cuda.max_memory_allocated(dev)
 
     def evidence_step():
-        S.set_step(layers, counter["step"])
+        S.set_step(layers, counter["step"] + 8)
         counter["step"] += 1
         if sync is not None:
             sync.zero_grad()
@@ -402,6 +425,7 @@ def run_ours(args):
                 "fused_dw_reduce_scatter": bool(sync and sync.n_fused and sync.backend == "symm"),
                 "optimizer_sharding": "ZeRO-1: reduce-to-owner buckets, 1/W optimizer per rank, bf16 weights published by multicast stores of the update kernel" if zero else "replicated",
                 "l2": "inputs larger than L2: every step streams 2.8 GB of bf16 weights and > 10 GB of activations through a 126 MB L2",
+                "cuda_graph": graphed is not None,
             },
             "clocks": clocks.summary(),
             "timing": {"regions": len(secs_all), "steps_per_region": args.steps, "reported": "median region",
@@ -549,6 +573,7 @@ def main():
     ap.add_argument("--comm", default="auto", choices=["auto", "symm", "nccl"], help="gradient all-reduce path (this framework)")
     ap.add_argument("--fused-dw", default="off", choices=["on", "off"],
                     help="N > 1: compressed layers' weight-gradient kernels reduce-scatter in their epilogue over NVLink peer memory")
+    ap.add_argument("--graph", default="on", choices=["on", "off"], help="N = 1: capture the training step into a CUDA graph and replay it")
     ap.add_argument("--zero", default="on", choices=["on", "off"], help="N > 1: shard the optimizer over the ranks (reduce-to-owner + multicast weight publication)")
     ap.add_argument("--gap-report", metavar="FILE", help="after the timed regions, write where the GPU idles inside two more steps to FILE")
     ap.add_argument("--kernel-table", metavar="FILE", help="after the timed regions, write per-kernel device times of two more steps to FILE")

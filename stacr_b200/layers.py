@@ -138,6 +138,10 @@ def _select_residual(x, coeff, basis, budget, chunk_rows, mode, block_size, samp
 # --------------------------------------------------------------------------------------
 # Kernel-path helpers
 # --------------------------------------------------------------------------------------
+# (old version, new version) of every basis rebound while a training step is being captured into a CUDA graph; None otherwise
+GRAPH_BASIS_PAIRS: list | None = None
+
+
 def _kernel_path(x: torch.Tensor, compute_dtype: torch.dtype) -> bool:
     return x.is_cuda and compute_dtype == torch.bfloat16
 
@@ -586,7 +590,12 @@ class STACRLinear(nn.Module):
             if x2d.is_cuda and x2d.dtype == torch.bfloat16:
                 from .ops.basis import oja_step_kernels
 
-                self.basis = oja_step_kernels(self.basis, x2d, self.oja_lr).to(store)
+                previous = self.basis
+                self.basis = oja_step_kernels(previous, x2d, self.oja_lr).to(store)
+                if GRAPH_BASIS_PAIRS is not None:
+                    # the step is being captured into a CUDA graph: replays read the basis from `previous`'s storage, so the
+                    # capture ends by copying the new version back there (see graphs.GraphedStep)
+                    GRAPH_BASIS_PAIRS.append((previous, self.basis))
             else:
                 self.basis = oja_step(self.basis, x2d.detach(), self.oja_lr).to(store)
             self._mark_updated(step, ready=False)

@@ -151,7 +151,7 @@ def poll_status(device=None, *, strict: bool | None = None) -> None:
     With ``strict`` (or ``STACR_STRICT_STATUS=1``) the word is read synchronously instead, which costs a device
     synchronisation per call but reports a failure before anything consumes the step's results.
     """
-    if not torch.cuda.is_available():
+    if not torch.cuda.is_available() or torch.cuda.is_current_stream_capturing():
         return
     if strict is None:
         strict = os.environ.get("STACR_STRICT_STATUS", "0") == "1"

@@ -56,8 +56,19 @@ struct AdamArgs {
   float lr, beta1, beta2, eps, weight_decay, bias1, bias2, grad_scale;
 };
 
+// Hyper-parameters from device memory when the step is replayed from a CUDA graph: kernel arguments are frozen at capture
+// time, the eight floats behind `hyper` are refreshed by a small copy in front of every replay.
+__device__ __forceinline__ AdamArgs resolve_args(AdamArgs a, const float* hyper) {
+  if (hyper) {
+    a.lr = hyper[0]; a.beta1 = hyper[1]; a.beta2 = hyper[2]; a.eps = hyper[3];
+    a.weight_decay = hyper[4]; a.bias1 = hyper[5]; a.bias2 = hyper[6]; a.grad_scale = hyper[7];
+  }
+  return a;
+}
+
 __global__ void __launch_bounds__(256) adamw_fp32_kernel(const TensorDesc* __restrict__ tensors, const ChunkDesc* __restrict__ chunks,
-                                                         AdamArgs a) {
+                                                         AdamArgs a0, const float* __restrict__ hyper) {
+  const AdamArgs a = resolve_args(a0, hyper);
   const ChunkDesc c = chunks[blockIdx.x];
   const TensorDesc t = tensors[c.tensor];
   const long long end = min(t.numel, c.offset + CHUNK);
@@ -97,7 +108,8 @@ __device__ __forceinline__ unsigned char encode_v(float v, float inv_amax) {
 // One warp = one 256-element quantisation block (8 consecutive elements per lane, 16-byte
 // loads/stores, absmax by warp shuffles only); one CTA of 8 warps = one 2048-element chunk.
 __global__ void __launch_bounds__(256) adamw_8bit_kernel(const TensorDesc* __restrict__ tensors, const ChunkDesc* __restrict__ chunks,
-                                                         AdamArgs a) {
+                                                         AdamArgs a0, const float* __restrict__ hyper) {
+  const AdamArgs a = resolve_args(a0, hyper);
   const ChunkDesc c = chunks[blockIdx.x];
   const TensorDesc t = tensors[c.tensor];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -237,15 +249,15 @@ extern "C" int sb_chunk_desc_size() { return static_cast<int>(sizeof(sb::ChunkDe
 extern "C" int sb_optim_chunk() { return sb::CHUNK; }
 
 extern "C" int sb_adamw_step(const void* tensors, const void* chunks, int n_chunks, int eight_bit, float lr, float beta1, float beta2,
-                             float eps, float weight_decay, float bias1, float bias2, float grad_scale, void* stream) {
+                             float eps, float weight_decay, float bias1, float bias2, float grad_scale, const float* hyper, void* stream) {
   using namespace sb;
   if (n_chunks <= 0) return 0;
   AdamArgs a{lr, beta1, beta2, eps, weight_decay, bias1, bias2, grad_scale};
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (eight_bit)
-    adamw_8bit_kernel<<<n_chunks, 256, 0, st>>>(static_cast<const TensorDesc*>(tensors), static_cast<const ChunkDesc*>(chunks), a);
+    adamw_8bit_kernel<<<n_chunks, 256, 0, st>>>(static_cast<const TensorDesc*>(tensors), static_cast<const ChunkDesc*>(chunks), a, hyper);
   else
-    adamw_fp32_kernel<<<n_chunks, 256, 0, st>>>(static_cast<const TensorDesc*>(tensors), static_cast<const ChunkDesc*>(chunks), a);
+    adamw_fp32_kernel<<<n_chunks, 256, 0, st>>>(static_cast<const TensorDesc*>(tensors), static_cast<const ChunkDesc*>(chunks), a, hyper);
   return static_cast<int>(cudaGetLastError());
 }
 

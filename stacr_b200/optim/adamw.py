@@ -82,6 +82,9 @@ class AdamW(torch.optim.Optimizer):
         # ``shard``: a ``parallel.zero.ShardedGradSync``.  Parameters it shards are updated only over the element ranges this
         # rank owns; their bf16 copies belong to it (views of one flat buffer) and it publishes the update to the other ranks.
         self.shard = shard
+        # CUDA-graph mode (see ``enable_graph_mode``): hyper-parameters and bias corrections live in device memory
+        self._graph_hyper = None
+        self._graph_pins: list = []
         self._tables: dict[int, dict] = {}
         self.kernel_launches = 0
 
@@ -106,6 +109,34 @@ class AdamW(torch.optim.Optimizer):
             p._bf16_shadow = p.detach().to(torch.bfloat16)
             p._bf16_shadow_version = p._version
         return st
+
+    # ------------------------------------------------------------------ CUDA-graph mode
+    def enable_graph_mode(self, device) -> None:
+        """Prepare the optimizer for a step that is captured once and replayed from a CUDA graph.
+
+        Kernel arguments are frozen at capture time, so the per-step scalars (learning rate, bias corrections, gradient
+        scale) move to a small device array; :meth:`graph_pre_step` advances the step counters on the host and refreshes
+        that array with one asynchronous copy in front of each replay.  Inside the captured ``step()`` nothing is counted.
+        """
+        n = len(self.param_groups)
+        self._graph_hyper = {"dev": torch.zeros(n, 8, dtype=torch.float32, device=device),
+                             "host": torch.zeros(n, 8, dtype=torch.float32).pin_memory(), "scale": 1.0}
+
+    def graph_pre_step(self, grad_scale: float = 1.0) -> None:
+        """Advance the step counters and upload this step's scalars (call before capture and before every replay)."""
+        gh = self._graph_hyper
+        for gi, group in enumerate(self.param_groups):
+            step = None
+            for p in group["params"]:
+                if p.requires_grad:
+                    st = self._init_state(p)
+                    st["step"] += 1
+                    step = st["step"]
+            if step is None:
+                continue
+            b1, b2 = group["betas"]
+            gh["host"][gi] = torch.tensor([group["lr"], b1, b2, group["eps"], group["weight_decay"], 1 - b1 ** step, 1 - b2 ** step, grad_scale])
+        gh["dev"].copy_(gh["host"], non_blocking=True)
 
     def _ranges(self, p: torch.Tensor):
         """Element ranges of ``p`` this rank updates: everything, unless a sharding synchroniser owns the partition."""
@@ -191,7 +222,16 @@ class AdamW(torch.optim.Optimizer):
                 ptr(st.get("v_absmax")), p.numel(), int(getattr(p, "_bf16_shadow_mc", 0) or 0),
             )
         blob = table.tobytes()
-        if blob != cache["last"]:
+        capturing = torch.cuda.is_current_stream_capturing()
+        if capturing:
+            # the copy becomes a node of the graph and is replayed with it: it needs a pinned source of its own that stays
+            # untouched for the life of the graph (no event may be waited on while a stream is capturing)
+            pin = torch.empty(len(blob), dtype=torch.uint8).pin_memory()
+            pin.numpy()[:] = np.frombuffer(blob, dtype=np.uint8)
+            self._graph_pins.append(pin)
+            cache["dev"].copy_(pin, non_blocking=True)
+            cache["last"] = None
+        elif blob != cache["last"]:
             # the pointers changed (gradients are reallocated when they are dropped between steps): upload through the
             # staging table whose previous upload has certainly finished
             turn = cache["turn"]
@@ -204,13 +244,14 @@ class AdamW(torch.optim.Optimizer):
             cache["events"][turn] = ev
             cache["turn"] = turn ^ 1
             cache["last"] = blob
-        step = self.state[plist[0]]["step"]
+        step = max(1, self.state[plist[0]]["step"])
         b1, b2 = group["betas"]
+        hyper = None if self._graph_hyper is None else self._graph_hyper["dev"][gi]
         rc = lib.sb_adamw_step(
             _lib.ptr(cache["dev"]), _lib.ptr(cache["chunks"]), ctypes.c_int(cache["n_chunks"]), ctypes.c_int(int(self.eight_bit)),
             ctypes.c_float(group["lr"]), ctypes.c_float(b1), ctypes.c_float(b2), ctypes.c_float(group["eps"]),
             ctypes.c_float(group["weight_decay"]), ctypes.c_float(1 - b1 ** step), ctypes.c_float(1 - b2 ** step),
-            ctypes.c_float(grad_scale), _lib.stream_ptr(),
+            ctypes.c_float(grad_scale), _lib.ptr(hyper), _lib.stream_ptr(),
         )
         _lib.check_rc(rc, "sb_adamw_step")
         self.kernel_launches += 1
@@ -232,7 +273,8 @@ class AdamW(torch.optim.Optimizer):
                 if p.grad.is_sparse:
                     raise RuntimeError("AdamW does not support sparse gradients")
                 st = self._init_state(p)
-                st["step"] += 1
+                if self._graph_hyper is None:
+                    st["step"] += 1          # in graph mode the counters are advanced by graph_pre_step()
                 ok = p.is_cuda and p.dtype == torch.float32 and p.grad.dtype == torch.float32 and p.is_contiguous() and p.grad.is_contiguous()
                 (fast if ok else slow).append(p)
             if fast:

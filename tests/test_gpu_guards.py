@@ -214,3 +214,61 @@ def test_bf16_shadow_is_refreshed_after_load_state_dict():
     assert abs(after - want) < 2e-2 and abs(after - before) > 1e-4, (before, after, want)
     opt.close()
     assert not hasattr(model.embed_out.weight, "_bf16_shadow")
+
+
+def test_training_step_replayed_from_a_cuda_graph_tracks_the_eager_step():
+    """Forward, backward and the optimizer update captured once: the replayed steps follow the eager loss curve, the tracked
+    bases keep moving, and the layers' state stays readable."""
+    import stacr_b200 as S
+    from stacr_b200.graphs import GraphedStep
+    from stacr_b200.models import GPTNeoXForCausalLM, NeoXConfig
+    from stacr_b200.ops import _lib
+    from stacr_b200.optim import AdamW8bit
+
+    dev = torch.device("cuda", torch.cuda.current_device())
+    cfg = NeoXConfig(vocab_size=1024, hidden_size=256, num_hidden_layers=2, num_attention_heads=4, intermediate_size=1024, max_position_embeddings=128)
+    gen = torch.Generator(device=dev).manual_seed(3)
+    batches = [torch.randint(0, 1024, (4, 128), device=dev, generator=gen) for _ in range(4)]
+
+    def run(graph: bool):
+        torch.manual_seed(11)
+        model = GPTNeoXForCausalLM(cfg).to(dev).train()
+        layers = S.apply_stacr(model, rank=8, residual_budget=0.01, residual_mode="global_topk", turbo_after_step=None, min_features=128)
+        opt = AdamW8bit(model.parameters(), lr=2e-3, weight_decay=0.0, bf16_shadow=True)
+
+        def core(ids):
+            opt.zero_grad(set_to_none=True)
+            with torch.autocast("cuda", dtype=torch.bfloat16):
+                loss = model(input_ids=ids, labels=ids).loss
+            loss.backward()
+            opt.step()
+            return loss
+
+        losses = []
+        for step in range(2):                                   # eager: bases are initialised here
+            S.set_step(layers, step)
+            losses.append(float(core(batches[step % 4])))
+        if graph:
+            g = GraphedStep(core, [batches[0]], optimizer=opt, layers=layers, first_step=2, warmup=2)
+            assert g.basis_pairs == len(layers) and g.valid_for()
+            first = layers[0].basis.clone()
+            for step in range(8):
+                losses.append(float(g(batches[step % 4])))
+            assert not torch.equal(first, layers[0].basis)       # the basis advanced through the replays
+            g.sync_state()
+            assert int(layers[0]._step) == g.step - 1
+        else:
+            for step in range(2, 13):                            # the graph path ran 2 warm-up steps + the capture before its 8 replays
+                S.set_step(layers, step)
+                value = float(core(batches[(step - 5) % 4 if step >= 5 else 0]))
+                if step >= 5:
+                    losses.append(value)
+        torch.cuda.synchronize()
+        _lib.check_status(dev)
+        return losses
+
+    eager, graphed = run(False), run(True)
+    assert len(eager) == len(graphed) == 10
+    assert all(l == l for l in graphed)
+    assert graphed[-1] < graphed[2] - 0.05                       # it trains
+    assert max(abs(a - b) for a, b in zip(eager, graphed)) < 0.15
