@@ -346,7 +346,7 @@ def run_ours(args):
 
     graphed = None
     graph_launches = 0
-    if args.graph == "on" and sync is None:
+    if args.graph == "on" and (sync is None or sync.backend == "symm"):
         # the whole step (forward, backward, optimizer) captured once and replayed: one launch per step instead of ~2000
         from stacr_b200.graphs import GraphedStep
 
@@ -573,7 +573,8 @@ def main():
     ap.add_argument("--comm", default="auto", choices=["auto", "symm", "nccl"], help="gradient all-reduce path (this framework)")
     ap.add_argument("--fused-dw", default="off", choices=["on", "off"],
                     help="N > 1: compressed layers' weight-gradient kernels reduce-scatter in their epilogue over NVLink peer memory")
-    ap.add_argument("--graph", default="on", choices=["on", "off"], help="N = 1: capture the training step into a CUDA graph and replay it")
+    ap.add_argument("--graph", default="on", choices=["on", "off"],
+                    help="capture the training step (with the in-tree collectives at N > 1) into a CUDA graph and replay it")
     ap.add_argument("--zero", default="on", choices=["on", "off"], help="N > 1: shard the optimizer over the ranks (reduce-to-owner + multicast weight publication)")
     ap.add_argument("--gap-report", metavar="FILE", help="after the timed regions, write where the GPU idles inside two more steps to FILE")
     ap.add_argument("--kernel-table", metavar="FILE", help="after the timed regions, write per-kernel device times of two more steps to FILE")

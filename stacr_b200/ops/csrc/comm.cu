@@ -33,7 +33,15 @@ struct CommArgs {
   int epoch;
   int* status;
   unsigned long long wait_ns;            // how long a flag wait may last before the kernel gives up
+  const int* epoch_ptr;                  // optional: the barrier epoch is read from device memory (CUDA-graph replays)
 };
+
+// The barrier epoch of this launch.  Kernel arguments are frozen when a step is captured into a CUDA graph, so a replayed
+// collective reads its epoch from a device counter that a one-thread kernel in front of it advances (sb_epoch_bump).
+__device__ __forceinline__ int epoch_of(const CommArgs& a) {
+  return a.epoch_ptr ? *reinterpret_cast<const volatile int*>(a.epoch_ptr) : a.epoch;
+}
+__global__ void epoch_bump_kernel(int* counter) { *counter += 1; }
 
 // Limit of the peer waits: 2 s unless STACR_WAIT_LIMIT_MS names another value (read once) or sb_comm_set_wait_limit_ns
 // was called.  Jobs whose ranks can legitimately drift further apart (a first-use build, a rank-0-only checkpoint that is
@@ -67,11 +75,12 @@ __device__ bool rank_barrier(const CommArgs& a, int phase, int* s_fail) {
     const int peer = threadIdx.x;
     __threadfence_system();
     int* remote = reinterpret_cast<int*>(a.flag_ptrs[peer]) + (phase * MAX_CTAS + blockIdx.x) * MAX_RANKS + a.rank;
-    st_release_sys(remote, a.epoch);
+    const int epoch = epoch_of(a);
+    st_release_sys(remote, epoch);
     const int* local = reinterpret_cast<const int*>(a.flag_ptrs[a.rank]) + (phase * MAX_CTAS + blockIdx.x) * MAX_RANKS + peer;
     const uint64_t t0 = globaltimer_ns();
     uint32_t polls = 0;
-    while (ld_acquire_sys(local) < a.epoch) {
+    while (ld_acquire_sys(local) < epoch) {
       if ((++polls & 255u) == 0u && globaltimer_ns() - t0 > a.wait_ns) {
         *s_fail = 1;
         if (a.status) atomicCAS(a.status, 0, ST_TIMEOUT_PEER_FLAG);
@@ -431,31 +440,38 @@ static int launch_allreduce(bool multimem, const CommArgs& a, int sms, cudaStrea
 extern "C" void sb_comm_set_wait_limit_ns(unsigned long long ns) { sb::g_comm_wait_ns = ns ? ns : SB_WAIT_LIMIT_NS; }
 extern "C" unsigned long long sb_comm_wait_limit_ns() { return sb::comm_wait_ns(); }
 
+// Advance a device-side epoch counter by one (stream-ordered; launch it in front of a collective that reads the counter).
+extern "C" int sb_epoch_bump(int* counter, void* stream) {
+  if (counter == nullptr) return -2;
+  sb::epoch_bump_kernel<<<1, 1, 0, static_cast<cudaStream_t>(stream)>>>(counter);
+  return static_cast<int>(cudaGetLastError());
+}
+
 extern "C" int sb_comm_flag_ints() { return 3 * sb::MAX_CTAS * sb::MAX_RANKS; }
 
 extern "C" int sb_allreduce_two_shot(const void* peer_ptrs, const void* flag_ptrs, unsigned long long mc_ptr, int rank, int world,
-                                     long long lo, long long hi, float scale, int epoch, int sms, int* status, void* stream) {
+                                     long long lo, long long hi, float scale, int epoch, const int* epoch_ptr, int sms, int* status, void* stream) {
   sb::CommArgs a{static_cast<const unsigned long long*>(peer_ptrs), static_cast<const unsigned long long*>(flag_ptrs), mc_ptr, rank,
-                 world, lo, hi, scale, epoch, status, sb::comm_wait_ns()};
+                 world, lo, hi, scale, epoch, status, sb::comm_wait_ns(), epoch_ptr};
   return sb::launch_allreduce(false, a, sms, static_cast<cudaStream_t>(stream));
 }
 
 extern "C" int sb_allreduce_multimem(const void* peer_ptrs, const void* flag_ptrs, unsigned long long mc_ptr, int rank, int world,
-                                     long long lo, long long hi, float scale, int epoch, int sms, int* status, void* stream) {
+                                     long long lo, long long hi, float scale, int epoch, const int* epoch_ptr, int sms, int* status, void* stream) {
   if (mc_ptr == 0) return -4;
   sb::CommArgs a{static_cast<const unsigned long long*>(peer_ptrs), static_cast<const unsigned long long*>(flag_ptrs), mc_ptr, rank,
-                 world, lo, hi, scale, epoch, status, sb::comm_wait_ns()};
+                 world, lo, hi, scale, epoch, status, sb::comm_wait_ns(), epoch_ptr};
   return sb::launch_allreduce(true, a, sms, static_cast<cudaStream_t>(stream));
 }
 
 // Broadcast every rank's slice of [lo, hi) to all ranks (scaled).  mc_ptr != 0 selects the multicast store.
 extern "C" int sb_allgather_slices(const void* peer_ptrs, const void* flag_ptrs, unsigned long long mc_ptr, int rank, int world,
-                                   long long lo, long long hi, float scale, int epoch, int sms, int* status, void* stream) {
+                                   long long lo, long long hi, float scale, int epoch, const int* epoch_ptr, int sms, int* status, void* stream) {
   using namespace sb;
   if (world < 1 || world > MAX_RANKS) return -2;
   if ((lo & 3) || (hi & 3) || hi < lo) return -3;
   CommArgs a{static_cast<const unsigned long long*>(peer_ptrs), static_cast<const unsigned long long*>(flag_ptrs), mc_ptr, rank, world,
-             lo, hi, scale, epoch, status, sb::comm_wait_ns()};
+             lo, hi, scale, epoch, status, sb::comm_wait_ns(), epoch_ptr};
   const long long vecs = (hi - lo) / 4 / world;
   const int grid = comm_grid(vecs, sms);
   allgather_slices_kernel<<<grid, 512, 0, static_cast<cudaStream_t>(stream)>>>(a);
@@ -465,12 +481,12 @@ extern "C" int sb_allgather_slices(const void* peer_ptrs, const void* flag_ptrs,
 // Reduce [lo, hi) across ranks into the owner's copy: this rank reduces [own_lo, own_hi) (clipped to [lo, hi); may be
 // empty) and stores it locally.  mc_ptr != 0 selects the in-switch reduction.  All bounds are multiples of 4 elements.
 extern "C" int sb_reduce_to_owner(const void* peer_ptrs, const void* flag_ptrs, unsigned long long mc_ptr, int rank, int world, long long lo,
-                                  long long hi, long long own_lo, long long own_hi, float scale, int epoch, int sms, int* status, void* stream) {
+                                  long long hi, long long own_lo, long long own_hi, float scale, int epoch, const int* epoch_ptr, int sms, int* status, void* stream) {
   using namespace sb;
   if (world < 1 || world > MAX_RANKS) return -2;
   if ((lo & 3) || (hi & 3) || (own_lo & 3) || (own_hi & 3) || hi < lo) return -3;
   CommArgs a{static_cast<const unsigned long long*>(peer_ptrs), static_cast<const unsigned long long*>(flag_ptrs), mc_ptr, rank, world,
-             lo, hi, scale, epoch, status, sb::comm_wait_ns()};
+             lo, hi, scale, epoch, status, sb::comm_wait_ns(), epoch_ptr};
   const long long b = own_lo > lo ? own_lo : lo, e = own_hi < hi ? own_hi : hi;
   const int grid = comm_grid(e > b ? (e - b) / 4 : 0, sms);
   reduce_to_owner_kernel<<<grid, 512, 0, static_cast<cudaStream_t>(stream)>>>(a, own_lo, own_hi);
@@ -479,21 +495,21 @@ extern "C" int sb_reduce_to_owner(const void* peer_ptrs, const void* flag_ptrs, 
 
 // In-place bf16 sum over ranks of elements [lo, hi) (multiples of 8) of a symmetric bf16 buffer; mc_ptr != 0 selects the in-switch form.
 extern "C" int sb_allreduce_bf16(const void* peer_ptrs, const void* flag_ptrs, unsigned long long mc_ptr, int rank, int world, long long lo,
-                                 long long hi, int epoch, int sms, int* status, void* stream) {
+                                 long long hi, int epoch, const int* epoch_ptr, int sms, int* status, void* stream) {
   using namespace sb;
   if (world < 1 || world > MAX_RANKS) return -2;
   if ((lo & 7) || (hi & 7) || hi < lo) return -3;
   CommArgs a{static_cast<const unsigned long long*>(peer_ptrs), static_cast<const unsigned long long*>(flag_ptrs), mc_ptr, rank, world,
-             lo, hi, 1.f, epoch, status, sb::comm_wait_ns()};
+             lo, hi, 1.f, epoch, status, sb::comm_wait_ns(), epoch_ptr};
   const int grid = comm_grid((hi - lo) / 8 / world, sms);
   allreduce_bf16_kernel<<<grid, 512, 0, static_cast<cudaStream_t>(stream)>>>(a);
   return static_cast<int>(cudaGetLastError());
 }
 
-extern "C" int sb_rank_barrier(const void* flag_ptrs, int rank, int world, int epoch, int* status, void* stream) {
+extern "C" int sb_rank_barrier(const void* flag_ptrs, int rank, int world, int epoch, const int* epoch_ptr, int* status, void* stream) {
   using namespace sb;
   if (world < 1 || world > MAX_RANKS) return -2;
-  CommArgs a{nullptr, static_cast<const unsigned long long*>(flag_ptrs), 0ull, rank, world, 0, 0, 1.f, epoch, status, sb::comm_wait_ns()};
+  CommArgs a{nullptr, static_cast<const unsigned long long*>(flag_ptrs), 0ull, rank, world, 0, 0, 1.f, epoch, status, sb::comm_wait_ns(), epoch_ptr};
   rank_barrier_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(a);
   return static_cast<int>(cudaGetLastError());
 }
@@ -513,12 +529,12 @@ extern "C" int sb_flag_set(int* flag, int value, void* stream) {
 }
 
 // See allreduce_finish_kernel.  rows * n must be a multiple of 8; dst is a contiguous [rows, n] bf16 tensor.
-extern "C" int sb_allreduce_finish(const void* flag_ptrs, int rank, int world, int epoch, const void* staging, void* dst,
+extern "C" int sb_allreduce_finish(const void* flag_ptrs, int rank, int world, int epoch, const int* epoch_ptr, const void* staging, void* dst,
                                    long long rows, int n, int sms, int* status, void* stream) {
   using namespace sb;
   if (world < 1 || world > MAX_RANKS) return -2;
   if ((rows * n) % 8) return -3;
-  CommArgs a{nullptr, static_cast<const unsigned long long*>(flag_ptrs), 0ull, rank, world, 0, 0, 1.f, epoch, status, sb::comm_wait_ns()};
+  CommArgs a{nullptr, static_cast<const unsigned long long*>(flag_ptrs), 0ull, rank, world, 0, 0, 1.f, epoch, status, sb::comm_wait_ns(), epoch_ptr};
   const int grid = comm_grid(rows * n / 8, sms);
   allreduce_finish_kernel<<<grid, 512, 0, static_cast<cudaStream_t>(stream)>>>(a, static_cast<const __nv_bfloat16*>(staging),
                                                                                static_cast<__nv_bfloat16*>(dst), rows, n);

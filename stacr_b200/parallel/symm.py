@@ -66,31 +66,41 @@ class SymmetricBuffer:
             self.multicast_ptr += off
         self.use_multimem = self.multicast_ptr != 0 and os.environ.get("STACR_SYMM_MULTIMEM", "1") == "1"
         self._epoch = 0
+        # the barrier epoch lives on the device: a one-thread kernel advances it in front of every collective, which reads it
+        # there.  A host-side counter passed by value would be frozen into a captured CUDA graph and break every replay.
+        self._epoch_dev = torch.zeros(1, dtype=torch.int32, device=device)
         self.numel = numel
         # CTAs per collective kernel: each one takes an SM away from the compute it overlaps with.  The switch-side
         # reduction (multimem) reaches its bandwidth with very few CTAs; peer loads/stores need many more in flight.
         self.max_ctas = int(os.environ.get("STACR_COMM_CTAS", "8" if self.use_multimem else "64"))
 
+    def _next_epoch(self):
+        """Advance the device-side epoch (stream-ordered) and return the ``(epoch, epoch_ptr)`` argument pair for the next kernel."""
+        self._epoch += 1
+        rc = _lib.load().sb_epoch_bump(_lib.ptr(self._epoch_dev), _lib.stream_ptr())
+        _lib.check_rc(rc, "sb_epoch_bump")
+        return ctypes.c_int(self._epoch), _lib.ptr(self._epoch_dev)
+
     def all_reduce_(self, lo: int, hi: int, average: bool = True) -> None:
         """In-place sum (or mean) of ``tensor[lo:hi]`` across ranks, on the current stream."""
-        self._epoch += 1
+        epoch = self._next_epoch()
         lib = _lib.load()
         scale = 1.0 / self.world if average else 1.0
         fn = lib.sb_allreduce_multimem if self.use_multimem else lib.sb_allreduce_two_shot
         rc = fn(
             _lib.ptr(self._peer_ptrs), _lib.ptr(self._pad_ptrs), ctypes.c_ulonglong(self.multicast_ptr), ctypes.c_int(self.rank),
             ctypes.c_int(self.world), ctypes.c_longlong(lo), ctypes.c_longlong(hi), ctypes.c_float(scale),
-            ctypes.c_int(self._epoch), ctypes.c_int(self.max_ctas), _lib.ptr(_lib.status_word(self.tensor.device)),
+            *epoch, ctypes.c_int(self.max_ctas), _lib.ptr(_lib.status_word(self.tensor.device)),
             _lib.stream_ptr(),
         )
         _lib.check_rc(rc, "sb_allreduce")
         _lib.count(1)
 
     def _call(self, fn, lo: int, hi: int, scale: float, name: str, multicast: bool) -> None:
-        self._epoch += 1
+        epoch = self._next_epoch()
         rc = fn(
             _lib.ptr(self._peer_ptrs), _lib.ptr(self._pad_ptrs), ctypes.c_ulonglong(self.multicast_ptr if multicast else 0), ctypes.c_int(self.rank),
-            ctypes.c_int(self.world), ctypes.c_longlong(lo), ctypes.c_longlong(hi), ctypes.c_float(scale), ctypes.c_int(self._epoch),
+            ctypes.c_int(self.world), ctypes.c_longlong(lo), ctypes.c_longlong(hi), ctypes.c_float(scale), *epoch,
             ctypes.c_int(self.max_ctas), _lib.ptr(_lib.status_word(self.tensor.device)), _lib.stream_ptr(),
         )
         _lib.check_rc(rc, name)
@@ -99,10 +109,10 @@ class SymmetricBuffer:
     def all_reduce_bf16_(self, lo: int, hi: int) -> None:
         """In-place sum over ranks of ``tensor[lo:hi]`` of a bf16 buffer (bounds multiples of 8), fp32 accumulation."""
         assert self.tensor.dtype == torch.bfloat16
-        self._epoch += 1
+        epoch = self._next_epoch()
         rc = _lib.load().sb_allreduce_bf16(
             _lib.ptr(self._peer_ptrs), _lib.ptr(self._pad_ptrs), ctypes.c_ulonglong(self.multicast_ptr if self.use_multimem else 0),
-            ctypes.c_int(self.rank), ctypes.c_int(self.world), ctypes.c_longlong(lo), ctypes.c_longlong(hi), ctypes.c_int(self._epoch),
+            ctypes.c_int(self.rank), ctypes.c_int(self.world), ctypes.c_longlong(lo), ctypes.c_longlong(hi), *epoch,
             ctypes.c_int(self.max_ctas), _lib.ptr(_lib.status_word(self.tensor.device)), _lib.stream_ptr(),
         )
         _lib.check_rc(rc, "sb_allreduce_bf16")
@@ -112,11 +122,11 @@ class SymmetricBuffer:
         """Sum (or mean) of ``tensor[lo:hi]`` across ranks, delivered only to owners: this rank ends up with the reduced
         ``tensor[own_lo:own_hi]`` in its own copy (the rest of ``[lo, hi)`` keeps its local values).  fp32 buffers only."""
         assert self.tensor.dtype == torch.float32
-        self._epoch += 1
+        epoch = self._next_epoch()
         rc = _lib.load().sb_reduce_to_owner(
             _lib.ptr(self._peer_ptrs), _lib.ptr(self._pad_ptrs), ctypes.c_ulonglong(self.multicast_ptr if self.use_multimem else 0),
             ctypes.c_int(self.rank), ctypes.c_int(self.world), ctypes.c_longlong(lo), ctypes.c_longlong(hi), ctypes.c_longlong(own_lo),
-            ctypes.c_longlong(own_hi), ctypes.c_float(1.0 / self.world if average else 1.0), ctypes.c_int(self._epoch),
+            ctypes.c_longlong(own_hi), ctypes.c_float(1.0 / self.world if average else 1.0), *epoch,
             ctypes.c_int(self.max_ctas), _lib.ptr(_lib.status_word(self.tensor.device)), _lib.stream_ptr(),
         )
         _lib.check_rc(rc, "sb_reduce_to_owner")
@@ -129,8 +139,8 @@ class SymmetricBuffer:
 
     def barrier(self) -> None:
         """Cross-rank barrier as a kernel on the current stream (bounded wait; a late peer sets the status word)."""
-        self._epoch += 1
-        rc = _lib.load().sb_rank_barrier(_lib.ptr(self._pad_ptrs), ctypes.c_int(self.rank), ctypes.c_int(self.world), ctypes.c_int(self._epoch),
+        epoch = self._next_epoch()
+        rc = _lib.load().sb_rank_barrier(_lib.ptr(self._pad_ptrs), ctypes.c_int(self.rank), ctypes.c_int(self.world), *epoch,
                                          _lib.ptr(_lib.status_word(self.tensor.device)), _lib.stream_ptr())
         _lib.check_rc(rc, "sb_rank_barrier")
         _lib.count(1)

@@ -84,9 +84,9 @@ class GemmAllReduce:
         _lib.check_rc(rc, "sb_gemm_bf16_allreduce")
         out = torch.empty((m, n), dtype=torch.bfloat16, device=a.device)
         flags = self.bufs[0]          # one flag plane and one epoch counter serve both staging buffers
-        flags._epoch += 1
+        epoch = flags._next_epoch()
         rc = lib.sb_allreduce_finish(
-            _lib.ptr(flags._pad_ptrs), ctypes.c_int(self.rank), ctypes.c_int(self.world), ctypes.c_int(flags._epoch), _lib.ptr(buf.tensor),
+            _lib.ptr(flags._pad_ptrs), ctypes.c_int(self.rank), ctypes.c_int(self.world), *epoch, _lib.ptr(buf.tensor),
             _lib.ptr(out), ctypes.c_longlong(m), ctypes.c_int(n), ctypes.c_int(max(flags.max_ctas, 32)),
             _lib.ptr(_lib.status_word(a.device)), _lib.stream_ptr(),
         )

