@@ -83,34 +83,51 @@ def run_gpt2m_turbo_dp(args, rank, world, dev):
     data = _tokens(model.config.vocab_size, batch, seq, 8, 100 + rank, dev)
     state = {"step": 0}
 
-    def step(_i):
-        S.set_step(layers, state["step"])
-        ids = data[state["step"] % len(data)]
-        state["step"] += 1
+    def core(ids):
         sync.zero_grad() if sync else opt.zero_grad(set_to_none=True)
         with torch.autocast("cuda", dtype=torch.bfloat16):
-            model(input_ids=ids, labels=ids).loss.backward()
+            loss = model(input_ids=ids, labels=ids).loss
+        loss.backward()
         if sync:
             sync.finish()
         opt.step()
+        return loss
 
+    def eager(_i):
+        S.set_step(layers, state["step"])
+        ids = data[state["step"] % len(data)]
+        state["step"] += 1
+        core(ids)
+
+    use_graph = args.graph == "on" and (sync is None or sync.backend == "symm")
     for phase, until in (("full (steps < 50)", 5), ("turbo (steps >= 50)", 55)):
         while state["step"] < until:
-            step(0)
+            eager(0)
+        step = eager
+        if use_graph:      # one graph per phase: the kernels of a step change when the residual is dropped at step 50
+            from stacr_b200.graphs import GraphedStep
+
+            graphed = GraphedStep(core, [data[0]], optimizer=opt, layers=layers, first_step=state["step"], warmup=2)
+            state["step"] = graphed.step
+
+            def step(_i, graphed=graphed):
+                graphed(data[graphed.step % len(data)])
+                state["step"] = graphed.step
         torch.cuda.reset_peak_memory_stats(dev)
         secs = _timed(args.steps, step, world)
         rows = batch * seq
         _emit(rank, config="gpt2m_turbo_dp", phase=phase, n_gpus=world, steps=args.steps, tokens_per_second=world * rows * args.steps / secs,
               ms_per_step=1e3 * secs / args.steps, peak_allocated_gb=torch.cuda.max_memory_allocated(dev) / 1e9,
               saved_gb_wrapped=sum(l.stored_bytes(rows, 2)["total"] for l in layers) / 1e9, dense_gb_same_layers=sum(rows * l.in_features * 2 for l in layers) / 1e9,
-              first_step_in_phase=until)
+              first_step_in_phase=until, cuda_graph=use_graph)
 
 
 def run_gpt2l_tp(args, rank, world, dev):
     import stacr_b200 as S
     from stacr_b200.models import build_model
     from stacr_b200.optim import AdamW
-    from stacr_b200.protocols.tensor_parallel import sync_replicated_grads
+    from stacr_b200.parallel import GradSync
+    from stacr_b200.protocols.tensor_parallel import replicated_parameters
     from stacr_b200.protocols.tp_gpt2 import apply_tensor_parallel_gpt2, disable_tp_dropout, get_tp_stacr_targets
 
     batch, seq = 4, 1024
@@ -122,27 +139,45 @@ def run_gpt2l_tp(args, rank, world, dev):
     layers = S.apply_stacr(model, surface="none", target_names=names, rank=8, residual_budget=0.005, residual_mode="block_sparse",
                            turbo_after_step=None, allow_empty=False)
     opt = AdamW(model.parameters(), lr=5e-5, weight_decay=0.0, bf16_shadow=True)
+    # gradients of the replicated parameters (embeddings, LayerNorms) are averaged over the ranks in one flat symmetric buffer by
+    # the in-tree all-reduce, overlapped with backward; the shards' gradients are local
+    sync = GradSync([p for _, p in replicated_parameters(model)]) if world > 1 else None
     data = _tokens(model.config.vocab_size, batch, seq, 8, 100, dev)   # the same batch on every rank: this is model parallelism
     state = {"step": 0}
+
+    def core(ids):
+        opt.zero_grad(set_to_none=True)
+        if sync:
+            sync.zero_grad()
+        with torch.autocast("cuda", dtype=torch.bfloat16):
+            loss = model(input_ids=ids, labels=ids).loss
+        loss.backward()
+        if sync:
+            sync.finish()
+        opt.step()
+        return loss
 
     def step(_i):
         S.set_step(layers, state["step"])
         ids = data[state["step"] % len(data)]
         state["step"] += 1
-        opt.zero_grad(set_to_none=True)
-        with torch.autocast("cuda", dtype=torch.bfloat16):
-            model(input_ids=ids, labels=ids).loss.backward()
-        if world > 1:
-            sync_replicated_grads(model, None)
-        opt.step()
+        core(ids)
 
     for _ in range(max(3, args.warmup)):
         step(0)
+    use_graph = args.graph == "on" and (sync is None or sync.backend == "symm")
+    if use_graph:
+        from stacr_b200.graphs import GraphedStep
+
+        graphed = GraphedStep(core, [data[0]], optimizer=opt, layers=layers, first_step=state["step"], warmup=2)
+
+        def step(_i):  # noqa: F811 - the replayed form of the step above
+            graphed(data[graphed.step % len(data)])
     torch.cuda.reset_peak_memory_stats(dev)
     secs = _timed(args.steps, step, world)
     _reports(args, step, rank)
     _emit(rank, config="gpt2l_tp", tp_degree=world, steps=args.steps, tokens_per_second=batch * seq * args.steps / secs, ms_per_step=1e3 * secs / args.steps,
-          peak_allocated_gb=torch.cuda.max_memory_allocated(dev) / 1e9, wrapped_layers=len(layers),
+          peak_allocated_gb=torch.cuda.max_memory_allocated(dev) / 1e9, wrapped_layers=len(layers), cuda_graph=use_graph,
           saved_gb_wrapped=sum(l.stored_bytes(batch * seq, 2)["total"] for l in layers) / 1e9,
           dense_gb_same_layers=sum(batch * seq * l.in_features * 2 for l in layers) / 1e9)
 
@@ -197,6 +232,7 @@ def main(argv=None) -> int:
     parser.add_argument("--config", required=True, choices=sorted(RUNNERS))
     parser.add_argument("--steps", type=int, default=10)
     parser.add_argument("--warmup", type=int, default=5)
+    parser.add_argument("--graph", default="on", choices=["on", "off"], help="replay the training step from a CUDA graph (projection-engine configurations)")
     parser.add_argument("--kernel-table", metavar="FILE", help="gpt2l_tp: write per-kernel device times of two more steps to FILE")
     parser.add_argument("--gap-report", metavar="FILE", help="gpt2l_tp: write where the GPU idles inside two more steps to FILE")
     args = parser.parse_args(argv)
