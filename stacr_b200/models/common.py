@@ -10,6 +10,7 @@ which runs the sm_100a kernels for bf16 CUDA tensors.
 
 from __future__ import annotations
 
+import os
 from dataclasses import dataclass
 from typing import Optional
 
@@ -17,6 +18,7 @@ import torch
 from torch import nn
 from torch.nn import functional as F
 
+from ..ops import attention as attention_ops
 from ..ops import nn_ops
 
 
@@ -63,12 +65,24 @@ class GELU(nn.Module):
         return nn_ops.gelu(x, self.approximate)
 
 
-def causal_attention(q, k, v, *, causal: bool, attention_mask=None, dropout_p: float = 0.0, training: bool = False):
-    """Softmax attention on ``[B, H, S, D]`` tensors.
+def _attention_engine() -> str:
+    """``STACR_ATTENTION``: ``library`` (default: the fused attention ``torch`` dispatches to, which measured faster on
+    B200) or ``intree`` (the tcgen05 forward kernel of ``ops/attention.py``, used where no gradient is needed)."""
+    return os.environ.get("STACR_ATTENTION", "library")
 
-    Uses the fused flash kernel of the framework runtime (no ``S x S`` score tensor).  A padding
-    mask ``[B, S]`` (1 = keep) is turned into an additive bias only when it actually masks something.
+
+def causal_attention(q, k, v, *, causal: bool, attention_mask=None, dropout_p: float = 0.0, training: bool = False):
+    """Softmax attention on ``[B, H, S, D]`` tensors (no ``S x S`` score tensor).
+
+    A padding mask ``[B, S]`` (1 = keep) is turned into an additive bias only when it actually masks something.  With
+    ``STACR_ATTENTION=intree`` and no gradient to record (evaluation, generation, recomputation-free inference) the
+    in-tree kernel runs instead: it reads strided views of a fused QKV projection in place.
     """
+    if (_attention_engine() == "intree" and not (torch.is_grad_enabled() and (q.requires_grad or k.requires_grad or v.requires_grad))
+            and not (training and dropout_p > 0.0) and attention_ops.supported(q, k, v)):
+        b, h, s, d = q.shape
+        out, _ = attention_ops.forward(q, k, v, causal=causal, key_mask=attention_mask, need_lse=False)
+        return out.view(b, s, h, d).transpose(1, 2)
     bias = None
     if attention_mask is not None and not bool(attention_mask.all()):
         keep = attention_mask[:, None, None, :].to(torch.bool)

@@ -1,16 +1,20 @@
 // Softmax attention forward on the fifth-generation tensor cores (tcgen05 + TMEM), flash style: the S x S score matrix
 // never exists in memory.
 //
-// One CTA owns 128 query rows of one (batch, head) and walks the key/value tiles (128 keys each) that those rows may
-// attend to.  Warp roles (192 threads, one CTA per SM):
-//   warp 0, lane 0   TMA producer: Q once; K and V tiles into two-stage rings.
+// One CTA owns 128 query rows of one (batch, head) and walks the key/value tiles (64 keys each) that those rows may
+// attend to.  Two CTAs share an SM (half of the shared memory and half of the tensor memory each), so one CTA's softmax
+// runs under the other's tensor-core work and prologues hide behind main loops.  Warp roles (224 threads):
+//   warp 0, lane 0   TMA producer: Q once, K tiles into a two-stage ring.
+//   warp 6, lane 0   TMA producer: V tiles into a two-stage ring.
 //   warp 1, lane 0   MMA issuer: S_j = Q K_j^T into one of two score accumulators in tensor memory, O += P_j V_j into
 //                    the output accumulator.  S_{j+1} is issued before P_j V_j, so the tensor core computes the next
 //                    scores while the softmax warps work on the current ones.
-//   warps 2..5       softmax: thread t owns query row t of the tile (its TMEM lane): reads the 128 scores of its row into
+//   warps 2..5       softmax: thread t owns query row t of the tile (its TMEM lane): reads the 64 scores of its row into
 //                    registers, masks (causal / key padding / sequence end), keeps a running maximum and sum in the base-2
-//                    domain, writes P_j as bf16 into shared memory in the 128-byte-swizzled K-major layout the MMA reads,
-//                    and rescales the output accumulator in tensor memory only when the running maximum has grown by more
+//                    domain, writes P_j as bf16 back into tensor memory (over the scores it came from), from where the
+//                    second product takes it as its A operand: P never touches shared memory, whose bandwidth is
+//                    what bounds this kernel (the tensor core reads every smem operand at 128 B/clk).  It
+//                    rescales the output accumulator in tensor memory only when the running maximum has grown by more
 //                    than 2^8 since the last rescale (a stale maximum is exact as long as nothing overflows).
 // The epilogue divides by the row sums, writes O as bf16 [tokens, heads * head_dim] and the row log-sum-exp for backward.
 //
@@ -27,10 +31,11 @@ int make_tensor_map_bf16(CUtensorMap* map, const void* ptr, uint64_t inner, uint
 
 namespace fa {
 
-constexpr int BQ = 128, BKV = 128, THREADS = 192, UMMA_K = 16;
-constexpr int TMEM_COLS = 512;
-constexpr int COL_S0 = 0, COL_S1 = 128, COL_O = 256;
+constexpr int BQ = 128, BKV = 64, THREADS = 224, UMMA_K = 16;
+constexpr int TMEM_COLS = 256;
+constexpr int COL_S0 = 0, COL_S1 = 64, COL_O = 128;
 constexpr float RESCALE_THRESHOLD = 8.f;   // in log2 units
+constexpr int ST_SMEM_MISALIGNED = 90;
 
 struct FwdParams {
   int B, H, S;
@@ -65,36 +70,91 @@ __device__ __forceinline__ void tmem_st_x16(uint32_t taddr, const uint32_t (&r)[
         "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
       : "memory");
 }
+__device__ __forceinline__ float ex2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ float max3(float a, float b, float c) {
+  float y;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(y) : "f"(a), "f"(b), "f"(c));
+  return y;
+}
+__device__ __forceinline__ void tmem_st_x32(uint32_t taddr, const uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+      "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
+      :
+      : "r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]),
+        "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]),
+        "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]),
+        "r"(r[30]), "r"(r[31])
+      : "memory");
+}
+// D[tmem] (+)= A[tmem] * B[smem desc]: the A operand (M = 128 rows on the 128 lanes, K along the columns, two bf16 per
+// 32-bit column) is read from tensor memory.
+__device__ __forceinline__ void umma_bf16_ta(uint32_t tmem_d, uint32_t tmem_a, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+      :
+      : "r"(tmem_d), "r"(tmem_a), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
 __device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
-// Shared-memory plan (all tile buffers 1024-byte aligned):
+// Shared-memory plan (all tile buffers 1024-byte aligned; no slack, so that two CTAs fit on an SM):
 //   Q        [D / 64 chunks][128 rows][128 B]
-//   K[2]     the same, two stages
-//   V[2]     [2 key blocks][D / 64 column atoms][64 rows][128 B], two stages
-//   P        [2 key chunks][128 rows][128 B]
+//   K[2]     [D / 64 chunks][64 rows][128 B], two stages
+//   V[2]     [D / 64 column atoms][64 rows][128 B], two stages
 template <int D>
 struct Plan {
   static constexpr int Q_BYTES = BQ * D * 2;
   static constexpr int K_BYTES = BKV * D * 2;
   static constexpr int V_BYTES = BKV * D * 2;
-  static constexpr int P_BYTES = BQ * BKV * 2;
   static constexpr int OFF_Q = 0;
   static constexpr int OFF_K = OFF_Q + Q_BYTES;
   static constexpr int OFF_V = OFF_K + 2 * K_BYTES;
-  static constexpr int OFF_P = OFF_V + 2 * V_BYTES;
-  static constexpr int OFF_BAR = OFF_P + P_BYTES;
-  static constexpr int SMEM_BYTES = OFF_BAR + 256 + 1024;
+  static constexpr int OFF_BAR = OFF_V + 2 * V_BYTES;
+  static constexpr int SMEM_BYTES = OFF_BAR + 256;
 };
 
-enum Bar { Q_FULL = 0, K_FULL = 1, K_EMPTY = 3, V_FULL = 5, V_EMPTY = 7, S_FULL = 9, S_EMPTY = 11, P_READY = 13, P_EMPTY = 14, O_DONE = 15, NBARS = 16 };
+// Barriers.  The MMA thread is a serial chain of waits, issues and commits, and each of those costs it a few hundred
+// cycles, so every event it needs is folded into as few barriers as possible:
+//   QK_GO[s]   K tile (and, for tile 0, Q) landed in stage s  AND  the softmax warps have taken the previous scores out of
+//              accumulator s (1 producer arrival with the byte count + 4 warp arrivals; the first use is pre-arrived)
+//   PV_GO[s]   V tile landed in stage s  AND  P_j is in tensor memory (1 + 4 arrivals)
+//   S_FULL[s]  S_j is complete (commit): read by the softmax warps and by the K producer (stage s may be refilled)
+//   PV_DONE    P_j V_j is complete (commit, one phase per tile): read by the V producer, by a softmax thread that has to
+//              rescale the output accumulator, and by the epilogue
+enum Bar { QK_GO = 0, PV_GO = 2, S_FULL = 4, PV_DONE = 6, NBARS = 8 };
+
+// Non-blocking probe first: a barrier that has already completed is the common case on the MMA thread's critical path.
+__device__ __forceinline__ bool wait_on(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int* status, int code) {
+  uint32_t done;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(done)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  if (done) return true;
+  return mbar_wait(bar, parity, abort_flag, status, code);
+}
 
 template <int D>
-__global__ void __launch_bounds__(THREADS, 1)
+__global__ void __launch_bounds__(THREADS, 2)
 flash_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
                  const __grid_constant__ CUtensorMap tmap_v, const FwdParams p) {
   using PL = Plan<D>;
-  extern __shared__ uint8_t smem_raw[];
-  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  extern __shared__ __align__(1024) uint8_t smem[];
+  if (smem_u32(smem) & 1023u) {   // the swizzled layouts need 1024-byte aligned tiles; nothing has been started yet
+    if (threadIdx.x == 0 && p.status) atomicCAS(p.status, 0, ST_SMEM_MISALIGNED);
+    return;
+  }
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + PL::OFF_BAR);
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + NBARS);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
@@ -107,23 +167,17 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
   const int b = bh / p.H, h = bh - b * p.H;
   const int q0 = qt * BQ;
   const int nkv_all = (p.S + BKV - 1) / BKV;
-  const int nkv = p.causal ? min(nkv_all, qt + 1) : nkv_all;
+  const int nkv = p.causal ? min(nkv_all, (q0 + BQ) / BKV) : nkv_all;
   const int row_base = b * p.S;                      // first token row of this batch entry in the source matrices
   const int qcol = p.q_col0 + h * p.head_stride, kcol = p.k_col0 + h * p.head_stride, vcol = p.v_col0 + h * p.head_stride;
 
   if (threadIdx.x == 0) {
-    mbar_init(&bars[Q_FULL], 1);
     for (int s = 0; s < 2; ++s) {
-      mbar_init(&bars[K_FULL + s], 1);
-      mbar_init(&bars[K_EMPTY + s], 1);
-      mbar_init(&bars[V_FULL + s], 1);
-      mbar_init(&bars[V_EMPTY + s], 1);
+      mbar_init(&bars[QK_GO + s], 5);
+      mbar_init(&bars[PV_GO + s], 5);
       mbar_init(&bars[S_FULL + s], 1);
-      mbar_init(&bars[S_EMPTY + s], 4);
     }
-    mbar_init(&bars[P_READY], 4);
-    mbar_init(&bars[P_EMPTY], 1);
-    mbar_init(&bars[O_DONE], 1);
+    mbar_init(&bars[PV_DONE], 1);
     *abort_flag = 0;
     fence_barrier_init();
   }
@@ -141,28 +195,35 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
     if (lane == 0) {
       tma_prefetch_desc(&tmap_q);
       tma_prefetch_desc(&tmap_k);
-      tma_prefetch_desc(&tmap_v);
-      mbar_expect_tx(&bars[Q_FULL], PL::Q_BYTES);
-#pragma unroll
-      for (int c = 0; c < D / 64; ++c) tma_load_2d(smem + PL::OFF_Q + c * (BQ * 128), &tmap_q, &bars[Q_FULL], qcol + c * 64, row_base + q0);
-      bool ok = true;
-      for (int j = 0; j < nkv && ok; ++j) {
+      for (int j = 0; j < nkv; ++j) {
         const int s = j & 1;
-        const uint32_t ph = (j >> 1) & 1;
         const int kv0 = j * BKV;
-        if (!mbar_wait(&bars[K_EMPTY + s], ph ^ 1u, abort_flag, p.status, ST_TIMEOUT_SMEM_EMPTY)) { ok = false; break; }
-        mbar_expect_tx(&bars[K_FULL + s], PL::K_BYTES);
+        // stage s is free once S_{j-2}, which read it, is complete
+        if (j >= 2 && !wait_on(&bars[S_FULL + s], ((j - 2) >> 1) & 1, abort_flag, p.status, ST_TIMEOUT_SMEM_EMPTY)) break;
+        mbar_expect_tx(&bars[QK_GO + s], PL::K_BYTES + (j == 0 ? PL::Q_BYTES : 0));
+        if (j == 0) {
+#pragma unroll
+          for (int c = 0; c < D / 64; ++c) tma_load_2d(smem + PL::OFF_Q + c * (BQ * 128), &tmap_q, &bars[QK_GO], qcol + c * 64, row_base + q0);
+        }
 #pragma unroll
         for (int c = 0; c < D / 64; ++c)
-          tma_load_2d(smem + PL::OFF_K + s * PL::K_BYTES + c * (BKV * 128), &tmap_k, &bars[K_FULL + s], kcol + c * 64, row_base + kv0);
-        if (!mbar_wait(&bars[V_EMPTY + s], ph ^ 1u, abort_flag, p.status, ST_TIMEOUT_SMEM_EMPTY)) { ok = false; break; }
-        mbar_expect_tx(&bars[V_FULL + s], PL::V_BYTES);
+          tma_load_2d(smem + PL::OFF_K + s * PL::K_BYTES + c * (BKV * 128), &tmap_k, &bars[QK_GO + s], kcol + c * 64, row_base + kv0);
+      }
+    }
+  } else if (warp == 6) {
+    // ------------------------------------------------------------------ TMA producer for V (its ring drains later than
+    // K's: a producer of its own keeps a late V slot from holding back the next K tile)
+    if (lane == 0) {
+      tma_prefetch_desc(&tmap_v);
+      for (int j = 0; j < nkv; ++j) {
+        const int s = j & 1;
+        const int kv0 = j * BKV;
+        // stage s is free once P_{j-2} V_{j-2} is complete (one phase of PV_DONE per tile, waited for in order)
+        if (j >= 2 && !wait_on(&bars[PV_DONE], (j - 2) & 1, abort_flag, p.status, ST_TIMEOUT_SMEM_EMPTY)) break;
+        mbar_expect_tx(&bars[PV_GO + s], PL::V_BYTES);
 #pragma unroll
-        for (int kb = 0; kb < 2; ++kb)
-#pragma unroll
-          for (int a = 0; a < D / 64; ++a)
-            tma_load_2d(smem + PL::OFF_V + s * PL::V_BYTES + (kb * (D / 64) + a) * 8192, &tmap_v, &bars[V_FULL + s], vcol + a * 64,
-                        row_base + kv0 + kb * 64);
+        for (int a = 0; a < D / 64; ++a)
+          tma_load_2d(smem + PL::OFF_V + s * PL::V_BYTES + a * 8192, &tmap_v, &bars[PV_GO + s], vcol + a * 64, row_base + kv0);
       }
     }
   } else if (warp == 1) {
@@ -181,12 +242,11 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
           for (int k = 0; k < 64 / UMMA_K; ++k)
             umma_bf16(d_tmem, make_smem_desc_sw128(q_addr + c * (BQ * 128) + k * 32, 16, 1024),
                       make_smem_desc_sw128(k_addr + c * (BKV * 128) + k * 32, 16, 1024), idesc_s, (c > 0 || k > 0) ? 1u : 0u);
-        umma_commit(&bars[K_EMPTY + s]);   // the K stage may be refilled once these MMAs have read it
         umma_commit(&bars[S_FULL + s]);
       };
-      bool ok = mbar_wait(&bars[Q_FULL], 0, abort_flag, p.status, ST_TIMEOUT_SMEM_FULL);
-      if (ok && nkv > 0) {
-        ok = mbar_wait(&bars[K_FULL], 0, abort_flag, p.status, ST_TIMEOUT_SMEM_FULL);
+      bool ok = true;
+      if (nkv > 0) {
+        ok = wait_on(&bars[QK_GO], 0, abort_flag, p.status, ST_TIMEOUT_SMEM_FULL);
         if (ok) {
           tc_fence_after();
           issue_scores(0);
@@ -194,103 +254,103 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
       }
       for (int j = 0; j < nkv && ok; ++j) {
         const int s = j & 1;
-        const uint32_t ph = (j >> 1) & 1;
         if (j + 1 < nkv) {
           const int s1 = (j + 1) & 1;
-          const uint32_t ph1 = ((j + 1) >> 1) & 1;
-          if (!mbar_wait(&bars[K_FULL + s1], ph1, abort_flag, p.status, ST_TIMEOUT_SMEM_FULL)) { ok = false; break; }
-          // the softmax warps have taken S_{j-1} (same accumulator) into registers
-          if (!mbar_wait(&bars[S_EMPTY + s1], ph1 ^ 1u, abort_flag, p.status, ST_TIMEOUT_TMEM_EMPTY)) { ok = false; break; }
+          if (!wait_on(&bars[QK_GO + s1], ((j + 1) >> 1) & 1, abort_flag, p.status, ST_TIMEOUT_SMEM_FULL)) { ok = false; break; }
           tc_fence_after();
           issue_scores(j + 1);
         }
-        if (!mbar_wait(&bars[P_READY], j & 1, abort_flag, p.status, ST_TIMEOUT_TMEM_FULL)) { ok = false; break; }
-        if (!mbar_wait(&bars[V_FULL + s], ph, abort_flag, p.status, ST_TIMEOUT_SMEM_FULL)) { ok = false; break; }
+        if (!wait_on(&bars[PV_GO + s], (j >> 1) & 1, abort_flag, p.status, ST_TIMEOUT_TMEM_FULL)) { ok = false; break; }
         tc_fence_after();
-        const uint32_t p_addr = smem_u32(smem + PL::OFF_P);
         const uint32_t v_addr = smem_u32(smem + PL::OFF_V + s * PL::V_BYTES);
+        // P_j sits in the first 32 columns of the score accumulator it was computed from (two bf16 per column)
+        const uint32_t p_tmem = tmem_base + (s ? COL_S1 : COL_S0);
 #pragma unroll
-        for (int kb = 0; kb < 2; ++kb)
-#pragma unroll
-          for (int k = 0; k < 64 / UMMA_K; ++k)
-            umma_bf16(tmem_base + COL_O, make_smem_desc_sw128(p_addr + kb * (BQ * 128) + k * 32, 16, 1024),
-                      make_smem_desc_sw128(v_addr + kb * (D / 64) * 8192 + k * 2048, 8192, 1024), idesc_o, (j > 0 || kb > 0 || k > 0) ? 1u : 0u);
-        umma_commit(&bars[V_EMPTY + s]);
-        umma_commit(&bars[P_EMPTY]);
+        for (int k = 0; k < BKV / UMMA_K; ++k)
+          umma_bf16_ta(tmem_base + COL_O, p_tmem + k * (UMMA_K / 2), make_smem_desc_sw128(v_addr + k * 2048, 8192, 1024), idesc_o,
+                       (j > 0 || k > 0) ? 1u : 0u);
+        umma_commit(&bars[PV_DONE]);
       }
-      if (ok) umma_commit(&bars[O_DONE]);
     }
   } else {
     // ------------------------------------------------------------------ softmax warps: thread = query row
-    const int quad = warp & 3;
+    const int quad = warp & 3;                       // warp w may touch the TMEM lanes of quarter w % 4
     const int r = quad * 32 + lane;                  // row of the tile = TMEM lane
     const int qrow = q0 + r;                         // position in the sequence
     const uint32_t t_lane = tmem_base + (static_cast<uint32_t>(quad * 32) << 16);
-    float m_used = -INFINITY;                        // maximum the stored exponentials are relative to (log2 domain)
+    float m_used = -INFINITY;                        // maximum the stored exponentials are relative to (log2 domain, scaled)
     float m_true = -INFINITY;                        // running maximum
     float l = 0.f;                                   // running sum of 2^(s - m_used)
     bool ok = true;
-    uint8_t* p_row = smem + PL::OFF_P + r * 128;
+    if (lane == 0) {   // both score accumulators start out free
+      mbar_arrive(&bars[QK_GO]);
+      mbar_arrive(&bars[QK_GO + 1]);
+    }
     for (int j = 0; j < nkv && ok; ++j) {
       const int s = j & 1;
       const uint32_t ph = (j >> 1) & 1;
       const int kv0 = j * BKV;
-      if (!mbar_wait(&bars[S_FULL + s], ph, abort_flag, p.status, ST_TIMEOUT_TMEM_FULL)) { ok = false; break; }
+      if (!wait_on(&bars[S_FULL + s], ph, abort_flag, p.status, ST_TIMEOUT_TMEM_FULL)) { ok = false; break; }
       tc_fence_after();
-      uint32_t raw[4][32];
-#pragma unroll
-      for (int c = 0; c < 4; ++c) tmem_ld_x32(t_lane + (s ? COL_S1 : COL_S0) + c * 32, raw[c]);
+      uint32_t raw[2][32];
+      tmem_ld_x32(t_lane + (s ? COL_S1 : COL_S0), raw[0]);
+      tmem_ld_x32(t_lane + (s ? COL_S1 : COL_S0) + 32, raw[1]);
       tmem_ld_wait();
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(&bars[S_EMPTY + s]);   // the accumulator may be overwritten by S_{j+2}
-      // masks: sequence end, causal diagonal, key padding
+      if (lane == 0) mbar_arrive(&bars[QK_GO + s]);   // the accumulator may be overwritten by S_{j+2}
+      // masks: sequence end, causal diagonal, key padding (scores stay unscaled here; the scale is positive)
       const bool edge = (kv0 + BKV > p.S) || (p.causal && kv0 + BKV - 1 > q0) || (p.key_mask != nullptr);
-      float mx = -INFINITY;
+      if (edge) {
 #pragma unroll
-      for (int c = 0; c < 4; ++c)
+        for (int c = 0; c < 2; ++c)
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          float v = __uint_as_float(raw[c][i]) * p.scale_log2;
-          if (edge) {
+          for (int i = 0; i < 32; ++i) {
             const int key = kv0 + c * 32 + i;
             bool keep = key < p.S && (!p.causal || key <= qrow);
             if (keep && p.key_mask) keep = p.key_mask[static_cast<size_t>(b) * p.S + key] != 0;
-            if (!keep) v = -INFINITY;
+            if (!keep) raw[c][i] = 0xff800000u;   // -inf
           }
-          raw[c][i] = __float_as_uint(v);
-          mx = fmaxf(mx, v);
+      }
+      float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+      for (int c = 0; c < 2; ++c)
+#pragma unroll
+        for (int i = 0; i < 32; i += 8) {
+          const int a = (i >> 3) & 3;
+          mx[a] = max3(mx[a], __uint_as_float(raw[c][i]), __uint_as_float(raw[c][i + 1]));
+          mx[a] = max3(mx[a], __uint_as_float(raw[c][i + 2]), __uint_as_float(raw[c][i + 3]));
+          mx[a] = max3(mx[a], __uint_as_float(raw[c][i + 4]), __uint_as_float(raw[c][i + 5]));
+          mx[a] = max3(mx[a], __uint_as_float(raw[c][i + 6]), __uint_as_float(raw[c][i + 7]));
         }
-      m_true = fmaxf(m_true, mx);
+      m_true = fmaxf(m_true, fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])) * p.scale_log2);
       // the output accumulator holds sums relative to m_used; rescale it (and l) only when the maximum has moved far
       float alpha = 1.f;
       bool rescale = false;
       if (m_true > m_used + RESCALE_THRESHOLD || m_used == -INFINITY) {
-        const float m_new = m_true;
         if (m_used != -INFINITY) {
-          alpha = exp2f(m_used - m_new);
+          alpha = ex2(m_used - m_true);
           rescale = true;
         }
-        m_used = m_new;
+        m_used = m_true;
       }
-      const float m_sub = (m_used == -INFINITY) ? 0.f : m_used;   // a row with nothing to attend to so far
-      float sum = 0.f;
-      uint32_t packed[64];
+      const float neg_m = (m_used == -INFINITY) ? 0.f : -m_used;   // a row with nothing to attend to so far
+      float sum[4] = {0.f, 0.f, 0.f, 0.f};
+      uint32_t packed[32];
 #pragma unroll
-      for (int c = 0; c < 4; ++c)
+      for (int c = 0; c < 2; ++c)
 #pragma unroll
         for (int i = 0; i < 32; i += 2) {
-          const float e0 = exp2f(__uint_as_float(raw[c][i]) - m_sub);
-          const float e1 = exp2f(__uint_as_float(raw[c][i + 1]) - m_sub);
-          const uint32_t pk = pack_bf16x2(e0, e1);
-          // the sum follows the rounded values that the tensor core will actually multiply
-          sum += __uint_as_float(pk << 16) + __uint_as_float(pk & 0xFFFF0000u);
-          packed[c * 16 + i / 2] = pk;
+          const float e0 = ex2(fmaf(__uint_as_float(raw[c][i]), p.scale_log2, neg_m));
+          const float e1 = ex2(fmaf(__uint_as_float(raw[c][i + 1]), p.scale_log2, neg_m));
+          sum[(i >> 1) & 3] += e0 + e1;
+          packed[c * 16 + i / 2] = pack_bf16x2(e0, e1);
         }
-      l = l * alpha + sum;
-      // P_{j-1} V_{j-1} has finished: the P buffer is free and the output accumulator is quiescent
-      if (j > 0 && !mbar_wait(&bars[P_EMPTY], (j - 1) & 1, abort_flag, p.status, ST_TIMEOUT_TMEM_EMPTY)) { ok = false; break; }
+      l = l * alpha + ((sum[0] + sum[1]) + (sum[2] + sum[3]));
       if (__any_sync(0xffffffffu, rescale)) {
+        // P_{j-1} V_{j-1} must have finished before the output accumulator is touched.  (Phase j - 1 of the barrier is
+        // the only one that can still be open here, so skipping this wait on other tiles leaves the parity unambiguous.)
+        if (j > 0 && !wait_on(&bars[PV_DONE], (j - 1) & 1, abort_flag, p.status, ST_TIMEOUT_TMEM_EMPTY)) { ok = false; break; }
         tc_fence_after();
 #pragma unroll 1
         for (int c = 0; c < D / 16; ++c) {
@@ -301,22 +361,18 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
           for (int i = 0; i < 16; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
           tmem_st_x16(t_lane + COL_O + c * 16, o);
         }
-        tmem_st_wait();
-        tc_fence_before();
       }
-      // P as the K-major, 128-byte-swizzled A operand: two 64-key chunks of [128 rows][128 B]
-#pragma unroll
-      for (int c16 = 0; c16 < 16; ++c16) {
-        const int chunk = c16 >> 3, slot = c16 & 7;
-        *reinterpret_cast<uint4*>(p_row + chunk * (BQ * 128) + ((slot ^ (r & 7)) << 4)) =
-            make_uint4(packed[c16 * 4], packed[c16 * 4 + 1], packed[c16 * 4 + 2], packed[c16 * 4 + 3]);
-      }
-      fence_proxy_async();
+      // P_j as the A operand of the second product, in tensor memory: it overwrites the scores it came from (this
+      // thread's lane only, already in registers).  The previous user of these columns, P_{j-2} V_{j-2}, ran before S_j
+      // was written, because the tensor core executes in issue order.
+      tmem_st_x32(t_lane + (s ? COL_S1 : COL_S0), packed);
+      tmem_st_wait();
+      tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(&bars[P_READY]);
+      if (lane == 0) mbar_arrive(&bars[PV_GO + s]);
     }
     // ---- epilogue
-    if (ok && nkv > 0) ok = mbar_wait(&bars[O_DONE], 0, abort_flag, p.status, ST_TIMEOUT_TMEM_FULL);
+    if (ok && nkv > 0) ok = wait_on(&bars[PV_DONE], (nkv - 1) & 1, abort_flag, p.status, ST_TIMEOUT_TMEM_FULL);
     if (ok) {
       tc_fence_after();
       const float inv = l > 0.f ? 1.f / l : 0.f;

@@ -58,3 +58,22 @@ def test_flash_forward_with_padding_keys_and_large_scores():
         ref = attention.reference(q, k, v, causal=causal, key_mask=keep)
         assert bool(torch.isfinite(out.float()).all())
         assert float((out.float() - ref).abs().max()) < 3e-2
+
+
+def test_model_attention_uses_the_in_tree_kernel_without_grad(monkeypatch):
+    """``STACR_ATTENTION=intree``: evaluation goes through the tcgen05 forward and agrees with the default path."""
+    from stacr_b200.models import GPTNeoXForCausalLM, NeoXConfig
+    from stacr_b200.ops import _lib
+
+    torch.manual_seed(5)
+    cfg = NeoXConfig(vocab_size=512, hidden_size=256, num_hidden_layers=2, num_attention_heads=4, intermediate_size=512, max_position_embeddings=256)
+    model = GPTNeoXForCausalLM(cfg).cuda().eval()
+    ids = torch.randint(0, 512, (2, 200), device="cuda")
+    with torch.no_grad(), torch.autocast("cuda", dtype=torch.bfloat16):
+        ref = model(input_ids=ids).logits.float()
+        monkeypatch.setenv("STACR_ATTENTION", "intree")
+        got = model(input_ids=ids).logits.float()
+    torch.cuda.synchronize()
+    _lib.check_status()
+    assert float((got - ref).abs().max()) < 0.1 * float(ref.abs().max())
+    assert float(torch.nn.functional.cosine_similarity(got.flatten(), ref.flatten(), dim=0)) > 0.999
