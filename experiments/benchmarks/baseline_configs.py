@@ -133,7 +133,9 @@ def run_gpt2l_tp(args, rank, world, dev):
     batch, seq = 4, 1024
     torch.manual_seed(7)                                   # every rank builds the same full model, then keeps its shard
     model = build_model("gpt2-large").to(dev).train()
-    apply_tensor_parallel_gpt2(model, rank, world, None, scope="full")
+    # GPT-2 large has 20 heads: degrees that do not divide them (8) shard the MLPs only and keep attention replicated
+    scope = "full" if model.config.n_head % world == 0 else "mlp_only"
+    apply_tensor_parallel_gpt2(model, rank, world, None, scope=scope)
     disable_tp_dropout(model)
     names = get_tp_stacr_targets(model, "all_linear")
     layers = S.apply_stacr(model, surface="none", target_names=names, rank=8, residual_budget=0.005, residual_mode="block_sparse",
@@ -176,7 +178,7 @@ def run_gpt2l_tp(args, rank, world, dev):
     torch.cuda.reset_peak_memory_stats(dev)
     secs = _timed(args.steps, step, world)
     _reports(args, step, rank)
-    _emit(rank, config="gpt2l_tp", tp_degree=world, steps=args.steps, tokens_per_second=batch * seq * args.steps / secs, ms_per_step=1e3 * secs / args.steps,
+    _emit(rank, config="gpt2l_tp", tp_degree=world, tp_scope=scope, steps=args.steps, tokens_per_second=batch * seq * args.steps / secs, ms_per_step=1e3 * secs / args.steps,
           peak_allocated_gb=torch.cuda.max_memory_allocated(dev) / 1e9, wrapped_layers=len(layers), cuda_graph=use_graph,
           saved_gb_wrapped=sum(l.stored_bytes(batch * seq, 2)["total"] for l in layers) / 1e9,
           dense_gb_same_layers=sum(batch * seq * l.in_features * 2 for l in layers) / 1e9)

@@ -96,8 +96,9 @@ def run_gpt2l_tp(args, ref, torch, dist, rank, world, dev):
     torch.manual_seed(7)
     cfg = GPT2Config(n_embd=1280, n_layer=36, n_head=20, n_positions=1024, vocab_size=50257, resid_pdrop=0.0, embd_pdrop=0.0, attn_pdrop=0.0)
     model = GPT2LMHeadModel(cfg).to(dev).train()
+    scope = "full" if cfg.n_head % world == 0 else "mlp_only"      # 20 heads: degree 8 shards the MLPs only
     if world > 1:
-        apply_tensor_parallel_gpt2(model, rank, world, None, scope="full")
+        apply_tensor_parallel_gpt2(model, rank, world, None, scope=scope)
         disable_tp_dropout(model)
         names = get_tp_stacr_targets(model, "all_linear")
         layers = ref.apply_stacr(model, surface="none", target_names=names, rank=8, residual_budget=0.005, residual_mode="block_sparse",
@@ -123,7 +124,7 @@ def run_gpt2l_tp(args, ref, torch, dist, rank, world, dev):
         step(0)
     torch.cuda.reset_peak_memory_stats(dev)
     secs = _timed(torch, dist, args.steps, step, world)
-    _emit(rank, config="gpt2l_tp", tp_degree=world, steps=args.steps, tokens_per_second=batch * seq * args.steps / secs, ms_per_step=1e3 * secs / args.steps,
+    _emit(rank, config="gpt2l_tp", tp_degree=world, tp_scope=scope if world > 1 else "none", steps=args.steps, tokens_per_second=batch * seq * args.steps / secs, ms_per_step=1e3 * secs / args.steps,
           peak_allocated_gb=torch.cuda.max_memory_allocated(dev) / 1e9, wrapped_layers=len(layers), optimizer="torch.optim.AdamW",
           model="HF GPT2LMHeadModel from config; the reference's own tp_gpt2 module replacement and sync_replicated_grads")
 

@@ -92,3 +92,25 @@ def test_cta_pair_kernel_matches_fp32_reference(a_mn, b_mn, m, n, k, out_dtype):
     _lib.check_status()
     tol = 2e-2 if out_dtype == torch.bfloat16 else 2e-3
     assert float((got.float() - ref).abs().max() / ref.abs().max()) < tol
+
+
+@pytest.mark.parametrize("m,n,k", [(129, 72, 200), (257, 264, 136), (1000, 520, 328)])
+@pytest.mark.parametrize("two_cta", [False, True])
+def test_ragged_edge_tiles_elementwise(m, n, k, two_cta):
+    """Shapes that are no multiple of any tile: every element of the last partial row and column tiles is checked against
+    the fp32 product of the same bf16 operands (integers, so the fp32 result is exact and the comparison is elementwise)."""
+    from stacr_b200.ops import _lib
+    from stacr_b200.ops.gemm import gemm
+
+    if two_cta and (m < 512 or n < 512):
+        pytest.skip("the CTA-pair kernel takes shapes of at least 512 x 512")
+    g = torch.Generator(device="cuda").manual_seed(m + n + k)
+    a = torch.randint(-3, 4, (m, k), device="cuda", generator=g).bfloat16()
+    b = torch.randint(-3, 4, (n, k), device="cuda", generator=g).bfloat16()
+    ref = a.float() @ b.float().t()
+    out = gemm(a, b, out_dtype=torch.float32, two_cta=two_cta, bn=256 if two_cta else None)
+    torch.cuda.synchronize()
+    _lib.check_status()
+    assert torch.equal(out, ref)
+    edge_rows, edge_cols = m - m % 128, n - n % 128
+    assert torch.equal(out[edge_rows:], ref[edge_rows:]) and torch.equal(out[:, edge_cols:], ref[:, edge_cols:])
