@@ -7,8 +7,13 @@ from dataclasses import dataclass
 import torch
 from torch import nn
 
+import os
+
 from ..ops import nn_ops
 from .common import causal_attention, Embedding, GELU, init_weights, LayerNorm, Linear, lm_loss, ModelOutput
+
+
+_FUSED_NORMS = os.environ.get("STACR_FUSED_NORMS", "1") == "1"   # 0: the two norms and the residual sum as separate ops
 
 
 @dataclass
@@ -121,6 +126,14 @@ class NeoXLayer(nn.Module):
         self.drop = nn.Dropout(cfg.hidden_dropout)
 
     def forward(self, x, attention_mask=None):
+        ln1, ln2 = self.input_layernorm, self.post_attention_layernorm
+        hooked = ln1._forward_hooks or ln1._forward_pre_hooks or ln2._forward_hooks or ln2._forward_pre_hooks
+        if (self.parallel and not hooked and _FUSED_NORMS and ln1.eps == ln2.eps and type(ln1) is LayerNorm and type(ln2) is LayerNorm
+                and nn_ops.parallel_norms_supported(x, ln1.weight, ln1.bias, ln2.weight, ln2.bias)):
+            # both branches normalise the same x: one kernel forward, and one kernel backward for the three gradients
+            # (two branches + residual) that meet at x
+            h1, h2, skip = nn_ops.parallel_layer_norms(x, ln1.weight, ln1.bias, ln2.weight, ln2.bias, ln1.eps)
+            return nn_ops.add3(skip, self.drop(self.attention(h1, attention_mask)), self.drop(self.mlp(h2)))
         attn = self.drop(self.attention(self.input_layernorm(x), attention_mask))
         if self.parallel:  # x + attn(ln1(x)) + mlp(ln2(x))
             return x + attn + self.drop(self.mlp(self.post_attention_layernorm(x)))

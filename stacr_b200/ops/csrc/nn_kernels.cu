@@ -32,11 +32,15 @@ __device__ __forceinline__ float warp_max(float v) {
 
 // ---------------------------------------------------------------------------- LayerNorm
 // One warp per row; the row (n <= 16384, n % 8 == 0) lives in registers: MAXV vectors of 8 per lane.
+// With a second (gamma2, beta2, y2) the same statistics feed a second affine output: the two normalisations of a
+// parallel-residual block (attention and MLP branch read the same x) cost one read of x.
 template <int MAXV>
 __global__ void __launch_bounds__(256) layernorm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict__ gamma,
                                                             const float* __restrict__ beta, int rows, int n, float eps,
                                                             __nv_bfloat16* __restrict__ y, float* __restrict__ mean_out,
-                                                            float* __restrict__ rstd_out) {
+                                                            float* __restrict__ rstd_out, const float* __restrict__ gamma2 = nullptr,
+                                                            const float* __restrict__ beta2 = nullptr,
+                                                            __nv_bfloat16* __restrict__ y2 = nullptr) {
   const int lane = threadIdx.x & 31;
   const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (row >= rows) return;
@@ -86,6 +90,18 @@ __global__ void __launch_bounds__(256) layernorm_fwd_kernel(const __nv_bfloat16*
 #pragma unroll
       for (int j = 0; j < 8; ++j) o[j] = (v[i][j] - mean) * rstd * g[j] + b[j];
       yr[vi] = pack8(o);
+      if (y2) {
+        const float4 h0 = __ldg(reinterpret_cast<const float4*>(gamma2) + vi * 2), h1 = __ldg(reinterpret_cast<const float4*>(gamma2) + vi * 2 + 1);
+        const float g2[8] = {h0.x, h0.y, h0.z, h0.w, h1.x, h1.y, h1.z, h1.w};
+        float b2[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+        if (beta2) {
+          const float4 c0 = __ldg(reinterpret_cast<const float4*>(beta2) + vi * 2), c1 = __ldg(reinterpret_cast<const float4*>(beta2) + vi * 2 + 1);
+          b2[0] = c0.x; b2[1] = c0.y; b2[2] = c0.z; b2[3] = c0.w; b2[4] = c1.x; b2[5] = c1.y; b2[6] = c1.z; b2[7] = c1.w;
+        }
+#pragma unroll
+        for (int j = 0; j < 8; ++j) o[j] = (v[i][j] - mean) * rstd * g2[j] + b2[j];
+        reinterpret_cast<uint4*>(y2 + static_cast<size_t>(row) * n)[vi] = pack8(o);
+      }
     }
   }
 }
@@ -146,6 +162,97 @@ __global__ void __launch_bounds__(256) layernorm_bwd_dx_kernel(const __nv_bfloat
       for (int j = 0; j < 8; ++j) o[j] = rs * (dv[j] * g[j] - s1 - (xv[j] - mu) * rs * s2);
       dxr[vi] = pack8(o);
     }
+  }
+}
+
+// dx of two normalisations of the same x plus a residual gradient, in one pass:
+//   dx = LNbwd(dy1; gamma1) + LNbwd(dy2; gamma2) + res
+// (x + f(LN1(x)) + g(LN2(x)): the three gradient streams that meet at x).  One warp per row.
+template <int MAXV>
+__global__ void __launch_bounds__(256) layernorm_bwd_dx2_kernel(const __nv_bfloat16* __restrict__ dy1, const __nv_bfloat16* __restrict__ dy2,
+                                                                const __nv_bfloat16* __restrict__ res, const __nv_bfloat16* __restrict__ x,
+                                                                const float* __restrict__ gamma1, const float* __restrict__ gamma2,
+                                                                const float* __restrict__ mean, const float* __restrict__ rstd, int rows, int n,
+                                                                __nv_bfloat16* __restrict__ dx) {
+  const int lane = threadIdx.x & 31;
+  const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (row >= rows) return;
+  const int nvec = n >> 3;
+  const size_t off = static_cast<size_t>(row) * n;
+  const uint4* xr = reinterpret_cast<const uint4*>(x + off);
+  const uint4* d1 = reinterpret_cast<const uint4*>(dy1 + off);
+  const uint4* d2 = reinterpret_cast<const uint4*>(dy2 + off);
+  const float mu = mean[row], rs = rstd[row];
+  uint4 xraw[MAXV], raw1[MAXV], raw2[MAXV];
+  float a1 = 0.f, a2 = 0.f, b1 = 0.f, b2 = 0.f;
+#pragma unroll
+  for (int i = 0; i < MAXV; ++i) {
+    const int vi = lane + i * 32;
+    if (vi < nvec) {
+      xraw[i] = __ldg(xr + vi);
+      raw1[i] = __ldg(d1 + vi);
+      raw2[i] = __ldg(d2 + vi);
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < MAXV; ++i) {
+    const int vi = lane + i * 32;
+    if (vi < nvec) {
+      float xv[8], u[8], w[8];
+      unpack8(xraw[i], xv);
+      unpack8(raw1[i], u);
+      unpack8(raw2[i], w);
+      const float4 g0 = __ldg(reinterpret_cast<const float4*>(gamma1) + vi * 2), g1 = __ldg(reinterpret_cast<const float4*>(gamma1) + vi * 2 + 1);
+      const float4 h0 = __ldg(reinterpret_cast<const float4*>(gamma2) + vi * 2), h1 = __ldg(reinterpret_cast<const float4*>(gamma2) + vi * 2 + 1);
+      const float g[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w};
+      const float h[8] = {h0.x, h0.y, h0.z, h0.w, h1.x, h1.y, h1.z, h1.w};
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const float xh = (xv[j] - mu) * rs;
+        const float p = u[j] * g[j], q = w[j] * h[j];
+        a1 += p;
+        a2 = fmaf(p, xh, a2);
+        b1 += q;
+        b2 = fmaf(q, xh, b2);
+      }
+    }
+  }
+  // the two backward formulas are linear in (sum, sum * xhat): add the moments of both branches
+  const float s1 = (warp_sum(a1) + warp_sum(b1)) / n;
+  const float s2 = (warp_sum(a2) + warp_sum(b2)) / n;
+  uint4* dxr = reinterpret_cast<uint4*>(dx + off);
+  const uint4* rr = res ? reinterpret_cast<const uint4*>(res + off) : nullptr;
+#pragma unroll
+  for (int i = 0; i < MAXV; ++i) {
+    const int vi = lane + i * 32;
+    if (vi < nvec) {
+      float xv[8], u[8], w[8], o[8], r[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+      unpack8(xraw[i], xv);
+      unpack8(raw1[i], u);
+      unpack8(raw2[i], w);
+      if (rr) unpack8(__ldg(rr + vi), r);
+      const float4 g0 = __ldg(reinterpret_cast<const float4*>(gamma1) + vi * 2), g1 = __ldg(reinterpret_cast<const float4*>(gamma1) + vi * 2 + 1);
+      const float4 h0 = __ldg(reinterpret_cast<const float4*>(gamma2) + vi * 2), h1 = __ldg(reinterpret_cast<const float4*>(gamma2) + vi * 2 + 1);
+      const float g[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w};
+      const float h[8] = {h0.x, h0.y, h0.z, h0.w, h1.x, h1.y, h1.z, h1.w};
+#pragma unroll
+      for (int j = 0; j < 8; ++j) o[j] = fmaf(rs, u[j] * g[j] + w[j] * h[j] - s1 - (xv[j] - mu) * rs * s2, r[j]);
+      dxr[vi] = pack8(o);
+    }
+  }
+}
+
+// out = a + b + c on contiguous bf16 (numel % 8 == 0): the residual sum of a parallel block in one pass.
+__global__ void __launch_bounds__(256) add3_kernel(const uint4* __restrict__ a, const uint4* __restrict__ b, const uint4* __restrict__ c,
+                                                   uint4* __restrict__ out, size_t nvec) {
+  for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < nvec; i += static_cast<size_t>(gridDim.x) * blockDim.x) {
+    float x[8], y[8], z[8];
+    unpack8(__ldg(a + i), x);
+    unpack8(__ldg(b + i), y);
+    unpack8(__ldg(c + i), z);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) x[j] = x[j] + y[j] + z[j];
+    out[i] = pack8(x);
   }
 }
 
@@ -531,11 +638,38 @@ static int ln_fwd_launch(const void* x, const float* g, const float* b, int rows
   return static_cast<int>(cudaGetLastError());
 }
 template <int MAXV>
+static int ln_fwd2_launch(const void* x, const float* g1, const float* b1, const float* g2, const float* b2, int rows, int n, float eps, void* y1,
+                          void* y2, float* mean, float* rstd, cudaStream_t st) {
+  const int wpb = 8;
+  layernorm_fwd_kernel<MAXV><<<(rows + wpb - 1) / wpb, wpb * 32, 0, st>>>(static_cast<const __nv_bfloat16*>(x), g1, b1, rows, n, eps,
+                                                                          static_cast<__nv_bfloat16*>(y1), mean, rstd, g2, b2,
+                                                                          static_cast<__nv_bfloat16*>(y2));
+  return static_cast<int>(cudaGetLastError());
+}
+static void ln_params_launch(const void* dy, const void* x, const float* mean, const float* rstd, int rows, int n, float* dg, float* db, int sms,
+                             cudaStream_t st);
+template <int MAXV>
+static int ln_bwd2_launch(const void* dy1, const void* dy2, const void* res, const void* x, const float* g1, const float* g2, const float* mean,
+                          const float* rstd, int rows, int n, void* dx, float* dg1, float* db1, float* dg2, float* db2, int sms, cudaStream_t st) {
+  const int wpb = 8;
+  layernorm_bwd_dx2_kernel<MAXV><<<(rows + wpb - 1) / wpb, wpb * 32, 0, st>>>(
+      static_cast<const __nv_bfloat16*>(dy1), static_cast<const __nv_bfloat16*>(dy2), static_cast<const __nv_bfloat16*>(res),
+      static_cast<const __nv_bfloat16*>(x), g1, g2, mean, rstd, rows, n, static_cast<__nv_bfloat16*>(dx));
+  ln_params_launch(dy1, x, mean, rstd, rows, n, dg1, db1, sms, st);
+  ln_params_launch(dy2, x, mean, rstd, rows, n, dg2, db2, sms, st);
+  return static_cast<int>(cudaGetLastError());
+}
+template <int MAXV>
 static int ln_bwd_launch(const void* dy, const void* x, const float* g, const float* mean, const float* rstd, int rows, int n, void* dx,
                          float* dg, float* db, int sms, cudaStream_t st) {
   const int wpb = 8;
   layernorm_bwd_dx_kernel<MAXV><<<(rows + wpb - 1) / wpb, wpb * 32, 0, st>>>(
       static_cast<const __nv_bfloat16*>(dy), static_cast<const __nv_bfloat16*>(x), g, mean, rstd, rows, n, static_cast<__nv_bfloat16*>(dx));
+  ln_params_launch(dy, x, mean, rstd, rows, n, dg, db, sms, st);
+  return static_cast<int>(cudaGetLastError());
+}
+static void ln_params_launch(const void* dy, const void* x, const float* mean, const float* rstd, int rows, int n, float* dg, float* db, int sms,
+                             cudaStream_t st) {
   const int colblocks = (n + 63) / 64;
   int slabs = (sms * 4 + colblocks - 1) / colblocks;
   if (slabs < 1) slabs = 1;
@@ -544,7 +678,6 @@ static int ln_bwd_launch(const void* dy, const void* x, const float* g, const fl
   dim3 grid(colblocks, (rows + slab - 1) / slab);
   layernorm_bwd_params_kernel<<<grid, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(dy), static_cast<const __nv_bfloat16*>(x), mean, rstd,
                                                     rows, n, slab, dg, db);
-  return static_cast<int>(cudaGetLastError());
 }
 
 }  // namespace sb
@@ -575,6 +708,45 @@ extern "C" int sb_layernorm_bwd(const void* dy, const void* x, const float* gamm
   if (nv <= 8) return ln_bwd_launch<8>(dy, x, gamma, mean, rstd, rows, n, dx, dgamma, dbeta, sms, st);
   if (nv <= 16) return ln_bwd_launch<16>(dy, x, gamma, mean, rstd, rows, n, dx, dgamma, dbeta, sms, st);
   return -3;
+}
+
+// Two affine outputs of one normalisation (see layernorm_fwd_kernel).
+extern "C" int sb_layernorm_fwd2(const void* x, const float* gamma1, const float* beta1, const float* gamma2, const float* beta2, int rows, int n,
+                                 float eps, void* y1, void* y2, float* mean, float* rstd, void* stream) {
+  using namespace sb;
+  if (rows <= 0) return 0;
+  if (n % 8 || n > 4096) return -2;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int nv = (n / 8 + 31) / 32;
+  if (nv <= 4) return ln_fwd2_launch<4>(x, gamma1, beta1, gamma2, beta2, rows, n, eps, y1, y2, mean, rstd, st);
+  if (nv <= 8) return ln_fwd2_launch<8>(x, gamma1, beta1, gamma2, beta2, rows, n, eps, y1, y2, mean, rstd, st);
+  if (nv <= 16) return ln_fwd2_launch<16>(x, gamma1, beta1, gamma2, beta2, rows, n, eps, y1, y2, mean, rstd, st);
+  return -3;
+}
+
+// dx = LNbwd(dy1) + LNbwd(dy2) + res (res may be null); the four parameter gradients are fp32 [n], zeroed by the caller.
+extern "C" int sb_layernorm_bwd2(const void* dy1, const void* dy2, const void* res, const void* x, const float* gamma1, const float* gamma2,
+                                 const float* mean, const float* rstd, int rows, int n, void* dx, float* dgamma1, float* dbeta1, float* dgamma2,
+                                 float* dbeta2, int sms, void* stream) {
+  using namespace sb;
+  if (rows <= 0) return 0;
+  if (n % 8 || n > 4096) return -2;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int nv = (n / 8 + 31) / 32;
+  if (nv <= 4) return ln_bwd2_launch<4>(dy1, dy2, res, x, gamma1, gamma2, mean, rstd, rows, n, dx, dgamma1, dbeta1, dgamma2, dbeta2, sms, st);
+  if (nv <= 8) return ln_bwd2_launch<8>(dy1, dy2, res, x, gamma1, gamma2, mean, rstd, rows, n, dx, dgamma1, dbeta1, dgamma2, dbeta2, sms, st);
+  return -3;
+}
+
+extern "C" int sb_add3(const void* a, const void* b, const void* c, void* out, long long numel, int sms, void* stream) {
+  if (numel <= 0) return 0;
+  if (numel % 8) return -2;
+  const size_t nvec = static_cast<size_t>(numel / 8);
+  size_t blocks = (nvec + 255) / 256;
+  if (blocks > static_cast<size_t>(sms) * 16) blocks = static_cast<size_t>(sms) * 16;
+  sb::add3_kernel<<<static_cast<unsigned>(blocks), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const uint4*>(a), static_cast<const uint4*>(b), static_cast<const uint4*>(c), static_cast<uint4*>(out), nvec);
+  return static_cast<int>(cudaGetLastError());
 }
 
 static inline unsigned gelu_blocks(size_t nvec, int sms) {

@@ -86,28 +86,17 @@ __global__ void __launch_bounds__(256) adamw_fp32_kernel(const TensorDesc* __res
   }
 }
 
-__device__ __forceinline__ float decode_m(unsigned char c, float amax) {
-  const float s = (static_cast<float>(c) - 128.f) * (1.f / 127.f);
-  return copysignf(s * s, s) * amax;
-}
-// The encoders take 1 / absmax (0 when the block is all zero), computed once per quantisation block.
-__device__ __forceinline__ unsigned char encode_m(float m, float inv_amax) {
-  if (inv_amax <= 0.f) return 128;
-  const float s = sqrtf(fminf(fabsf(m) * inv_amax, 1.f));
-  return static_cast<unsigned char>(128.f + rintf(copysignf(s, m) * 127.f));
-}
-__device__ __forceinline__ float decode_v(unsigned char c, float amax) {
-  const float s = static_cast<float>(c) * (1.f / 255.f);
-  return s * s * s * s * amax;
-}
-__device__ __forceinline__ unsigned char encode_v(float v, float inv_amax) {
-  if (inv_amax <= 0.f) return 0;
-  return static_cast<unsigned char>(rintf(sqrtf(sqrtf(fminf(v * inv_amax, 1.f))) * 255.f));
-}
+// 8-bit code <-> float through the mantissa: 0x4B0000cc is 2^23 + c exactly, and adding 1.5 * 2^23 to a value in [0, 2^22)
+// rounds it to nearest-even into the low mantissa bits (what rintf + a conversion would give).
+__device__ __forceinline__ float byte_to_float(unsigned char c) { return __uint_as_float(0x4B000000u | c) - 8388608.f; }
+__device__ __forceinline__ unsigned char float_to_byte(float x) { return static_cast<unsigned char>(__float_as_uint(x + 12582912.f) & 0xFFu); }
+
+// Code formats: m -> 128 + round(127 * sign(m) * sqrt(|m| / absmax)), v -> round(255 * (v / absmax)^(1/4)), one absmax pair per
+// 256-element block.
 
 // One warp = one 256-element quantisation block (8 consecutive elements per lane, 16-byte
 // loads/stores, absmax by warp shuffles only); one CTA of 8 warps = one 2048-element chunk.
-__global__ void __launch_bounds__(256) adamw_8bit_kernel(const TensorDesc* __restrict__ tensors, const ChunkDesc* __restrict__ chunks,
+__global__ void __launch_bounds__(256, 4) adamw_8bit_kernel(const TensorDesc* __restrict__ tensors, const ChunkDesc* __restrict__ chunks,
                                                          AdamArgs a0, const float* __restrict__ hyper) {
   const AdamArgs a = resolve_args(a0, hyper);
   const ChunkDesc c = chunks[blockIdx.x];
@@ -151,43 +140,51 @@ __global__ void __launch_bounds__(256) adamw_8bit_kernel(const TensorDesc* __res
       }
     }
   }
+  // The special-function pipe (conversions, roots, reciprocals: 16 per clock per SM) is as scarce here as DRAM bandwidth, so
+  // the 8-bit path spends four of its operations per element instead of nine: codes become floats and back through the
+  // mantissa (no int<->float conversion), sqrt(v) is shared by the update and the encoder, and the encoders' divisions by the
+  // block maximum are one rsqrt per block.
   if (q8) {
-    const float am_old = t.m_absmax[qb], av_old = t.v_absmax[qb];
+    const float sm = t.m_absmax[qb] * (1.f / (127.f * 127.f)), sv = t.v_absmax[qb] * (1.f / (255.f * 255.f * 255.f * 255.f));
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
-      m[j] = decode_m(cm[j], am_old);
-      v[j] = decode_v(cv[j], av_old);
+      const float cf = byte_to_float(cm[j]) - 128.f;
+      m[j] = cf * fabsf(cf) * sm;                       // sign(c) * (|c| / 127)^2 * absmax
+      const float vf = byte_to_float(cv[j]);
+      const float v2 = vf * vf;
+      v[j] = v2 * v2 * sv;                              // (c / 255)^4 * absmax
     }
   }
-  float am = 0.f, av = 0.f;
-  const float inv_b1 = 1.f / a.bias1, inv_b2 = 1.f / a.bias2, decay = 1.f - a.lr * a.weight_decay;
+  float am = 0.f, rmax = 0.f, r[8];
+  const float inv_b1 = 1.f / a.bias1, rs_b2 = rsqrtf(a.bias2), decay = 1.f - a.lr * a.weight_decay;
   const float step1 = a.lr * inv_b1;  // one reciprocal per element instead of three divisions
 #pragma unroll
   for (int j = 0; j < 8; ++j) {
     const float gj = g[j] * a.grad_scale;
     m[j] = a.beta1 * m[j] + (1.f - a.beta1) * gj;
     v[j] = a.beta2 * v[j] + (1.f - a.beta2) * gj * gj;
-    p[j] = p[j] * decay - step1 * m[j] * __frcp_rn(sqrtf(v[j] * inv_b2) + a.eps);
+    r[j] = sqrtf(v[j]);
+    p[j] = p[j] * decay - step1 * m[j] * __frcp_rn(fmaf(r[j], rs_b2, a.eps));
     if (i0 + j < t.numel) {
       am = fmaxf(am, fabsf(m[j]));
-      av = fmaxf(av, v[j]);
+      rmax = fmaxf(rmax, r[j]);
     }
   }
   if (q8) {
 #pragma unroll
     for (int off = 16; off; off >>= 1) {
       am = fmaxf(am, __shfl_xor_sync(0xffffffffu, am, off));
-      av = fmaxf(av, __shfl_xor_sync(0xffffffffu, av, off));
+      rmax = fmaxf(rmax, __shfl_xor_sync(0xffffffffu, rmax, off));
     }
-    const float inv_am = am > 0.f ? 1.f / am : 0.f, inv_av = av > 0.f ? 1.f / av : 0.f;
+    const float rs_am = am > 0.f ? rsqrtf(am) * 127.f : 0.f, rs_r = rmax > 0.f ? rsqrtf(rmax) * 255.f : 0.f;
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
-      cm[j] = encode_m(m[j], inv_am);
-      cv[j] = encode_v(v[j], inv_av);
+      cm[j] = float_to_byte(128.f + copysignf(fminf(sqrtf(fabsf(m[j])) * rs_am, 127.f), m[j]));   // sqrt(|m| / absmax)
+      cv[j] = float_to_byte(fminf(sqrtf(r[j]) * rs_r, 255.f));                                    // (v / absmax)^(1/4)
     }
     if (lane == 0) {
       t.m_absmax[qb] = am;
-      t.v_absmax[qb] = av;
+      t.v_absmax[qb] = rmax * rmax;
     }
   }
   if (vec) {

@@ -39,6 +39,40 @@ def layernorm_bwd(dy2d, x2d, weight, mean, rstd):
     return dx, dwb[0], dwb[1]
 
 
+def layernorm_fwd2(x2d: torch.Tensor, w1, b1, w2, b2, eps: float):
+    """Two affine outputs of one normalisation of ``x2d`` (one read of the input, shared statistics)."""
+    rows, n = x2d.shape
+    y1, y2 = torch.empty_like(x2d), torch.empty_like(x2d)
+    mean = torch.empty(rows, dtype=torch.float32, device=x2d.device)
+    rstd = torch.empty(rows, dtype=torch.float32, device=x2d.device)
+    rc = _lib.load().sb_layernorm_fwd2(_lib.ptr(x2d), _lib.ptr(_f32(w1)), _lib.ptr(_f32(b1)), _lib.ptr(_f32(w2)), _lib.ptr(_f32(b2)), c_int(rows),
+                                       c_int(n), c_float(eps), _lib.ptr(y1), _lib.ptr(y2), _lib.ptr(mean), _lib.ptr(rstd), _lib.stream_ptr())
+    _lib.check_rc(rc, "sb_layernorm_fwd2")
+    _lib.count(1)
+    return y1, y2, mean, rstd
+
+
+def layernorm_bwd2(dy1, dy2, res, x2d, w1, w2, mean, rstd):
+    """``dx = LNbwd(dy1; w1) + LNbwd(dy2; w2) + res`` in one pass, plus the four parameter gradients (fp32)."""
+    rows, n = x2d.shape
+    dx = torch.empty_like(x2d)
+    grads = torch.zeros(4, n, dtype=torch.float32, device=x2d.device)
+    rc = _lib.load().sb_layernorm_bwd2(_lib.ptr(dy1), _lib.ptr(dy2), _lib.ptr(res), _lib.ptr(x2d), _lib.ptr(_f32(w1)), _lib.ptr(_f32(w2)),
+                                       _lib.ptr(mean), _lib.ptr(rstd), c_int(rows), c_int(n), _lib.ptr(dx), _lib.ptr(grads[0]), _lib.ptr(grads[1]),
+                                       _lib.ptr(grads[2]), _lib.ptr(grads[3]), c_int(_lib.sm_count(x2d.device)), _lib.stream_ptr())
+    _lib.check_rc(rc, "sb_layernorm_bwd2")
+    _lib.count(3)
+    return dx, grads[0], grads[1], grads[2], grads[3]
+
+
+def add3(a: torch.Tensor, b: torch.Tensor, c: torch.Tensor) -> torch.Tensor:
+    out = torch.empty_like(a)
+    rc = _lib.load().sb_add3(_lib.ptr(a), _lib.ptr(b), _lib.ptr(c), _lib.ptr(out), c_ll(a.numel()), c_int(_lib.sm_count(a.device)), _lib.stream_ptr())
+    _lib.check_rc(rc, "sb_add3")
+    _lib.count(1)
+    return out
+
+
 def gelu_fwd(x: torch.Tensor, tanh_form: bool) -> torch.Tensor:
     y = torch.empty_like(x)
     rc = _lib.load().sb_gelu_fwd(_lib.ptr(x), _lib.ptr(y), c_ll(x.numel()), c_int(int(tanh_form)), c_int(_lib.sm_count(x.device)),

@@ -46,6 +46,71 @@ def layer_norm(x, weight, bias, eps: float = 1e-5):
     return F.layer_norm(x, (x.shape[-1],), weight, bias, eps)
 
 
+class _ParallelNormsFn(torch.autograd.Function):
+    """``(LN1(x), LN2(x), x)`` for a parallel-residual block ``x + f(LN1(x)) + g(LN2(x))``.
+
+    Forward reads ``x`` once for both normalisations.  The third output is ``x`` itself, handed on to the residual sum,
+    so that all three gradient streams that meet at ``x`` arrive in this function's backward, which forms
+    ``LNbwd(g1) + LNbwd(g2) + g3`` in one kernel instead of two normalisation backwards and two accumulating adds.
+    """
+
+    @staticmethod
+    def forward(ctx, x, w1, b1, w2, b2, eps):
+        from . import nn_kernels
+
+        x2d = x.reshape(-1, x.shape[-1]).contiguous()
+        y1, y2, mean, rstd = nn_kernels.layernorm_fwd2(x2d, w1, b1, w2, b2, eps)
+        ctx.save_for_backward(x2d, w1, w2, mean, rstd)
+        ctx.x_shape = x.shape
+        return y1.reshape(x.shape), y2.reshape(x.shape), x.view_as(x)
+
+    @staticmethod
+    def backward(ctx, g1, g2, g3):
+        from . import nn_kernels
+
+        x2d, w1, w2, mean, rstd = ctx.saved_tensors
+
+        def flat(g):
+            return None if g is None else g.reshape(x2d.shape).to(torch.bfloat16).contiguous()
+
+        g1, g2, g3 = flat(g1), flat(g2), flat(g3)
+        if g1 is None:
+            g1 = torch.zeros_like(x2d)
+        if g2 is None:
+            g2 = torch.zeros_like(x2d)
+        dx, dw1, db1, dw2, db2 = nn_kernels.layernorm_bwd2(g1, g2, g3, x2d, w1, w2, mean, rstd)
+        return dx.reshape(ctx.x_shape), dw1.to(w1.dtype), db1.to(w1.dtype), dw2.to(w2.dtype), db2.to(w2.dtype), None
+
+
+def parallel_norms_supported(x, w1, b1, w2, b2) -> bool:
+    return (_kernel_tensor(x) and x.shape[-1] % 8 == 0 and x.shape[-1] <= 2048 and b1 is not None and b2 is not None
+            and w1.shape == w2.shape)
+
+
+def parallel_layer_norms(x, w1, b1, w2, b2, eps: float = 1e-5):
+    """``(LN(x; w1, b1), LN(x; w2, b2), x)``: use the third result as the residual operand (see ``_ParallelNormsFn``)."""
+    return _ParallelNormsFn.apply(x, w1, b1, w2, b2, eps)
+
+
+class _Add3Fn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, a, b, c):
+        from . import nn_kernels
+
+        return nn_kernels.add3(a.contiguous(), b.contiguous(), c.contiguous())
+
+    @staticmethod
+    def backward(ctx, g):
+        return g, g, g
+
+
+def add3(a, b, c):
+    """``a + b + c`` in one pass for bf16 CUDA tensors of one shape."""
+    if _kernel_tensor(a) and a.shape == b.shape == c.shape and b.dtype == c.dtype == a.dtype and a.numel() % 8 == 0:
+        return _Add3Fn.apply(a, b, c)
+    return a + b + c
+
+
 # ------------------------------------------------------------------------------ column sums handed from producer to consumer
 class _ColumnSums:
     """Column sums of a gradient matrix that some kernel produced as a by-product, offered to whoever needs them next.

@@ -236,3 +236,60 @@ def test_plain_linear_writes_fp32_weight_gradient_and_uses_a_lent_slot():
     torch.testing.assert_close(lin.weight.grad, 2 * exact, rtol=2e-3, atol=4e-3 * float(exact.abs().max()))
     # fp32 inputs outside autocast and tiny heads keep the stock path
     assert "_LinearFn" not in type(lin(x.detach().reshape(-1, 264)).grad_fn).__name__
+
+
+@pytest.mark.parametrize("rows,n", [(1000, 776), (4096, 2048), (37, 256)])
+def test_parallel_block_norms_match_two_layer_norms_and_a_residual(rows, n):
+    """(LN1(x), LN2(x), x) from one kernel, and one backward kernel for the three gradients that meet at x."""
+    from stacr_b200.ops import _lib, nn_ops
+
+    g = torch.Generator(device="cuda").manual_seed(rows + n)
+    x = torch.randn(rows, n, device="cuda", generator=g).bfloat16().requires_grad_(True)
+    params = [torch.randn(n, device="cuda", generator=g).requires_grad_(True) for _ in range(4)]
+    up = [torch.randn(rows, n, device="cuda", generator=g).bfloat16() for _ in range(3)]
+    assert nn_ops.parallel_norms_supported(x, *params)
+    y1, y2, skip = nn_ops.parallel_layer_norms(x, *params, 1e-5)
+    out = nn_ops.add3(skip * 1.0, y1, y2)
+    (y1.float() * up[0].float()).sum().backward(retain_graph=True)
+    (y2.float() * up[1].float()).sum().backward(retain_graph=True)
+    (skip.float() * up[2].float()).sum().backward()
+    torch.cuda.synchronize()
+    _lib.check_status()
+    got = [x.grad.float().clone()] + [p.grad.clone() for p in params]
+    xr = x.detach().float().requires_grad_(True)
+    pr = [p.detach().clone().requires_grad_(True) for p in params]
+    r1 = torch.nn.functional.layer_norm(xr, (n,), pr[0], pr[1], 1e-5)
+    r2 = torch.nn.functional.layer_norm(xr, (n,), pr[2], pr[3], 1e-5)
+    ((r1 * up[0].float()).sum() + (r2 * up[1].float()).sum() + (xr * up[2].float()).sum()).backward()
+    assert float((y1.float() - r1).abs().max()) < 5e-2 and float((y2.float() - r2).abs().max()) < 5e-2
+    assert torch.equal(skip, x)
+    torch.testing.assert_close(out.float(), (x.float() + y1.float() + y2.float()), rtol=2e-2, atol=5e-2)
+    scale = float(xr.grad.abs().max())
+    assert float((got[0] - xr.grad).abs().max()) < 2e-2 * scale + 2e-2
+    for mine, ref in zip(got[1:], pr):
+        torch.testing.assert_close(mine, ref.grad, rtol=2e-2, atol=2e-2 * float(ref.grad.abs().max()))
+
+
+def test_neox_layer_with_fused_norms_matches_the_unfused_layer():
+    from stacr_b200.models.neox import NeoXConfig, NeoXLayer
+
+    torch.manual_seed(3)
+    cfg = NeoXConfig(vocab_size=128, hidden_size=256, num_hidden_layers=1, num_attention_heads=4, intermediate_size=512, max_position_embeddings=64)
+    layer = NeoXLayer(cfg).cuda().train()
+    x = torch.randn(2, 64, 256, device="cuda").bfloat16()
+    xa, xb = x.clone().requires_grad_(True), x.clone().requires_grad_(True)
+    with torch.autocast("cuda", dtype=torch.bfloat16):
+        fused = layer(xa)
+        handle = layer.input_layernorm.register_forward_hook(lambda m, i, o: None)     # a hooked norm keeps the module-by-module route
+        plain = layer(xb)
+        handle.remove()
+    up = torch.randn_like(fused)
+    fused.backward(up)
+    grads_fused = {n: p.grad.clone() for n, p in layer.named_parameters()}
+    layer.zero_grad(set_to_none=True)
+    plain.backward(up)
+    torch.testing.assert_close(fused.float(), plain.float(), rtol=3e-2, atol=3e-2)
+    torch.testing.assert_close(xa.grad.float(), xb.grad.float(), rtol=5e-2, atol=5e-2)
+    for n, p in layer.named_parameters():
+        ref = p.grad.float()
+        assert float((grads_fused[n].float() - ref).abs().max()) <= 5e-2 * float(ref.abs().max()) + 1e-3, n
