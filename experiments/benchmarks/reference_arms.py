@@ -130,6 +130,19 @@ def run_gpt2l_tp(args, ref, torch, dist, rank, world, dev):
 
 
 def run_bert_adaptive_composed(args, ref, torch, dist, rank, world, dev):
+    """bf16 autocast as configured; if the reference's adaptive engine cannot run in bf16 on this torch (its sparse residual
+    product has no bf16 CUDA kernel), the same configuration is timed in fp32 and the line says so."""
+    try:
+        _bert_adaptive_composed(args, ref, torch, dist, rank, world, dev, "bf16")
+    except (NotImplementedError, RuntimeError) as exc:
+        _emit(rank, config="bert_adaptive_composed", amp="bf16", unavailable=f"{type(exc).__name__}: {str(exc)[:200]}")
+        torch.cuda.empty_cache()
+        _bert_adaptive_composed(args, ref, torch, dist, rank, world, dev, "fp32")
+
+
+def _bert_adaptive_composed(args, ref, torch, dist, rank, world, dev, amp):
+    import contextlib
+
     from stacr.training import configure_model
     from torch.nn.parallel import DistributedDataParallel as DDP
     from transformers import BertConfig, BertForSequenceClassification
@@ -140,7 +153,7 @@ def run_bert_adaptive_composed(args, ref, torch, dist, rank, world, dev):
     model = BertForSequenceClassification(cfg).to(dev).train()
     run_cfg = {
         "task": "sequence_classification", "method": "stacr_checkpointing", "engine": "adaptive", "model_name": "bert-base-uncased",
-        "seq_len": seq, "batch_size": batch, "steps": 100, "lr": 2.0e-5, "amp": "bf16", "rank": 32, "residual_budget": 0.005,
+        "seq_len": seq, "batch_size": batch, "steps": 100, "lr": 2.0e-5, "amp": amp if amp == "bf16" else "none", "rank": 32, "residual_budget": 0.005,
         "checkpoint_every": 2, "offload_every": 2, "offload_offset": 1,
         "compression": {"quantize_coefficients": True, "rank_mode": "sensitivity", "rank_min": 4, "rank_max": 32, "refresh_trigger": "residual_energy",
                         "residual_mode": "topk"},
@@ -158,7 +171,7 @@ def run_bert_adaptive_composed(args, ref, torch, dist, rank, world, dev):
         ids, labels = data[state["step"] % len(data)]
         state["step"] += 1
         opt.zero_grad(set_to_none=True)
-        with torch.autocast("cuda", dtype=torch.bfloat16):
+        with (torch.autocast("cuda", dtype=torch.bfloat16) if amp == "bf16" else contextlib.nullcontext()):
             net(input_ids=ids, attention_mask=torch.ones_like(ids), labels=labels).loss.backward()
         opt.step()
 
@@ -166,7 +179,7 @@ def run_bert_adaptive_composed(args, ref, torch, dist, rank, world, dev):
         step(0)
     torch.cuda.reset_peak_memory_stats(dev)
     secs = _timed(torch, dist, args.steps, step, world)
-    _emit(rank, config="bert_adaptive_composed", n_gpus=world, steps=args.steps, tokens_per_second=world * batch * seq * args.steps / secs,
+    _emit(rank, config="bert_adaptive_composed", amp=amp, n_gpus=world, steps=args.steps, tokens_per_second=world * batch * seq * args.steps / secs,
           ms_per_step=1e3 * secs / args.steps, peak_allocated_gb=torch.cuda.max_memory_allocated(dev) / 1e9, wrapped_layers=len(layers),
           checkpointed_blocks=info["checkpointed_blocks"], offloaded_blocks=info["offloaded_blocks"], optimizer="torch.optim.AdamW",
           model="HF BertForSequenceClassification from config; the reference's own configure_model (adaptive engine, checkpoint + offload)")

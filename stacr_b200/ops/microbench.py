@@ -3,6 +3,7 @@
     python -m stacr_b200.ops.microbench gemm   [--m 8192 --n 8192 --k 2048 --bn 256 --iters 20]
     python -m stacr_b200.ops.microbench stacr  [--rows 8192 --features 8192 --out 2048 --rank 8]
     python -m stacr_b200.ops.microbench optim  [--numel 268435456]
+    python -m stacr_b200.ops.microbench attention [--batch 4 --heads 16 --seq 2048 --head-dim 128]
 
 Each case runs warm-up launches, then ``--iters`` timed launches between CUDA events; operands are larger than the
 126 MB L2 at the default sizes (the ``stacr`` and ``optim`` cases stream several hundred MB per launch; the default
@@ -128,9 +129,33 @@ def case_optim(args, pk) -> list:
              f"frac_of_{pk['source']}_hbm": moved / ms / 1e6 / pk["hbm_gbs"]}]
 
 
+def case_attention(args, pk) -> list:
+    """The in-tree flash-attention forward against the library kernel on views of a fused, per-head interleaved QKV matrix."""
+    import torch.nn.functional as F
+
+    from . import attention
+
+    b, h, s, d = args.batch, args.heads, args.seq, args.head_dim
+    qkv = torch.randn(b * s, h * 3 * d, device="cuda").bfloat16()
+    q, k, v = (t.transpose(1, 2) for t in qkv.view(b, s, h, 3 * d).split(d, dim=-1))
+    causal = not args.full
+    flops = 4.0 * b * h * s * s * d * (0.5 if causal else 1.0)
+    rows = []
+    ms = timed(lambda: attention.forward(q, k, v, causal=causal), args.iters, args.warmup)
+    rows.append({"kernel": "flash_fwd_kernel (in-tree)", "shape": [b, h, s, d], "causal": causal, "ms": ms, "TFLOPs": flops / ms / 1e9,
+                 f"frac_of_{pk['source']}_bf16": flops / ms / 1e9 / pk["bf16_tflops"]})
+    if not args.only_ours:
+        ms = timed(lambda: F.scaled_dot_product_attention(q, k, v, is_causal=causal), args.iters, args.warmup)
+        rows.append({"kernel": "scaled_dot_product_attention (library)", "shape": [b, h, s, d], "causal": causal, "ms": ms, "TFLOPs": flops / ms / 1e9})
+        mine, _ = attention.forward(q, k, v, causal=causal)
+        ref = F.scaled_dot_product_attention(q, k, v, is_causal=causal).transpose(1, 2).reshape(b, s, h * d)
+        rows[0]["max_abs_diff_vs_library"] = float((mine.float() - ref.float()).abs().max())
+    return rows
+
+
 def main(argv=None) -> int:
     parser = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
-    parser.add_argument("case", choices=("gemm", "stacr", "optim"))
+    parser.add_argument("case", choices=("gemm", "stacr", "optim", "attention"))
     parser.add_argument("--iters", type=int, default=20)
     parser.add_argument("--warmup", type=int, default=5)
     parser.add_argument("--m", type=int, default=8192)
@@ -146,11 +171,16 @@ def main(argv=None) -> int:
     parser.add_argument("--budget", type=float, default=0.005)
     parser.add_argument("--only", choices=("project", "topk", "oja", "dw", "gelu"))
     parser.add_argument("--numel", type=int, default=1 << 28)
+    parser.add_argument("--batch", type=int, default=4)
+    parser.add_argument("--heads", type=int, default=16)
+    parser.add_argument("--seq", type=int, default=2048)
+    parser.add_argument("--head-dim", type=int, default=128)
+    parser.add_argument("--full", action="store_true", help="attention case: no causal mask")
     args = parser.parse_args(argv)
     from . import _lib
 
     pk = peaks()
-    rows = {"gemm": case_gemm, "stacr": case_stacr, "optim": case_optim}[args.case](args, pk)
+    rows = {"gemm": case_gemm, "stacr": case_stacr, "optim": case_optim, "attention": case_attention}[args.case](args, pk)
     _lib.check_status()
     for row in rows:
         print(json.dumps(row))
