@@ -251,7 +251,22 @@ def _select_residual_kernels(x, coeff, qb, budget, chunk_rows, mode, block_size,
             blocks = torch.cat([energy[lo:hi].reshape(-1).topk(c, sorted=False).indices + lo * per_row for (lo, hi), c in zip(bounds, counts)])
         idx = (blocks[:, None] * block_size + torch.arange(block_size, device=x.device)).reshape(-1).to(idt)
         return idx, quantize_values(stacr_ops.residual_gather(x, coeff, qb, idx), bits)
-    # sampled (a control selector whose dense workspace is part of its definition) and odd block sizes
+    if mode == "sampled" and feats % 8 == 0:
+        # the same selector without the dense residual: the probe is a gather of residual values at the random positions, the cut
+        # is the probe's quantile, and one pass over X lists the entries at or above the cut; the first k_total of them in index
+        # order are kept, as in the framework form (the cut is lowered by one bf16 step so that ">=" survives the strict compare)
+        gen = torch.Generator(device=x.device).manual_seed(0)
+        pos = torch.randint(total, (max(1024, int(total * sample_ratio)),), device=x.device, generator=gen)
+        probe = stacr_ops.residual_gather(x, coeff, qb, pos).float().abs()
+        cut = float(torch.quantile(probe, 1.0 - float(budget)))
+        idx, val = stacr_ops.residual_above(x, coeff, qb, cut * (1.0 - 2.0 ** -8) if cut > 0 else -1.0)
+        keep = val.float().abs() >= cut
+        idx, val = idx[keep], val[keep]
+        if idx.numel() == 0:
+            return None, None
+        order = torch.argsort(idx)[:k_total]
+        return idx[order].to(idt), quantize_values(val[order], bits)
+    # odd block sizes (and sampled on widths that are no multiple of 8): framework ops
     idx, val = _select_residual(x, coeff, qb, budget, chunk_rows, mode, block_size, sample_ratio)
     if idx is None:
         return None, None

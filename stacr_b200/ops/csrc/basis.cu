@@ -16,6 +16,7 @@
 // stacr/oja.py:8-11 of the reference project).
 #include <cooperative_groups.h>
 
+#define OJA_TRACE 1
 #include "common.cuh"
 
 namespace cg = cooperative_groups;
@@ -308,11 +309,19 @@ __device__ void cluster_gram8(cg::cluster_group& cluster, const float (&acc)[36]
   __syncthreads();
 }
 
+#ifdef OJA_TRACE
+__device__ long long g_oja_trace[16];
+#define OT(k) if (blockIdx.x == 0 && threadIdx.x == 0) g_oja_trace[k] = static_cast<long long>(globaltimer_ns());
+#else
+#define OT(k)
+#endif
+
 template <int ROWS_PT>
 __global__ void __launch_bounds__(1024) oja_update_cluster8_kernel(const float* __restrict__ q_in, const float* __restrict__ g, int ldg,
                                                                    const float* __restrict__ y, int ldy, int rows, int n, int r, float lr,
                                                                    float* __restrict__ q_out, __nv_bfloat16* __restrict__ q_bf16,
                                                                    __nv_bfloat16* __restrict__ qt_bf16, int rpad, int* status) {
+  OT(0)
   cg::cluster_group cluster = cg::this_cluster();
   __shared__ float s_part[36];
   __shared__ float s_mat[RMAX * RMAX];
@@ -337,6 +346,7 @@ __global__ void __launch_bounds__(1024) oja_update_cluster8_kernel(const float* 
       for (int j = 0; j < 8; ++j) qrow[t][j] = (row < n && j < r) ? q_in[static_cast<size_t>(row) * r + j] : 0.f;
     }
   }
+  OT(1)
   if (lr != 0.f && g != nullptr) {
     float acc[36];
 #pragma unroll
@@ -356,7 +366,9 @@ __global__ void __launch_bounds__(1024) oja_update_cluster8_kernel(const float* 
       for (int j = 0; j < 8; ++j) v[j] = (j < r) ? __bfloat162float(__float2bfloat16_rn(v[j])) : 0.f;
       accumulate_upper8(v, acc);
     }
+    OT(2)
     cluster_gram8(cluster, acc, s_part, s_mat);
+    OT(3)
 #pragma unroll
     for (int t = 0; t < ROWS_PT; ++t) {
       const int row = gtid + t * gthreads;
@@ -373,15 +385,19 @@ __global__ void __launch_bounds__(1024) oja_update_cluster8_kernel(const float* 
       for (int j = 0; j < 8; ++j) qrow[t][j] = next[j];
     }
   }
+  OT(4)
   for (int pass = 0; pass < 2; ++pass) {  // CholeskyQR2
     float acc[36];
 #pragma unroll
     for (int k = 0; k < 36; ++k) acc[k] = 0.f;
 #pragma unroll
     for (int t = 0; t < ROWS_PT; ++t) accumulate_upper8(qrow[t], acc);  // rows past n are zero
+    OT(5 + pass * 3)
     cluster_gram8(cluster, acc, s_part, s_mat);
+    OT(6 + pass * 3)
     if (threadIdx.x == 0) s_ok = chol_and_invert8_regs(s_mat, s_inv, r) ? 1 : 0;  // the same numbers in every CTA: uniform outcome
     __syncthreads();
+    OT(7 + pass * 3)
     if (!s_ok) {
       if (threadIdx.x == 0 && status) atomicCAS(status, 0, ST_BAD_ARGUMENT);
       break;
@@ -417,7 +433,9 @@ __global__ void __launch_bounds__(1024) oja_update_cluster8_kernel(const float* 
       for (int j = 0; j < rpad; ++j)
         qt_bf16[static_cast<size_t>(j) * n + row] = (j < 8 && j < r) ? __float2bfloat16_rn(qrow[t][j]) : __float2bfloat16_rn(0.f);
   }
+  OT(11)
   cluster.sync();  // no CTA leaves while a peer may still read its shared memory
+  OT(12)
 }
 
 }  // namespace sb
@@ -615,6 +633,10 @@ extern "C" int sb_jacobi_eig(const double* m, int w, double* evals, double* evec
   sb::jacobi_eig_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(m, w, evals, evecs);
   return static_cast<int>(cudaGetLastError());
 }
+
+#ifdef OJA_TRACE
+extern "C" int sb_debug_oja_trace(long long* out) { return static_cast<int>(cudaMemcpyFromSymbol(out, sb::g_oja_trace, sizeof(long long) * 16)); }
+#endif
 
 extern "C" int sb_oja_update(const float* q_in, const float* g, int ldg, const float* y, int ldy, int rows, int n, int r,
                              float lr, float* q_out, void* q_bf16, void* qt_bf16, int rpad, int* status, void* stream) {

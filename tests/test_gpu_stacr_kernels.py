@@ -313,3 +313,26 @@ def test_adaptive_engine_selects_on_kernels_without_a_dense_residual(mode, monke
     got, want = layer.linear.weight.grad.float().reshape(-1), lin.weight.grad.float().reshape(-1)
     cos = float(torch.dot(got, want) / (got.norm() * want.norm()))
     assert cos > (0.6 if mode == "sparse_only" else 0.9), cos
+
+
+def test_sampled_selector_runs_on_the_kernels_and_agrees_with_the_framework_form(monkeypatch):
+    """``sampled``: probe by the gather kernel, one pass over X for the entries above the probe's quantile, no dense residual."""
+    from stacr_b200 import layers
+    from stacr_b200.ops import _lib
+
+    rows, n, r = 2048, 1024, 8
+    x, q, qb, c, e = _setup(rows, n, r, seed=21)
+    budget, ratio = 0.005, 0.05
+    monkeypatch.setattr(layers, "_select_residual", lambda *a, **k: (_ for _ in ()).throw(AssertionError("framework selector reached")))
+    idx, packed = layers._select_residual_kernels(x, c, qb, budget, 512, "sampled", 16, ratio, 8)
+    torch.cuda.synchronize()
+    _lib.check_status()
+    monkeypatch.undo()
+    k_total = int(round(budget * rows * n))
+    assert 0 < idx.numel() <= k_total and packed.count == idx.numel()
+    assert bool((idx[1:] > idx[:-1]).all())                          # index order, unique
+    ref_idx, ref_val = layers._select_residual(x.float(), c.float(), qb.float(), budget, 512, "sampled", 16, ratio)
+    common = torch.isin(idx.long(), ref_idx.long()).sum().item()
+    assert common >= 0.9 * min(idx.numel(), ref_idx.numel()), (common, idx.numel(), ref_idx.numel())
+    got = e.reshape(-1)[idx.long()].float().abs()
+    assert float(got.min()) >= 0.9 * float(ref_val.float().abs().min())
