@@ -16,7 +16,6 @@
 // stacr/oja.py:8-11 of the reference project).
 #include <cooperative_groups.h>
 
-#define OJA_TRACE 1
 #include "common.cuh"
 
 namespace cg = cooperative_groups;
@@ -281,14 +280,38 @@ __device__ __forceinline__ void accumulate_upper8(const float (&v)[8], float (&a
 
 // acc (36 upper-triangle sums of this thread) -> symmetric r x r total over the whole cluster in s_gram.
 // s_part must be zero on entry and is zero again on exit.
+// One round of a reduce-scatter across the warp: of N_IN values per lane, the lanes with bit `OFF` clear keep the first N_OUT,
+// the others the rest, each adding what its partner (lane ^ OFF) held of the kept half.
+template <int N_IN, int N_OUT, int OFF>
+__device__ __forceinline__ void scatter_round(const float (&in)[N_IN], float (&out)[N_OUT], int lane) {
+  const bool hi = (lane & OFF) != 0;
+#pragma unroll
+  for (int i = 0; i < N_OUT; ++i) {
+    const float lo_v = in[i];
+    const float hi_v = (i + N_OUT < N_IN) ? in[i + N_OUT] : 0.f;
+    out[i] = (hi ? hi_v : lo_v) + __shfl_xor_sync(0xffffffffu, hi ? lo_v : hi_v, OFF);
+  }
+}
+
 __device__ void cluster_gram8(cg::cluster_group& cluster, const float (&acc)[36], float* s_part, float* s_gram) {
   const int lane = threadIdx.x & 31;
-#pragma unroll
-  for (int k = 0; k < 36; ++k) {
-    float v = acc[k];
-#pragma unroll
-    for (int off = 16; off; off >>= 1) v += __shfl_xor_sync(0xffffffffu, v, off);
-    if (lane == 0) atomicAdd(&s_part[k], v);
+  // 36 sums per lane -> at most 2 finished sums per lane in 37 shuffles (a butterfly that halves the values it carries at
+  // every step) instead of 36 x 5: the shuffle unit moves one warp per clock per SM, and 32 warps x 180 shuffles per Gram
+  // matrix, three matrices per update, was most of this kernel's 43 us.
+  float a18[18], a9[9], a5[5], a3[3], a2[2];
+  scatter_round<36, 18, 16>(acc, a18, lane);
+  scatter_round<18, 9, 8>(a18, a9, lane);
+  scatter_round<9, 5, 4>(a9, a5, lane);
+  scatter_round<5, 3, 2>(a5, a3, lane);
+  scatter_round<3, 2, 1>(a3, a2, lane);
+  {
+    const int b4 = (lane >> 4) & 1, b3 = (lane >> 3) & 1, b2 = (lane >> 2) & 1, b1 = (lane >> 1) & 1, b0 = lane & 1;
+    const int l3 = b2 ? 4 : 5;                       // values this lane's group still carried after each uneven split
+    const int l4 = b1 ? l3 - 3 : 3;
+    const int l5 = b0 ? l4 - 2 : (l4 < 2 ? l4 : 2);
+    const int base = 18 * b4 + 9 * b3 + 5 * b2 + 3 * b1 + 2 * b0;
+    if (0 < l5) atomicAdd(&s_part[base], a2[0]);
+    if (1 < l5) atomicAdd(&s_part[base + 1], a2[1]);
   }
   cluster.sync();  // every CTA's partial is complete
   if (threadIdx.x < 36) {
@@ -309,19 +332,11 @@ __device__ void cluster_gram8(cg::cluster_group& cluster, const float (&acc)[36]
   __syncthreads();
 }
 
-#ifdef OJA_TRACE
-__device__ long long g_oja_trace[16];
-#define OT(k) if (blockIdx.x == 0 && threadIdx.x == 0) g_oja_trace[k] = static_cast<long long>(globaltimer_ns());
-#else
-#define OT(k)
-#endif
-
 template <int ROWS_PT>
 __global__ void __launch_bounds__(1024) oja_update_cluster8_kernel(const float* __restrict__ q_in, const float* __restrict__ g, int ldg,
                                                                    const float* __restrict__ y, int ldy, int rows, int n, int r, float lr,
                                                                    float* __restrict__ q_out, __nv_bfloat16* __restrict__ q_bf16,
                                                                    __nv_bfloat16* __restrict__ qt_bf16, int rpad, int* status) {
-  OT(0)
   cg::cluster_group cluster = cg::this_cluster();
   __shared__ float s_part[36];
   __shared__ float s_mat[RMAX * RMAX];
@@ -346,7 +361,6 @@ __global__ void __launch_bounds__(1024) oja_update_cluster8_kernel(const float* 
       for (int j = 0; j < 8; ++j) qrow[t][j] = (row < n && j < r) ? q_in[static_cast<size_t>(row) * r + j] : 0.f;
     }
   }
-  OT(1)
   if (lr != 0.f && g != nullptr) {
     float acc[36];
 #pragma unroll
@@ -366,38 +380,40 @@ __global__ void __launch_bounds__(1024) oja_update_cluster8_kernel(const float* 
       for (int j = 0; j < 8; ++j) v[j] = (j < r) ? __bfloat162float(__float2bfloat16_rn(v[j])) : 0.f;
       accumulate_upper8(v, acc);
     }
-    OT(2)
     cluster_gram8(cluster, acc, s_part, s_mat);
-    OT(3)
 #pragma unroll
     for (int t = 0; t < ROWS_PT; ++t) {
       const int row = gtid + t * gthreads;
       if (row >= n) continue;
-      float next[8];
+      float next[8], gv[8];
+      const float* gr = g + static_cast<size_t>(row) * ldg;
+      if ((ldg & 3) == 0) {  // rows are 16-byte aligned: two vector loads
+        const float4 lo = reinterpret_cast<const float4*>(gr)[0], hi = reinterpret_cast<const float4*>(gr)[1];
+        gv[0] = lo.x; gv[1] = lo.y; gv[2] = lo.z; gv[3] = lo.w; gv[4] = hi.x; gv[5] = hi.y; gv[6] = hi.z; gv[7] = hi.w;
+      } else {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) gv[j] = (j < r) ? gr[j] : 0.f;
+      }
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
         float qs = 0.f;
 #pragma unroll
         for (int k = 0; k < 8; ++k) qs = fmaf(qrow[t][k], s_mat[k * RMAX + j], qs);
-        next[j] = (j < r) ? qrow[t][j] + lr * inv_n * (g[static_cast<size_t>(row) * ldg + j] - qs) : 0.f;
+        next[j] = (j < r) ? qrow[t][j] + lr * inv_n * (gv[j] - qs) : 0.f;
       }
 #pragma unroll
       for (int j = 0; j < 8; ++j) qrow[t][j] = next[j];
     }
   }
-  OT(4)
   for (int pass = 0; pass < 2; ++pass) {  // CholeskyQR2
     float acc[36];
 #pragma unroll
     for (int k = 0; k < 36; ++k) acc[k] = 0.f;
 #pragma unroll
     for (int t = 0; t < ROWS_PT; ++t) accumulate_upper8(qrow[t], acc);  // rows past n are zero
-    OT(5 + pass * 3)
     cluster_gram8(cluster, acc, s_part, s_mat);
-    OT(6 + pass * 3)
     if (threadIdx.x == 0) s_ok = chol_and_invert8_regs(s_mat, s_inv, r) ? 1 : 0;  // the same numbers in every CTA: uniform outcome
     __syncthreads();
-    OT(7 + pass * 3)
     if (!s_ok) {
       if (threadIdx.x == 0 && status) atomicCAS(status, 0, ST_BAD_ARGUMENT);
       break;
@@ -422,20 +438,31 @@ __global__ void __launch_bounds__(1024) oja_update_cluster8_kernel(const float* 
   for (int t = 0; t < ROWS_PT; ++t) {
     const int row = gtid + t * gthreads;
     if (row >= n) continue;
+    if (r == 8) {  // a row is 32 bytes of fp32 and 16 bytes of bf16: vector stores
+      float4* qo = reinterpret_cast<float4*>(q_out + static_cast<size_t>(row) * 8);
+      qo[0] = make_float4(qrow[t][0], qrow[t][1], qrow[t][2], qrow[t][3]);
+      qo[1] = make_float4(qrow[t][4], qrow[t][5], qrow[t][6], qrow[t][7]);
+      if (q_bf16)
+        *reinterpret_cast<uint4*>(q_bf16 + static_cast<size_t>(row) * 8) =
+            make_uint4(pack_bf16x2(qrow[t][0], qrow[t][1]), pack_bf16x2(qrow[t][2], qrow[t][3]), pack_bf16x2(qrow[t][4], qrow[t][5]),
+                       pack_bf16x2(qrow[t][6], qrow[t][7]));
+    } else {
 #pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      if (j < r) {
-        q_out[static_cast<size_t>(row) * r + j] = qrow[t][j];
-        if (q_bf16) q_bf16[static_cast<size_t>(row) * r + j] = __float2bfloat16_rn(qrow[t][j]);
+      for (int j = 0; j < 8; ++j) {
+        if (j < r) {
+          q_out[static_cast<size_t>(row) * r + j] = qrow[t][j];
+          if (q_bf16) q_bf16[static_cast<size_t>(row) * r + j] = __float2bfloat16_rn(qrow[t][j]);
+        }
       }
     }
-    if (qt_bf16)
-      for (int j = 0; j < rpad; ++j)
-        qt_bf16[static_cast<size_t>(j) * n + row] = (j < 8 && j < r) ? __float2bfloat16_rn(qrow[t][j]) : __float2bfloat16_rn(0.f);
+    if (qt_bf16) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j)
+        if (j < rpad) qt_bf16[static_cast<size_t>(j) * n + row] = __float2bfloat16_rn(j < r ? qrow[t][j] : 0.f);
+      for (int j = 8; j < rpad; ++j) qt_bf16[static_cast<size_t>(j) * n + row] = __float2bfloat16_rn(0.f);
+    }
   }
-  OT(11)
   cluster.sync();  // no CTA leaves while a peer may still read its shared memory
-  OT(12)
 }
 
 }  // namespace sb
@@ -633,10 +660,6 @@ extern "C" int sb_jacobi_eig(const double* m, int w, double* evals, double* evec
   sb::jacobi_eig_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(m, w, evals, evecs);
   return static_cast<int>(cudaGetLastError());
 }
-
-#ifdef OJA_TRACE
-extern "C" int sb_debug_oja_trace(long long* out) { return static_cast<int>(cudaMemcpyFromSymbol(out, sb::g_oja_trace, sizeof(long long) * 16)); }
-#endif
 
 extern "C" int sb_oja_update(const float* q_in, const float* g, int ldg, const float* y, int ldy, int rows, int n, int r,
                              float lr, float* q_out, void* q_bf16, void* qt_bf16, int rpad, int* status, void* stream) {

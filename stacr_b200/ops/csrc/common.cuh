@@ -185,6 +185,17 @@ __host__ __device__ constexpr uint32_t make_idesc_bf16(int m, int n, bool a_mn, 
          (static_cast<uint32_t>(m >> 4) << 24);
 }
 
+// One-time, per-device configuration of a kernel (cudaFuncSetAttribute applies to the current device only, so a process that
+// drives several GPUs has to repeat it on each of them).
+struct PerDeviceOnce {
+  bool done[64] = {};
+  bool* slot() {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+    return &done[dev];
+  }
+};
+
 __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
   __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
   return *reinterpret_cast<uint32_t*>(&v);

@@ -431,12 +431,14 @@ template <int BN, bool A_MN, bool B_MN>
 static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, int sms,
                        cudaStream_t stream) {
   using Cfg = GemmCfg<BN>;
-  static bool configured = false;
+  static PerDeviceOnce once;
+  bool* configured = once.slot();
+  if (configured == nullptr) return -8;
   auto kern = gemm_bf16_kernel<BN, A_MN, B_MN>;
-  if (!configured) {
+  if (!*configured) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES);
     if (e != cudaSuccess) return static_cast<int>(e);
-    configured = true;
+    *configured = true;
   }
   const int num_m = (p.M + BM - 1) / BM, num_n = (p.N + BN - 1) / BN;
   const int total = num_m * num_n * p.splits;

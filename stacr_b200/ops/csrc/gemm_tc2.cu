@@ -347,12 +347,14 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
 
 template <bool A_MN, bool B_MN>
 static int launch(const CUtensorMap& ta, const CUtensorMap& tb, const Params& p, int sms, cudaStream_t stream) {
-  static bool configured = false;
+  static PerDeviceOnce once;
+  bool* configured = once.slot();
+  if (configured == nullptr) return -8;
   auto kern = gemm2_bf16_kernel<A_MN, B_MN>;
-  if (!configured) {
+  if (!*configured) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
     if (e != cudaSuccess) return static_cast<int>(e);
-    configured = true;
+    *configured = true;
   }
   const int tiles = ((p.M + TM - 1) / TM) * ((p.N + TN - 1) / TN);
   int pairs = sms / 2;

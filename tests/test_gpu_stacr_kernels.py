@@ -329,7 +329,7 @@ def test_sampled_selector_runs_on_the_kernels_and_agrees_with_the_framework_form
     _lib.check_status()
     monkeypatch.undo()
     k_total = int(round(budget * rows * n))
-    assert 0 < idx.numel() <= k_total and packed.count == idx.numel()
+    assert 0 < idx.numel() <= k_total and packed.length == idx.numel()
     assert bool((idx[1:] > idx[:-1]).all())                          # index order, unique
     ref_idx, ref_val = layers._select_residual(x.float(), c.float(), qb.float(), budget, 512, "sampled", 16, ratio)
     common = torch.isin(idx.long(), ref_idx.long()).sum().item()
