@@ -473,14 +473,14 @@ __global__ void residual_gather_kernel(const __nv_bfloat16* x, const __nv_bfloat
 // bs is a power of two in [8, 256] dividing n.  A thread owns 8 consecutive columns for BE_ROWS rows: its 8 basis rows
 // stay in registers, the coefficient rows of the CTA come from shared memory as broadcasts, X is read with one 16-byte
 // load per row, and the bs / 8 lanes of a block are shuffle-reduced.
-constexpr int BE_ROWS = 32;
+constexpr int BE_ROWS = 8;   // rows per CTA: small, so that a 4096-row activation gives every SM several CTAs (the kernel is latency-bound)
 
 template <int RP>
 __global__ void __launch_bounds__(256) residual_block_energy_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ c,
                                                                     const __nv_bfloat16* __restrict__ q, int rows, int n, int r, int ldx,
                                                                     int bs, float* __restrict__ energy) {
   __shared__ float s_c[BE_ROWS * RP];
-  const int row0 = blockIdx.y * BE_ROWS;
+  const int row0 = blockIdx.x * BE_ROWS;   // rows on the x dimension of the grid: it has no 65535 limit
   const int nrows = min(BE_ROWS, rows - row0);
   for (int i = threadIdx.x; i < BE_ROWS * RP; i += blockDim.x) {
     const int lr = i / RP, j = i - lr * RP;
@@ -488,13 +488,27 @@ __global__ void __launch_bounds__(256) residual_block_energy_kernel(const __nv_b
   }
   __syncthreads();
   const int tpb = bs / 8;
-  const int col = (blockIdx.x * blockDim.x + threadIdx.x) * 8;
+  const int col = (blockIdx.y * blockDim.x + threadIdx.x) * 8;
   const bool live = col < n;  // n is a multiple of bs >= 8, so a live thread owns 8 valid columns
   float qreg[8][RP];
+  if (RP == 8 && r == 8 && live && (reinterpret_cast<uintptr_t>(q) & 15) == 0) {
+    // a basis row is 16 bytes: one vector load per column instead of eight 2-byte loads
 #pragma unroll
-  for (int i = 0; i < 8; ++i)
+    for (int i = 0; i < 8; ++i) {
+      const uint4 raw = __ldg(reinterpret_cast<const uint4*>(q + static_cast<size_t>(col + i) * 8));
+      const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
 #pragma unroll
-    for (int j = 0; j < RP; ++j) qreg[i][j] = (live && j < r) ? __bfloat162float(q[static_cast<size_t>(col + i) * r + j]) : 0.f;
+      for (int k = 0; k < 4; ++k) {
+        qreg[i][2 * k] = __uint_as_float(w[k] << 16);
+        qreg[i][2 * k + 1] = __uint_as_float(w[k] & 0xFFFF0000u);
+      }
+    }
+  } else {
+#pragma unroll
+    for (int i = 0; i < 8; ++i)
+#pragma unroll
+      for (int j = 0; j < RP; ++j) qreg[i][j] = (live && j < r) ? __bfloat162float(q[static_cast<size_t>(col + i) * r + j]) : 0.f;
+  }
   const bool vec = ((ldx & 7) == 0) && ((reinterpret_cast<uintptr_t>(x) & 15) == 0);
   // BE_UNROLL rows in flight per thread: with one load per row and iteration the kernel ran at DRAM latency (40 us for 10 MB)
   constexpr int BE_UNROLL = RP <= 8 ? 8 : (RP <= 16 ? 4 : 1);   // the basis rows already take 8 * RP registers
@@ -1313,7 +1327,7 @@ extern "C" int sb_residual_block_energy(const void* x, const void* c, const void
   if (rows <= 0) return 0;
   if (bs % 8 || bs > 256 || (bs & (bs - 1)) || n % bs) return -2;
   if (r < 1 || r > 32) return -2;
-  dim3 grid((n / 8 + 255) / 256, (rows + sb::BE_ROWS - 1) / sb::BE_ROWS);
+  dim3 grid((rows + sb::BE_ROWS - 1) / sb::BE_ROWS, (n / 8 + 255) / 256);
   const __nv_bfloat16* xb = static_cast<const __nv_bfloat16*>(x);
   const __nv_bfloat16* cb = static_cast<const __nv_bfloat16*>(c);
   const __nv_bfloat16* qb = static_cast<const __nv_bfloat16*>(q);
