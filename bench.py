@@ -426,6 +426,7 @@ def run_ours(args):
                 "optimizer_sharding": "ZeRO-1: reduce-to-owner buckets, 1/W optimizer per rank, bf16 weights published by multicast stores of the update kernel" if zero else "replicated",
                 "l2": "inputs larger than L2: every step streams 2.8 GB of bf16 weights and > 10 GB of activations through a 126 MB L2",
                 "cuda_graph": graphed is not None,
+                "attention": "in-tree tcgen05 forward + backward on the fused QKV projection" if args.attention == "intree" else "library (scaled_dot_product_attention)",
             },
             "clocks": clocks.summary(),
             "timing": {"regions": len(secs_all), "steps_per_region": args.steps, "reported": "median region",
@@ -576,12 +577,16 @@ def main():
     ap.add_argument("--graph", default="on", choices=["on", "off"],
                     help="capture the training step (with the in-tree collectives at N > 1) into a CUDA graph and replay it")
     ap.add_argument("--zero", default="on", choices=["on", "off"], help="N > 1: shard the optimizer over the ranks (reduce-to-owner + multicast weight publication)")
+    ap.add_argument("--attention", default="library", choices=["library", "intree"],
+                    help="softmax attention: the fused library kernel (default, faster) or the in-tree tcgen05 forward + backward")
     ap.add_argument("--gap-report", metavar="FILE", help="after the timed regions, write where the GPU idles inside two more steps to FILE")
     ap.add_argument("--kernel-table", metavar="FILE", help="after the timed regions, write per-kernel device times of two more steps to FILE")
     ap.add_argument("--small", action="store_true", help="tiny shape for smoke runs (not a benchmark number)")
     ap.add_argument("--repeats", type=int, default=3, help="timed regions of --steps steps per measurement; the median region is reported")
     ap.add_argument("--no-evidence", action="store_true", help="skip the extra step that measures dW cosine and saved bytes after the timed regions")
     args = ap.parse_args()
+    if args.impl == "ours":
+        os.environ["STACR_ATTENTION"] = args.attention
     if args.gpus > 1 and "RANK" not in os.environ:
         raise SystemExit("for --gpus > 1 launch with: python -m torch.distributed.run --nproc-per-node N bench.py --gpus N ...")
     (run_reference if args.impl == "reference" else run_ours)(args)

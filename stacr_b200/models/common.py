@@ -67,7 +67,8 @@ class GELU(nn.Module):
 
 def _attention_engine() -> str:
     """``STACR_ATTENTION``: ``library`` (default: the fused attention ``torch`` dispatches to, which measured faster on
-    B200) or ``intree`` (the tcgen05 forward kernel of ``ops/attention.py``, used where no gradient is needed)."""
+    B200) or ``intree`` (the tcgen05 kernels of ``ops/attention.py``: forward for gradient-free passes of every model,
+    forward + backward on the fused QKV projection for the GPT-NeoX family at head_dim 128)."""
     return os.environ.get("STACR_ATTENTION", "library")
 
 

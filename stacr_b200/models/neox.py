@@ -9,8 +9,9 @@ from torch import nn
 
 import os
 
+from ..ops import attention as attention_ops
 from ..ops import nn_ops
-from .common import causal_attention, Embedding, GELU, init_weights, LayerNorm, Linear, lm_loss, ModelOutput
+from .common import _attention_engine as attention_engine, causal_attention, Embedding, GELU, init_weights, LayerNorm, Linear, lm_loss, ModelOutput
 
 
 _FUSED_NORMS = os.environ.get("STACR_FUSED_NORMS", "1") == "1"   # 0: the two norms and the residual sum as separate ops
@@ -94,6 +95,12 @@ class NeoXAttention(nn.Module):
         if nn_ops.rotary_qk_supported(qkv, self.head_dim, self.rot):
             cos, sin = self._half_tables(s, x.device)
             qkv = nn_ops.rotary_qk(qkv, cos, sin, s, self.n_head, self.head_dim, self.rot)  # fused, in place
+            if (attention_engine() == "intree" and attention_ops.fused_supported(qkv, self.head_dim)
+                    and not (self.training and self.attention_dropout > 0.0)):
+                # in-tree forward and backward straight on the fused projection: no split, cat or transpose copies
+                mask = attention_mask if attention_mask is not None and not bool(attention_mask.all()) else None
+                ctx = attention_ops.fused_qkv_attention(qkv, b, s, self.n_head, self.head_dim, layout="interleaved", causal=True, key_mask=mask)
+                return self.dense(ctx)
             q, k, v = (t.transpose(1, 2) for t in qkv.view(b, s, self.n_head, 3 * self.head_dim).split(self.head_dim, dim=-1))
         else:
             # NeoX interleaves per head: [H, 3 * head_dim]

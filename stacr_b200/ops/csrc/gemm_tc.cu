@@ -17,6 +17,8 @@
 //
 // Replaces the library GEMMs the reference issues from its autograd function
 // (stacr/layers.py:128-137 and :168-173 of the reference project).
+#include <cstdio>
+
 #include "common.cuh"
 
 namespace sb {
@@ -419,6 +421,17 @@ static int make_map(CUtensorMap* map, const void* ptr, uint64_t inner, uint64_t 
   CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r == CUDA_ERROR_INVALID_CONTEXT) {
+    // the driver entry point wants a current context, and a thread that has made no runtime call yet (an autograd worker
+    // whose first CUDA work is this launch) has none bound: bind the device's primary context and encode again
+    int dev = 0;
+    if (cudaGetDevice(&dev) == cudaSuccess && cudaSetDevice(dev) == cudaSuccess && cudaFree(nullptr) == cudaSuccess)
+      r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+             CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  }
+  if (r != CUDA_SUCCESS)   // rare and always a caller error: say which argument set the driver refused
+    fprintf(stderr, "stacr_b200: cuTensorMapEncodeTiled failed (%d): ptr=%p inner=%llu outer=%llu ld=%llu box_outer=%u\n", static_cast<int>(r), ptr,
+            static_cast<unsigned long long>(inner), static_cast<unsigned long long>(outer), static_cast<unsigned long long>(ld), box_outer);
   return r == CUDA_SUCCESS ? 0 : -2;
 }
 

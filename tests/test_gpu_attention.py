@@ -77,3 +77,36 @@ def test_model_attention_uses_the_in_tree_kernel_without_grad(monkeypatch):
     _lib.check_status()
     assert float((got - ref).abs().max()) < 0.1 * float(ref.abs().max())
     assert float(torch.nn.functional.cosine_similarity(got.flatten(), ref.flatten(), dim=0)) > 0.999
+
+
+@pytest.mark.parametrize("b,h,s,causal,layout", [
+    (2, 4, 256, True, "interleaved"),
+    (1, 3, 200, True, "blocked"),            # ragged: the last key tile and the last query tile are partial
+    (2, 2, 130, False, "interleaved"),
+    (1, 2, 72, True, "blocked"),
+    (2, 16, 1024, True, "interleaved"),
+])
+def test_flash_backward_matches_autograd_of_the_formula(b, h, s, causal, layout):
+    """dq, dk, dv of the in-tree backward (written into one fused gradient matrix) against autograd through the fp32 formula."""
+    from stacr_b200.ops import _lib, attention
+
+    d = 128
+    g = torch.Generator(device="cuda").manual_seed(11 * s + h)
+    qkv = (0.5 * torch.randn(b * s, 3 * h * d, device="cuda", generator=g)).bfloat16().requires_grad_(True)
+    up = torch.randn(b, s, h * d, device="cuda", generator=g).bfloat16()
+    assert attention.fused_supported(qkv, d)
+    out = attention.fused_qkv_attention(qkv, b, s, h, d, layout=layout, causal=causal)
+    out.backward(up)
+    torch.cuda.synchronize()
+    _lib.check_status()
+    ref_in = qkv.detach().float().requires_grad_(True)
+    q, k, v = attention.qkv_views(ref_in, b, s, h, d, layout)
+    ref = attention.reference(q, k, v, causal=causal)
+    ref.backward(up.float())
+    assert float((out.float() - ref).abs().max()) < 2e-2
+    got, want = qkv.grad.float(), ref_in.grad
+    scale = float(want.abs().max())
+    assert bool(torch.isfinite(got).all())
+    assert float((got - want).abs().max()) < 3e-2 * scale + 1e-3, (float((got - want).abs().max()), scale)
+    cos = torch.nn.functional.cosine_similarity(got.flatten(), want.flatten(), dim=0)
+    assert float(cos) > 0.999, float(cos)
