@@ -453,10 +453,10 @@ static int launch_fwd(const CUtensorMap& tq, const CUtensorMap& tk, const CUtens
 //     dQ_i^T = K^T dS^T     (A = K, MN-major;   B = dS^T, MN-major)      [head_dim x 64 queries]
 // dQ is summed over the key tiles of a row with fp32 reductions into a scratch matrix (coalesced: a warp adds 32 consecutive
 // head_dim entries of one query), which a small kernel scales and converts afterwards.  head_dim 128 only.
-// Warps: 0 producer (TMA, and lse / delta of the query tile into shared memory), 1 MMA, 2..5 softmax (thread = key),
-// 6..9 dQ epilogue (thread = head_dim index).
+// Warps: 0 producer (TMA, and lse / delta of the query tile into shared memory), 1 MMA, 2..9 softmax (two threads per key,
+// 32 queries each), 10..17 dQ epilogue (two threads per head_dim index).
 // =====================================================================================================================
-constexpr int BWD_BK = 128, BWD_BQ = 64, BWD_THREADS = 320, BWD_D = 128;
+constexpr int BWD_BK = 128, BWD_BQ = 64, BWD_THREADS = 576, BWD_D = 128;
 constexpr int BWD_TMEM_COLS = 512;
 constexpr int BCOL_S = 0, BCOL_DP = 64, BCOL_DV = 128, BCOL_DK = 256, BCOL_DQ = 384;
 
@@ -494,12 +494,12 @@ struct BwdPlan {
 //   KV_FULL      K and V tiles landed (once)
 //   QDO_FULL[s]  Q_i and dO_i landed in stage s and their lse / delta are in shared memory (byte count + 1 warp arrival)
 //   S_FULL       S^T and dP^T of this iteration are complete (commit)
-//   S_FREE       the softmax warps have taken both out of tensor memory (4 warp arrivals)
-//   PDS_READY    P^T and dS^T are in shared memory (4 warp arrivals)
+//   S_FREE       the softmax warps have taken both out of tensor memory (8 warp arrivals)
+//   PDS_READY    P^T and dS^T are in shared memory (8 warp arrivals)
 //   ITER_DONE[s] dV, dK and dQ^T products of this iteration are complete (commit): stage s, the P / dS buffers are free again
 //                and dQ^T can be read.  Per stage, so that the producer, which waits for the iteration before last, can
 //                never fall two phases behind the barrier it names by parity
-//   DQ_FREE      the epilogue warps have taken dQ^T out of tensor memory (4 warp arrivals)
+//   DQ_FREE      the epilogue warps have taken dQ^T out of tensor memory (8 warp arrivals)
 enum BBar { KV_FULL = 0, QDO_FULL = 1, S_FULL_B = 3, S_FREE = 4, PDS_READY = 5, ITER_DONE = 6, DQ_FREE = 8, BNBARS = 9 };
 
 __global__ void __launch_bounds__(BWD_THREADS, 1)
@@ -535,11 +535,11 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
     mbar_init(&bars[QDO_FULL], 2);
     mbar_init(&bars[QDO_FULL + 1], 2);
     mbar_init(&bars[S_FULL_B], 1);
-    mbar_init(&bars[S_FREE], 4);
-    mbar_init(&bars[PDS_READY], 4);
+    mbar_init(&bars[S_FREE], 8);
+    mbar_init(&bars[PDS_READY], 8);
     mbar_init(&bars[ITER_DONE], 1);
     mbar_init(&bars[ITER_DONE + 1], 1);
-    mbar_init(&bars[DQ_FREE], 4);
+    mbar_init(&bars[DQ_FREE], 8);
     *abort_flag = 0;
     fence_barrier_init();
   }
@@ -605,13 +605,11 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
       constexpr uint32_t idesc_dq = make_idesc_bf16(D, BWD_BQ, true, true);         // dQ^T: A = K MN-major, B = dS^T MN-major
       const uint32_t k_addr = smem_u32(smem + PL::OFF_K), v_addr = smem_u32(smem + PL::OFF_V);
       const uint32_t p_addr = smem_u32(smem + PL::OFF_P), ds_addr = smem_u32(smem + PL::OFF_DS);
-      bool ok = wait_on(&bars[KV_FULL], 0, abort_flag, p.status, ST_TIMEOUT_SMEM_FULL);
-      for (int it = 0; it < niter && ok; ++it) {
+      // S^T and dP^T of iteration it + 1 are issued before the three products of iteration it, so that they run on the tensor
+      // core while the softmax warps work on iteration it (whose scores they have already taken into registers).
+      auto issue_scores = [&](int it) {
         const int s = it & 1;
         const uint32_t q_addr = smem_u32(smem + PL::OFF_Q + s * PL::QT_BYTES), do_addr = smem_u32(smem + PL::OFF_DO + s * PL::QT_BYTES);
-        if (!wait_on(&bars[QDO_FULL + s], (it >> 1) & 1, abort_flag, p.status, ST_TIMEOUT_SMEM_FULL)) { ok = false; break; }
-        if (it > 0 && !wait_on(&bars[S_FREE], (it - 1) & 1, abort_flag, p.status, ST_TIMEOUT_TMEM_EMPTY)) { ok = false; break; }
-        tc_fence_after();
 #pragma unroll
         for (int c = 0; c < D / 64; ++c)
 #pragma unroll
@@ -622,6 +620,24 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
                       make_smem_desc_sw128(do_addr + c * (BWD_BQ * 128) + k * 32, 16, 1024), idesc_s, (c > 0 || k > 0) ? 1u : 0u);
           }
         umma_commit(&bars[S_FULL_B]);
+      };
+      bool ok = wait_on(&bars[KV_FULL], 0, abort_flag, p.status, ST_TIMEOUT_SMEM_FULL);
+      if (ok && niter > 0) {
+        ok = wait_on(&bars[QDO_FULL], 0, abort_flag, p.status, ST_TIMEOUT_SMEM_FULL);
+        if (ok) {
+          tc_fence_after();
+          issue_scores(0);
+        }
+      }
+      for (int it = 0; it < niter && ok; ++it) {
+        const int s = it & 1;
+        const uint32_t q_addr = smem_u32(smem + PL::OFF_Q + s * PL::QT_BYTES), do_addr = smem_u32(smem + PL::OFF_DO + s * PL::QT_BYTES);
+        if (it + 1 < niter) {
+          if (!wait_on(&bars[QDO_FULL + ((it + 1) & 1)], ((it + 1) >> 1) & 1, abort_flag, p.status, ST_TIMEOUT_SMEM_FULL)) { ok = false; break; }
+          if (!wait_on(&bars[S_FREE], it & 1, abort_flag, p.status, ST_TIMEOUT_TMEM_EMPTY)) { ok = false; break; }
+          tc_fence_after();
+          issue_scores(it + 1);
+        }
         if (!wait_on(&bars[PDS_READY], it & 1, abort_flag, p.status, ST_TIMEOUT_TMEM_FULL)) { ok = false; break; }
         if (it > 0 && !wait_on(&bars[DQ_FREE], (it - 1) & 1, abort_flag, p.status, ST_TIMEOUT_TMEM_EMPTY)) { ok = false; break; }
         tc_fence_after();
@@ -639,9 +655,11 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
         umma_commit(&bars[ITER_DONE + s]);
       }
     }
-  } else if (warp < 6) {
-    // ------------------------------------------------------------------ softmax-backward warps: thread = key row
+  } else if (warp < 10) {
+    // ------------------------------------------------------------------ softmax-backward warps: two threads per key row
+    // (warp w may touch the TMEM lanes of quarter w % 4; warps 2..5 take queries 0..31 of the tile, warps 6..9 queries 32..63)
     const int quad = warp & 3;
+    const int hsel = (warp - 2) >> 2;
     const int r = quad * 32 + lane;
     const int key = kv0 + r;
     const uint32_t t_lane = tmem_base + (static_cast<uint32_t>(quad * 32) << 16);
@@ -651,49 +669,56 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
     bool ok = true;
     for (int it = 0; it < niter && ok; ++it) {
       const int s = it & 1;
-      const int q0 = (i_first + it) * BWD_BQ;
+      const int q0 = (i_first + it) * BWD_BQ + hsel * 32;   // first query of this thread's half
       if (!wait_on(&bars[QDO_FULL + s], (it >> 1) & 1, abort_flag, p.status, ST_TIMEOUT_SMEM_FULL)) { ok = false; break; }   // lse / delta visible
       if (!wait_on(&bars[S_FULL_B], it & 1, abort_flag, p.status, ST_TIMEOUT_TMEM_FULL)) { ok = false; break; }
+      tc_fence_after();
+      // everything into registers first: the accumulators are then free for the next query tile's scores
+      uint32_t sv[32], dpv[32];
+      tmem_ld_x32(t_lane + BCOL_S + hsel * 32, sv);
+      tmem_ld_x32(t_lane + BCOL_DP + hsel * 32, dpv);
+      tmem_ld_wait();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&bars[S_FREE]);
+      // a tile is an edge tile if any of its entries is masked: sequence end, the causal diagonal, or a padding key
+      const bool edge = !key_ok || q0 + 32 > p.S || (p.causal && kv0 + BWD_BK - 1 > q0) || kv0 + BWD_BK > p.S;
+      const float4* l4 = reinterpret_cast<const float4*>(s_lse + s * 64 + hsel * 32);
+      const float4* d4 = reinterpret_cast<const float4*>(s_delta + s * 64 + hsel * 32);
+      uint32_t pp[16], dd[16];
+#pragma unroll
+      for (int g4 = 0; g4 < 8; ++g4) {
+        const float4 lv = l4[g4], dl = d4[g4];
+        const float lse4[4] = {lv.x, lv.y, lv.z, lv.w}, del4[4] = {dl.x, dl.y, dl.z, dl.w};
+        float pv[4], ds4[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const int col = g4 * 4 + u;
+          float pr = ex2(fmaf(__uint_as_float(sv[col]), p.scale_log2, -lse4[u]));
+          if (edge) {
+            const int q = q0 + col;
+            if (!(key_ok && q < p.S && (!p.causal || key <= q))) pr = 0.f;
+          }
+          pv[u] = pr;
+          ds4[u] = pr * (__uint_as_float(dpv[col]) - del4[u]);
+        }
+        pp[g4 * 2] = pack_bf16x2(pv[0], pv[1]);
+        pp[g4 * 2 + 1] = pack_bf16x2(pv[2], pv[3]);
+        dd[g4 * 2] = pack_bf16x2(ds4[0], ds4[1]);
+        dd[g4 * 2 + 1] = pack_bf16x2(ds4[2], ds4[3]);
+      }
       // the P / dS buffers were read by the products of iteration it - 1
       if (it > 0 && !wait_on(&bars[ITER_DONE + ((it - 1) & 1)], ((it - 1) >> 1) & 1, abort_flag, p.status, ST_TIMEOUT_SMEM_EMPTY)) { ok = false; break; }
-      tc_fence_after();
+      // K-major, 128-byte-swizzled rows: 16-byte slot k holds queries 8k .. 8k + 7; this thread owns slots 4 * hsel .. + 3
 #pragma unroll
-      for (int half = 0; half < 2; ++half) {
-        uint32_t sv[32], dpv[32];
-        tmem_ld_x32(t_lane + BCOL_S + half * 32, sv);
-        tmem_ld_x32(t_lane + BCOL_DP + half * 32, dpv);
-        tmem_ld_wait();
-        uint32_t pp[16], dd[16];
-#pragma unroll
-        for (int j = 0; j < 32; j += 2) {
-          float pv[2], dv2[2];
-#pragma unroll
-          for (int u = 0; u < 2; ++u) {
-            const int col = half * 32 + j + u;
-            const int q = q0 + col;
-            const bool keep = key_ok && q < p.S && (!p.causal || key <= q);
-            const float pr = keep ? ex2(fmaf(__uint_as_float(sv[j + u]), p.scale_log2, -s_lse[s * 64 + col])) : 0.f;
-            pv[u] = pr;
-            dv2[u] = pr * (__uint_as_float(dpv[j + u]) - s_delta[s * 64 + col]);
-          }
-          pp[j >> 1] = pack_bf16x2(pv[0], pv[1]);
-          dd[j >> 1] = pack_bf16x2(dv2[0], dv2[1]);
-        }
-        // K-major, 128-byte-swizzled rows: this half is 16-byte slots 4 * half .. 4 * half + 3 of the row
-#pragma unroll
-        for (int q4 = 0; q4 < 4; ++q4) {
-          const int slot = half * 4 + q4;
-          *reinterpret_cast<uint4*>(p_row + ((slot ^ (r & 7)) << 4)) = make_uint4(pp[q4 * 4], pp[q4 * 4 + 1], pp[q4 * 4 + 2], pp[q4 * 4 + 3]);
-          *reinterpret_cast<uint4*>(ds_row + ((slot ^ (r & 7)) << 4)) = make_uint4(dd[q4 * 4], dd[q4 * 4 + 1], dd[q4 * 4 + 2], dd[q4 * 4 + 3]);
-        }
+      for (int q4 = 0; q4 < 4; ++q4) {
+        const int slot = hsel * 4 + q4;
+        *reinterpret_cast<uint4*>(p_row + ((slot ^ (r & 7)) << 4)) = make_uint4(pp[q4 * 4], pp[q4 * 4 + 1], pp[q4 * 4 + 2], pp[q4 * 4 + 3]);
+        *reinterpret_cast<uint4*>(ds_row + ((slot ^ (r & 7)) << 4)) = make_uint4(dd[q4 * 4], dd[q4 * 4 + 1], dd[q4 * 4 + 2], dd[q4 * 4 + 3]);
       }
-      tc_fence_before();
       fence_proxy_async();
       __syncwarp();
-      if (lane == 0) {
-        mbar_arrive(&bars[S_FREE]);
-        mbar_arrive(&bars[PDS_READY]);
-      }
+      if (lane == 0) mbar_arrive(&bars[PDS_READY]);
     }
     // ---- dK and dV of this key row
     if (ok && niter > 0) ok = wait_on(&bars[ITER_DONE + ((niter - 1) & 1)], ((niter - 1) >> 1) & 1, abort_flag, p.status, ST_TIMEOUT_TMEM_FULL);
@@ -702,7 +727,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
       __nv_bfloat16* dv_row = p.dv + (static_cast<size_t>(row_base) + key) * p.ld_dv + p.dv_col0 + h * p.dhead_stride;
       __nv_bfloat16* dk_row = p.dk + (static_cast<size_t>(row_base) + key) * p.ld_dk + p.dk_col0 + h * p.dhead_stride;
 #pragma unroll 1
-      for (int c = 0; c < D / 16; ++c) {
+      for (int c = hsel * (D / 32); c < (hsel + 1) * (D / 32); ++c) {   // this thread's half of the head_dim columns
         uint32_t a[16], k16[16];
         if (niter > 0) {
           tmem_ld_x16(t_lane + BCOL_DV + c * 16, a);
@@ -728,31 +753,28 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
       tc_fence_before();
     }
   } else {
-    // ------------------------------------------------------------------ dQ epilogue warps: thread = head_dim index
+    // ------------------------------------------------------------------ dQ epilogue warps: two threads per head_dim index
     const int quad = warp & 3;
+    const int hsel = (warp - 10) >> 2;
     const int dlane = quad * 32 + lane;
     const uint32_t t_lane = tmem_base + (static_cast<uint32_t>(quad * 32) << 16);
+    const size_t row_floats = static_cast<size_t>(p.H) * D;
     bool ok = true;
     for (int it = 0; it < niter && ok; ++it) {
-      const int q0 = (i_first + it) * BWD_BQ;
+      const int q0 = (i_first + it) * BWD_BQ + hsel * 32;
       if (!wait_on(&bars[ITER_DONE + (it & 1)], (it >> 1) & 1, abort_flag, p.status, ST_TIMEOUT_TMEM_FULL)) { ok = false; break; }
       tc_fence_after();
+      uint32_t v[32];
+      tmem_ld_x32(t_lane + BCOL_DQ + hsel * 32, v);
+      tmem_ld_wait();
+      tc_fence_before();   // everything is in registers: the next dQ^T may overwrite the accumulator
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&bars[DQ_FREE]);
+      float* dst = p.dq32 + (static_cast<size_t>(row_base) + q0) * row_floats + h * D + dlane;
+      const int valid = min(32, p.S - q0);
 #pragma unroll
-      for (int half = 0; half < 2; ++half) {
-        uint32_t v[32];
-        tmem_ld_x32(t_lane + BCOL_DQ + half * 32, v);
-        tmem_ld_wait();
-        if (half == 1) {   // everything is in registers: the next dQ^T may overwrite the accumulator
-          tc_fence_before();
-          __syncwarp();
-          if (lane == 0) mbar_arrive(&bars[DQ_FREE]);
-        }
-#pragma unroll
-        for (int j = 0; j < 32; ++j) {
-          const int q = q0 + half * 32 + j;
-          if (q < p.S) atomicAdd(p.dq32 + (static_cast<size_t>(row_base) + q) * (p.H * D) + h * D + dlane, __uint_as_float(v[j]));
-        }
-      }
+      for (int j = 0; j < 32; ++j)
+        if (j < valid) atomicAdd(dst + j * row_floats, __uint_as_float(v[j]));
     }
   }
 

@@ -144,6 +144,21 @@ def case_attention(args, pk) -> list:
     ms = timed(lambda: attention.forward(q, k, v, causal=causal), args.iters, args.warmup)
     rows.append({"kernel": "flash_fwd_kernel (in-tree)", "shape": [b, h, s, d], "causal": causal, "ms": ms, "TFLOPs": flops / ms / 1e9,
                  f"frac_of_{pk['source']}_bf16": flops / ms / 1e9 / pk["bf16_tflops"]})
+    if d == 128:
+        out, lse = attention.forward(q, k, v, causal=causal)
+        dout = torch.randn(b, s, h * d, device="cuda").bfloat16()
+        dqkv = torch.empty_like(qkv)
+        dq, dk, dv = (t.transpose(1, 2) for t in dqkv.view(b, s, h, 3 * d).split(d, dim=-1))
+        ms = timed(lambda: attention.backward(q, k, v, out, dout, lse, dq, dk, dv, causal=causal), args.iters, args.warmup)
+        rows.append({"kernel": "flash_bwd_kernel + delta + dq convert (in-tree)", "shape": [b, h, s, d], "causal": causal, "ms": ms,
+                     "TFLOPs": 2.5 * flops / ms / 1e9})
+        if not args.only_ours:
+            ql, kl, vl = (t.detach().clone().requires_grad_(True) for t in (q, k, v))
+            ol = F.scaled_dot_product_attention(ql, kl, vl, is_causal=causal)
+            gl = dout.view(b, s, h, d).transpose(1, 2)
+            ms = timed(lambda: torch.autograd.grad(ol, (ql, kl, vl), gl, retain_graph=True), args.iters, args.warmup)
+            rows.append({"kernel": "scaled_dot_product_attention backward (library)", "shape": [b, h, s, d], "causal": causal, "ms": ms,
+                         "TFLOPs": 2.5 * flops / ms / 1e9})
     if not args.only_ours:
         ms = timed(lambda: F.scaled_dot_product_attention(q, k, v, is_causal=causal), args.iters, args.warmup)
         rows.append({"kernel": "scaled_dot_product_attention (library)", "shape": [b, h, s, d], "causal": causal, "ms": ms, "TFLOPs": flops / ms / 1e9})
