@@ -186,3 +186,36 @@ def test_override_parsing_keeps_on_off_as_strings():
     assert parse_override("3") == 3 and parse_override("1e-3") == pytest.approx(1e-3) or isinstance(parse_override("1e-3"), (float, str))
     assert parse_override("null") is None and parse_override("[a, on]") == ["a", "on"]
     assert math.isclose(parse_override("0.5"), 0.5)
+
+
+def test_attention_helpers_on_cpu():
+    """Layout helpers and the fp32 formula used as the oracle of the attention kernels (the kernels themselves need a B200)."""
+    import torch
+
+    from stacr_b200.ops import attention, nn_ops
+
+    b, s, h, d = 2, 6, 3, 8
+    torch.manual_seed(0)
+    qkv = torch.randn(b * s, 3 * h * d)
+    qi, ki, vi = attention.qkv_views(qkv, b, s, h, d, "interleaved")
+    qb, kb, vb = attention.qkv_views(qkv, b, s, h, d, "blocked")
+    assert qi.shape == qb.shape == (b, h, s, d)
+    # both are views into the same storage, at the columns their layout names
+    assert qi.data_ptr() == qkv.data_ptr() and ki.data_ptr() == qkv.data_ptr() + d * 4 and vb.data_ptr() == qkv.data_ptr() + 2 * h * d * 4
+    assert torch.equal(qi[1, 2, 3], qkv[1 * s + 3, 2 * 3 * d: 2 * 3 * d + d]) and torch.equal(kb[1, 2, 3], qkv[1 * s + 3, h * d + 2 * d: h * d + 3 * d])
+    ref = attention.reference(qi, ki, vi, causal=True)
+    want = torch.nn.functional.scaled_dot_product_attention(qi, ki, vi, is_causal=True).transpose(1, 2).reshape(b, s, h * d)
+    torch.testing.assert_close(ref, want, rtol=1e-5, atol=1e-5)
+    keep = torch.ones(b, s, dtype=torch.bool)
+    keep[0, 4:] = False
+    masked = attention.reference(qi, ki, vi, causal=False, key_mask=keep)
+    bias = keep[:, None, None, :]
+    want = torch.nn.functional.scaled_dot_product_attention(qi, ki, vi, attn_mask=bias).transpose(1, 2).reshape(b, s, h * d)
+    torch.testing.assert_close(masked, want, rtol=1e-5, atol=1e-5)
+    assert not attention.fused_supported(qkv, d) and not attention.supported(qi, ki, vi)
+    with pytest.raises(ValueError):
+        attention.qkv_views(qkv, b, s, h, d, "strided")
+    # the fused block ops fall back to plain arithmetic off the GPU
+    x, y, z = torch.randn(4, 8), torch.randn(4, 8), torch.randn(4, 8)
+    torch.testing.assert_close(nn_ops.add3(x, y, z), x + y + z)
+    assert not nn_ops.parallel_norms_supported(x, torch.ones(8), torch.zeros(8), torch.ones(8), torch.zeros(8))
