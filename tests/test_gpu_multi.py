@@ -78,3 +78,18 @@ def test_a_rank_that_leaves_between_steps_is_seen_before_the_next_collective(tmp
     survivor = next((l for l in run.stdout.splitlines() if l.startswith("RANK0")), "")
     assert survivor.startswith("RANK0 detected:") and "left at step" in survivor, run.stdout[-1500:] + run.stderr[-2500:]
     assert "RANK1 left" in run.stdout
+
+
+@pytest.mark.skipif(_gpus() < 2, reason="needs two GPUs")
+def test_sharded_optimizer_step_replayed_as_a_graph_on_two_gpus():
+    """The benchmark's own path at a small shape: reduce-to-owner buckets, 1/W optimizer with multicast weight publication,
+    the whole step captured once and replayed; both ranks finish and report one finite number."""
+    if int(os.environ.get("RANK", "0")) != 0:
+        pytest.skip("launched once, from rank 0")
+    run = _launch(["bench.py", "--gpus", "2", "--small", "--steps", "3", "--warmup", "3", "--repeats", "1", "--no-evidence"], 2, 29745)
+    assert run.returncode == 0, run.stdout[-1500:] + run.stderr[-3000:]
+    line = json.loads([l for l in run.stdout.splitlines() if l.startswith("{")][-1])
+    assert line["n_gpus"] == 2 and line["value"] > 0 and line["value"] == line["value"]
+    assert line["config"]["cuda_graph"] is True, line["config"].get("cuda_graph_error")
+    assert line["config"]["optimizer_sharding"].startswith("ZeRO-1")
+    assert line["e2e"]["value"] > 0 and line["gpu_launches"] > 0
