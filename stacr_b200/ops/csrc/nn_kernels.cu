@@ -46,15 +46,17 @@ __global__ void __launch_bounds__(256) layernorm_fwd_kernel(const __nv_bfloat16*
   if (row >= rows) return;
   const int nvec = n >> 3;
   const uint4* xr = reinterpret_cast<const uint4*>(x + static_cast<size_t>(row) * n);
-  float v[MAXV][8];
+  uint4 raw[MAXV];   // the row stays packed (half the registers of its fp32 form) and is unpacked once per pass
   float sum = 0.f;
 #pragma unroll
   for (int i = 0; i < MAXV; ++i) {
     const int vi = lane + i * 32;
     if (vi < nvec) {
-      unpack8(__ldg(xr + vi), v[i]);
+      raw[i] = __ldg(xr + vi);
+      float v[8];
+      unpack8(raw[i], v);
 #pragma unroll
-      for (int j = 0; j < 8; ++j) sum += v[i][j];
+      for (int j = 0; j < 8; ++j) sum += v[j];
     }
   }
   const float mean = warp_sum(sum) / n;
@@ -62,9 +64,11 @@ __global__ void __launch_bounds__(256) layernorm_fwd_kernel(const __nv_bfloat16*
 #pragma unroll
   for (int i = 0; i < MAXV; ++i) {
     if (lane + i * 32 < nvec) {
+      float v[8];
+      unpack8(raw[i], v);
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
-        const float d = v[i][j] - mean;
+        const float d = v[j] - mean;
         sq = fmaf(d, d, sq);
       }
     }
@@ -88,7 +92,10 @@ __global__ void __launch_bounds__(256) layernorm_fwd_kernel(const __nv_bfloat16*
         b[0] = b0.x; b[1] = b0.y; b[2] = b0.z; b[3] = b0.w; b[4] = b1.x; b[5] = b1.y; b[6] = b1.z; b[7] = b1.w;
       }
 #pragma unroll
-      for (int j = 0; j < 8; ++j) o[j] = (v[i][j] - mean) * rstd * g[j] + b[j];
+      float v[8];
+      unpack8(raw[i], v);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) o[j] = (v[j] - mean) * rstd * g[j] + b[j];
       yr[vi] = pack8(o);
       if (y2) {
         const float4 h0 = __ldg(reinterpret_cast<const float4*>(gamma2) + vi * 2), h1 = __ldg(reinterpret_cast<const float4*>(gamma2) + vi * 2 + 1);
@@ -99,14 +106,14 @@ __global__ void __launch_bounds__(256) layernorm_fwd_kernel(const __nv_bfloat16*
           b2[0] = c0.x; b2[1] = c0.y; b2[2] = c0.z; b2[3] = c0.w; b2[4] = c1.x; b2[5] = c1.y; b2[6] = c1.z; b2[7] = c1.w;
         }
 #pragma unroll
-        for (int j = 0; j < 8; ++j) o[j] = (v[i][j] - mean) * rstd * g2[j] + b2[j];
+        for (int j = 0; j < 8; ++j) o[j] = (v[j] - mean) * rstd * g2[j] + b2[j];
         reinterpret_cast<uint4*>(y2 + static_cast<size_t>(row) * n)[vi] = pack8(o);
       }
     }
   }
 }
 
-// dx per row (one warp per row, row kept packed in registers and unpacked twice).
+// dx per row: one warp per row, two passes, the second re-reading the row from L1 / L2 (see layernorm_bwd_dx2_kernel).
 template <int MAXV>
 __global__ void __launch_bounds__(256) layernorm_bwd_dx_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x,
                                                                const float* __restrict__ gamma, const float* __restrict__ mean,
@@ -118,25 +125,17 @@ __global__ void __launch_bounds__(256) layernorm_bwd_dx_kernel(const __nv_bfloat
   const int nvec = n >> 3;
   const uint4* xr = reinterpret_cast<const uint4*>(x + static_cast<size_t>(row) * n);
   const uint4* dr = reinterpret_cast<const uint4*>(dy + static_cast<size_t>(row) * n);
+  const float4* gv = reinterpret_cast<const float4*>(gamma);
   const float mu = mean[row], rs = rstd[row];
-  uint4 xraw[MAXV], draw[MAXV];
   float s1 = 0.f, s2 = 0.f;
 #pragma unroll
   for (int i = 0; i < MAXV; ++i) {
     const int vi = lane + i * 32;
     if (vi < nvec) {
-      xraw[i] = __ldg(xr + vi);
-      draw[i] = __ldg(dr + vi);
-    }
-  }
-#pragma unroll
-  for (int i = 0; i < MAXV; ++i) {
-    const int vi = lane + i * 32;
-    if (vi < nvec) {
       float xv[8], dv[8];
-      unpack8(xraw[i], xv);
-      unpack8(draw[i], dv);
-      const float4 g0 = __ldg(reinterpret_cast<const float4*>(gamma) + vi * 2), g1 = __ldg(reinterpret_cast<const float4*>(gamma) + vi * 2 + 1);
+      unpack8(__ldg(xr + vi), xv);
+      unpack8(__ldg(dr + vi), dv);
+      const float4 g0 = __ldg(gv + vi * 2), g1 = __ldg(gv + vi * 2 + 1);
       const float g[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w};
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
@@ -154,9 +153,9 @@ __global__ void __launch_bounds__(256) layernorm_bwd_dx_kernel(const __nv_bfloat
     const int vi = lane + i * 32;
     if (vi < nvec) {
       float xv[8], dv[8], o[8];
-      unpack8(xraw[i], xv);
-      unpack8(draw[i], dv);
-      const float4 g0 = __ldg(reinterpret_cast<const float4*>(gamma) + vi * 2), g1 = __ldg(reinterpret_cast<const float4*>(gamma) + vi * 2 + 1);
+      unpack8(__ldg(xr + vi), xv);
+      unpack8(__ldg(dr + vi), dv);
+      const float4 g0 = __ldg(gv + vi * 2), g1 = __ldg(gv + vi * 2 + 1);
       const float g[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w};
 #pragma unroll
       for (int j = 0; j < 8; ++j) o[j] = rs * (dv[j] * g[j] - s1 - (xv[j] - mu) * rs * s2);
@@ -174,6 +173,9 @@ __global__ void __launch_bounds__(256) layernorm_bwd_dx2_kernel(const __nv_bfloa
                                                                 const float* __restrict__ gamma1, const float* __restrict__ gamma2,
                                                                 const float* __restrict__ mean, const float* __restrict__ rstd, int rows, int n,
                                                                 __nv_bfloat16* __restrict__ dx) {
+  // Two passes over the row, the second re-reading it (from L1 / L2: the same warp has just touched those lines) instead of
+  // keeping three operands of the row in registers: 243 registers allowed one 8-warp CTA per SM and the kernel ran at a third
+  // of the memory bandwidth; at ~64 registers four CTAs are resident and their phases overlap.
   const int lane = threadIdx.x & 31;
   const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (row >= rows) return;
@@ -182,44 +184,32 @@ __global__ void __launch_bounds__(256) layernorm_bwd_dx2_kernel(const __nv_bfloa
   const uint4* xr = reinterpret_cast<const uint4*>(x + off);
   const uint4* d1 = reinterpret_cast<const uint4*>(dy1 + off);
   const uint4* d2 = reinterpret_cast<const uint4*>(dy2 + off);
+  const float4* g1v = reinterpret_cast<const float4*>(gamma1);
+  const float4* g2v = reinterpret_cast<const float4*>(gamma2);
   const float mu = mean[row], rs = rstd[row];
-  uint4 xraw[MAXV], raw1[MAXV], raw2[MAXV];
-  float a1 = 0.f, a2 = 0.f, b1 = 0.f, b2 = 0.f;
-#pragma unroll
-  for (int i = 0; i < MAXV; ++i) {
-    const int vi = lane + i * 32;
-    if (vi < nvec) {
-      xraw[i] = __ldg(xr + vi);
-      raw1[i] = __ldg(d1 + vi);
-      raw2[i] = __ldg(d2 + vi);
-    }
-  }
+  float a1 = 0.f, a2 = 0.f;
 #pragma unroll
   for (int i = 0; i < MAXV; ++i) {
     const int vi = lane + i * 32;
     if (vi < nvec) {
       float xv[8], u[8], w[8];
-      unpack8(xraw[i], xv);
-      unpack8(raw1[i], u);
-      unpack8(raw2[i], w);
-      const float4 g0 = __ldg(reinterpret_cast<const float4*>(gamma1) + vi * 2), g1 = __ldg(reinterpret_cast<const float4*>(gamma1) + vi * 2 + 1);
-      const float4 h0 = __ldg(reinterpret_cast<const float4*>(gamma2) + vi * 2), h1 = __ldg(reinterpret_cast<const float4*>(gamma2) + vi * 2 + 1);
+      unpack8(__ldg(xr + vi), xv);
+      unpack8(__ldg(d1 + vi), u);
+      unpack8(__ldg(d2 + vi), w);
+      const float4 g0 = __ldg(g1v + vi * 2), g1 = __ldg(g1v + vi * 2 + 1), h0 = __ldg(g2v + vi * 2), h1 = __ldg(g2v + vi * 2 + 1);
       const float g[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w};
       const float h[8] = {h0.x, h0.y, h0.z, h0.w, h1.x, h1.y, h1.z, h1.w};
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
-        const float xh = (xv[j] - mu) * rs;
-        const float p = u[j] * g[j], q = w[j] * h[j];
-        a1 += p;
-        a2 = fmaf(p, xh, a2);
-        b1 += q;
-        b2 = fmaf(q, xh, b2);
+        // the two backward formulas are linear in (sum, sum * xhat): the moments of both branches add
+        const float t = fmaf(u[j], g[j], w[j] * h[j]);
+        a1 += t;
+        a2 = fmaf(t, (xv[j] - mu) * rs, a2);
       }
     }
   }
-  // the two backward formulas are linear in (sum, sum * xhat): add the moments of both branches
-  const float s1 = (warp_sum(a1) + warp_sum(b1)) / n;
-  const float s2 = (warp_sum(a2) + warp_sum(b2)) / n;
+  const float s1 = warp_sum(a1) / n;
+  const float s2 = warp_sum(a2) / n;
   uint4* dxr = reinterpret_cast<uint4*>(dx + off);
   const uint4* rr = res ? reinterpret_cast<const uint4*>(res + off) : nullptr;
 #pragma unroll
@@ -227,16 +217,15 @@ __global__ void __launch_bounds__(256) layernorm_bwd_dx2_kernel(const __nv_bfloa
     const int vi = lane + i * 32;
     if (vi < nvec) {
       float xv[8], u[8], w[8], o[8], r[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-      unpack8(xraw[i], xv);
-      unpack8(raw1[i], u);
-      unpack8(raw2[i], w);
+      unpack8(__ldg(xr + vi), xv);
+      unpack8(__ldg(d1 + vi), u);
+      unpack8(__ldg(d2 + vi), w);
       if (rr) unpack8(__ldg(rr + vi), r);
-      const float4 g0 = __ldg(reinterpret_cast<const float4*>(gamma1) + vi * 2), g1 = __ldg(reinterpret_cast<const float4*>(gamma1) + vi * 2 + 1);
-      const float4 h0 = __ldg(reinterpret_cast<const float4*>(gamma2) + vi * 2), h1 = __ldg(reinterpret_cast<const float4*>(gamma2) + vi * 2 + 1);
+      const float4 g0 = __ldg(g1v + vi * 2), g1 = __ldg(g1v + vi * 2 + 1), h0 = __ldg(g2v + vi * 2), h1 = __ldg(g2v + vi * 2 + 1);
       const float g[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w};
       const float h[8] = {h0.x, h0.y, h0.z, h0.w, h1.x, h1.y, h1.z, h1.w};
 #pragma unroll
-      for (int j = 0; j < 8; ++j) o[j] = fmaf(rs, u[j] * g[j] + w[j] * h[j] - s1 - (xv[j] - mu) * rs * s2, r[j]);
+      for (int j = 0; j < 8; ++j) o[j] = fmaf(rs, fmaf(u[j], g[j], w[j] * h[j]) - s1 - (xv[j] - mu) * rs * s2, r[j]);
       dxr[vi] = pack8(o);
     }
   }
