@@ -374,20 +374,50 @@ __global__ void __launch_bounds__(256) dw_fused_kernel(const float* __restrict__
   }
 }
 
-// colsum[o] = sum_rows dy[row, o]  (bias gradient); fp32 atomics over row slabs.
-__global__ void __launch_bounds__(256) colsum_kernel(const __nv_bfloat16* dy, int rows, int o_total, int ldy, int slab,
-                                                     float* out) {
-  const int o = (blockIdx.x * blockDim.x + threadIdx.x) * 2;
-  if (o >= o_total) return;
+// colsum[o] = sum_rows dy[row, o]  (bias gradient).  A CTA owns 256 columns x a slab of 256 rows: its 8 warps take every
+// eighth row (a warp reads 512 contiguous bytes of a row with 16-byte loads, 4 rows in flight), the warps' partial sums meet in
+// shared memory, and one fp32 atomic per column and CTA goes out: 32 atomics per address for 8192 rows (more slabs made the
+// same-address atomics the bottleneck, fewer CTAs left the SMs idle).
+constexpr int CSUM_COLS = 256, CSUM_SLAB = 256, CSUM_UNROLL = 4;
+__global__ void __launch_bounds__(256) colsum_kernel(const __nv_bfloat16* dy, int rows, int o_total, int ldy, int slab, float* out) {
+  __shared__ float s_part[8][CSUM_COLS + 8];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int o = blockIdx.x * CSUM_COLS + lane * 8;
   const int r0 = blockIdx.y * slab, r1 = min(rows, r0 + slab);
-  float a = 0.f, b = 0.f;
-  for (int row = r0; row < r1; ++row) {
-    const __nv_bfloat162 v = *reinterpret_cast<const __nv_bfloat162*>(dy + static_cast<size_t>(row) * ldy + o);
-    a += __low2float(v);
-    b += __high2float(v);
+  float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+  const bool vec = (o + 8 <= o_total) && ((ldy & 7) == 0) && ((reinterpret_cast<uintptr_t>(dy) & 15) == 0);
+  if (vec) {
+    for (int row = r0 + warp; row < r1; row += 8 * CSUM_UNROLL) {
+      uint4 raw[CSUM_UNROLL];
+#pragma unroll
+      for (int u = 0; u < CSUM_UNROLL; ++u)
+        raw[u] = row + 8 * u < r1 ? __ldg(reinterpret_cast<const uint4*>(dy + static_cast<size_t>(row + 8 * u) * ldy + o)) : make_uint4(0u, 0u, 0u, 0u);
+#pragma unroll
+      for (int u = 0; u < CSUM_UNROLL; ++u) {
+        const uint32_t w[4] = {raw[u].x, raw[u].y, raw[u].z, raw[u].w};
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          acc[2 * k] += __uint_as_float(w[k] << 16);
+          acc[2 * k + 1] += __uint_as_float(w[k] & 0xFFFF0000u);
+        }
+      }
+    }
+  } else if (o < o_total) {
+    for (int row = r0 + warp; row < r1; row += 8)
+#pragma unroll
+      for (int j = 0; j < 8; ++j)
+        if (o + j < o_total) acc[j] += __bfloat162float(dy[static_cast<size_t>(row) * ldy + o + j]);
   }
-  atomicAdd(out + o, a);
-  if (o + 1 < o_total) atomicAdd(out + o + 1, b);
+#pragma unroll
+  for (int j = 0; j < 8; ++j) s_part[warp][lane * 8 + j] = acc[j];
+  __syncthreads();
+  const int col = blockIdx.x * CSUM_COLS + threadIdx.x;
+  if (col < o_total) {
+    float total = 0.f;
+#pragma unroll
+    for (int w = 0; w < 8; ++w) total += s_part[w][threadIdx.x];
+    atomicAdd(out + col, total);
+  }
 }
 
 // 8 output features per thread need 16-byte aligned dY rows and enough output features to fill the wider CTA.
@@ -503,10 +533,9 @@ extern "C" int sb_dw_fused_sink(const float* t, int ldt, const float* q, int r, 
 extern "C" int sb_colsum_bf16(const void* dy, int rows, int o_total, int ldy, float* out, void* stream) {
   using namespace sb;
   if (rows <= 0 || o_total <= 0) return 0;
-  if (ldy & 1) return -2;
-  const int slab = 256;
-  dim3 grid((o_total / 2 + 255) / 256 + 1, (rows + slab - 1) / slab);
-  colsum_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(static_cast<const __nv_bfloat16*>(dy), rows, o_total, ldy,
-                                                                      slab, out);
+  int slab = sb::CSUM_SLAB;
+  while ((rows + slab - 1) / slab > 65535) slab *= 2;   // grid.y limit
+  dim3 grid((o_total + sb::CSUM_COLS - 1) / sb::CSUM_COLS, (rows + slab - 1) / slab);
+  sb::colsum_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(static_cast<const __nv_bfloat16*>(dy), rows, o_total, ldy, slab, out);
   return static_cast<int>(cudaGetLastError());
 }

@@ -293,3 +293,18 @@ def test_neox_layer_with_fused_norms_matches_the_unfused_layer():
     for n, p in layer.named_parameters():
         ref = p.grad.float()
         assert float((grads_fused[n].float() - ref).abs().max()) <= 5e-2 * float(ref.abs().max()) + 1e-3, n
+
+
+@pytest.mark.parametrize("rows,cols,view_off", [(1000, 776, 0), (8192, 2048, 0), (300, 264, 8), (129, 1030, 0), (64, 6, 0)])
+def test_column_sums_match_the_fp32_sum(rows, cols, view_off):
+    """Bias-gradient column sums: ragged row counts, widths that are no multiple of 8, and a strided view."""
+    from stacr_b200.ops import _lib, stacr_ops
+
+    g = torch.Generator(device="cuda").manual_seed(rows + cols)
+    frame = torch.randn(rows, cols + 2 * view_off, device="cuda", generator=g).bfloat16()
+    dy = frame[:, view_off:view_off + cols] if view_off else frame
+    got = stacr_ops.colsum(dy)
+    torch.cuda.synchronize()
+    _lib.check_status()
+    want = dy.float().sum(0)
+    torch.testing.assert_close(got, want, rtol=1e-3, atol=1e-2 * float(want.abs().max()) + 1e-3)
