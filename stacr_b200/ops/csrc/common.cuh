@@ -73,6 +73,19 @@ __device__ __forceinline__ uint32_t mbar_try_wait(uint64_t* bar, uint32_t parity
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
                                           int* status, int code,
                                           uint64_t limit_ns = SB_WAIT_LIMIT_NS) {
+  // Non-blocking probe first: on the MMA thread's critical path the barrier has usually completed already, and the probe
+  // answers sooner than the (potentially suspending) try_wait.
+  {
+    uint32_t done;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(done)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    if (done) return true;
+  }
   uint32_t polls = 0;
   uint64_t t0 = 0;
   while (!mbar_try_wait(bar, parity)) {
