@@ -14,7 +14,7 @@ Two measurements, each the median of ``--repeats`` back-to-back timed regions of
 (every region bracketed by barrier + synchronize and timed with CUDA events, max over ranks):
 (1) device-resident inputs, no host read-back -> ``value``; (2) end to end through the public API,
 with the step's token batch copied from pinned host memory and the loss read back every step ->
-``e2e``.  After the timed regions one extra step measures, for both arms alike, the cosine of every
+``e2e``.  After the timed regions eight extra passes (one per synthetic batch) measure, for both arms alike, the cosine of every
 wrapped layer's weight gradient to the dense ``dY^T X`` and the bytes autograd actually saved inside
 the wrapped layers.  One JSON line is printed by rank 0.
 """
@@ -105,7 +105,7 @@ def timed_region(torch, dist, steps, step_fn, world):
 
 
 def fidelity_and_saved_bytes(torch, model, layers, run_forward_backward):
-    """Evidence gathered by one extra step outside every timed region, identically for both arms.
+    """Evidence gathered by one extra forward + backward pass outside every timed region, identically for both arms.
 
     * Saved bytes, measured: while a wrapped layer's forward runs, every tensor autograd saves that is not a parameter is
       recorded through ``saved_tensors_hooks`` (distinct storage addresses, so a tensor saved twice counts once); the
@@ -172,10 +172,24 @@ def fidelity_and_saved_bytes(torch, model, layers, run_forward_backward):
             "dw_cosine_layers": len(cosines), "saved_bytes_measured": state["bytes"], "dense_bytes": state["dense"]}
 
 
+PREP_STEPS = 5              # untimed training steps on batches 0..4 before the warm-up, identical in both arms (see run_ours)
+EVIDENCE_STEPS = 8          # one per synthetic batch: the tracked bases favour the batches seen last, so a single batch would
+                            # make the figure depend on where in the cycle the timed regions happened to stop
+
+
 def guarded_evidence(torch, model, layers, run_forward_backward):
-    """The evidence step must never cost the benchmark its line: a failure is reported on stderr and the fields stay null."""
+    """The evidence steps must never cost the benchmark its line: a failure is reported on stderr and the fields stay null.
+
+    ``run_forward_backward(i)`` runs one training-mode forward + backward on synthetic batch ``i``; it is called for every batch
+    of the cycle and the cosines are averaged (worst = worst layer of any batch).  Saved bytes are those of the first step."""
     try:
-        return fidelity_and_saved_bytes(torch, model, layers, run_forward_backward)
+        runs = [fidelity_and_saved_bytes(torch, model, layers, lambda i=i: run_forward_backward(i)) for i in range(EVIDENCE_STEPS)]
+        out = dict(runs[0])
+        out["dw_cosine_mean"] = sum(r["dw_cosine_mean"] for r in runs) / len(runs)
+        worst = [r["dw_cosine_worst"] for r in runs if r["dw_cosine_worst"] is not None]
+        out["dw_cosine_worst"] = min(worst) if worst else None
+        out["dw_cosine_per_batch"] = [round(r["dw_cosine_mean"], 4) for r in runs]
+        return out
     except Exception as exc:  # noqa: BLE001
         print(f"evidence step failed: {type(exc).__name__}: {exc}", file=sys.stderr, flush=True)
         return None
@@ -351,16 +365,24 @@ def run_ours(args):
         # the whole step (forward, backward, optimizer) captured once and replayed: one launch per step instead of ~2000
         from stacr_b200.graphs import GraphedStep
 
+        # PREP_STEPS untimed training steps on batches 0..4 precede the warm-up in both arms and in the eager mode: here they are
+        # two eager steps (bases initialised, caches filled), the two warm-up runs of the capture and the captured step itself
         for i in range(2):
-            eager_step(dev_batches[i])          # bases initialised, caches filled
+            eager_step(dev_batches[i])
         before = _lib.launch_count() + opt.kernel_launches
         try:
-            graphed = GraphedStep(core_step, [dev_batches[0]], optimizer=opt, layers=layers, first_step=counter["step"], warmup=2)
+            graphed = GraphedStep(core_step, [dev_batches[0]], optimizer=opt, layers=layers, first_step=counter["step"], warmup=2,
+                                  prep_inputs=[[dev_batches[2]], [dev_batches[3]], [dev_batches[4]]])
+            counter["step"] += 3
             graph_launches = (_lib.launch_count() + opt.kernel_launches - before) // 3     # two warm-up runs and the capture
         except Exception as exc:  # noqa: BLE001 - a capture the driver refuses must not cost the measurement: time the eager step
             graphed, graph_error = None, f"{type(exc).__name__}: {str(exc)[:160]}"
             torch.cuda.synchronize()
             print(f"[bench] CUDA graph capture failed on rank {rank}, timing the eager step instead: {graph_error}", file=sys.stderr, flush=True)
+
+    if graphed is None:
+        for i in range(0 if graph_error is None else 2, PREP_STEPS):
+            eager_step(dev_batches[i])
 
     def train_step(ids):
         if graphed is not None:
@@ -397,7 +419,7 @@ def run_ours(args):
     _lib.check_status(dev)
     peak = torch.cuda.max_memory_allocated(dev)
 
-    def evidence_step():
+    def evidence_step(i):
         S.set_step(layers, counter["step"] + 8)
         counter["step"] += 1
         if sync is not None:
@@ -405,7 +427,7 @@ def run_ours(args):
         else:
             opt.zero_grad(set_to_none=True)
         with torch.autocast("cuda", dtype=torch.bfloat16):
-            loss = model(input_ids=dev_batches[0], labels=dev_batches[0]).loss
+            loss = model(input_ids=dev_batches[i % len(dev_batches)], labels=dev_batches[i % len(dev_batches)]).loss
         loss.backward()
         if sync is not None:
             sync.finish()
@@ -449,7 +471,8 @@ def run_ours(args):
                        "how": "measured: bytes of the non-parameter tensors autograd saved inside the wrapped layers' forwards (saved_tensors_hooks) plus their persistent bases; the unsuffixed figure is the layers' stored_bytes() formula"},
             "fidelity": None if evidence is None else {
                 "dw_cosine_mean": evidence["dw_cosine_mean"], "dw_cosine_worst": evidence["dw_cosine_worst"], "layers": evidence["dw_cosine_layers"],
-                "how": "one extra step after the timed regions: each wrapped layer's weight.grad against fp32 dY^T X formed from the same input and output gradient"},
+                "dw_cosine_per_batch": evidence.get("dw_cosine_per_batch"),
+                "how": "eight extra forward + backward passes after the timed regions, one per synthetic batch, no optimizer step: each wrapped layer's weight.grad against fp32 dY^T X formed from the same input and output gradient; mean over layers and batches, worst layer of any batch"},
         })
     if world > 1:
         dist.destroy_process_group()
@@ -518,6 +541,8 @@ def run_reference(args):
         if i == args.steps - 1:
             last["loss"] = reader.drain()
 
+    for i in range(PREP_STEPS):                 # the same untimed steps on batches 0..4 that this framework's arm takes
+        step_device(i)
     warm = max(3, args.warmup)
     for i in range(warm):
         step_e2e(i)
@@ -529,12 +554,12 @@ def run_reference(args):
         secs_e2e, secs_e2e_all = timed_regions(torch, dist, args.steps, step_e2e, world, args.repeats)
     peak = torch.cuda.max_memory_allocated(dev)
 
-    def evidence_step():
+    def evidence_step(i):
         ref.set_step(layers, counter["step"])
         counter["step"] += 1
         opt.zero_grad(set_to_none=True)
         with torch.autocast("cuda", dtype=torch.bfloat16):
-            loss = net(input_ids=dev_batches[0], labels=dev_batches[0]).loss
+            loss = net(input_ids=dev_batches[i % len(dev_batches)], labels=dev_batches[i % len(dev_batches)]).loss
         loss.backward()
 
     evidence = None if args.no_evidence else guarded_evidence(torch, model, layers, evidence_step)
@@ -566,7 +591,8 @@ def run_reference(args):
                        "dense_saved_gb_same_layers": None if evidence is None else evidence["dense_bytes"] / 1e9},
             "fidelity": None if evidence is None else {
                 "dw_cosine_mean": evidence["dw_cosine_mean"], "dw_cosine_worst": evidence["dw_cosine_worst"], "layers": evidence["dw_cosine_layers"],
-                "how": "one extra step after the timed regions: each wrapped layer's weight.grad against fp32 dY^T X formed from the same input and output gradient"},
+                "dw_cosine_per_batch": evidence.get("dw_cosine_per_batch"),
+                "how": "eight extra forward + backward passes after the timed regions, one per synthetic batch, no optimizer step: each wrapped layer's weight.grad against fp32 dY^T X formed from the same input and output gradient; mean over layers and batches, worst layer of any batch"},
         })
     if world > 1:
         dist.destroy_process_group()

@@ -36,7 +36,7 @@ class GraphedStep:
     """
 
     def __init__(self, step_fn: Callable, example_inputs: Sequence[torch.Tensor], *, optimizer=None, layers: Iterable = (),
-                 first_step: int = 0, warmup: int = 3):
+                 first_step: int = 0, warmup: int = 3, prep_inputs: Optional[Sequence[Sequence[torch.Tensor]]] = None):
         self.step_fn = step_fn
         self.optimizer = optimizer
         self.layers = list(layers)
@@ -48,14 +48,25 @@ class GraphedStep:
         # eager warm-up on a side stream (lazy initialisation, caches, the allocator's pools), as capture requires
         side = torch.cuda.Stream(device=dev)
         side.wait_stream(torch.cuda.current_stream(dev))
+        # ``prep_inputs``: the inputs of the warm-up steps and of the captured step, in order (each a sequence like
+        # ``example_inputs``).  These are real training steps; feeding them the next batches of the data stream, rather than
+        # the example batch every time, keeps the run on the trajectory an eager loop would have taken.
+        prep = [list(p) for p in (prep_inputs or [])]
         with torch.cuda.stream(side):
-            for _ in range(max(1, warmup)):
+            for k in range(max(1, warmup)):
+                if k < len(prep):
+                    for static, new in zip(self.static_inputs, prep[k]):
+                        static.copy_(new)
                 self._pre()
                 out = step_fn(*self.static_inputs)
         torch.cuda.current_stream(dev).wait_stream(side)
         torch.cuda.synchronize(dev)
         del out
         self.graph = torch.cuda.CUDAGraph()
+        if len(prep) > max(1, warmup):
+            for static, new in zip(self.static_inputs, prep[max(1, warmup)]):
+                static.copy_(new)
+            torch.cuda.synchronize(dev)
         self._pre()
         _layers.GRAPH_BASIS_PAIRS = pairs = []
         try:
