@@ -22,6 +22,7 @@ the wrapped layers.  One JSON line is printed by rank 0.
 from __future__ import annotations
 
 import argparse
+import contextlib
 import json
 import os
 import statistics
@@ -428,9 +429,11 @@ def run_ours(args):
             opt.zero_grad(set_to_none=True)
         with torch.autocast("cuda", dtype=torch.bfloat16):
             loss = model(input_ids=dev_batches[i % len(dev_batches)], labels=dev_batches[i % len(dev_batches)]).loss
-        loss.backward()
         if sync is not None:
-            sync.finish()
+            with sync.no_sync():            # the rank's own gradient is what is compared with its own dense dY^T X: no reduction
+                loss.backward()
+        else:
+            loss.backward()
 
     evidence = None if args.no_evidence else guarded_evidence(torch, model, layers, evidence_step)
     if args.kernel_table:  # every rank runs the extra steps (their collectives need all ranks); rank 0 writes the table
@@ -558,9 +561,11 @@ def run_reference(args):
         ref.set_step(layers, counter["step"])
         counter["step"] += 1
         opt.zero_grad(set_to_none=True)
-        with torch.autocast("cuda", dtype=torch.bfloat16):
-            loss = net(input_ids=dev_batches[i % len(dev_batches)], labels=dev_batches[i % len(dev_batches)]).loss
-        loss.backward()
+        # under DDP the pass runs without the gradient all-reduce: a rank's own gradient is compared with its own dense dY^T X
+        with (net.no_sync() if world > 1 else contextlib.nullcontext()):
+            with torch.autocast("cuda", dtype=torch.bfloat16):
+                loss = net(input_ids=dev_batches[i % len(dev_batches)], labels=dev_batches[i % len(dev_batches)]).loss
+            loss.backward()
 
     evidence = None if args.no_evidence else guarded_evidence(torch, model, layers, evidence_step)
     rows = batch * seq
