@@ -329,12 +329,17 @@ def run_ours(args):
     layers = S.apply_stacr(model, **STACR)
     fused = [layer.weight for layer in layers] if args.fused_dw == "on" else []
     zero = world > 1 and args.zero == "on" and not fused
+    zero_error = None
     if zero:
         # optimizer sharded over the ranks: buckets are reduced to their owners only, every rank updates 1/W of the matrices
         # and its update kernel stores the new bf16 weights through the NVSwitch multicast address (no separate all-gather)
-        sync = ShardedGradSync(model.parameters(), backend=args.comm)
-        opt = AdamW8bit(model.parameters(), lr=2e-5, weight_decay=0.0, bf16_shadow=True, shard=sync)
-    else:
+        try:
+            sync = ShardedGradSync(model.parameters(), backend=args.comm)
+            opt = AdamW8bit(model.parameters(), lr=2e-5, weight_decay=0.0, bf16_shadow=True, shard=sync)
+        except Exception as exc:  # noqa: BLE001 - e.g. a fabric that refuses the symmetric allocations: fall back to the replicated optimizer
+            zero, zero_error = False, f"{type(exc).__name__}: {str(exc)[:160]}"
+            print(f"[bench] sharded optimizer unavailable on rank {rank}, using the replicated one: {zero_error}", file=sys.stderr, flush=True)
+    if not zero:
         sync = GradSync(model.parameters(), backend=args.comm, fused=fused) if world > 1 else None
         opt = AdamW8bit(model.parameters(), lr=2e-5, weight_decay=0.0, bf16_shadow=True)
     host_batches = [t.pin_memory() for t in make_tokens(torch, shape["vocab_size"], batch, seq, 8, 100 + rank)]
@@ -458,6 +463,7 @@ def run_ours(args):
                 "l2": "inputs larger than L2: every step streams 2.8 GB of bf16 weights and > 10 GB of activations through a 126 MB L2",
                 "cuda_graph": graphed is not None,
                 **({"cuda_graph_error": graph_error} if graph_error else {}),
+                **({"optimizer_sharding_error": zero_error} if zero_error else {}),
                 "attention": "in-tree tcgen05 forward + backward on the fused QKV projection" if args.attention == "intree" else "library (scaled_dot_product_attention)",
             },
             "clocks": clocks.summary(),

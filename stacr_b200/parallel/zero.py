@@ -130,7 +130,13 @@ class ShardedGradSync(GradSync):
         self._shadow = None
         self.shadow_flat = None
         if dev.type == "cuda" and self.n_sharded:
-            self._make_shadows(dev)
+            try:
+                self._make_shadows(dev)
+            except Exception:
+                # leave the parameters as they were found (hooks and gradient views gone), so that a caller can fall back to
+                # the replicated path
+                GradSync.close(self)
+                raise
 
     # ------------------------------------------------------------------ bf16 weights
     def _make_shadows(self, dev) -> None:
