@@ -2,6 +2,7 @@
 
     python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 -m experiments.benchmarks.distributed_data
     python -m experiments.benchmarks.distributed_data --smoke      # one CPU rank over gloo, tiny model, 3 steps
+    python -m experiments.benchmarks.distributed_data --dry-run    # print the cell plan; also: --seeds 42,123 --steps N --output FILE
 
 Gradients are averaged by ``stacr_b200.parallel.GradSync`` (flat buffer, bucketed, overlapped with backward; NVLink
 all-reduce kernels when symmetric memory is available, else NCCL/gloo); bases stay rank-local.
@@ -14,6 +15,7 @@ from __future__ import annotations
 import os
 import sys
 import time
+from pathlib import Path
 
 import torch
 import torch.distributed as dist
@@ -92,6 +94,16 @@ def one_run(cell: dict, seed: int, *, device: str, smoke: bool = False) -> dict:
             "comm": sync.backend if sync else "none", "status": "ok"}
 
 
+def _flag(name: str, default: str) -> str:
+    """Value of ``name VALUE`` or ``name=VALUE`` on the command line."""
+    for i, arg in enumerate(sys.argv):
+        if arg == name and i + 1 < len(sys.argv):
+            return sys.argv[i + 1]
+        if arg.startswith(name + "="):
+            return arg.split("=", 1)[1]
+    return default
+
+
 def main() -> int:
     smoke = "--smoke" in sys.argv
     cells = EXPERIMENTS["distributed_data"]["cells"]
@@ -100,6 +112,14 @@ def main() -> int:
     cells = [c for c in cells if (not only or c["method"] == only) and c["method"] not in skip]
     if not cells:
         raise SystemExit("STACR_ARM / STACR_SKIP_ARMS removed every arm")
+    seeds = [int(x) for x in _flag("--seeds", "").replace(",", " ").split()] or SEEDS
+    steps = _flag("--steps", "")
+    if steps:
+        cells = [dict(c, steps=int(steps), measure_from=min(c.get("measure_from", 20), max(1, int(steps) // 4))) for c in cells]
+    if "--dry-run" in sys.argv:
+        import json
+        print(json.dumps({"experiment": "distributed_data", "n_cells": len(cells) * len(seeds), "seeds": seeds, "cells": cells}, indent=1))
+        return 0
     if smoke:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         os.environ.setdefault("MASTER_PORT", "29517")
@@ -110,9 +130,9 @@ def main() -> int:
         dist.destroy_process_group()
         return 0
     rank, world, local = init_distributed("nccl")
-    out = common.RESULTS / "x7_ddp.jsonl"
+    out = Path(_flag("--output", "") or common.RESULTS / "x7_ddp.jsonl")
     for cell in cells:
-        for seed in SEEDS:
+        for seed in seeds:
             try:
                 rec = one_run(cell, seed, device="cuda")
             except torch.cuda.OutOfMemoryError:
