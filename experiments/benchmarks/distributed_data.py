@@ -87,10 +87,15 @@ def one_run(cell: dict, seed: int, *, device: str, smoke: bool = False) -> dict:
         dist.all_gather(buf, torch.tensor([float(peak)], dtype=torch.float64, device=device))
         peaks = [float(b) for b in buf]
     measured = max(0, len(batches) - measure_from)
+    final_loss = float(loss.detach())
+    # the symmetric-memory gradient buffer is mapped outside the caching allocator, so the allocator's peak does not hold it
+    outside = sync.flat.numel() * sync.flat.element_size() if sync and sync.backend == "symm" else 0
+    if sync:
+        sync.close()         # unhook before the next arm builds its own model and buffer
     return {"tag": f"ddp_w{world}", "method": method, "seed": seed, "world_size": world, "model": model_id, "bs_per_rank": bs, "seq": seq,
             "steps": steps, "steps_measured": measured, "n_checkpointed_blocks": n_ckpt, "n_wrapped_layers": len(layers), "time_s": dt,
-            "peak_bytes": peak, "peak_GiB": common.gib(peak), "peak_GiB_all_ranks": [common.gib(p) for p in peaks],
-            "tokens_per_s_per_rank": bs * seq * measured / dt if dt > 0 and measured else None, "final_train_loss": float(loss),
+            "peak_bytes": peak, "peak_GiB": common.gib(peak), "grad_buffer_outside_allocator_GiB": common.gib(outside), "peak_GiB_all_ranks": [common.gib(p) for p in peaks],
+            "tokens_per_s_per_rank": bs * seq * measured / dt if dt > 0 and measured else None, "final_train_loss": final_loss,
             "comm": sync.backend if sync else "none", "status": "ok"}
 
 

@@ -22,6 +22,7 @@ from __future__ import annotations
 import contextlib
 
 import os
+import weakref
 from typing import Iterable
 
 import torch
@@ -198,21 +199,30 @@ class GradSync:
 
     # ------------------------------------------------------------------ hooks
     def _make_hook(self, index: int):
+        # The hook is owned by the tensor's C++ autograd state, which Python's cycle collector cannot see through: a hook that
+        # held this object strongly would tie it (and the flat buffer, and every parameter) to the parameters for ever.
+        ref = weakref.ref(self)
         if index < self.n_fused:
             def fused_hook(param):
-                self._adopt(index, param)
-                self._fused_state[index] = 2      # autograd accumulated a dense gradient locally (layer ran uncompressed)
+                me = ref()
+                if me is None:
+                    return
+                me._adopt(index, param)
+                me._fused_state[index] = 2      # autograd accumulated a dense gradient locally (layer ran uncompressed)
             return fused_hook
 
         def hook(param):
-            self._written[index] = True       # moved into its slot together with the rest of its bucket
-            if not self._syncing or self._counted[index]:
+            me = ref()
+            if me is None:
+                return
+            me._written[index] = True         # moved into its slot together with the rest of its bucket
+            if not me._syncing or me._counted[index]:
                 return                        # a layer that handed its slot over directly has already been counted this pass
-            self._counted[index] = True
-            b = self._bucket_of[index]
-            self._pending[b] -= 1
-            if self._pending[b] == 0:
-                self._launch(b)
+            me._counted[index] = True
+            b = me._bucket_of[index]
+            me._pending[b] -= 1
+            if me._pending[b] == 0:
+                me._launch(b)
         return hook
 
     def _make_ready(self, index: int):

@@ -283,6 +283,27 @@ def test_two_rank_gloo_fused_parameter_slots_and_accumulation(tmp_path):
     assert run.returncode == 0 and run.stdout.count("FUSED_OK") == 2, run.stdout[-2000:] + run.stderr[-2000:]
 
 
+def test_grad_sync_and_its_buffer_are_collected_with_the_model():
+    """The gradient hooks live in the tensors' C++ autograd state, out of the cycle collector's sight: they must not keep the
+    sync object, its flat buffer and every parameter alive after the last outside reference is gone."""
+    import gc
+    import weakref
+
+    import torch
+    from torch import nn
+
+    from stacr_b200.parallel.ddp import GradSync
+
+    model = nn.Sequential(nn.Linear(16, 16), nn.Linear(16, 4))
+    sync = GradSync(model.parameters(), backend="none")
+    model(torch.randn(3, 16)).sum().backward()
+    sync.finish()
+    refs = [weakref.ref(model[0].weight), weakref.ref(sync), weakref.ref(sync.flat)]
+    del model, sync
+    gc.collect()
+    assert all(r() is None for r in refs)
+
+
 def test_gradient_slot_hand_over_counts_each_parameter_once():
     """A layer that wrote a parameter's gradient into its slot calls ``_sb_grad_ready`` and returns nothing to autograd."""
     import torch
