@@ -323,11 +323,14 @@ def _dense_threshold() -> int:
     return int(os.environ.get("STACR_DW_DENSE_MIN", str(1 << 33)))
 
 
-def rebuild_input(coeff: torch.Tensor, basis_fp32: torch.Tensor, residual, rows: int, in_features: int) -> torch.Tensor:
-    """``bf16(C Q^T + S)`` in a per-shape scratch buffer that later calls overwrite (valid until the next call of this shape)."""
+def rebuild_input(coeff: torch.Tensor, basis_fp32: torch.Tensor, residual, rows: int, in_features: int, out: torch.Tensor | None = None) -> torch.Tensor:
+    """``bf16(C Q^T + S)``, written into ``out`` (contiguous bf16 ``[rows, in_features]``) or, without one, into a per-shape
+    scratch buffer that later calls overwrite (valid until the next call of this shape)."""
     dev = coeff.device
     key = (dev.index, rows, in_features)
-    buf = _REBUILD.get(key)
+    buf = out if out is not None else _REBUILD.get(key)
+    if out is not None:
+        assert out.dtype == torch.bfloat16 and out.is_contiguous() and tuple(out.shape) == (rows, in_features)
     if buf is None:
         if len(_REBUILD) > 8:
             _REBUILD.clear()

@@ -336,3 +336,40 @@ def test_sampled_selector_runs_on_the_kernels_and_agrees_with_the_framework_form
     assert common >= 0.9 * min(idx.numel(), ref_idx.numel()), (common, idx.numel(), ref_idx.numel())
     got = e.reshape(-1)[idx.long()].float().abs()
     assert float(got.min()) >= 0.9 * float(ref_val.float().abs().min())
+
+
+def test_saved_tensor_compressor_runs_on_the_kernels_and_agrees_with_the_framework_codec():
+    """``STACRCompressor`` on a bf16 CUDA activation: projection, exact global top-k and the rebuild all on the kernels, against
+    the same basis version through the framework codec in fp32."""
+    from stacr_b200 import compressor as C
+
+    torch.manual_seed(0)
+    x = (torch.randn(768, 12, device="cuda") @ torch.randn(12, 512, device="cuda") + 0.2 * torch.randn(768, 512, device="cuda")).bfloat16()
+    x[5, 7] = 40.0                                                  # an outlier the residual channel must carry
+    comp = C.STACRCompressor(C.STACRConfig(rank=8, residual_budget=0.01, min_features=1, min_numel=1, update_interval=10 ** 9))
+    comp.pack(x)                                                    # step 0: the basis is initialised from this batch
+    comp.set_step(1)
+    packed = comp.pack(x.view(4, 192, 512))
+    assert packed.codec == "kernels" and packed.residual[4] == round(0.01 * x.numel())
+    got = comp.unpack(packed)
+    assert got.shape == (4, 192, 512) and got.dtype == torch.bfloat16
+    xf = x.float()
+    oracle = C._FrameworkCodec.encode(xf, xf, comp._tracker(x), 0.01)
+    want = C._FrameworkCodec.decode(oracle)
+    got2d = got.reshape(768, 512).float()
+    # bf16 basis, coefficients and output against fp32 cost ~0.3 %; the rest is entries near the selection threshold that the two
+    # forms rank differently (each one moves the reconstruction by about the threshold value)
+    assert (got2d - want).norm() / want.norm() < 0.05
+    assert (got2d - xf).norm() <= 1.05 * (want - xf).norm() + 1e-3
+    assert abs(float(got2d[5, 7]) - 40.0) < 0.5
+    # through autograd: the saved activation of tanh is replaced and rebuilt, parameters are left alone
+    w = torch.nn.Parameter(torch.randn(64, 512, device="cuda", dtype=torch.bfloat16) * 0.05)
+    inp = (x * 0.05).detach().requires_grad_(True)
+    comp.set_step(2)
+    with C.stacr_saved_tensors(comp):
+        y = inp.tanh() @ w.t()
+    y.float().sum().backward()
+    plain = (x * 0.05).detach().requires_grad_(True)
+    (plain.tanh() @ w.detach().t()).float().sum().backward()
+    cos = torch.nn.functional.cosine_similarity(inp.grad.float().flatten(), plain.grad.float().flatten(), dim=0)
+    assert torch.isfinite(inp.grad).all() and float(cos) > 0.9
