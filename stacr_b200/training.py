@@ -15,82 +15,110 @@ import importlib
 import math
 import time
 from pathlib import Path
-from typing import Any
+from typing import Any, NamedTuple
 
 import torch
 
 from .surgery import _SELECTION_KEYS, apply_stacr, select_target_names, set_step
 from .utils import device_from_config, set_seed, write_csv
 
-STACR_METHODS = {
-    "stacr", "turbofast", "stacr_galore", "turbofast_galore", "subtrack_stacr", "stacr_checkpointing", "turbofast_checkpointing",
+class _Method(NamedTuple):
+    """What a method name stands for; the trainer reads these flags, never the name's spelling."""
+
+    compresses: bool = False              # wraps linear layers with STAC-R
+    turbo: bool = False                   # residual channel switched off after ``turbo_after_step`` (default 50)
+    optimizer_family: str | None = None   # low-rank-gradient optimizer the method is defined with
+    checkpoints: bool = False             # activation checkpointing on a block stride
+
+
+_METHOD_TABLE = {
+    "baseline": _Method(),
+    "freeze": _Method(),
+    "checkpointing": _Method(checkpoints=True),
+    "galore": _Method(optimizer_family="galore"),
+    "subtrack": _Method(optimizer_family="subtrack"),
+    "stacr": _Method(compresses=True),
+    "turbofast": _Method(compresses=True, turbo=True),
+    "stacr_galore": _Method(compresses=True, optimizer_family="galore"),
+    "turbofast_galore": _Method(compresses=True, turbo=True, optimizer_family="galore"),
+    "subtrack_stacr": _Method(compresses=True, optimizer_family="subtrack"),
+    "stacr_checkpointing": _Method(compresses=True, checkpoints=True),
+    "turbofast_checkpointing": _Method(compresses=True, turbo=True, checkpoints=True),
 }
-METHODS = STACR_METHODS | {"baseline", "checkpointing", "galore", "subtrack", "freeze"}
+STACR_METHODS = {name for name, spec in _METHOD_TABLE.items() if spec.compresses}
+METHODS = set(_METHOD_TABLE)
+_FAMILY_LABEL = {"galore": "GaLore", "subtrack": "SubTrack"}
+TASKS = ("synthetic", "language_modeling", "sequence_classification")
+
+# keys handed to the wrapped layers / the layer selection
 CORE_KEYS = (
     "rank", "residual_budget", "residual_bits", "oja_lr", "update_interval", "warmup_steps", "freeze_after_warmup",
     "turbo_after_step", "chunk_rows", "basis_dtype", "residual_mode", "residual_block_size", "residual_sample_ratio", "surface",
     "min_features", "extra_names", "target_names", "target_pattern", "exclude_names", "trainable_only", "allow_empty",
 )
+# keys of the run itself, grouped by what reads them
 RUN_KEYS = {
-    "task", "method", "engine", "compression", "model_name", "dataset", "device", "seed", "steps", "batch_size", "seq_len",
-    "max_examples", "max_eval_examples", "fidelity_steps", "features", "hidden", "lr", "weight_decay", "optimizer",
-    "use_8bit_optimizer", "gradient_accumulation_steps", "measure_from", "amp", "model_dtype", "lr_warmup_steps", "lr_schedule",
-    "max_grad_norm", "checkpoint_path", "checkpoint_every", "checkpoint_offset", "offload_every", "offload_offset",
-    "compression_blocks", "attention_surface", "freeze_basis_after_warmup", "model_revision", "dataset_revision",
-    "attn_implementation", "local_files_only", "train_file", "validation_file", "galore_rank", "galore_update_proj_gap",
-    "galore_scale", "galore_proj_type", "galore_target_modules", "subtrack_rank", "subtrack_scale", "subtrack_update_interval",
-    "subtrack_step_size", "subtrack_target_modules", "subtrack_proj_type", "subtrack_adaptive_optimizer",
-    "subtrack_recovery_scaling", "subtrack_norm_growth_limit",
+    # what is trained, on what
+    "task", "method", "engine", "compression", "model_name", "model_revision", "model_dtype", "attn_implementation", "local_files_only",
+    "dataset", "dataset_revision", "train_file", "validation_file", "max_examples", "max_eval_examples", "features", "hidden",
+    # the loop
+    "device", "seed", "steps", "batch_size", "seq_len", "gradient_accumulation_steps", "measure_from", "fidelity_steps", "amp",
+    # optimisation
+    "lr", "weight_decay", "optimizer", "use_8bit_optimizer", "lr_warmup_steps", "lr_schedule", "max_grad_norm",
+    "galore_rank", "galore_update_proj_gap", "galore_scale", "galore_proj_type", "galore_target_modules",
+    "subtrack_rank", "subtrack_scale", "subtrack_update_interval", "subtrack_step_size", "subtrack_target_modules",
+    "subtrack_proj_type", "subtrack_adaptive_optimizer", "subtrack_recovery_scaling", "subtrack_norm_growth_limit",
+    # composition with checkpointing / offload, and the saved state
+    "checkpoint_path", "checkpoint_every", "checkpoint_offset", "offload_every", "offload_offset", "compression_blocks",
+    "attention_surface", "freeze_basis_after_warmup",
     # additions of this framework
     "random_init", "vocab_size", "resume_from", "model_overrides",
 }
+_PER_TASK_DEFAULTS = {
+    True: {"method": "turbofast", "steps": 5, "batch_size": 8},       # synthetic
+    False: {"method": "baseline", "steps": 500, "batch_size": 2},     # Hugging Face tasks
+}
+_SHARED_DEFAULTS = {"seed": 42, "gradient_accumulation_steps": 1, "measure_from": 0, "engine": "projection"}
+
+
+def _range_problems(cfg: dict):
+    """Yield ``(violated, message)`` in the order the checks are reported."""
+    yield cfg["engine"] not in ("projection", "adaptive"), "engine must be projection or adaptive"
+    yield cfg["method"] not in METHODS, f"Unknown method {cfg['method']!r}; choose from {sorted(METHODS)}"
+    yield cfg["task"] not in TASKS, f"Unknown task {cfg['task']!r}"
+    for key in ("steps", "batch_size", "gradient_accumulation_steps"):
+        yield int(cfg[key]) < 1, f"{key} must be positive"
+    yield not 0 <= int(cfg["measure_from"]) < int(cfg["steps"]), "measure_from must be in [0, steps)"
+    yield cfg["task"] != "synthetic" and not cfg.get("model_name"), "model_name is required for Hugging Face training"
 
 
 def validate_config(config: dict) -> dict:
-    """Reject unknown keys, fill method-dependent defaults, and check ranges.  Returns a copy."""
+    """A copy of ``config`` with task- and method-dependent defaults filled in; unknown keys, names and ranges are rejected."""
     cfg = copy.deepcopy(config)
-    stray = cfg.keys() - RUN_KEYS - set(CORE_KEYS)
-    if stray:
-        raise ValueError(f"Unknown training configuration fields: {sorted(stray)}")
-    task = cfg.setdefault("task", "synthetic")
-    synthetic = task == "synthetic"
-    cfg.setdefault("method", "turbofast" if synthetic else "baseline")
-    cfg.setdefault("steps", 5 if synthetic else 500)
-    cfg.setdefault("batch_size", 8 if synthetic else 2)
-    cfg.setdefault("seed", 42)
-    cfg.setdefault("gradient_accumulation_steps", 1)
-    cfg.setdefault("measure_from", 0)
-    cfg.setdefault("engine", "projection")
-    if cfg["engine"] not in ("projection", "adaptive"):
-        raise ValueError("engine must be projection or adaptive")
-    method = cfg["method"]
-    if method not in METHODS:
-        raise ValueError(f"Unknown method {method!r}; choose from {sorted(METHODS)}")
-    if task not in ("synthetic", "language_modeling", "sequence_classification"):
-        raise ValueError(f"Unknown task {task!r}")
-    for key in ("steps", "batch_size", "gradient_accumulation_steps"):
-        if int(cfg[key]) < 1:
-            raise ValueError(f"{key} must be positive")
-    if not 0 <= int(cfg["measure_from"]) < int(cfg["steps"]):
-        raise ValueError("measure_from must be in [0, steps)")
-    if not synthetic and not cfg.get("model_name"):
-        raise ValueError("model_name is required for Hugging Face training")
-    if method.startswith("turbofast"):
-        cfg.setdefault("turbo_after_step", 50)
-    elif method in STACR_METHODS:
-        cfg.setdefault("turbo_after_step", None)
-    for family in ("galore", "subtrack"):
-        if family in method:
-            cfg.setdefault("optimizer", family)
-            if cfg["optimizer"] != family:
-                raise ValueError(f"A {'GaLore' if family == 'galore' else 'SubTrack'} method requires optimizer={family}")
-    if "checkpointing" in method:
-        cfg.setdefault("checkpoint_every", 2 if method in STACR_METHODS else 1)
+    unknown = sorted(set(cfg) - RUN_KEYS - set(CORE_KEYS))
+    if unknown:
+        raise ValueError(f"Unknown training configuration fields: {unknown}")
+    cfg.setdefault("task", "synthetic")
+    for key, value in {**_PER_TASK_DEFAULTS[cfg["task"] == "synthetic"], **_SHARED_DEFAULTS}.items():
+        cfg.setdefault(key, value)
+    for violated, message in _range_problems(cfg):
+        if violated:
+            raise ValueError(message)
+    spec = _METHOD_TABLE[cfg["method"]]
+    if spec.compresses:
+        cfg.setdefault("turbo_after_step", 50 if spec.turbo else None)
+    if spec.optimizer_family:
+        if cfg.setdefault("optimizer", spec.optimizer_family) != spec.optimizer_family:
+            raise ValueError(f"A {_FAMILY_LABEL[spec.optimizer_family]} method requires optimizer={spec.optimizer_family}")
+    if spec.checkpoints:
+        cfg.setdefault("checkpoint_every", 2 if spec.compresses else 1)
     return cfg
 
 
+# ---------------------------------------------------------------------------------------------- layer options
 def _projection_options(cfg: dict) -> dict:
-    opts = {k: cfg[k] for k in CORE_KEYS if k in cfg}
+    """Layer options of the projection engine: the core keys present, then the ``compression`` mapping, then the two aliases."""
+    opts = {key: cfg[key] for key in CORE_KEYS if key in cfg}
     if cfg.get("engine", "projection") == "projection":
         opts.update(cfg.get("compression", {}))
     if cfg.get("attention_surface"):
@@ -100,19 +128,20 @@ def _projection_options(cfg: dict) -> dict:
     return opts
 
 
+_ADAPTIVE_PASSTHROUGH = ("basis_dtype", "update_interval", "warmup_steps", "residual_block_size", "residual_mode")
+_ADAPTIVE_RENAMED = {"oja_lr": "oja_learning_rate", "chunk_rows": "chunk_size", "freeze_after_warmup": "freeze_basis_after_warmup"}
+_ADAPTIVE_TURBO = {"post_warmup_residual_mode": "none", "refresh_trigger": "residual_energy", "cache_basis_per_optimizer_step": True,
+                   "oja_update_per_optimizer_step": True}
+
+
 def _adaptive_options(cfg: dict, core: dict) -> dict:
-    """Translate trainer keys into adaptive-engine config fields."""
-    opts = {k: v for k, v in core.items() if k in _SELECTION_KEYS}
-    opts["rank"] = int(cfg.get("rank", 8))
-    opts["residual_budget"] = float(cfg.get("residual_budget", 0.005))
-    for key in ("basis_dtype", "update_interval", "warmup_steps", "residual_block_size", "residual_mode"):
-        if key in cfg:
-            opts[key] = cfg[key]
-    for src, dst in (("oja_lr", "oja_learning_rate"), ("chunk_rows", "chunk_size"), ("freeze_after_warmup", "freeze_basis_after_warmup")):
-        if src in core:
-            opts[dst] = core[src]
-    if "residual_bits" in cfg:
-        bits = cfg["residual_bits"]
+    """The same settings in the adaptive engine's vocabulary (``compression`` entries, already in that vocabulary, win)."""
+    opts = {key: value for key, value in core.items() if key in _SELECTION_KEYS}
+    opts.update(rank=int(cfg.get("rank", 8)), residual_budget=float(cfg.get("residual_budget", 0.005)))
+    opts.update({key: cfg[key] for key in _ADAPTIVE_PASSTHROUGH if key in cfg})
+    opts.update({theirs: core[ours] for ours, theirs in _ADAPTIVE_RENAMED.items() if ours in core})
+    bits = cfg.get("residual_bits")
+    if bits is not None:
         if bits not in (0, 4, 8):
             raise ValueError("residual_bits must be 0, 4, or 8")
         opts["quantize_residuals"] = bits != 0
@@ -120,79 +149,81 @@ def _adaptive_options(cfg: dict, core: dict) -> dict:
             opts["residual_quantize_bits"] = bits
     if "residual_sample_ratio" in cfg:
         raise ValueError("The adaptive engine uses compression.streaming_topk_sample_ratio for threshold sampling")
-    if cfg["method"].startswith("turbofast"):
-        opts.update(
-            post_warmup_residual_mode="none", residual_warmup_steps=int(cfg["turbo_after_step"]),
-            refresh_trigger="residual_energy", cache_basis_per_optimizer_step=True, oja_update_per_optimizer_step=True,
-        )
+    if _METHOD_TABLE[cfg["method"]].turbo:
+        opts.update(_ADAPTIVE_TURBO, residual_warmup_steps=int(cfg["turbo_after_step"]))
     opts.update(cfg.get("compression", {}))
     return opts
 
 
+# ---------------------------------------------------------------------------------------------- composition
+def _strided_blocks(n_blocks: int, every: int, offset: int, what: str) -> list[int]:
+    """Block indices ``offset, offset + every, ...`` of a ``what`` plan (``every == 0``: none)."""
+    if not every:
+        return []
+    if not 0 <= offset < every:
+        raise ValueError(f"{what}_offset must be in [0, {what}_every)")
+    return list(range(offset, n_blocks, every))
+
+
+def _selection_of(options: dict) -> dict:
+    return {key: value for key, value in options.items() if key in _SELECTION_KEYS and key != "allow_empty"}
+
+
 def configure_model(model, config: dict):
-    """Freeze -> wrap -> checkpoint -> offload, in that order, before building the optimizer or DDP."""
+    """Plan, then mutate: freeze -> wrap -> checkpoint -> offload, before any optimizer or gradient synchroniser is built.
+
+    With ``compression_blocks: complement`` (the default) a STAC-R method wraps only the blocks that are *not* checkpointed:
+    a checkpointed block recomputes its activations anyway, so compressing them would cost time and save nothing.
+    """
     from .composition import block_target_names, checkpoint_blocks, offload_blocks, transformer_blocks
 
     cfg = validate_config(config)
-    core = _projection_options(cfg)
+    spec = _METHOD_TABLE[cfg["method"]]
+    options = _projection_options(cfg)
     if cfg["task"] == "synthetic":
-        core.setdefault("surface", "all")
-        core.setdefault("min_features", 1)
+        options.setdefault("surface", "all")
+        options.setdefault("min_features", 1)
     if cfg["engine"] == "adaptive":
-        core = _adaptive_options(cfg, core)
-    mode = cfg.get("compression_blocks", "complement")
-    if mode not in ("complement", "all"):
+        options = _adaptive_options(cfg, options)
+    scope = cfg.get("compression_blocks", "complement")
+    if scope not in ("complement", "all"):
         raise ValueError("compression_blocks must be 'complement' or 'all'")
-    every_ckpt, every_off = int(cfg.get("checkpoint_every", 0)), int(cfg.get("offload_every", 0))
-    if every_ckpt < 0 or every_off < 0:
+    strides = {what: int(cfg.get(f"{what}_every", 0)) for what in ("checkpoint", "offload")}
+    if min(strides.values()) < 0:
         raise ValueError("checkpoint_every and offload_every must be nonnegative")
-    is_stacr = cfg["method"] in STACR_METHODS
-    checkpointed: list[int] = []
-    offloaded: list[int] = []
-    blocks = None
-    if every_ckpt or every_off:
-        blocks = transformer_blocks(model)
-    if every_ckpt:
-        phase = int(cfg.get("checkpoint_offset", 0))
-        if not 0 <= phase < every_ckpt:
-            raise ValueError("checkpoint_offset must be in [0, checkpoint_every)")
-        checkpointed = [i for i in range(len(blocks)) if i % every_ckpt == phase]
-        if is_stacr and mode == "complement":
-            pick = {k: v for k, v in core.items() if k in _SELECTION_KEYS and k != "allow_empty"}
-            names = block_target_names(model, blocks, lambda i: i not in checkpointed, **pick)
-            if not names:
-                raise ValueError("No uncheckpointed STAC-R surface remains; use selective checkpointing")
-            core = {k: v for k, v in core.items() if k not in _SELECTION_KEYS}
-            core["surface"], core["target_names"] = "none", names
-    if every_off:
-        phase = int(cfg.get("offload_offset", 0))
-        if not 0 <= phase < every_off:
-            raise ValueError("offload_offset must be in [0, offload_every)")
-        offloaded = [i for i in range(len(blocks)) if i % every_off == phase]
-    if cfg["method"] == "freeze":
-        pick = {k: v for k, v in core.items() if k in _SELECTION_KEYS and k != "allow_empty"}
-        names = select_target_names(model, **pick)
-        if not names:
-            raise ValueError("No modules selected for the freeze control")
-        for name in names:
-            model.get_submodule(name).requires_grad_(False)
-    layers: list = []
-    if is_stacr:
-        if cfg["engine"] == "adaptive":
-            from .adaptive import apply_adaptive_stacr
 
-            layers = apply_adaptive_stacr(model, core)
+    # ---- plan (nothing is modified yet)
+    blocks = transformer_blocks(model) if any(strides.values()) else None
+    n_blocks = len(blocks) if blocks is not None else 0
+    checkpointed = _strided_blocks(n_blocks, strides["checkpoint"], int(cfg.get("checkpoint_offset", 0)), "checkpoint")
+    if checkpointed and spec.compresses and scope == "complement":
+        remaining = block_target_names(model, blocks, lambda index: index not in checkpointed, **_selection_of(options))
+        if not remaining:
+            raise ValueError("No uncheckpointed STAC-R surface remains; use selective checkpointing")
+        options = {key: value for key, value in options.items() if key not in _SELECTION_KEYS}
+        options.update(surface="none", target_names=remaining)
+    offloaded = _strided_blocks(n_blocks, strides["offload"], int(cfg.get("offload_offset", 0)), "offload")
+    frozen: list[str] = []
+    if cfg["method"] == "freeze":
+        frozen = select_target_names(model, **_selection_of(options))
+        if not frozen:
+            raise ValueError("No modules selected for the freeze control")
+
+    # ---- apply
+    for name in frozen:
+        model.get_submodule(name).requires_grad_(False)
+    layers: list = []
+    if spec.compresses:
+        if cfg["engine"] == "adaptive":
+            from .adaptive import apply_adaptive_stacr as wrap
         else:
-            layers = apply_stacr(model, core)
+            wrap = apply_stacr
+        layers = wrap(model, options)
     if checkpointed:
         checkpoint_blocks(blocks, checkpointed)
     if offloaded:
         offload_blocks(blocks, offloaded)
-    return layers, {
-        "checkpointed_blocks": checkpointed,
-        "offloaded_blocks": offloaded,
-        "wrapped_names": [layer.source_name for layer in layers],
-    }
+    return layers, {"checkpointed_blocks": checkpointed, "offloaded_blocks": offloaded, "wrapped_names": [layer.source_name for layer in layers]}
 
 
 def _build_optimizer(model, config):
