@@ -149,6 +149,11 @@ def test_byte_accounting():
     assert saved_surface_predictor(50.0, 200.0) == 0.25 and saved_surface_predictor(-5, 10) == 0.0
     with pytest.raises(ValueError):
         saved_surface_predictor(1, 0)
+    from stacr_b200.memory import payload_ledger
+
+    items = payload_ledger((128, 64), 8, torch.float16, 0.01, include_basis=True, coeff_bits=8, residual_bits=4)
+    assert items == (128 * 8, 82 * 4, 41, 8, 64 * 8 * 2) and items.total == stacr_stored_bytes((128, 64), 8, torch.float16, 0.01, include_basis=True, coeff_bits=8, residual_bits=4)
+    assert payload_ledger((), 8).total == 2 and payload_ledger((5, 0), 8).total == 0
     ledger = surface_ledger(1000, 100, 10000, basis_bytes=50, workspace_bytes=20)
     assert ledger["ssp"] == 0.09 and ledger["net_after_workspace_bytes"] == 830
 
