@@ -2,6 +2,7 @@
 
     python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 -m experiments.benchmarks.distributed_sharding
     python -m experiments.benchmarks.distributed_sharding --smoke      # one rank, tiny model
+    python -m experiments.benchmarks.distributed_sharding --dry-run    # the cell plan; also: --models a,b --steps N --output FILE
 
 Parity: experiments/benchmarks/distributed_sharding.py:1-362 of the reference project (bf16 parameters, torch AdamW,
 per-rank peak via all_reduce MAX, cohorts up to 14B parameters).  Compression state stays per rank; the sharded
@@ -13,6 +14,7 @@ from __future__ import annotations
 import os
 import sys
 import time
+from pathlib import Path
 
 import torch
 import torch.distributed as dist
@@ -72,7 +74,7 @@ def one_run(cell: dict, seed: int, smoke: bool = False) -> dict:
     cell = dict(cell)
     method = cell.pop("method")
     model_id, bs, seq = ("llama-tiny", 2, 64) if smoke else (cell["model_id"], cell["bs"], cell["seq"])
-    steps, measure_from = (4, 1) if smoke else (30, 10)
+    steps, measure_from = (4, 1) if smoke else (int(cell.get("steps", 30)), int(cell.get("measure_from", 10)))
     device = "cuda" if torch.cuda.is_available() else "cpu"
     common.free_all()
     common.set_seed(seed)
@@ -137,16 +139,37 @@ def run_cohort(name: str, cells, out, smoke: bool = False, seeds=(42,)) -> list:
     return records
 
 
+def _flag(name: str, default: str) -> str:
+    """Value of ``name VALUE`` or ``name=VALUE`` on the command line."""
+    for i, arg in enumerate(sys.argv):
+        if arg == name and i + 1 < len(sys.argv):
+            return sys.argv[i + 1]
+        if arg.startswith(name + "="):
+            return arg.split("=", 1)[1]
+    return default
+
+
 def main() -> int:
     smoke = "--smoke" in sys.argv
+    cells = EXPERIMENTS["distributed_sharding"]["cells"]
+    wanted = set(_flag("--models", "").replace(",", " ").split())
+    if wanted:
+        cells = [c for c in cells if c.get("model_id") in wanted]
+    if _flag("--steps", ""):
+        n = int(_flag("--steps", ""))
+        cells = [dict(c, steps=n, measure_from=max(1, n // 3)) for c in cells]
+    if "--dry-run" in sys.argv:
+        import json
+
+        print(json.dumps({"experiment": "distributed_sharding", "n_cells": len(cells), "cells": cells}, indent=1))
+        return 0
     if smoke and "RANK" not in os.environ:
         os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT="29518", RANK="0", WORLD_SIZE="1", LOCAL_RANK="0")
     cuda = torch.cuda.is_available()
     if cuda:
         torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", "0")))
     dist.init_process_group("nccl" if cuda else "gloo")
-    out = common.RESULTS / "x8_fsdp2.jsonl"
-    cells = EXPERIMENTS["distributed_sharding"]["cells"]
+    out = Path(_flag("--output", "") or common.RESULTS / "x8_fsdp2.jsonl")
     if smoke:
         cells = cells[:2]
     by_model: dict = {}
