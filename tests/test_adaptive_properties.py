@@ -27,7 +27,7 @@ def _grads(layer, x, g):
     return xin.grad, layer.linear.weight.grad.clone(), layer.linear.bias.grad.clone()
 
 
-@settings(max_examples=30, deadline=None)
+@settings(max_examples=30, deadline=None, derandomize=True)
 @given(shape=shapes, mode=st.sampled_from(MODES), seed=st.integers(0, 10 ** 6), rank=st.integers(1, 6))
 def test_output_input_gradient_and_bias_gradient_do_not_depend_on_the_compression(shape, mode, seed, rank):
     rows, feats, out = shape
@@ -39,7 +39,7 @@ def test_output_input_gradient_and_bias_gradient_do_not_depend_on_the_compressio
     torch.testing.assert_close(db, g.sum(0), rtol=1e-5, atol=1e-6)
 
 
-@settings(max_examples=20, deadline=None)
+@settings(max_examples=20, deadline=None, derandomize=True)
 @given(shape=shapes, seed=st.integers(0, 10 ** 6))
 def test_weight_gradient_is_exact_when_nothing_is_discarded(shape, seed):
     """Either channel alone can carry everything: a basis of full width, or a residual budget of one."""
@@ -53,7 +53,7 @@ def test_weight_gradient_is_exact_when_nothing_is_discarded(shape, seed):
         torch.testing.assert_close(dw, dense, rtol=2e-3, atol=2e-3)
 
 
-@settings(max_examples=25, deadline=None)
+@settings(max_examples=25, deadline=None, derandomize=True)
 @given(shape=shapes, seed=st.integers(0, 10 ** 6), rank=st.integers(1, 4), budget=st.sampled_from([0.0, 0.05, 0.3]))
 def test_weight_gradient_error_obeys_the_bridge_bound(shape, seed, rank, budget):
     """``dW_c - dW = dY^T (X_hat - X)``, hence ``||dW_c - dW||_F <= ||dY||_2 ||X_hat - X||_F``.  ``||X_hat - X||_F`` is at most the
@@ -69,7 +69,7 @@ def test_weight_gradient_error_obeys_the_bridge_bound(shape, seed, rank, budget)
     assert (dw - g.t() @ x).norm() <= bound * (1 + 1e-4) + 1e-5
 
 
-@settings(max_examples=15, deadline=None)
+@settings(max_examples=15, deadline=None, derandomize=True)
 @given(shape=shapes, seed=st.integers(0, 10 ** 6))
 def test_more_residual_budget_never_hurts_the_weight_gradient_of_the_same_basis(shape, seed):
     rows, feats, out = shape

@@ -13,7 +13,7 @@ from stacr_b200.layers import STACRFunction
 from stacr_b200.quant import QuantizedValues, pack_int4, quantize_values, unpack_int4
 
 
-@settings(max_examples=60, deadline=None)
+@settings(max_examples=60, deadline=None, derandomize=True)
 @given(rows=st.integers(1, 40), cols=st.integers(1, 300), frac=st.floats(0.0, 1.0), mode=st.sampled_from(["none", "csr", "delta"]),
        keep_order=st.booleans(), wide=st.booleans(), seed=st.integers(0, 10 ** 6))
 def test_index_codecs_are_lossless_for_any_subset(rows, cols, frac, mode, keep_order, wide, seed):
@@ -32,7 +32,7 @@ def test_index_codecs_are_lossless_for_any_subset(rows, cols, frac, mode, keep_o
         assert packed.memory_bytes() > 0
 
 
-@settings(max_examples=60, deadline=None)
+@settings(max_examples=60, deadline=None, derandomize=True)
 @given(n=st.integers(1, 500), bits=st.sampled_from([4, 8]), scale=st.floats(1e-6, 1e4), seed=st.integers(0, 10 ** 6))
 def test_quantiser_error_is_at_most_half_a_step_of_the_largest_value(n, bits, scale, seed):
     g = torch.Generator().manual_seed(seed)
@@ -46,7 +46,7 @@ def test_quantiser_error_is_at_most_half_a_step_of_the_largest_value(n, bits, sc
     assert torch.equal(quantize_values(torch.zeros(n), bits).dequantize(torch.float32), torch.zeros(n))
 
 
-@settings(max_examples=40, deadline=None)
+@settings(max_examples=40, deadline=None, derandomize=True)
 @given(n=st.integers(0, 257), seed=st.integers(0, 10 ** 6))
 def test_int4_packing_round_trips_every_length(n, seed):
     g = torch.Generator().manual_seed(seed)
@@ -67,7 +67,7 @@ def _saved_selection(x, q, budget, mode, chunk_rows=16, block=8, bits=0):
     return coeff, qs, idx.long(), QuantizedValues(data, scale, bits, idx.numel()).dequantize(x.dtype)
 
 
-@settings(max_examples=40, deadline=None)
+@settings(max_examples=40, deadline=None, derandomize=True)
 @given(rows=st.integers(2, 40), feats=st.sampled_from([8, 16, 40]), rank=st.integers(1, 4), budget=st.floats(0.01, 0.5), seed=st.integers(0, 10 ** 6))
 def test_global_topk_keeps_exactly_the_budget_and_nothing_larger_is_left_out(rows, feats, rank, budget, seed):
     torch.manual_seed(seed)
@@ -84,7 +84,7 @@ def test_global_topk_keeps_exactly_the_budget_and_nothing_larger_is_left_out(row
         assert float(left.max()) <= float(vals.abs().min()) + 1e-12
 
 
-@settings(max_examples=40, deadline=None)
+@settings(max_examples=40, deadline=None, derandomize=True)
 @given(rows=st.integers(2, 48), feats=st.sampled_from([8, 16, 40]), budget=st.floats(0.02, 0.4), chunk=st.sampled_from([4, 16, 64]),
        mode=st.sampled_from(["chunk_topk", "uniform", "block_sparse", "sampled"]), seed=st.integers(0, 10 ** 6))
 def test_every_selector_stores_true_residual_values_at_distinct_positions_within_budget(rows, feats, budget, chunk, mode, seed):
@@ -103,7 +103,7 @@ def test_every_selector_stores_true_residual_values_at_distinct_positions_within
     assert idx.numel() <= budget * total + slack
 
 
-@settings(max_examples=30, deadline=None)
+@settings(max_examples=30, deadline=None, derandomize=True)
 @given(rows=st.integers(4, 32), feats=st.sampled_from([8, 24]), out=st.integers(1, 6), bits=st.sampled_from([0, 4, 8]),
        mode=st.sampled_from(["chunk_topk", "global_topk", "none"]), seed=st.integers(0, 10 ** 6))
 def test_weight_gradient_error_is_bounded_by_what_was_discarded(rows, feats, out, bits, mode, seed):
